@@ -1,0 +1,148 @@
+/*
+ * nha_b200 — C ABI of the B200 (sm_100a) implementation of the NHA attention operator.
+ *
+ * One shared library, plain pointers and sizes, no torch types.  Every entry
+ * point returns an int status (NHA_OK == 0), never throws and never aborts;
+ * nha_status_string() names a status.  All pointers are DEVICE pointers unless
+ * stated otherwise; bf16 tensors are passed as `const void*`.  Entry points
+ * allocate nothing: workspaces are sized by the *_workspace_bytes helpers and
+ * passed in by the caller.  Launches go to the stream given (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream).
+ *
+ * Path names below are relative to the reference project (JusenD/NHA).
+ *
+ * Token layout: sequences are packed along the token axis, [Ttot, heads, dim]
+ * row-major, delimited by cu_seqlens[N+1] (int32, device).  A batch of B
+ * equal-length sequences [B, T, ...] is the same memory with N = B.
+ * HQ query heads share H kv heads group-major (kv head = q head / (HQ/H)).
+ */
+#ifndef NHA_B200_H
+#define NHA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  NHA_OK = 0,
+  NHA_ERR_BAD_ARG = 1,       /* null pointer, negative size, HQ % H != 0 ... */
+  NHA_ERR_UNSUPPORTED = 2,   /* head dim / slot count / window outside what the kernels cover */
+  NHA_ERR_SMEM = 3,          /* tile set does not fit the 227 KB of shared memory */
+  NHA_ERR_LAUNCH = 4,        /* cudaGetLastError() after a launch was not cudaSuccess */
+  NHA_ERR_WORKSPACE = 5      /* workspace pointer null or too small */
+};
+
+#define NHA_CHUNK 64         /* tokens per chunk of the chunked kernels */
+
+const char* nha_status_string(int status);
+/* last CUDA error text seen by this library on the calling thread ("" if none) */
+const char* nha_last_cuda_error(void);
+int nha_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused decode step.  Replaces fused_recurrent_nha_decode
+ * (nha_fla/ops/nha/fused_recurrent.py:431-584: the k-kernel :229-353 and v-kernel :356-428)
+ * and, with `win_logits` given, fused_recurrent_nha (nha_fla/ops/nha/fused_recurrent.py:588-682).
+ *
+ *   q        [B, HQ, K] bf16   raw query (slot logits; rotated in-kernel when cos/sin given)
+ *   sq       [B, HQ, K] bf16   pre-rotated query, or NULL
+ *   k, v, g  [B, H, K|V|M] bf16  the token leaving the window (enters the slot memory)
+ *   s        [B, H, M] bf16 or NULL (then s = 1 - exp(g) in fp32)
+ *   sw_k     [B, W, H, K] bf16 window keys, time ascending (raw when cos/sin given), or NULL
+ *   sw_v     [B, W, H, V] bf16 window values, or NULL
+ *   cos, sin [1|B, W, K] bf16 rotate-half tables for the W window positions (row W-1 = query),
+ *            row stride `cs_row`, batch stride `cs_batch` (0 = shared), or NULL
+ *   win_logits [B, HQ, W] bf16 caller-computed window logits (fused_recurrent_nha mode), or NULL
+ *   hk [B,H,K,M], hv [B,H,M,V] fp32: state, read as the initial state (or taken as zero when
+ *            `zero_state` != 0) and OVERWRITTEN IN PLACE with the updated state
+ *   o        [B, HQ, V] bf16   output (slot readout + window readout; slot readout only in
+ *            win_logits mode)
+ *   win_prob [B, HQ, W] fp32   window probabilities of the joint softmax, or NULL
+ */
+int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
+                    const void* sw_k, const void* sw_v, const void* cos, const void* sin, int64_t cs_batch,
+                    int64_t cs_row, const void* win_logits, float* hk, float* hv, int zero_state, void* o,
+                    float* win_prob, int B, int HQ, int H, int K, int V, int M, int W, float scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Chunked prefill / training.  One descriptor serves the state pass, the output pass and the
+ * backward.  Replaces chunk_nha (nha_fla/ops/nha/chunk.py:568-690; autograd node :352-564,
+ * GSA half nha_fla/ops/nha/chunk_gsa.py:16-122, third-party flash-attn varlen fwd/bwd call
+ * sites chunk.py:241-270,333-344) and fused_chunk_nha_prefill
+ * (nha_fla/ops/nha/chunk_fused.py:291-380: state kernel :31-114, output kernel :117-283).
+ */
+typedef struct nha_chunk_desc {
+  /* inputs, bf16 */
+  const void* q_gsa;            /* [Ttot, HQ, K] un-rotated query (slot logits) */
+  const void* q_swa;            /* [Ttot, HQ, K] rotated query (window logits) */
+  const void* k_gsa;            /* [Ttot, H, K]  un-rotated key (slot memory) */
+  const void* k_swa;            /* [Ttot, H, K]  rotated key (window) */
+  const void* v;                /* [Ttot, H, V] */
+  const void* s;                /* [Ttot, H, M]  slot write weights */
+  const void* g;                /* [Ttot, H, M]  log forget gates (<= 0) */
+  const int32_t* cu_seqlens;    /* [N+1] */
+  const int32_t* window_left;   /* [N] per-sequence window (keys t-wl..t; <0 = unbounded) or NULL */
+  const int32_t* shift;         /* [N] per-sequence gsa_kv_shift or NULL */
+  const float* hk0;             /* [N, H, K, M] or NULL (zero) */
+  const float* hv0;             /* [N, H, M, V] or NULL (zero) */
+  /* forward outputs */
+  void* o;                      /* [Ttot, HQ, V] bf16 */
+  float* lse_swa;               /* [Ttot, HQ] */
+  float* lse_gsa;               /* [Ttot, HQ] */
+  float* hkt;                   /* [N, H, K, M] or NULL */
+  float* hvt;                   /* [N, H, M, V] or NULL */
+  /* chunk-start states written by the state pass, read by the output pass and the backward */
+  void* hk_chunks;              /* [NC, H, K, M] bf16 */
+  void* hv_chunks;              /* [NC, H, M, V] bf16 */
+  /* plan (int32 workspace written by nha_chunk_plan): [0..N] first chunk of each sequence,
+     then [N+1 .. N+1+NC) the sequence of each chunk; NC = nha_chunk_count_bound(Ttot, N) */
+  int32_t* plan;
+  void* workspace;              /* scratch, see nha_chunk_*_workspace_bytes */
+  size_t workspace_bytes;
+  /* backward inputs */
+  const void* d_o;              /* [Ttot, HQ, V] bf16 */
+  const float* d_lse_gsa;       /* [Ttot, HQ] or NULL */
+  const float* d_hkt;           /* [N, H, K, M] or NULL */
+  const float* d_hvt;           /* [N, H, M, V] or NULL (both or neither) */
+  /* backward outputs, bf16 like the inputs */
+  void* dq_gsa; void* dq_swa; void* dk_gsa; void* dk_swa; void* dv; void* ds; void* dg;
+  float* dhk0;                  /* [N, H, K, M] or NULL */
+  float* dhv0;                  /* [N, H, M, V] or NULL */
+  /* sizes */
+  int32_t Ttot, N, HQ, H, K, V, M;
+  int32_t max_seqlen;           /* longest sequence (grid sizing of the state pass) */
+  int32_t window_left_all;      /* used when window_left == NULL */
+  int32_t shift_all;            /* used when shift == NULL */
+  int32_t seg_chunks;           /* chunks per state-pass segment; 0 = library default */
+  float scale;
+} nha_chunk_desc;
+
+/* sizeof(nha_chunk_desc) as compiled into the library, for bindings that mirror the struct */
+int64_t nha_chunk_desc_size(void);
+/* upper bound of the number of chunks of N packed sequences holding Ttot tokens */
+int64_t nha_chunk_count_bound(int64_t Ttot, int64_t N);
+/* number of int32 of desc->plan */
+int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N);
+/* bytes of desc->workspace for the forward (state pass + output pass) / the backward */
+int64_t nha_chunk_fwd_workspace_bytes(const nha_chunk_desc* d);
+int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d);
+
+/* fills desc->plan from cu_seqlens on the device (no host synchronisation) */
+int nha_chunk_plan(const nha_chunk_desc* d, void* stream);
+/* state pass: chunk-start states hk_chunks/hv_chunks (+ final states hkt/hvt when non-NULL) */
+int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream);
+/* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
+int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
+/* plan + state pass + output pass */
+int nha_chunk_fwd(const nha_chunk_desc* d, void* stream);
+/* backward: needs the forward's o, lse_swa, lse_gsa, hk_chunks, hv_chunks, plan (and hkt/hvt
+   when d_hkt/d_hvt are given); writes dq_*, dk_*, dv, ds, dg (+ dhk0/dhv0 when non-NULL) */
+int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NHA_B200_H */

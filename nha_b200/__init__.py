@@ -1,0 +1,11 @@
+"""nha_b200: the NHA attention operator on hand-written CUDA kernels for B200 (sm_100a).
+
+The public names and signatures are those of ``nha_fla.ops.nha`` so that the
+reference's layers and model classes can call them unchanged.
+"""
+from .chunk import chunk_nha
+from .chunk_fused import fused_chunk_nha_prefill
+from .fused_recurrent import fused_recurrent_nha, fused_recurrent_nha_decode
+
+__all__ = ['chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode']
+__version__ = '0.1.0'

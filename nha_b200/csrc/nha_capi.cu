@@ -1,0 +1,40 @@
+// Status plumbing and size helpers of the C ABI.
+#include <string.h>
+
+#include "nha_common.cuh"
+
+namespace nha {
+
+static thread_local char g_last_error[256] = "";
+
+int record_cuda_error(cudaError_t e) {
+  strncpy(g_last_error, cudaGetErrorString(e), sizeof(g_last_error) - 1);
+  g_last_error[sizeof(g_last_error) - 1] = 0;
+  return NHA_ERR_LAUNCH;
+}
+
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return record_cuda_error(e);
+  return NHA_OK;
+}
+
+}  // namespace nha
+
+extern "C" const char* nha_status_string(int status) {
+  switch (status) {
+    case NHA_OK: return "ok";
+    case NHA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or HQ not a multiple of H)";
+    case NHA_ERR_UNSUPPORTED: return "unsupported head dim / slot count / group size";
+    case NHA_ERR_SMEM: return "tile set does not fit in shared memory";
+    case NHA_ERR_LAUNCH: return "CUDA launch failed (see nha_last_cuda_error)";
+    case NHA_ERR_WORKSPACE: return "workspace missing or too small";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* nha_last_cuda_error(void) { return nha::g_last_error; }
+
+extern "C" int nha_abi_version(void) { return 1; }
+
+extern "C" int64_t nha_chunk_desc_size(void) { return (int64_t)sizeof(nha_chunk_desc); }

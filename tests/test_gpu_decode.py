@@ -1,0 +1,127 @@
+"""GPU: fused decode step / recurrent step through the C ABI against the oracle and the fixtures."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nha_oracle as orc
+from tests import inputs as gen
+from tests.gpu_util import TOL_OUT, assert_close, cuda
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), 'golden')
+MAN = json.load(open(os.path.join(GOLD, 'manifest.json')))
+
+# the reference's decode grid (scripts/verify_opt_parity.py:322-329), incl. the non-power-of-two M = 80
+GRID = [(NG, M, W, K, B) for NG in (1, 4, 8) for M in (16, 64, 80) for W in (32, 64) for K in (64, 128) for B in (1, 4)]
+
+
+def _seed(i):
+    return 2000 + i
+
+
+@pytest.mark.parametrize('idx', range(len(GRID)))
+def test_decode_grid(idx):
+    from nha_b200 import fused_recurrent_nha_decode
+    NG, M, W, K, B = GRID[idx]
+    d = gen.decode_inputs(_seed(idx), B, 2, NG, K, K, M, W)
+    ref_o, ref_hk, ref_hv, _, _ = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'],
+                                                  s=d['s'], cos=d['cos'], sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    c = cuda(d)
+    # in-kernel rotary, s recomputed from g in-kernel
+    ref2 = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'],
+                           cos=d['cos'], sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'],
+                                             cos=c['cos'], sin=c['sin'],
+                                             initial_state=(c['hk0'].clone(), c['hv0'].clone()),
+                                             output_final_state=True, scale=d['scale'])
+    assert_close(o, ref2[0], TOL_OUT, 'o (rotary)')
+    assert_close(hk, ref2[1], 1e-5, 'hkt (rotary)')
+    assert_close(hv, ref2[2], 1e-5, 'hvt (rotary)')
+    # pre-rotated query/keys and caller-supplied s
+    hk0, hv0 = c['hk0'].clone(), c['hv0'].clone()
+    o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], sq=c['sq'], k=c['k'], v=c['v'], g=c['g'], s=c['s'],
+                                             sw_k=c['sk'], sw_v=c['vw'], initial_state=(hk0, hv0),
+                                             output_final_state=True, scale=d['scale'])
+    assert_close(o, ref_o, TOL_OUT, 'o (eager)')
+    assert_close(hk, ref_hk, 1e-5, 'hkt (eager)')
+    assert_close(hv, ref_hv, 1e-5, 'hvt (eager)')
+    assert hk.data_ptr() == hk0.data_ptr(), 'state must be updated in place'
+    # no final state requested: the caller's state must stay untouched
+    keep = c['hk0'].clone()
+    o2, st = fused_recurrent_nha_decode(q=c['q'], sq=c['sq'], k=c['k'], v=c['v'], g=c['g'], s=c['s'], sw_k=c['sk'],
+                                        sw_v=c['vw'], initial_state=(keep, c['hv0'].clone()), scale=d['scale'])
+    assert st == (None, None) and torch.equal(keep, c['hk0'])
+    assert torch.equal(o2, o)
+
+
+@pytest.mark.parametrize('idx', range(0, len(GRID), 3))
+def test_recurrent_grid(idx):
+    from nha_b200 import fused_recurrent_nha
+    NG, M, W, K, B = GRID[idx]
+    d = gen.recurrent_inputs(1000 + idx, B, 2, NG, K, K, M, W)
+    ref_o, ref_pw, ref_hk, ref_hv = orc.recurrent_step(d['q'], d['k'], d['v'], d['sliding_window'], d['s'], d['g'],
+                                                       d['scale'], d['hk0'], d['hv0'])
+    c = cuda(d)
+    o, pw, (hk, hv) = fused_recurrent_nha(c['q'], c['k'], c['v'], c['sliding_window'], c['s'], c['g'],
+                                          scale=d['scale'], initial_state=(c['hk0'].clone(), c['hv0'].clone()),
+                                          output_final_state=True)
+    assert_close(o, ref_o, TOL_OUT, 'o')
+    assert_close(pw, ref_pw, TOL_OUT, 'swa_score')
+    assert_close(hk, ref_hk, 1e-5, 'hkt')
+    assert_close(hv, ref_hv, 1e-5, 'hvt')
+
+
+@pytest.mark.parametrize('case', sorted(MAN['decode']))
+def test_decode_against_reference_fixture(case):
+    from nha_b200 import fused_recurrent_nha_decode
+    c = MAN['decode'][case]
+    z = np.load(os.path.join(GOLD, 'decode.npz'))
+    d = gen.decode_inputs(c['seed'], c['B'], c['H'], c['NG'], c['K'], c['V'], c['M'], c['W'])
+    assert gen.digest(d) == c['digest']
+    g = cuda(d)
+    o, (hk, hv) = fused_recurrent_nha_decode(q=g['q'], k=g['k'], v=g['v'], g=g['g'], s=g['s'], sw_k=g['sw_k_raw'],
+                                             sw_v=g['vw'], cos=g['cos'], sin=g['sin'],
+                                             initial_state=(g['hk0'].clone(), g['hv0'].clone()),
+                                             output_final_state=True, scale=d['scale'])
+    assert_close(o, torch.from_numpy(z[f'{case}/o']), TOL_OUT, 'o')
+    assert_close(hk, torch.from_numpy(z[f'{case}/hkt']), 1e-5, 'hkt')
+    assert_close(hv, torch.from_numpy(z[f'{case}/hvt']), 1e-5, 'hvt')
+
+
+def test_decode_edge_cases():
+    """Zero state, a window shorter than 16 keys, a dummy popped entry, T != 1 and autograd misuse."""
+    from nha_b200 import fused_recurrent_nha, fused_recurrent_nha_decode
+    d = gen.decode_inputs(77, 2, 2, 4, 64, 64, 32, 5)
+    d['k'].zero_(); d['v'].zero_(); d['g'].zero_()
+    ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'], sin=d['sin'])
+    c = cuda(d)
+    o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'],
+                                             cos=c['cos'], sin=c['sin'], initial_state=(None, None),
+                                             output_final_state=True)
+    assert_close(o, ref[0], TOL_OUT, 'o')
+    assert float(hk.abs().max()) == 0.0 and float(hv.abs().max()) == 0.0
+    with pytest.raises(ValueError):
+        fused_recurrent_nha(c['q'].repeat(1, 2, 1, 1), c['k'], c['v'], c['sliding_window'], c['s'], c['g'])
+    with pytest.raises(AssertionError):
+        fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'])
+
+
+def test_decode_headline_shape():
+    """One layer of the batched-decode workload: HQ=32, H=4, D=128, M=64, W=512, rotary in-kernel."""
+    from nha_b200 import fused_recurrent_nha_decode
+    torch.manual_seed(5)
+    B, H, NG, K, M, W = 3, 4, 8, 128, 64, 512
+    d = gen.decode_inputs(5, B, H, NG, K, K, M, W)
+    d['cos'], d['sin'] = gen.rope_tables(W, K, first_pos=32768 - W + 1)
+    ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'],
+                          sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    c = cuda(d)
+    o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'],
+                                             cos=c['cos'], sin=c['sin'], initial_state=(c['hk0'], c['hv0']),
+                                             output_final_state=True)
+    assert_close(o, ref[0], TOL_OUT, 'o')
+    assert_close(hk, ref[1], 1e-5, 'hkt')
+    assert_close(hv, ref[2], 1e-5, 'hvt')

@@ -1,0 +1,125 @@
+"""CPU: the oracle against the fixtures generated from the reference's own naive functions."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nha_oracle as orc
+from tests import inputs as gen
+
+GOLD = os.path.join(os.path.dirname(__file__), 'golden')
+MAN = json.load(open(os.path.join(GOLD, 'manifest.json')))
+TOL = 1e-6   # fixtures are stored in fp32; the oracle is fp64
+
+
+def _npz(name):
+    return np.load(os.path.join(GOLD, name))
+
+
+def _t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+@pytest.mark.parametrize('case', sorted(MAN['decode']))
+def test_decode_matches_reference_fixture(case):
+    c = MAN['decode'][case]
+    z = _npz('decode.npz')
+    d = gen.decode_inputs(c['seed'], c['B'], c['H'], c['NG'], c['K'], c['V'], c['M'], c['W'])
+    assert gen.digest(d) == c['digest'], 'input generator drifted from the one that made the fixture'
+    o, hk, hv, ps, pw = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'],
+                                        s=d['s'], cos=d['cos'], sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    for got, key in ((o, 'o'), (hk, 'hkt'), (hv, 'hvt'), (ps, 'qv'), (pw, 'swp')):
+        assert orc.rel_l2(got, _t(z[f'{case}/{key}'])) < TOL, key
+
+
+@pytest.mark.parametrize('case', sorted(MAN['recurrent']))
+def test_recurrent_matches_reference_fixture(case):
+    c = MAN['recurrent'][case]
+    z = _npz('recurrent.npz')
+    d = gen.recurrent_inputs(c['seed'], c['B'], c['H'], c['NG'], c['K'], c['V'], c['M'], c['W'])
+    assert gen.digest(d) == c['digest']
+    o, pw, hk, hv = orc.recurrent_step(d['q'], d['k'], d['v'], d['sliding_window'], d['s'], d['g'], d['scale'],
+                                       d['hk0'], d['hv0'])
+    for got, key in ((o, 'o'), (pw, 'swa_score'), (hk, 'hkt'), (hv, 'hvt')):
+        assert orc.rel_l2(got, _t(z[f'{case}/{key}'])) < TOL, key
+
+
+@pytest.mark.parametrize('case', sorted(MAN['prefill']))
+def test_prefill_matches_reference_fixture(case):
+    c = MAN['prefill'][case]
+    z = _npz('prefill.npz')
+    d = gen.prefill_inputs(c['seed'], c['B'], c['H'], c['NG'], c['K'], c['V'], c['M'], c['W'], c['T'], c['with_state'])
+    assert gen.digest(d) == c['digest']
+    o, hk, hv = orc.prefill(d['q'], d['k'], d['v'], d['rotary_q'], d['rotary_k'], d['s'], d['g'], c['W'], d['scale'],
+                            d.get('hk0'), d.get('hv0'))
+    for got, key in ((o, 'o'), (hk, 'hkt'), (hv, 'hvt')):
+        assert orc.rel_l2(got, _t(z[f'{case}/{key}'])) < TOL, key
+
+
+def training_case(name):
+    """Inputs, oracle outputs and oracle gradients of a stored training case."""
+    c = MAN['training'][name]
+    B, T, H, K, V, M = c['B'], c['T'], c['H'], c['K'], c['V'], c['M']
+    d = gen.training_inputs(c['seed'], B, T, H, K, V, M)
+    assert gen.digest(d) == c['digest']
+    cu = c['cu'] if c['cu'] is not None else [i * T for i in range(B + 1)]
+    N = len(cu) - 1
+    hk0 = hv0 = None
+    if c['with_state']:
+        torch.manual_seed(c['seed'] + 50000)
+        hk0 = (torch.randn(N, H, K, M) * 0.5).float()
+        hv0 = (torch.randn(N, H, M, V) * 0.5).float()
+    torch.manual_seed(c['seed'] + 70000)
+    dlse = (torch.randn(B * T, H) * 0.1).double()
+    return c, d, cu, hk0, hv0, dlse
+
+
+@pytest.mark.parametrize('case', sorted(MAN['training']))
+def test_training_matches_reference_replay_fixture(case):
+    c, d, cu, hk0, hv0, dlse = training_case(case)
+    z = _npz('training.npz')
+    B, T = c['B'], c['T']
+    names = ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v', 's', 'g')
+    xs = {n: d[n].reshape(B * T, *d[n].shape[2:]).double().requires_grad_(True) for n in names}
+    st = []
+    if hk0 is not None:
+        st = [hk0.double().requires_grad_(True), hv0.double().requires_grad_(True)]
+    o, ls, lg, hk, hv = orc.nha_varlen(xs['q_gsa'], xs['q_swa'], xs['k_gsa'], xs['k_swa'], xs['v'], xs['s'], xs['g'],
+                                       cu, c['K'] ** -0.5, c['window_left'], c['shift'], *(st or [None, None]))
+    do = d['do'].reshape(B * T, *d['do'].shape[2:]).double()
+    ((o * do).sum() + (lg * dlse).sum()).backward()
+    for got, key in ((o, 'o'), (ls, 'lse_swa'), (lg, 'lse_gsa'), (hk, 'hkt'), (hv, 'hvt')):
+        assert orc.rel_l2(got, _t(z[f'{case}/{key}'])) < TOL, key
+    for n in names:
+        assert orc.rel_l2(xs[n].grad, _t(z[f'{case}/grad_{n}'])) < TOL, n
+    if st:
+        assert orc.rel_l2(st[0].grad, _t(z[f'{case}/grad_hk0'])) < TOL
+        assert orc.rel_l2(st[1].grad, _t(z[f'{case}/grad_hv0'])) < TOL
+
+
+def test_lse_merge_equals_joint_softmax():
+    """The reference merges two branch outputs by log-sum-exp (nha_fla/ops/nha/chunk.py:458-470);
+    the oracle takes one softmax over the concatenation.  Both must agree."""
+    torch.manual_seed(1)
+    T, H, K, V, M, W = 40, 2, 16, 16, 8, 6
+    dd = torch.float64
+    q, qs, k, ks = (torch.randn(T, H, K, dtype=dd) for _ in range(4))
+    v = torch.randn(T, H, V, dtype=dd)
+    g = torch.nn.functional.logsigmoid(torch.randn(T, H, M, dtype=dd))
+    s = 1 - g.exp()
+    o, ls, lg, hk, hv = orc.nha_sequence(q, qs, k, ks, v, s, g, 0.25, W, 0)
+    # slot-only and window-only outputs recomputed separately
+    hkc = torch.zeros(H, K, M, dtype=dd); hvc = torch.zeros(H, M, V, dtype=dd)
+    for t in range(T):
+        hkc, hvc = orc.gsa_step(hkc, hvc, k[t], v[t], s[t], g[t])
+        ok = torch.einsum('hk,hkm->hm', q[t] * 0.25, hkc)
+        og = torch.einsum('hm,hmv->hv', torch.softmax(ok, -1), hvc)
+        lo = max(0, t - W)
+        sw = torch.einsum('hk,whk->hw', qs[t] * 0.25, ks[lo:t + 1])
+        osw = torch.einsum('hw,whv->hv', torch.softmax(sw, -1), v[lo:t + 1])
+        mx = torch.maximum(ls[t], lg[t])
+        ws, wg = (ls[t] - mx).exp(), (lg[t] - mx).exp()
+        merged = (ws[:, None] * osw + wg[:, None] * og) / (ws + wg)[:, None]
+        assert torch.allclose(merged, o[t], atol=1e-12)
