@@ -1,3 +1,875 @@
+// Backward of the chunked NHA operator (sm_100a).
+//
+// With p = softmax([ok | sw]) recomputed from the saved log-sum-exps, dp = <do, values>,
+// delta = <do, o> and dz = p .* (dp - delta) (+ d_lse_gsa * softmax(ok) on the slot part):
+//   1. window rows    (chunk-parallel)  dq_swa = scale * dz_win k_swa            (+ delta, joint LSE)
+//   2. window columns (chunk-parallel)  dk_swa = scale * dz_win^T q_swa, dv_win = p_win^T do
+//   3. slot pass      (chunk-parallel)  dq_gsa and the parts of dk', dv', ds' that stay inside a chunk,
+//                                       dgA = ok .* dz + p .* dp, and the decayed dz / p the march needs
+//   4. reverse march  (per sequence and kv head, last chunk first) carries the gradients DK, DV of
+//      the slot memory across chunks, adds the inter-chunk parts of dk', dv', ds', turns
+//      dgA - s' .* ds' into dg by a reverse cumulative sum, undoes the shift, writes the results.
+// Primes are the inputs shifted right by gsa_kv_shift inside their sequence.
+//
+// Replaces ChunkNativeHybridAttentionFunction.backward (nha_fla/ops/nha/chunk.py:491-564): the
+// flash-attn varlen backward called with the merged output and the joint LSE (:500-512), fla's
+// chunk_gsa backward with the folded d_lse (nha_fla/ops/nha/chunk_gsa.py:52-122) and the shift
+// adjoints (chunk.py:80-126).  A gradient on lse_swa is ignored, as there (:491-512).
 #include "nha_common.cuh"
-extern "C" int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d) { return 0; }
-extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) { return NHA_ERR_UNSUPPORTED; }
+
+namespace nha {
+
+constexpr int kBwThreads = 256;
+constexpr int kBwWarps = kBwThreads / 32;
+
+__host__ __device__ inline int bup128(int x) { return (x + 127) & ~127; }
+__device__ __forceinline__ int sb_row0b(int I) { return 8 * I * (I + 1); }
+__device__ __forceinline__ float block_refb(const float* G, int ldg, int I, int m) {
+  const float gn = I > 0 ? G[(16 * I - 1) * ldg + m] : 0.f;
+  return 0.5f * (gn + G[(16 * I + 15) * ldg + m]);
+}
+
+struct BwdWs {
+  float* delta;   // [Ttot, HQ]      <do, o>
+  float* lj;      // [Ttot, HQ]      joint log-sum-exp
+  float* dvacc;   // [Ttot, H, V]    window part of dv
+  float* dkp;     // [Ttot, H, K]    intra-chunk part of dk' (row = shifted position)
+  float* dvp;     // [Ttot, H, V]    intra-chunk part of dv'
+  float* dsp;     // [Ttot, H, M]    intra-chunk part of ds'
+  float* dga;     // [Ttot, H, M]    ok .* dz + p .* dp summed over the group
+  bf16* dzg;      // [Ttot, HQ, M]   scale * dz_slot .* exp(G)
+  bf16* pgq;      // [Ttot, HQ, M]   p_slot .* exp(G)
+};
+
+__host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* base) {
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = (off + bytes + 255) & ~(int64_t)255; return o; };
+  const int64_t T = d->Ttot;
+  const int64_t o_delta = take(T * d->HQ * 4), o_lj = take(T * d->HQ * 4), o_dvacc = take(T * d->H * d->V * 4);
+  const int64_t o_dkp = take(T * d->H * d->K * 4), o_dvp = take(T * d->H * d->V * 4);
+  const int64_t o_dsp = take(T * d->H * d->M * 4), o_dga = take(T * d->H * d->M * 4);
+  const int64_t o_dzg = take(T * d->HQ * d->M * 2), o_pgq = take(T * d->HQ * d->M * 2);
+  if (w && base) {
+    char* b = (char*)base;
+    w->delta = (float*)(b + o_delta); w->lj = (float*)(b + o_lj); w->dvacc = (float*)(b + o_dvacc);
+    w->dkp = (float*)(b + o_dkp); w->dvp = (float*)(b + o_dvp); w->dsp = (float*)(b + o_dsp);
+    w->dga = (float*)(b + o_dga); w->dzg = (bf16*)(b + o_dzg); w->pgq = (bf16*)(b + o_pgq);
+  }
+  return off;
+}
+
+struct ChunkCtx {
+  int n, ci, t0, len, c0, wl, shift;
+};
+
+__device__ __forceinline__ bool chunk_ctx(const nha_chunk_desc& d, int cg, ChunkCtx& c) {
+  c.n = d.plan[d.N + 1 + cg];
+  if (c.n < 0) return false;
+  c.ci = cg - d.plan[c.n];
+  c.t0 = d.cu_seqlens[c.n];
+  c.len = d.cu_seqlens[c.n + 1] - c.t0;
+  c.c0 = c.ci * kChunk;
+  c.wl = seq_window(d, c.n);
+  c.shift = seq_shift(d, c.n);
+  return true;
+}
+
+// ================================================================================================
+// 1. window rows: delta, joint LSE, dq_swa
+// ================================================================================================
+struct WRowLayout { int qb, dob, wt, SA, DP, PB, DQ, rows, total; };
+__host__ __device__ inline WRowLayout wrow_layout(int K, int V) {
+  WRowLayout L; int off = 0;
+  const int KV = K > V ? K : V;
+  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.wt = off; off = bup128(off + kChunk * (KV + 8) * 2);
+  L.SA = off; off = bup128(off + kChunk * (kChunk + 4) * 4);
+  L.DP = off; off = bup128(off + kChunk * (kChunk + 4) * 4);
+  L.PB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.DQ = off; off = bup128(off + kChunk * (K + 4) * 4);
+  L.rows = off; off = bup128(off + 2 * kChunk * 4);
+  L.total = off;
+  return L;
+}
+
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const nha_chunk_desc d, const BwdWs w) {
+  ChunkCtx c;
+  if (!chunk_ctx(d, blockIdx.x, c)) return;
+  const int K = d.K, V = d.V, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const WRowLayout L = wrow_layout(K, V);
+  const int KV = K > V ? K : V;
+  const int ldk = K + 8, ldv = V + 8, ldw = KV + 8, lds = kChunk + 4, ldp = kChunk + 8, ldq = K + 4;
+  bf16* qb = (bf16*)(smem + L.qb);
+  bf16* dob = (bf16*)(smem + L.dob);
+  bf16* wt = (bf16*)(smem + L.wt);
+  float* SA = (float*)(smem + L.SA);
+  float* DP = (float*)(smem + L.DP);
+  bf16* PB = (bf16*)(smem + L.PB);
+  float* DQ = (float*)(smem + L.DQ);
+  float* row_L = (float*)(smem + L.rows);
+  float* row_d = row_L + kChunk;
+  const int jt_hi = c.ci;
+  const int jt_lo = c.wl < 0 ? 0 : max(0, c.c0 - c.wl) / kChunk;
+  const int rq = tid >> 2, sub = tid & 3;
+
+  for (int qh = 0; qh < NG; ++qh) {
+    const int hq = h * NG + qh;
+    __syncthreads();
+    load_tile_bf16(qb, ldk, (const bf16*)d.q_swa + ((size_t)c.t0 * HQ + hq) * K, (int64_t)HQ * K, c.c0, 0, c.len, kChunk,
+                   K, tid, kBwThreads);
+    load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)c.t0 * HQ + hq) * V, (int64_t)HQ * V, c.c0, 0, c.len, kChunk, V,
+                   tid, kBwThreads);
+    // delta = <do, o>, joint LSE
+    {
+      const int pos = c.c0 + rq;
+      float acc = 0.f;
+      if (pos < c.len) {
+        const bf16* orow = (const bf16*)d.o + ((size_t)(c.t0 + pos) * HQ + hq) * V;
+        const bf16* grow = (const bf16*)d.d_o + ((size_t)(c.t0 + pos) * HQ + hq) * V;
+        for (int v8 = sub; v8 < V / 8; v8 += 4) {
+          float a[8], b[8];
+          unpack8(*reinterpret_cast<const uint4*>(orow + 8 * v8), a);
+          unpack8(*reinterpret_cast<const uint4*>(grow + 8 * v8), b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc += a[e] * b[e];
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (sub == 0) {
+        float Lj = 0.f;
+        if (pos < c.len) {
+          const float a = d.lse_swa[(size_t)(c.t0 + pos) * HQ + hq], b = d.lse_gsa[(size_t)(c.t0 + pos) * HQ + hq];
+          const float mx = fmaxf(a, b);
+          Lj = mx + __logf(__expf(a - mx) + __expf(b - mx));
+          w.delta[(size_t)(c.t0 + pos) * HQ + hq] = acc;
+          w.lj[(size_t)(c.t0 + pos) * HQ + hq] = Lj;
+        }
+        row_L[rq] = Lj;
+        row_d[rq] = acc;
+      }
+    }
+    for (int i = tid; i < kChunk * ldq; i += kBwThreads) DQ[i] = 0.f;
+    for (int jt = jt_lo; jt <= jt_hi; ++jt) {
+      __syncthreads();
+      load_tile_bf16(wt, ldw, (const bf16*)d.v + ((size_t)c.t0 * H + h) * V, (int64_t)H * V, jt * kChunk, 0, c.len, kChunk,
+                     V, tid, kBwThreads);
+      __syncthreads();
+      tile_gemm<true, false, false>(DP, lds, dob, ldv, wt, ldw, 4, 4, V / 16, warp, kBwWarps);   // do v^T
+      __syncthreads();
+      load_tile_bf16(wt, ldw, (const bf16*)d.k_swa + ((size_t)c.t0 * H + h) * K, (int64_t)H * K, jt * kChunk, 0, c.len,
+                     kChunk, K, tid, kBwThreads);
+      __syncthreads();
+      tile_gemm<true, false, false>(SA, lds, qb, ldk, wt, ldw, 4, 4, K / 16, warp, kBwWarps);    // q k^T
+      __syncthreads();
+      for (int i = tid; i < kChunk * kChunk; i += kBwThreads) {
+        const int r = i >> 6, cc = i & 63;
+        const int key = jt * kChunk + cc, pq = c.c0 + r;
+        const bool ok = key <= pq && (c.wl < 0 || key >= pq - c.wl) && pq < c.len;
+        float dz = 0.f;
+        if (ok) dz = __expf(SA[r * lds + cc] * d.scale - row_L[r]) * (DP[r * lds + cc] - row_d[r]) * d.scale;
+        PB[r * ldp + cc] = f2bf(dz);
+      }
+      __syncthreads();
+      tile_gemm<true, true, true>(DQ, ldq, PB, ldp, wt, ldw, 4, K / 16, 4, warp, kBwWarps);      // dq += dz k
+    }
+    __syncthreads();
+    for (int i = tid; i < kChunk * (K / 8); i += kBwThreads) {
+      const int r = i / (K / 8), c8 = i - r * (K / 8);
+      const int pq = c.c0 + r;
+      if (pq < c.len)
+        *reinterpret_cast<uint4*>((bf16*)d.dq_swa + ((size_t)(c.t0 + pq) * HQ + hq) * K + 8 * c8) = pack8(DQ + r * ldq + 8 * c8);
+    }
+  }
+}
+
+// ================================================================================================
+// 2. window columns: dk_swa, window part of dv; one CTA per (key chunk, kv head)
+// ================================================================================================
+struct WColLayout { int kt, vt, qb, dob, SA, DP, PB, ZB, DK, DV, rows, total; };
+__host__ __device__ inline WColLayout wcol_layout(int K, int V) {
+  WColLayout L; int off = 0;
+  L.kt = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.vt = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.SA = off; off = bup128(off + kChunk * (kChunk + 4) * 4);
+  L.DP = off; off = bup128(off + kChunk * (kChunk + 4) * 4);
+  L.PB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.ZB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.DK = off; off = bup128(off + kChunk * (K + 4) * 4);
+  L.DV = off; off = bup128(off + kChunk * (V + 4) * 4);
+  L.rows = off; off = bup128(off + 2 * kChunk * 4);
+  L.total = off;
+  return L;
+}
+
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_window_cols_kernel(const nha_chunk_desc d, const BwdWs w) {
+  ChunkCtx c;
+  if (!chunk_ctx(d, blockIdx.x, c)) return;
+  const int K = d.K, V = d.V, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const WColLayout L = wcol_layout(K, V);
+  const int ldk = K + 8, ldv = V + 8, lds = kChunk + 4, ldp = kChunk + 8, lddk = K + 4, lddv = V + 4;
+  bf16* kt = (bf16*)(smem + L.kt);
+  bf16* vt = (bf16*)(smem + L.vt);
+  bf16* qb = (bf16*)(smem + L.qb);
+  bf16* dob = (bf16*)(smem + L.dob);
+  float* SA = (float*)(smem + L.SA);
+  float* DP = (float*)(smem + L.DP);
+  bf16* PB = (bf16*)(smem + L.PB);
+  bf16* ZB = (bf16*)(smem + L.ZB);
+  float* DK = (float*)(smem + L.DK);
+  float* DV = (float*)(smem + L.DV);
+  float* row_L = (float*)(smem + L.rows);
+  float* row_d = row_L + kChunk;
+  const int nchunks = (c.len + kChunk - 1) / kChunk;
+  // query chunks that can see a key of this chunk
+  const int qi_lo = c.ci;
+  const int qi_hi = c.wl < 0 ? nchunks - 1 : min(nchunks - 1, (c.c0 + kChunk - 1 + c.wl) / kChunk);
+
+  load_tile_bf16(kt, ldk, (const bf16*)d.k_swa + ((size_t)c.t0 * H + h) * K, (int64_t)H * K, c.c0, 0, c.len, kChunk, K, tid,
+                 kBwThreads);
+  load_tile_bf16(vt, ldv, (const bf16*)d.v + ((size_t)c.t0 * H + h) * V, (int64_t)H * V, c.c0, 0, c.len, kChunk, V, tid,
+                 kBwThreads);
+  for (int i = tid; i < kChunk * lddk; i += kBwThreads) DK[i] = 0.f;
+  for (int i = tid; i < kChunk * lddv; i += kBwThreads) DV[i] = 0.f;
+  for (int qi = qi_lo; qi <= qi_hi; ++qi) {
+    const int q0 = qi * kChunk;
+    for (int qh = 0; qh < NG; ++qh) {
+      const int hq = h * NG + qh;
+      __syncthreads();
+      load_tile_bf16(qb, ldk, (const bf16*)d.q_swa + ((size_t)c.t0 * HQ + hq) * K, (int64_t)HQ * K, q0, 0, c.len, kChunk, K,
+                     tid, kBwThreads);
+      load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)c.t0 * HQ + hq) * V, (int64_t)HQ * V, q0, 0, c.len, kChunk, V,
+                     tid, kBwThreads);
+      if (tid < kChunk) {
+        const int pq = q0 + tid;
+        row_L[tid] = pq < c.len ? w.lj[(size_t)(c.t0 + pq) * HQ + hq] : 0.f;
+        row_d[tid] = pq < c.len ? w.delta[(size_t)(c.t0 + pq) * HQ + hq] : 0.f;
+      }
+      __syncthreads();
+      tile_gemm<true, false, false>(SA, lds, qb, ldk, kt, ldk, 4, 4, K / 16, warp, kBwWarps);    // q k^T
+      tile_gemm<true, false, false>(DP, lds, dob, ldv, vt, ldv, 4, 4, V / 16, warp, kBwWarps);   // do v^T
+      __syncthreads();
+      for (int i = tid; i < kChunk * kChunk; i += kBwThreads) {
+        const int r = i >> 6, cc = i & 63;
+        const int key = c.c0 + cc, pq = q0 + r;
+        const bool ok = key <= pq && (c.wl < 0 || key >= pq - c.wl) && pq < c.len;
+        float p = 0.f, dz = 0.f;
+        if (ok) {
+          p = __expf(SA[r * lds + cc] * d.scale - row_L[r]);
+          dz = p * (DP[r * lds + cc] - row_d[r]) * d.scale;
+        }
+        PB[r * ldp + cc] = f2bf(p);
+        ZB[r * ldp + cc] = f2bf(dz);
+      }
+      __syncthreads();
+      tile_gemm<false, true, true>(DV, lddv, PB, ldp, dob, ldv, 4, V / 16, 4, warp, kBwWarps);   // dv += p^T do
+      tile_gemm<false, true, true>(DK, lddk, ZB, ldp, qb, ldk, 4, K / 16, 4, warp, kBwWarps);    // dk += dz^T q
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < kChunk * (K / 8); i += kBwThreads) {
+    const int r = i / (K / 8), c8 = i - r * (K / 8);
+    const int pk = c.c0 + r;
+    if (pk < c.len)
+      *reinterpret_cast<uint4*>((bf16*)d.dk_swa + ((size_t)(c.t0 + pk) * H + h) * K + 8 * c8) = pack8(DK + r * lddk + 8 * c8);
+  }
+  for (int i = tid; i < kChunk * (V / 4); i += kBwThreads) {
+    const int r = i / (V / 4), c4 = i - r * (V / 4);
+    const int pk = c.c0 + r;
+    if (pk < c.len)
+      *reinterpret_cast<float4*>(w.dvacc + ((size_t)(c.t0 + pk) * H + h) * V + 4 * c4) =
+          *reinterpret_cast<const float4*>(DV + r * lddv + 4 * c4);
+  }
+}
+
+// ================================================================================================
+// 3. slot pass: everything of the slot branch that stays inside a chunk
+// ================================================================================================
+struct SlotLayout { int kp, vp, G, Hk, Hv, SB, qb, dob, OK, Y, SA, AB, AvB, dzg, dza, paq, DQ, rows, total; };
+__host__ __device__ inline SlotLayout slot_layout(int K, int V, int M) {
+  SlotLayout L; int off = 0;
+  const int KV = K > V ? K : V;
+  L.kp = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.vp = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.G = off; off = bup128(off + kChunk * (M + 4) * 4);
+  L.Hk = off; off = bup128(off + K * (M + 8) * 2);
+  L.Hv = off; off = bup128(off + M * (V + 8) * 2);
+  L.SB = off; off = bup128(off + 160 * (M + 8) * 2);
+  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.OK = off; off = bup128(off + kChunk * (M + 4) * 4);
+  L.Y = off; off = bup128(off + kChunk * (M + 4) * 4);
+  const int sa_cols = M > kChunk ? M : kChunk;
+  L.SA = off; off = bup128(off + kChunk * (sa_cols + 4) * 4);
+  L.AB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.AvB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.dzg = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.dza = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.paq = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.DQ = off; off = bup128(off + kChunk * (KV + 4) * 4);
+  L.rows = off; off = bup128(off + 4 * kChunk * 4);
+  L.total = off;
+  return L;
+}
+
+__device__ __forceinline__ void tril_bf16(bf16* AB, int ldab, const float* SA, int ldsa, int tid) {
+  for (int i = tid; i < kChunk * kChunk; i += kBwThreads) {
+    const int r = i >> 6, c = i & 63;
+    AB[r * ldab + c] = f2bf(c <= r ? SA[r * ldsa + c] : 0.f);
+  }
+}
+
+// X[16I.., :M] = AB[16I.., 0:16(I+1)] * SB_I
+__device__ __forceinline__ void rows_times_sb(float* X, int ldx, const bf16* AB, int ldab, const bf16* SB, int ldsb,
+                                              int M, int warp) {
+  using namespace nvcuda::wmma;
+  const int Nt = M / 16;
+  for (int t = warp; t < 4 * Nt; t += kBwWarps) {
+    const int I = t / Nt, nt = t % Nt;
+    fragment<accumulator, 16, 16, 16, float> acc;
+    fill_fragment(acc, 0.f);
+    for (int kt = 0; kt <= I; ++kt) {
+      fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
+      fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+      load_matrix_sync(fa, AB + 16 * I * ldab + 16 * kt, ldab);
+      load_matrix_sync(fb, SB + (sb_row0b(I) + 16 * kt) * ldsb + 16 * nt, ldsb);
+      mma_sync(acc, fa, fb, acc);
+    }
+    store_matrix_sync(X + 16 * I * ldx + 16 * nt, acc, ldx, mem_row_major);
+  }
+}
+
+// Y[16I.., 0:16(I+1)] = PA[16I.., :M] * SB_I^T
+__device__ __forceinline__ void rows_times_sbT(float* Y, int ldy, const bf16* PA, int ldpa, const bf16* SB, int ldsb,
+                                               int M, int warp) {
+  using namespace nvcuda::wmma;
+  for (int t = warp; t < 16; t += kBwWarps) {
+    const int I = t >> 2, nt = t & 3;
+    if (nt > I) continue;
+    fragment<accumulator, 16, 16, 16, float> acc;
+    fill_fragment(acc, 0.f);
+    for (int kt = 0; kt < M / 16; ++kt) {
+      fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
+      fragment<matrix_b, 16, 16, 16, bf16, col_major> fb;
+      load_matrix_sync(fa, PA + 16 * I * ldpa + 16 * kt, ldpa);
+      load_matrix_sync(fb, SB + (sb_row0b(I) + 16 * nt) * ldsb + 16 * kt, ldsb);
+      mma_sync(acc, fa, fb, acc);
+    }
+    store_matrix_sync(Y + 16 * I * ldy + 16 * nt, acc, ldy, mem_row_major);
+  }
+}
+
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chunk_desc d, const BwdWs w) {
+  using namespace nvcuda::wmma;
+  ChunkCtx c;
+  const int cg = blockIdx.x;
+  if (!chunk_ctx(d, cg, c)) return;
+  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const SlotLayout L = slot_layout(K, V, M);
+  const int KV = K > V ? K : V;
+  const int ldk = K + 8, ldv = V + 8, ldg = M + 4, ldhk = M + 8, ldhv = V + 8, ldsb = M + 8;
+  const int ldsa = (M > kChunk ? M : kChunk) + 4, ldab = kChunk + 8, ldp = M + 8, lddq = KV + 4;
+  bf16* kp = (bf16*)(smem + L.kp);
+  bf16* vp = (bf16*)(smem + L.vp);
+  float* G = (float*)(smem + L.G);
+  bf16* Hk = (bf16*)(smem + L.Hk);
+  bf16* Hv = (bf16*)(smem + L.Hv);
+  bf16* SB = (bf16*)(smem + L.SB);
+  bf16* qb = (bf16*)(smem + L.qb);
+  bf16* dob = (bf16*)(smem + L.dob);
+  float* OK = (float*)(smem + L.OK);
+  float* Y = (float*)(smem + L.Y);
+  float* SA = (float*)(smem + L.SA);
+  bf16* AB = (bf16*)(smem + L.AB);
+  bf16* AvB = (bf16*)(smem + L.AvB);
+  bf16* dzg = (bf16*)(smem + L.dzg);
+  bf16* dza = (bf16*)(smem + L.dza);
+  bf16* paq = (bf16*)(smem + L.paq);
+  float* DQ = (float*)(smem + L.DQ);
+  float* row_L = (float*)(smem + L.rows);
+  float* row_d = row_L + kChunk;
+  float* row_lg = row_d + kChunk;      // lse_gsa
+  float* row_dl = row_lg + kChunk;     // d_lse_gsa
+
+  // ---- kv-head data (same staging as the forward output pass) -------------------------------------
+  {
+    const int lo = 0, hi = c.len - c.shift;
+    load_tile_bf16(kp, ldk, (const bf16*)d.k_gsa + ((size_t)c.t0 * H + h) * K, (int64_t)H * K, c.c0 - c.shift, lo, hi,
+                   kChunk, K, tid, kBwThreads);
+    load_tile_bf16(vp, ldv, (const bf16*)d.v + ((size_t)c.t0 * H + h) * V, (int64_t)H * V, c.c0 - c.shift, lo, hi, kChunk,
+                   V, tid, kBwThreads);
+    load_tile_bf16(dzg, ldp, (const bf16*)d.s + ((size_t)c.t0 * H + h) * M, (int64_t)H * M, c.c0 - c.shift, lo, hi,
+                   kChunk, M, tid, kBwThreads);                                   // s' staged in dzg
+    const bf16* gg = (const bf16*)d.g + ((size_t)c.t0 * H + h) * M;
+    for (int i = tid; i < kChunk * (M / 8); i += kBwThreads) {
+      const int r = i / (M / 8), c8 = i - r * (M / 8);
+      const int j = c.c0 + r - c.shift;
+      float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (j >= lo && j < hi) unpack8(*reinterpret_cast<const uint4*>(gg + (size_t)j * H * M + 8 * c8), gv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
+    }
+    load_tile_bf16(Hk, ldhk, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * K * M, M, 0, 0, K, K, M, tid, kBwThreads);
+    load_tile_bf16(Hv, ldhv, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * V, V, 0, 0, M, M, V, tid, kBwThreads);
+  }
+  __syncthreads();
+  for (int m = tid; m < M; m += kBwThreads) {
+    float run = 0.f;
+#pragma unroll 16
+    for (int r = 0; r < kChunk; ++r) {
+      run += G[r * ldg + m];
+      G[r * ldg + m] = run;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 160 * M; i += kBwThreads) {
+    const int row = i / M, m = i - row * M;
+    const int I = row < 16 ? 0 : (row < 48 ? 1 : (row < 96 ? 2 : 3));
+    const int r = row - sb_row0b(I);
+    SB[row * ldsb + m] = f2bf(bf2f(dzg[r * ldp + m]) * clamp_exp(block_refb(G, ldg, I, m) - G[r * ldg + m]));
+  }
+  // register accumulators of dk' [64 x K] and dv' [64 x V]: warp -> row tile (warp & 3), col tiles (warp >> 2) + 2 i
+  constexpr int kMaxCT = 4;
+  const int mt = warp & 3;
+  const int CTK = K / 32, CTV = V / 32;
+  fragment<accumulator, 16, 16, 16, float> dkacc[kMaxCT], dvacc[kMaxCT];
+#pragma unroll
+  for (int i = 0; i < kMaxCT; ++i) { fill_fragment(dkacc[i], 0.f); fill_fragment(dvacc[i], 0.f); }
+  __syncthreads();
+
+  for (int qh = 0; qh < NG; ++qh) {
+    const int hq = h * NG + qh;
+    // ---- 1. tiles of this head ------------------------------------------------------------------
+    load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((size_t)c.t0 * HQ + hq) * K, (int64_t)HQ * K, c.c0, 0, c.len, kChunk, K,
+                   tid, kBwThreads);
+    load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)c.t0 * HQ + hq) * V, (int64_t)HQ * V, c.c0, 0, c.len, kChunk, V,
+                   tid, kBwThreads);
+    if (tid < kChunk) {
+      const int pq = c.c0 + tid;
+      const bool in = pq < c.len;
+      const size_t idx = (size_t)(c.t0 + pq) * HQ + hq;
+      row_L[tid] = in ? w.lj[idx] : 0.f;
+      row_d[tid] = in ? w.delta[idx] : 0.f;
+      row_lg[tid] = in ? d.lse_gsa[idx] : 0.f;
+      row_dl[tid] = (in && d.d_lse_gsa) ? d.d_lse_gsa[idx] : 0.f;
+    }
+    __syncthreads();
+    // ---- 2. slot logits OK (as in the forward) and Y0 = do Hv^T, A = q k'^T, Av = do v'^T ----------
+    tile_gemm<true, true, false>(OK, ldg, qb, ldk, Hk, ldhk, 4, M / 16, K / 16, warp, kBwWarps);
+    tile_gemm<true, false, false>(Y, ldg, dob, ldv, Hv, ldhv, 4, M / 16, V / 16, warp, kBwWarps);
+    tile_gemm<true, false, false, 0, 1>(SA, ldsa, qb, ldk, kp, ldk, 4, 4, K / 16, warp, kBwWarps);
+    __syncthreads();
+    tril_bf16(AB, ldab, SA, ldsa, tid);
+    __syncthreads();
+    tile_gemm<true, false, false, 0, 1>(SA, ldsa, dob, ldv, vp, ldv, 4, 4, V / 16, warp, kBwWarps);
+    __syncthreads();
+    tril_bf16(AvB, ldab, SA, ldsa, tid);
+    for (int i = tid; i < kChunk * M; i += kBwThreads) {
+      const int r = i / M, m = i - r * M;
+      const float eg = __expf(G[r * ldg + m]);
+      OK[r * ldg + m] *= d.scale * eg;
+      Y[r * ldg + m] *= eg;
+    }
+    __syncthreads();
+    rows_times_sb(SA, ldsa, AB, ldab, SB, ldsb, M, warp);
+    __syncthreads();
+    for (int i = tid; i < kChunk * M; i += kBwThreads) {
+      const int r = i / M, m = i - r * M;
+      OK[r * ldg + m] += d.scale * clamp_exp(G[r * ldg + m] - block_refb(G, ldg, r >> 4, m)) * SA[r * ldsa + m];
+    }
+    __syncthreads();
+    rows_times_sb(SA, ldsa, AvB, ldab, SB, ldsb, M, warp);
+    __syncthreads();
+    // ---- 3. dz on the slot part; decayed copies for the march; dgA ---------------------------------
+    for (int i = tid; i < kChunk * M; i += kBwThreads) {
+      const int r = i / M, m = i - r * M;
+      const int pq = c.c0 + r;
+      const float gl = G[r * ldg + m];
+      const float aI = clamp_exp(gl - block_refb(G, ldg, r >> 4, m));
+      const float ok = OK[r * ldg + m];
+      const float dps = Y[r * ldg + m] + aI * SA[r * ldsa + m];
+      float ps = 0.f, dz = 0.f;
+      if (pq < c.len) {
+        ps = __expf(ok - row_L[r]);
+        dz = ps * (dps - row_d[r]) + row_dl[r] * __expf(ok - row_lg[r]);
+      }
+      const float eg = __expf(gl);
+      const bf16 zg = f2bf(d.scale * dz * eg), pg = f2bf(ps * eg);
+      dzg[r * ldp + m] = zg;
+      dza[r * ldp + m] = f2bf(d.scale * dz * aI);
+      paq[r * ldp + m] = f2bf(ps * aI);
+      if (pq < c.len) {
+        const size_t gi = ((size_t)(c.t0 + pq) * HQ + hq) * M + m;
+        w.dzg[gi] = zg;
+        w.pgq[gi] = pg;
+        const size_t hi = ((size_t)(c.t0 + pq) * H + h) * M + m;
+        const float val = ok * dz + ps * dps;
+        w.dga[hi] = qh == 0 ? val : w.dga[hi] + val;
+      }
+    }
+    __syncthreads();
+    // ---- 4. intra-chunk ds': for every row block I, b_I .* (A_I^T dza_I + Av_I^T pa_I) ---------------
+    for (int I = 0; I < 4; ++I) {
+      const int Nt = M / 16;
+      for (int t = warp; t < (I + 1) * Nt; t += kBwWarps) {
+        const int it = t / Nt, nt = t % Nt;
+        fragment<accumulator, 16, 16, 16, float> acc;
+        fill_fragment(acc, 0.f);
+        fragment<matrix_a, 16, 16, 16, bf16, col_major> fa;
+        fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+        load_matrix_sync(fa, AB + 16 * I * ldab + 16 * it, ldab);
+        load_matrix_sync(fb, dza + 16 * I * ldp + 16 * nt, ldp);
+        mma_sync(acc, fa, fb, acc);
+        load_matrix_sync(fa, AvB + 16 * I * ldab + 16 * it, ldab);
+        load_matrix_sync(fb, paq + 16 * I * ldp + 16 * nt, ldp);
+        mma_sync(acc, fa, fb, acc);
+        store_matrix_sync(SA + 16 * it * ldsa + 16 * nt, acc, ldsa, mem_row_major);
+      }
+      __syncthreads();
+      for (int i = tid; i < 16 * (I + 1) * M; i += kBwThreads) {
+        const int r = i / M, m = i - r * M;
+        const int p = c.c0 + r;
+        if (p < c.len) {
+          const float bI = clamp_exp(block_refb(G, ldg, I, m) - G[r * ldg + m]);
+          const size_t hi = ((size_t)(c.t0 + p) * H + h) * M + m;
+          const float val = bI * SA[r * ldsa + m];
+          w.dsp[hi] = (qh == 0 && I == 0) ? val : ((qh == 0 && r >= 16 * I) ? val : w.dsp[hi] + val);
+        }
+      }
+      __syncthreads();
+    }
+    // ---- 5. E = tril(dza SB^T), Bv = tril(pa SB^T) (reuse AB / AvB), dq_gsa -----------------------------
+    rows_times_sbT(SA, ldsa, dza, ldp, SB, ldsb, M, warp);
+    __syncthreads();
+    tril_bf16(AB, ldab, SA, ldsa, tid);
+    __syncthreads();
+    rows_times_sbT(SA, ldsa, paq, ldp, SB, ldsb, M, warp);
+    tile_gemm<true, false, false>(DQ, lddq, dzg, ldp, Hk, ldhk, 4, K / 16, M / 16, warp, kBwWarps);   // (dz exp G) Hk^T
+    __syncthreads();
+    tril_bf16(AvB, ldab, SA, ldsa, tid);
+    tile_gemm<true, true, true, 1>(DQ, lddq, AB, ldab, kp, ldk, 4, K / 16, 4, warp, kBwWarps);          // + E k'
+    __syncthreads();
+    for (int i = tid; i < kChunk * (K / 8); i += kBwThreads) {
+      const int r = i / (K / 8), c8 = i - r * (K / 8);
+      const int pq = c.c0 + r;
+      if (pq < c.len)
+        *reinterpret_cast<uint4*>((bf16*)d.dq_gsa + ((size_t)(c.t0 + pq) * HQ + hq) * K + 8 * c8) = pack8(DQ + r * lddq + 8 * c8);
+    }
+    // ---- 6. dk' += E^T q, dv' += Bv^T do (register accumulators, k tiles kt >= mt) ---------------------
+    for (int kt = mt; kt < 4; ++kt) {
+      fragment<matrix_a, 16, 16, 16, bf16, col_major> fa;
+      load_matrix_sync(fa, AB + 16 * kt * ldab + 16 * mt, ldab);
+#pragma unroll
+      for (int i = 0; i < kMaxCT; ++i) {
+        if (i < CTK) {
+          fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+          load_matrix_sync(fb, qb + 16 * kt * ldk + 16 * ((warp >> 2) + 2 * i), ldk);
+          mma_sync(dkacc[i], fa, fb, dkacc[i]);
+        }
+      }
+      load_matrix_sync(fa, AvB + 16 * kt * ldab + 16 * mt, ldab);
+#pragma unroll
+      for (int i = 0; i < kMaxCT; ++i) {
+        if (i < CTV) {
+          fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+          load_matrix_sync(fb, dob + 16 * kt * ldv + 16 * ((warp >> 2) + 2 * i), ldv);
+          mma_sync(dvacc[i], fa, fb, dvacc[i]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- intra-chunk dk', dv' to the workspace (row = shifted position) ---------------------------------
+#pragma unroll
+  for (int i = 0; i < kMaxCT; ++i)
+    if (i < CTK) store_matrix_sync(DQ + 16 * mt * lddq + 16 * ((warp >> 2) + 2 * i), dkacc[i], lddq, mem_row_major);
+  __syncthreads();
+  for (int i = tid; i < kChunk * (K / 4); i += kBwThreads) {
+    const int r = i / (K / 4), c4 = i - r * (K / 4);
+    const int p = c.c0 + r;
+    if (p < c.len)
+      *reinterpret_cast<float4*>(w.dkp + ((size_t)(c.t0 + p) * H + h) * K + 4 * c4) =
+          *reinterpret_cast<const float4*>(DQ + r * lddq + 4 * c4);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kMaxCT; ++i)
+    if (i < CTV) store_matrix_sync(DQ + 16 * mt * lddq + 16 * ((warp >> 2) + 2 * i), dvacc[i], lddq, mem_row_major);
+  __syncthreads();
+  for (int i = tid; i < kChunk * (V / 4); i += kBwThreads) {
+    const int r = i / (V / 4), c4 = i - r * (V / 4);
+    const int p = c.c0 + r;
+    if (p < c.len)
+      *reinterpret_cast<float4*>(w.dvp + ((size_t)(c.t0 + p) * H + h) * V + 4 * c4) =
+          *reinterpret_cast<const float4*>(DQ + r * lddq + 4 * c4);
+  }
+}
+
+// ================================================================================================
+// 4. reverse march over the chunks of one (sequence, kv head)
+// ================================================================================================
+struct MarchLayout { int kp, vp, sp, sbe, G, DK, DV, DKb, DVb, qb, dob, zg, pg, X, cg, total; };
+__host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
+  MarchLayout L; int off = 0;
+  const int kv_ = K > V ? K : V;
+  const int mx = kv_ > M ? kv_ : M;
+  L.kp = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.vp = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.sp = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.sbe = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.G = off; off = bup128(off + kChunk * (M + 4) * 4);
+  L.DK = off; off = bup128(off + K * (M + 4) * 4);
+  L.DV = off; off = bup128(off + M * (V + 4) * 4);
+  L.DKb = off; off = bup128(off + K * (M + 8) * 2);
+  L.DVb = off; off = bup128(off + M * (V + 8) * 2);
+  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.zg = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.pg = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.X = off; off = bup128(off + kChunk * (mx + 4) * 4);
+  L.cg = off; off = bup128(off + M * 4);
+  L.total = off;
+  return L;
+}
+
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chunk_desc d, const BwdWs w) {
+  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
+  const int n = blockIdx.x / H, h = blockIdx.x % H;
+  const int t0 = d.cu_seqlens[n];
+  const int len = d.cu_seqlens[n + 1] - t0;
+  const int shift = seq_shift(d, n);
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const size_t nh = (size_t)n * H + h;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const MarchLayout L = march_layout(K, V, M);
+  const int mx = max(max(K, V), M);
+  const int ldk = K + 8, ldv = V + 8, ldm = M + 8, ldg = M + 4, lddk = M + 4, lddv = V + 4, ldx = mx + 4;
+  bf16* kp = (bf16*)(smem + L.kp);
+  bf16* vp = (bf16*)(smem + L.vp);
+  bf16* sp = (bf16*)(smem + L.sp);
+  bf16* sbe = (bf16*)(smem + L.sbe);
+  float* G = (float*)(smem + L.G);
+  float* DK = (float*)(smem + L.DK);        // [K][M+4]
+  float* DV = (float*)(smem + L.DV);        // [M][V+4]
+  bf16* DKb = (bf16*)(smem + L.DKb);        // [K][M+8]
+  bf16* DVb = (bf16*)(smem + L.DVb);        // [M][V+8]
+  bf16* qb = (bf16*)(smem + L.qb);
+  bf16* dob = (bf16*)(smem + L.dob);
+  bf16* zg = (bf16*)(smem + L.zg);
+  bf16* pg = (bf16*)(smem + L.pg);
+  float* X = (float*)(smem + L.X);
+  float* cgv = (float*)(smem + L.cg);
+
+  // ---- gradients arriving on the final state ---------------------------------------------------------
+  for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] = d.d_hkt ? d.d_hkt[nh * K * M + i] : 0.f;
+  for (int i = tid; i < M * V; i += kBwThreads) DV[(i / V) * lddv + (i % V)] = d.d_hvt ? d.d_hvt[nh * M * V + i] : 0.f;
+  for (int m = tid; m < M; m += kBwThreads) {
+    float acc = 0.f;
+    if (d.d_hkt && d.hkt && d.hvt) {
+      for (int kk = 0; kk < K; ++kk) acc += d.d_hkt[nh * K * M + (size_t)kk * M + m] * d.hkt[nh * K * M + (size_t)kk * M + m];
+      for (int vv = 0; vv < V; ++vv) acc += d.d_hvt[nh * M * V + (size_t)m * V + vv] * d.hvt[nh * M * V + (size_t)m * V + vv];
+    }
+    cgv[m] = acc;
+  }
+  __syncthreads();
+
+  for (int ci = nchunks - 1; ci >= 0; --ci) {
+    const int c0 = ci * kChunk;
+    const int lo = 0, hi = len - shift;
+    // ---- shifted kv-head tiles, cumulative gates, s' exp(Gend - G) --------------------------------------
+    load_tile_bf16(kp, ldk, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * K, (int64_t)H * K, c0 - shift, lo, hi, kChunk, K,
+                   tid, kBwThreads);
+    load_tile_bf16(vp, ldv, (const bf16*)d.v + ((size_t)t0 * H + h) * V, (int64_t)H * V, c0 - shift, lo, hi, kChunk, V, tid,
+                   kBwThreads);
+    load_tile_bf16(sp, ldm, (const bf16*)d.s + ((size_t)t0 * H + h) * M, (int64_t)H * M, c0 - shift, lo, hi, kChunk, M, tid,
+                   kBwThreads);
+    {
+      const bf16* gg = (const bf16*)d.g + ((size_t)t0 * H + h) * M;
+      for (int i = tid; i < kChunk * (M / 8); i += kBwThreads) {
+        const int r = i / (M / 8), c8 = i - r * (M / 8);
+        const int j = c0 + r - shift;
+        float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (j >= lo && j < hi) unpack8(*reinterpret_cast<const uint4*>(gg + (size_t)j * H * M + 8 * c8), gv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
+      }
+    }
+    for (int i = tid; i < K * M; i += kBwThreads) DKb[(i / M) * ldm + (i % M)] = f2bf(DK[(i / M) * lddk + (i % M)]);
+    for (int i = tid; i < M * V; i += kBwThreads) DVb[(i / V) * ldv + (i % V)] = f2bf(DV[(i / V) * lddv + (i % V)]);
+    __syncthreads();
+    for (int m = tid; m < M; m += kBwThreads) {
+      float run = 0.f;
+#pragma unroll 16
+      for (int r = 0; r < kChunk; ++r) {
+        run += G[r * ldg + m];
+        G[r * ldg + m] = run;
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < kChunk * M; i += kBwThreads) {
+      const int r = i / M, m = i - r * M;
+      sbe[r * ldm + m] = f2bf(bf2f(sp[r * ldm + m]) * __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]));
+    }
+    __syncthreads();
+    // ---- dk = intra + sbe DK^T --------------------------------------------------------------------------
+    tile_gemm<true, false, false>(X, ldx, sbe, ldm, DKb, ldm, 4, K / 16, M / 16, warp, kBwWarps);
+    __syncthreads();
+    for (int i = tid; i < kChunk * (K / 8); i += kBwThreads) {
+      const int r = i / (K / 8), c8 = i - r * (K / 8);
+      const int p = c0 + r, j = p - shift;
+      if (j >= 0 && p < len) {
+        const float* in = w.dkp + ((size_t)(t0 + p) * H + h) * K + 8 * c8;
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = X[r * ldx + 8 * c8 + e] + in[e];
+        *reinterpret_cast<uint4*>((bf16*)d.dk_gsa + ((size_t)(t0 + j) * H + h) * K + 8 * c8) = pack8(f);
+      }
+    }
+    __syncthreads();
+    // ---- dv = window part + intra + sbe DV ----------------------------------------------------------------
+    tile_gemm<true, true, false>(X, ldx, sbe, ldm, DVb, ldv, 4, V / 16, M / 16, warp, kBwWarps);
+    __syncthreads();
+    for (int i = tid; i < kChunk * (V / 8); i += kBwThreads) {
+      const int r = i / (V / 8), c8 = i - r * (V / 8);
+      const int p = c0 + r, j = p - shift;
+      if (j >= 0 && p < len) {
+        const float* in = w.dvp + ((size_t)(t0 + p) * H + h) * V + 8 * c8;
+        const float* wa = w.dvacc + ((size_t)(t0 + j) * H + h) * V + 8 * c8;
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = X[r * ldx + 8 * c8 + e] + in[e] + wa[e];
+        *reinterpret_cast<uint4*>((bf16*)d.dv + ((size_t)(t0 + j) * H + h) * V + 8 * c8) = pack8(f);
+      }
+    }
+    __syncthreads();
+    // ---- ds = intra + exp(Gend - G) .* (k' DK + v' DV^T); dg by reverse cumulative sum ------------------------
+    tile_gemm<true, true, false>(X, ldx, kp, ldk, DKb, ldm, 4, M / 16, K / 16, warp, kBwWarps);
+    __syncthreads();
+    tile_gemm<true, false, true>(X, ldx, vp, ldv, DVb, ldv, 4, M / 16, V / 16, warp, kBwWarps);
+    __syncthreads();
+    for (int i = tid; i < kChunk * M; i += kBwThreads) {
+      const int r = i / M, m = i - r * M;
+      const int p = c0 + r, j = p - shift;
+      float ds = 0.f, dgraw = 0.f;
+      if (j >= 0 && p < len) {
+        const size_t hi2 = ((size_t)(t0 + p) * H + h) * M + m;
+        ds = w.dsp[hi2] + __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]) * X[r * ldx + m];
+        dgraw = w.dga[hi2] - bf2f(sp[r * ldm + m]) * ds;
+        ((bf16*)d.ds)[((size_t)(t0 + j) * H + h) * M + m] = f2bf(ds);
+      }
+      X[r * ldx + m] = dgraw;
+    }
+    __syncthreads();
+    for (int m = tid; m < M; m += kBwThreads) {
+      float run = cgv[m];
+      for (int r = kChunk - 1; r >= 0; --r) {
+        run += X[r * ldx + m];
+        const int p = c0 + r, j = p - shift;
+        if (j >= 0 && p < len) ((bf16*)d.dg)[((size_t)(t0 + j) * H + h) * M + m] = f2bf(run);
+      }
+      cgv[m] = run;
+    }
+    // ---- carry DK, DV to the chunk start -------------------------------------------------------------------
+    for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] *= __expf(G[(kChunk - 1) * ldg + (i % M)]);
+    for (int i = tid; i < M * V; i += kBwThreads) DV[(i / V) * lddv + (i % V)] *= __expf(G[(kChunk - 1) * ldg + (i / V)]);
+    for (int qh = 0; qh < NG; ++qh) {
+      const int hq = h * NG + qh;
+      __syncthreads();
+      load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K, tid,
+                     kBwThreads);
+      load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * V, (int64_t)HQ * V, c0, 0, len, kChunk, V, tid,
+                     kBwThreads);
+      load_tile_bf16(zg, ldm, w.dzg + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid, kBwThreads);
+      load_tile_bf16(pg, ldm, w.pgq + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid, kBwThreads);
+      __syncthreads();
+      tile_gemm<false, true, true>(DK, lddk, qb, ldk, zg, ldm, K / 16, M / 16, 4, warp, kBwWarps);   // q^T (scale dz exp G)
+      tile_gemm<false, true, true>(DV, lddv, pg, ldm, dob, ldv, M / 16, V / 16, 4, warp, kBwWarps);  // (p exp G)^T do
+    }
+    __syncthreads();
+  }
+  // ---- tokens that never enter the slot memory; gradients of the initial state -----------------------------
+  const int tail0 = max(0, len - shift);
+  for (int i = tid; i < (len - tail0) * (V / 8); i += kBwThreads) {
+    const int j = tail0 + i / (V / 8), c8 = i % (V / 8);
+    const float* wa = w.dvacc + ((size_t)(t0 + j) * H + h) * V + 8 * c8;
+    *reinterpret_cast<uint4*>((bf16*)d.dv + ((size_t)(t0 + j) * H + h) * V + 8 * c8) = pack8(wa);
+  }
+  const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+  for (int i = tid; i < (len - tail0) * (K / 8); i += kBwThreads) {
+    const int j = tail0 + i / (K / 8), c8 = i % (K / 8);
+    *reinterpret_cast<uint4*>((bf16*)d.dk_gsa + ((size_t)(t0 + j) * H + h) * K + 8 * c8) = z4;
+  }
+  for (int i = tid; i < (len - tail0) * (M / 8); i += kBwThreads) {
+    const int j = tail0 + i / (M / 8), c8 = i % (M / 8);
+    *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = z4;
+    *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = z4;
+  }
+  if (d.dhk0)
+    for (int i = tid; i < K * M; i += kBwThreads) d.dhk0[nh * K * M + i] = DK[(i / M) * lddk + (i % M)];
+  if (d.dhv0)
+    for (int i = tid; i < M * V; i += kBwThreads) d.dhv0[nh * M * V + i] = DV[(i / V) * lddv + (i % V)];
+}
+
+int check_chunk_desc(const nha_chunk_desc* d);
+
+}  // namespace nha
+
+using namespace nha;
+
+extern "C" int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d) {
+  if (!d) return 0;
+  return bwd_ws_layout(d, nullptr, nullptr);
+}
+
+extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) {
+  int st = check_chunk_desc(d);
+  if (st != NHA_OK) return st;
+  if (!d->o || !d->lse_swa || !d->lse_gsa || !d->hk_chunks || !d->hv_chunks || !d->d_o || !d->dq_gsa || !d->dq_swa ||
+      !d->dk_gsa || !d->dk_swa || !d->dv || !d->ds || !d->dg)
+    return NHA_ERR_BAD_ARG;
+  if ((d->d_hkt == nullptr) != (d->d_hvt == nullptr)) return NHA_ERR_BAD_ARG;
+  if (d->d_hkt && (!d->hkt || !d->hvt)) return NHA_ERR_BAD_ARG;
+  if (d->V % 32 || d->K % 32) return NHA_ERR_UNSUPPORTED;
+  const int64_t need = bwd_ws_layout(d, nullptr, nullptr);
+  if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
+  BwdWs w;
+  bwd_ws_layout(d, &w, d->workspace);
+  const WRowLayout L1 = wrow_layout(d->K, d->V);
+  const WColLayout L2 = wcol_layout(d->K, d->V);
+  const SlotLayout L3 = slot_layout(d->K, d->V, d->M);
+  const MarchLayout L4 = march_layout(d->K, d->V, d->M);
+  if (L1.total > kMaxSmem || L2.total > kMaxSmem || L3.total > kMaxSmem || L4.total > kMaxSmem) return NHA_ERR_SMEM;
+  cudaStream_t cs = (cudaStream_t)stream;
+  cudaError_t e;
+  e = cudaFuncSetAttribute(nha_bwd_window_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L1.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  e = cudaFuncSetAttribute(nha_bwd_window_cols_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L2.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  e = cudaFuncSetAttribute(nha_bwd_slot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L3.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  e = cudaFuncSetAttribute(nha_bwd_march_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L4.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  dim3 grid(NCB, d->H), block(kBwThreads);
+  nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, w);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_bwd_window_cols_kernel<<<grid, block, L2.total, cs>>>(*d, w);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, w);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_bwd_march_kernel<<<dim3(d->N * d->H), block, L4.total, cs>>>(*d, w);
+  return check_launch();
+}
