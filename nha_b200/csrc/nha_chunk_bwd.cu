@@ -617,7 +617,7 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chun
 // ================================================================================================
 // 4. reverse march over the chunks of one (sequence, kv head)
 // ================================================================================================
-struct MarchLayout { int kp, vp, sp, sbe, G, DK, DV, DKb, DVb, qb, dob, zg, pg, X, cg, total; };
+struct MarchLayout { int kp, vp, sp, sbe, G, DK, DV, DKb, DVb, qb, dob, zg, pg, X, cg, red, total; };
 __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   MarchLayout L; int off = 0;
   const int kv_ = K > V ? K : V;
@@ -637,6 +637,7 @@ __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   L.pg = off; off = bup128(off + kChunk * (M + 8) * 2);
   L.X = off; off = bup128(off + kChunk * (mx + 4) * 4);
   L.cg = off; off = bup128(off + M * 4);
+  L.red = off; off = bup128(off + kBwThreads * 4);
   L.total = off;
   return L;
 }
@@ -669,6 +670,8 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
   bf16* pg = (bf16*)(smem + L.pg);
   float* X = (float*)(smem + L.X);
   float* cgv = (float*)(smem + L.cg);
+  float* red = (float*)(smem + L.red);
+  const int chunk0 = d.plan[n];
 
   // ---- gradients arriving on the final state ---------------------------------------------------------
   for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] = d.d_hkt ? d.d_hkt[nh * K * M + i] : 0.f;
@@ -686,6 +689,29 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
   for (int ci = nchunks - 1; ci >= 0; --ci) {
     const int c0 = ci * kChunk;
     const int lo = 0, hi = len - shift;
+    // ---- gate-gradient carry of all later chunks, rebuilt from the state and its gradient at this
+    //      chunk's end: cg[m] = <DK[:,m], hk[:,m]> + <DV[m,:], hv[m,:]>.  A running sum of
+    //      dgA - s' ds' over the later tokens equals it exactly but would pile up rounding noise
+    //      along the whole sequence.
+    if (ci < nchunks - 1) {
+      const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(chunk0 + ci + 1) * H + h) * K * M;
+      const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(chunk0 + ci + 1) * H + h) * M * V;
+      const int parts = kBwThreads / M;
+      const int m = tid % M, part = tid / M;
+      float acc = 0.f;
+      if (part < parts) {
+        for (int kk = part; kk < K; kk += parts) acc += DK[kk * lddk + m] * bf2f(hkn[(size_t)kk * M + m]);
+        for (int vv = part; vv < V; vv += parts) acc += DV[m * lddv + vv] * bf2f(hvn[(size_t)m * V + vv]);
+      }
+      red[tid] = acc;
+      __syncthreads();
+      if (tid < M) {
+        float sum = 0.f;
+        for (int q = 0; q < parts; ++q) sum += red[q * M + tid];
+        cgv[tid] = sum;
+      }
+      __syncthreads();
+    }
     // ---- shifted kv-head tiles, cumulative gates, s' exp(Gend - G) --------------------------------------
     load_tile_bf16(kp, ldk, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * K, (int64_t)H * K, c0 - shift, lo, hi, kChunk, K,
                    tid, kBwThreads);

@@ -196,6 +196,10 @@ def backward(q_gsa, q_swa, k_gsa, k_swa, v, s, g, scale, wl, shift, saved, o, ls
         c1 = min(T, c0 + C)
         sl = slice(c0, c1)
         G, Gend, be = _chunk_decays(gp[sl])
+        if ci < len(starts) - 1:
+            # carry of all later chunks rebuilt from the state at this chunk's end and its gradient
+            # (equal to the running sum of dgraw over the later tokens, without its rounding noise)
+            cg = (DK * hks[ci + 1]).sum(0) + (DV * hvs[ci + 1]).sum(1)
         sbe = sp[sl] * be
         dkp[sl] += sbe @ DK.T
         dvp[sl] += sbe @ DV
