@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the NHA attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (config.workload): fused NHA attention forward + backward at the
+340M-layer shape, B=16 T=2048 H=16 head_dim=64 M=64 slots window=64 chunk 64,
+bf16, q/k/v ~ N(0,1)/8, gate logits ~ N(0,1) through logsigmoid, upstream
+gradients ~ N(0,1), synthetic seeded inputs.  A step is one forward + backward
+over one such batch.  With N > 1 (launched by torchrun) every rank runs the
+same batch shape on its own GPU (sequences are independent: batch sharding, no
+collective); `value` is the tokens all ranks processed per second of the
+slowest rank.
+
+One JSON line is printed by rank 0.  `value` times the C-ABI calls with inputs
+resident in HBM; `e2e` times the public `chunk_nha` call + autograd backward
+with pinned HOST buffers (host->device of the 8 inputs and device->host of the
+output, both LSEs and the 7 gradients inside the timed region).  `roofline`
+describes the kernel with the largest share of the step, timed on its own with
+CUDA events.  `cpu_baseline` is the CPU oracle (a port of the reference's naive
+PyTorch path) timed on this box's host cores on a bounded slice.
+
+`--impl reference` times that CPU oracle alone (rank 0 only), same metric/unit.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+METRIC = 'NHA attn fwd+bwd tokens/s (bf16)'
+UNIT = 'tokens/s'
+CFG = dict(B=16, T=2048, H=16, D=64, M=64, W=64, shift=0)
+WORKLOAD = 'nha_attn_fwd_bwd B16 T2048 H16 D64 M64 W64 chunk64 bf16 (340M-layer shape)'
+ALG_BYTES_PER_TOKEN = 16512 + 32832          # forward + backward, all 16 heads (each input read once per pass)
+NAMES = ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v', 's', 'g')
+
+
+def peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d['hbm_gbs']), 'measured'
+    return 6650.0, 'fallback'
+
+
+def gen_inputs(seed, B, T, H, D, M, pin=False):
+    """CPU-generated fp32 -> bf16, like the reference's generators."""
+    g = torch.Generator().manual_seed(seed)
+    sc = D ** -0.5
+    out = {}
+    for n in ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v'):
+        out[n] = (torch.randn(B, T, H, D, generator=g) * sc).to(torch.bfloat16)
+    gl = F.logsigmoid(torch.randn(B, T, H, M, generator=g))
+    out['g'] = gl.to(torch.bfloat16)
+    out['s'] = (1 - gl.exp()).to(torch.bfloat16)
+    out['do'] = torch.randn(B, T, H, D, generator=g).to(torch.bfloat16)
+    if pin:
+        out = {k: v.pin_memory() for k, v in out.items()}
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '100', '-i', str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(',')])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), r[3:7]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        busy = [x for x in sm if x > 0]
+        return {'sm_mhz': statistics.median(busy) if busy else None, 'sm_max_mhz': mx or None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+def cpu_oracle_tokens_per_s(T, repeats=1):
+    """fwd+bwd of the CPU oracle on a B=1, T-token slice of the workload (all heads)."""
+    from oracle import nha_oracle as orc
+    torch.set_num_threads(os.cpu_count())
+    c = CFG
+    d = gen_inputs(0, 1, T, c['H'], c['D'], c['M'])
+    best = None
+    for _ in range(repeats):
+        xs = {n: d[n][0].double().requires_grad_(True) for n in NAMES}
+        t0 = time.perf_counter()
+        o, ls, lg, hk, hv = orc.nha_sequence(xs['q_gsa'], xs['q_swa'], xs['k_gsa'], xs['k_swa'], xs['v'], xs['s'],
+                                             xs['g'], c['D'] ** -0.5, c['W'], c['shift'])
+        (o * d['do'][0].double()).sum().backward()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return T / best, best
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU path for this op is its naive PyTorch functions
+    (scripts/verify_opt_parity.py:147-191); they cannot travel to the GPU box, so the oracle port,
+    pinned against them by tests/golden, is timed instead."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    T = 256
+    for _ in range(min(args.warmup, 3)):
+        cpu_oracle_tokens_per_s(T)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_tokens_per_s(T)
+    dt = time.perf_counter() - t0
+    val = T * args.steps / dt
+    sample = f'B=1 T={T} slice of the workload (H16 D64 M64 W64), fp64 oracle fwd + autograd bwd per step'
+    line = {
+        'metric': METRIC, 'value': val, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': 1e3 * dt / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'f64', 'data': 'synthetic', 'impl': 'reference',
+        'config': {'workload': WORKLOAD, 'sample': sample},
+        'cpu_baseline': {'value': val, 'unit': UNIT, 'cores': os.cpu_count(), 'kind': 'port', 'sample': sample},
+        'e2e': {'value': val, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--small', action='store_true', help='B=2 instead of 16 (profiling captures)')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == 'reference':
+        return run_reference(args)
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+
+    import nha_b200
+    from nha_b200 import _lib
+    from nha_b200.chunk import _Geometry, _fill_desc, chunk_backward, chunk_forward
+    lib = _lib.load()
+
+    c = dict(CFG)
+    if args.small:
+        c['B'] = 2
+    B, T, H, D, M, W, shift = c['B'], c['T'], c['H'], c['D'], c['M'], c['W'], c['shift']
+    scale = D ** -0.5
+    host = gen_inputs(1234 + rank, B, T, H, D, M, pin=not args.no_e2e)
+    flat = lambda x: x.reshape(B * T, *x.shape[2:])
+    x = {n: flat(host[n]).to(dev) for n in NAMES}
+    do = flat(host['do']).to(dev)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=dev)
+    tokens = B * T
+
+    def step():
+        o, ls, lg, _, _, saved = chunk_forward(x['q_gsa'], x['q_swa'], x['k_gsa'], x['k_swa'], x['v'], x['s'], x['g'],
+                                               cu, T, scale, W, shift)
+        return chunk_backward(x['q_gsa'], x['q_swa'], x['k_gsa'], x['k_swa'], x['v'], x['s'], x['g'], cu, scale, saved,
+                              o, ls, lg, do)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        step()
+    with ClockSampler(local) as clk:
+        ms = timed(step, args.steps)
+    value = world * tokens * args.steps / (ms * 1e-3)
+    launches_per_step = 7
+
+    # ---- per-kernel timing: every kernel of a step on its own, CUDA events on the launching stream ----
+    kernels = {}
+    o, ls, lg, _, _, saved = chunk_forward(x['q_gsa'], x['q_swa'], x['k_gsa'], x['k_swa'], x['v'], x['s'], x['g'], cu, T,
+                                           scale, W, shift)
+    geo = saved['geo']
+    t = dict(x, cu_seqlens=cu, o=o, lse_swa=ls, lse_gsa=lg, hk_chunks=saved['hk_chunks'], hv_chunks=saved['hv_chunks'],
+             d_o=do)
+    for n in NAMES:
+        t['d' + n] = torch.empty_like(x[n])
+    d0 = _fill_desc(geo, t, scale, None, W, None, shift)
+    t['workspace'] = torch.empty(max(16, int(lib.nha_chunk_bwd_workspace_bytes(d0))), dtype=torch.uint8, device=dev)
+    desc = _fill_desc(geo, t, scale, None, W, None, shift)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    import ctypes
+    calls = {
+        'state_pass': lambda: lib.nha_chunk_state_pass(ctypes.byref(desc), stream),
+        'output_pass': lambda: lib.nha_chunk_output_pass(ctypes.byref(desc), stream),
+        'bwd_window_rows': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 0, stream),
+        'bwd_window_cols': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 1, stream),
+        'bwd_slot': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 2, stream),
+        'bwd_march': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 3, stream),
+    }
+    # compulsory bytes of each kernel per token (all heads): what it must read once and write once
+    e, f = 2, 4
+    per_tok = {
+        'state_pass': H * ((2 * D + 2 * M) * e + (2 * D * M) * e / 64),
+        'output_pass': H * ((5 * D + 2 * M) * e + (2 * D * M) * e / 64 + D * e + 2 * f),
+        'bwd_window_rows': H * (5 * D * e + 2 * f + D * e + 2 * f),
+        'bwd_window_cols': H * (4 * D * e + 2 * f + D * e + D * f),
+        'bwd_slot': H * ((4 * D + 2 * M) * e + (2 * D * M) * e / 64 + 4 * f + D * e + (2 * D + 2 * M) * f + 2 * M * e),
+        'bwd_march': H * ((4 * D + 2 * M) * e + 2 * M * e + (3 * D + 2 * M) * f + (2 * D * M) * e / 64 + (2 * D + 2 * M) * e),
+    }
+    for name, fn in calls.items():
+        for _ in range(3):
+            assert fn() == 0
+        kms = timed(fn, args.steps) / args.steps
+        kernels[name] = {'ms': kms, 'gbs': per_tok[name] * tokens / (kms * 1e-3) / 1e9}
+    top = max(kernels, key=lambda k: kernels[k]['ms'])
+    peak, how = peaks()
+    roofline = {'bound': 'hbm', 'kernel': top, 'achieved': kernels[top]['gbs'], 'peak': peak, 'unit': 'GB/s',
+                'frac': kernels[top]['gbs'] / peak, 'traffic': None, 'peak_source': how,
+                'algorithmic_bytes_per_launch': per_tok[top] * tokens}
+    step_gbs = ALG_BYTES_PER_TOKEN * tokens * args.steps / (ms * 1e-3) / 1e9
+    step_roofline = {'bound': 'hbm', 'achieved': step_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': step_gbs / peak,
+                     'algorithmic_bytes_per_step': ALG_BYTES_PER_TOKEN * tokens}
+
+    # ---- end to end through the public API with host buffers -------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        dbuf = {n: torch.empty(B, T, *host[n].shape[2:], dtype=torch.bfloat16, device=dev) for n in NAMES + ('do',)}
+        out_host = {n: torch.empty_like(host[n]).pin_memory() for n in NAMES}
+        o_host = torch.empty(B, T, H, D, dtype=torch.bfloat16).pin_memory()
+        lse_host = torch.empty(2, B, T, H, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            for n in NAMES + ('do',):
+                dbuf[n].copy_(host[n], non_blocking=True)
+            leaves = {n: dbuf[n].detach().requires_grad_(True) for n in NAMES}
+            o, ls, lg = nha_b200.chunk_nha(leaves['q_swa'], leaves['k_swa'], leaves['q_gsa'], leaves['k_gsa'],
+                                           leaves['v'], leaves['s'], leaves['g'], scale=scale, window_size_left=W,
+                                           window_size_right=0, gsa_kv_shift=shift)
+            o.backward(dbuf['do'])
+            o_host.copy_(o.detach(), non_blocking=True)
+            lse_host[0].copy_(ls, non_blocking=True)
+            lse_host[1].copy_(lg, non_blocking=True)
+            for n in NAMES:
+                out_host[n].copy_(leaves[n].grad, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        ems = timed(e2e_step, args.steps)
+        h2d = sum(host[n].numel() * 2 for n in NAMES + ('do',))
+        d2h = o_host.numel() * 2 + lse_host.numel() * 4 + sum(out_host[n].numel() * 2 for n in NAMES)
+        e2e = {'value': world * tokens * args.steps / (ems * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': h2d,
+               'd2h_bytes_per_step': d2h, 'ms_per_step': ems / args.steps}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        Ts = 1024
+        tps, secs = cpu_oracle_tokens_per_s(Ts)
+        cpu = {'value': tps, 'unit': UNIT, 'cores': os.cpu_count(), 'kind': 'port',
+               'sample': f'B=1 T={Ts} slice of the workload, fp64 oracle fwd + autograd bwd, {secs:.1f} s'}
+
+    if rank == 0:
+        line = {
+            'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'bf16', 'data': 'synthetic',
+            'config': {'workload': WORKLOAD if not args.small else WORKLOAD.replace('B16', 'B2'),
+                       'tokens_per_gpu_per_step': tokens, 'window_left': W, 'gsa_kv_shift': shift,
+                       'parallelism': f'batch-sharded x{world}, no collective',
+                       'l2': 'inputs of one step (0.54 GB) exceed the 126 MB L2; no flush between steps'},
+            'roofline': roofline, 'step_roofline': step_roofline, 'kernels': kernels,
+            'cpu_baseline': cpu, 'e2e': e2e, 'gpu_launches': launches_per_step * args.steps,
+            'clocks': clk.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -142,6 +142,13 @@ int nha_chunk_fwd(const nha_chunk_desc* d, void* stream);
    when d_hkt/d_hvt are given); writes dq_*, dk_*, dv, ds, dg (+ dhk0/dhv0 when non-NULL) */
 int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
 
+/* one stage of nha_chunk_bwd on its own, so a harness can time each kernel with events on the
+   launching stream: 0 = window rows (delta, joint LSE, dq_swa), 1 = window columns (dk_swa, window
+   part of dv), 2 = slot pass (dq_gsa, intra-chunk parts), 3 = reverse march (dk_gsa, dv, ds, dg,
+   dhk0/dhv0).  The stages of one backward must run in this order; running all four equals
+   nha_chunk_bwd.  No counterpart in the reference (it has no timing hooks). */
+int nha_chunk_bwd_stage(const nha_chunk_desc* d, int stage, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

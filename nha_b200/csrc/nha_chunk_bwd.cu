@@ -857,7 +857,7 @@ extern "C" int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d) {
   return bwd_ws_layout(d, nullptr, nullptr);
 }
 
-extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) {
+static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   int st = check_chunk_desc(d);
   if (st != NHA_OK) return st;
   if (!d->o || !d->lse_swa || !d->lse_gsa || !d->hk_chunks || !d->hv_chunks || !d->d_o || !d->dq_gsa || !d->dq_swa ||
@@ -887,15 +887,31 @@ extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) {
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kBwThreads);
-  nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, w);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  nha_bwd_window_cols_kernel<<<grid, block, L2.total, cs>>>(*d, w);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, w);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  nha_bwd_march_kernel<<<dim3(d->N * d->H), block, L4.total, cs>>>(*d, w);
-  return check_launch();
+  if (stage_mask & 1) {
+    nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, w);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+  }
+  if (stage_mask & 2) {
+    nha_bwd_window_cols_kernel<<<grid, block, L2.total, cs>>>(*d, w);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+  }
+  if (stage_mask & 4) {
+    nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, w);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+  }
+  if (stage_mask & 8) {
+    nha_bwd_march_kernel<<<dim3(d->N * d->H), block, L4.total, cs>>>(*d, w);
+    st = check_launch();
+  }
+  return st;
+}
+
+extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) { return bwd_run(d, 15, stream); }
+
+extern "C" int nha_chunk_bwd_stage(const nha_chunk_desc* d, int stage, void* stream) {
+  if (stage < 0 || stage > 3) return NHA_ERR_BAD_ARG;
+  return bwd_run(d, 1 << stage, stream);
 }
