@@ -175,7 +175,7 @@ def main():
     ap.add_argument('--impl', default='ours')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
-    ap.add_argument('--small', action='store_true', help='B=2 instead of 16 (profiling captures)')
+    ap.add_argument('--small', action='store_true', help='B=4 instead of 16 (profiling captures)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == 'reference':
@@ -199,7 +199,7 @@ def main():
 
     c = dict(CFG)
     if args.small:
-        c['B'] = 2
+        c['B'] = 4
     B, T, H, D, M, W, shift = c['B'], c['T'], c['H'], c['D'], c['M'], c['W'], c['shift']
     scale = D ** -0.5
     host = gen_inputs(1234 + rank, B, T, H, D, M, pin=not args.no_e2e)
@@ -330,7 +330,7 @@ def main():
             'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
             'dtype': 'bf16', 'data': 'synthetic',
-            'config': {'workload': WORKLOAD if not args.small else WORKLOAD.replace('B16', 'B2'),
+            'config': {'workload': WORKLOAD if not args.small else WORKLOAD.replace('B16', 'B4'),
                        'tokens_per_gpu_per_step': tokens, 'window_left': W, 'gsa_kv_shift': shift,
                        'parallelism': f'batch-sharded x{world}, no collective',
                        'l2': 'inputs of one step (0.54 GB) exceed the 126 MB L2; no flush between steps'},
