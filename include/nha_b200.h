@@ -32,7 +32,8 @@ enum {
   NHA_ERR_UNSUPPORTED = 2,   /* head dim / slot count / window outside what the kernels cover */
   NHA_ERR_SMEM = 3,          /* tile set does not fit the 227 KB of shared memory */
   NHA_ERR_LAUNCH = 4,        /* cudaGetLastError() after a launch was not cudaSuccess */
-  NHA_ERR_WORKSPACE = 5      /* workspace pointer null or too small */
+  NHA_ERR_WORKSPACE = 5,     /* workspace pointer null or too small */
+  NHA_ERR_STATIC_SCRATCH = 6 /* the call needs more scratch than the library's built-in array holds */
 };
 
 #define NHA_CHUNK 64         /* tokens per chunk of the chunked kernels */
@@ -141,6 +142,22 @@ int nha_chunk_fwd(const nha_chunk_desc* d, void* stream);
 /* backward: needs the forward's o, lse_swa, lse_gsa, hk_chunks, hv_chunks, plan (and hkt/hvt
    when d_hkt/d_hvt are given); writes dq_*, dk_*, dv, ds, dg (+ dhk0/dhv0 when non-NULL) */
 int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
+
+/* State pass for callers that cannot allocate device memory (a plugin host that passes only
+   input and output buffers, a serving loop that forbids allocation after start-up).  Same
+   inputs, outputs and results as nha_chunk_state_pass, but desc->workspace is ignored: the
+   segment scratch comes from a fixed array inside the library's device image
+   (nha_chunk_state_pass_static_max_bytes() bytes, 16 MiB, held on every GPU that loads the
+   library until the process exits).  The call itself allocates nothing.  A problem whose
+   segment scratch (N*H*segments*(2*(K*M+M*V)+M) floats; raise desc->seg_chunks to shrink it)
+   exceeds the array is refused with NHA_ERR_STATIC_SCRATCH and nothing is launched.  The first
+   call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+   device current); make that first call before any stream capture begins.  All calls on a
+   device share the one array: calls that overlap on the GPU (different streams) race; calls
+   in stream order do not, and no call depends on what an earlier call left in the array.
+   No counterpart in the reference (its ops allocate through torch). */
+int64_t nha_chunk_state_pass_static_max_bytes(void);
+int nha_chunk_state_pass_static(const nha_chunk_desc* d, void* stream);
 
 /* one stage of nha_chunk_bwd on its own, so a harness can time each kernel with events on the
    launching stream: 0 = window rows (delta, joint LSE, dq_swa), 1 = window columns (dk_swa, window

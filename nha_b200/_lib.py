@@ -53,6 +53,8 @@ SYMBOLS = {
     'nha_chunk_output_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_fwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
+    'nha_chunk_state_pass_static_max_bytes': (C.c_int64, []),
+    'nha_chunk_state_pass_static': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd_stage': (C.c_int, [C.POINTER(ChunkDesc), C.c_int, c_void_p]),
 }
 

@@ -29,6 +29,7 @@ extern "C" const char* nha_status_string(int status) {
     case NHA_ERR_SMEM: return "tile set does not fit in shared memory";
     case NHA_ERR_LAUNCH: return "CUDA launch failed (see nha_last_cuda_error)";
     case NHA_ERR_WORKSPACE: return "workspace missing or too small";
+    case NHA_ERR_STATIC_SCRATCH: return "problem needs more scratch than the built-in static array holds";
     default: return "unknown status";
   }
 }

@@ -12,6 +12,8 @@
 // Replaces chunk_nha_fused_state_kernel (nha_fla/ops/nha/chunk_fused.py:31-114) and the state part of
 // fla's chunk_gsa_fwd reached from nha_fla/ops/nha/chunk_gsa.py:38-45; the in-sequence shift replaces
 // _packed_shift_right / _batch_shift_right (nha_fla/ops/nha/chunk.py:53-111).
+#include <mutex>
+
 #include "nha_common.cuh"
 
 namespace nha {
@@ -311,6 +313,87 @@ extern "C" int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream) {
   if (st != NHA_OK) return st;
   dim3 cgrid((unsigned)((SD + 255) / 256), d->N * d->H);
   nha_state_combine_kernel<<<cgrid, 256, 0, cs>>>(a);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  a.mode = 2;
+  nha_state_kernel<<<grid, block, smem, cs>>>(a);
+  return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// State pass for callers that cannot allocate device memory.
+//
+// Some hosts of this library own no device allocator: a plugin that is handed only its input and
+// output buffers, or a serving loop that forbids allocation after start-up because cudaMalloc
+// synchronises the device and can fail under memory pressure.  nha_chunk_state_pass needs a
+// caller-provided workspace as soon as a sequence spans more than one segment; the variant below
+// takes that workspace from a fixed array that lives in the library's own device image instead.
+// Every GPU that loads the library holds the array (kStaticScratchBytes) until the process exits.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_state_scratch[kStaticScratchBytes];
+
+// In host code `g_state_scratch` is only a handle for the runtime, not a device address, so the
+// address is looked up once per device with cudaGetSymbolAddress and cached.
+constexpr int kMaxDevices = 64;
+static void* g_state_scratch_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_state_scratch_mutex;
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return nha::record_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevices) return NHA_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_state_scratch_mutex);
+  if (!g_state_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_state_scratch);
+    if (e != cudaSuccess) return nha::record_cuda_error(e);
+    g_state_scratch_ptr[dev] = p;
+  }
+  *out = g_state_scratch_ptr[dev];
+  return NHA_OK;
+}
+
+extern "C" int64_t nha_chunk_state_pass_static_max_bytes(void) { return (int64_t)kStaticScratchBytes; }
+
+extern "C" int nha_chunk_state_pass_static(const nha_chunk_desc* d, void* stream) {
+  int st = check_chunk_desc(d);
+  if (st != NHA_OK) return st;
+  if (!d->hk_chunks || !d->hv_chunks) return NHA_ERR_BAD_ARG;
+  const int64_t need = state_workspace_bytes(d);
+  if (need > (int64_t)kStaticScratchBytes) return NHA_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  st = static_scratch_for_current_device(&scratch);
+  if (st != NHA_OK) return st;
+  cudaStream_t cs = (cudaStream_t)stream;
+  StateArgs a;
+  a.d = *d;
+  a.seg_chunks = seg_chunks_of(d);
+  a.nseg_max = nseg_max_of(d);
+  a.seg_local = a.seg_start = a.seg_decay = nullptr;
+  const int smem = state_smem(d->M);
+  cudaError_t e = cudaFuncSetAttribute(nha_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int slices = d->K / 16 + d->V / 16;
+  dim3 block(kStThreads);
+  if (a.nseg_max <= 1) {
+    a.mode = 0;
+    nha_state_kernel<<<dim3(slices, d->N * d->H, 1), block, smem, cs>>>(a);
+    return check_launch();
+  }
+  // every element of the scratch that is read below is written earlier in this same call, so the
+  // contents left by the previous call never matter and nothing has to be cleared
+  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  const int64_t per = (int64_t)d->N * d->H * a.nseg_max;
+  a.seg_local = (float*)scratch;
+  a.seg_start = a.seg_local + per * SD;
+  a.seg_decay = a.seg_start + per * SD;
+  dim3 grid(slices, d->N * d->H, a.nseg_max);
+  a.mode = 1;
+  nha_state_kernel<<<grid, block, smem, cs>>>(a);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_state_combine_kernel<<<dim3((unsigned)((SD + 255) / 256), d->N * d->H), 256, 0, cs>>>(a);
   st = check_launch();
   if (st != NHA_OK) return st;
   a.mode = 2;
