@@ -62,11 +62,18 @@ int nha_abi_version(void);
  *   o        [B, HQ, V] bf16   output (slot readout + window readout; slot readout only in
  *            win_logits mode)
  *   win_prob [B, HQ, W] fp32   window probabilities of the joint softmax, or NULL
+ *   workspace  scratch of nha_decode_workspace_bytes(B, HQ, H, V, W) bytes, needed when W > 64
+ *            (a (sequence, kv head) is then split over ceil(W/64) CTAs whose partial softmaxes are
+ *            merged by the last one to finish).  Its first B*H int32 are arrival counters: they must
+ *            be zero before the first call and every call leaves them zero, so one zero-initialised
+ *            buffer can be reused by all calls that do not overlap on the GPU.  May be NULL for W <= 64.
  */
+int64_t nha_decode_workspace_bytes(int B, int HQ, int H, int V, int W);
 int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
                     const void* sw_k, const void* sw_v, const void* cos, const void* sin, int64_t cs_batch,
                     int64_t cs_row, const void* win_logits, float* hk, float* hv, int zero_state, void* o,
-                    float* win_prob, int B, int HQ, int H, int K, int V, int M, int W, float scale, void* stream);
+                    float* win_prob, void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V,
+                    int M, int W, float scale, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Chunked prefill / training.  One descriptor serves the state pass, the output pass and the

@@ -41,8 +41,10 @@ SYMBOLS = {
     'nha_status_string': (C.c_char_p, [C.c_int]),
     'nha_last_cuda_error': (C.c_char_p, []),
     'nha_abi_version': (C.c_int, []),
+    'nha_decode_workspace_bytes': (C.c_int64, [C.c_int] * 5),
     'nha_decode_step': (C.c_int, [c_void_p] * 10 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, C.c_int,
-                                                     c_void_p, c_void_p] + [C.c_int] * 7 + [C.c_float, c_void_p]),
+                                                     c_void_p, c_void_p, c_void_p, C.c_int64] + [C.c_int] * 7
+                        + [C.c_float, c_void_p]),
     'nha_chunk_desc_size': (C.c_int64, []),
     'nha_chunk_count_bound': (C.c_int64, [C.c_int64, C.c_int64]),
     'nha_chunk_plan_ints': (C.c_int64, [C.c_int64, C.c_int64]),

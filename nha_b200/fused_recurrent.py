@@ -20,6 +20,22 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_WORKSPACES = {}
+
+
+def _decode_workspace(device, B, HQ, H, V, W):
+    """Zero-initialised scratch for the split decode kernel, one per (device, stream); the kernel
+    leaves its counters at zero, so the buffer is reused by later calls on the same stream."""
+    lib = _lib.load()
+    need = int(lib.nha_decode_workspace_bytes(B, HQ, H, V, W))
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def _bf16c(x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if x is None:
         return None
@@ -130,10 +146,12 @@ def fused_recurrent_nha_decode(
     o = torch.empty(B, HQ, V, dtype=_BF16, device=dev)
     lib = _lib.load()
     with torch.cuda.device(dev):
+        ws = _decode_workspace(dev, B, HQ, H, V, W) if W > 64 else None
         st = lib.nha_decode_step(
             _lib.ptr(qf), _lib.ptr(sqf), _lib.ptr(kf), _lib.ptr(vf), _lib.ptr(gf), _lib.ptr(sf),
             _lib.ptr(swk), _lib.ptr(swv), _lib.ptr(cos if rotary else None), _lib.ptr(sin if rotary else None),
             cs_batch, cs_row, None, _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o), None,
+            _lib.ptr(ws), 0 if ws is None else ws.numel(),
             B, HQ, H, K, V, M, W, float(scale), _stream(dev))
     _lib.check(st, 'nha_decode_step')
     o = o.view(B, 1, HQ, V)
@@ -189,7 +207,7 @@ def fused_recurrent_nha(
         st = lib.nha_decode_step(
             _lib.ptr(qf), None, _lib.ptr(kf), _lib.ptr(vf), _lib.ptr(gf), _lib.ptr(sf),
             None, None, None, None, 0, 0, _lib.ptr(wlog), _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o),
-            _lib.ptr(prob), B, HQ, H, K, V, M, W, float(scale), _stream(dev))
+            _lib.ptr(prob), None, 0, B, HQ, H, K, V, M, W, float(scale), _stream(dev))
     _lib.check(st, 'nha_decode_step')
     o = o.view(B, 1, HQ, V)
     if out_dtype != _BF16:

@@ -37,7 +37,7 @@ def test_argument_validation_needs_no_gpu():
     lib = _lib.load()
     # null pointers are rejected before any CUDA call
     st = lib.nha_decode_step(None, None, None, None, None, None, None, None, None, None, 0, 0, None, None, None, 0,
-                             None, None, 1, 4, 2, 64, 64, 16, 8, 0.125, None)
+                             None, None, None, 0, 1, 4, 2, 64, 64, 16, 8, 0.125, None)
     assert st == 1
     d = _lib.ChunkDesc()
     assert lib.nha_chunk_fwd(ctypes.byref(d), None) == 1
