@@ -105,8 +105,10 @@ typedef struct nha_chunk_desc {
   /* chunk-start states written by the state pass, read by the output pass and the backward */
   void* hk_chunks;              /* [NC, H, K, M] bf16 */
   void* hv_chunks;              /* [NC, H, M, V] bf16 */
-  /* plan (int32 workspace written by nha_chunk_plan): [0..N] first chunk of each sequence,
-     then [N+1 .. N+1+NC) the sequence of each chunk; NC = nha_chunk_count_bound(Ttot, N) */
+  /* plan (int32 workspace of nha_chunk_plan_ints(Ttot, N, H) entries, written by nha_chunk_plan):
+     [0..N] first chunk of each sequence, [N+1 .. N+1+NC) the sequence of each chunk, then NC*H
+     per-(chunk, head) flags and a device error word used by the output pass;
+     NC = nha_chunk_count_bound(Ttot, N) */
   int32_t* plan;
   void* workspace;              /* scratch, see nha_chunk_*_workspace_bytes */
   size_t workspace_bytes;
@@ -133,7 +135,7 @@ int64_t nha_chunk_desc_size(void);
 /* upper bound of the number of chunks of N packed sequences holding Ttot tokens */
 int64_t nha_chunk_count_bound(int64_t Ttot, int64_t N);
 /* number of int32 of desc->plan */
-int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N);
+int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N, int64_t H);
 /* bytes of desc->workspace for the forward (state pass + output pass) / the backward */
 int64_t nha_chunk_fwd_workspace_bytes(const nha_chunk_desc* d);
 int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d);
@@ -144,6 +146,10 @@ int nha_chunk_plan(const nha_chunk_desc* d, void* stream);
 int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream);
 /* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
 int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
+/* device-side error word of the last output pass run with this descriptor's plan (0 = none; non-zero:
+   a bounded wait on a tensor-core completion barrier ran out and the affected chunks are invalid);
+   synchronises the stream.  No counterpart in the reference. */
+int nha_chunk_device_error(const nha_chunk_desc* d, void* stream);
 /* plan + state pass + output pass */
 int nha_chunk_fwd(const nha_chunk_desc* d, void* stream);
 /* backward: needs the forward's o, lse_swa, lse_gsa, hk_chunks, hv_chunks, plan (and hkt/hvt

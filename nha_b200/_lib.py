@@ -47,7 +47,8 @@ SYMBOLS = {
                         + [C.c_float, c_void_p]),
     'nha_chunk_desc_size': (C.c_int64, []),
     'nha_chunk_count_bound': (C.c_int64, [C.c_int64, C.c_int64]),
-    'nha_chunk_plan_ints': (C.c_int64, [C.c_int64, C.c_int64]),
+    'nha_chunk_plan_ints': (C.c_int64, [C.c_int64, C.c_int64, C.c_int64]),
+    'nha_chunk_device_error': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_fwd_workspace_bytes': (C.c_int64, [C.POINTER(ChunkDesc)]),
     'nha_chunk_bwd_workspace_bytes': (C.c_int64, [C.POINTER(ChunkDesc)]),
     'nha_chunk_plan': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),

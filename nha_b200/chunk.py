@@ -50,7 +50,7 @@ class _Geometry:
         self.device = q_gsa.device
         lib = _lib.load()
         self.ncb = int(lib.nha_chunk_count_bound(self.Ttot, self.N))
-        self.plan = torch.empty(int(lib.nha_chunk_plan_ints(self.Ttot, self.N)), dtype=torch.int32, device=self.device)
+        self.plan = torch.empty(int(lib.nha_chunk_plan_ints(self.Ttot, self.N, self.H)), dtype=torch.int32, device=self.device)
 
 
 def _fill_desc(geo: _Geometry, t: dict, scale, wl_t, wl_all, sh_t, sh_all) -> _lib.ChunkDesc:

@@ -11,6 +11,8 @@
 // Replaces chunk_nha_fused_o_kernel (nha_fla/ops/nha/chunk_fused.py:117-283) and, for chunk_nha,
 // the flash-attn varlen forward + fla chunk_gsa forward + log-sum-exp merge
 // (nha_fla/ops/nha/chunk.py:423-470).
+#include <stdlib.h>
+
 #include "nha_common.cuh"
 
 namespace nha {
@@ -105,7 +107,9 @@ __device__ __forceinline__ void tril_to_bf16(bf16* AB, int ldab, const float* SA
   }
 }
 
-__global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_chunk_desc d) {
+// `only_flagged` (optional): [chunks, H] flags; when given, a CTA whose flag is zero has nothing to do
+// (the tensor-memory kernel already produced that chunk).
+__global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_chunk_desc d, const int* __restrict__ only_flagged) {
   using namespace nvcuda::wmma;
   const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
   const int N = d.N;
@@ -113,6 +117,7 @@ __global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_ch
   const int h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
   if (n < 0) return;
+  if (only_flagged && only_flagged[(size_t)cg * H + h] == 0) return;
   const int ci = cg - d.plan[n];
   const int t0 = d.cu_seqlens[n];
   const int len = d.cu_seqlens[n + 1] - t0;
@@ -373,6 +378,7 @@ __global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_ch
 
 int64_t state_workspace_bytes(const nha_chunk_desc* d);
 int check_chunk_desc(const nha_chunk_desc* d);
+int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs);
 
 }  // namespace nha
 
@@ -388,14 +394,39 @@ extern "C" int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream) {
   if (st != NHA_OK) return st;
   if (!d->o || !d->lse_swa || !d->lse_gsa || !d->hk_chunks || !d->hv_chunks) return NHA_ERR_BAD_ARG;
   if (d->V % 32) return NHA_ERR_UNSUPPORTED;
+  cudaStream_t cs = (cudaStream_t)stream;
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  // Shapes with a tensor-memory kernel run it first; it flags the (rare) chunks whose gates decay too
+  // fast for its single decay reference, and the general kernel below then computes only those.
+  int* flags = d->plan + d->N + 1 + NCB;
+  int* err = flags + (size_t)NCB * d->H;
+  const char* off = getenv("NHA_B200_NO_UMMA");
+  bool umma_done = false;
+  if (!(off && off[0] == '1')) {
+    st = chunk_output_pass_umma(d, flags, err, cs);
+    if (st == NHA_OK) umma_done = true;
+    else if (st != NHA_ERR_UNSUPPORTED) return st;
+  }
   const FwdLayout L = fwd_layout(d->K, d->V, d->M);
-  if (L.total > kMaxSmem) return NHA_ERR_SMEM;
+  if (L.total > kMaxSmem) return umma_done ? NHA_OK : NHA_ERR_SMEM;
   cudaError_t e = cudaFuncSetAttribute(nha_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kFwdThreads);
-  nha_chunk_fwd_kernel<<<grid, block, L.total, (cudaStream_t)stream>>>(*d);
+  nha_chunk_fwd_kernel<<<grid, block, L.total, cs>>>(*d, umma_done ? flags : nullptr);
   return check_launch();
+}
+
+// Device-side error word of the last tensor-memory output pass that used this descriptor's plan
+// (non-zero: a bounded wait on an MMA completion barrier ran out).  Synchronises the stream.
+extern "C" int nha_chunk_device_error(const nha_chunk_desc* d, void* stream) {
+  if (!d || !d->plan) return -1;
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, d->plan + d->N + 1 + NCB + (size_t)NCB * d->H, sizeof(int), cudaMemcpyDeviceToHost,
+                                  (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return -1;
+  return v;
 }
 
 extern "C" int nha_chunk_fwd(const nha_chunk_desc* d, void* stream) {

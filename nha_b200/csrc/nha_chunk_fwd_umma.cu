@@ -1,0 +1,452 @@
+// Output pass of the chunked NHA forward on the sm_100a tensor-core path: tcgen05.mma with operands in
+// 128-byte-swizzled shared memory, accumulators in tensor memory (TMEM), one thread per query row
+// for the softmax (tcgen05.ld hands every thread a whole row, so row maxima and sums need no
+// shuffles).  One CTA per (chunk, kv head); an MMA tile is 64 tokens x 1 head (R = 64, for
+// HQ == H) or 64 tokens x 2 heads of the group (R = 128), and the CTA walks the heads of the group
+// reusing the chunk's k', v', gates and chunk-start states.
+//
+// Per tile:   A  = q k'^T,  QH = q Hk                       (TMEM)
+//             X  = tril(A) (s' .* b)                         ok = scale (exp(G) .* QH + a .* X)
+//             S  = q_swa k_swa^T per 64-key window tile       two sweeps: statistics, probabilities
+//             O  = (p .* exp(G)) Hv + tril((p .* a)(s' .* b)^T) v' + sum_tiles P v_win
+// a = exp(G - R), b = exp(R - G) with ONE reference R[m] = Gend[m] / 2 per chunk and slot.  That keeps
+// every factor inside exp(+-70) as long as a chunk decays by less than 140 nats per slot; a chunk
+// beyond that is left untouched and flagged, and the general kernel (16-row block references,
+// nha_chunk_fwd.cu) computes it instead, so the result never depends on the bound.
+//
+// Replaces chunk_nha_fused_o_kernel (nha_fla/ops/nha/chunk_fused.py:117-283) and, for chunk_nha, the
+// flash-attn varlen forward + fla chunk_gsa forward + log-sum-exp merge (nha_fla/ops/nha/chunk.py:423-470).
+#include "nha_common.cuh"
+#include "nha_umma.cuh"
+
+namespace nha {
+
+using namespace umma;
+
+constexpr int kUThreads = 128;
+constexpr float kUmmaDecayLimit = 140.0f;
+
+__device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+
+// Asynchronously copy `rows` x COLS bf16 (global rows row0.., stride gstride elements; rows outside
+// [lo, hi) become zeros) into COLS/64 swizzled tiles of `tile_bytes` each, starting at tile row dst_row0.
+template <int COLS>
+__device__ __forceinline__ void load_sw(unsigned char* tile, int tile_bytes, const bf16* base, int64_t gstride, int row0,
+                                        int lo, int hi, int rows, int dst_row0, int tid) {
+  constexpr int C8 = COLS / 8;
+  for (int i = tid; i < rows * C8; i += kUThreads) {
+    const int r = i / C8, c = i % C8;
+    const int gr = row0 + r;
+    const bool ok = gr >= lo && gr < hi;
+    const bf16* src = base + (int64_t)(ok ? gr : lo) * gstride + 8 * c;
+    cp16(tile + (c >> 3) * tile_bytes + sw_off(dst_row0 + r, c & 7), src, ok);
+  }
+}
+
+template <int D, int R>
+struct UmmaLayout {
+  static constexpr int KT = D / 64;
+  static constexpr int kATile = R * 128;             // one 64-wide k tile of an R-row A operand
+  static constexpr int tQ = 0;                        // q_gsa; later p .* a
+  static constexpr int tQS = tQ + KT * kATile;        // q_swa
+  static constexpr int tK = tQS + KT * kATile;        // k'
+  static constexpr int tV = tK + KT * 8192;           // v'
+  static constexpr int tHk = tV + KT * 8192;          // Hk [D][64]
+  static constexpr int tHv = tHk + D * 128;           // Hv [64][D]
+  static constexpr int tSB = tHv + KT * 8192;         // s' .* b [64][64]
+  static constexpr int tW = tSB + 8192;               // window keys [64][D]
+  static constexpr int tWV = tW + KT * 8192;          // window values [64][D]
+  static constexpr int tAB = tWV + KT * 8192;         // tril(A) / tril(Bv) / P   [R][64]
+  static constexpr int tPG = tAB + kATile;            // p .* exp(G)             [R][64]
+  static constexpr int oG = tPG + kATile;             // fp32 [64][65] cumulative gates
+  static constexpr int oR = oG + 64 * 65 * 4;         // fp32 [64] reference exponent
+  static constexpr int oBar = oR + 256;               // mbarrier + TMEM slot
+  static constexpr int total = oBar + 64 + 1024;      // + slack for the 1024-byte alignment of the base
+  static constexpr int kTmemCols = D == 64 ? 256 : 512;
+  static constexpr int cA = 0, cQH = 64, cS = 128, cO = D == 64 ? 64 : 256;
+};
+
+template <int D, int R>
+__global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
+                                                                  int* __restrict__ err) {
+  typedef UmmaLayout<D, R> L;
+  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int n = d.plan[N + 1 + cg];
+  if (n < 0) return;
+  const int ci = cg - d.plan[n];
+  const int t0 = d.cu_seqlens[n];
+  const int len = d.cu_seqlens[n + 1] - t0;
+  const int c0 = ci * kChunk;
+  const int wl = seq_window(d, n);
+  const int shift = seq_shift(d, n);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* Gs = (float*)(sm + L::oG);
+  float* Rs = (float*)(sm + L::oR);
+  uint64_t* mbar = (uint64_t*)(sm + L::oBar);
+  uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
+
+  // ---- kv-head tiles of the chunk and the first tile's queries go in flight ------------------------
+  const int lo = 0, hi = len - shift;              // valid source rows of the shifted inputs
+  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<64>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
+  cp_commit();
+  // gates and write weights through registers: G needs an fp32 scan, s' is folded into s' .* b
+  uint4 sreg[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    const int src = c0 + r - shift;
+    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= lo && src < hi) {
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
+      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+  }
+  if (tid == 0) mbar_init(mbar, 1);
+  __syncthreads();
+  // inclusive scan along the rows: two threads per column (rows 0..31 and 32..63), then a fix-up
+  {
+    const int m = tid & 63, half = tid >> 6;
+    float run = 0.f;
+#pragma unroll 8
+    for (int r = 32 * half; r < 32 * half + 32; ++r) {
+      run += Gs[r * 65 + m];
+      Gs[r * 65 + m] = run;
+    }
+    __syncthreads();
+    if (half == 1) {
+      const float add = Gs[31 * 65 + m];
+#pragma unroll 8
+      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+    }
+    __syncthreads();
+  }
+  const bool mine_unsafe = tid < 64 && fabsf(Gs[63 * 65 + tid]) > kUmmaDecayLimit;
+  const int unsafe = __syncthreads_or(mine_unsafe ? 1 : 0);
+  if (tid == 0) flags[(size_t)cg * H + h] = unsafe;
+  if (unsafe) {
+    cp_wait_all();
+    return;
+  }
+  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
+  __syncthreads();
+  // s' .* b into its swizzled tile ([64 i][64 m]: K-major for (p .* a) SB^T, MN-major for tril(A) SB)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    float sv[8], out[8];
+    unpack8(sreg[j], sv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(out);
+  }
+  if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tslot;
+  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  uint32_t phase = 0;
+  bool failed = false;
+
+  // row of this thread inside the tile
+  const bool active = R == 128 ? true : lane < 16;
+  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int tk = row & 63;                          // token inside the chunk
+  const int th = row >> 6;                          // head inside the tile
+  const int pos = c0 + tk;
+  const bool in_seq = pos < len;
+  const int jt_hi = ci;
+  const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
+  const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aK = smem_u32(sm + L::tK);
+  const uint32_t aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk), aHv = smem_u32(sm + L::tHv);
+  const uint32_t aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW), aWV = smem_u32(sm + L::tWV);
+  const uint32_t aAB = smem_u32(sm + L::tAB), aPG = smem_u32(sm + L::tPG), aPA = aQ;
+  const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
+  const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
+
+#define NHA_MMA_WAIT()                                   \
+  do {                                                   \
+    if (tid == 0) commit(mbar);                          \
+    if (!mbar_wait(mbar, phase)) failed = true;          \
+    phase ^= 1;                                          \
+    tc_fence_after();                                    \
+  } while (0)
+#define NHA_SMEM_TO_MMA()                                \
+  do {                                                   \
+    fence_async_smem();                                  \
+    tc_fence_before();                                   \
+    __syncthreads();                                     \
+    tc_fence_after();                                    \
+  } while (0)
+
+  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+    const int hq0 = h * NG + ht * TH;
+    const int hq = hq0 + th;
+    // ---- queries of this tile ------------------------------------------------------------------------
+#pragma unroll
+    for (int t2 = 0; t2 < TH; ++t2) {
+      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
+                 64, 64 * t2, tid);
+      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0,
+                 len, 64, 64 * t2, tid);
+    }
+    cp_commit();
+    cp_wait_all();
+    NHA_SMEM_TO_MMA();
+    // ---- A = q k'^T, QH = q Hk --------------------------------------------------------------------------
+    if (tid == 0) {
+      mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
+      mma_tile(tbase + L::cQH, aQ, L::kATile, aHk, 0, R, 64, D / 16, 1, false);
+    }
+    NHA_MMA_WAIT();
+    // ---- tril(A) -> bf16 A operand ------------------------------------------------------------------------
+    {
+      float av[32];
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cA + 32 * part, av);
+        if (active) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int i = 32 * part + 8 * c8 + e;
+              o8[e] = i <= tk ? av[8 * c8 + e] : 0.f;
+            }
+            *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
+          }
+        }
+      }
+    }
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) mma_tile(tbase + L::cA, aAB, L::kATile, aSB, 0, R, 64, 4, 1, false);   // X = tril(A) SB
+    NHA_MMA_WAIT();
+    // ---- slot logits ok = scale (exp(G) .* QH + a .* X), kept in registers --------------------------------
+    float ok[64];
+    float mg = -INFINITY;
+    {
+      float qh[32], xv[32];
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cQH + 32 * part, qh);
+        tmem_ld32(tlane + L::cA + 32 * part, xv);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int m = 32 * part + e;
+          const float gl = Gs[tk * 65 + m];
+          const float v = d.scale * (__expf(gl) * qh[e] + __expf(gl - Rs[m]) * xv[e]);
+          ok[m] = v;
+          mg = fmaxf(mg, v);
+        }
+      }
+    }
+    float lg = 0.f;
+#pragma unroll
+    for (int m = 0; m < 64; ++m) lg += __expf(ok[m] - mg);
+    // ---- window sweep 1: statistics --------------------------------------------------------------------------
+    float ms = -INFINITY, ls = 0.f;
+    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+      __syncthreads();
+      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      cp_commit();
+      cp_wait_all();
+      NHA_SMEM_TO_MMA();
+      if (tid == 0) mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);
+      NHA_MMA_WAIT();
+      float sv[32];
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cS + 32 * part, sv);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = jt * kChunk + 32 * part + e;
+          const bool vis = key <= pos && (wl < 0 || key >= pos - wl);
+          if (vis) tmax = fmaxf(tmax, sv[e] * d.scale);
+        }
+      }
+      const float mnew = fmaxf(ms, tmax);
+      float part_sum = 0.f;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cS + 32 * part, sv);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = jt * kChunk + 32 * part + e;
+          const bool vis = key <= pos && (wl < 0 || key >= pos - wl);
+          if (vis) part_sum += __expf(sv[e] * d.scale - mnew);
+        }
+      }
+      if (mnew > -INFINITY) {
+        ls = ls * __expf(ms - mnew) + part_sum;
+        ms = mnew;
+      }
+      tc_fence_before();
+    }
+    const float lse_g = mg + __logf(lg);
+    const float lse_s = ms + __logf(ls);
+    const float mx = fmaxf(lse_g, lse_s);
+    const float Lj = mx + __logf(__expf(lse_g - mx) + __expf(lse_s - mx));
+    if (active && in_seq) {
+      d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = lse_g;
+      d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = lse_s;
+    }
+    // ---- slot probabilities: p .* exp(G) and p .* a as bf16 A operands -------------------------------------------
+    __syncthreads();                                  // every thread is past its last read of tQ's MMAs
+    if (active) {
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        float pg8[8], pa8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int m = 8 * c8 + e;
+          const float p = in_seq ? __expf(ok[m] - Lj) : 0.f;
+          const float gl = Gs[tk * 65 + m];
+          pg8[e] = p * __expf(gl);
+          pa8[e] = p * __expf(gl - Rs[m]);
+        }
+        *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, c8)) = pack8(pg8);
+        *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, c8)) = pack8(pa8);
+      }
+    }
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+#pragma unroll
+      for (int ct = 0; ct < KT; ++ct)                 // O = (p exp G) Hv, 64 output columns at a time
+        mma_tile(tbase + L::cO + 64 * ct, aPG, L::kATile, aHv + ct * 8192, 0, R, 64, 4, 1, false);
+      mma_tile(tbase + L::cA, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);   // Bv = (p a) SB^T
+    }
+    NHA_MMA_WAIT();
+    {
+      float bv[32];
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cA + 32 * part, bv);
+        if (active) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            float o8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int i = 32 * part + 8 * c8 + e;
+              o8[e] = i <= tk ? bv[8 * c8 + e] : 0.f;
+            }
+            *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
+          }
+        }
+      }
+    }
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+#pragma unroll
+      for (int ct = 0; ct < KT; ++ct)                 // O += tril(Bv) v'
+        mma_tile(tbase + L::cO + 64 * ct, aAB, L::kATile, aV + ct * 8192, 0, R, 64, 4, 1, true);
+    }
+    NHA_MMA_WAIT();
+    // ---- window sweep 2: probabilities and readout ------------------------------------------------------------------
+    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+      tc_fence_before();
+      __syncthreads();
+      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      cp_commit();
+      cp_wait_all();
+      NHA_SMEM_TO_MMA();
+      if (tid == 0) mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);
+      NHA_MMA_WAIT();
+      {
+        float sv[32];
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          tmem_ld32(tlane + L::cS + 32 * part, sv);
+          if (active) {
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+              float o8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int key = jt * kChunk + 32 * part + 8 * c8 + e;
+                const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && in_seq;
+                o8[e] = vis ? __expf(sv[8 * c8 + e] * d.scale - Lj) : 0.f;
+              }
+              *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
+            }
+          }
+        }
+      }
+      NHA_SMEM_TO_MMA();
+      if (tid == 0) {
+#pragma unroll
+        for (int ct = 0; ct < KT; ++ct)
+          mma_tile(tbase + L::cO + 64 * ct, aAB, L::kATile, aWV + ct * 8192, 0, R, 64, 4, 1, true);
+      }
+      NHA_MMA_WAIT();
+    }
+    // ---- output row ----------------------------------------------------------------------------------------------------------
+    {
+      float ov[32];
+#pragma unroll
+      for (int part = 0; part < D / 32; ++part) {
+        tmem_ld32(tlane + L::cO + 32 * part, ov);
+        if (active && in_seq) {
+          bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D + 32 * part;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+#undef NHA_MMA_WAIT
+#undef NHA_SMEM_TO_MMA
+  if (failed && tid == 0) atomicExch(err, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
+}
+
+template <int D, int R>
+static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
+  typedef UmmaLayout<D, R> L;
+  cudaError_t e = cudaFuncSetAttribute(nha_fwd_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), kUThreads, L::total, cs>>>(*d, flags, err);
+  return check_launch();
+}
+
+// Runs the tensor-memory output pass when the shape has one (K == V in {64, 128}, M == 64, one or an
+// even number of query heads per kv head).  Returns NHA_ERR_UNSUPPORTED otherwise.
+int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
+  const int NG = d->HQ / d->H;
+  if (d->K != d->V || d->M != 64) return NHA_ERR_UNSUPPORTED;
+  if (d->K == 64 && NG == 1) return launch_umma<64, 64>(d, flags, err, cs);
+  if (d->K == 64 && NG % 2 == 0) return launch_umma<64, 128>(d, flags, err, cs);
+  if (d->K == 128 && NG == 1) return launch_umma<128, 64>(d, flags, err, cs);
+  if (d->K == 128 && NG % 2 == 0) return launch_umma<128, 128>(d, flags, err, cs);
+  return NHA_ERR_UNSUPPORTED;
+}
+
+}  // namespace nha

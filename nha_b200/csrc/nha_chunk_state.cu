@@ -23,7 +23,8 @@ constexpr int kStWarps = kStThreads / 32;
 constexpr int kDefaultSegChunks = 32;
 
 // ---------------------------------------------------------------------------------------------
-__global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ plan, int N, int NCB) {
+__global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ plan, int N, int NCB, int H) {
+  if (threadIdx.x == 0) plan[N + 1 + NCB + (size_t)NCB * H] = 0;   // device-side error word
   // plan[0..N]: first chunk of each sequence; plan[N+1+c]: sequence of chunk c (-1 = unused)
   __shared__ int total;
   if (threadIdx.x == 0) {
@@ -269,12 +270,15 @@ int check_chunk_desc(const nha_chunk_desc* d) {
 using namespace nha;
 
 extern "C" int64_t nha_chunk_count_bound(int64_t Ttot, int64_t N) { return (Ttot + kChunk - 1) / kChunk + N; }
-extern "C" int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N) { return N + 1 + nha_chunk_count_bound(Ttot, N); }
+extern "C" int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N, int64_t H) {
+  const int64_t ncb = nha_chunk_count_bound(Ttot, N);
+  return N + 1 + ncb + ncb * H + 4;     // offsets, chunk -> sequence, per-(chunk, head) flags, error word
+}
 
 extern "C" int nha_chunk_plan(const nha_chunk_desc* d, void* stream) {
   if (!d || !d->cu_seqlens || !d->plan || d->N <= 0) return NHA_ERR_BAD_ARG;
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  nha_plan_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(d->cu_seqlens, d->plan, d->N, NCB);
+  nha_plan_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(d->cu_seqlens, d->plan, d->N, NCB, d->H);
   return check_launch();
 }
 

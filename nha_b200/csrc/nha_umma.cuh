@@ -1,0 +1,123 @@
+// Thin wrappers over the sm_100a tensor-core path: tcgen05.mma with operands in 128-byte-swizzled
+// shared memory and accumulators in tensor memory (TMEM), tcgen05.ld for the epilogues, mbarrier
+// completion.  Layout facts used by the kernels (checked on B200 against a host reference):
+//   * K-major operand tile [rows][64 bf16]: row r at (r/8)*1024 + (r%8)*128 bytes, its 16-byte chunk c
+//     stored at chunk slot c ^ (r%8); descriptor SBO = 1024; a 16-element k step advances the start
+//     address by 32 bytes.
+//   * MN-major operand tile [k rows][64 bf16 along N]: same physical layout; descriptor SBO = 1024;
+//     a 16-row k step advances the start address by 2048 bytes.
+//   * D of an M = 128 product: row r in TMEM lane r.  D of an M = 64 product: row r in lane
+//     (r/16)*32 + r%16 (each warp's 32-lane quarter holds 16 rows).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace nha {
+namespace umma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(1024 >> 4) << 16;   // LBO (not used by the single-atom-wide tiles here)
+  d |= (uint64_t)(1024 >> 4) << 32;   // SBO: 8-row group pitch
+  d |= (uint64_t)1 << 46;             // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: bf16 x bf16 -> f32, A K-major, B K-major or MN-major
+__device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
+  uint32_t d = 0;
+  d |= 1u << 4;                       // D = f32
+  d |= 1u << 7;                       // A = bf16
+  d |= 1u << 10;                      // B = bf16
+  d |= (uint32_t)b_mn_major << 16;
+  d |= (uint32_t)(N >> 3) << 17;
+  d |= (uint32_t)(M >> 4) << 24;
+  return d;
+}
+
+// byte offset of 16-byte chunk c of row r inside a swizzled [rows][64 bf16] tile
+__device__ __forceinline__ int sw_off(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+// D[M x N] (+)= A[M x 16*ksteps] * B: A K-major tile(s), B K-major (b_mn = 0) or MN-major (b_mn = 1).
+// a_tile_bytes / b_tile_bytes: distance between consecutive 64-wide k tiles of the operand.
+__device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, int a_tile_bytes, uint32_t b_addr,
+                                         int b_tile_bytes, int M, int N, int ksteps, int b_mn, bool accumulate) {
+  const uint32_t idesc = make_idesc(M, N, b_mn);
+  for (int ks = 0; ks < ksteps; ++ks) {
+    const int kt = ks >> 2, kin = ks & 3;
+    const uint64_t da = make_desc(a_addr + kt * a_tile_bytes + kin * 32);
+    const uint64_t db = b_mn ? make_desc(b_addr + ks * 2048) : make_desc(b_addr + kt * b_tile_bytes + kin * 32);
+    mma_f16(d_tmem, da, db, idesc, accumulate || ks > 0);
+  }
+}
+
+__device__ __forceinline__ void commit(uint64_t* mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar))
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* mbar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(mbar)), "r"(count));
+}
+
+// Bounded wait on an mbarrier phase; returns false when the limit is hit (the caller records an
+// error and leaves instead of spinning forever).
+__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int it = 0; it < (1 << 22) && !done; ++it) {
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(smem_u32(mbar)), "r"(parity)
+        : "memory");
+  }
+  return done != 0;
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, int cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, int cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* out) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) out[i] = __uint_as_float(r[i]);
+}
+
+}  // namespace umma
+}  // namespace nha

@@ -30,7 +30,7 @@ def test_desc_layout_and_status_strings():
     assert lib.nha_status_string(0) == b'ok'
     assert b'unsupported' in lib.nha_status_string(2)
     assert lib.nha_chunk_count_bound(130, 2) == 3 + 2
-    assert lib.nha_chunk_plan_ints(130, 2) == 3 + 5
+    assert lib.nha_chunk_plan_ints(130, 2, 3) == 3 + 5 + 5 * 3 + 4
 
 
 def test_argument_validation_needs_no_gpu():
