@@ -250,3 +250,27 @@ def chunk_nha(
     if output_final_state:
         return o, lse_swa, lse_gsa, (hkt, hvt)
     return o, lse_swa, lse_gsa
+
+
+def chunk_final_state(k_gsa, v, s, g, cu_seqlens, max_seqlen, shift, hk0=None, hv0=None, seg_chunks=0):
+    """State pass alone on flat packed ``[Ttot, H, dim]`` bf16 tensors: the fp32 slot memory
+    ``(hkt [N,H,K,M], hvt [N,H,M,V])`` after the last token that enters it.  Used by the
+    sequence-parallel prefill to summarise a rank's segment before the cross-rank scan."""
+    lib = _lib.load()
+    geo = _Geometry(k_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, seg_chunks)
+    dev = geo.device
+    sh_t, sh_all = _per_seq(shift, geo.N, dev)
+    t = dict(q_gsa=k_gsa, q_swa=k_gsa, k_gsa=k_gsa, k_swa=k_gsa, v=v, s=s, g=g, cu_seqlens=cu_seqlens, hk0=hk0, hv0=hv0)
+    t['hkt'] = torch.empty(geo.N, geo.H, geo.K, geo.M, dtype=torch.float32, device=dev)
+    t['hvt'] = torch.empty(geo.N, geo.H, geo.M, geo.V, dtype=torch.float32, device=dev)
+    t['hk_chunks'] = torch.empty(geo.ncb, geo.H, geo.K, geo.M, dtype=_BF16, device=dev)
+    t['hv_chunks'] = torch.empty(geo.ncb, geo.H, geo.M, geo.V, dtype=_BF16, device=dev)
+    d = _fill_desc(geo, t, 1.0, None, 0, sh_t, sh_all)
+    nbytes = int(lib.nha_chunk_fwd_workspace_bytes(d))
+    if nbytes > 0:
+        t['workspace'] = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        d = _fill_desc(geo, t, 1.0, None, 0, sh_t, sh_all)
+    with torch.cuda.device(dev):
+        _lib.check(lib.nha_chunk_plan(d, _stream(dev)), 'nha_chunk_plan')
+        _lib.check(lib.nha_chunk_state_pass(d, _stream(dev)), 'nha_chunk_state_pass')
+    return t['hkt'], t['hvt']

@@ -1,0 +1,66 @@
+"""CPU, world_size 2 and 3 over gloo: the host logic of the sequence-parallel prefill (halo exchange,
+segment summaries, cross-rank scan) with the oracle standing in for the CUDA arithmetic."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import nha_oracle as orc
+from tests import inputs as gen
+
+
+def _oracle_local_state(k, v, s, g, W):
+    B = k.shape[0]
+    z = torch.zeros(B, k.shape[1], k.shape[2], k.shape[3])
+    _, hk, hv = orc.prefill(z, k, v, z, k, s, g, W, 1.0)
+    return hk.float(), hv.float()
+
+
+def _oracle_forward(q, k, v, rq, rk, s, g, W, scale, state):
+    o, hk, hv = orc.prefill(q, k, v, rq, rk, s, g, W, scale, state[0], state[1])
+    return o.float(), hk.float(), hv.float()
+
+
+def _worker(rank, world, port, T, W, with_state, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        from nha_b200.sharding import sequence_parallel_prefill
+        d = gen.prefill_inputs(777, 2, 2, 2, 16, 16, 8, W, T, with_state)
+        d = {k: (v.float() if torch.is_tensor(v) else v) for k, v in d.items()}
+        bounds = [T * r // world for r in range(world + 1)]
+        a, b = bounds[rank], bounds[rank + 1]
+        seg = lambda x: x[:, a:b].contiguous()
+        st = (d['hk0'], d['hv0']) if with_state else None
+        o, (hk, hv) = sequence_parallel_prefill(seg(d['q']), seg(d['k']), seg(d['v']), seg(d['rotary_q']),
+                                                seg(d['rotary_k']), seg(d['s']), seg(d['g']), W, initial_state=st,
+                                                scale=d['scale'], local_state=_oracle_local_state,
+                                                forward=_oracle_forward)
+        ref_o, ref_hk, ref_hv = orc.prefill(d['q'], d['k'], d['v'], d['rotary_q'], d['rotary_k'], d['s'], d['g'], W,
+                                            d['scale'], d.get('hk0'), d.get('hv0'))
+        err = orc.rel_l2(o, ref_o[:, a:b])
+        if rank == world - 1:
+            err = max(err, orc.rel_l2(hk, ref_hk), orc.rel_l2(hv, ref_hv))
+        out[rank] = err
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize('world,T,W,with_state', [(2, 96, 8, False), (3, 150, 16, True), (2, 64, 32, True)])
+def test_sequence_parallel_prefill_matches_single_process(world, T, W, with_state):
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), T, W, with_state, out), nprocs=world, join=True)
+        assert len(out) == world
+        for r in range(world):
+            assert out[r] < 1e-5, f'rank {r}: rel-L2 {out[r]:.2e}'
