@@ -166,6 +166,84 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+
+# ---------------------------------------------------------------------------------------------
+def bench_decode(lib, dev, rank, world, timed, peak):
+    """Batched decode in a Qwen3-MoE-style stack: 48 layers, 32 sequences per GPU (256 over 8 GPUs), HQ=32, H=4,
+    D=128, M=64 slots, W=512 window with in-kernel rotary; one fused step per layer, 48 C-ABI calls back to back.
+    Attention only (projections and MoE are outside the operator).  Batch-sharded: no collective."""
+    B, H, NG, K, M, W, LAYERS = 32, 4, 8, 128, 64, 512, 48
+    g = torch.Generator(device='cpu').manual_seed(99 + rank)
+    mk = lambda *sh: torch.randn(*sh, generator=g).to(dev)
+    layers = []
+    for _ in range(LAYERS):
+        layers.append(dict(q=mk(B, H * NG, K).bfloat16(), k=mk(B, H, K).bfloat16(), v=mk(B, H, K).bfloat16(),
+                           g=(F.logsigmoid(mk(B, H, M)) / 8).bfloat16(), sw_k=mk(B, W, H, K).bfloat16(),
+                           sw_v=mk(B, W, H, K).bfloat16(), hk=mk(B, H, K, M) * 0.5, hv=mk(B, H, M, K) * 0.5,
+                           o=torch.empty(B, H * NG, K, device=dev, dtype=torch.bfloat16)))
+    inv = 1.0 / (10000.0 ** (torch.arange(0, K, 2, dtype=torch.float32) / K))
+    fr = torch.outer(torch.arange(32768 - W + 1, 32768 + 1, dtype=torch.float32), inv)
+    emb = torch.cat([fr, fr], -1)
+    cos, sin = emb.cos().bfloat16()[None], emb.sin().bfloat16()[None]
+    cos, sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+    ws = torch.zeros(int(lib.nha_decode_workspace_bytes(B, H * NG, H, K, W)), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        for d in layers:
+            st = lib.nha_decode_step(d['q'].data_ptr(), None, d['k'].data_ptr(), d['v'].data_ptr(), d['g'].data_ptr(), None,
+                                     d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), cos.data_ptr(), sin.data_ptr(), 0,
+                                     cos.stride(1), None, d['hk'].data_ptr(), d['hv'].data_ptr(), 0, d['o'].data_ptr(), None,
+                                     ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, K ** -0.5, stream)
+            assert st == 0
+    for _ in range(3):
+        step()
+    ms = timed(step, 10) / 10
+    per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
+    gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
+    return {'workload': 'decode 48 layers x 32 seq/GPU HQ32 H4 D128 M64 W512 bf16, fp32 state', 'ms_per_token_step': ms,
+            'tokens_per_s': world * B / (ms * 1e-3), 'us_per_layer': 1e3 * ms / LAYERS,
+            'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': peak, 'unit': 'GB/s', 'frac': gbs / peak,
+                         'algorithmic_bytes_per_launch': per_seq_layer * B}, 'gpu_launches_per_step': LAYERS}
+
+
+def bench_prefill(dev, rank, world, dist, timed):
+    """Long-context prefill, Llama-3-8B attention shape: B=1 T=131072 HQ=32 H=8 D=128 M=64 W=512 bf16, forward.
+    With N > 1 the sequence is cut into N contiguous segments (sequence parallel: halo + all-gather of state summaries)."""
+    import nha_b200
+    from nha_b200.sharding import sequence_parallel_prefill
+    T, HQ, H, K, M, W = 131072, 32, 8, 128, 64, 512
+    Tr = T // world
+    g = torch.Generator(device='cpu').manual_seed(7 + rank)
+    mk = lambda *sh: torch.randn(*sh, generator=g).bfloat16().to(dev)
+    q, rq = mk(1, Tr, HQ, K), mk(1, Tr, HQ, K)
+    k, rk, v = mk(1, Tr, H, K), mk(1, Tr, H, K), mk(1, Tr, H, K)
+    gl = F.logsigmoid(torch.randn(1, Tr, H, M, generator=g)) / 8
+    gg, ss = gl.bfloat16().to(dev), (1 - gl.exp()).bfloat16().to(dev)
+
+    def step():
+        if world == 1:
+            return nha_b200.fused_chunk_nha_prefill(q=q, k=k, v=v, rotary_q=rq, rotary_k=rk, s=ss, g=gg, window_size=W,
+                                                    output_final_state=True)
+        return sequence_parallel_prefill(q, k, v, rq, rk, ss, gg, W)
+    for _ in range(2):
+        step()
+    ms = timed(step, 5) / 5
+    flops = T * 9699328.0
+    return {'workload': f'prefill fwd B1 T131072 HQ32 H8 D128 M64 W512 bf16, sequence-parallel x{world}', 'ms': ms,
+            'tokens_per_s': T / (ms * 1e-3), 'tflops': flops / (ms * 1e-3) / 1e12,
+            'roofline': {'bound': 'tensor', 'achieved': flops / (ms * 1e-3) / 1e12 / world,
+                         'peak': tensor_peak(), 'unit': 'TFLOP/s per GPU',
+                         'frac': flops / (ms * 1e-3) / 1e12 / world / tensor_peak()}}
+
+
+def tensor_peak():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        return float(json.load(open(p))['bf16_tflops'])
+    return 1590.0
+
+
 # ---------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -175,6 +253,7 @@ def main():
     ap.add_argument('--impl', default='ours')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-extras', action='store_true', help='skip the decode and long-context prefill side measurements')
     ap.add_argument('--small', action='store_true', help='B=4 instead of 16 (profiling captures)')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -318,6 +397,13 @@ def main():
         e2e = {'value': world * tokens * args.steps / (ems * 1e-3), 'unit': UNIT, 'h2d_bytes_per_step': h2d,
                'd2h_bytes_per_step': d2h, 'ms_per_step': ems / args.steps}
 
+
+    # ---- side measurements (not the headline): batched decode and long-context prefill ---------------------
+    extras = None
+    if not args.no_extras and not args.small:
+        extras = {'decode': bench_decode(lib, dev, rank, world, timed, peak),
+                  'prefill': bench_prefill(dev, rank, world, dist, timed)}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         Ts = 1024
@@ -335,7 +421,7 @@ def main():
                        'parallelism': f'batch-sharded x{world}, no collective',
                        'l2': 'inputs of one step (0.54 GB) exceed the 126 MB L2; no flush between steps'},
             'roofline': roofline, 'step_roofline': step_roofline, 'kernels': kernels,
-            'cpu_baseline': cpu, 'e2e': e2e, 'gpu_launches': launches_per_step * args.steps,
+            'cpu_baseline': cpu, 'e2e': e2e, 'gpu_launches': launches_per_step * args.steps, 'extras': extras,
             'clocks': clk.summary(),
         }
         print(json.dumps(line), flush=True)
