@@ -6,16 +6,21 @@
 //   2. window columns (chunk-parallel)  dk_swa = scale * dz_win^T q_swa, dv_win = p_win^T do
 //   3. slot pass      (chunk-parallel)  dq_gsa and the parts of dk', dv', ds' that stay inside a chunk,
 //                                       dgA = ok .* dz + p .* dp, and the decayed dz / p the march needs
-//   4. reverse march  (per sequence and kv head, last chunk first) carries the gradients DK, DV of
-//      the slot memory across chunks, adds the inter-chunk parts of dk', dv', ds', turns
-//      dgA - s' .* ds' into dg by a reverse cumulative sum, undoes the shift, writes the results.
+//   4. state-gradient march (16-row / 16-column slices per sequence and kv head, last chunk first)
+//      stores the gradients DK, DV of the slot memory at every chunk end; the inter-chunk pass
+//      (chunk-parallel) adds the inter-chunk parts of dk', dv', ds', turns dgA - s' .* ds' into dg by a
+//      reverse cumulative sum inside the chunk plus a carry rebuilt from <DK,hk> + <DV,hv>, undoes the
+//      shift and writes the results.
 // Primes are the inputs shifted right by gsa_kv_shift inside their sequence.
 //
 // Replaces ChunkNativeHybridAttentionFunction.backward (nha_fla/ops/nha/chunk.py:491-564): the
 // flash-attn varlen backward called with the merged output and the joint LSE (:500-512), fla's
 // chunk_gsa backward with the folded d_lse (nha_fla/ops/nha/chunk_gsa.py:52-122) and the shift
 // adjoints (chunk.py:80-126).  A gradient on lse_swa is ignored, as there (:491-512).
+#include <stdlib.h>
+
 #include "nha_common.cuh"
+#include "nha_bwd_common.cuh"
 
 namespace nha {
 
@@ -27,51 +32,6 @@ __device__ __forceinline__ int sb_row0b(int I) { return 8 * I * (I + 1); }
 __device__ __forceinline__ float block_refb(const float* G, int ldg, int I, int m) {
   const float gn = I > 0 ? G[(16 * I - 1) * ldg + m] : 0.f;
   return 0.5f * (gn + G[(16 * I + 15) * ldg + m]);
-}
-
-struct BwdWs {
-  float* delta;   // [Ttot, HQ]      <do, o>
-  float* lj;      // [Ttot, HQ]      joint log-sum-exp
-  float* dvacc;   // [Ttot, H, V]    window part of dv
-  float* dkp;     // [Ttot, H, K]    intra-chunk part of dk' (row = shifted position)
-  float* dvp;     // [Ttot, H, V]    intra-chunk part of dv'
-  float* dsp;     // [Ttot, H, M]    intra-chunk part of ds'
-  float* dga;     // [Ttot, H, M]    ok .* dz + p .* dp summed over the group
-  bf16* dzg;      // [Ttot, HQ, M]   scale * dz_slot .* exp(G)
-  bf16* pgq;      // [Ttot, HQ, M]   p_slot .* exp(G)
-};
-
-__host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* base) {
-  int64_t off = 0;
-  auto take = [&](int64_t bytes) { int64_t o = off; off = (off + bytes + 255) & ~(int64_t)255; return o; };
-  const int64_t T = d->Ttot;
-  const int64_t o_delta = take(T * d->HQ * 4), o_lj = take(T * d->HQ * 4), o_dvacc = take(T * d->H * d->V * 4);
-  const int64_t o_dkp = take(T * d->H * d->K * 4), o_dvp = take(T * d->H * d->V * 4);
-  const int64_t o_dsp = take(T * d->H * d->M * 4), o_dga = take(T * d->H * d->M * 4);
-  const int64_t o_dzg = take(T * d->HQ * d->M * 2), o_pgq = take(T * d->HQ * d->M * 2);
-  if (w && base) {
-    char* b = (char*)base;
-    w->delta = (float*)(b + o_delta); w->lj = (float*)(b + o_lj); w->dvacc = (float*)(b + o_dvacc);
-    w->dkp = (float*)(b + o_dkp); w->dvp = (float*)(b + o_dvp); w->dsp = (float*)(b + o_dsp);
-    w->dga = (float*)(b + o_dga); w->dzg = (bf16*)(b + o_dzg); w->pgq = (bf16*)(b + o_pgq);
-  }
-  return off;
-}
-
-struct ChunkCtx {
-  int n, ci, t0, len, c0, wl, shift;
-};
-
-__device__ __forceinline__ bool chunk_ctx(const nha_chunk_desc& d, int cg, ChunkCtx& c) {
-  c.n = d.plan[d.N + 1 + cg];
-  if (c.n < 0) return false;
-  c.ci = cg - d.plan[c.n];
-  c.t0 = d.cu_seqlens[c.n];
-  c.len = d.cu_seqlens[c.n + 1] - c.t0;
-  c.c0 = c.ci * kChunk;
-  c.wl = seq_window(d, c.n);
-  c.shift = seq_shift(d, c.n);
-  return true;
 }
 
 // ================================================================================================
@@ -96,6 +56,7 @@ __host__ __device__ inline WRowLayout wrow_layout(int K, int V) {
 __global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const nha_chunk_desc d, const BwdWs w) {
   ChunkCtx c;
   if (!chunk_ctx(d, blockIdx.x, c)) return;
+  if (!chunk_gate(w, blockIdx.x, blockIdx.y, d.H)) return;
   const int K = d.K, V = d.V, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -371,6 +332,7 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chun
   ChunkCtx c;
   const int cg = blockIdx.x;
   if (!chunk_ctx(d, cg, c)) return;
+  if (!chunk_gate(w, cg, blockIdx.y, d.H)) return;
   const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -615,9 +577,107 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chun
 }
 
 // ================================================================================================
-// 4. reverse march over the chunks of one (sequence, kv head)
+// 4a. state-gradient march: DK (gradient of hk) and DV (gradient of hv) at the end of every chunk.
+//     Like the forward state pass in reverse: one CTA owns 16 rows of DK or 16 columns of DV of one
+//     (sequence, kv head) and walks its chunks last to first,
+//         D_end[c-1] = D_end[c] .* exp(Gend_c) + (local term of chunk c),
+//     local terms q^T (scale dz exp G) and (p exp G)^T do summed over the query heads of the group.
 // ================================================================================================
-struct MarchLayout { int kp, vp, sp, sbe, G, DK, DV, DKb, DVb, qb, dob, zg, pg, X, cg, red, total; };
+constexpr int kSgThreads = 128;
+constexpr int kSgWarps = kSgThreads / 32;
+
+__global__ void __launch_bounds__(kSgThreads) nha_bwd_stategrad_kernel(const nha_chunk_desc d, const BwdWs w) {
+  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
+  const int nks = K / 16;
+  const int slice = blockIdx.x;
+  const bool is_k = slice < nks;
+  const int s0 = (is_k ? slice : slice - nks) * 16;
+  const int n = blockIdx.y / H, h = blockIdx.y % H;
+  const int t0 = d.cu_seqlens[n];
+  const int len = d.cu_seqlens[n + 1] - t0;
+  const int shift = seq_shift(d, n);
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int chunk0 = d.plan[n];
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const size_t nh = (size_t)n * H + h;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int ldm = M + 8, ldx = 16 + 8;
+  bf16* zt = (bf16*)smem;                                   // [64][M+8] scale dz exp G, or p exp G
+  bf16* xt = zt + kChunk * ldm;                             // [64][24]  slice of q or of do
+  float* hs = (float*)(xt + kChunk * ldx);                  // DK slice [16][M+4] or DV slice [M][16+4]
+  const int ldh = is_k ? M + 4 : 16 + 4;
+  const int hrows = is_k ? 16 : M, hcols = is_k ? M : 16;
+  float* gend = hs + (is_k ? 16 * (M + 4) : M * 20);        // [M]
+  for (int i = tid; i < hrows * hcols; i += kSgThreads) {
+    const int r = i / hcols, c = i - r * hcols;
+    float val = 0.f;
+    if (is_k) { if (d.d_hkt) val = d.d_hkt[nh * K * M + (size_t)(s0 + r) * M + c]; }
+    else { if (d.d_hvt) val = d.d_hvt[nh * M * V + (size_t)r * V + s0 + c]; }
+    hs[r * ldh + c] = val;
+  }
+  __syncthreads();
+  const bf16* gg = (const bf16*)d.g + ((size_t)t0 * H + h) * M;
+  for (int ci = nchunks - 1; ci >= 0; --ci) {
+    const int c0 = ci * kChunk;
+    // ---- emit the gradient at this chunk's end
+    {
+      const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+      if (is_k) {
+        float* dst = w.dkc + cgi * K * M + (size_t)s0 * M;
+        for (int i = tid; i < 16 * M; i += kSgThreads) dst[i] = hs[(i / M) * ldh + (i % M)];
+      } else {
+        float* dst = w.dvc + cgi * M * V + s0;
+        for (int i = tid; i < M * 16; i += kSgThreads) dst[(size_t)(i / 16) * V + (i % 16)] = hs[(i / 16) * ldh + (i % 16)];
+      }
+    }
+    // ---- total shifted log gate of the chunk per slot
+    {
+      // rows of the chunk whose shifted source exists: j = c0 + r - shift in [0, len - shift)
+      const int r_lo = max(0, shift - c0), r_hi = min(kChunk, len - c0);
+      for (int m = tid; m < M; m += kSgThreads) {
+        float acc = 0.f;
+        const bf16* col = gg + (size_t)(c0 - shift) * H * M + m;
+#pragma unroll 8
+        for (int r = r_lo; r < r_hi; ++r) acc += bf2f(col[(size_t)r * H * M]);
+        gend[m] = acc;
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < hrows * hcols; i += kSgThreads) {
+      const int r = i / hcols, cc = i - r * hcols;
+      hs[r * ldh + cc] *= __expf(gend[is_k ? cc : r]);
+    }
+    for (int qh = 0; qh < NG; ++qh) {
+      const int hq = h * NG + qh;
+      __syncthreads();
+      load_tile_bf16(zt, ldm, (is_k ? w.dzg : w.pgq) + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid,
+                     kSgThreads);
+      const bf16* xsrc = is_k ? (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq) * K + s0
+                              : (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * V + s0;
+      load_tile_bf16(xt, ldx, xsrc, (int64_t)HQ * (is_k ? K : V), c0, 0, len, kChunk, 16, tid, kSgThreads);
+      __syncthreads();
+      if (is_k) tile_gemm<false, true, true>(hs, ldh, xt, ldx, zt, ldm, 1, M / 16, kChunk / 16, warp, kSgWarps);
+      else tile_gemm<false, true, true>(hs, ldh, zt, ldm, xt, ldx, M / 16, 1, kChunk / 16, warp, kSgWarps);
+    }
+    __syncthreads();
+  }
+  if (is_k && d.dhk0)
+    for (int i = tid; i < 16 * M; i += kSgThreads) d.dhk0[nh * K * M + (size_t)s0 * M + i] = hs[(i / M) * ldh + (i % M)];
+  if (!is_k && d.dhv0)
+    for (int i = tid; i < M * 16; i += kSgThreads) d.dhv0[nh * M * V + (size_t)(i / 16) * V + s0 + (i % 16)] = hs[(i / 16) * ldh + (i % 16)];
+}
+
+static int stategrad_smem(int M) {
+  const int hs = (16 * (M + 4) > M * 20 ? 16 * (M + 4) : M * 20) * 4;
+  return kChunk * (M + 8) * 2 + kChunk * 24 * 2 + hs + M * 4 + 128;
+}
+
+// ================================================================================================
+// 4b. inter-chunk pass (chunk-parallel): with DK, DV at the chunk's end, adds the inter-chunk parts of
+//     dk', dv', ds', turns dgA - s' .* ds' into dg (reverse cumulative sum inside the chunk plus the
+//     carry of all later chunks), undoes the shift and writes dk_gsa, dv, ds, dg.
+// ================================================================================================
+struct MarchLayout { int kp, vp, sp, sbe, G, DK, DV, DKb, DVb, X, cg, red, total; };
 __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   MarchLayout L; int off = 0;
   const int kv_ = K > V ? K : V;
@@ -631,10 +691,6 @@ __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   L.DV = off; off = bup128(off + M * (V + 4) * 4);
   L.DKb = off; off = bup128(off + K * (M + 8) * 2);
   L.DVb = off; off = bup128(off + M * (V + 8) * 2);
-  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
-  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
-  L.zg = off; off = bup128(off + kChunk * (M + 8) * 2);
-  L.pg = off; off = bup128(off + kChunk * (M + 8) * 2);
   L.X = off; off = bup128(off + kChunk * (mx + 4) * 4);
   L.cg = off; off = bup128(off + M * 4);
   L.red = off; off = bup128(off + kBwThreads * 4);
@@ -642,12 +698,19 @@ __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   return L;
 }
 
-__global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chunk_desc d, const BwdWs w) {
-  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
-  const int n = blockIdx.x / H, h = blockIdx.x % H;
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
-  const int shift = seq_shift(d, n);
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chunk_desc d, const BwdWs w) {
+  ChunkCtx c;
+  const int cgx = blockIdx.x;
+  if (!chunk_ctx(d, cgx, c)) return;
+  // a chunk that another kernel handles is skipped, except that the CTA of a sequence's first chunk
+  // always finishes the tail rows at the end of this kernel
+  const bool mine = chunk_gate(w, cgx, blockIdx.y, d.H);
+  if (!mine && c.ci != 0) return;
+  const int K = d.K, V = d.V, M = d.M, H = d.H;
+  const int n = c.n, h = blockIdx.y;
+  const int t0 = c.t0;
+  const int len = c.len;
+  const int shift = c.shift;
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int tid = threadIdx.x, warp = tid >> 5;
   const size_t nh = (size_t)n * H + h;
@@ -664,21 +727,23 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
   float* DV = (float*)(smem + L.DV);        // [M][V+4]
   bf16* DKb = (bf16*)(smem + L.DKb);        // [K][M+8]
   bf16* DVb = (bf16*)(smem + L.DVb);        // [M][V+8]
-  bf16* qb = (bf16*)(smem + L.qb);
-  bf16* dob = (bf16*)(smem + L.dob);
-  bf16* zg = (bf16*)(smem + L.zg);
-  bf16* pg = (bf16*)(smem + L.pg);
   float* X = (float*)(smem + L.X);
   float* cgv = (float*)(smem + L.cg);
   float* red = (float*)(smem + L.red);
   const int chunk0 = d.plan[n];
 
-  // ---- gradients arriving on the final state ---------------------------------------------------------
-  for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] = d.d_hkt ? d.d_hkt[nh * K * M + i] : 0.f;
-  for (int i = tid; i < M * V; i += kBwThreads) DV[(i / V) * lddv + (i % V)] = d.d_hvt ? d.d_hvt[nh * M * V + i] : 0.f;
+  const int ci = c.ci;
+  if (mine) {
+  // ---- state gradients at this chunk's end
+  {
+    const float* dkg = w.dkc + ((size_t)cgx * H + h) * K * M;
+    const float* dvg = w.dvc + ((size_t)cgx * H + h) * M * V;
+    for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] = dkg[i];
+    for (int i = tid; i < M * V; i += kBwThreads) DV[(i / V) * lddv + (i % V)] = dvg[i];
+  }
   for (int m = tid; m < M; m += kBwThreads) {
     float acc = 0.f;
-    if (d.d_hkt && d.hkt && d.hvt) {
+    if (ci == nchunks - 1 && d.d_hkt && d.hkt && d.hvt) {
       for (int kk = 0; kk < K; ++kk) acc += d.d_hkt[nh * K * M + (size_t)kk * M + m] * d.hkt[nh * K * M + (size_t)kk * M + m];
       for (int vv = 0; vv < V; ++vv) acc += d.d_hvt[nh * M * V + (size_t)m * V + vv] * d.hvt[nh * M * V + (size_t)m * V + vv];
     }
@@ -686,7 +751,7 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
   }
   __syncthreads();
 
-  for (int ci = nchunks - 1; ci >= 0; --ci) {
+  {
     const int c0 = ci * kChunk;
     const int lo = 0, hi = len - shift;
     // ---- gate-gradient carry of all later chunks, rebuilt from the state and its gradient at this
@@ -803,27 +868,11 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
         const int p = c0 + r, j = p - shift;
         if (j >= 0 && p < len) ((bf16*)d.dg)[((size_t)(t0 + j) * H + h) * M + m] = f2bf(run);
       }
-      cgv[m] = run;
     }
-    // ---- carry DK, DV to the chunk start -------------------------------------------------------------------
-    for (int i = tid; i < K * M; i += kBwThreads) DK[(i / M) * lddk + (i % M)] *= __expf(G[(kChunk - 1) * ldg + (i % M)]);
-    for (int i = tid; i < M * V; i += kBwThreads) DV[(i / V) * lddv + (i % V)] *= __expf(G[(kChunk - 1) * ldg + (i / V)]);
-    for (int qh = 0; qh < NG; ++qh) {
-      const int hq = h * NG + qh;
-      __syncthreads();
-      load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K, tid,
-                     kBwThreads);
-      load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * V, (int64_t)HQ * V, c0, 0, len, kChunk, V, tid,
-                     kBwThreads);
-      load_tile_bf16(zg, ldm, w.dzg + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid, kBwThreads);
-      load_tile_bf16(pg, ldm, w.pgq + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid, kBwThreads);
-      __syncthreads();
-      tile_gemm<false, true, true>(DK, lddk, qb, ldk, zg, ldm, K / 16, M / 16, 4, warp, kBwWarps);   // q^T (scale dz exp G)
-      tile_gemm<false, true, true>(DV, lddv, pg, ldm, dob, ldv, M / 16, V / 16, 4, warp, kBwWarps);  // (p exp G)^T do
-    }
-    __syncthreads();
   }
-  // ---- tokens that never enter the slot memory; gradients of the initial state -----------------------------
+  }  // mine
+  // ---- tokens that never enter the slot memory (done by the CTA of the sequence's first chunk) ---------------
+  if (ci != 0) return;
   const int tail0 = max(0, len - shift);
   for (int i = tid; i < (len - tail0) * (V / 8); i += kBwThreads) {
     const int j = tail0 + i / (V / 8), c8 = i % (V / 8);
@@ -840,13 +889,12 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_march_kernel(const nha_chu
     *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = z4;
     *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = z4;
   }
-  if (d.dhk0)
-    for (int i = tid; i < K * M; i += kBwThreads) d.dhk0[nh * K * M + i] = DK[(i / M) * lddk + (i % M)];
-  if (d.dhv0)
-    for (int i = tid; i < M * V; i += kBwThreads) d.dhv0[nh * M * V + i] = DV[(i / V) * lddv + (i % V)];
 }
 
+
 int check_chunk_desc(const nha_chunk_desc* d);
+bool bwd_umma_supported(const nha_chunk_desc* d);
+int bwd_umma_launch(const nha_chunk_desc* d, const BwdWs& w, int which, int* err, cudaStream_t cs);
 
 }  // namespace nha
 
@@ -883,12 +931,32 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   if (e != cudaSuccess) return record_cuda_error(e);
   e = cudaFuncSetAttribute(nha_bwd_slot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L3.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  e = cudaFuncSetAttribute(nha_bwd_march_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L4.total);
+  e = cudaFuncSetAttribute(nha_bwd_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L4.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int sg_smem = stategrad_smem(d->M);
+  e = cudaFuncSetAttribute(nha_bwd_stategrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sg_smem);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kBwThreads);
+  // Shapes with tensor-memory kernels: those handle every chunk the forward did not flag, the general
+  // kernels below are launched gated on the flags and pick up the rest.
+  const char* off = getenv("NHA_B200_NO_UMMA");
+  const bool umma = bwd_umma_supported(d) && !(off && off[0] == '1');
+  int* flags = d->plan + d->N + 1 + NCB;
+  int* err = flags + (size_t)NCB * d->H;
+  BwdWs wu = w, wg = w;                 // tensor-memory kernels: unflagged chunks; general kernels: flagged ones
+  if (umma) {
+    wu.flags = flags; wu.gate = 2;
+    wg.flags = flags; wg.gate = 1;
+  }
   if (stage_mask & 1) {
-    nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, w);
+    if (umma) {
+      cudaError_t e2 = cudaMemsetAsync(w.dga, 0, (size_t)d->Ttot * d->H * d->M * sizeof(float), cs);
+      if (e2 != cudaSuccess) return record_cuda_error(e2);
+      st = bwd_umma_launch(d, wu, 0, err, cs);
+      if (st != NHA_OK) return st;
+    }
+    nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, wg);
     st = check_launch();
     if (st != NHA_OK) return st;
   }
@@ -898,12 +966,19 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 4) {
-    nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, w);
+    nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, wg);
     st = check_launch();
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 8) {
-    nha_bwd_march_kernel<<<dim3(d->N * d->H), block, L4.total, cs>>>(*d, w);
+    nha_bwd_stategrad_kernel<<<dim3(d->K / 16 + d->V / 16, d->N * d->H), kSgThreads, sg_smem, cs>>>(*d, w);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+    if (umma) {
+      st = bwd_umma_launch(d, wu, 1, err, cs);
+      if (st != NHA_OK) return st;
+    }
+    nha_bwd_inter_kernel<<<grid, block, L4.total, cs>>>(*d, wg);
     st = check_launch();
   }
   return st;

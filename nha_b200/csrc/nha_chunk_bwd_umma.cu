@@ -1,0 +1,732 @@
+// Backward of the chunked NHA operator on the sm_100a tensor-core path (tcgen05.mma, accumulators in
+// tensor memory, one thread per row for the element-wise work).  Two chunk-parallel kernels bracket the
+// state-gradient march of nha_chunk_bwd.cu:
+//
+//   rows pass  (per chunk, kv head; query-row side)
+//       ok, p_slot recomputed as in the forward;  dp_slot = exp(G) .* (do Hv^T) + a .* (tril(do v'^T) SB)
+//       dz_slot = p (dp - delta) + d_lse_gsa softmax(ok);  dz_win = p_win (do v_win^T - delta)
+//       dq_gsa = scale (dz exp G) Hk^T + tril(scale (dz a) SB^T) k',   dq_swa = scale dz_win k_swa
+//       stores delta, the joint LSE, dgA = ok dz + p dp, and the bf16 copies of dz and p (decayed by
+//       exp(G) for the march, by a for the columns pass)
+//   columns pass (per chunk, kv head; key-row side), after the march has left DK, DV at every chunk end
+//       dk' = tril(dza SB^T)^T q + sbe DK^T,   dv' = tril(pa SB^T)^T do + sbe DV
+//       ds' = b .* (tril(q k'^T)^T dza + tril(do v'^T)^T pa) + be .* (k' DK + v' DV^T)
+//       dg  = reverse cumulative sum of dgA - s' ds' inside the chunk + carry <DK,hk> + <DV,hv>
+//       un-shifted stores of dk_gsa, dv (+ window part), ds, dg
+//   (SB = s' .* b, sbe = s' .* exp(Gend - G), a = exp(G - R), b = exp(R - G), R = Gend / 2 per slot.)
+// Transposed products use MN-major operand descriptors, so no tile is ever transposed in memory.
+// Chunks the forward flagged (gates too steep for the single reference R) are skipped here and
+// handled by the general kernels.
+//
+// Replaces, with nha_chunk_bwd.cu, ChunkNativeHybridAttentionFunction.backward
+// (nha_fla/ops/nha/chunk.py:491-564) and chunk_gsa_bwd_with_lse (nha_fla/ops/nha/chunk_gsa.py:52-122).
+#include "nha_bwd_common.cuh"
+#include "nha_common.cuh"
+#include "nha_umma.cuh"
+
+namespace nha {
+
+using namespace umma;
+
+constexpr int kBUThreads = 128;
+
+// ================================================================================================
+// rows pass
+// ================================================================================================
+template <int D, int R>
+struct RowsLayout {
+  static constexpr int KT = D / 64;
+  static constexpr int kATile = R * 128;
+  static constexpr int tQ = 0;                          // q_gsa; reused for the window key/value tiles
+  static constexpr int tQS = tQ + KT * kATile;          // q_swa
+  static constexpr int tDO = tQS + KT * kATile;         // do
+  static constexpr int tK = tDO + KT * kATile;          // k'
+  static constexpr int tV = tK + KT * 8192;             // v'
+  static constexpr int tHk = tV + KT * 8192;            // Hk [D][64]
+  static constexpr int tHv = tHk + D * 128;             // Hv [64][D]
+  static constexpr int tSB = tHv + KT * 8192;           // s' .* b
+  static constexpr int tWVx = tSB + 8192;               // window values when they do not fit behind tQ
+  static constexpr int bufA = tWVx + (R == 128 ? 0 : KT * 8192);   // tril(A) -> dza -> tril(E) -> dz_win
+  static constexpr int bufB = bufA + kATile;            // tril(Av) -> dzg
+  static constexpr int oG = bufB + kATile;
+  static constexpr int oR = oG + 64 * 65 * 4;
+  static constexpr int oBar = oR + 256;
+  static constexpr int total = oBar + 64 + 1024;
+  static constexpr int tW = tQ;
+  static constexpr int tWV = R == 128 ? tQ + KT * 8192 : tWVx;
+  static constexpr int cA = 0, cAv = 64, cQH = 128, cY = 192, cDQ = 256, cDQS = 256 + D;
+  static constexpr int cS = cQH, cDP = cY;
+};
+
+template <int D, int R>
+__global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha_chunk_desc d, const BwdWs w,
+                                                                       int* __restrict__ err) {
+  typedef RowsLayout<D, R> L;
+  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int n = d.plan[N + 1 + cg];
+  if (n < 0) return;
+  if (!chunk_gate(w, cg, h, H)) return;
+  const int ci = cg - d.plan[n];
+  const int t0 = d.cu_seqlens[n];
+  const int len = d.cu_seqlens[n + 1] - t0;
+  const int c0 = ci * kChunk;
+  const int wl = seq_window(d, n);
+  const int shift = seq_shift(d, n);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* Gs = (float*)(sm + L::oG);
+  float* Rs = (float*)(sm + L::oR);
+  uint64_t* mbar = (uint64_t*)(sm + L::oBar);
+  uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
+
+  const int lo = 0, hi = len - shift;
+  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<64>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
+  cp_commit();
+  uint4 sreg[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kBUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    const int src = c0 + r - shift;
+    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= lo && src < hi) {
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
+      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+  }
+  if (tid == 0) mbar_init(mbar, 1);
+  __syncthreads();
+  {
+    const int m = tid & 63, half = tid >> 6;
+    float run = 0.f;
+#pragma unroll 8
+    for (int r = 32 * half; r < 32 * half + 32; ++r) {
+      run += Gs[r * 65 + m];
+      Gs[r * 65 + m] = run;
+    }
+    __syncthreads();
+    if (half == 1) {
+      const float add = Gs[31 * 65 + m];
+#pragma unroll 8
+      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+    }
+    __syncthreads();
+  }
+  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kBUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    float sv[8], out[8];
+    unpack8(sreg[j], sv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(out);
+  }
+  if (warp == 0) tmem_alloc(tslot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tslot;
+  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  uint32_t phase = 0;
+  bool failed = false;
+
+  const bool active = R == 128 ? true : lane < 16;
+  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int tk = row & 63, th = row >> 6;
+  const int pos = c0 + tk;
+  const bool in_seq = pos < len;
+  const bool live = active && in_seq;
+  const int jt_hi = ci;
+  const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
+  const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aDO = smem_u32(sm + L::tDO);
+  const uint32_t aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk);
+  const uint32_t aHv = smem_u32(sm + L::tHv), aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW);
+  const uint32_t aWV = smem_u32(sm + L::tWV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
+  const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
+  const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
+
+#define NHA_MMA_WAIT()                                   \
+  do {                                                   \
+    if (tid == 0) commit(mbar);                          \
+    if (!mbar_wait(mbar, phase)) failed = true;          \
+    phase ^= 1;                                          \
+    tc_fence_after();                                    \
+  } while (0)
+#define NHA_SMEM_TO_MMA()                                \
+  do {                                                   \
+    fence_async_smem();                                  \
+    tc_fence_before();                                   \
+    __syncthreads();                                     \
+    tc_fence_after();                                    \
+  } while (0)
+// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+#define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
+  do {                                                                                           \
+    float tv_[32];                                                                               \
+    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
+      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
+      if (active) {                                                                              \
+        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
+          float o8[8];                                                                           \
+          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
+            const int i_ = 32 * part + 8 * c8 + e;                                               \
+            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
+          }                                                                                      \
+          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+        }                                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  } while (0)
+
+  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+    const int hq0 = h * NG + ht * TH;
+    const int hq = hq0 + th;
+    const size_t rowq = (size_t)(t0 + pos) * HQ + hq;          // (token, query head) index of this thread's row
+    // ---- tiles of this head tile -------------------------------------------------------------------------
+#pragma unroll
+    for (int t2 = 0; t2 < TH; ++t2) {
+      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
+                 64, 64 * t2, tid);
+      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0,
+                 len, 64, 64 * t2, tid);
+      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
+                 64, 64 * t2, tid);
+    }
+    cp_commit();
+    // per-row scalars: delta = <do, o>, joint LSE, lse_gsa, d_lse_gsa
+    float delta = 0.f, Lj = 0.f, lse_g = 0.f, dlse = 0.f;
+    if (live) {
+      const bf16* orow = (const bf16*)d.o + rowq * D;
+      const bf16* grow = (const bf16*)d.d_o + rowq * D;
+#pragma unroll
+      for (int c8 = 0; c8 < D / 8; ++c8) {
+        float a8[8], b8[8];
+        unpack8(*reinterpret_cast<const uint4*>(orow + 8 * c8), a8);
+        unpack8(*reinterpret_cast<const uint4*>(grow + 8 * c8), b8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) delta += a8[e] * b8[e];
+      }
+      const float ls = d.lse_swa[rowq];
+      lse_g = d.lse_gsa[rowq];
+      const float mx = fmaxf(ls, lse_g);
+      Lj = mx + __logf(__expf(ls - mx) + __expf(lse_g - mx));
+      dlse = d.d_lse_gsa ? d.d_lse_gsa[rowq] : 0.f;
+      w.delta[rowq] = delta;
+      w.lj[rowq] = Lj;
+    }
+    cp_wait_all();
+    NHA_SMEM_TO_MMA();
+    // ---- A = q k'^T, Av = do v'^T, QH = q Hk, Y0 = do Hv^T ---------------------------------------------------
+    if (tid == 0) {
+      mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
+      mma_tile(tbase + L::cAv, aDO, L::kATile, aV, 8192, R, 64, D / 16, 0, false);
+      mma_tile(tbase + L::cQH, aQ, L::kATile, aHk, 0, R, 64, D / 16, 1, false);
+      mma_tile(tbase + L::cY, aDO, L::kATile, aHv, 8192, R, 64, D / 16, 0, false);      // Hv tiles as K-major [m][v]
+    }
+    NHA_MMA_WAIT();
+    NHA_TRIL_TO_SMEM(L::cA, L::bufA);
+    NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+      mma_tile(tbase + L::cA, aA, L::kATile, aSB, 0, R, 64, 4, 1, false);               // X  = tril(A)  SB
+      mma_tile(tbase + L::cAv, aB, L::kATile, aSB, 0, R, 64, 4, 1, false);              // X2 = tril(Av) SB
+    }
+    NHA_MMA_WAIT();
+    // ---- slot part of dz; decayed bf16 copies; dgA -------------------------------------------------------------
+    // (the MMAs that read bufA / bufB have completed, so the tiles can take dza / dzg now)
+    {
+      float qh[32], xv[32], y0[32], x2[32];
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        tmem_ld32(tlane + L::cQH + 32 * part, qh);
+        tmem_ld32(tlane + L::cA + 32 * part, xv);
+        tmem_ld32(tlane + L::cY + 32 * part, y0);
+        tmem_ld32(tlane + L::cAv + 32 * part, x2);
+        if (active) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            float zg8[8], za8[8], pg8[8], pa8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int m = 32 * part + 8 * c8 + e;
+              const float gl = Gs[tk * 65 + m];
+              const float eg = __expf(gl), aI = __expf(gl - Rs[m]);
+              const float ok = d.scale * (eg * qh[8 * c8 + e] + aI * xv[8 * c8 + e]);
+              const float dps = eg * y0[8 * c8 + e] + aI * x2[8 * c8 + e];
+              float ps = 0.f, dz = 0.f;
+              if (in_seq) {
+                ps = __expf(ok - Lj);
+                dz = ps * (dps - delta) + dlse * __expf(ok - lse_g);
+                atomicAdd(w.dga + ((size_t)(t0 + pos) * H + h) * M + m, ok * dz + ps * dps);
+              }
+              zg8[e] = d.scale * dz * eg;
+              za8[e] = d.scale * dz * aI;
+              pg8[e] = ps * eg;
+              pa8[e] = ps * aI;
+            }
+            const uint4 zg = pack8(zg8), za = pack8(za8);
+            *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, 4 * part + c8)) = zg;
+            *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * part + c8)) = za;
+            if (in_seq) {
+              const size_t gi = rowq * M + 32 * part + 8 * c8;
+              *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
+              *reinterpret_cast<uint4*>(w.dza + gi) = za;
+              *reinterpret_cast<uint4*>(w.pgq + gi) = pack8(pg8);
+              *reinterpret_cast<uint4*>(w.paq + gi) = pack8(pa8);
+            }
+          }
+        }
+      }
+    }
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) mma_tile(tbase + L::cA, aA, L::kATile, aSB, 0, R, 64, 4, 0, false);  // E = (scale dz a) SB^T
+    NHA_MMA_WAIT();
+    NHA_TRIL_TO_SMEM(L::cA, L::bufA);
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+#pragma unroll
+      for (int nb = 0; nb < KT; ++nb) {
+        // dq_gsa columns [64 nb, 64 nb + 64): (scale dz exp G) Hk^T (Hk rows kk as K-major N rows) + tril(E) k'
+        mma_tile(tbase + L::cDQ + 64 * nb, aB, L::kATile, aHk + nb * 8192, 0, R, 64, 4, 0, false);
+        mma_tile(tbase + L::cDQ + 64 * nb, aA, L::kATile, aK + nb * 8192, 0, R, 64, 4, 1, true);
+      }
+    }
+    NHA_MMA_WAIT();
+    // ---- window part: dz_win tile by tile, dq_swa --------------------------------------------------------------------
+    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+      tc_fence_before();
+      __syncthreads();
+      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      cp_commit();
+      cp_wait_all();
+      NHA_SMEM_TO_MMA();
+      if (tid == 0) {
+        mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);      // S  = q_swa k^T
+        mma_tile(tbase + L::cDP, aDO, L::kATile, aWV, 8192, R, 64, D / 16, 0, false);    // dP = do v^T
+      }
+      NHA_MMA_WAIT();
+      {
+        float sv[32], dp[32];
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          tmem_ld32(tlane + L::cS + 32 * part, sv);
+          tmem_ld32(tlane + L::cDP + 32 * part, dp);
+          if (active) {
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+              float o8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int key = jt * kChunk + 32 * part + 8 * c8 + e;
+                const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && in_seq;
+                o8[e] = vis ? __expf(sv[8 * c8 + e] * d.scale - Lj) * (dp[8 * c8 + e] - delta) * d.scale : 0.f;
+              }
+              *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * part + c8)) = pack8(o8);
+            }
+          }
+        }
+      }
+      NHA_SMEM_TO_MMA();
+      if (tid == 0) {
+#pragma unroll
+        for (int nb = 0; nb < KT; ++nb)                     // dq_swa += dz_win k_swa (keys as the k dimension)
+          mma_tile(tbase + L::cDQS + 64 * nb, aA, L::kATile, aW + nb * 8192, 0, R, 64, 4, 1, jt > jt_lo);
+      }
+      NHA_MMA_WAIT();
+    }
+    // ---- dq rows out -----------------------------------------------------------------------------------------------------
+    {
+      float ov[32];
+#pragma unroll
+      for (int part = 0; part < D / 32; ++part) {
+        tmem_ld32(tlane + L::cDQ + 32 * part, ov);
+        if (live) {
+          bf16* orow = (bf16*)d.dq_gsa + rowq * D + 32 * part;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
+        }
+        tmem_ld32(tlane + L::cDQS + 32 * part, ov);
+        if (live) {
+          bf16* orow = (bf16*)d.dq_swa + rowq * D + 32 * part;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+  if (failed && tid == 0) atomicExch(err, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+// ================================================================================================
+// columns pass
+// ================================================================================================
+template <int D, int R>
+struct ColsLayout {
+  static constexpr int KT = D / 64;
+  static constexpr int kATile = R * 128;
+  static constexpr int tQ = 0;                          // q_gsa [R][D]; q..pa later hold the fp32 scan buffer of dg
+  static constexpr int tDO = tQ + KT * kATile;          // do [R][D]
+  static constexpr int tZA = tDO + KT * kATile;         // scale dz a [R][64]
+  static constexpr int tPA = tZA + kATile;              // p a [R][64]
+  static constexpr int tK = tPA + kATile;               // k' [64][D]
+  static constexpr int tV = tK + KT * 8192;             // v' [64][D]
+  static constexpr int tSB = tV + KT * 8192;            // s' b
+  static constexpr int tSBE = tSB + 8192;               // s' exp(Gend - G)
+  static constexpr int tDK = tSBE + 8192;               // DK at the chunk end [D][64]
+  static constexpr int tDV = tDK + D * 128;             // DV at the chunk end [64][D]
+  static constexpr int bufA = tDV + KT * 8192;          // tril(A) -> tril(E)
+  static constexpr int bufB = bufA + kATile;            // tril(Av) -> tril(Bv)
+  static constexpr int oG = bufB + kATile;
+  static constexpr int oR = oG + 64 * 65 * 4;           // [64] reference, [64] carry
+  static constexpr int oBar = oR + 512;
+  static constexpr int total = oBar + 64 + 1024;
+  static constexpr int cA = 0, cAv = 64, cDK = 128, cDV = 128 + D, cDS = 128 + 2 * D, cDS2 = cA;
+  static_assert(tK - tQ >= 64 * 65 * 4, "the dg scan buffer must fit in the per-head tiles (q, do, dza, pa), dead by then");
+};
+
+template <int D, int R>
+__global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha_chunk_desc d, const BwdWs w,
+                                                                       int* __restrict__ err) {
+  typedef ColsLayout<D, R> L;
+  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int n = d.plan[N + 1 + cg];
+  if (n < 0) return;
+  if (!chunk_gate(w, cg, h, H)) return;
+  const int chunk0 = d.plan[n];
+  const int ci = cg - chunk0;
+  const int t0 = d.cu_seqlens[n];
+  const int len = d.cu_seqlens[n + 1] - t0;
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int c0 = ci * kChunk;
+  const int shift = seq_shift(d, n);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t nh = (size_t)n * H + h;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* Gs = (float*)(sm + L::oG);
+  float* Rs = (float*)(sm + L::oR);
+  float* cgv = Rs + 64;
+  uint64_t* mbar = (uint64_t*)(sm + L::oBar);
+  uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
+
+  const int lo = 0, hi = len - shift;
+  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  cp_commit();
+  uint4 sreg[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kBUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    const int src = c0 + r - shift;
+    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= lo && src < hi) {
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
+      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+  }
+  // state gradients at the chunk end: fp32 in global, bf16 operands here
+  const float* dkg = w.dkc + ((size_t)cg * H + h) * D * M;
+  const float* dvg = w.dvc + ((size_t)cg * H + h) * M * D;
+  for (int i = tid; i < D * 8; i += kBUThreads) {          // DK [D rows kk][64 m]
+    const int r = i >> 3, c8 = i & 7;
+    float f[8];
+    *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8);
+    *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8 + 4);
+    *reinterpret_cast<uint4*>(sm + L::tDK + sw_off(r, c8)) = pack8(f);
+  }
+  for (int i = tid; i < M * (D / 8); i += kBUThreads) {    // DV [64 m][D v] as D/64 column tiles
+    const int r = i / (D / 8), c = i % (D / 8);
+    float f[8];
+    *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c);
+    *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c + 4);
+    *reinterpret_cast<uint4*>(sm + L::tDV + (c >> 3) * 8192 + sw_off(r, c & 7)) = pack8(f);
+  }
+  // gate-gradient carry of all later chunks: <DK, hk> + <DV, hv> at this chunk's end (= the next chunk's start)
+  {
+    const int m = tid & 63, half = tid >> 6;
+    float acc = 0.f;
+    if (ci < nchunks - 1) {
+      const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(cg + 1) * H + h) * D * M;
+      const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(cg + 1) * H + h) * M * D;
+      for (int kk = half * (D / 2); kk < (half + 1) * (D / 2); ++kk) acc += dkg[(size_t)kk * M + m] * bf2f(hkn[(size_t)kk * M + m]);
+      for (int vv = half * (D / 2); vv < (half + 1) * (D / 2); ++vv) acc += dvg[(size_t)m * D + vv] * bf2f(hvn[(size_t)m * D + vv]);
+    } else if (d.d_hkt && d.hkt && d.hvt) {
+      for (int kk = half * (D / 2); kk < (half + 1) * (D / 2); ++kk)
+        acc += d.d_hkt[nh * D * M + (size_t)kk * M + m] * d.hkt[nh * D * M + (size_t)kk * M + m];
+      for (int vv = half * (D / 2); vv < (half + 1) * (D / 2); ++vv)
+        acc += d.d_hvt[nh * M * D + (size_t)m * D + vv] * d.hvt[nh * M * D + (size_t)m * D + vv];
+    }
+    if (half == 1) cgv[m] = acc;
+    __syncthreads();
+    if (half == 0) cgv[m] += acc;
+  }
+  if (tid == 0) mbar_init(mbar, 1);
+  __syncthreads();
+  {
+    const int m = tid & 63, half = tid >> 6;
+    float run = 0.f;
+#pragma unroll 8
+    for (int r = 32 * half; r < 32 * half + 32; ++r) {
+      run += Gs[r * 65 + m];
+      Gs[r * 65 + m] = run;
+    }
+    __syncthreads();
+    if (half == 1) {
+      const float add = Gs[31 * 65 + m];
+#pragma unroll 8
+      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+    }
+    __syncthreads();
+  }
+  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kBUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    float sv[8], o1[8], o2[8];
+    unpack8(sreg[j], sv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float gl = Gs[r * 65 + 8 * c8 + e];
+      o1[e] = sv[e] * __expf(Rs[8 * c8 + e] - gl);
+      o2[e] = sv[e] * __expf(Gs[63 * 65 + 8 * c8 + e] - gl);
+    }
+    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(o1);
+    *reinterpret_cast<uint4*>(sm + L::tSBE + sw_off(r, c8)) = pack8(o2);
+  }
+  if (warp == 0) tmem_alloc(tslot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tslot;
+  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  uint32_t phase = 0;
+  bool failed = false;
+
+  // rows of the R-row products (query rows) and of the 64-row products (key rows)
+  const bool active = R == 128 ? true : lane < 16;
+  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int tk = row & 63;
+  const bool kactive = lane < 16;
+  const int krow = warp * 16 + (lane & 15);
+  const uint32_t aQ = smem_u32(sm + L::tQ), aDO = smem_u32(sm + L::tDO), aZA = smem_u32(sm + L::tZA);
+  const uint32_t aPA = smem_u32(sm + L::tPA), aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV);
+  const uint32_t aSB = smem_u32(sm + L::tSB), aSBE = smem_u32(sm + L::tSBE), aDK = smem_u32(sm + L::tDK);
+  const uint32_t aDV = smem_u32(sm + L::tDV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
+
+  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+    const int hq0 = h * NG + ht * TH;
+#pragma unroll
+    for (int t2 = 0; t2 < TH; ++t2) {
+      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
+                 64, 64 * t2, tid);
+      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
+                 64, 64 * t2, tid);
+      load_sw<64>(sm + L::tZA, 0, w.dza + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
+      load_sw<64>(sm + L::tPA, 0, w.paq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
+    }
+    cp_commit();
+    cp_wait_all();
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+      mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);         // A  = q k'^T
+      mma_tile(tbase + L::cAv, aDO, L::kATile, aV, 8192, R, 64, D / 16, 0, false);       // Av = do v'^T
+    }
+    NHA_MMA_WAIT();
+    NHA_TRIL_TO_SMEM(L::cA, L::bufA);
+    NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+      // ds' (intra) += tril(A)^T dza + tril(Av)^T pa      (both operands MN-major, k = query row)
+      mma_tile_ex(tbase + L::cDS, aA, 0, 1, aZA, 0, 1, 64, 64, R / 16, ht > 0);
+      mma_tile_ex(tbase + L::cDS, aB, 0, 1, aPA, 0, 1, 64, 64, R / 16, true);
+      mma_tile(tbase + L::cA, aZA, L::kATile, aSB, 0, R, 64, 4, 0, false);                // E  = dza SB^T
+      mma_tile(tbase + L::cAv, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);               // Bv = pa SB^T
+    }
+    NHA_MMA_WAIT();
+    NHA_TRIL_TO_SMEM(L::cA, L::bufA);
+    NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+#pragma unroll
+      for (int nb = 0; nb < KT; ++nb) {
+        // dk' += tril(E)^T q,  dv' += tril(Bv)^T do      (64 output columns at a time)
+        mma_tile_ex(tbase + L::cDK + 64 * nb, aA, 0, 1, aQ + nb * L::kATile, 0, 1, 64, 64, R / 16, ht > 0);
+        mma_tile_ex(tbase + L::cDV + 64 * nb, aB, 0, 1, aDO + nb * L::kATile, 0, 1, 64, 64, R / 16, ht > 0);
+      }
+    }
+    NHA_MMA_WAIT();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+  // ---- inter-chunk parts from the state gradients at the chunk end ------------------------------------------
+  if (!failed) {
+    if (tid == 0) {
+#pragma unroll
+      for (int nb = 0; nb < KT; ++nb) {
+        // dk' += sbe DK^T (DK rows kk as the N rows of a K-major operand), dv' += sbe DV (DV as MN-major, k = slot)
+        mma_tile(tbase + L::cDK + 64 * nb, aSBE, 0, aDK + nb * 8192, 0, 64, 64, 4, 0, true);
+        mma_tile(tbase + L::cDV + 64 * nb, aSBE, 0, aDV + nb * 8192, 0, 64, 64, 4, 1, true);
+      }
+      // DS2 = k' DK + v' DV^T
+      mma_tile(tbase + L::cDS2, aK, 8192, aDK, 0, 64, 64, D / 16, 1, false);
+      mma_tile(tbase + L::cDS2, aV, 8192, aDV, 8192, 64, 64, D / 16, 0, true);
+    }
+    NHA_MMA_WAIT();
+  }
+  // ---- epilogue: one thread per key row ---------------------------------------------------------------------------
+  float* scan = (float*)(sm + L::tQ);                     // [64][65] dgraw, then its reverse cumulative sum
+  const int p = c0 + krow, j = p - shift;
+  const bool keep = kactive && j >= 0 && p < len;
+  {
+    float dsi[32], ds2[32];
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      tmem_ld32(tlane + L::cDS + 32 * part, dsi);
+      tmem_ld32(tlane + L::cDS2 + 32 * part, ds2);
+      if (kactive) {
+        float sv[32];
+        if (keep) {
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8)
+            unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 32 * part + 8 * c8), sv + 8 * c8);
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float ds8[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int m = 32 * part + 8 * c8 + e;
+            const float gl = Gs[krow * 65 + m];
+            const float ds = __expf(Rs[m] - gl) * dsi[8 * c8 + e] + __expf(Gs[63 * 65 + m] - gl) * ds2[8 * c8 + e];
+            ds8[e] = ds;
+            float graw = 0.f;
+            if (keep) graw = w.dga[((size_t)(t0 + p) * H + h) * M + m] - sv[8 * c8 + e] * ds;
+            scan[krow * 65 + m] = graw;
+          }
+          if (keep) *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + j) * H + h) * M + 32 * part + 8 * c8) = pack8(ds8);
+        }
+      }
+    }
+    float ov[32];
+#pragma unroll
+    for (int part = 0; part < D / 32; ++part) {
+      tmem_ld32(tlane + L::cDK + 32 * part, ov);
+      if (keep) {
+        bf16* orow = (bf16*)d.dk_gsa + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
+      }
+      tmem_ld32(tlane + L::cDV + 32 * part, ov);
+      if (keep) {
+        const float* wa = w.dvacc + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) ov[e] += wa[e];
+        bf16* orow = (bf16*)d.dv + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
+      }
+    }
+  }
+  __syncthreads();
+  // reverse cumulative sum of dgraw along the rows (two threads per column), plus the carry
+  {
+    const int m = tid & 63, half = tid >> 6;
+    float run = 0.f;
+#pragma unroll 8
+    for (int r = 32 * half + 31; r >= 32 * half; --r) {
+      run += scan[r * 65 + m];
+      scan[r * 65 + m] = run;
+    }
+    __syncthreads();
+    const float add = cgv[m] + (half == 0 ? scan[32 * 65 + m] : 0.f);
+    __syncthreads();                                  // every read of the upper half's total precedes its update
+#pragma unroll 8
+    for (int r = 32 * half; r < 32 * half + 32; ++r) scan[r * 65 + m] += add;
+    __syncthreads();
+  }
+  if (keep) {
+#pragma unroll
+    for (int c8 = 0; c8 < 8; ++c8) {
+      float g8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g8[e] = scan[krow * 65 + 8 * c8 + e];
+      *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = pack8(g8);
+    }
+  }
+  if (failed && tid == 0) atomicExch(err, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+#undef NHA_MMA_WAIT
+#undef NHA_SMEM_TO_MMA
+#undef NHA_TRIL_TO_SMEM
+
+template <int D, int R>
+static int launch_rows(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs) {
+  typedef RowsLayout<D, R> L;
+  cudaError_t e = cudaFuncSetAttribute(nha_bwd_rows_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  nha_bwd_rows_umma_kernel<D, R><<<dim3(NCB, d->H), kBUThreads, L::total, cs>>>(*d, w, err);
+  return check_launch();
+}
+
+template <int D, int R>
+static int launch_cols(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs) {
+  typedef ColsLayout<D, R> L;
+  cudaError_t e = cudaFuncSetAttribute(nha_bwd_cols_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  nha_bwd_cols_umma_kernel<D, R><<<dim3(NCB, d->H), kBUThreads, L::total, cs>>>(*d, w, err);
+  return check_launch();
+}
+
+bool bwd_umma_supported(const nha_chunk_desc* d) {
+  const int NG = d->HQ / d->H;
+  return d->K == d->V && d->M == 64 && (d->K == 64 || d->K == 128) && (NG == 1 || NG % 2 == 0);
+}
+
+// which: 0 = rows pass, 1 = columns pass.  The caller has checked bwd_umma_supported().
+int bwd_umma_launch(const nha_chunk_desc* d, const BwdWs& w, int which, int* err, cudaStream_t cs) {
+  const int NG = d->HQ / d->H;
+  const bool one = NG == 1;
+  if (d->K == 64) {
+    if (which == 0) return one ? launch_rows<64, 64>(d, w, err, cs) : launch_rows<64, 128>(d, w, err, cs);
+    return one ? launch_cols<64, 64>(d, w, err, cs) : launch_cols<64, 128>(d, w, err, cs);
+  }
+  if (which == 0) return one ? launch_rows<128, 64>(d, w, err, cs) : launch_rows<128, 128>(d, w, err, cs);
+  return one ? launch_cols<128, 64>(d, w, err, cs) : launch_cols<128, 128>(d, w, err, cs);
+}
+
+}  // namespace nha

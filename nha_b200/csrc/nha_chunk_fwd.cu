@@ -407,6 +407,11 @@ extern "C" int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream) {
     if (st == NHA_OK) umma_done = true;
     else if (st != NHA_ERR_UNSUPPORTED) return st;
   }
+  if (!umma_done) {
+    // every chunk is the general kernels' job, in the backward too
+    cudaError_t e0 = cudaMemsetAsync(flags, 1, (size_t)NCB * d->H * sizeof(int), cs);
+    if (e0 != cudaSuccess) return record_cuda_error(e0);
+  }
   const FwdLayout L = fwd_layout(d->K, d->V, d->M);
   if (L.total > kMaxSmem) return umma_done ? NHA_OK : NHA_ERR_SMEM;
   cudaError_t e = cudaFuncSetAttribute(nha_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);

@@ -26,29 +26,6 @@ using namespace umma;
 constexpr int kUThreads = 128;
 constexpr float kUmmaDecayLimit = 140.0f;
 
-__device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
-  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-  const int n = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
-
-// Asynchronously copy `rows` x COLS bf16 (global rows row0.., stride gstride elements; rows outside
-// [lo, hi) become zeros) into COLS/64 swizzled tiles of `tile_bytes` each, starting at tile row dst_row0.
-template <int COLS>
-__device__ __forceinline__ void load_sw(unsigned char* tile, int tile_bytes, const bf16* base, int64_t gstride, int row0,
-                                        int lo, int hi, int rows, int dst_row0, int tid) {
-  constexpr int C8 = COLS / 8;
-  for (int i = tid; i < rows * C8; i += kUThreads) {
-    const int r = i / C8, c = i % C8;
-    const int gr = row0 + r;
-    const bool ok = gr >= lo && gr < hi;
-    const bf16* src = base + (int64_t)(ok ? gr : lo) * gstride + 8 * c;
-    cp16(tile + (c >> 3) * tile_bytes + sw_off(dst_row0 + r, c & 7), src, ok);
-  }
-}
-
 template <int D, int R>
 struct UmmaLayout {
   static constexpr int KT = D / 64;

@@ -65,6 +65,19 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, int a
   }
 }
 
+// General form: either operand K-major (mn = 0: 64-wide k tiles `tile_bytes` apart, 32 bytes per k step)
+// or MN-major (mn = 1: 16 k rows = 2048 bytes per k step).
+__device__ __forceinline__ void mma_tile_ex(uint32_t d_tmem, uint32_t a_addr, int a_tile_bytes, int a_mn, uint32_t b_addr,
+                                            int b_tile_bytes, int b_mn, int M, int N, int ksteps, bool accumulate) {
+  const uint32_t idesc = make_idesc(M, N, b_mn) | ((uint32_t)a_mn << 15);
+  for (int ks = 0; ks < ksteps; ++ks) {
+    const int kt = ks >> 2, kin = ks & 3;
+    const uint64_t da = a_mn ? make_desc(a_addr + ks * 2048) : make_desc(a_addr + kt * a_tile_bytes + kin * 32);
+    const uint64_t db = b_mn ? make_desc(b_addr + ks * 2048) : make_desc(b_addr + kt * b_tile_bytes + kin * 32);
+    mma_f16(d_tmem, da, db, idesc, accumulate || ks > 0);
+  }
+}
+
 __device__ __forceinline__ void commit(uint64_t* mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar))
                : "memory");
@@ -118,6 +131,31 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* out) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) out[i] = __uint_as_float(r[i]);
 }
+
+// ---- asynchronous 16-byte copies into swizzled tiles (128-thread CTAs) -----------------------------
+__device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+
+// Asynchronously copy `rows` x COLS bf16 (global rows row0.., stride gstride elements; rows outside
+// [lo, hi) become zeros) into COLS/64 swizzled tiles of `tile_bytes` each, starting at tile row dst_row0.
+template <int COLS>
+__device__ __forceinline__ void load_sw(unsigned char* tile, int tile_bytes, const bf16* base, int64_t gstride, int row0,
+                                        int lo, int hi, int rows, int dst_row0, int tid) {
+  constexpr int C8 = COLS / 8;
+  for (int i = tid; i < rows * C8; i += 128) {
+    const int r = i / C8, c = i % C8;
+    const int gr = row0 + r;
+    const bool ok = gr >= lo && gr < hi;
+    const bf16* src = base + (int64_t)(ok ? gr : lo) * gstride + 8 * c;
+    cp16(tile + (c >> 3) * tile_bytes + sw_off(dst_row0 + r, c & 7), src, ok);
+  }
+}
+
 
 }  // namespace umma
 }  // namespace nha
