@@ -16,8 +16,10 @@ struct BwdWs {
   float* dga;     // [Ttot, H, M]    ok .* dz + p .* dp summed over the group
   bf16* dzg;      // [Ttot, HQ, M]   scale * dz_slot .* exp(G)
   bf16* pgq;      // [Ttot, HQ, M]   p_slot .* exp(G)
-  float* dkc;     // [NC, H, K, M]   gradient of hk at the END of each chunk
-  float* dvc;     // [NC, H, M, V]   gradient of hv at the END of each chunk
+  float* dkc;     // [NC, H, K, M]   first the chunk's own term q^T (scale dz exp G), then (after the scan)
+                  //                 the gradient of hk at the END of the chunk
+  float* dvc;     // [NC, H, M, V]   likewise (p exp G)^T do, then the gradient of hv at the chunk end
+  float* gend;    // [NC, H, M]      total shifted log gate of each chunk
   bf16* dza;      // [Ttot, HQ, M]   scale * dz_slot .* a   (tensor-memory path only)
   bf16* paq;      // [Ttot, HQ, M]   p_slot .* a            (tensor-memory path only)
   const int* flags;   // [NC, H] chunks the tensor-memory forward left to the general kernels, or NULL
@@ -35,6 +37,7 @@ __host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* b
   const int64_t NC = nha_chunk_count_bound(d->Ttot, d->N);
   const int64_t o_dkc = take(NC * d->H * d->K * d->M * 4), o_dvc = take(NC * d->H * d->M * d->V * 4);
   const int64_t o_dza = take(T * d->HQ * d->M * 2), o_paq = take(T * d->HQ * d->M * 2);
+  const int64_t o_gend = take(NC * d->H * d->M * 4);
   if (w && base) {
     char* b = (char*)base;
     w->delta = (float*)(b + o_delta); w->lj = (float*)(b + o_lj); w->dvacc = (float*)(b + o_dvacc);
@@ -42,6 +45,7 @@ __host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* b
     w->dga = (float*)(b + o_dga); w->dzg = (bf16*)(b + o_dzg); w->pgq = (bf16*)(b + o_pgq);
     w->dkc = (float*)(b + o_dkc); w->dvc = (float*)(b + o_dvc);
     w->dza = (bf16*)(b + o_dza); w->paq = (bf16*)(b + o_paq);
+    w->gend = (float*)(b + o_gend);
     w->flags = nullptr; w->gate = 0;
   }
   return off;

@@ -577,99 +577,131 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chun
 }
 
 // ================================================================================================
-// 4a. state-gradient march: DK (gradient of hk) and DV (gradient of hv) at the end of every chunk.
-//     Like the forward state pass in reverse: one CTA owns 16 rows of DK or 16 columns of DV of one
-//     (sequence, kv head) and walks its chunks last to first,
-//         D_end[c-1] = D_end[c] .* exp(Gend_c) + (local term of chunk c),
-//     local terms q^T (scale dz exp G) and (p exp G)^T do summed over the query heads of the group.
+// 4a. state gradients at every chunk end.  The gradient D of the slot memory obeys, last chunk first,
+//         D_end[c-1] = D_end[c] .* exp(Gend_c) + L_c,
+//     L_c = q^T (scale dz exp G) for hk and (p exp G)^T do for hv, summed over the query heads of the
+//     group.  L_c depends on chunk c alone, so it is produced chunk-parallel (by the tensor-memory rows
+//     pass, or by the kernel below for the chunks the general kernels own) and what remains is an
+//     element-wise scan over the chunks, done in place over the buffers that held L.
 // ================================================================================================
-constexpr int kSgThreads = 128;
-constexpr int kSgWarps = kSgThreads / 32;
-
-__global__ void __launch_bounds__(kSgThreads) nha_bwd_stategrad_kernel(const nha_chunk_desc d, const BwdWs w) {
-  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
-  const int nks = K / 16;
-  const int slice = blockIdx.x;
-  const bool is_k = slice < nks;
-  const int s0 = (is_k ? slice : slice - nks) * 16;
-  const int n = blockIdx.y / H, h = blockIdx.y % H;
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
-  const int shift = seq_shift(d, n);
-  const int nchunks = (len + kChunk - 1) / kChunk;
-  const int chunk0 = d.plan[n];
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const size_t nh = (size_t)n * H + h;
-  extern __shared__ __align__(128) unsigned char smem[];
-  const int ldm = M + 8, ldx = 16 + 8;
-  bf16* zt = (bf16*)smem;                                   // [64][M+8] scale dz exp G, or p exp G
-  bf16* xt = zt + kChunk * ldm;                             // [64][24]  slice of q or of do
-  float* hs = (float*)(xt + kChunk * ldx);                  // DK slice [16][M+4] or DV slice [M][16+4]
-  const int ldh = is_k ? M + 4 : 16 + 4;
-  const int hrows = is_k ? 16 : M, hcols = is_k ? M : 16;
-  float* gend = hs + (is_k ? 16 * (M + 4) : M * 20);        // [M]
-  for (int i = tid; i < hrows * hcols; i += kSgThreads) {
-    const int r = i / hcols, c = i - r * hcols;
-    float val = 0.f;
-    if (is_k) { if (d.d_hkt) val = d.d_hkt[nh * K * M + (size_t)(s0 + r) * M + c]; }
-    else { if (d.d_hvt) val = d.d_hvt[nh * M * V + (size_t)r * V + s0 + c]; }
-    hs[r * ldh + c] = val;
-  }
-  __syncthreads();
-  const bf16* gg = (const bf16*)d.g + ((size_t)t0 * H + h) * M;
-  for (int ci = nchunks - 1; ci >= 0; --ci) {
-    const int c0 = ci * kChunk;
-    // ---- emit the gradient at this chunk's end
-    {
-      const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-      if (is_k) {
-        float* dst = w.dkc + cgi * K * M + (size_t)s0 * M;
-        for (int i = tid; i < 16 * M; i += kSgThreads) dst[i] = hs[(i / M) * ldh + (i % M)];
-      } else {
-        float* dst = w.dvc + cgi * M * V + s0;
-        for (int i = tid; i < M * 16; i += kSgThreads) dst[(size_t)(i / 16) * V + (i % 16)] = hs[(i / 16) * ldh + (i % 16)];
-      }
-    }
-    // ---- total shifted log gate of the chunk per slot
-    {
-      // rows of the chunk whose shifted source exists: j = c0 + r - shift in [0, len - shift)
-      const int r_lo = max(0, shift - c0), r_hi = min(kChunk, len - c0);
-      for (int m = tid; m < M; m += kSgThreads) {
-        float acc = 0.f;
-        const bf16* col = gg + (size_t)(c0 - shift) * H * M + m;
-#pragma unroll 8
-        for (int r = r_lo; r < r_hi; ++r) acc += bf2f(col[(size_t)r * H * M]);
-        gend[m] = acc;
-      }
-    }
-    __syncthreads();
-    for (int i = tid; i < hrows * hcols; i += kSgThreads) {
-      const int r = i / hcols, cc = i - r * hcols;
-      hs[r * ldh + cc] *= __expf(gend[is_k ? cc : r]);
-    }
-    for (int qh = 0; qh < NG; ++qh) {
-      const int hq = h * NG + qh;
-      __syncthreads();
-      load_tile_bf16(zt, ldm, (is_k ? w.dzg : w.pgq) + ((size_t)t0 * HQ + hq) * M, (int64_t)HQ * M, c0, 0, len, kChunk, M, tid,
-                     kSgThreads);
-      const bf16* xsrc = is_k ? (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq) * K + s0
-                              : (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * V + s0;
-      load_tile_bf16(xt, ldx, xsrc, (int64_t)HQ * (is_k ? K : V), c0, 0, len, kChunk, 16, tid, kSgThreads);
-      __syncthreads();
-      if (is_k) tile_gemm<false, true, true>(hs, ldh, xt, ldx, zt, ldm, 1, M / 16, kChunk / 16, warp, kSgWarps);
-      else tile_gemm<false, true, true>(hs, ldh, zt, ldm, xt, ldx, M / 16, 1, kChunk / 16, warp, kSgWarps);
-    }
-    __syncthreads();
-  }
-  if (is_k && d.dhk0)
-    for (int i = tid; i < 16 * M; i += kSgThreads) d.dhk0[nh * K * M + (size_t)s0 * M + i] = hs[(i / M) * ldh + (i % M)];
-  if (!is_k && d.dhv0)
-    for (int i = tid; i < M * 16; i += kSgThreads) d.dhv0[nh * M * V + (size_t)(i / 16) * V + s0 + (i % 16)] = hs[(i / 16) * ldh + (i % 16)];
+struct LocalLayout { int qb, dob, zt, pt, G, OK, OV, total; };
+__host__ __device__ inline LocalLayout local_layout(int K, int V, int M) {
+  LocalLayout L; int off = 0;
+  L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
+  L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
+  L.zt = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.pt = off; off = bup128(off + kChunk * (M + 8) * 2);
+  L.G = off; off = bup128(off + M * 4);
+  L.OK = off; off = bup128(off + K * (M + 4) * 4);
+  L.OV = off; off = bup128(off + M * (V + 4) * 4);
+  L.total = off;
+  return L;
 }
 
-static int stategrad_smem(int M) {
-  const int hs = (16 * (M + 4) > M * 20 ? 16 * (M + 4) : M * 20) * 4;
-  return kChunk * (M + 8) * 2 + kChunk * 24 * 2 + hs + M * 4 + 128;
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_local_terms_kernel(const nha_chunk_desc d, const BwdWs w) {
+  ChunkCtx c;
+  const int cg = blockIdx.x;
+  if (!chunk_ctx(d, cg, c)) return;
+  if (!chunk_gate(w, cg, blockIdx.y, d.H)) return;
+  const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const LocalLayout L = local_layout(K, V, M);
+  const int ldk = K + 8, ldv = V + 8, ldm = M + 8, ldok = M + 4, ldov = V + 4;
+  bf16* qb = (bf16*)(smem + L.qb);
+  bf16* dob = (bf16*)(smem + L.dob);
+  bf16* zt = (bf16*)(smem + L.zt);
+  bf16* pt = (bf16*)(smem + L.pt);
+  float* OK = (float*)(smem + L.OK);
+  float* OV = (float*)(smem + L.OV);
+  {
+    // total shifted log gate of the chunk per slot
+    const bf16* gg = (const bf16*)d.g + ((size_t)c.t0 * H + h) * M;
+    const int r_lo = max(0, c.shift - c.c0), r_hi = min(kChunk, c.len - c.c0);
+    for (int m = tid; m < M; m += kBwThreads) {
+      float acc = 0.f;
+      for (int r = r_lo; r < r_hi; ++r) acc += bf2f(gg[(size_t)(c.c0 + r - c.shift) * H * M + m]);
+      w.gend[((size_t)cg * H + h) * M + m] = acc;
+    }
+  }
+  for (int qh = 0; qh < NG; ++qh) {
+    const int hq = h * NG + qh;
+    __syncthreads();
+    load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((size_t)c.t0 * HQ + hq) * K, (int64_t)HQ * K, c.c0, 0, c.len, kChunk, K,
+                   tid, kBwThreads);
+    load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)c.t0 * HQ + hq) * V, (int64_t)HQ * V, c.c0, 0, c.len, kChunk, V,
+                   tid, kBwThreads);
+    load_tile_bf16(zt, ldm, w.dzg + ((size_t)c.t0 * HQ + hq) * M, (int64_t)HQ * M, c.c0, 0, c.len, kChunk, M, tid, kBwThreads);
+    load_tile_bf16(pt, ldm, w.pgq + ((size_t)c.t0 * HQ + hq) * M, (int64_t)HQ * M, c.c0, 0, c.len, kChunk, M, tid, kBwThreads);
+    __syncthreads();
+    if (qh == 0) {
+      tile_gemm<false, true, false>(OK, ldok, qb, ldk, zt, ldm, K / 16, M / 16, 4, warp, kBwWarps);
+      tile_gemm<false, true, false>(OV, ldov, pt, ldm, dob, ldv, M / 16, V / 16, 4, warp, kBwWarps);
+    } else {
+      tile_gemm<false, true, true>(OK, ldok, qb, ldk, zt, ldm, K / 16, M / 16, 4, warp, kBwWarps);
+      tile_gemm<false, true, true>(OV, ldov, pt, ldm, dob, ldv, M / 16, V / 16, 4, warp, kBwWarps);
+    }
+  }
+  __syncthreads();
+  float* dk = w.dkc + ((size_t)cg * H + h) * K * M;
+  float* dv = w.dvc + ((size_t)cg * H + h) * M * V;
+  for (int i = tid; i < K * M; i += kBwThreads) dk[i] = OK[(i / M) * ldok + (i % M)];
+  for (int i = tid; i < M * V; i += kBwThreads) dv[i] = OV[(i / V) * ldov + (i % V)];
+}
+
+// In-place reverse scan over the chunks of one (sequence, kv head): on entry dkc/dvc hold L_c, on exit
+// the gradient at the END of chunk c; the value carried past chunk 0 is the initial state's gradient.
+// One thread owns four consecutive state elements and fetches kScanBatch chunks ahead of the serial
+// recurrence so that enough loads are in flight to cover the memory latency.
+constexpr int kScanBatch = 8;
+__global__ void __launch_bounds__(256) nha_bwd_state_scan_kernel(const nha_chunk_desc d, const BwdWs w) {
+  const int K = d.K, V = d.V, M = d.M, H = d.H;
+  const int KM = K * M, MV = M * V;
+  const size_t nh = blockIdx.y;
+  const int n = nh / H, h = nh % H;
+  const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int chunk0 = d.plan[n];
+  const int el = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (el >= KM + MV) return;
+  const bool is_k = el < KM;
+  const int e = is_k ? el : el - KM;
+  const int m = is_k ? e % M : e / V;
+  const size_t per = is_k ? KM : MV;
+  float* buf = is_k ? w.dkc : w.dvc;
+  float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* dht = is_k ? d.d_hkt : d.d_hvt;
+  if (dht) run = *(const float4*)(dht + nh * per + e);
+  for (int hi = nchunks - 1; hi >= 0; hi -= kScanBatch) {
+    float4 local[kScanBatch], decay[kScanBatch];
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int ci = hi - u;
+      if (ci >= 0) {
+        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+        local[u] = __ldcs((const float4*)(buf + cgi * per + e));
+        if (is_k) decay[u] = *(const float4*)(w.gend + cgi * M + m);
+        else decay[u].x = w.gend[cgi * M + m];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kScanBatch; ++u) {
+      const int ci = hi - u;
+      if (ci >= 0) {
+        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+        __stcs((float4*)(buf + cgi * per + e), run);
+        float4 a;
+        if (is_k) a = make_float4(__expf(decay[u].x), __expf(decay[u].y), __expf(decay[u].z), __expf(decay[u].w));
+        else { const float x = __expf(decay[u].x); a = make_float4(x, x, x, x); }
+        run.x = run.x * a.x + local[u].x;
+        run.y = run.y * a.y + local[u].y;
+        run.z = run.z * a.z + local[u].z;
+        run.w = run.w * a.w + local[u].w;
+      }
+    }
+  }
+  float* d0 = is_k ? d.dhk0 : d.dhv0;
+  if (d0) *(float4*)(d0 + nh * per + e) = run;
 }
 
 // ================================================================================================
@@ -933,8 +965,9 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   if (e != cudaSuccess) return record_cuda_error(e);
   e = cudaFuncSetAttribute(nha_bwd_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L4.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  const int sg_smem = stategrad_smem(d->M);
-  e = cudaFuncSetAttribute(nha_bwd_stategrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sg_smem);
+  const LocalLayout L5 = local_layout(d->K, d->V, d->M);
+  if (L5.total > kMaxSmem) return NHA_ERR_SMEM;
+  e = cudaFuncSetAttribute(nha_bwd_local_terms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L5.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kBwThreads);
@@ -971,7 +1004,11 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 8) {
-    nha_bwd_stategrad_kernel<<<dim3(d->K / 16 + d->V / 16, d->N * d->H), kSgThreads, sg_smem, cs>>>(*d, w);
+    nha_bwd_local_terms_kernel<<<grid, block, L5.total, cs>>>(*d, wg);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+    const int SD = d->K * d->M + d->M * d->V;
+    nha_bwd_state_scan_kernel<<<dim3((SD / 4 + 255) / 256, d->N * d->H), 256, 0, cs>>>(*d, w);
     st = check_launch();
     if (st != NHA_OK) return st;
     if (umma) {

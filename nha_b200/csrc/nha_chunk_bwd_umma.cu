@@ -56,6 +56,8 @@ struct RowsLayout {
   static constexpr int tWV = R == 128 ? tQ + KT * 8192 : tWVx;
   static constexpr int cA = 0, cAv = 64, cQH = 128, cY = 192, cDQ = 256, cDQS = 256 + D;
   static constexpr int cS = cQH, cDP = cY;
+  // chunk-local state-gradient terms, read out before the window loop reuses the columns
+  static constexpr int cLK = D == 64 ? 384 : 0, cLV = D == 64 ? 448 : 128;
 };
 
 template <int D, int R>
@@ -122,7 +124,10 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     }
     __syncthreads();
   }
-  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
+  if (tid < 64) {
+    Rs[tid] = 0.5f * Gs[63 * 65 + tid];
+    w.gend[((size_t)cg * H + h) * M + tid] = Gs[63 * 65 + tid];
+  }
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -305,6 +310,61 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
       }
     }
     NHA_MMA_WAIT();
+    // ---- the chunk's own contribution to the state gradients: q^T (scale dz exp G) and (p exp G)^T do -------------
+    // (p exp G) comes back from the scratch this CTA just wrote; bufA (tril(E)) is free again
+    tc_fence_before();
+    __syncthreads();
+#pragma unroll
+    for (int t2 = 0; t2 < TH; ++t2)
+      load_sw<64>(sm + L::bufA, 0, w.pgq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
+    cp_commit();
+    cp_wait_all();
+    NHA_SMEM_TO_MMA();
+    if (tid == 0) {
+#pragma unroll
+      for (int nb = 0; nb < KT; ++nb) {
+        mma_tile_ex(tbase + L::cLK + 64 * nb, aQ + nb * L::kATile, 0, 1, aB, 0, 1, 64, 64, R / 16, false);
+        mma_tile_ex(tbase + L::cLV + 64 * nb, aA, 0, 1, aDO + nb * L::kATile, 0, 1, 64, 64, R / 16, false);
+      }
+    }
+    NHA_MMA_WAIT();
+    {
+      const bool kact = lane < 16;
+      const int krow = warp * 16 + (lane & 15);
+      float lv[32];
+#pragma unroll
+      for (int nb = 0; nb < KT; ++nb) {
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          tmem_ld32(tlane + L::cLK + 64 * nb + 32 * part, lv);
+          if (kact) {
+            float* dst = w.dkc + (((size_t)cg * H + h) * D + 64 * nb + krow) * M + 32 * part;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
+              if (ht > 0) {
+                const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
+                v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
+              }
+              *reinterpret_cast<float4*>(dst + e) = v4;
+            }
+          }
+          tmem_ld32(tlane + L::cLV + 64 * nb + 32 * part, lv);
+          if (kact) {
+            float* dst = w.dvc + (((size_t)cg * H + h) * M + krow) * D + 64 * nb + 32 * part;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
+              if (ht > 0) {
+                const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
+                v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
+              }
+              *reinterpret_cast<float4*>(dst + e) = v4;
+            }
+          }
+        }
+      }
+    }
     // ---- window part: dz_win tile by tile, dq_swa --------------------------------------------------------------------
     for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
       tc_fence_before();
