@@ -2,12 +2,13 @@
 //
 // The slot memory obeys a per-element linear recurrence
 //     hk[k,m] <- hk[k,m] * exp(g'[m]) + k'[k] * s'[m],   hv[m,v] <- hv[m,v] * exp(g'[m]) + s'[m] * v'[v]
-// (primes = inputs shifted right by gsa_kv_shift inside their sequence).  The state pass marches over
-// the chunks of a sequence and stores the state at every chunk start (bf16, the operand type of the
-// later matrix products) plus the fp32 final state.  Parallelism: the K rows of hk and the V columns
-// of hv are independent, so one CTA owns a 16-row / 16-column slice; long sequences are cut into
-// segments whose local end states are computed from a zero start, combined by a short sequential
-// scan (the recurrence is linear), and marched a second time from the true segment start.
+// (primes = inputs shifted right by gsa_kv_shift inside their sequence).  Over one chunk this is
+//     h_end = h_start .* exp(Gend) + L,   L_k = k'^T (s' exp(Gend - G)),  L_v = (s' exp(Gend - G))^T v',
+// with G the running sum of g' inside the chunk and Gend its total.  L and Gend depend on their own
+// chunk only, so a chunk-parallel kernel produces them with two 64-deep matrix products per
+// (chunk, kv head), and what remains of the march is an element-wise scan over the chunks that stores
+// the state at every chunk start (bf16, the operand type of the later matrix products) and the fp32
+// final state.  Every exponent is <= 0, so no reference point is needed.
 //
 // Replaces chunk_nha_fused_state_kernel (nha_fla/ops/nha/chunk_fused.py:31-114) and the state part of
 // fla's chunk_gsa_fwd reached from nha_fla/ops/nha/chunk_gsa.py:38-45; the in-sequence shift replaces
@@ -18,9 +19,8 @@
 
 namespace nha {
 
-constexpr int kStThreads = 128;
+constexpr int kStThreads = 256;
 constexpr int kStWarps = kStThreads / 32;
-constexpr int kDefaultSegChunks = 32;
 
 // ---------------------------------------------------------------------------------------------
 __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ plan, int N, int NCB, int H) {
@@ -46,210 +46,205 @@ __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restr
 }
 
 // ---------------------------------------------------------------------------------------------
-// mode 0: single march from the initial state (sequence fits one segment per grid.z slot)
-// mode 1: local march from zero, emits segment end state + segment log-decay
-// mode 2: march from the combined segment start, emits chunk-start states and the final state
-struct StateArgs {
-  nha_chunk_desc d;
-  int mode;
-  int seg_chunks;
-  int nseg_max;
-  float* seg_local;   // [N*H, nseg_max, K*M + M*V] end state of each segment marched from zero
-  float* seg_start;   // [N*H, nseg_max, K*M + M*V] true state at each segment start
-  float* seg_decay;   // [N*H, nseg_max, M] sum of the shifted log gates of the segment
+// Scratch of the state pass: L [NCB*H][K*M + M*V] fp32, then Gend [NCB*H][M] fp32.
+struct StateWs {
+  float* local;
+  float* gend;
 };
 
-__global__ void __launch_bounds__(kStThreads) nha_state_kernel(const StateArgs a) {
-  const nha_chunk_desc& d = a.d;
+struct StLocalLayout { int kt, vt, sbe, G, total; };
+__host__ __device__ inline int st_up128(int x) { return (x + 127) & ~127; }
+__host__ __device__ inline StLocalLayout st_local_layout(int K, int V, int M) {
+  StLocalLayout L; int off = 0;
+  L.kt = off; off = st_up128(off + kChunk * (K + 8) * 2);
+  L.vt = off; off = st_up128(off + kChunk * (V + 8) * 2);
+  L.sbe = off; off = st_up128(off + kChunk * (M + 8) * 2);
+  L.G = off; off = st_up128(off + kChunk * (M + 4) * 4);
+  L.total = off;
+  return L;
+}
+
+// One CTA per (chunk, kv head): L_k, L_v and Gend of that chunk.
+__global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_chunk_desc d, const StateWs w) {
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int NCB = gridDim.x;
+  const int n = d.plan[d.N + 1 + cg];
+  if (n < 0) return;
   const int K = d.K, V = d.V, M = d.M, H = d.H;
-  const int nks = K / 16, nvs = V / 16;
-  const int slice = blockIdx.x;                 // < nks: rows of hk, else columns of hv
-  const bool is_k = slice < nks;
-  const int s0 = (is_k ? slice : slice - nks) * 16;
-  const int n = blockIdx.y / H, h = blockIdx.y % H;
-  const int seg = blockIdx.z;
   const int t0 = d.cu_seqlens[n];
   const int len = d.cu_seqlens[n + 1] - t0;
-  const int nchunks = (len + kChunk - 1) / kChunk;
-  const int c_begin = seg * a.seg_chunks;
-  if (c_begin >= nchunks && !(seg == 0)) return;
-  const int c_end = min(nchunks, c_begin + a.seg_chunks);
+  const int p0 = (cg - d.plan[n]) * kChunk;       // shifted position of row 0
   const int shift = seq_shift(d, n);
-  const int chunk0 = d.plan[n];
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int SD = K * M + M * V;
+  (void)NCB;
 
   extern __shared__ __align__(128) unsigned char smem[];
-  const int ldg = M + 4, ldsb = M + 8, ldx = 16 + 8;
-  float* G = reinterpret_cast<float*>(smem);                       // [64][M+4] cumulative shifted gates
-  bf16* sbe = reinterpret_cast<bf16*>(G + kChunk * ldg);           // [64][M+8] s' * exp(Gend - G)
-  bf16* xt = sbe + kChunk * ldsb;                                  // [64][24]  slice of k' or v'
-  float* hs = reinterpret_cast<float*>(xt + kChunk * ldx);         // hk slice [16][M+4] or hv slice [M][16+4]
-  const int ldh = is_k ? M + 4 : 16 + 4;
-  const int hrows = is_k ? 16 : M, hcols = is_k ? M : 16;
+  const StLocalLayout L = st_local_layout(K, V, M);
+  const int ldk = K + 8, ldv = V + 8, ldsb = M + 8, ldg = M + 4;
+  bf16* kt = (bf16*)(smem + L.kt);
+  bf16* vt = (bf16*)(smem + L.vt);
+  bf16* sbe = (bf16*)(smem + L.sbe);
+  float* G = (float*)(smem + L.G);
 
-  // ---- initial state of this march
-  const size_t nh = (size_t)n * H + h;
-  for (int i = tid; i < hrows * hcols; i += kStThreads) {
-    const int r = i / hcols, c = i - r * hcols;
-    float val = 0.f;
-    const size_t el = is_k ? (size_t)(s0 + r) * M + c : (size_t)K * M + (size_t)r * V + s0 + c;
-    if (a.mode == 2) {
-      val = a.seg_start[(nh * a.nseg_max + seg) * SD + el];
-    } else if (a.mode == 0) {
-      if (is_k) { if (d.hk0) val = d.hk0[nh * K * M + el]; }
-      else { if (d.hv0) val = d.hv0[nh * M * V + (el - (size_t)K * M)]; }
+  // rows of the chunk hold shifted tokens j = p - shift; rows before the sequence start or past its
+  // end contribute nothing
+  const int lo = shift, hi = len;                  // valid shifted positions p: lo <= p < hi
+  load_tile_bf16(kt, ldk, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * K - (size_t)shift * H * K, (int64_t)H * K, p0, lo,
+                 hi, kChunk, K, tid, kStThreads);
+  load_tile_bf16(vt, ldv, (const bf16*)d.v + ((size_t)t0 * H + h) * V - (size_t)shift * H * V, (int64_t)H * V, p0, lo, hi,
+                 kChunk, V, tid, kStThreads);
+  for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
+    const int r = i / (M / 8), c8 = i - r * (M / 8);
+    const int p = p0 + r, j = p - shift;
+    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (j >= 0 && p < len) {
+      const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
+      unpack8(u, gv);
     }
-    hs[r * ldh + c] = val;
-  }
-  float decay_sum = 0.f;   // per thread m = tid (< M): running sum of Gend over the segment
-  __syncthreads();
-
-  const bf16* xsrc = is_k ? (const bf16*)d.k_gsa : (const bf16*)d.v;
-  const int D = is_k ? K : V;
-  for (int c = c_begin; c < c_end; ++c) {
-    const int p0 = c * kChunk;            // shifted position of row 0
-    // ---- emit the chunk-start slice
-    if (a.mode != 1) {
-      const size_t cg = (size_t)(chunk0 + c) * H + h;
-      if (is_k) {
-        bf16* dst = (bf16*)d.hk_chunks + cg * K * M + (size_t)s0 * M;
-        for (int i = tid; i < 16 * M; i += kStThreads) dst[i] = f2bf(hs[(i / M) * ldh + (i % M)]);
-      } else {
-        bf16* dst = (bf16*)d.hv_chunks + cg * M * V + s0;
-        for (int i = tid; i < M * 16; i += kStThreads) dst[(size_t)(i / 16) * V + (i % 16)] = f2bf(hs[(i / 16) * ldh + (i % 16)]);
-      }
-    }
-    // ---- load shifted g' (fp32) and the k'/v' slice
-    for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
-      const int r = i / (M / 8), c8 = i - r * (M / 8);
-      const int p = p0 + r, j = p - shift;
-      float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (j >= 0 && p < len) {
-        const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
-        unpack8(u, gv);
-      }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
-    }
-    for (int i = tid; i < kChunk * 2; i += kStThreads) {
-      const int r = i >> 1, c8 = i & 1;
-      const int p = p0 + r, j = p - shift;
-      uint4 u = make_uint4(0u, 0u, 0u, 0u);
-      if (j >= 0 && p < len) u = *reinterpret_cast<const uint4*>(xsrc + ((size_t)(t0 + j) * H + h) * D + s0 + 8 * c8);
-      *reinterpret_cast<uint4*>(xt + r * ldx + 8 * c8) = u;
-    }
-    __syncthreads();
-    // ---- inclusive cumsum along the rows, one column per thread
-    for (int m = tid; m < M; m += kStThreads) {
+    for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
+  }
+  __syncthreads();
+  // inclusive running sum down the rows: two threads per column, the second adds the first half's total
+  {
+    const int m = tid >> 1, half = tid & 1;
+    if (m < M) {
       float run = 0.f;
-#pragma unroll 16
-      for (int r = 0; r < kChunk; ++r) {
+#pragma unroll 8
+      for (int r = half * 32; r < half * 32 + 32; ++r) {
         run += G[r * ldg + m];
         G[r * ldg + m] = run;
       }
-      if (m == tid) decay_sum += run;
     }
     __syncthreads();
-    // ---- sbe = s' * exp(Gend - G); scale the state slice by exp(Gend)
-    for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
-      const int r = i / (M / 8), c8 = i - r * (M / 8);
-      const int p = p0 + r, j = p - shift;
-      float sv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (j >= 0 && p < len) {
-        const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
-        unpack8(u, sv);
-      }
-      float out[8];
+    if (m < M && half == 1) {
+      const float add = G[31 * ldg + m];
+#pragma unroll 8
+      for (int r = 32; r < 64; ++r) G[r * ldg + m] += add;
+    }
+    __syncthreads();
+  }
+  if (tid < M) w.gend[((size_t)cg * H + h) * M + tid] = G[(kChunk - 1) * ldg + tid];
+  for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
+    const int r = i / (M / 8), c8 = i - r * (M / 8);
+    const int p = p0 + r, j = p - shift;
+    float sv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (j >= 0 && p < len) {
+      const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
+      unpack8(u, sv);
+    }
+    float out[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int m = 8 * c8 + e;
-        out[e] = sv[e] * __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]);
-      }
-      *reinterpret_cast<uint4*>(sbe + r * ldsb + 8 * c8) = pack8(out);
+    for (int e = 0; e < 8; ++e) {
+      const int m = 8 * c8 + e;
+      out[e] = sv[e] * __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]);
     }
-    for (int i = tid; i < hrows * hcols; i += kStThreads) {
-      const int r = i / hcols, cc = i - r * hcols;
-      const int m = is_k ? cc : r;
-      hs[r * ldh + cc] *= __expf(G[(kChunk - 1) * ldg + m]);
-    }
-    __syncthreads();
-    // ---- rank-64 update on the tensor cores
-    if (is_k) {
-      // hk_slice[16 x M] += k'_slice^T [16 x 64] * sbe [64 x M]
-      tile_gemm<false, true, true>(hs, ldh, xt, ldx, sbe, ldsb, 1, M / 16, kChunk / 16, warp, kStWarps);
-    } else {
-      // hv_slice[M x 16] += sbe^T [M x 64] * v'_slice [64 x 16]
-      tile_gemm<false, true, true>(hs, ldh, sbe, ldsb, xt, ldx, M / 16, 1, kChunk / 16, warp, kStWarps);
-    }
-    __syncthreads();
+    *reinterpret_cast<uint4*>(sbe + r * ldsb + 8 * c8) = pack8(out);
   }
-
-  // ---- epilogue
-  if (a.mode == 1) {
-    float* dst = a.seg_local + (nh * a.nseg_max + seg) * SD;
-    for (int i = tid; i < hrows * hcols; i += kStThreads) {
-      const int r = i / hcols, c = i - r * hcols;
-      const size_t el = is_k ? (size_t)(s0 + r) * M + c : (size_t)K * M + (size_t)r * V + s0 + c;
-      dst[el] = hs[r * ldh + c];
-    }
-    if (slice == 0 && tid < M) a.seg_decay[(nh * a.nseg_max + seg) * M + tid] = decay_sum;
-    if (slice == 0 && M > kStThreads)
-      for (int m = tid + kStThreads; m < M; m += kStThreads) a.seg_decay[(nh * a.nseg_max + seg) * M + m] = 0.f;
-  } else if (c_end >= nchunks) {
-    // last segment (or an empty sequence on segment 0): final state
-    if (is_k && d.hkt) {
-      for (int i = tid; i < 16 * M; i += kStThreads) d.hkt[nh * K * M + (size_t)s0 * M + i] = hs[(i / M) * ldh + (i % M)];
-    } else if (!is_k && d.hvt) {
-      for (int i = tid; i < M * 16; i += kStThreads)
-        d.hvt[nh * M * V + (size_t)(i / 16) * V + s0 + (i % 16)] = hs[(i / 16) * ldh + (i % 16)];
-    }
-  }
+  __syncthreads();
+  float* Lk = w.local + ((size_t)cg * H + h) * ((size_t)K * M + (size_t)M * V);
+  float* Lv = Lk + (size_t)K * M;
+  // L_k [K x M] = k'^T [K x 64] * sbe [64 x M];  L_v [M x V] = sbe^T [M x 64] * v' [64 x V], stored
+  // straight to global memory from the accumulator fragments
+  tile_gemm<false, true, false>(Lk, M, kt, ldk, sbe, ldsb, K / 16, M / 16, kChunk / 16, warp, kStWarps);
+  tile_gemm<false, true, false>(Lv, V, sbe, ldsb, vt, ldv, M / 16, V / 16, kChunk / 16, warp, kStWarps);
 }
 
-// Sequential combine over the segments of one (sequence, kv head): start[0] = h0,
-// start[z+1] = start[z] * exp(decay[z]) + local[z].
-__global__ void nha_state_combine_kernel(const StateArgs a) {
-  const nha_chunk_desc& d = a.d;
+// Forward scan over the chunks of one (sequence, kv head): stores the state at every chunk start and
+// the final state.  One thread owns eight consecutive state elements (one 16-byte bf16 store per
+// chunk) and fetches kStScanBatch chunks of L ahead of the serial recurrence.
+constexpr int kStScanBatch = 4;
+__global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w) {
   const int K = d.K, V = d.V, M = d.M, H = d.H;
-  const int SD = K * M + M * V;
+  const int KM = K * M, MV = M * V;
+  const size_t SD = (size_t)KM + MV;
   const size_t nh = blockIdx.y;
-  const int n = nh / H;
+  const int n = nh / H, h = nh % H;
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
-  const int nseg = max(1, (nchunks + a.seg_chunks - 1) / a.seg_chunks);
-  const int el = blockIdx.x * blockDim.x + threadIdx.x;
-  if (el >= SD) return;
-  const int m = el < K * M ? el % M : (el - K * M) / V;
-  float val = 0.f;
-  if (el < K * M) { if (d.hk0) val = d.hk0[nh * K * M + el]; }
-  else { if (d.hv0) val = d.hv0[nh * M * V + (el - K * M)]; }
-  for (int z = 0; z < nseg; ++z) {
-    const size_t base = nh * a.nseg_max + z;
-    a.seg_start[base * SD + el] = val;
-    val = val * __expf(a.seg_decay[base * M + m]) + a.seg_local[base * SD + el];
+  const int chunk0 = d.plan[n];
+  const int el = 8 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (el >= KM + MV) return;
+  const bool is_k = el < KM;
+  const int e = is_k ? el : el - KM;
+  const int m = is_k ? e % M : e / V;
+  const size_t per = is_k ? KM : MV;
+  bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
+  float run[8];
+  {
+    const float* h0 = is_k ? d.hk0 : d.hv0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) run[i] = h0 ? h0[nh * per + e + i] : 0.f;
   }
-}
-
-static int state_smem(int M) {
-  const int hs = max(16 * (M + 4), M * (16 + 4)) * 4;
-  return kChunk * (M + 4) * 4 + kChunk * (M + 8) * 2 + kChunk * 24 * 2 + hs;
-}
-
-static int seg_chunks_of(const nha_chunk_desc* d) { return d->seg_chunks > 0 ? d->seg_chunks : kDefaultSegChunks; }
-
-static int nseg_max_of(const nha_chunk_desc* d) {
-  const int maxchunks = (d->max_seqlen + kChunk - 1) / kChunk;
-  const int sc = seg_chunks_of(d);
-  return max(1, (maxchunks + sc - 1) / sc);
+  for (int lo = 0; lo < nchunks; lo += kStScanBatch) {
+    float4 la[kStScanBatch], lb[kStScanBatch], da[kStScanBatch], db[kStScanBatch];
+#pragma unroll
+    for (int u = 0; u < kStScanBatch; ++u) {
+      const int ci = lo + u;
+      if (ci < nchunks) {
+        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+        const float* src = w.local + cgi * SD + el;
+        la[u] = __ldcs((const float4*)src);
+        lb[u] = __ldcs((const float4*)(src + 4));
+        if (is_k) {
+          da[u] = *(const float4*)(w.gend + cgi * M + m);
+          db[u] = *(const float4*)(w.gend + cgi * M + m + 4);
+        } else {
+          da[u].x = w.gend[cgi * M + m];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kStScanBatch; ++u) {
+      const int ci = lo + u;
+      if (ci < nchunks) {
+        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+        *reinterpret_cast<uint4*>(out + cgi * per + e) = pack8(run);
+        float a[8];
+        if (is_k) {
+          a[0] = __expf(da[u].x); a[1] = __expf(da[u].y); a[2] = __expf(da[u].z); a[3] = __expf(da[u].w);
+          a[4] = __expf(db[u].x); a[5] = __expf(db[u].y); a[6] = __expf(db[u].z); a[7] = __expf(db[u].w);
+        } else {
+          const float x = __expf(da[u].x);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[i] = x;
+        }
+        run[0] = run[0] * a[0] + la[u].x; run[1] = run[1] * a[1] + la[u].y;
+        run[2] = run[2] * a[2] + la[u].z; run[3] = run[3] * a[3] + la[u].w;
+        run[4] = run[4] * a[4] + lb[u].x; run[5] = run[5] * a[5] + lb[u].y;
+        run[6] = run[6] * a[6] + lb[u].z; run[7] = run[7] * a[7] + lb[u].w;
+      }
+    }
+  }
+  float* ht = is_k ? d.hkt : d.hvt;
+  if (ht) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ht[nh * per + e + i] = run[i];
+  }
 }
 
 int64_t state_workspace_bytes(const nha_chunk_desc* d) {
-  const int nseg = nseg_max_of(d);
-  if (nseg <= 1) return 0;
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
-  const int64_t per = (int64_t)d->N * d->H * nseg;
-  return (per * SD * 2 + per * d->M) * 4 + 256;
+  const int64_t rows = nha_chunk_count_bound(d->Ttot, d->N) * d->H;
+  return rows * (SD + d->M) * 4 + 256;
+}
+
+// Both launches of the state pass on `scratch` (>= state_workspace_bytes(d) bytes, 16-byte aligned).
+// Every scratch element that the scan reads is written by the first kernel of the same call.
+static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs) {
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  StateWs w;
+  w.local = (float*)scratch;
+  w.gend = w.local + (int64_t)NCB * d->H * SD;
+  const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
+  cudaError_t e = cudaFuncSetAttribute(nha_state_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
+  int st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_state_scan_kernel<<<dim3((unsigned)((SD / 8 + 255) / 256), d->N * d->H), 256, 0, cs>>>(*d, w);
+  return check_launch();
 }
 
 int check_chunk_desc(const nha_chunk_desc* d) {
@@ -286,42 +281,9 @@ extern "C" int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream) {
   int st = check_chunk_desc(d);
   if (st != NHA_OK) return st;
   if (!d->hk_chunks || !d->hv_chunks) return NHA_ERR_BAD_ARG;
-  cudaStream_t cs = (cudaStream_t)stream;
-  StateArgs a;
-  a.d = *d;
-  a.seg_chunks = seg_chunks_of(d);
-  a.nseg_max = nseg_max_of(d);
-  a.seg_local = a.seg_start = a.seg_decay = nullptr;
-  const int smem = state_smem(d->M);
-  cudaError_t e = cudaFuncSetAttribute(nha_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return record_cuda_error(e);
-  const int slices = d->K / 16 + d->V / 16;
-  dim3 block(kStThreads);
-  if (a.nseg_max <= 1) {
-    a.mode = 0;
-    dim3 grid(slices, d->N * d->H, 1);
-    nha_state_kernel<<<grid, block, smem, cs>>>(a);
-    return check_launch();
-  }
   const int64_t need = state_workspace_bytes(d);
   if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
-  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
-  const int64_t per = (int64_t)d->N * d->H * a.nseg_max;
-  a.seg_local = (float*)d->workspace;
-  a.seg_start = a.seg_local + per * SD;
-  a.seg_decay = a.seg_start + per * SD;
-  dim3 grid(slices, d->N * d->H, a.nseg_max);
-  a.mode = 1;
-  nha_state_kernel<<<grid, block, smem, cs>>>(a);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  dim3 cgrid((unsigned)((SD + 255) / 256), d->N * d->H);
-  nha_state_combine_kernel<<<cgrid, 256, 0, cs>>>(a);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  a.mode = 2;
-  nha_state_kernel<<<grid, block, smem, cs>>>(a);
-  return check_launch();
+  return state_pass_on(d, d->workspace, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -330,8 +292,8 @@ extern "C" int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream) {
 // Some hosts of this library own no device allocator: a plugin that is handed only its input and
 // output buffers, or a serving loop that forbids allocation after start-up because cudaMalloc
 // synchronises the device and can fail under memory pressure.  nha_chunk_state_pass needs a
-// caller-provided workspace as soon as a sequence spans more than one segment; the variant below
-// takes that workspace from a fixed array that lives in the library's own device image instead.
+// caller-provided workspace for the per-chunk terms; the variant below takes that workspace from
+// a fixed array that lives in the library's own device image instead.
 // Every GPU that loads the library holds the array (kStaticScratchBytes) until the process exits.
 constexpr size_t kStaticScratchBytes = 16u << 20;
 static __device__ __align__(256) unsigned char g_state_scratch[kStaticScratchBytes];
@@ -369,38 +331,7 @@ extern "C" int nha_chunk_state_pass_static(const nha_chunk_desc* d, void* stream
   void* scratch = nullptr;
   st = static_scratch_for_current_device(&scratch);
   if (st != NHA_OK) return st;
-  cudaStream_t cs = (cudaStream_t)stream;
-  StateArgs a;
-  a.d = *d;
-  a.seg_chunks = seg_chunks_of(d);
-  a.nseg_max = nseg_max_of(d);
-  a.seg_local = a.seg_start = a.seg_decay = nullptr;
-  const int smem = state_smem(d->M);
-  cudaError_t e = cudaFuncSetAttribute(nha_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return record_cuda_error(e);
-  const int slices = d->K / 16 + d->V / 16;
-  dim3 block(kStThreads);
-  if (a.nseg_max <= 1) {
-    a.mode = 0;
-    nha_state_kernel<<<dim3(slices, d->N * d->H, 1), block, smem, cs>>>(a);
-    return check_launch();
-  }
-  // every element of the scratch that is read below is written earlier in this same call, so the
-  // contents left by the previous call never matter and nothing has to be cleared
-  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
-  const int64_t per = (int64_t)d->N * d->H * a.nseg_max;
-  a.seg_local = (float*)scratch;
-  a.seg_start = a.seg_local + per * SD;
-  a.seg_decay = a.seg_start + per * SD;
-  dim3 grid(slices, d->N * d->H, a.nseg_max);
-  a.mode = 1;
-  nha_state_kernel<<<grid, block, smem, cs>>>(a);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  nha_state_combine_kernel<<<dim3((unsigned)((SD + 255) / 256), d->N * d->H), 256, 0, cs>>>(a);
-  st = check_launch();
-  if (st != NHA_OK) return st;
-  a.mode = 2;
-  nha_state_kernel<<<grid, block, smem, cs>>>(a);
-  return check_launch();
+  // every element of the scratch that is read is written earlier in this same call, so the contents
+  // left by the previous call never matter and nothing has to be cleared
+  return state_pass_on(d, scratch, (cudaStream_t)stream);
 }
