@@ -511,41 +511,75 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
 #pragma unroll
     for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
   }
-  // state gradients at the chunk end: fp32 in global, bf16 operands here
+  // State gradients at the chunk end: fp32 in global, bf16 operands here.  The same pass forms the
+  // gate-gradient carry of all later chunks, <DK, hk> + <DV, hv> with the states at this chunk's end
+  // (the next chunk's start; the fp32 final state for the last chunk), per slot.
   const float* dkg = w.dkc + ((size_t)cg * H + h) * D * M;
   const float* dvg = w.dvc + ((size_t)cg * H + h) * M * D;
-  for (int i = tid; i < D * 8; i += kBUThreads) {          // DK [D rows kk][64 m]
-    const int r = i >> 3, c8 = i & 7;
-    float f[8];
-    *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8);
-    *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8 + 4);
-    *reinterpret_cast<uint4*>(sm + L::tDK + sw_off(r, c8)) = pack8(f);
-  }
-  for (int i = tid; i < M * (D / 8); i += kBUThreads) {    // DV [64 m][D v] as D/64 column tiles
-    const int r = i / (D / 8), c = i % (D / 8);
-    float f[8];
-    *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c);
-    *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c + 4);
-    *reinterpret_cast<uint4*>(sm + L::tDV + (c >> 3) * 8192 + sw_off(r, c & 7)) = pack8(f);
-  }
-  // gate-gradient carry of all later chunks: <DK, hk> + <DV, hv> at this chunk's end (= the next chunk's start)
+  if (tid < 64) cgv[tid] = 0.f;
+  __syncthreads();
   {
-    const int m = tid & 63, half = tid >> 6;
-    float acc = 0.f;
-    if (ci < nchunks - 1) {
-      const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(cg + 1) * H + h) * D * M;
-      const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(cg + 1) * H + h) * M * D;
-      for (int kk = half * (D / 2); kk < (half + 1) * (D / 2); ++kk) acc += dkg[(size_t)kk * M + m] * bf2f(hkn[(size_t)kk * M + m]);
-      for (int vv = half * (D / 2); vv < (half + 1) * (D / 2); ++vv) acc += dvg[(size_t)m * D + vv] * bf2f(hvn[(size_t)m * D + vv]);
-    } else if (d.d_hkt && d.hkt && d.hvt) {
-      for (int kk = half * (D / 2); kk < (half + 1) * (D / 2); ++kk)
-        acc += d.d_hkt[nh * D * M + (size_t)kk * M + m] * d.hkt[nh * D * M + (size_t)kk * M + m];
-      for (int vv = half * (D / 2); vv < (half + 1) * (D / 2); ++vv)
-        acc += d.d_hvt[nh * M * D + (size_t)m * D + vv] * d.hvt[nh * M * D + (size_t)m * D + vv];
+    const bool last = ci >= nchunks - 1;
+    const bool have_next = !last || (d.d_hkt && d.hkt && d.hvt);
+    const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(cg + 1) * H + h) * D * M;
+    const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(cg + 1) * H + h) * M * D;
+    const float* hkf = d.hkt ? d.hkt + nh * D * M : nullptr;
+    const float* hvf = d.hvt ? d.hvt + nh * M * D : nullptr;
+    // DK [D rows kk][64 m]: this thread always owns the same eight slots
+    float ck[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int jj = 0; jj < D * 8 / kBUThreads; ++jj) {
+      const int i = tid + kBUThreads * jj;
+      const int r = i >> 3, c8 = i & 7;
+      float f[8], nx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8);
+      *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8 + 4);
+      if (have_next) {
+        if (!last) {
+          unpack8(*reinterpret_cast<const uint4*>(hkn + (size_t)r * M + 8 * c8), nx);
+        } else {
+          *reinterpret_cast<float4*>(nx) = *reinterpret_cast<const float4*>(hkf + (size_t)r * M + 8 * c8);
+          *reinterpret_cast<float4*>(nx + 4) = *reinterpret_cast<const float4*>(hkf + (size_t)r * M + 8 * c8 + 4);
+        }
+      }
+      *reinterpret_cast<uint4*>(sm + L::tDK + sw_off(r, c8)) = pack8(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ck[e] += f[e] * nx[e];
     }
-    if (half == 1) cgv[m] = acc;
-    __syncthreads();
-    if (half == 0) cgv[m] += acc;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 8);
+      ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 16);
+    }
+    if (lane < 8) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) atomicAdd(&cgv[8 * lane + e], ck[e]);
+    }
+    // DV [64 m][D v] as D/64 column tiles: a slot's row is spread over D/8 neighbouring lanes
+    constexpr int C8 = D / 8;
+#pragma unroll
+    for (int jj = 0; jj < M * C8 / kBUThreads; ++jj) {
+      const int i = tid + kBUThreads * jj;
+      const int r = i / C8, c = i % C8;
+      float f[8], nx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c);
+      *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c + 4);
+      if (have_next) {
+        if (!last) {
+          unpack8(*reinterpret_cast<const uint4*>(hvn + (size_t)r * D + 8 * c), nx);
+        } else {
+          *reinterpret_cast<float4*>(nx) = *reinterpret_cast<const float4*>(hvf + (size_t)r * D + 8 * c);
+          *reinterpret_cast<float4*>(nx + 4) = *reinterpret_cast<const float4*>(hvf + (size_t)r * D + 8 * c + 4);
+        }
+      }
+      *reinterpret_cast<uint4*>(sm + L::tDV + (c >> 3) * 8192 + sw_off(r, c & 7)) = pack8(f);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += f[e] * nx[e];
+#pragma unroll
+      for (int o = 1; o < C8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (c == 0) atomicAdd(&cgv[r], acc);
+    }
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
