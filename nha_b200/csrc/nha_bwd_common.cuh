@@ -22,6 +22,9 @@ struct BwdWs {
   float* gend;    // [NC, H, M]      total shifted log gate of each chunk
   bf16* dza;      // [Ttot, HQ, M]   scale * dz_slot .* a   (tensor-memory path only)
   bf16* paq;      // [Ttot, HQ, M]   p_slot .* a            (tensor-memory path only)
+  bf16* dkb;      // [NC, H, K, M]   bf16 copy of the scanned dkc (tensor-memory path only)
+  bf16* dvb;      // [NC, H, M, V]   bf16 copy of the scanned dvc
+  float* gcarry;  // [NC, H, M]      gate-gradient carry of all later chunks
   const int* flags;   // [NC, H] chunks the tensor-memory forward left to the general kernels, or NULL
   int gate;           // 0: a kernel handles every chunk; 1: only flagged chunks; 2: only unflagged chunks
 };
@@ -38,6 +41,8 @@ __host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* b
   const int64_t o_dkc = take(NC * d->H * d->K * d->M * 4), o_dvc = take(NC * d->H * d->M * d->V * 4);
   const int64_t o_dza = take(T * d->HQ * d->M * 2), o_paq = take(T * d->HQ * d->M * 2);
   const int64_t o_gend = take(NC * d->H * d->M * 4);
+  const int64_t o_dkb = take(NC * d->H * d->K * d->M * 2), o_dvb = take(NC * d->H * d->M * d->V * 2);
+  const int64_t o_gcarry = take(NC * d->H * d->M * 4);
   if (w && base) {
     char* b = (char*)base;
     w->delta = (float*)(b + o_delta); w->lj = (float*)(b + o_lj); w->dvacc = (float*)(b + o_dvacc);
@@ -46,6 +51,7 @@ __host__ inline int64_t bwd_ws_layout(const nha_chunk_desc* d, BwdWs* w, void* b
     w->dkc = (float*)(b + o_dkc); w->dvc = (float*)(b + o_dvc);
     w->dza = (bf16*)(b + o_dza); w->paq = (bf16*)(b + o_paq);
     w->gend = (float*)(b + o_gend);
+    w->dkb = (bf16*)(b + o_dkb); w->dvb = (bf16*)(b + o_dvb); w->gcarry = (float*)(b + o_gcarry);
     w->flags = nullptr; w->gate = 0;
   }
   return off;

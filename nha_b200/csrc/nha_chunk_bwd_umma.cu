@@ -438,30 +438,129 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
 }
 
 // ================================================================================================
+// gate-gradient carry and bf16 copies of the state gradients (between the scan and the columns pass)
+// ================================================================================================
+// For chunk c the gate gradient of every later chunk enters as one number per slot,
+//     carry[m] = <DK_end[:, m], hk_next[:, m]> + <DV_end[m, :], hv_next[m, :]>,
+// with the states at the end of chunk c (the next chunk's start state; the fp32 final state for the
+// last chunk of a sequence).  The same sweep over DK_end / DV_end stores the bf16 operand copies the
+// columns pass multiplies with.  One CTA per (chunk, kv head); M == 64.
+constexpr int kCarryThreads = 256;
+__global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const nha_chunk_desc d, const BwdWs w) {
+  constexpr int M = 64;
+  const int H = d.H, N = d.N, K = d.K, V = d.V;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const int n = d.plan[N + 1 + cg];
+  if (n < 0) return;
+  if (!chunk_gate(w, cg, h, H)) return;
+  const int ci = cg - d.plan[n];
+  const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const size_t nh = (size_t)n * H + h, ch = (size_t)cg * H + h;
+  __shared__ float acc_s[M];
+  if (tid < M) acc_s[tid] = 0.f;
+  __syncthreads();
+  const bool last = ci >= nchunks - 1;
+  const bool have_next = !last || (d.d_hkt && d.hkt && d.hvt);
+  const float* dkg = w.dkc + ch * K * M;
+  const float* dvg = w.dvc + ch * M * V;
+  bf16* dkb = w.dkb + ch * K * M;
+  bf16* dvb = w.dvb + ch * M * V;
+  const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(cg + 1) * H + h) * K * M;
+  const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(cg + 1) * H + h) * M * V;
+  const float* hkf = d.hkt ? d.hkt + nh * K * M : nullptr;
+  const float* hvf = d.hvt ? d.hvt + nh * M * V : nullptr;
+  // DK [K][64]: a thread always owns the same four slots
+  float ck[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = tid; i < K * (M / 4); i += kCarryThreads) {
+    const float4 f = *reinterpret_cast<const float4*>(dkg + 4 * (size_t)i);
+    float4 nx = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (have_next) {
+      if (!last) {
+        const uint2 u = *reinterpret_cast<const uint2*>(hkn + 4 * (size_t)i);
+        const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        nx = make_float4(lo2.x, lo2.y, hi2.x, hi2.y);
+      } else {
+        nx = *reinterpret_cast<const float4*>(hkf + 4 * (size_t)i);
+      }
+    }
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(f.x, f.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(f.z, f.w);
+    *reinterpret_cast<uint2*>(dkb + 4 * (size_t)i) = o;
+    ck[0] += f.x * nx.x; ck[1] += f.y * nx.y; ck[2] += f.z * nx.z; ck[3] += f.w * nx.w;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 16);
+  if (lane < 16) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) atomicAdd(&acc_s[4 * lane + e], ck[e]);
+  }
+  // DV [64][V]: a slot's row is spread over V/4 neighbouring lanes
+  const int C4 = V / 4;
+  for (int i = tid; i < M * C4; i += kCarryThreads) {
+    const int r = i / C4, c = i - r * C4;
+    const float4 f = *reinterpret_cast<const float4*>(dvg + 4 * (size_t)i);
+    float4 nx = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (have_next) {
+      if (!last) {
+        const uint2 u = *reinterpret_cast<const uint2*>(hvn + 4 * (size_t)i);
+        const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        nx = make_float4(lo2.x, lo2.y, hi2.x, hi2.y);
+      } else {
+        nx = *reinterpret_cast<const float4*>(hvf + 4 * (size_t)i);
+      }
+    }
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(f.x, f.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(f.z, f.w);
+    *reinterpret_cast<uint2*>(dvb + 4 * (size_t)i) = o;
+    float acc = f.x * nx.x + f.y * nx.y + f.z * nx.z + f.w * nx.w;
+    for (int o2 = 1; o2 < C4 && o2 < 32; o2 <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+    if (c == 0) atomicAdd(&acc_s[r], acc);
+  }
+  __syncthreads();
+  if (tid < M) w.gcarry[ch * M + tid] = acc_s[tid];
+}
+
+// ================================================================================================
 // columns pass
 // ================================================================================================
 template <int D, int R>
 struct ColsLayout {
   static constexpr int KT = D / 64;
   static constexpr int kATile = R * 128;
-  static constexpr int tQ = 0;                          // q_gsa [R][D]; q..pa later hold the fp32 scan buffer of dg
+  // per-head tiles and the tril buffers first: together they are dead once the head loop is over and
+  // then hold the staged epilogue inputs (gate terms, window dv, s') and the dg scan
+  static constexpr int tQ = 0;                          // q_gsa [R][D]
   static constexpr int tDO = tQ + KT * kATile;          // do [R][D]
   static constexpr int tZA = tDO + KT * kATile;         // scale dz a [R][64]
   static constexpr int tPA = tZA + kATile;              // p a [R][64]
-  static constexpr int tK = tPA + kATile;               // k' [64][D]
-  static constexpr int tV = tK + KT * 8192;             // v' [64][D]
-  static constexpr int tSB = tV + KT * 8192;            // s' b
-  static constexpr int tSBE = tSB + 8192;               // s' exp(Gend - G)
-  static constexpr int tDK = tSBE + 8192;               // DK at the chunk end [D][64]
-  static constexpr int tDV = tDK + D * 128;             // DV at the chunk end [64][D]
-  static constexpr int bufA = tDV + KT * 8192;          // tril(A) -> tril(E)
+  static constexpr int bufA = tPA + kATile;             // tril(A) -> tril(E)
   static constexpr int bufB = bufA + kATile;            // tril(Av) -> tril(Bv)
-  static constexpr int oG = bufB + kATile;
+  static constexpr int tK = bufB + kATile;              // k' [64][D]
+  static constexpr int tV = tK + KT * 8192;             // v' [64][D]
+  static constexpr int tSB = tV + KT * 8192;            // s' b, after the head loop s' exp(Gend - G)
+  static constexpr int tDK = tSB + 8192;                // DK at the chunk end [D][64]
+  static constexpr int tDV = tDK + D * 128;             // DV at the chunk end [64][D]
+  static constexpr int oG = tDV + KT * 8192;
   static constexpr int oR = oG + 64 * 65 * 4;           // [64] reference, [64] carry
   static constexpr int oBar = oR + 512;
   static constexpr int total = oBar + 64 + 1024;
-  static constexpr int cA = 0, cAv = 64, cDK = 128, cDV = 128 + D, cDS = 128 + 2 * D, cDS2 = cA;
-  static_assert(tK - tQ >= 64 * 65 * 4, "the dg scan buffer must fit in the per-head tiles (q, do, dza, pa), dead by then");
+  // staged epilogue inputs, fp32 rows padded to 16-byte multiples that spread over the banks
+  static constexpr int kLdG = 68, kLdV = D + 4, kLdS = 72;
+  static constexpr int eG = 0;                          // [64][68] fp32 dgA, then dgraw and its scan
+  static constexpr int eV = eG + 64 * kLdG * 4;         // [64][D+4] fp32 window part of dv
+  static constexpr int eS = eV + 64 * kLdV * 4;         // [64][72] bf16 s'
+  static_assert(eS + 64 * kLdS * 2 <= tK, "the staged epilogue inputs must fit in the per-head tiles");
+  // D == 64 with one query head per kv head: 256 columns, so two CTAs share an SM; the intra-chunk ds'
+  // accumulator then borrows the dk' columns for one round and waits in registers
+  static constexpr bool kDsInRegs = D == 64 && R == 64;
+  static constexpr int kTmemCols = kDsInRegs ? 256 : 512;
+  static constexpr int cA = 0, cAv = 64, cDK = 128, cDV = 128 + D, cDS = kDsInRegs ? cDK : 128 + 2 * D, cDS2 = cA;
 };
 
 template <int D, int R>
@@ -474,15 +573,13 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   const int n = d.plan[N + 1 + cg];
   if (n < 0) return;
   if (!chunk_gate(w, cg, h, H)) return;
-  const int chunk0 = d.plan[n];
-  const int ci = cg - chunk0;
+  const int ci = cg - d.plan[n];
   const int t0 = d.cu_seqlens[n];
   const int len = d.cu_seqlens[n + 1] - t0;
-  const int nchunks = (len + kChunk - 1) / kChunk;
   const int c0 = ci * kChunk;
   const int shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const size_t nh = (size_t)n * H + h;
+  const size_t ch = (size_t)cg * H + h;
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -492,10 +589,28 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
 
+  // ---- everything the first head tile needs goes in flight at once -------------------------------------
   const int lo = 0, hi = len - shift;
   load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
   load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  cp_commit();
+  load_sw<64>(sm + L::tDK, 0, w.dkb + ch * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D>(sm + L::tDV, 8192, w.dvb + ch * M * D, D, 0, 0, M, M, 0, tid);
+#define NHA_LOAD_HEAD_TILE(ht_)                                                                                      \
+  do {                                                                                                               \
+    const int hq0_ = h * NG + (ht_) * TH;                                                                            \
+    _Pragma("unroll") for (int t2 = 0; t2 < TH; ++t2) {                                                              \
+      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
+                 c0, 0, len, 64, 64 * t2, tid);                                                                      \
+      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,    \
+                 c0, 0, len, 64, 64 * t2, tid);                                                                      \
+      load_sw<64>(sm + L::tZA, 0, w.dza + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,        \
+                  64 * t2, tid);                                                                                     \
+      load_sw<64>(sm + L::tPA, 0, w.paq + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,        \
+                  64 * t2, tid);                                                                                     \
+    }                                                                                                                \
+    cp_commit();                                                                                                     \
+  } while (0)
+  NHA_LOAD_HEAD_TILE(0);
   uint4 sreg[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -511,76 +626,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
 #pragma unroll
     for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
   }
-  // State gradients at the chunk end: fp32 in global, bf16 operands here.  The same pass forms the
-  // gate-gradient carry of all later chunks, <DK, hk> + <DV, hv> with the states at this chunk's end
-  // (the next chunk's start; the fp32 final state for the last chunk), per slot.
-  const float* dkg = w.dkc + ((size_t)cg * H + h) * D * M;
-  const float* dvg = w.dvc + ((size_t)cg * H + h) * M * D;
-  if (tid < 64) cgv[tid] = 0.f;
-  __syncthreads();
-  {
-    const bool last = ci >= nchunks - 1;
-    const bool have_next = !last || (d.d_hkt && d.hkt && d.hvt);
-    const bf16* hkn = (const bf16*)d.hk_chunks + ((size_t)(cg + 1) * H + h) * D * M;
-    const bf16* hvn = (const bf16*)d.hv_chunks + ((size_t)(cg + 1) * H + h) * M * D;
-    const float* hkf = d.hkt ? d.hkt + nh * D * M : nullptr;
-    const float* hvf = d.hvt ? d.hvt + nh * M * D : nullptr;
-    // DK [D rows kk][64 m]: this thread always owns the same eight slots
-    float ck[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int jj = 0; jj < D * 8 / kBUThreads; ++jj) {
-      const int i = tid + kBUThreads * jj;
-      const int r = i >> 3, c8 = i & 7;
-      float f[8], nx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8);
-      *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dkg + (size_t)r * M + 8 * c8 + 4);
-      if (have_next) {
-        if (!last) {
-          unpack8(*reinterpret_cast<const uint4*>(hkn + (size_t)r * M + 8 * c8), nx);
-        } else {
-          *reinterpret_cast<float4*>(nx) = *reinterpret_cast<const float4*>(hkf + (size_t)r * M + 8 * c8);
-          *reinterpret_cast<float4*>(nx + 4) = *reinterpret_cast<const float4*>(hkf + (size_t)r * M + 8 * c8 + 4);
-        }
-      }
-      *reinterpret_cast<uint4*>(sm + L::tDK + sw_off(r, c8)) = pack8(f);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) ck[e] += f[e] * nx[e];
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 8);
-      ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 16);
-    }
-    if (lane < 8) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) atomicAdd(&cgv[8 * lane + e], ck[e]);
-    }
-    // DV [64 m][D v] as D/64 column tiles: a slot's row is spread over D/8 neighbouring lanes
-    constexpr int C8 = D / 8;
-#pragma unroll
-    for (int jj = 0; jj < M * C8 / kBUThreads; ++jj) {
-      const int i = tid + kBUThreads * jj;
-      const int r = i / C8, c = i % C8;
-      float f[8], nx[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c);
-      *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dvg + (size_t)r * D + 8 * c + 4);
-      if (have_next) {
-        if (!last) {
-          unpack8(*reinterpret_cast<const uint4*>(hvn + (size_t)r * D + 8 * c), nx);
-        } else {
-          *reinterpret_cast<float4*>(nx) = *reinterpret_cast<const float4*>(hvf + (size_t)r * D + 8 * c);
-          *reinterpret_cast<float4*>(nx + 4) = *reinterpret_cast<const float4*>(hvf + (size_t)r * D + 8 * c + 4);
-        }
-      }
-      *reinterpret_cast<uint4*>(sm + L::tDV + (c >> 3) * 8192 + sw_off(r, c & 7)) = pack8(f);
-      float acc = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc += f[e] * nx[e];
-#pragma unroll
-      for (int o = 1; o < C8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (c == 0) atomicAdd(&cgv[r], acc);
-    }
-  }
+  if (tid < 64) cgv[tid] = w.gcarry[ch * M + tid];
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
   {
@@ -605,18 +651,13 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   for (int j = 0; j < 4; ++j) {
     const int i = tid + kBUThreads * j;
     const int r = i >> 3, c8 = i & 7;
-    float sv[8], o1[8], o2[8];
+    float sv[8], o1[8];
     unpack8(sreg[j], sv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float gl = Gs[r * 65 + 8 * c8 + e];
-      o1[e] = sv[e] * __expf(Rs[8 * c8 + e] - gl);
-      o2[e] = sv[e] * __expf(Gs[63 * 65 + 8 * c8 + e] - gl);
-    }
+    for (int e = 0; e < 8; ++e) o1[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
     *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(o1);
-    *reinterpret_cast<uint4*>(sm + L::tSBE + sw_off(r, c8)) = pack8(o2);
   }
-  if (warp == 0) tmem_alloc(tslot, 512);
+  if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -633,21 +674,12 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   const int krow = warp * 16 + (lane & 15);
   const uint32_t aQ = smem_u32(sm + L::tQ), aDO = smem_u32(sm + L::tDO), aZA = smem_u32(sm + L::tZA);
   const uint32_t aPA = smem_u32(sm + L::tPA), aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV);
-  const uint32_t aSB = smem_u32(sm + L::tSB), aSBE = smem_u32(sm + L::tSBE), aDK = smem_u32(sm + L::tDK);
+  const uint32_t aSB = smem_u32(sm + L::tSB), aDK = smem_u32(sm + L::tDK);
   const uint32_t aDV = smem_u32(sm + L::tDV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
+  float dsk[L::kDsInRegs ? 64 : 1];
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
-    const int hq0 = h * NG + ht * TH;
-#pragma unroll
-    for (int t2 = 0; t2 < TH; ++t2) {
-      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
-                 64, 64 * t2, tid);
-      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
-                 64, 64 * t2, tid);
-      load_sw<64>(sm + L::tZA, 0, w.dza + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
-      load_sw<64>(sm + L::tPA, 0, w.paq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
-    }
-    cp_commit();
+    if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
     cp_wait_all();
     NHA_SMEM_TO_MMA();
     if (tid == 0) {
@@ -666,6 +698,10 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
       mma_tile(tbase + L::cAv, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);               // Bv = pa SB^T
     }
     NHA_MMA_WAIT();
+    if constexpr (L::kDsInRegs) {
+      tmem_ld32(tlane + L::cDS, dsk);
+      tmem_ld32(tlane + L::cDS + 32, dsk + 32);
+    }
     NHA_TRIL_TO_SMEM(L::cA, L::bufA);
     NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
     NHA_SMEM_TO_MMA();
@@ -682,14 +718,59 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
     __syncthreads();
     tc_fence_after();
   }
+#undef NHA_LOAD_HEAD_TILE
   // ---- inter-chunk parts from the state gradients at the chunk end ------------------------------------------
+  // The per-head tiles are dead now: the rows the epilogue needs from global memory (gate terms of the
+  // rows pass, window part of dv, s') are fetched into their place while the last products run.
+  const int kp = c0 + krow, kj = kp - shift;                     // this thread's key row: shifted position, source token
+  const bool keep = kactive && kj >= 0 && kp < len;
+  float* eG = (float*)(sm + L::eG);
+  float* eV = (float*)(sm + L::eV);
+  bf16* eS = (bf16*)(sm + L::eS);
+  {
+    // rows r of the chunk: shifted position c0 + r, source token c0 + r - shift
+    const float* gsrc = w.dga + ((size_t)t0 * H + h) * M;
+    for (int i = tid; i < 64 * 16; i += kBUThreads) {
+      const int r = i >> 4, c = i & 15;
+      const int p = c0 + r;
+      const bool ok = p - shift >= 0 && p < len;
+      cp16(eG + r * L::kLdG + 4 * c, gsrc + (size_t)(ok ? p : 0) * H * M + 4 * c, ok);
+    }
+    const float* vsrc = w.dvacc + ((size_t)t0 * H + h) * D;
+    for (int i = tid; i < 64 * (D / 4); i += kBUThreads) {
+      const int r = i / (D / 4), c = i % (D / 4);
+      const int p = c0 + r, j = p - shift;
+      const bool ok = j >= 0 && p < len;
+      cp16(eV + r * L::kLdV + 4 * c, vsrc + (size_t)(ok ? j : 0) * H * D + 4 * c, ok);
+    }
+    const bf16* ssrc = (const bf16*)d.s + ((size_t)t0 * H + h) * M;
+    for (int i = tid; i < 64 * 8; i += kBUThreads) {
+      const int r = i >> 3, c = i & 7;
+      const int p = c0 + r, j = p - shift;
+      const bool ok = j >= 0 && p < len;
+      cp16(eS + r * L::kLdS + 8 * c, ssrc + (size_t)(ok ? j : 0) * H * M + 8 * c, ok);
+    }
+    cp_commit();
+  }
+  // s' exp(Gend - G) replaces s' b (every product that read it has completed)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + kBUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    float sv[8], o2[8];
+    unpack8(sreg[j], sv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o2[e] = sv[e] * __expf(Gs[63 * 65 + 8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(o2);
+  }
+  NHA_SMEM_TO_MMA();
   if (!failed) {
     if (tid == 0) {
 #pragma unroll
       for (int nb = 0; nb < KT; ++nb) {
         // dk' += sbe DK^T (DK rows kk as the N rows of a K-major operand), dv' += sbe DV (DV as MN-major, k = slot)
-        mma_tile(tbase + L::cDK + 64 * nb, aSBE, 0, aDK + nb * 8192, 0, 64, 64, 4, 0, true);
-        mma_tile(tbase + L::cDV + 64 * nb, aSBE, 0, aDV + nb * 8192, 0, 64, 64, 4, 1, true);
+        mma_tile(tbase + L::cDK + 64 * nb, aSB, 0, aDK + nb * 8192, 0, 64, 64, 4, 0, true);
+        mma_tile(tbase + L::cDV + 64 * nb, aSB, 0, aDV + nb * 8192, 0, 64, 64, 4, 1, true);
       }
       // DS2 = k' DK + v' DV^T
       mma_tile(tbase + L::cDS2, aK, 8192, aDK, 0, 64, 64, D / 16, 1, false);
@@ -697,37 +778,40 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
     }
     NHA_MMA_WAIT();
   }
+  cp_wait_all();
+  __syncthreads();
   // ---- epilogue: one thread per key row ---------------------------------------------------------------------------
-  float* scan = (float*)(sm + L::tQ);                     // [64][65] dgraw, then its reverse cumulative sum
-  const int p = c0 + krow, j = p - shift;
-  const bool keep = kactive && j >= 0 && p < len;
   {
     float dsi[32], ds2[32];
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
-      tmem_ld32(tlane + L::cDS + 32 * part, dsi);
+      if constexpr (L::kDsInRegs) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) dsi[e] = dsk[32 * part + e];
+      } else {
+        tmem_ld32(tlane + L::cDS + 32 * part, dsi);
+      }
       tmem_ld32(tlane + L::cDS2 + 32 * part, ds2);
       if (kactive) {
-        float sv[32];
-        if (keep) {
-#pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8)
-            unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 32 * part + 8 * c8), sv + 8 * c8);
-        }
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          float ds8[8];
+          float ds8[8], sv[8];
+          unpack8(*reinterpret_cast<const uint4*>(eS + krow * L::kLdS + 32 * part + 8 * c8), sv);
+          float* grow = eG + krow * L::kLdG + 32 * part + 8 * c8;
+          const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
+          const float ga[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+          float gr[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int m = 32 * part + 8 * c8 + e;
             const float gl = Gs[krow * 65 + m];
             const float ds = __expf(Rs[m] - gl) * dsi[8 * c8 + e] + __expf(Gs[63 * 65 + m] - gl) * ds2[8 * c8 + e];
             ds8[e] = ds;
-            float graw = 0.f;
-            if (keep) graw = w.dga[((size_t)(t0 + p) * H + h) * M + m] - sv[8 * c8 + e] * ds;
-            scan[krow * 65 + m] = graw;
+            gr[e] = keep ? ga[e] - sv[e] * ds : 0.f;
           }
-          if (keep) *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + j) * H + h) * M + 32 * part + 8 * c8) = pack8(ds8);
+          *reinterpret_cast<float4*>(grow) = make_float4(gr[0], gr[1], gr[2], gr[3]);
+          *reinterpret_cast<float4*>(grow + 4) = make_float4(gr[4], gr[5], gr[6], gr[7]);
+          if (keep) *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + kj) * H + h) * M + 32 * part + 8 * c8) = pack8(ds8);
         }
       }
     }
@@ -736,51 +820,54 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
     for (int part = 0; part < D / 32; ++part) {
       tmem_ld32(tlane + L::cDK + 32 * part, ov);
       if (keep) {
-        bf16* orow = (bf16*)d.dk_gsa + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+        bf16* orow = (bf16*)d.dk_gsa + ((size_t)(t0 + kj) * H + h) * D + 32 * part;
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
       }
       tmem_ld32(tlane + L::cDV + 32 * part, ov);
       if (keep) {
-        const float* wa = w.dvacc + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+        const float* wa = eV + krow * L::kLdV + 32 * part;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) ov[e] += wa[e];
-        bf16* orow = (bf16*)d.dv + ((size_t)(t0 + j) * H + h) * D + 32 * part;
+        for (int e = 0; e < 32; e += 4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(wa + e);
+          ov[e] += a4.x; ov[e + 1] += a4.y; ov[e + 2] += a4.z; ov[e + 3] += a4.w;
+        }
+        bf16* orow = (bf16*)d.dv + ((size_t)(t0 + kj) * H + h) * D + 32 * part;
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
       }
     }
   }
+  // the accumulators are drained: release the tensor memory before the tail of the epilogue
+  tc_fence_before();
   __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
   // reverse cumulative sum of dgraw along the rows (two threads per column), plus the carry
   {
     const int m = tid & 63, half = tid >> 6;
     float run = 0.f;
 #pragma unroll 8
     for (int r = 32 * half + 31; r >= 32 * half; --r) {
-      run += scan[r * 65 + m];
-      scan[r * 65 + m] = run;
+      run += eG[r * L::kLdG + m];
+      eG[r * L::kLdG + m] = run;
     }
     __syncthreads();
-    const float add = cgv[m] + (half == 0 ? scan[32 * 65 + m] : 0.f);
+    const float add = cgv[m] + (half == 0 ? eG[32 * L::kLdG + m] : 0.f);
     __syncthreads();                                  // every read of the upper half's total precedes its update
 #pragma unroll 8
-    for (int r = 32 * half; r < 32 * half + 32; ++r) scan[r * 65 + m] += add;
+    for (int r = 32 * half; r < 32 * half + 32; ++r) eG[r * L::kLdG + m] += add;
     __syncthreads();
   }
   if (keep) {
 #pragma unroll
     for (int c8 = 0; c8 < 8; ++c8) {
-      float g8[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) g8[e] = scan[krow * 65 + 8 * c8 + e];
-      *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + j) * H + h) * M + 8 * c8) = pack8(g8);
+      const float* grow = eG + krow * L::kLdG + 8 * c8;
+      const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
+      const float g8[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + kj) * H + h) * M + 8 * c8) = pack8(g8);
     }
   }
   if (failed && tid == 0) atomicExch(err, 1);
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tbase, 512);
 }
 #undef NHA_MMA_WAIT
 #undef NHA_SMEM_TO_MMA
@@ -802,6 +889,9 @@ static int launch_cols(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaSt
   cudaError_t e = cudaFuncSetAttribute(nha_bwd_cols_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  nha_bwd_gate_carry_kernel<<<dim3(NCB, d->H), kCarryThreads, 0, cs>>>(*d, w);
+  int st = check_launch();
+  if (st != NHA_OK) return st;
   nha_bwd_cols_umma_kernel<D, R><<<dim3(NCB, d->H), kBUThreads, L::total, cs>>>(*d, w, err);
   return check_launch();
 }
