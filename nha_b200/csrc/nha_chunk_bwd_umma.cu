@@ -54,10 +54,15 @@ struct RowsLayout {
   static constexpr int total = oBar + 64 + 1024;
   static constexpr int tW = tQ;
   static constexpr int tWV = R == 128 ? tQ + KT * 8192 : tWVx;
-  static constexpr int cA = 0, cAv = 64, cQH = 128, cY = 192, cDQ = 256, cDQS = 256 + D;
-  static constexpr int cS = cQH, cDP = cY;
+  // Tensor-memory columns.  D == 64 fits 256 columns (two CTAs per SM) by reusing columns as soon as
+  // their accumulator has been read: A, Av, QH, Y -> X, X2 -> E -> dq_gsa (over QH), local terms (over
+  // Av, Y), then the window loop's S, dP, dq_swa (over A, Av, Y).
+  static constexpr int kTmemCols = D == 64 ? 256 : 512;
+  static constexpr int cA = 0, cAv = 64, cQH = 128, cY = 192;
+  static constexpr int cDQ = D == 64 ? 128 : 256, cDQS = D == 64 ? 192 : 384;
+  static constexpr int cS = D == 64 ? 0 : 128, cDP = D == 64 ? 64 : 192;
   // chunk-local state-gradient terms, read out before the window loop reuses the columns
-  static constexpr int cLK = D == 64 ? 384 : 0, cLV = D == 64 ? 448 : 128;
+  static constexpr int cLK = D == 64 ? 64 : 0, cLV = D == 64 ? 192 : 128;
 };
 
 template <int D, int R>
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     for (int e = 0; e < 8; ++e) out[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
     *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(out);
   }
-  if (warp == 0) tmem_alloc(tslot, 512);
+  if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -263,7 +268,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
         if (active) {
 #pragma unroll
           for (int c8 = 0; c8 < 4; ++c8) {
-            float zg8[8], za8[8], pg8[8], pa8[8];
+            float zg8[8], za8[8], pg8[8], pa8[8], ga8[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               const int m = 32 * part + 8 * c8 + e;
@@ -275,12 +280,17 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
               if (in_seq) {
                 ps = __expf(ok - Lj);
                 dz = ps * (dps - delta) + dlse * __expf(ok - lse_g);
-                atomicAdd(w.dga + ((size_t)(t0 + pos) * H + h) * M + m, ok * dz + ps * dps);
               }
+              ga8[e] = ok * dz + ps * dps;
               zg8[e] = d.scale * dz * eg;
               za8[e] = d.scale * dz * aI;
               pg8[e] = ps * eg;
               pa8[e] = ps * aI;
+            }
+            if (in_seq) {
+              float4* gdst = reinterpret_cast<float4*>(w.dga + ((size_t)(t0 + pos) * H + h) * M + 32 * part + 8 * c8);
+              atomicAdd(gdst, make_float4(ga8[0], ga8[1], ga8[2], ga8[3]));
+              atomicAdd(gdst + 1, make_float4(ga8[4], ga8[5], ga8[6], ga8[7]));
             }
             const uint4 zg = pack8(zg8), za = pack8(za8);
             *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, 4 * part + c8)) = zg;
@@ -434,7 +444,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
   if (failed && tid == 0) atomicExch(err, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tbase, 512);
+  if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
 }
 
 // ================================================================================================
