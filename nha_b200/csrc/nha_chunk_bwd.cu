@@ -927,6 +927,8 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chu
 int check_chunk_desc(const nha_chunk_desc* d);
 bool bwd_umma_supported(const nha_chunk_desc* d);
 int bwd_umma_launch(const nha_chunk_desc* d, const BwdWs& w, int which, int* err, cudaStream_t cs);
+bool bwd_wcols_umma_supported(const nha_chunk_desc* d);
+int bwd_wcols_umma_launch(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs);
 
 }  // namespace nha
 
@@ -994,8 +996,14 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 2) {
-    nha_bwd_window_cols_kernel<<<grid, block, L2.total, cs>>>(*d, w);
-    st = check_launch();
+    // the window part does not depend on the gates: every chunk takes the tensor-memory kernel when the
+    // shape has one
+    if (bwd_wcols_umma_supported(d) && !(off && off[0] == '1')) {
+      st = bwd_wcols_umma_launch(d, w, err, cs);
+    } else {
+      nha_bwd_window_cols_kernel<<<grid, block, L2.total, cs>>>(*d, w);
+      st = check_launch();
+    }
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 4) {
