@@ -320,7 +320,9 @@ def main():
     with ClockSampler(local) as clk:
         ms = timed(step, args.steps)
     value = world * tokens * args.steps / (ms * 1e-3)
-    launches_per_step = 7
+    # plan, state pass (2), output pass (2), backward: rows (2), window columns (1), slot (1), state-gradient terms +
+    # scan + gate carry + columns + general inter-chunk kernel (5); the general kernels run gated on the chunk flags
+    launches_per_step = 14
 
     # ---- per-kernel timing: every kernel of a step on its own, CUDA events on the launching stream ----
     kernels = {}
@@ -339,20 +341,31 @@ def main():
     calls = {
         'state_pass': lambda: lib.nha_chunk_state_pass(ctypes.byref(desc), stream),
         'output_pass': lambda: lib.nha_chunk_output_pass(ctypes.byref(desc), stream),
-        'bwd_window_rows': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 0, stream),
+        'bwd_rows': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 0, stream),
         'bwd_window_cols': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 1, stream),
-        'bwd_slot': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 2, stream),
-        'bwd_march': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 3, stream),
+        'bwd_slot_general': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 2, stream),
+        'bwd_state_grads_and_cols': lambda: lib.nha_chunk_bwd_stage(ctypes.byref(desc), 3, stream),
     }
-    # compulsory bytes of each kernel per token (all heads): what it must read once and write once
+    # compulsory bytes of each stage per token (all heads): what its kernels must read once and write once,
+    # scratch that one kernel hands to the next included (e = bf16, f = fp32; states per 64-token chunk)
     e, f = 2, 4
+    st = 2 * D * M / 64
     per_tok = {
-        'state_pass': H * ((2 * D + 2 * M) * e + (2 * D * M) * e / 64),
-        'output_pass': H * ((5 * D + 2 * M) * e + (2 * D * M) * e / 64 + D * e + 2 * f),
-        'bwd_window_rows': H * (5 * D * e + 2 * f + D * e + 2 * f),
+        # k', v, s, g in; per-chunk terms out (fp32) and back in; chunk-start states out (bf16)
+        'state_pass': H * ((2 * D + 2 * M) * e + st * (2 * f + e)),
+        # q_gsa, q_swa, k_gsa, k_swa, v, s, g, states in; o and both log-sum-exps out
+        'output_pass': H * ((5 * D + 2 * M) * e + st * e + D * e + 2 * f),
+        # q_gsa, q_swa, do, o, k_gsa, k_swa, v, s, g, states, log-sum-exps in; dq_gsa, dq_swa, delta, joint LSE,
+        # gate terms (fp32), four bf16 copies of dz / p, the chunk's state-gradient terms (fp32) out
+        'bwd_rows': H * ((7 * D + 2 * M) * e + st * e + 2 * f + 2 * D * e + 2 * f + M * f + 4 * M * e + st * f),
+        # k_swa, v, q_swa, do, joint LSE, delta in; dk_swa and the fp32 window part of dv out
         'bwd_window_cols': H * (4 * D * e + 2 * f + D * e + D * f),
-        'bwd_slot': H * ((4 * D + 2 * M) * e + (2 * D * M) * e / 64 + 4 * f + D * e + (2 * D + 2 * M) * f + 2 * M * e),
-        'bwd_march': H * ((4 * D + 2 * M) * e + 2 * M * e + (3 * D + 2 * M) * f + (2 * D * M) * e / 64 + (2 * D + 2 * M) * e),
+        # general kernel of the slot branch: runs only on chunks flagged by the forward (none here)
+        'bwd_slot_general': H * ((4 * D + 2 * M) * e + st * e + 4 * f + D * e + (2 * D + 2 * M) * f + 2 * M * e),
+        # scan (fp32 terms in and out), gate carry (fp32 in, states in, bf16 out), columns pass (q_gsa, do, k_gsa, v,
+        # s, g, dz / p copies, bf16 state gradients, gate terms, window dv in; dk_gsa, dv, ds, dg out)
+        'bwd_state_grads_and_cols': H * (st * 2 * f + st * (f + 2 * e) + (4 * D + 4 * M) * e + st * e + M * f + D * f
+                                         + (2 * D + 2 * M) * e),
     }
     for name, fn in calls.items():
         for _ in range(3):
