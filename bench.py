@@ -374,8 +374,12 @@ def main():
         kernels[name] = {'ms': kms, 'gbs': per_tok[name] * tokens / (kms * 1e-3) / 1e9}
     top = max(kernels, key=lambda k: kernels[k]['ms'])
     peak, how = peaks()
+    # DRAM bytes per token of the stage's dominant kernel from the committed ncu capture (B=4 case; traffic grows
+    # in proportion to the tokens): profiles/bwd_rows_umma_B4_T2048.md, 376.2 MB for 8192 tokens
+    ncu_traffic_per_tok = {'bwd_rows': 376.2e6 / 8192}
+    traffic = ncu_traffic_per_tok[top] * tokens if top in ncu_traffic_per_tok else None
     roofline = {'bound': 'hbm', 'kernel': top, 'achieved': kernels[top]['gbs'], 'peak': peak, 'unit': 'GB/s',
-                'frac': kernels[top]['gbs'] / peak, 'traffic': None, 'peak_source': how,
+                'frac': kernels[top]['gbs'] / peak, 'traffic': traffic, 'peak_source': how,
                 'algorithmic_bytes_per_launch': per_tok[top] * tokens}
     step_gbs = ALG_BYTES_PER_TOKEN * tokens * args.steps / (ms * 1e-3) / 1e9
     step_roofline = {'bound': 'hbm', 'achieved': step_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': step_gbs / peak,

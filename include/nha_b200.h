@@ -126,7 +126,7 @@ typedef struct nha_chunk_desc {
   int32_t max_seqlen;           /* longest sequence (grid sizing of the state pass) */
   int32_t window_left_all;      /* used when window_left == NULL */
   int32_t shift_all;            /* used when shift == NULL */
-  int32_t seg_chunks;           /* chunks per state-pass segment; 0 = library default */
+  int32_t seg_chunks;           /* unused (kept so the struct layout stays put); set 0 */
   float scale;
 } nha_chunk_desc;
 
@@ -159,10 +159,10 @@ int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
 /* State pass for callers that cannot allocate device memory (a plugin host that passes only
    input and output buffers, a serving loop that forbids allocation after start-up).  Same
    inputs, outputs and results as nha_chunk_state_pass, but desc->workspace is ignored: the
-   segment scratch comes from a fixed array inside the library's device image
+   per-chunk scratch comes from a fixed array inside the library's device image
    (nha_chunk_state_pass_static_max_bytes() bytes, 16 MiB, held on every GPU that loads the
    library until the process exits).  The call itself allocates nothing.  A problem whose
-   segment scratch (N*H*segments*(2*(K*M+M*V)+M) floats; raise desc->seg_chunks to shrink it)
+   scratch (nha_chunk_count_bound(Ttot, N)*H*(K*M+M*V+M) floats, = nha_chunk_fwd_workspace_bytes)
    exceeds the array is refused with NHA_ERR_STATIC_SCRATCH and nothing is launched.  The first
    call on each device looks up the array's device address (cudaGetSymbolAddress, with that
    device current); make that first call before any stream capture begins.  All calls on a
