@@ -5,14 +5,20 @@
 // HQ == H) or 64 tokens x 2 heads of the group (R = 128), and the CTA walks the heads of the group
 // reusing the chunk's k', v', gates and chunk-start states.
 //
-// Per tile:   A  = q k'^T,  QH = q Hk                       (TMEM)
-//             X  = tril(A) (s' .* b)                         ok = scale (exp(G) .* QH + a .* X)
-//             S  = q_swa k_swa^T per 64-key window tile       two sweeps: statistics, probabilities
-//             O  = (p .* exp(G)) Hv + tril((p .* a)(s' .* b)^T) v' + sum_tiles P v_win
-// a = exp(G - R), b = exp(R - G) with ONE reference R[m] = Gend[m] / 2 per chunk and slot.  That keeps
-// every factor inside exp(+-70) as long as a chunk decays by less than 140 nats per slot; a chunk
-// beyond that is left untouched and flagged, and the general kernel (16-row block references,
-// nha_chunk_fwd.cu) computes it instead, so the result never depends on the bound.
+// Per tile:   A  = q k'^T,  QH = q Hk,  S = q_swa k_swa^T (newest window step)           round 1
+//             X  = tril(A) (s' .* b)                                                      round 2
+//             ok = scale a .* (e^R .* QH + X);   window maxima step by step (older steps: load, S, max)
+//             O  = (p~ a e^R) Hv,  Bv = (p~ a)(s' .* b)^T                                  round 3
+//             O += tril(Bv) v' + P~ v_win (newest step, its S still in TMEM)              round 4
+//             older window steps: load, S, P~, O += P~ v_win
+// a = exp(G - R), b = exp(R - G) with ONE reference R[m] = Gend[m] / 2 per chunk and slot, kept as a
+// shared fp32 table so the row threads spend no exponentials on the decay.  That keeps every factor
+// inside exp(+-70) as long as a chunk decays by less than 140 nats per slot; a chunk beyond that is left
+// untouched and flagged, and the general kernel (16-row block references, nha_chunk_fwd.cu) computes it
+// instead, so the result never depends on the bound.  Probabilities are formed unnormalised against the
+// joint row maximum (p~ = exp(x - max)), accumulated in one TMEM accumulator and divided by the row sum
+// at the end, so every logit is exponentiated once.  A window step is two 64-key tiles for D = 64 and
+// one for D = 128; a window of up to one step (W <= 64 at D = 64) needs no loop at all.
 //
 // Replaces chunk_nha_fused_o_kernel (nha_fla/ops/nha/chunk_fused.py:117-283) and, for chunk_nha, the
 // flash-attn varlen forward + fla chunk_gsa forward + log-sum-exp merge (nha_fla/ops/nha/chunk.py:423-470).
@@ -29,31 +35,41 @@ constexpr float kUmmaDecayLimit = 140.0f;
 template <int D, int R>
 struct UmmaLayout {
   static constexpr int KT = D / 64;
-  static constexpr int kATile = R * 128;             // one 64-wide k tile of an R-row A operand
-  static constexpr int tQ = 0;                        // q_gsa; later p .* a
+  static constexpr int TP = D == 64 ? 2 : 1;          // 64-key tiles per window step
+  static constexpr int kATile = R * 128;              // one 64-wide k tile of an R-row A operand
+  static constexpr int kWTile = TP * 8192;            // one 64-wide k tile of a window-step operand (64 TP rows)
+  static constexpr bool kAlias = R == 64;             // one head per CTA: k' and Hk are dead after round 1
+  static constexpr bool kPOverW = R <= D;             // P~ fits over the window keys it was computed from
+  static constexpr int tQ = 0;                        // q_gsa; later p~ .* a
   static constexpr int tQS = tQ + KT * kATile;        // q_swa
   static constexpr int tK = tQS + KT * kATile;        // k'
   static constexpr int tV = tK + KT * 8192;           // v'
   static constexpr int tHk = tV + KT * 8192;          // Hk [D][64]
   static constexpr int tHv = tHk + D * 128;           // Hv [64][D]
   static constexpr int tSB = tHv + KT * 8192;         // s' .* b [64][64]
-  static constexpr int tW = tSB + 8192;               // window keys [64][D]
-  static constexpr int tWV = tW + KT * 8192;          // window values [64][D]
-  static constexpr int tAB = tWV + KT * 8192;         // tril(A) / tril(Bv) / P   [R][64]
-  static constexpr int tPG = tAB + kATile;            // p .* exp(G)             [R][64]
-  static constexpr int oG = tPG + kATile;             // fp32 [64][65] cumulative gates
-  static constexpr int oR = oG + 64 * 65 * 4;         // fp32 [64] reference exponent
+  static constexpr int tW = tSB + 8192;               // window keys of one step [64 TP][D]
+  static constexpr int tWV = tW + KT * kWTile;        // window values of one step [64 TP][D]
+  static constexpr int end0 = tWV + KT * kWTile;
+  static constexpr int tP = kPOverW ? tW : end0;      // P~ [R][64 TP]
+  static constexpr int end1 = kPOverW ? end0 : end0 + TP * kATile;
+  static constexpr int tAB = kAlias ? tHk : end1;     // tril(A) / tril(Bv)  [R][64]
+  static constexpr int tPG = kAlias ? tK : end1 + kATile;   // p~ .* a .* e^R   [R][64]
+  static constexpr int end2 = kAlias ? end1 : end1 + 2 * kATile;
+  static constexpr int oA = end2;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
+  static constexpr int oR = oA + 64 * 65 * 4;         // fp32 [64] exp(R)
   static constexpr int oBar = oR + 256;               // mbarrier + TMEM slot
   static constexpr int total = oBar + 64 + 1024;      // + slack for the 1024-byte alignment of the base
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
+  // O reuses QH's columns at D = 64 (QH has been read by then)
   static constexpr int cA = 0, cQH = 64, cS = 128, cO = D == 64 ? 64 : 256;
+  static_assert(total <= 227 * 1024, "shared memory of the output pass");
 };
 
 template <int D, int R>
 __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
                                                                   int* __restrict__ err) {
   typedef UmmaLayout<D, R> L;
-  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  constexpr int KT = L::KT, TH = R / 64, M = 64, TP = L::TP, WK = 64 * TP;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
@@ -68,18 +84,40 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* Gs = (float*)(sm + L::oG);
-  float* Rs = (float*)(sm + L::oR);
+  float* As = (float*)(sm + L::oA);
+  float* ER = (float*)(sm + L::oR);
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
 
-  // ---- kv-head tiles of the chunk and the first tile's queries go in flight ------------------------
+  // window steps, newest first: step p covers the keys [kbase(p), kbase(p) + WK)
+  const int jt_hi = ci;
+  const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
+  const int nsteps = (jt_hi - jt_lo + TP) / TP;
+#define NHA_KBASE(p_) ((jt_hi + 1 - TP * ((p_) + 1)) * kChunk)
+  const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
+  const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
+
+  // ---- everything the first head tile needs goes in flight at once -------------------------------------
   const int lo = 0, hi = len - shift;              // valid source rows of the shifted inputs
   load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
   load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
   load_sw<64>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
   load_sw<D>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
-  cp_commit();
+#define NHA_LOAD_HEAD_TILE(ht_)                                                                                       \
+  do {                                                                                                                \
+    const int hq0_ = h * NG + (ht_) * TH;                                                                             \
+    _Pragma("unroll") for (int t2 = 0; t2 < TH; ++t2) {                                                               \
+      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,    \
+                 c0, 0, len, 64, 64 * t2, tid);                                                                       \
+      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
+                 c0, 0, len, 64, 64 * t2, tid);                                                                       \
+    }                                                                                                                 \
+    /* keys of the OLDEST step (the first one the maxima sweep needs); with a single step also its values */         \
+    load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(nsteps - 1), 0, len, WK, 0, tid);                \
+    if (nsteps == 1) load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);       \
+    cp_commit();                                                                                                      \
+  } while (0)
+  NHA_LOAD_HEAD_TILE(0);
   // gates and write weights through registers: G needs an fp32 scan, s' is folded into s' .* b
   uint4 sreg[4];
 #pragma unroll
@@ -94,7 +132,7 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
       sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+    for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
@@ -104,27 +142,37 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     float run = 0.f;
 #pragma unroll 8
     for (int r = 32 * half; r < 32 * half + 32; ++r) {
-      run += Gs[r * 65 + m];
-      Gs[r * 65 + m] = run;
+      run += As[r * 65 + m];
+      As[r * 65 + m] = run;
     }
     __syncthreads();
     if (half == 1) {
-      const float add = Gs[31 * 65 + m];
+      const float add = As[31 * 65 + m];
 #pragma unroll 8
-      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+      for (int r = 32; r < 64; ++r) As[r * 65 + m] += add;
     }
     __syncthreads();
   }
-  const bool mine_unsafe = tid < 64 && fabsf(Gs[63 * 65 + tid]) > kUmmaDecayLimit;
+  const bool mine_unsafe = tid < 64 && fabsf(As[63 * 65 + tid]) > kUmmaDecayLimit;
   const int unsafe = __syncthreads_or(mine_unsafe ? 1 : 0);
   if (tid == 0) flags[(size_t)cg * H + h] = unsafe;
   if (unsafe) {
     cp_wait_all();
     return;
   }
-  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
-  __syncthreads();
-  // s' .* b into its swizzled tile ([64 i][64 m]: K-major for (p .* a) SB^T, MN-major for tril(A) SB)
+  // a = exp(G - R) replaces G in place, s' .* b = s' exp(R - G) goes into its swizzled tile ([64 i][64 m]:
+  // K-major for (p~ a) SB^T, MN-major for tril(A) SB); each thread converts the elements it also reads
+  float rref[8];
+  {
+    const int c8 = tid & 7;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) rref[e] = 0.5f * As[63 * 65 + 8 * c8 + e];
+  }
+  __syncthreads();                                    // every thread holds its references before the table changes
+  if (tid < 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ER[8 * tid + e] = __expf(rref[e]);
+  }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int i = tid + kUThreads * j;
@@ -132,7 +180,11 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     float sv[8], out[8];
     unpack8(sreg[j], sv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) out[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    for (int e = 0; e < 8; ++e) {
+      const float x = As[r * 65 + 8 * c8 + e] - rref[e];
+      As[r * 65 + 8 * c8 + e] = __expf(x);
+      out[e] = sv[e] * __expf(-x);
+    }
     *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(out);
   }
   if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
@@ -151,14 +203,10 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
   const int th = row >> 6;                          // head inside the tile
   const int pos = c0 + tk;
   const bool in_seq = pos < len;
-  const int jt_hi = ci;
-  const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
   const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aK = smem_u32(sm + L::tK);
   const uint32_t aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk), aHv = smem_u32(sm + L::tHv);
   const uint32_t aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW), aWV = smem_u32(sm + L::tWV);
-  const uint32_t aAB = smem_u32(sm + L::tAB), aPG = smem_u32(sm + L::tPG), aPA = aQ;
-  const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
-  const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
+  const uint32_t aAB = smem_u32(sm + L::tAB), aPG = smem_u32(sm + L::tPG), aPA = aQ, aP = smem_u32(sm + L::tP);
 
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
@@ -174,51 +222,89 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     __syncthreads();                                     \
     tc_fence_after();                                    \
   } while (0)
+// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+#define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
+  do {                                                                                           \
+    float tv_[32];                                                                               \
+    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
+      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
+      if (active) {                                                                              \
+        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
+          float o8[8];                                                                           \
+          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
+            const int i_ = 32 * part + 8 * c8 + e;                                               \
+            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
+          }                                                                                      \
+          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+        }                                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  } while (0)
+// S = q_swa (window keys of one step)^T
+#define NHA_ISSUE_S() mma_tile(tbase + L::cS, aQS, L::kATile, aW, L::kWTile, R, WK, D / 16, 0, false)
+// running maximum of the visible logits of the step whose keys start at kb_
+#define NHA_STEP_MAX(kb_)                                                                        \
+  do {                                                                                           \
+    float sv_[32];                                                                               \
+    _Pragma("unroll") for (int part = 0; part < 2 * TP; ++part) {                                \
+      tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
+      _Pragma("unroll") for (int e = 0; e < 32; ++e) {                                           \
+        const int key = (kb_) + 32 * part + e;                                                   \
+        const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && key >= 0;                  \
+        if (vis) ms = fmaxf(ms, sv_[e] * d.scale);                                               \
+      }                                                                                          \
+    }                                                                                            \
+  } while (0)
+// P~ = exp(scale S - ms) cw of the step whose keys start at kb_, into the swizzled tile; row sum into ls
+#define NHA_STEP_PROB(kb_)                                                                       \
+  do {                                                                                           \
+    float sv_[32];                                                                               \
+    _Pragma("unroll") for (int part = 0; part < 2 * TP; ++part) {                                \
+      tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
+      if (active) {                                                                              \
+        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
+          float o8[8];                                                                           \
+          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
+            const int key = (kb_) + 32 * part + 8 * c8 + e;                                      \
+            const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && key >= 0 && in_seq;    \
+            const float pe = vis ? __expf(sv_[8 * c8 + e] * d.scale - ms) : 0.f;                 \
+            ls += pe;                                                                            \
+            o8[e] = pe * cw;                                                                     \
+          }                                                                                      \
+          *reinterpret_cast<uint4*>(sm + L::tP + (part >> 1) * L::kATile +                       \
+                                    sw_off(row, 4 * (part & 1) + c8)) = pack8(o8);               \
+        }                                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  } while (0)
+// O += P~ (window values of one step)
+#define NHA_ISSUE_PV()                                                                           \
+  do {                                                                                           \
+    _Pragma("unroll") for (int ct = 0; ct < KT; ++ct)                                            \
+      mma_tile(tbase + L::cO + 64 * ct, aP, L::kATile, aWV + ct * L::kWTile, 0, R, 64, 4 * TP, 1, true); \
+  } while (0)
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
     const int hq0 = h * NG + ht * TH;
     const int hq = hq0 + th;
-    // ---- queries of this tile ------------------------------------------------------------------------
-#pragma unroll
-    for (int t2 = 0; t2 < TH; ++t2) {
-      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
-                 64, 64 * t2, tid);
-      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0,
-                 len, 64, 64 * t2, tid);
-    }
-    cp_commit();
+    if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
     cp_wait_all();
     NHA_SMEM_TO_MMA();
-    // ---- A = q k'^T, QH = q Hk --------------------------------------------------------------------------
+    // ---- round 1: A = q k'^T, QH = q Hk, S of the oldest window step --------------------------------------
     if (tid == 0) {
       mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
       mma_tile(tbase + L::cQH, aQ, L::kATile, aHk, 0, R, 64, D / 16, 1, false);
+      NHA_ISSUE_S();
     }
     NHA_MMA_WAIT();
-    // ---- tril(A) -> bf16 A operand ------------------------------------------------------------------------
-    {
-      float av[32];
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cA + 32 * part, av);
-        if (active) {
-#pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int i = 32 * part + 8 * c8 + e;
-              o8[e] = i <= tk ? av[8 * c8 + e] : 0.f;
-            }
-            *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
-          }
-        }
-      }
-    }
+    NHA_TRIL_TO_SMEM(L::cA, L::tAB);
     NHA_SMEM_TO_MMA();
-    if (tid == 0) mma_tile(tbase + L::cA, aAB, L::kATile, aSB, 0, R, 64, 4, 1, false);   // X = tril(A) SB
+    // ---- round 2: X = tril(A) SB; the window maxima are taken while it runs ---------------------------------
+    if (tid == 0) mma_tile(tbase + L::cA, aAB, L::kATile, aSB, 0, R, 64, 4, 1, false);
+    float ms = -INFINITY;
+    NHA_STEP_MAX(NHA_KBASE(nsteps - 1));
     NHA_MMA_WAIT();
-    // ---- slot logits ok = scale (exp(G) .* QH + a .* X), kept in registers --------------------------------
+    // ---- slot logits ok = scale a .* (e^R .* QH + X), kept in registers ----------------------------------------
     float ok[64];
     float mg = -INFINITY;
     {
@@ -230,8 +316,7 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int m = 32 * part + e;
-          const float gl = Gs[tk * 65 + m];
-          const float v = d.scale * (__expf(gl) * qh[e] + __expf(gl - Rs[m]) * xv[e]);
+          const float v = d.scale * As[tk * 65 + m] * (ER[m] * qh[e] + xv[e]);
           ok[m] = v;
           mg = fmaxf(mg, v);
         }
@@ -239,57 +324,29 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     }
     float lg = 0.f;
 #pragma unroll
-    for (int m = 0; m < 64; ++m) lg += __expf(ok[m] - mg);
-    // ---- window sweep 1: statistics --------------------------------------------------------------------------
-    float ms = -INFINITY, ls = 0.f;
-    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+    for (int m = 0; m < 64; ++m) {
+      ok[m] = __expf(ok[m] - mg);                     // from here on ok holds exp(ok - mg)
+      lg += ok[m];
+    }
+    // ---- maxima of the newer window steps (the newest one last: its S stays in TMEM) -----------------------------
+    for (int p = nsteps - 2; p >= 0 && !failed; --p) {
+      tc_fence_before();
       __syncthreads();
-      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+      if (p == 0) load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);
       cp_commit();
       cp_wait_all();
       NHA_SMEM_TO_MMA();
-      if (tid == 0) mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);
+      if (tid == 0) NHA_ISSUE_S();
       NHA_MMA_WAIT();
-      float sv[32];
-      float tmax = -INFINITY;
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cS + 32 * part, sv);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = jt * kChunk + 32 * part + e;
-          const bool vis = key <= pos && (wl < 0 || key >= pos - wl);
-          if (vis) tmax = fmaxf(tmax, sv[e] * d.scale);
-        }
-      }
-      const float mnew = fmaxf(ms, tmax);
-      float part_sum = 0.f;
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cS + 32 * part, sv);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = jt * kChunk + 32 * part + e;
-          const bool vis = key <= pos && (wl < 0 || key >= pos - wl);
-          if (vis) part_sum += __expf(sv[e] * d.scale - mnew);
-        }
-      }
-      if (mnew > -INFINITY) {
-        ls = ls * __expf(ms - mnew) + part_sum;
-        ms = mnew;
-      }
-      tc_fence_before();
+      NHA_STEP_MAX(NHA_KBASE(p));
     }
-    const float lse_g = mg + __logf(lg);
-    const float lse_s = ms + __logf(ls);
-    const float mx = fmaxf(lse_g, lse_s);
-    const float Lj = mx + __logf(__expf(lse_g - mx) + __expf(lse_s - mx));
-    if (active && in_seq) {
-      d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = lse_g;
-      d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = lse_s;
-    }
-    // ---- slot probabilities: p .* exp(G) and p .* a as bf16 A operands -------------------------------------------
-    __syncthreads();                                  // every thread is past its last read of tQ's MMAs
+    // ---- joint maximum; unnormalised slot probabilities as bf16 A operands -----------------------------------------
+    const float mx = fmaxf(mg, ms);
+    const float cgs = __expf(mg - mx);               // slot entries:   p~ = exp(ok - mg) cgs
+    const float cw = __expf(ms - mx);                // window entries: p~ = exp(s  - ms) cw
+    tc_fence_before();
+    __syncthreads();                                  // every thread is past its reads of QH / X and of tQ's products
     if (active) {
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
@@ -297,95 +354,66 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int m = 8 * c8 + e;
-          const float p = in_seq ? __expf(ok[m] - Lj) : 0.f;
-          const float gl = Gs[tk * 65 + m];
-          pg8[e] = p * __expf(gl);
-          pa8[e] = p * __expf(gl - Rs[m]);
+          const float pa = in_seq ? ok[m] * cgs * As[tk * 65 + m] : 0.f;
+          pa8[e] = pa;
+          pg8[e] = pa * ER[m];
         }
         *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, c8)) = pack8(pg8);
         *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, c8)) = pack8(pa8);
       }
     }
     NHA_SMEM_TO_MMA();
+    // ---- round 3: O = (p~ a e^R) Hv, Bv = (p~ a) SB^T; the newest step's P~ is formed while it runs ---------------
     if (tid == 0) {
 #pragma unroll
-      for (int ct = 0; ct < KT; ++ct)                 // O = (p exp G) Hv, 64 output columns at a time
+      for (int ct = 0; ct < KT; ++ct)
         mma_tile(tbase + L::cO + 64 * ct, aPG, L::kATile, aHv + ct * 8192, 0, R, 64, 4, 1, false);
-      mma_tile(tbase + L::cA, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);   // Bv = (p a) SB^T
+      mma_tile(tbase + L::cA, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);
     }
+    float ls = 0.f;
+    NHA_STEP_PROB(NHA_KBASE(0));
     NHA_MMA_WAIT();
-    {
-      float bv[32];
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cA + 32 * part, bv);
-        if (active) {
-#pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            float o8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int i = 32 * part + 8 * c8 + e;
-              o8[e] = i <= tk ? bv[8 * c8 + e] : 0.f;
-            }
-            *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
-          }
-        }
-      }
-    }
+    NHA_TRIL_TO_SMEM(L::cA, L::tAB);
     NHA_SMEM_TO_MMA();
+    // ---- round 4: O += tril(Bv) v' + P~ v_win (newest step) -------------------------------------------------------------
     if (tid == 0) {
 #pragma unroll
-      for (int ct = 0; ct < KT; ++ct)                 // O += tril(Bv) v'
+      for (int ct = 0; ct < KT; ++ct)
         mma_tile(tbase + L::cO + 64 * ct, aAB, L::kATile, aV + ct * 8192, 0, R, 64, 4, 1, true);
+      NHA_ISSUE_PV();
     }
     NHA_MMA_WAIT();
-    // ---- window sweep 2: probabilities and readout ------------------------------------------------------------------
-    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+    // ---- older window steps ------------------------------------------------------------------------------------------------
+    for (int p = 1; p < nsteps && !failed; ++p) {
       tc_fence_before();
       __syncthreads();
-      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
-      load_sw<D>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+      load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
       cp_commit();
       cp_wait_all();
       NHA_SMEM_TO_MMA();
-      if (tid == 0) mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);
+      if (tid == 0) NHA_ISSUE_S();
       NHA_MMA_WAIT();
-      {
-        float sv[32];
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          tmem_ld32(tlane + L::cS + 32 * part, sv);
-          if (active) {
-#pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-              float o8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const int key = jt * kChunk + 32 * part + 8 * c8 + e;
-                const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && in_seq;
-                o8[e] = vis ? __expf(sv[8 * c8 + e] * d.scale - Lj) : 0.f;
-              }
-              *reinterpret_cast<uint4*>(sm + L::tAB + sw_off(row, 4 * part + c8)) = pack8(o8);
-            }
-          }
-        }
-      }
+      NHA_STEP_PROB(NHA_KBASE(p));
       NHA_SMEM_TO_MMA();
-      if (tid == 0) {
-#pragma unroll
-        for (int ct = 0; ct < KT; ++ct)
-          mma_tile(tbase + L::cO + 64 * ct, aAB, L::kATile, aWV + ct * 8192, 0, R, 64, 4, 1, true);
-      }
+      if (tid == 0) NHA_ISSUE_PV();
       NHA_MMA_WAIT();
     }
-    // ---- output row ----------------------------------------------------------------------------------------------------------
+    // ---- normalise and store -----------------------------------------------------------------------------------------------
+    const float lsum = lg * cgs + ls * cw;
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    if (active && in_seq) {
+      d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg);
+      d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = ms + __logf(ls);
+    }
     {
       float ov[32];
 #pragma unroll
       for (int part = 0; part < D / 32; ++part) {
         tmem_ld32(tlane + L::cO + 32 * part, ov);
         if (active && in_seq) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] *= inv;
           bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D + 32 * part;
 #pragma unroll
           for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
@@ -398,7 +426,15 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
   }
 #undef NHA_MMA_WAIT
 #undef NHA_SMEM_TO_MMA
+#undef NHA_TRIL_TO_SMEM
+#undef NHA_ISSUE_S
+#undef NHA_STEP_MAX
+#undef NHA_STEP_PROB
+#undef NHA_ISSUE_PV
+#undef NHA_LOAD_HEAD_TILE
+#undef NHA_KBASE
   if (failed && tid == 0) atomicExch(err, 1);
+  cp_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
