@@ -1,7 +1,9 @@
 // Output pass of the chunked NHA forward on the sm_100a tensor-core path: tcgen05.mma with operands in
-// 128-byte-swizzled shared memory, accumulators in tensor memory (TMEM), one thread per query row
-// for the softmax (tcgen05.ld hands every thread a whole row, so row maxima and sums need no
-// shuffles).  One CTA per (chunk, kv head); an MMA tile is 64 tokens x 1 head (R = 64, for
+// 128-byte-swizzled shared memory, accumulators in tensor memory (TMEM), two threads per query row
+// for the softmax: tcgen05.ld hands a thread 32 columns of its row, the two warps that share a TMEM
+// lane quarter (warp w and w + 4) take alternate halves of the columns and swap row maxima and sums
+// through shared memory.  Eight warps per CTA keep the element-wise phases, which are bound by
+// instruction issue, from stalling on their own dependencies.  One CTA per (chunk, kv head); an MMA tile is 64 tokens x 1 head (R = 64, for
 // HQ == H) or 64 tokens x 2 heads of the group (R = 128), and the CTA walks the heads of the group
 // reusing the chunk's k', v', gates and chunk-start states.
 //
@@ -29,7 +31,7 @@ namespace nha {
 
 using namespace umma;
 
-constexpr int kUThreads = 128;
+constexpr int kUThreads = 256;
 constexpr float kUmmaDecayLimit = 140.0f;
 
 template <int D, int R>
@@ -57,7 +59,8 @@ struct UmmaLayout {
   static constexpr int end2 = kAlias ? end1 : end1 + 2 * kATile;
   static constexpr int oA = end2;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
   static constexpr int oR = oA + 64 * 65 * 4;         // fp32 [64] exp(R)
-  static constexpr int oBar = oR + 256;               // mbarrier + TMEM slot
+  static constexpr int oX = oR + 256;                 // fp32 [4][2][128] row statistics swapped between the column halves
+  static constexpr int oBar = oX + 4096;              // mbarrier + TMEM slot
   static constexpr int total = oBar + 64 + 1024;      // + slack for the 1024-byte alignment of the base
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
   // O reuses QH's columns at D = 64 (QH has been read by then)
@@ -66,7 +69,7 @@ struct UmmaLayout {
 };
 
 template <int D, int R>
-__global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
+__global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
                                                                   int* __restrict__ err) {
   typedef UmmaLayout<D, R> L;
   constexpr int KT = L::KT, TH = R / 64, M = 64, TP = L::TP, WK = 64 * TP;
@@ -97,59 +100,71 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
   const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
   const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
 
-  // ---- everything the first head tile needs goes in flight at once -------------------------------------
+  // gates and write weights through registers (G needs an fp32 scan, s' is folded into s' .* b): their loads
+  // go out first, the tile copies follow, and the registers are consumed after those have been issued
   const int lo = 0, hi = len - shift;              // valid source rows of the shifted inputs
-  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<64>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
-  load_sw<D>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
+  constexpr int kGS = 512 / kUThreads;              // 16-byte pieces of the [64][64] gate / write-weight tiles per thread
+  uint4 sreg[kGS], greg[kGS];
+#pragma unroll
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + kUThreads * j;
+    const int r = i >> 3, c8 = i & 7;
+    const int src = c0 + r - shift;
+    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    greg[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= lo && src < hi) {
+      greg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+    }
+  }
+  // ---- everything the first head tile needs goes in flight at once -------------------------------------
+  load_sw<D, kUThreads>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D, kUThreads>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<64, kUThreads>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D, kUThreads>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
 #define NHA_LOAD_HEAD_TILE(ht_)                                                                                       \
   do {                                                                                                                \
     const int hq0_ = h * NG + (ht_) * TH;                                                                             \
     _Pragma("unroll") for (int t2 = 0; t2 < TH; ++t2) {                                                               \
-      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,    \
+      load_sw<D, kUThreads>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,    \
                  c0, 0, len, 64, 64 * t2, tid);                                                                       \
-      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
+      load_sw<D, kUThreads>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
                  c0, 0, len, 64, 64 * t2, tid);                                                                       \
     }                                                                                                                 \
     /* keys of the OLDEST step (the first one the maxima sweep needs); with a single step also its values */         \
-    load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(nsteps - 1), 0, len, WK, 0, tid);                \
-    if (nsteps == 1) load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);       \
+    load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(nsteps - 1), 0, len, WK, 0, tid);                \
+    if (nsteps == 1) load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);       \
     cp_commit();                                                                                                      \
   } while (0)
   NHA_LOAD_HEAD_TILE(0);
-  // gates and write weights through registers: G needs an fp32 scan, s' is folded into s' .* b
-  uint4 sreg[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < kGS; ++j) {
     const int i = tid + kUThreads * j;
     const int r = i >> 3, c8 = i & 7;
-    const int src = c0 + r - shift;
-    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= lo && src < hi) {
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
-      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
-    }
+    float gv[8];
+    unpack8(greg[j], gv);
 #pragma unroll
     for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
-  // inclusive scan along the rows: two threads per column (rows 0..31 and 32..63), then a fix-up
+  // inclusive scan along the rows: four threads per column (16 rows each), then the totals of the earlier
+  // quarters are added
   {
-    const int m = tid & 63, half = tid >> 6;
+    const int m = tid & 63, seg = tid >> 6;
     float run = 0.f;
-#pragma unroll 8
-    for (int r = 32 * half; r < 32 * half + 32; ++r) {
+#pragma unroll
+    for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
       run += As[r * 65 + m];
       As[r * 65 + m] = run;
     }
     __syncthreads();
-    if (half == 1) {
-      const float add = As[31 * 65 + m];
-#pragma unroll 8
-      for (int r = 32; r < 64; ++r) As[r * 65 + m] += add;
+    float add = 0.f;
+    for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * 65 + m];
+    __syncthreads();                                  // every total is read before any of them changes
+    if (seg > 0) {
+#pragma unroll
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * 65 + m] += add;
     }
     __syncthreads();
   }
@@ -174,7 +189,7 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     for (int e = 0; e < 8; ++e) ER[8 * tid + e] = __expf(rref[e]);
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < kGS; ++j) {
     const int i = tid + kUThreads * j;
     const int r = i >> 3, c8 = i & 7;
     float sv[8], out[8];
@@ -192,17 +207,25 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  const int quarter = warp & 3, half = warp >> 2;   // TMEM lane quarter of this warp; column half it works on
+  const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
   uint32_t phase = 0;
   bool failed = false;
 
-  // row of this thread inside the tile
+  // row of this thread inside the tile (two threads, one per column half, share a row)
   const bool active = R == 128 ? true : lane < 16;
-  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
   const int tk = row & 63;                          // token inside the chunk
   const int th = row >> 6;                          // head inside the tile
   const int pos = c0 + tk;
   const bool in_seq = pos < len;
+  float* xch = (float*)(sm + L::oX);                // [4 exchange points][2 halves][128 rows]
+  // visible keys of this row: klo <= key <= pos, tested as (unsigned)(key - klo) <= kspan; a row past the
+  // sequence end sees nothing
+  constexpr float kLog2e = 1.4426950408889634f;
+  const int klo = in_seq ? (wl < 0 ? 0 : max(0, pos - wl)) : (1 << 30);
+  const unsigned kspan = in_seq ? (unsigned)(pos - klo) : 0u;
+  const float sc2 = d.scale * kLog2e;
   const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aK = smem_u32(sm + L::tK);
   const uint32_t aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk), aHv = smem_u32(sm + L::tHv);
   const uint32_t aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW), aWV = smem_u32(sm + L::tWV);
@@ -222,58 +245,61 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     __syncthreads();                                     \
     tc_fence_after();                                    \
   } while (0)
-// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+// this thread's half of tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 A-operand tile
 #define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
   do {                                                                                           \
     float tv_[32];                                                                               \
-    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
-      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
-      if (active) {                                                                              \
-        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
-          float o8[8];                                                                           \
-          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
-            const int i_ = 32 * part + 8 * c8 + e;                                               \
-            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
-          }                                                                                      \
-          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+    tmem_ld32(tlane + (col0) + 32 * half, tv_);                                                  \
+    if (active) {                                                                                \
+      _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                         \
+        float o8[8];                                                                             \
+        _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                          \
+          const int i_ = 32 * half + 8 * c8 + e;                                                 \
+          o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                              \
         }                                                                                        \
+        *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * half + c8)) = pack8(o8);      \
       }                                                                                          \
     }                                                                                            \
   } while (0)
 // S = q_swa (window keys of one step)^T
 #define NHA_ISSUE_S() mma_tile(tbase + L::cS, aQS, L::kATile, aW, L::kWTile, R, WK, D / 16, 0, false)
-// running maximum of the visible logits of the step whose keys start at kb_
+// this thread's 32 TP keys of a window step: keys kb_ + 32 TP half + [0, 32 TP)
 #define NHA_STEP_MAX(kb_)                                                                        \
   do {                                                                                           \
     float sv_[32];                                                                               \
-    _Pragma("unroll") for (int part = 0; part < 2 * TP; ++part) {                                \
+    _Pragma("unroll") for (int pp = 0; pp < TP; ++pp) {                                          \
+      const int part = TP * half + pp;                                                           \
       tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
-      _Pragma("unroll") for (int e = 0; e < 32; ++e) {                                           \
-        const int key = (kb_) + 32 * part + e;                                                   \
-        const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && key >= 0;                  \
-        if (vis) ms = fmaxf(ms, sv_[e] * d.scale);                                               \
-      }                                                                                          \
+      const int off_ = (kb_) + 32 * part - klo;                                                  \
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};                                \
+      _Pragma("unroll") for (int e = 0; e < 32; ++e)                                             \
+        m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off_ + e) <= kspan ? sv_[e] : -INFINITY);        \
+      ms = fmaxf(ms, d.scale * fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));                 \
     }                                                                                            \
   } while (0)
-// P~ = exp(scale S - ms) cw of the step whose keys start at kb_, into the swizzled tile; row sum into ls
+// P~ = exp(scale S - ms) cw of this thread's keys of a step, into the swizzled tile; row sum into ls
 #define NHA_STEP_PROB(kb_)                                                                       \
   do {                                                                                           \
     float sv_[32];                                                                               \
-    _Pragma("unroll") for (int part = 0; part < 2 * TP; ++part) {                                \
+    const float nms_ = -ms * kLog2e;                                                             \
+    _Pragma("unroll") for (int pp = 0; pp < TP; ++pp) {                                          \
+      const int part = TP * half + pp;                                                           \
       tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
+      const int off_ = (kb_) + 32 * part - klo;                                                  \
       if (active) {                                                                              \
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};                                                      \
         _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
           float o8[8];                                                                           \
           _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
-            const int key = (kb_) + 32 * part + 8 * c8 + e;                                      \
-            const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && key >= 0 && in_seq;    \
-            const float pe = vis ? __expf(sv_[8 * c8 + e] * d.scale - ms) : 0.f;                 \
-            ls += pe;                                                                            \
+            const float pe = (unsigned)(off_ + 8 * c8 + e) <= kspan                              \
+                                 ? exp2f(fmaf(sv_[8 * c8 + e], sc2, nms_)) : 0.f;                \
+            l4[e & 3] += pe;                                                                     \
             o8[e] = pe * cw;                                                                     \
           }                                                                                      \
           *reinterpret_cast<uint4*>(sm + L::tP + (part >> 1) * L::kATile +                       \
                                     sw_off(row, 4 * (part & 1) + c8)) = pack8(o8);               \
         }                                                                                        \
+        ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);                                                 \
       }                                                                                          \
     }                                                                                            \
   } while (0)
@@ -282,6 +308,14 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
   do {                                                                                           \
     _Pragma("unroll") for (int ct = 0; ct < KT; ++ct)                                            \
       mma_tile(tbase + L::cO + 64 * ct, aP, L::kATile, aWV + ct * L::kWTile, 0, R, 64, 4 * TP, 1, true); \
+  } while (0)
+// swap a row statistic with the thread that owns the other column half (slot_: exchange point 0..3);
+// the barrier inside is reached by every thread of the CTA
+#define NHA_SWAP(slot_, mine_, other_)                                                           \
+  do {                                                                                           \
+    xch[((slot_) * 2 + half) * 128 + row] = (mine_);                                             \
+    __syncthreads();                                                                             \
+    (other_) = xch[((slot_) * 2 + (half ^ 1)) * 128 + row];                                      \
   } while (0)
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
@@ -304,36 +338,46 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     float ms = -INFINITY;
     NHA_STEP_MAX(NHA_KBASE(nsteps - 1));
     NHA_MMA_WAIT();
-    // ---- slot logits ok = scale a .* (e^R .* QH + X), kept in registers ----------------------------------------
-    float ok[64];
+    // ---- this thread's 32 slot logits ok = scale a .* (e^R .* QH + X), kept in registers --------------------------
+    float ok[32];
     float mg = -INFINITY;
     {
-      float qh[32], xv[32];
+      float qh[32];
+      tmem_ld32(tlane + L::cQH + 32 * half, qh);
+      tmem_ld32(tlane + L::cA + 32 * half, ok);
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cQH + 32 * part, qh);
-        tmem_ld32(tlane + L::cA + 32 * part, xv);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int m = 32 * part + e;
-          const float v = d.scale * As[tk * 65 + m] * (ER[m] * qh[e] + xv[e]);
-          ok[m] = v;
-          mg = fmaxf(mg, v);
-        }
+      for (int e = 0; e < 32; ++e) {
+        const int m = 32 * half + e;
+        const float v = d.scale * As[tk * 65 + m] * (ER[m] * qh[e] + ok[e]);
+        ok[e] = v;
+        m4[e & 3] = fmaxf(m4[e & 3], v);
       }
+      mg = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    }
+    {
+      float other;
+      NHA_SWAP(0, mg, other);
+      mg = fmaxf(mg, other);
     }
     float lg = 0.f;
+    {
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int m = 0; m < 64; ++m) {
-      ok[m] = __expf(ok[m] - mg);                     // from here on ok holds exp(ok - mg)
-      lg += ok[m];
+      const float nmg = -mg * kLog2e;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        ok[e] = exp2f(fmaf(ok[e], kLog2e, nmg));      // from here on ok holds exp(ok - mg)
+        l4[e & 3] += ok[e];
+      }
+      lg = (l4[0] + l4[1]) + (l4[2] + l4[3]);
     }
     // ---- maxima of the newer window steps (the newest one last: its S stays in TMEM) -----------------------------
     for (int p = nsteps - 2; p >= 0 && !failed; --p) {
       tc_fence_before();
       __syncthreads();
-      load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
-      if (p == 0) load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);
+      load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+      if (p == 0) load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);
       cp_commit();
       cp_wait_all();
       NHA_SMEM_TO_MMA();
@@ -342,24 +386,28 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
       NHA_STEP_MAX(NHA_KBASE(p));
     }
     // ---- joint maximum; unnormalised slot probabilities as bf16 A operands -----------------------------------------
+    tc_fence_before();
+    {
+      float other;
+      NHA_SWAP(1, ms, other);                         // its barrier also puts every thread past its reads of QH / X
+      ms = fmaxf(ms, other);                          // and of the products that read tQ
+    }
     const float mx = fmaxf(mg, ms);
     const float cgs = __expf(mg - mx);               // slot entries:   p~ = exp(ok - mg) cgs
     const float cw = __expf(ms - mx);                // window entries: p~ = exp(s  - ms) cw
-    tc_fence_before();
-    __syncthreads();                                  // every thread is past its reads of QH / X and of tQ's products
     if (active) {
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
+      for (int c8 = 0; c8 < 4; ++c8) {
         float pg8[8], pa8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int m = 8 * c8 + e;
-          const float pa = in_seq ? ok[m] * cgs * As[tk * 65 + m] : 0.f;
+          const int m = 32 * half + 8 * c8 + e;
+          const float pa = in_seq ? ok[8 * c8 + e] * cgs * As[tk * 65 + m] : 0.f;
           pa8[e] = pa;
           pg8[e] = pa * ER[m];
         }
-        *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, c8)) = pack8(pg8);
-        *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, c8)) = pack8(pa8);
+        *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, 4 * half + c8)) = pack8(pg8);
+        *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, 4 * half + c8)) = pack8(pa8);
       }
     }
     NHA_SMEM_TO_MMA();
@@ -387,8 +435,8 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
     for (int p = 1; p < nsteps && !failed; ++p) {
       tc_fence_before();
       __syncthreads();
-      load_sw<D>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
-      load_sw<D>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+      load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+      load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
       cp_commit();
       cp_wait_all();
       NHA_SMEM_TO_MMA();
@@ -399,17 +447,28 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
       if (tid == 0) NHA_ISSUE_PV();
       NHA_MMA_WAIT();
     }
-    // ---- normalise and store -----------------------------------------------------------------------------------------------
+    // ---- row sums of both halves, normalise and store ----------------------------------------------------------------------
+    {
+      float other_g, other_s;
+      xch[(2 * 2 + half) * 128 + row] = lg;
+      xch[(3 * 2 + half) * 128 + row] = ls;
+      __syncthreads();
+      other_g = xch[(2 * 2 + (half ^ 1)) * 128 + row];
+      other_s = xch[(3 * 2 + (half ^ 1)) * 128 + row];
+      lg += other_g;
+      ls += other_s;
+    }
     const float lsum = lg * cgs + ls * cw;
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-    if (active && in_seq) {
+    if (active && in_seq && half == 0) {
       d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg);
       d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = ms + __logf(ls);
     }
     {
       float ov[32];
 #pragma unroll
-      for (int part = 0; part < D / 32; ++part) {
+      for (int pp = 0; pp < D / 64; ++pp) {
+        const int part = (D / 64) * half + pp;        // this thread's half of the output columns
         tmem_ld32(tlane + L::cO + 32 * part, ov);
         if (active && in_seq) {
 #pragma unroll
@@ -431,6 +490,7 @@ __global__ void __launch_bounds__(kUThreads) nha_fwd_umma_kernel(const nha_chunk
 #undef NHA_STEP_MAX
 #undef NHA_STEP_PROB
 #undef NHA_ISSUE_PV
+#undef NHA_SWAP
 #undef NHA_LOAD_HEAD_TILE
 #undef NHA_KBASE
   if (failed && tid == 0) atomicExch(err, 1);
@@ -451,10 +511,11 @@ static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream
 }
 
 // Runs the tensor-memory output pass when the shape has one (K == V in {64, 128}, M == 64, one or an
-// even number of query heads per kv head).  Returns NHA_ERR_UNSUPPORTED otherwise.
+// even number of query heads per kv head, positive scale).  Returns NHA_ERR_UNSUPPORTED otherwise.
 int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
   const int NG = d->HQ / d->H;
   if (d->K != d->V || d->M != 64) return NHA_ERR_UNSUPPORTED;
+  if (!(d->scale > 0.f)) return NHA_ERR_UNSUPPORTED;     // row maxima are taken before scaling
   if (d->K == 64 && NG == 1) return launch_umma<64, 64>(d, flags, err, cs);
   if (d->K == 64 && NG % 2 == 0) return launch_umma<64, 128>(d, flags, err, cs);
   if (d->K == 128 && NG == 1) return launch_umma<128, 64>(d, flags, err, cs);

@@ -132,7 +132,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* out) {
   for (int i = 0; i < 32; ++i) out[i] = __uint_as_float(r[i]);
 }
 
-// ---- asynchronous 16-byte copies into swizzled tiles (128-thread CTAs) -----------------------------
+// ---- asynchronous 16-byte copies into swizzled tiles (NT-thread CTAs) ------------------------------
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
   const int n = valid ? 16 : 0;
@@ -143,11 +143,11 @@ __device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_grou
 
 // Asynchronously copy `rows` x COLS bf16 (global rows row0.., stride gstride elements; rows outside
 // [lo, hi) become zeros) into COLS/64 swizzled tiles of `tile_bytes` each, starting at tile row dst_row0.
-template <int COLS>
+template <int COLS, int NT = 128>
 __device__ __forceinline__ void load_sw(unsigned char* tile, int tile_bytes, const bf16* base, int64_t gstride, int row0,
                                         int lo, int hi, int rows, int dst_row0, int tid) {
   constexpr int C8 = COLS / 8;
-  for (int i = tid; i < rows * C8; i += 128) {
+  for (int i = tid; i < rows * C8; i += NT) {
     const int r = i / C8, c = i % C8;
     const int gr = row0 + r;
     const bool ok = gr >= lo && gr < hi;
