@@ -28,7 +28,8 @@ namespace nha {
 
 using namespace umma;
 
-constexpr int kBUThreads = 128;
+constexpr int kBUThreads = 128;          // columns pass: one thread per row
+constexpr int kRowsThreads = 256;        // rows pass: two threads per row
 
 // ================================================================================================
 // rows pass
@@ -48,9 +49,10 @@ struct RowsLayout {
   static constexpr int tWVx = tSB + 8192;               // window values when they do not fit behind tQ
   static constexpr int bufA = tWVx + (R == 128 ? 0 : KT * 8192);   // tril(A) -> dza -> tril(E) -> dz_win
   static constexpr int bufB = bufA + kATile;            // tril(Av) -> dzg
-  static constexpr int oG = bufB + kATile;
-  static constexpr int oR = oG + 64 * 65 * 4;
-  static constexpr int oBar = oR + 256;
+  static constexpr int oA = bufB + kATile;              // fp32 [64][65]: cumulative gates, then a = exp(G - R)
+  static constexpr int oR = oA + 64 * 65 * 4;           // fp32 [64] exp(R)
+  static constexpr int oX = oR + 256;                   // fp32 [2 halves][128 rows]: partial <do, o> of the column halves
+  static constexpr int oBar = oX + 1024;
   static constexpr int total = oBar + 64 + 1024;
   static constexpr int tW = tQ;
   static constexpr int tWV = R == 128 ? tQ + KT * 8192 : tWVx;
@@ -63,13 +65,17 @@ struct RowsLayout {
   static constexpr int cS = D == 64 ? 0 : 128, cDP = D == 64 ? 64 : 192;
   // chunk-local state-gradient terms, read out before the window loop reuses the columns
   static constexpr int cLK = D == 64 ? 64 : 0, cLV = D == 64 ? 192 : 128;
+  static_assert(total <= 227 * 1024, "shared memory of the rows pass");
 };
 
+// Two threads per row: the warps w and w + 4 share a TMEM lane quarter and take alternate 32-column
+// halves of every 64-column accumulator.
 template <int D, int R>
-__global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha_chunk_desc d, const BwdWs w,
-                                                                       int* __restrict__ err) {
+__global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
+    nha_bwd_rows_umma_kernel(const nha_chunk_desc d, const BwdWs w, int* __restrict__ err) {
   typedef RowsLayout<D, R> L;
-  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  constexpr int KT = L::KT, TH = R / 64, M = 64, NT = kRowsThreads;
+  constexpr float kLog2e = 1.4426950408889634f;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
@@ -85,63 +91,101 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* Gs = (float*)(sm + L::oG);
-  float* Rs = (float*)(sm + L::oR);
+  float* As = (float*)(sm + L::oA);
+  float* ER = (float*)(sm + L::oR);
+  float* xch = (float*)(sm + L::oX);
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
 
+  // gates and write weights through registers; their loads go out first, the tile copies follow
   const int lo = 0, hi = len - shift;
-  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<64>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
-  load_sw<D>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
-  cp_commit();
-  uint4 sreg[4];
+  constexpr int kGS = 512 / NT;
+  uint4 sreg[kGS], greg[kGS];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int i = tid + kBUThreads * j;
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
     const int r = i >> 3, c8 = i & 7;
     const int src = c0 + r - shift;
-    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    greg[j] = make_uint4(0u, 0u, 0u, 0u);
     if (src >= lo && src < hi) {
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
+      greg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
       sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
     }
+  }
+  load_sw<D, NT>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D, NT>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<64, NT>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D, NT>(sm + L::tHv, 8192, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * D, D, 0, 0, M, M, 0, tid);
+#define NHA_LOAD_HEAD_TILE(ht_)                                                                                        \
+  do {                                                                                                                 \
+    const int hq0_ = h * NG + (ht_) * TH;                                                                              \
+    _Pragma("unroll") for (int t2 = 0; t2 < TH; ++t2) {                                                                \
+      load_sw<D, NT>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D,                  \
+                     (int64_t)HQ * D, c0, 0, len, 64, 64 * t2, tid);                                                   \
+      load_sw<D, NT>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0_ + t2) * D,                 \
+                     (int64_t)HQ * D, c0, 0, len, 64, 64 * t2, tid);                                                   \
+      load_sw<D, NT>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0_ + t2) * D,                   \
+                     (int64_t)HQ * D, c0, 0, len, 64, 64 * t2, tid);                                                   \
+    }                                                                                                                  \
+    cp_commit();                                                                                                       \
+  } while (0)
+  NHA_LOAD_HEAD_TILE(0);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
+    const int r = i >> 3, c8 = i & 7;
+    float gv[8];
+    unpack8(greg[j], gv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
+  // inclusive scan along the rows: four threads per column (16 rows each), then the earlier quarters' totals
   {
-    const int m = tid & 63, half = tid >> 6;
+    const int m = tid & 63, seg = tid >> 6;
     float run = 0.f;
-#pragma unroll 8
-    for (int r = 32 * half; r < 32 * half + 32; ++r) {
-      run += Gs[r * 65 + m];
-      Gs[r * 65 + m] = run;
+#pragma unroll
+    for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
+      run += As[r * 65 + m];
+      As[r * 65 + m] = run;
     }
     __syncthreads();
-    if (half == 1) {
-      const float add = Gs[31 * 65 + m];
-#pragma unroll 8
-      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+    float add = 0.f;
+    for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * 65 + m];
+    __syncthreads();
+    if (seg > 0) {
+#pragma unroll
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * 65 + m] += add;
     }
     __syncthreads();
   }
-  if (tid < 64) {
-    Rs[tid] = 0.5f * Gs[63 * 65 + tid];
-    w.gend[((size_t)cg * H + h) * M + tid] = Gs[63 * 65 + tid];
+  if (tid < 64) w.gend[((size_t)cg * H + h) * M + tid] = As[63 * 65 + tid];
+  // a = exp(G - R) replaces G in place; s' .* b = s' exp(R - G) goes into its swizzled tile
+  float rref[8];
+  {
+    const int c8 = tid & 7;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) rref[e] = 0.5f * As[63 * 65 + 8 * c8 + e];
   }
   __syncthreads();
+  if (tid < 8) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int i = tid + kBUThreads * j;
+    for (int e = 0; e < 8; ++e) ER[8 * tid + e] = __expf(rref[e]);
+  }
+#pragma unroll
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
     const int r = i >> 3, c8 = i & 7;
     float sv[8], out[8];
     unpack8(sreg[j], sv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) out[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    for (int e = 0; e < 8; ++e) {
+      const float x = As[r * 65 + 8 * c8 + e] - rref[e];
+      As[r * 65 + 8 * c8 + e] = __expf(x);
+      out[e] = sv[e] * __expf(-x);
+    }
     *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(out);
   }
   if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
@@ -149,18 +193,23 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  const int quarter = warp & 3, half = warp >> 2;
+  const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
   uint32_t phase = 0;
   bool failed = false;
 
   const bool active = R == 128 ? true : lane < 16;
-  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
   const int tk = row & 63, th = row >> 6;
   const int pos = c0 + tk;
   const bool in_seq = pos < len;
   const bool live = active && in_seq;
   const int jt_hi = ci;
   const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
+  // visible keys of this row: klo <= key <= pos, tested as (unsigned)(key - klo) <= kspan
+  const int klo = in_seq ? (wl < 0 ? 0 : max(0, pos - wl)) : (1 << 30);
+  const unsigned kspan = in_seq ? (unsigned)(pos - klo) : 0u;
+  const float sc2 = d.scale * kLog2e;
   const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aDO = smem_u32(sm + L::tDO);
   const uint32_t aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk);
   const uint32_t aHv = smem_u32(sm + L::tHv), aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW);
@@ -182,21 +231,19 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     __syncthreads();                                     \
     tc_fence_after();                                    \
   } while (0)
-// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+// this thread's half of tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 A-operand tile
 #define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
   do {                                                                                           \
     float tv_[32];                                                                               \
-    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
-      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
-      if (active) {                                                                              \
-        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
-          float o8[8];                                                                           \
-          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
-            const int i_ = 32 * part + 8 * c8 + e;                                               \
-            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
-          }                                                                                      \
-          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+    tmem_ld32(tlane + (col0) + 32 * half, tv_);                                                  \
+    if (active) {                                                                                \
+      _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                         \
+        float o8[8];                                                                             \
+        _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                          \
+          const int i_ = 32 * half + 8 * c8 + e;                                                 \
+          o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                              \
         }                                                                                        \
+        *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * half + c8)) = pack8(o8);      \
       }                                                                                          \
     }                                                                                            \
   } while (0)
@@ -205,24 +252,14 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     const int hq0 = h * NG + ht * TH;
     const int hq = hq0 + th;
     const size_t rowq = (size_t)(t0 + pos) * HQ + hq;          // (token, query head) index of this thread's row
-    // ---- tiles of this head tile -------------------------------------------------------------------------
-#pragma unroll
-    for (int t2 = 0; t2 < TH; ++t2) {
-      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
-                 64, 64 * t2, tid);
-      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0,
-                 len, 64, 64 * t2, tid);
-      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0 + t2) * D, (int64_t)HQ * D, c0, 0, len,
-                 64, 64 * t2, tid);
-    }
-    cp_commit();
-    // per-row scalars: delta = <do, o>, joint LSE, lse_gsa, d_lse_gsa
+    if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
+    // per-row scalars: delta = <do, o> (each thread its half of the columns), joint LSE, lse_gsa, d_lse_gsa
     float delta = 0.f, Lj = 0.f, lse_g = 0.f, dlse = 0.f;
     if (live) {
-      const bf16* orow = (const bf16*)d.o + rowq * D;
-      const bf16* grow = (const bf16*)d.d_o + rowq * D;
+      const bf16* orow = (const bf16*)d.o + rowq * D + (D / 2) * half;
+      const bf16* grow = (const bf16*)d.d_o + rowq * D + (D / 2) * half;
 #pragma unroll
-      for (int c8 = 0; c8 < D / 8; ++c8) {
+      for (int c8 = 0; c8 < D / 16; ++c8) {
         float a8[8], b8[8];
         unpack8(*reinterpret_cast<const uint4*>(orow + 8 * c8), a8);
         unpack8(*reinterpret_cast<const uint4*>(grow + 8 * c8), b8);
@@ -234,11 +271,15 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
       const float mx = fmaxf(ls, lse_g);
       Lj = mx + __logf(__expf(ls - mx) + __expf(lse_g - mx));
       dlse = d.d_lse_gsa ? d.d_lse_gsa[rowq] : 0.f;
+    }
+    xch[half * 128 + row] = delta;
+    cp_wait_all();
+    NHA_SMEM_TO_MMA();                                           // its barrier also publishes the partial deltas
+    delta += xch[(half ^ 1) * 128 + row];
+    if (live && half == 0) {
       w.delta[rowq] = delta;
       w.lj[rowq] = Lj;
     }
-    cp_wait_all();
-    NHA_SMEM_TO_MMA();
     // ---- A = q k'^T, Av = do v'^T, QH = q Hk, Y0 = do Hv^T ---------------------------------------------------
     if (tid == 0) {
       mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
@@ -255,53 +296,50 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
       mma_tile(tbase + L::cAv, aB, L::kATile, aSB, 0, R, 64, 4, 1, false);              // X2 = tril(Av) SB
     }
     NHA_MMA_WAIT();
-    // ---- slot part of dz; decayed bf16 copies; dgA -------------------------------------------------------------
+    // ---- slot part of dz (this thread's 32 slots); decayed bf16 copies; gate terms ---------------------------------
     // (the MMAs that read bufA / bufB have completed, so the tiles can take dza / dzg now)
     {
       float qh[32], xv[32], y0[32], x2[32];
+      tmem_ld32(tlane + L::cQH + 32 * half, qh);
+      tmem_ld32(tlane + L::cA + 32 * half, xv);
+      tmem_ld32(tlane + L::cY + 32 * half, y0);
+      tmem_ld32(tlane + L::cAv + 32 * half, x2);
+      if (active) {
+        const float nLj = -Lj * kLog2e, nLg = -lse_g * kLog2e;
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cQH + 32 * part, qh);
-        tmem_ld32(tlane + L::cA + 32 * part, xv);
-        tmem_ld32(tlane + L::cY + 32 * part, y0);
-        tmem_ld32(tlane + L::cAv + 32 * part, x2);
-        if (active) {
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float zg8[8], za8[8], pg8[8], pa8[8], ga8[8];
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            float zg8[8], za8[8], pg8[8], pa8[8], ga8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int m = 32 * part + 8 * c8 + e;
-              const float gl = Gs[tk * 65 + m];
-              const float eg = __expf(gl), aI = __expf(gl - Rs[m]);
-              const float ok = d.scale * (eg * qh[8 * c8 + e] + aI * xv[8 * c8 + e]);
-              const float dps = eg * y0[8 * c8 + e] + aI * x2[8 * c8 + e];
-              float ps = 0.f, dz = 0.f;
-              if (in_seq) {
-                ps = __expf(ok - Lj);
-                dz = ps * (dps - delta) + dlse * __expf(ok - lse_g);
-              }
-              ga8[e] = ok * dz + ps * dps;
-              zg8[e] = d.scale * dz * eg;
-              za8[e] = d.scale * dz * aI;
-              pg8[e] = ps * eg;
-              pa8[e] = ps * aI;
-            }
+          for (int e = 0; e < 8; ++e) {
+            const int m = 32 * half + 8 * c8 + e;
+            const float aI = As[tk * 65 + m], er = ER[m];
+            const float ok = d.scale * aI * (er * qh[8 * c8 + e] + xv[8 * c8 + e]);
+            const float dps = aI * (er * y0[8 * c8 + e] + x2[8 * c8 + e]);
+            float ps = 0.f, dz = 0.f;
             if (in_seq) {
-              float4* gdst = reinterpret_cast<float4*>(w.dga + ((size_t)(t0 + pos) * H + h) * M + 32 * part + 8 * c8);
-              atomicAdd(gdst, make_float4(ga8[0], ga8[1], ga8[2], ga8[3]));
-              atomicAdd(gdst + 1, make_float4(ga8[4], ga8[5], ga8[6], ga8[7]));
+              ps = exp2f(fmaf(ok, kLog2e, nLj));
+              dz = ps * (dps - delta) + dlse * exp2f(fmaf(ok, kLog2e, nLg));
             }
-            const uint4 zg = pack8(zg8), za = pack8(za8);
-            *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, 4 * part + c8)) = zg;
-            *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * part + c8)) = za;
-            if (in_seq) {
-              const size_t gi = rowq * M + 32 * part + 8 * c8;
-              *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
-              *reinterpret_cast<uint4*>(w.dza + gi) = za;
-              *reinterpret_cast<uint4*>(w.pgq + gi) = pack8(pg8);
-              *reinterpret_cast<uint4*>(w.paq + gi) = pack8(pa8);
-            }
+            ga8[e] = ok * dz + ps * dps;
+            za8[e] = d.scale * dz * aI;
+            zg8[e] = za8[e] * er;
+            pa8[e] = ps * aI;
+            pg8[e] = pa8[e] * er;
+          }
+          if (in_seq) {
+            float4* gdst = reinterpret_cast<float4*>(w.dga + ((size_t)(t0 + pos) * H + h) * M + 32 * half + 8 * c8);
+            atomicAdd(gdst, make_float4(ga8[0], ga8[1], ga8[2], ga8[3]));
+            atomicAdd(gdst + 1, make_float4(ga8[4], ga8[5], ga8[6], ga8[7]));
+          }
+          const uint4 zg = pack8(zg8), za = pack8(za8);
+          *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, 4 * half + c8)) = zg;
+          *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * half + c8)) = za;
+          if (in_seq) {
+            const size_t gi = rowq * M + 32 * half + 8 * c8;
+            *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
+            *reinterpret_cast<uint4*>(w.dza + gi) = za;
+            *reinterpret_cast<uint4*>(w.pgq + gi) = pack8(pg8);
+            *reinterpret_cast<uint4*>(w.paq + gi) = pack8(pa8);
           }
         }
       }
@@ -326,7 +364,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     __syncthreads();
 #pragma unroll
     for (int t2 = 0; t2 < TH; ++t2)
-      load_sw<64>(sm + L::bufA, 0, w.pgq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
+      load_sw<64, NT>(sm + L::bufA, 0, w.pgq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
     cp_commit();
     cp_wait_all();
     NHA_SMEM_TO_MMA();
@@ -339,48 +377,47 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     }
     NHA_MMA_WAIT();
     {
+      // 64-row products: rows in the first 16 lanes of each quarter; this thread's half of the columns
       const bool kact = lane < 16;
-      const int krow = warp * 16 + (lane & 15);
+      const int krow = quarter * 16 + (lane & 15);
       float lv[32];
 #pragma unroll
       for (int nb = 0; nb < KT; ++nb) {
+        tmem_ld32(tlane + L::cLK + 64 * nb + 32 * half, lv);
+        if (kact) {
+          float* dst = w.dkc + (((size_t)cg * H + h) * D + 64 * nb + krow) * M + 32 * half;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          tmem_ld32(tlane + L::cLK + 64 * nb + 32 * part, lv);
-          if (kact) {
-            float* dst = w.dkc + (((size_t)cg * H + h) * D + 64 * nb + krow) * M + 32 * part;
-#pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
-              if (ht > 0) {
-                const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
-                v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
-              }
-              *reinterpret_cast<float4*>(dst + e) = v4;
+          for (int e = 0; e < 32; e += 4) {
+            float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
+            if (ht > 0) {
+              const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
+              v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
             }
+            *reinterpret_cast<float4*>(dst + e) = v4;
           }
-          tmem_ld32(tlane + L::cLV + 64 * nb + 32 * part, lv);
-          if (kact) {
-            float* dst = w.dvc + (((size_t)cg * H + h) * M + krow) * D + 64 * nb + 32 * part;
+        }
+        tmem_ld32(tlane + L::cLV + 64 * nb + 32 * half, lv);
+        if (kact) {
+          float* dst = w.dvc + (((size_t)cg * H + h) * M + krow) * D + 64 * nb + 32 * half;
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
-              if (ht > 0) {
-                const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
-                v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
-              }
-              *reinterpret_cast<float4*>(dst + e) = v4;
+          for (int e = 0; e < 32; e += 4) {
+            float4 v4 = make_float4(lv[e], lv[e + 1], lv[e + 2], lv[e + 3]);
+            if (ht > 0) {
+              const float4 o4 = *reinterpret_cast<const float4*>(dst + e);
+              v4.x += o4.x; v4.y += o4.y; v4.z += o4.z; v4.w += o4.w;
             }
+            *reinterpret_cast<float4*>(dst + e) = v4;
           }
         }
       }
     }
     // ---- window part: dz_win tile by tile, dq_swa --------------------------------------------------------------------
+    const float nLjw = -Lj * kLog2e;
     for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
       tc_fence_before();
       __syncthreads();
-      load_sw<D>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
-      load_sw<D>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D, NT>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+      load_sw<D, NT>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
       cp_commit();
       cp_wait_all();
       NHA_SMEM_TO_MMA();
@@ -391,22 +428,18 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
       NHA_MMA_WAIT();
       {
         float sv[32], dp[32];
+        tmem_ld32(tlane + L::cS + 32 * half, sv);
+        tmem_ld32(tlane + L::cDP + 32 * half, dp);
+        if (active) {
+          const int off = jt * kChunk + 32 * half - klo;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          tmem_ld32(tlane + L::cS + 32 * part, sv);
-          tmem_ld32(tlane + L::cDP + 32 * part, dp);
-          if (active) {
+          for (int c8 = 0; c8 < 4; ++c8) {
+            float o8[8];
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-              float o8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const int key = jt * kChunk + 32 * part + 8 * c8 + e;
-                const bool vis = key <= pos && (wl < 0 || key >= pos - wl) && in_seq;
-                o8[e] = vis ? __expf(sv[8 * c8 + e] * d.scale - Lj) * (dp[8 * c8 + e] - delta) * d.scale : 0.f;
-              }
-              *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * part + c8)) = pack8(o8);
-            }
+            for (int e = 0; e < 8; ++e)
+              o8[e] = (unsigned)(off + 8 * c8 + e) <= kspan
+                          ? exp2f(fmaf(sv[8 * c8 + e], sc2, nLjw)) * (dp[8 * c8 + e] - delta) * d.scale : 0.f;
+            *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * half + c8)) = pack8(o8);
           }
         }
       }
@@ -418,11 +451,12 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
       }
       NHA_MMA_WAIT();
     }
-    // ---- dq rows out -----------------------------------------------------------------------------------------------------
+    // ---- dq rows out: this thread's half of the columns --------------------------------------------------------------------
     {
       float ov[32];
 #pragma unroll
-      for (int part = 0; part < D / 32; ++part) {
+      for (int pp = 0; pp < D / 64; ++pp) {
+        const int part = (D / 64) * half + pp;
         tmem_ld32(tlane + L::cDQ + 32 * part, ov);
         if (live) {
           bf16* orow = (bf16*)d.dq_gsa + rowq * D + 32 * part;
@@ -441,11 +475,16 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_rows_umma_kernel(const nha
     __syncthreads();
     tc_fence_after();
   }
+#undef NHA_LOAD_HEAD_TILE
   if (failed && tid == 0) atomicExch(err, 1);
+  cp_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
 }
+#undef NHA_MMA_WAIT
+#undef NHA_SMEM_TO_MMA
+#undef NHA_TRIL_TO_SMEM
 
 // ================================================================================================
 // gate-gradient carry and bf16 copies of the state gradients (between the scan and the columns pass)
@@ -539,6 +578,39 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
 // ================================================================================================
 // columns pass
 // ================================================================================================
+#define NHA_MMA_WAIT()                                   \
+  do {                                                   \
+    if (tid == 0) commit(mbar);                          \
+    if (!mbar_wait(mbar, phase)) failed = true;          \
+    phase ^= 1;                                          \
+    tc_fence_after();                                    \
+  } while (0)
+#define NHA_SMEM_TO_MMA()                                \
+  do {                                                   \
+    fence_async_smem();                                  \
+    tc_fence_before();                                   \
+    __syncthreads();                                     \
+    tc_fence_after();                                    \
+  } while (0)
+// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+#define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
+  do {                                                                                           \
+    float tv_[32];                                                                               \
+    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
+      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
+      if (active) {                                                                              \
+        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
+          float o8[8];                                                                           \
+          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
+            const int i_ = 32 * part + 8 * c8 + e;                                               \
+            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
+          }                                                                                      \
+          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+        }                                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+  } while (0)
+
 template <int D, int R>
 struct ColsLayout {
   static constexpr int KT = D / 64;
@@ -889,7 +961,7 @@ static int launch_rows(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaSt
   cudaError_t e = cudaFuncSetAttribute(nha_bwd_rows_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  nha_bwd_rows_umma_kernel<D, R><<<dim3(NCB, d->H), kBUThreads, L::total, cs>>>(*d, w, err);
+  nha_bwd_rows_umma_kernel<D, R><<<dim3(NCB, d->H), kRowsThreads, L::total, cs>>>(*d, w, err);
   return check_launch();
 }
 
