@@ -985,9 +985,12 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     wg.flags = flags; wg.gate = 1;
   }
   if (stage_mask & 1) {
-    if (umma) {
+    if (umma && d->HQ != d->H) {
+      // several query heads add their gate terms atomically; with one head per kv head every element has one writer
       cudaError_t e2 = cudaMemsetAsync(w.dga, 0, (size_t)d->Ttot * d->H * d->M * sizeof(float), cs);
       if (e2 != cudaSuccess) return record_cuda_error(e2);
+    }
+    if (umma) {
       st = bwd_umma_launch(d, wu, 0, err, cs);
       if (st != NHA_OK) return st;
     }

@@ -54,8 +54,17 @@ struct RowsLayout {
   static constexpr int oX = oR + 256;                   // fp32 [2 halves][128 rows]: partial <do, o> of the column halves
   static constexpr int oBar = oX + 1024;
   static constexpr int total = oBar + 64 + 1024;
-  static constexpr int tW = tQ;
-  static constexpr int tWV = R == 128 ? tQ + KT * 8192 : tWVx;
+  // One head per CTA (R == 64): tiles are reused as soon as the last product that reads them has completed.
+  //   v' and Hv are read by round 1 only      -> p .* a and p .* exp(G) (operands of the local terms, and the
+  //                                              source of the coalesced copy-out of the four bf16 copies)
+  //   k' and Hk are dead after dq_gsa          -> window keys / values of the even window tiles
+  //   q_gsa is dead after the local terms     -> window keys of the odd window tiles (values: tWVx)
+  // so the window loop is double-buffered and needs no global round trip.  With two heads per tile (R == 128)
+  // k', v', Hk, Hv serve every head tile and nothing is reused: one window buffer behind q_gsa.
+  static constexpr bool kAlias = R == 64;
+  static constexpr int tPA = tV, tPG = tHv;             // only with kAlias
+  static constexpr int tW0 = kAlias ? tK : tQ, tWV0 = kAlias ? tHk : (R == 128 ? tQ + KT * 8192 : tWVx);
+  static constexpr int tW1 = tQ, tWV1 = R == 128 ? tQ + KT * 8192 : tWVx;
   // Tensor-memory columns.  D == 64 fits 256 columns (two CTAs per SM) by reusing columns as soon as
   // their accumulator has been read: A, Av, QH, Y -> X, X2 -> E -> dq_gsa (over QH), local terms (over
   // Av, Y), then the window loop's S, dP, dq_swa (over A, Av, Y).
@@ -97,7 +106,17 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
 
-  // gates and write weights through registers; their loads go out first, the tile copies follow
+  // row of this thread: the warps w and w + 4 share a TMEM lane quarter and the rows in it
+  const int quarter = warp & 3, half = warp >> 2;
+  const bool active = R == 128 ? true : lane < 16;
+  const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
+  const int tk = row & 63, th = row >> 6;
+  const int pos = c0 + tk;
+  const bool in_seq = pos < len;
+  const bool live = active && in_seq;
+
+  // gates and write weights through registers; their loads and the first head tile's row scalars go out
+  // first, the tile copies follow
   const int lo = 0, hi = len - shift;
   constexpr int kGS = 512 / NT;
   uint4 sreg[kGS], greg[kGS];
@@ -112,6 +131,48 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
       greg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
       sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
     }
+  }
+  // per-row scalars: delta = <do, o> (each thread its half of the columns), joint LSE, lse_gsa, d_lse_gsa
+  float delta = 0.f, Lj = 0.f, lse_g = 0.f, dlse = 0.f;
+#define NHA_ROW_SCALARS(hq_)                                                                     \
+  do {                                                                                           \
+    delta = 0.f; Lj = 0.f; lse_g = 0.f; dlse = 0.f;                                              \
+    if (live) {                                                                                  \
+      const size_t rq_ = (size_t)(t0 + pos) * HQ + (hq_);                                        \
+      const bf16* orow = (const bf16*)d.o + rq_ * D + (D / 2) * half;                            \
+      const bf16* grow = (const bf16*)d.d_o + rq_ * D + (D / 2) * half;                          \
+      uint4 ou[D / 16], gu[D / 16];                                                              \
+      _Pragma("unroll") for (int c8 = 0; c8 < D / 16; ++c8) {                                    \
+        ou[c8] = *reinterpret_cast<const uint4*>(orow + 8 * c8);                                 \
+        gu[c8] = *reinterpret_cast<const uint4*>(grow + 8 * c8);                                 \
+      }                                                                                          \
+      const float ls_ = d.lse_swa[rq_];                                                          \
+      lse_g = d.lse_gsa[rq_];                                                                    \
+      dlse = d.d_lse_gsa ? d.d_lse_gsa[rq_] : 0.f;                                               \
+      _Pragma("unroll") for (int c8 = 0; c8 < D / 16; ++c8) {                                    \
+        float a8[8], b8[8];                                                                      \
+        unpack8(ou[c8], a8);                                                                     \
+        unpack8(gu[c8], b8);                                                                     \
+        _Pragma("unroll") for (int e = 0; e < 8; ++e) delta += a8[e] * b8[e];                    \
+      }                                                                                          \
+      const float mx_ = fmaxf(ls_, lse_g);                                                       \
+      Lj = mx_ + __logf(__expf(ls_ - mx_) + __expf(lse_g - mx_));                                \
+    }                                                                                            \
+  } while (0)
+  uint4 ou0[D / 16], gu0[D / 16];
+  float ls0 = 0.f;
+  if (live) {
+    const size_t rq = (size_t)(t0 + pos) * HQ + h * NG + th;
+    const bf16* orow = (const bf16*)d.o + rq * D + (D / 2) * half;
+    const bf16* grow = (const bf16*)d.d_o + rq * D + (D / 2) * half;
+#pragma unroll
+    for (int c8 = 0; c8 < D / 16; ++c8) {
+      ou0[c8] = *reinterpret_cast<const uint4*>(orow + 8 * c8);
+      gu0[c8] = *reinterpret_cast<const uint4*>(grow + 8 * c8);
+    }
+    ls0 = d.lse_swa[rq];
+    lse_g = d.lse_gsa[rq];
+    dlse = d.d_lse_gsa ? d.d_lse_gsa[rq] : 0.f;
   }
   load_sw<D, NT>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
   load_sw<D, NT>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
@@ -139,6 +200,18 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     unpack8(greg[j], gv);
 #pragma unroll
     for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
+  }
+  if (live) {
+#pragma unroll
+    for (int c8 = 0; c8 < D / 16; ++c8) {
+      float a8[8], b8[8];
+      unpack8(ou0[c8], a8);
+      unpack8(gu0[c8], b8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) delta += a8[e] * b8[e];
+    }
+    const float mx = fmaxf(ls0, lse_g);
+    Lj = mx + __logf(__expf(ls0 - mx) + __expf(lse_g - mx));
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
@@ -193,17 +266,10 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const int quarter = warp & 3, half = warp >> 2;
   const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
   uint32_t phase = 0;
   bool failed = false;
 
-  const bool active = R == 128 ? true : lane < 16;
-  const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
-  const int tk = row & 63, th = row >> 6;
-  const int pos = c0 + tk;
-  const bool in_seq = pos < len;
-  const bool live = active && in_seq;
   const int jt_hi = ci;
   const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
   // visible keys of this row: klo <= key <= pos, tested as (unsigned)(key - klo) <= kspan
@@ -212,8 +278,9 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
   const float sc2 = d.scale * kLog2e;
   const uint32_t aQ = smem_u32(sm + L::tQ), aQS = smem_u32(sm + L::tQS), aDO = smem_u32(sm + L::tDO);
   const uint32_t aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV), aHk = smem_u32(sm + L::tHk);
-  const uint32_t aHv = smem_u32(sm + L::tHv), aSB = smem_u32(sm + L::tSB), aW = smem_u32(sm + L::tW);
-  const uint32_t aWV = smem_u32(sm + L::tWV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
+  const uint32_t aHv = smem_u32(sm + L::tHv), aSB = smem_u32(sm + L::tSB);
+  const uint32_t aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
+  const uint32_t aPG = smem_u32(sm + L::tPG);
   const bf16* ksw = (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D;
   const bf16* vsw = (const bf16*)d.v + ((size_t)t0 * H + h) * D;
 
@@ -252,25 +319,9 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     const int hq0 = h * NG + ht * TH;
     const int hq = hq0 + th;
     const size_t rowq = (size_t)(t0 + pos) * HQ + hq;          // (token, query head) index of this thread's row
-    if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
-    // per-row scalars: delta = <do, o> (each thread its half of the columns), joint LSE, lse_gsa, d_lse_gsa
-    float delta = 0.f, Lj = 0.f, lse_g = 0.f, dlse = 0.f;
-    if (live) {
-      const bf16* orow = (const bf16*)d.o + rowq * D + (D / 2) * half;
-      const bf16* grow = (const bf16*)d.d_o + rowq * D + (D / 2) * half;
-#pragma unroll
-      for (int c8 = 0; c8 < D / 16; ++c8) {
-        float a8[8], b8[8];
-        unpack8(*reinterpret_cast<const uint4*>(orow + 8 * c8), a8);
-        unpack8(*reinterpret_cast<const uint4*>(grow + 8 * c8), b8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) delta += a8[e] * b8[e];
-      }
-      const float ls = d.lse_swa[rowq];
-      lse_g = d.lse_gsa[rowq];
-      const float mx = fmaxf(ls, lse_g);
-      Lj = mx + __logf(__expf(ls - mx) + __expf(lse_g - mx));
-      dlse = d.d_lse_gsa ? d.d_lse_gsa[rowq] : 0.f;
+    if (ht > 0) {
+      NHA_LOAD_HEAD_TILE(ht);
+      NHA_ROW_SCALARS(hq);
     }
     xch[half * 128 + row] = delta;
     cp_wait_all();
@@ -296,56 +347,87 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
       mma_tile(tbase + L::cAv, aB, L::kATile, aSB, 0, R, 64, 4, 1, false);              // X2 = tril(Av) SB
     }
     NHA_MMA_WAIT();
-    // ---- slot part of dz (this thread's 32 slots); decayed bf16 copies; gate terms ---------------------------------
-    // (the MMAs that read bufA / bufB have completed, so the tiles can take dza / dzg now)
+    // ---- slot part of dz (this thread's 32 slots, 16 at a time); decayed bf16 copies; gate terms -------------------
+    // (the MMAs that read bufA / bufB, v' and Hv have completed, so the tiles can take the copies now)
     {
-      float qh[32], xv[32], y0[32], x2[32];
-      tmem_ld32(tlane + L::cQH + 32 * half, qh);
-      tmem_ld32(tlane + L::cA + 32 * half, xv);
-      tmem_ld32(tlane + L::cY + 32 * half, y0);
-      tmem_ld32(tlane + L::cAv + 32 * half, x2);
-      if (active) {
-        const float nLj = -Lj * kLog2e, nLg = -lse_g * kLog2e;
+      const float nLj = -Lj * kLog2e, nLg = -lse_g * kLog2e;
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          float zg8[8], za8[8], pg8[8], pa8[8], ga8[8];
+      for (int hh = 0; hh < 2; ++hh) {
+        const int m0 = 32 * half + 16 * hh;
+        float qh[16], xv[16], y0[16], x2[16];
+        tmem_ld16(tlane + L::cQH + m0, qh);
+        tmem_ld16(tlane + L::cA + m0, xv);
+        tmem_ld16(tlane + L::cY + m0, y0);
+        tmem_ld16(tlane + L::cAv + m0, x2);
+        if (active) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int m = 32 * half + 8 * c8 + e;
-            const float aI = As[tk * 65 + m], er = ER[m];
-            const float ok = d.scale * aI * (er * qh[8 * c8 + e] + xv[8 * c8 + e]);
-            const float dps = aI * (er * y0[8 * c8 + e] + x2[8 * c8 + e]);
-            float ps = 0.f, dz = 0.f;
-            if (in_seq) {
-              ps = exp2f(fmaf(ok, kLog2e, nLj));
-              dz = ps * (dps - delta) + dlse * exp2f(fmaf(ok, kLog2e, nLg));
+          for (int c8 = 0; c8 < 2; ++c8) {
+            float zg8[8], za8[8], pg8[8], pa8[8], ga8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int m = m0 + 8 * c8 + e;
+              const float aI = As[tk * 65 + m], er = ER[m];
+              const float ok = d.scale * aI * (er * qh[8 * c8 + e] + xv[8 * c8 + e]);
+              const float dps = aI * (er * y0[8 * c8 + e] + x2[8 * c8 + e]);
+              float ps = 0.f, dz = 0.f;
+              if (in_seq) {
+                ps = exp2f(fmaf(ok, kLog2e, nLj));
+                dz = ps * (dps - delta) + dlse * exp2f(fmaf(ok, kLog2e, nLg));
+              }
+              ga8[e] = ok * dz + ps * dps;
+              za8[e] = d.scale * dz * aI;
+              zg8[e] = za8[e] * er;
+              pa8[e] = ps * aI;
+              pg8[e] = pa8[e] * er;
             }
-            ga8[e] = ok * dz + ps * dps;
-            za8[e] = d.scale * dz * aI;
-            zg8[e] = za8[e] * er;
-            pa8[e] = ps * aI;
-            pg8[e] = pa8[e] * er;
-          }
-          if (in_seq) {
-            float4* gdst = reinterpret_cast<float4*>(w.dga + ((size_t)(t0 + pos) * H + h) * M + 32 * half + 8 * c8);
-            atomicAdd(gdst, make_float4(ga8[0], ga8[1], ga8[2], ga8[3]));
-            atomicAdd(gdst + 1, make_float4(ga8[4], ga8[5], ga8[6], ga8[7]));
-          }
-          const uint4 zg = pack8(zg8), za = pack8(za8);
-          *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, 4 * half + c8)) = zg;
-          *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, 4 * half + c8)) = za;
-          if (in_seq) {
-            const size_t gi = rowq * M + 32 * half + 8 * c8;
-            *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
-            *reinterpret_cast<uint4*>(w.dza + gi) = za;
-            *reinterpret_cast<uint4*>(w.pgq + gi) = pack8(pg8);
-            *reinterpret_cast<uint4*>(w.paq + gi) = pack8(pa8);
+            const int ch = (m0 >> 3) + c8;                       // 16-byte chunk of the row
+            if (in_seq) {
+              float4* gdst = reinterpret_cast<float4*>(w.dga + ((size_t)(t0 + pos) * H + h) * M + 8 * ch);
+              if (NG == 1) {                                     // one writer per element: plain stores
+                gdst[0] = make_float4(ga8[0], ga8[1], ga8[2], ga8[3]);
+                gdst[1] = make_float4(ga8[4], ga8[5], ga8[6], ga8[7]);
+              } else {
+                atomicAdd(gdst, make_float4(ga8[0], ga8[1], ga8[2], ga8[3]));
+                atomicAdd(gdst + 1, make_float4(ga8[4], ga8[5], ga8[6], ga8[7]));
+              }
+            }
+            const uint4 zg = pack8(zg8), za = pack8(za8), pg = pack8(pg8), pa = pack8(pa8);
+            *reinterpret_cast<uint4*>(sm + L::bufB + sw_off(row, ch)) = zg;
+            *reinterpret_cast<uint4*>(sm + L::bufA + sw_off(row, ch)) = za;
+            if constexpr (L::kAlias) {
+              *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, ch)) = pg;
+              *reinterpret_cast<uint4*>(sm + L::tPA + sw_off(row, ch)) = pa;
+            } else if (in_seq) {
+              const size_t gi = rowq * M + 8 * ch;
+              *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
+              *reinterpret_cast<uint4*>(w.dza + gi) = za;
+              *reinterpret_cast<uint4*>(w.pgq + gi) = pg;
+              *reinterpret_cast<uint4*>(w.paq + gi) = pa;
+            }
           }
         }
       }
     }
     NHA_SMEM_TO_MMA();
     if (tid == 0) mma_tile(tbase + L::cA, aA, L::kATile, aSB, 0, R, 64, 4, 0, false);  // E = (scale dz a) SB^T
+    if constexpr (L::kAlias) {
+      // while E runs: the four bf16 copies leave through coalesced 128-byte rows
+      const bf16* tiles[4] = {(const bf16*)(sm + L::bufB), (const bf16*)(sm + L::bufA), (const bf16*)(sm + L::tPG),
+                              (const bf16*)(sm + L::tPA)};
+      bf16* dsts[4] = {w.dzg, w.dza, w.pgq, w.paq};
+#pragma unroll
+      for (int t4 = 0; t4 < 4; ++t4) {
+#pragma unroll
+        for (int j = 0; j < 512 / NT; ++j) {
+          const int i = tid + NT * j;
+          const int r = i >> 3, c = i & 7;
+          const uint4 v4 = *reinterpret_cast<const uint4*>((const unsigned char*)tiles[t4] + sw_off(r, c));
+          if (c0 + r < len)
+            *reinterpret_cast<uint4*>(dsts[t4] + ((size_t)(t0 + c0 + r) * HQ + hq0) * M + 8 * c) = v4;
+        }
+      }
+      __syncthreads();                                          // bufA is read out before tril(E) replaces it
+    }
     NHA_MMA_WAIT();
     NHA_TRIL_TO_SMEM(L::cA, L::bufA);
     NHA_SMEM_TO_MMA();
@@ -359,23 +441,42 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     }
     NHA_MMA_WAIT();
     // ---- the chunk's own contribution to the state gradients: q^T (scale dz exp G) and (p exp G)^T do -------------
-    // (p exp G) comes back from the scratch this CTA just wrote; bufA (tril(E)) is free again
-    tc_fence_before();
-    __syncthreads();
+    const int ntile = jt_hi - jt_lo + 1;
+    uint32_t aLP = aPG;
+    if constexpr (L::kAlias) {
+      // k' and Hk are dead: the first window tile goes in flight behind the local terms
+      load_sw<D, NT>(sm + L::tW0, 8192, ksw, (int64_t)H * D, jt_lo * kChunk, 0, len, 64, 0, tid);
+      load_sw<D, NT>(sm + L::tWV0, 8192, vsw, (int64_t)H * D, jt_lo * kChunk, 0, len, 64, 0, tid);
+      cp_commit();
+    } else {
+      // (p exp G) comes back from the scratch this CTA just wrote; bufA (tril(E)) is free again
+      tc_fence_before();
+      __syncthreads();
 #pragma unroll
-    for (int t2 = 0; t2 < TH; ++t2)
-      load_sw<64, NT>(sm + L::bufA, 0, w.pgq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2, tid);
-    cp_commit();
-    cp_wait_all();
-    NHA_SMEM_TO_MMA();
+      for (int t2 = 0; t2 < TH; ++t2)
+        load_sw<64, NT>(sm + L::bufA, 0, w.pgq + ((size_t)t0 * HQ + hq0 + t2) * M, (int64_t)HQ * M, c0, 0, len, 64, 64 * t2,
+                        tid);
+      cp_commit();
+      cp_wait_all();
+      NHA_SMEM_TO_MMA();
+      aLP = aA;
+    }
     if (tid == 0) {
 #pragma unroll
       for (int nb = 0; nb < KT; ++nb) {
         mma_tile_ex(tbase + L::cLK + 64 * nb, aQ + nb * L::kATile, 0, 1, aB, 0, 1, 64, 64, R / 16, false);
-        mma_tile_ex(tbase + L::cLV + 64 * nb, aA, 0, 1, aDO + nb * L::kATile, 0, 1, 64, 64, R / 16, false);
+        mma_tile_ex(tbase + L::cLV + 64 * nb, aLP, 0, 1, aDO + nb * L::kATile, 0, 1, 64, 64, R / 16, false);
       }
     }
     NHA_MMA_WAIT();
+    if constexpr (L::kAlias) {
+      if (ntile > 1) {
+        // q_gsa is dead: the second window tile goes in flight behind the read-out of the local terms
+        load_sw<D, NT>(sm + L::tW1, 8192, ksw, (int64_t)H * D, (jt_lo + 1) * kChunk, 0, len, 64, 0, tid);
+        load_sw<D, NT>(sm + L::tWV1, 8192, vsw, (int64_t)H * D, (jt_lo + 1) * kChunk, 0, len, 64, 0, tid);
+        cp_commit();
+      }
+    }
     {
       // 64-row products: rows in the first 16 lanes of each quarter; this thread's half of the columns
       const bool kact = lane < 16;
@@ -414,12 +515,20 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     // ---- window part: dz_win tile by tile, dq_swa --------------------------------------------------------------------
     const float nLjw = -Lj * kLog2e;
     for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+      const int wi = jt - jt_lo;
+      const int set = L::kAlias ? (wi & 1) : 0;
+      const uint32_t aW = smem_u32(sm + (set ? L::tW1 : L::tW0)), aWV = smem_u32(sm + (set ? L::tWV1 : L::tWV0));
       tc_fence_before();
-      __syncthreads();
-      load_sw<D, NT>(sm + L::tW, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
-      load_sw<D, NT>(sm + L::tWV, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
-      cp_commit();
-      cp_wait_all();
+      if constexpr (L::kAlias) {
+        // tiles wi and (when it exists) wi + 1 are in flight; groups complete in order
+        if (wi + 1 < ntile) cp_wait_but_one(); else cp_wait_all();
+      } else {
+        __syncthreads();
+        load_sw<D, NT>(sm + L::tW0, 8192, ksw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+        load_sw<D, NT>(sm + L::tWV0, 8192, vsw, (int64_t)H * D, jt * kChunk, 0, len, 64, 0, tid);
+        cp_commit();
+        cp_wait_all();
+      }
       NHA_SMEM_TO_MMA();
       if (tid == 0) {
         mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);      // S  = q_swa k^T
@@ -450,6 +559,14 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
           mma_tile(tbase + L::cDQS + 64 * nb, aA, L::kATile, aW + nb * 8192, 0, R, 64, 4, 1, jt > jt_lo);
       }
       NHA_MMA_WAIT();
+      if constexpr (L::kAlias) {
+        if (wi + 2 < ntile) {
+          // this tile's buffers are free again (every product that read them has completed): tile wi + 2 goes in flight
+          load_sw<D, NT>(sm + (set ? L::tW1 : L::tW0), 8192, ksw, (int64_t)H * D, (jt + 2) * kChunk, 0, len, 64, 0, tid);
+          load_sw<D, NT>(sm + (set ? L::tWV1 : L::tWV0), 8192, vsw, (int64_t)H * D, (jt + 2) * kChunk, 0, len, 64, 0, tid);
+          cp_commit();
+        }
+      }
     }
     // ---- dq rows out: this thread's half of the columns --------------------------------------------------------------------
     {
@@ -476,6 +593,7 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     tc_fence_after();
   }
 #undef NHA_LOAD_HEAD_TILE
+#undef NHA_ROW_SCALARS
   if (failed && tid == 0) atomicExch(err, 1);
   cp_wait_all();
   tc_fence_before();

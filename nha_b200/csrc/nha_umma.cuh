@@ -132,6 +132,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* out) {
   for (int i = 0; i < 32; ++i) out[i] = __uint_as_float(r[i]);
 }
 
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* out) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) out[i] = __uint_as_float(r[i]);
+}
+
 // ---- asynchronous 16-byte copies into swizzled tiles (NT-thread CTAs) ------------------------------
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -140,6 +155,8 @@ __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+// wait until at most the newest committed group is still in flight
+__device__ __forceinline__ void cp_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::); }
 
 // Asynchronously copy `rows` x COLS bf16 (global rows row0.., stride gstride elements; rows outside
 // [lo, hi) become zeros) into COLS/64 swizzled tiles of `tile_bytes` each, starting at tile row dst_row0.
