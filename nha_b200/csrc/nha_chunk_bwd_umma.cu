@@ -28,8 +28,8 @@ namespace nha {
 
 using namespace umma;
 
-constexpr int kBUThreads = 128;          // columns pass: one thread per row
 constexpr int kRowsThreads = 256;        // rows pass: two threads per row
+constexpr int kColsThreads = 256;        // columns pass: likewise
 
 // ================================================================================================
 // rows pass
@@ -710,21 +710,19 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
     __syncthreads();                                     \
     tc_fence_after();                                    \
   } while (0)
-// tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 swizzled A-operand tile
+// this thread's half of tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 A-operand tile
 #define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
   do {                                                                                           \
     float tv_[32];                                                                               \
-    _Pragma("unroll") for (int part = 0; part < 2; ++part) {                                     \
-      tmem_ld32(tlane + (col0) + 32 * part, tv_);                                                \
-      if (active) {                                                                              \
-        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
-          float o8[8];                                                                           \
-          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
-            const int i_ = 32 * part + 8 * c8 + e;                                               \
-            o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                            \
-          }                                                                                      \
-          *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * part + c8)) = pack8(o8);    \
+    tmem_ld32(tlane + (col0) + 32 * half, tv_);                                                  \
+    if (active) {                                                                                \
+      _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                         \
+        float o8[8];                                                                             \
+        _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                          \
+          const int i_ = 32 * half + 8 * c8 + e;                                                 \
+          o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                              \
         }                                                                                        \
+        *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * half + c8)) = pack8(o8);      \
       }                                                                                          \
     }                                                                                            \
   } while (0)
@@ -763,11 +761,13 @@ struct ColsLayout {
   static constexpr int cA = 0, cAv = 64, cDK = 128, cDV = 128 + D, cDS = kDsInRegs ? cDK : 128 + 2 * D, cDS2 = cA;
 };
 
+// Two threads per row, as in the rows pass: the warps w and w + 4 share a TMEM lane quarter and take
+// alternate 32-column halves of every 64-column accumulator.
 template <int D, int R>
-__global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha_chunk_desc d, const BwdWs w,
-                                                                       int* __restrict__ err) {
+__global__ void __launch_bounds__(kColsThreads, (D == 64 && R == 64) ? 2 : 1)
+    nha_bwd_cols_umma_kernel(const nha_chunk_desc d, const BwdWs w, int* __restrict__ err) {
   typedef ColsLayout<D, R> L;
-  constexpr int KT = L::KT, TH = R / 64, M = 64;
+  constexpr int KT = L::KT, TH = R / 64, M = 64, NT = kColsThreads;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
@@ -783,100 +783,132 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* Gs = (float*)(sm + L::oG);
-  float* Rs = (float*)(sm + L::oR);
-  float* cgv = Rs + 64;
+  float* Bs = (float*)(sm + L::oG);                   // cumulative gates, then b = exp(R - G)
+  float* ER = (float*)(sm + L::oR);                   // exp(R)
+  float* cgv = ER + 64;
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
 
-  // ---- everything the first head tile needs goes in flight at once -------------------------------------
+  // ---- gate / write-weight loads first, then everything the first head tile needs goes in flight at once -------
   const int lo = 0, hi = len - shift;
-  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
-  load_sw<64>(sm + L::tDK, 0, w.dkb + ch * D * M, M, 0, 0, D, D, 0, tid);
-  load_sw<D>(sm + L::tDV, 8192, w.dvb + ch * M * D, D, 0, 0, M, M, 0, tid);
+  constexpr int kGS = 512 / NT;
+  uint4 sreg[kGS], greg[kGS];
+#pragma unroll
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
+    const int r = i >> 3, c8 = i & 7;
+    const int src = c0 + r - shift;
+    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+    greg[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= lo && src < hi) {
+      greg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+    }
+  }
+  float carry_in = 0.f;
+  if (tid < 64) carry_in = w.gcarry[ch * M + tid];
+  load_sw<D, NT>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<D, NT>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0 - shift, lo, hi, 64, 0, tid);
+  load_sw<64, NT>(sm + L::tDK, 0, w.dkb + ch * D * M, M, 0, 0, D, D, 0, tid);
+  load_sw<D, NT>(sm + L::tDV, 8192, w.dvb + ch * M * D, D, 0, 0, M, M, 0, tid);
 #define NHA_LOAD_HEAD_TILE(ht_)                                                                                      \
   do {                                                                                                               \
     const int hq0_ = h * NG + (ht_) * TH;                                                                            \
     _Pragma("unroll") for (int t2 = 0; t2 < TH; ++t2) {                                                              \
-      load_sw<D>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
-                 c0, 0, len, 64, 64 * t2, tid);                                                                      \
-      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,    \
-                 c0, 0, len, 64, 64 * t2, tid);                                                                      \
-      load_sw<64>(sm + L::tZA, 0, w.dza + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,        \
-                  64 * t2, tid);                                                                                     \
-      load_sw<64>(sm + L::tPA, 0, w.paq + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,        \
-                  64 * t2, tid);                                                                                     \
+      load_sw<D, NT>(sm + L::tQ, L::kATile, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq0_ + t2) * D,                \
+                     (int64_t)HQ * D, c0, 0, len, 64, 64 * t2, tid);                                                 \
+      load_sw<D, NT>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq0_ + t2) * D,                 \
+                     (int64_t)HQ * D, c0, 0, len, 64, 64 * t2, tid);                                                 \
+      load_sw<64, NT>(sm + L::tZA, 0, w.dza + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,    \
+                      64 * t2, tid);                                                                                 \
+      load_sw<64, NT>(sm + L::tPA, 0, w.paq + ((size_t)t0 * HQ + hq0_ + t2) * M, (int64_t)HQ * M, c0, 0, len, 64,    \
+                      64 * t2, tid);                                                                                 \
     }                                                                                                                \
     cp_commit();                                                                                                     \
   } while (0)
   NHA_LOAD_HEAD_TILE(0);
-  uint4 sreg[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int i = tid + kBUThreads * j;
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
     const int r = i >> 3, c8 = i & 7;
-    const int src = c0 + r - shift;
-    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    sreg[j] = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= lo && src < hi) {
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8), gv);
-      sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
-    }
+    float gv[8];
+    unpack8(greg[j], gv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) Gs[r * 65 + 8 * c8 + e] = gv[e];
+    for (int e = 0; e < 8; ++e) Bs[r * 65 + 8 * c8 + e] = gv[e];
   }
-  if (tid < 64) cgv[tid] = w.gcarry[ch * M + tid];
+  if (tid < 64) cgv[tid] = carry_in;
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
+  // inclusive scan along the rows: four threads per column (16 rows each), then the earlier quarters' totals
   {
-    const int m = tid & 63, half = tid >> 6;
+    const int m = tid & 63, seg = tid >> 6;
     float run = 0.f;
-#pragma unroll 8
-    for (int r = 32 * half; r < 32 * half + 32; ++r) {
-      run += Gs[r * 65 + m];
-      Gs[r * 65 + m] = run;
+#pragma unroll
+    for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
+      run += Bs[r * 65 + m];
+      Bs[r * 65 + m] = run;
     }
     __syncthreads();
-    if (half == 1) {
-      const float add = Gs[31 * 65 + m];
-#pragma unroll 8
-      for (int r = 32; r < 64; ++r) Gs[r * 65 + m] += add;
+    float add = 0.f;
+    for (int s2 = 0; s2 < seg; ++s2) add += Bs[(16 * s2 + 15) * 65 + m];
+    __syncthreads();
+    if (seg > 0) {
+#pragma unroll
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) Bs[r * 65 + m] += add;
     }
     __syncthreads();
   }
-  if (tid < 64) Rs[tid] = 0.5f * Gs[63 * 65 + tid];
-  __syncthreads();
+  // b = exp(R - G) replaces G in place; s' .* b goes into its swizzled tile (s' .* b .* exp(R) = s' exp(Gend - G)
+  // follows after the head loop)
+  float rref[8];
+  {
+    const int c8 = tid & 7;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int i = tid + kBUThreads * j;
+    for (int e = 0; e < 8; ++e) rref[e] = 0.5f * Bs[63 * 65 + 8 * c8 + e];
+  }
+  __syncthreads();
+  if (tid < 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ER[8 * tid + e] = __expf(rref[e]);
+  }
+  uint4 sbe[kGS];                                      // s' exp(Gend - G), written after the head loop
+#pragma unroll
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
     const int r = i >> 3, c8 = i & 7;
-    float sv[8], o1[8];
+    float sv[8], o1[8], o2[8];
     unpack8(sreg[j], sv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o1[e] = sv[e] * __expf(Rs[8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
+    for (int e = 0; e < 8; ++e) {
+      const float b = __expf(rref[e] - Bs[r * 65 + 8 * c8 + e]);
+      Bs[r * 65 + 8 * c8 + e] = b;
+      o1[e] = sv[e] * b;
+      o2[e] = o1[e] * __expf(rref[e]);
+    }
     *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(o1);
+    sbe[j] = pack8(o2);
   }
   if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  const int quarter = warp & 3, half = warp >> 2;
+  const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
   uint32_t phase = 0;
   bool failed = false;
 
   // rows of the R-row products (query rows) and of the 64-row products (key rows)
   const bool active = R == 128 ? true : lane < 16;
-  const int row = R == 128 ? tid : warp * 16 + (lane & 15);
+  const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
   const int tk = row & 63;
   const bool kactive = lane < 16;
-  const int krow = warp * 16 + (lane & 15);
+  const int krow = quarter * 16 + (lane & 15);
   const uint32_t aQ = smem_u32(sm + L::tQ), aDO = smem_u32(sm + L::tDO), aZA = smem_u32(sm + L::tZA);
   const uint32_t aPA = smem_u32(sm + L::tPA), aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV);
   const uint32_t aSB = smem_u32(sm + L::tSB), aDK = smem_u32(sm + L::tDK);
   const uint32_t aDV = smem_u32(sm + L::tDV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
-  float dsk[L::kDsInRegs ? 64 : 1];
+  float dsk[L::kDsInRegs ? 32 : 1];                   // this thread's half of the intra-chunk ds' accumulator
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
     if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
@@ -898,10 +930,7 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
       mma_tile(tbase + L::cAv, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);               // Bv = pa SB^T
     }
     NHA_MMA_WAIT();
-    if constexpr (L::kDsInRegs) {
-      tmem_ld32(tlane + L::cDS, dsk);
-      tmem_ld32(tlane + L::cDS + 32, dsk + 32);
-    }
+    if constexpr (L::kDsInRegs) tmem_ld32(tlane + L::cDS + 32 * half, dsk);
     NHA_TRIL_TO_SMEM(L::cA, L::bufA);
     NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
     NHA_SMEM_TO_MMA();
@@ -928,23 +957,22 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   float* eV = (float*)(sm + L::eV);
   bf16* eS = (bf16*)(sm + L::eS);
   {
-    // rows r of the chunk: shifted position c0 + r, source token c0 + r - shift
     const float* gsrc = w.dga + ((size_t)t0 * H + h) * M;
-    for (int i = tid; i < 64 * 16; i += kBUThreads) {
+    for (int i = tid; i < 64 * 16; i += NT) {
       const int r = i >> 4, c = i & 15;
       const int p = c0 + r;
       const bool ok = p - shift >= 0 && p < len;
       cp16(eG + r * L::kLdG + 4 * c, gsrc + (size_t)(ok ? p : 0) * H * M + 4 * c, ok);
     }
     const float* vsrc = w.dvacc + ((size_t)t0 * H + h) * D;
-    for (int i = tid; i < 64 * (D / 4); i += kBUThreads) {
+    for (int i = tid; i < 64 * (D / 4); i += NT) {
       const int r = i / (D / 4), c = i % (D / 4);
       const int p = c0 + r, j = p - shift;
       const bool ok = j >= 0 && p < len;
       cp16(eV + r * L::kLdV + 4 * c, vsrc + (size_t)(ok ? j : 0) * H * D + 4 * c, ok);
     }
     const bf16* ssrc = (const bf16*)d.s + ((size_t)t0 * H + h) * M;
-    for (int i = tid; i < 64 * 8; i += kBUThreads) {
+    for (int i = tid; i < 64 * 8; i += NT) {
       const int r = i >> 3, c = i & 7;
       const int p = c0 + r, j = p - shift;
       const bool ok = j >= 0 && p < len;
@@ -954,14 +982,10 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   }
   // s' exp(Gend - G) replaces s' b (every product that read it has completed)
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int i = tid + kBUThreads * j;
+  for (int j = 0; j < kGS; ++j) {
+    const int i = tid + NT * j;
     const int r = i >> 3, c8 = i & 7;
-    float sv[8], o2[8];
-    unpack8(sreg[j], sv);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o2[e] = sv[e] * __expf(Gs[63 * 65 + 8 * c8 + e] - Gs[r * 65 + 8 * c8 + e]);
-    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = pack8(o2);
+    *reinterpret_cast<uint4*>(sm + L::tSB + sw_off(r, c8)) = sbe[j];
   }
   NHA_SMEM_TO_MMA();
   if (!failed) {
@@ -980,44 +1004,43 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   }
   cp_wait_all();
   __syncthreads();
-  // ---- epilogue: one thread per key row ---------------------------------------------------------------------------
+  // ---- epilogue: two threads per key row, each its half of the columns ----------------------------------------------
   {
     float dsi[32], ds2[32];
+    if constexpr (L::kDsInRegs) {
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      if constexpr (L::kDsInRegs) {
+      for (int e = 0; e < 32; ++e) dsi[e] = dsk[e];
+    } else {
+      tmem_ld32(tlane + L::cDS + 32 * half, dsi);
+    }
+    tmem_ld32(tlane + L::cDS2 + 32 * half, ds2);
+    if (kactive) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) dsi[e] = dsk[32 * part + e];
-      } else {
-        tmem_ld32(tlane + L::cDS + 32 * part, dsi);
-      }
-      tmem_ld32(tlane + L::cDS2 + 32 * part, ds2);
-      if (kactive) {
+      for (int c8 = 0; c8 < 4; ++c8) {
+        const int m0 = 32 * half + 8 * c8;
+        float ds8[8], sv[8];
+        unpack8(*reinterpret_cast<const uint4*>(eS + krow * L::kLdS + m0), sv);
+        float* grow = eG + krow * L::kLdG + m0;
+        const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
+        const float ga[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        float gr[8];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          float ds8[8], sv[8];
-          unpack8(*reinterpret_cast<const uint4*>(eS + krow * L::kLdS + 32 * part + 8 * c8), sv);
-          float* grow = eG + krow * L::kLdG + 32 * part + 8 * c8;
-          const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
-          const float ga[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-          float gr[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int m = 32 * part + 8 * c8 + e;
-            const float gl = Gs[krow * 65 + m];
-            const float ds = __expf(Rs[m] - gl) * dsi[8 * c8 + e] + __expf(Gs[63 * 65 + m] - gl) * ds2[8 * c8 + e];
-            ds8[e] = ds;
-            gr[e] = keep ? ga[e] - sv[e] * ds : 0.f;
-          }
-          *reinterpret_cast<float4*>(grow) = make_float4(gr[0], gr[1], gr[2], gr[3]);
-          *reinterpret_cast<float4*>(grow + 4) = make_float4(gr[4], gr[5], gr[6], gr[7]);
-          if (keep) *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + kj) * H + h) * M + 32 * part + 8 * c8) = pack8(ds8);
+        for (int e = 0; e < 8; ++e) {
+          const int m = m0 + e;
+          // ds' = b .* (intra-chunk part) + exp(Gend - G) .* (inter-chunk part), exp(Gend - G) = b exp(R)
+          const float ds = Bs[krow * 65 + m] * (dsi[8 * c8 + e] + ER[m] * ds2[8 * c8 + e]);
+          ds8[e] = ds;
+          gr[e] = keep ? ga[e] - sv[e] * ds : 0.f;
         }
+        *reinterpret_cast<float4*>(grow) = make_float4(gr[0], gr[1], gr[2], gr[3]);
+        *reinterpret_cast<float4*>(grow + 4) = make_float4(gr[4], gr[5], gr[6], gr[7]);
+        if (keep) *reinterpret_cast<uint4*>((bf16*)d.ds + ((size_t)(t0 + kj) * H + h) * M + m0) = pack8(ds8);
       }
     }
     float ov[32];
 #pragma unroll
-    for (int part = 0; part < D / 32; ++part) {
+    for (int pp = 0; pp < D / 64; ++pp) {
+      const int part = (D / 64) * half + pp;
       tmem_ld32(tlane + L::cDK + 32 * part, ov);
       if (keep) {
         bf16* orow = (bf16*)d.dk_gsa + ((size_t)(t0 + kj) * H + h) * D + 32 * part;
@@ -1042,29 +1065,31 @@ __global__ void __launch_bounds__(kBUThreads) nha_bwd_cols_umma_kernel(const nha
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
-  // reverse cumulative sum of dgraw along the rows (two threads per column), plus the carry
+  // reverse cumulative sum of dgraw along the rows (four threads per column), plus the carry
   {
-    const int m = tid & 63, half = tid >> 6;
+    const int m = tid & 63, seg = tid >> 6;
     float run = 0.f;
-#pragma unroll 8
-    for (int r = 32 * half + 31; r >= 32 * half; --r) {
+#pragma unroll
+    for (int r = 16 * seg + 15; r >= 16 * seg; --r) {
       run += eG[r * L::kLdG + m];
       eG[r * L::kLdG + m] = run;
     }
     __syncthreads();
-    const float add = cgv[m] + (half == 0 ? eG[32 * L::kLdG + m] : 0.f);
-    __syncthreads();                                  // every read of the upper half's total precedes its update
-#pragma unroll 8
-    for (int r = 32 * half; r < 32 * half + 32; ++r) eG[r * L::kLdG + m] += add;
+    float add = cgv[m];
+    for (int s2 = seg + 1; s2 < 4; ++s2) add += eG[(16 * s2) * L::kLdG + m];
+    __syncthreads();                                  // every read of the later quarters' totals precedes their update
+#pragma unroll
+    for (int r = 16 * seg; r < 16 * seg + 16; ++r) eG[r * L::kLdG + m] += add;
     __syncthreads();
   }
   if (keep) {
 #pragma unroll
-    for (int c8 = 0; c8 < 8; ++c8) {
-      const float* grow = eG + krow * L::kLdG + 8 * c8;
+    for (int c8 = 0; c8 < 4; ++c8) {
+      const int m0 = 32 * half + 8 * c8;
+      const float* grow = eG + krow * L::kLdG + m0;
       const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
       const float g8[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-      *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + kj) * H + h) * M + 8 * c8) = pack8(g8);
+      *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + kj) * H + h) * M + m0) = pack8(g8);
     }
   }
   if (failed && tid == 0) atomicExch(err, 1);
@@ -1092,7 +1117,7 @@ static int launch_cols(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaSt
   nha_bwd_gate_carry_kernel<<<dim3(NCB, d->H), kCarryThreads, 0, cs>>>(*d, w);
   int st = check_launch();
   if (st != NHA_OK) return st;
-  nha_bwd_cols_umma_kernel<D, R><<<dim3(NCB, d->H), kBUThreads, L::total, cs>>>(*d, w, err);
+  nha_bwd_cols_umma_kernel<D, R><<<dim3(NCB, d->H), kColsThreads, L::total, cs>>>(*d, w, err);
   return check_launch();
 }
 
