@@ -63,10 +63,14 @@ int nha_abi_version(void);
  *            win_logits mode)
  *   win_prob [B, HQ, W] fp32   window probabilities of the joint softmax, or NULL
  *   workspace  scratch of nha_decode_workspace_bytes(B, HQ, H, V, W) bytes, needed when W > 64
- *            (a (sequence, kv head) is then split over ceil(W/64) CTAs whose partial softmaxes are
- *            merged by the last one to finish).  Its first B*H int32 are arrival counters: they must
- *            be zero before the first call and every call leaves them zero, so one zero-initialised
- *            buffer can be reused by all calls that do not overlap on the GPU.  May be NULL for W <= 64.
+ *            (a (sequence, kv head) is then split over several CTAs whose partial softmaxes are
+ *            merged by the last one to finish).  Its first B*H int32 are arrival counters, the next
+ *            int32 is a device error word (nha_decode_device_error): they must be zero before the
+ *            first call and every call leaves the counters zero, so one zero-initialised buffer can
+ *            be reused by all calls with the same B*H that do not overlap on the GPU.  May be NULL
+ *            for W <= 64.
+ * K == V in {64, 128} with window keys takes a streaming kernel (ring of cp.async.bulk copies, whole
+ * grid resident in one wave); other shapes and the win_logits mode take the general kernel.
  */
 int64_t nha_decode_workspace_bytes(int B, int HQ, int H, int V, int W);
 int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
@@ -74,6 +78,9 @@ int nha_decode_step(const void* q, const void* sq, const void* k, const void* v,
                     int64_t cs_row, const void* win_logits, float* hk, float* hv, int zero_state, void* o,
                     float* win_prob, void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V,
                     int M, int W, float scale, void* stream);
+/* reads the workspace's device error word (synchronises the stream): non-zero when a bounded wait
+   inside the streaming decode kernel ran out.  No counterpart in the reference. */
+int nha_decode_device_error(const void* workspace, int B, int H, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Chunked prefill / training.  One descriptor serves the state pass, the output pass and the

@@ -458,15 +458,40 @@ static int decode_splits(int W, bool logits_mode) {
   return (W + per - 1) / per;
 }
 
+int decode_stream_splits(int B, int H, int W, int M);
+bool decode_stream_supported(int K, int V, int M, int W, int NG, bool logits_mode);
+int decode_stream_try(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
+                      const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
+                      int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
+                      float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
+                      cudaStream_t st);
+
+// Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
+// every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
+static int decode_max_splits(int B, int H, int W) {
+  const int a = decode_splits(W, false), b = decode_stream_splits(B, H, W, 1 << 20);
+  return a > b ? a : b;
+}
+
 }  // namespace nha
 
 using namespace nha;
 
 extern "C" int64_t nha_decode_workspace_bytes(int B, int HQ, int H, int V, int W) {
   if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H) return 0;
-  const int64_t spl = decode_splits(W, false);
+  const int64_t spl = decode_max_splits(B, H, W);
   const int64_t NG = HQ / H;
-  return (int64_t)B * H * spl * NG * (V + 2) * 4 + (int64_t)B * H * 4 + 1024;
+  return (int64_t)B * H * spl * NG * (V + 2) * 4 + ((int64_t)B * H + 1) * 4 + 1024;
+}
+
+extern "C" int nha_decode_device_error(const void* workspace, int B, int H, void* stream) {
+  if (!workspace || B <= 0 || H <= 0) return 0;
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, (const int*)workspace + (size_t)B * H, sizeof(int), cudaMemcpyDeviceToHost,
+                                  (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  return v;
 }
 
 extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g,
@@ -492,7 +517,10 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   a.hk = hk; a.hv = hv; a.o = (bf16*)o; a.win_prob = win_prob;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.K = K; a.V = V; a.M = M; a.W = W; a.NG = NG;
-  a.SPLITS = decode_splits(W, logits_mode);
+  // common shapes take the streaming kernel (ring of bulk copies, whole grid resident in one wave)
+  const char* force_general = getenv("NHA_B200_DECODE_GENERAL");
+  const bool stream_ok = decode_stream_supported(K, V, M, W, NG, logits_mode) && !(force_general && force_general[0] == '1');
+  a.SPLITS = stream_ok ? decode_stream_splits(B, H, W, M) : decode_splits(W, logits_mode);
   if (a.SPLITS > kMaxSplits) return NHA_ERR_UNSUPPORTED;
   if (logits_mode) {
     a.KS = 0;
@@ -504,14 +532,21 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   a.MQ = align_up((M + a.SPLITS - 1) / a.SPLITS, 4);
   a.zero_state = zero_state; a.scale = scale;
   a.part_o = nullptr; a.part_ml = nullptr; a.tickets = nullptr;
-  if (a.SPLITS > 1) {
-    if (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W)) return NHA_ERR_WORKSPACE;
-    // tickets first (they must stay zero between calls), then the partials
-    a.tickets = (int*)workspace;
-    char* base = (char*)workspace + align_up(B * H * 4, 256);
-    a.part_ml = (float*)base;
-    a.part_o = (float*)(base + align_up(B * H * a.SPLITS * NG * 2 * 4, 256));
+  int* errw = nullptr;
+  if (a.SPLITS > 1 || stream_ok) {
+    if (a.SPLITS > 1 && (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W))) return NHA_ERR_WORKSPACE;
+    if (workspace && workspace_bytes >= nha_decode_workspace_bytes(B, HQ, H, V, W)) {
+      // tickets and the error word first (they must stay zero between calls), then the partials
+      a.tickets = (int*)workspace;
+      errw = a.tickets + (size_t)B * H;
+      char* base = (char*)workspace + align_up((B * H + 1) * 4, 256);
+      a.part_ml = (float*)base;
+      a.part_o = (float*)(base + align_up(B * H * a.SPLITS * NG * 2 * 4, 256));
+    }
   }
+  if (stream_ok)
+    return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
+                             errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;

@@ -1,0 +1,544 @@
+// Streaming variant of the fused NHA decode step (sm_100a) for the common shapes: K == V in {64, 128},
+// window keys in the cache (not caller-supplied logits).  Same arithmetic and the same split / merge
+// protocol as nha_decode.cu, organised so that the whole grid is resident at once and every byte a CTA
+// needs is requested as early as shared memory allows:
+//
+//   * a (sequence, kv head) is cut into SPLITS CTAs chosen so that B*H*SPLITS CTAs fit the GPU in ONE
+//     wave (two CTAs per SM); split s owns a contiguous range of window keys and of slots;
+//   * window keys and values stream through a ring of four 64-key slots filled by 16-byte asynchronous
+//     copies with one commit group per stage (the rows of one kv head are 2 D bytes long and H times that
+//     apart, too short for bulk copies to pay: one cp.async.bulk per row measured slower): first every key
+//     stage, then - into slots as their keys have been used - the value stages.  All logits of
+//     the CTA are kept ([16][keys] fp32), so the softmax is exact in one pass and the value readout
+//     accumulates in registers without rescaling;
+//   * the hk columns of the split never touch shared memory: a thread updates its elements in registers,
+//     stores them back and contributes to the slot logits of all query heads, which are then summed over
+//     the warps; the hv rows, contiguous in memory, arrive by ONE bulk copy (cp.async.bulk on an mbarrier).
+//
+// Replaces the two Triton launches of fused_recurrent_nha_decode
+// (nha_fla/ops/nha/fused_recurrent.py:229-353 k-kernel, :356-428 v-kernel).
+#include "nha_common.cuh"
+#include "nha_umma.cuh"
+
+namespace nha {
+
+constexpr int kStrThreads = 256;
+constexpr int kStrWarps = kStrThreads / 32;
+constexpr int kStrStage = 64;            // keys per ring slot
+constexpr int kStrSlots = 4;
+
+struct DecodeStreamArgs {
+  const bf16* q; const bf16* sq; const bf16* k; const bf16* v; const bf16* g; const bf16* s;
+  const bf16* sw_k; const bf16* sw_v; const bf16* cosp; const bf16* sinp;
+  float* hk; float* hv; bf16* o;
+  float* part_o;      // [B*H, SPLITS, NG, V] unnormalised partial outputs
+  float* part_ml;     // [B*H, SPLITS, NG, 2] maximum and sum of each split
+  int* tickets;       // [B*H] arrival counters, zero between calls
+  int* err;           // device error word (a bounded wait ran out)
+  int64_t cs_batch, cs_row;
+  int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
+  float scale;
+  int off_ring, off_hv, off_S, off_red, off_q, off_sqA, off_oks, off_eg, off_sv, off_kpop, off_vpop, off_ml, off_bar;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   umma::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(umma::smem_u32(mbar))
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint64_t* mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(umma::smem_u32(mbar)), "r"(bytes) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const DecodeStreamArgs a) {
+  using namespace nvcuda::wmma;
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int K = D, V = D, ldk = D + 8, ldq = D + 8, ldo = D + 8;
+  constexpr int kSlotBytes = kStrStage * ldk * 2;
+  unsigned char* ring = smem + a.off_ring;                         // [4 slots][64][D+8] bf16
+  float* hvS = reinterpret_cast<float*>(smem + a.off_hv);          // [MQ][V] my rows of hv
+  float* S = reinterpret_cast<float*>(smem + a.off_S);             // [16][nkp+8] logits, then bf16 weights in place
+  float* red = reinterpret_cast<float*>(smem + a.off_red);         // [warps][NG][32] partial slot logits
+  bf16* qs = reinterpret_cast<bf16*>(smem + a.off_q);              // [NG][K] raw query
+  bf16* sqA = reinterpret_cast<bf16*>(smem + a.off_sqA);           // [16][K+8] rotated query (rows >= NG zero)
+  float* oks = reinterpret_cast<float*>(smem + a.off_oks);         // [NG][MQ] slot logits -> unnormalised weights
+  float* eg = reinterpret_cast<float*>(smem + a.off_eg);
+  float* sv = reinterpret_cast<float*>(smem + a.off_sv);
+  float* kpop = reinterpret_cast<float*>(smem + a.off_kpop);
+  float* vpop = reinterpret_cast<float*>(smem + a.off_vpop);
+  float* ml = reinterpret_cast<float*>(smem + a.off_ml);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + a.off_bar);  // [4] ring slots, [4] = hv rows
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int SPL = a.SPLITS, NG = a.NG, M = a.M, W = a.W, MQ = a.MQ;
+  const int bh = blockIdx.x / SPL, sp = blockIdx.x % SPL;
+  const int b = bh / a.H, h = bh % a.H;
+  const bool rotary = a.cosp != nullptr;
+  const int w0 = sp * a.KSPL;
+  const int nkeys = max(0, min(a.KSPL, W - w0));
+  const int nst = (nkeys + kStrStage - 1) / kStrStage;
+  const int nkp = nst * kStrStage;
+  const int lds = nkp + 8;
+  const int m0 = sp * MQ;
+  const int nslots = max(0, min(MQ, M - m0));
+  const int nloads = 2 * nst;                                      // key stages, then value stages
+  bool failed = false;
+
+  if (tid == 0) {
+    for (int i = 0; i < kStrSlots + 1; ++i) umma::mbar_init(&bars[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // ring load j (j < nst: keys of stage j; else values of stage j - nst) into slot j % 4: 16-byte asynchronous
+  // copies, a thread always copies the same 16-byte column of rows 256 / (D / 8) apart, so the address
+  // arithmetic is one add per copy; rows past the end of the split are zero-filled.  One commit group per
+  // load and thread: groups complete in order, which is the order the stages are consumed in.
+  constexpr int kC8 = D / 8;                                       // 16-byte columns of a row
+  constexpr int kRStep = kStrThreads / kC8;                        // rows between two copies of a thread
+  const int lc = tid % kC8, lr = tid / kC8;
+#define NHA_ISSUE_LOAD(j_)                                                                          \
+  do {                                                                                              \
+    const int j__ = (j_);                                                                           \
+    const int st__ = j__ < nst ? j__ : j__ - nst;                                                   \
+    const bf16* src__ = (j__ < nst ? a.sw_k : a.sw_v) +                                             \
+                        (((size_t)b * W + w0 + st__ * kStrStage) * a.H + h) * D + 8 * lc;           \
+    unsigned char* dst__ = ring + (j__ % kStrSlots) * kSlotBytes + 16 * lc;                         \
+    const int rows__ = min(kStrStage, nkeys - st__ * kStrStage);                                    \
+    _Pragma("unroll") for (int r__ = lr; r__ < kStrStage; r__ += kRStep) {                          \
+      const bool ok__ = r__ < rows__;                                                               \
+      umma::cp16(dst__ + r__ * ldk * 2, src__ + (size_t)(ok__ ? r__ : 0) * a.H * D, ok__);          \
+    }                                                                                               \
+    umma::cp_commit();                                                                              \
+  } while (0)
+// wait until ring load j_ has landed: the loads issued after it may stay in flight
+#define NHA_WAIT_LOAD(j_, issued_)                                                                  \
+  do {                                                                                              \
+    const int pend__ = (issued_) - (j_) - 1;                                                        \
+    if (pend__ >= 3) asm volatile("cp.async.wait_group 3;\n" ::);                                   \
+    else if (pend__ == 2) asm volatile("cp.async.wait_group 2;\n" ::);                              \
+    else if (pend__ == 1) asm volatile("cp.async.wait_group 1;\n" ::);                              \
+    else asm volatile("cp.async.wait_group 0;\n" ::);                                               \
+  } while (0)
+
+  // ---- everything that fits goes in flight: the first ring loads and my rows of hv -----------------------
+  for (int j = 0; j < min(nloads, kStrSlots); ++j) NHA_ISSUE_LOAD(j);
+  if (nslots > 0 && !a.zero_state && tid == 0) {
+    mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);
+    bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);
+  }
+  // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = warp + 8 j.  The first
+  // block of columns (all of them unless the split owns more than 32 slots) is fetched now.
+  constexpr int kRowsPer = K / kStrWarps;
+  float hreg[kRowsPer];
+  const int ncb = (nslots + 31) / 32;
+  if (!a.zero_state && nslots > 0) {
+#pragma unroll
+    for (int j = 0; j < kRowsPer; ++j)
+      hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + warp + kStrWarps * j) * M + m0 + lane] : 0.f;
+  }
+  // ---- the popped token, the gates and the queries: disjoint groups of threads, so that the loads of the four
+  //      small inputs overlap instead of queueing behind one another --------------------------------------------
+  if (tid < 64) {
+    for (int m = tid; m < MQ; m += 64) {
+      float e = 1.f, sm = 0.f;
+      if (m < nslots) {
+        e = __expf(bf2f(a.g[(size_t)bh * M + m0 + m]));
+        sm = a.s ? bf2f(a.s[(size_t)bh * M + m0 + m]) : 1.0f - e;
+      }
+      eg[m] = e;
+      sv[m] = sm;
+    }
+  } else if (tid < 96) {
+    for (int i = tid - 64; i < (K >> 3); i += 32) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(a.k + (size_t)bh * K + 8 * i), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) kpop[8 * i + e] = f[e];
+    }
+  } else if (tid < 128) {
+    for (int i = tid - 96; i < (V >> 3); i += 32) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(a.v + (size_t)bh * V + 8 * i), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vpop[8 * i + e] = f[e];
+    }
+  } else {
+    constexpr int c8h = K >> 4;
+    const bf16* cq = rotary ? a.cosp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row : nullptr;
+    const bf16* sn = rotary ? a.sinp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row : nullptr;
+    for (int i = tid - 128; i < 16 * c8h; i += 128) {
+      const int r = i / c8h, c = i - r * c8h;
+      uint4 o1 = make_uint4(0u, 0u, 0u, 0u), o2 = o1;
+      if (r < NG) {
+        const bf16* qrow = a.q + ((size_t)b * a.HQ + h * NG + r) * K;
+        const uint4 xu = *reinterpret_cast<const uint4*>(qrow + 8 * c);
+        const uint4 yu = *reinterpret_cast<const uint4*>(qrow + 8 * (c + c8h));
+        if (rotary) {
+          const uint4 c1u = *reinterpret_cast<const uint4*>(cq + 8 * c), s1u = *reinterpret_cast<const uint4*>(sn + 8 * c);
+          const uint4 c2u = *reinterpret_cast<const uint4*>(cq + 8 * (c + c8h));
+          const uint4 s2u = *reinterpret_cast<const uint4*>(sn + 8 * (c + c8h));
+          float x[8], y[8], c1[8], s1[8], c2[8], s2[8], p1[8], p2[8];
+          unpack8(xu, x); unpack8(yu, y);
+          unpack8(c1u, c1); unpack8(s1u, s1); unpack8(c2u, c2); unpack8(s2u, s2);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            p1[e] = x[e] * c1[e] - y[e] * s1[e];
+            p2[e] = y[e] * c2[e] + x[e] * s2[e];
+          }
+          o1 = pack8(p1); o2 = pack8(p2);
+        } else {
+          const bf16* srow = a.sq + ((size_t)b * a.HQ + h * NG + r) * K;
+          o1 = *reinterpret_cast<const uint4*>(srow + 8 * c);
+          o2 = *reinterpret_cast<const uint4*>(srow + 8 * (c + c8h));
+        }
+        *reinterpret_cast<uint4*>(qs + r * K + 8 * c) = xu;
+        *reinterpret_cast<uint4*>(qs + r * K + 8 * (c + c8h)) = yu;
+      }
+      *reinterpret_cast<uint4*>(sqA + r * ldq + 8 * c) = o1;
+      *reinterpret_cast<uint4*>(sqA + r * ldq + 8 * (c + c8h)) = o2;
+    }
+  }
+  __syncthreads();
+
+  // ---- my columns of hk <- hk exp(g) + k s^T (registers -> global), partial slot logits of every query head ----
+  for (int cb = 0; cb < ncb; ++cb) {
+    const int m = 32 * cb + lane;
+    if (cb > 0 && !a.zero_state) {
+#pragma unroll
+      for (int j = 0; j < kRowsPer; ++j)
+        hreg[j] = m < nslots ? a.hk[((size_t)bh * K + warp + kStrWarps * j) * M + m0 + m] : 0.f;
+    }
+    const float e = m < MQ ? eg[m] : 1.f, sm = m < MQ ? sv[m] : 0.f;
+    float acc[16];
+#pragma unroll
+    for (int qh = 0; qh < 16; ++qh) acc[qh] = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowsPer; ++j) {
+      const int kk = warp + kStrWarps * j;
+      const float hval = (a.zero_state ? 0.f : hreg[j]) * e + kpop[kk] * sm;
+      if (m < nslots) a.hk[((size_t)bh * K + kk) * M + m0 + m] = hval;
+#pragma unroll
+      for (int qh = 0; qh < 16; ++qh)
+        if (qh < NG) acc[qh] += bf2f(qs[qh * K + kk]) * hval;
+    }
+#pragma unroll
+    for (int qh = 0; qh < 16; ++qh)
+      if (qh < NG) red[(warp * NG + qh) * 32 + lane] = acc[qh];
+    __syncthreads();
+    for (int i = tid; i < NG * 32; i += kStrThreads) {
+      const int qh = i >> 5, l = i & 31;
+      float sum = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < kStrWarps; ++w8) sum += red[(w8 * NG + qh) * 32 + l];
+      if (32 * cb + l < MQ) oks[qh * MQ + 32 * cb + l] = sum * a.scale;
+    }
+    __syncthreads();
+  }
+
+  // ---- key stages: wait, rotate-half in place, S = sq K^T; the freed slot takes the next ring load ------------
+  constexpr int c8h = K >> 4;
+  constexpr int kTasks = kStrStage * c8h / kStrThreads;            // rotary tasks per thread (8 values x 2 halves each)
+  uint4 cs[kTasks][4];                                             // rotate-half table entries of the stage being rotated
+  for (int st = 0; st < nst; ++st) {
+    const int slot = st % kStrSlots;
+    bf16* kst = reinterpret_cast<bf16*>(ring + slot * kSlotBytes);
+    if (rotary && st == 0) {
+#pragma unroll
+      for (int u = 0; u < kTasks; ++u) {
+        const int i = tid + u * kStrThreads;
+        const int r = i / c8h, c = i - r * c8h;
+        const int wpos = min(w0 + r, W - 1);
+        const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
+        const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
+        cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));
+        cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));
+        cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));
+        cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));
+      }
+    }
+    NHA_WAIT_LOAD(st, min(nloads, kStrSlots + st));
+    __syncthreads();                                               // every thread's copies of the stage have landed
+    if (rotary) {
+#pragma unroll
+      for (int u = 0; u < kTasks; ++u) {
+        const int i = tid + u * kStrThreads;
+        const int r = i / c8h, c = i - r * c8h;
+        float x[8], y[8], c1[8], s1[8], c2[8], s2[8], o1[8], o2[8];
+        unpack8(*reinterpret_cast<const uint4*>(kst + r * ldk + 8 * c), x);
+        unpack8(*reinterpret_cast<const uint4*>(kst + r * ldk + 8 * (c + c8h)), y);
+        unpack8(cs[u][0], c1); unpack8(cs[u][1], s1); unpack8(cs[u][2], c2); unpack8(cs[u][3], s2);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          o1[e] = x[e] * c1[e] - y[e] * s1[e];
+          o2[e] = y[e] * c2[e] + x[e] * s2[e];
+        }
+        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * c) = pack8(o1);
+        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * (c + c8h)) = pack8(o2);
+      }
+      if (st + 1 < nst) {
+        // the next stage's table entries travel while this stage's logits are formed
+#pragma unroll
+        for (int u = 0; u < kTasks; ++u) {
+          const int i = tid + u * kStrThreads;
+          const int r = i / c8h, c = i - r * c8h;
+          const int wpos = min(w0 + (st + 1) * kStrStage + r, W - 1);
+          const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
+          const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
+          cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));
+          cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));
+          cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));
+          cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));
+        }
+      }
+    }
+    __syncthreads();
+    if (warp < kStrStage / 16) {
+      fragment<accumulator, 16, 16, 16, float> acc;
+      fill_fragment(acc, 0.f);
+#pragma unroll
+      for (int ks = 0; ks < K / 16; ++ks) {
+        fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
+        fragment<matrix_b, 16, 16, 16, bf16, col_major> fb;
+        load_matrix_sync(fa, sqA + 16 * ks, ldq);
+        load_matrix_sync(fb, kst + (size_t)16 * warp * ldk + 16 * ks, ldk);
+        mma_sync(acc, fa, fb, acc);
+      }
+      store_matrix_sync(S + st * kStrStage + 16 * warp, acc, lds, mem_row_major);
+    }
+    __syncthreads();
+    if (st + kStrSlots < nloads) NHA_ISSUE_LOAD(st + kStrSlots);
+  }
+
+  // ---- partial softmax over [my slots | my keys], one warp per query head; weights replace the logits in place ---
+  for (int qh = warp; qh < NG; qh += kStrWarps) {
+    float* srow = S + (size_t)qh * lds;
+    bf16* prow = reinterpret_cast<bf16*>(srow);
+    float mx = -INFINITY;
+    for (int m = lane; m < nslots; m += 32) mx = fmaxf(mx, oks[qh * MQ + m]);
+    for (int w = lane; w < nkeys; w += 32) mx = fmaxf(mx, srow[w] * a.scale);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int m = lane; m < nslots; m += 32) {
+      const float e = __expf(oks[qh * MQ + m] - mx);
+      oks[qh * MQ + m] = e;
+      sum += e;
+    }
+    // the bf16 weight of key w lands inside the fp32 logit of key w / 2: convert 32 keys at a time, reading
+    // all of them before any is written
+    for (int w32 = 0; w32 < nkp; w32 += 32) {
+      const int w = w32 + lane;
+      const float e = w < nkeys ? __expf(srow[w] * a.scale - mx) : 0.f;
+      sum += e;
+      __syncwarp();
+      prow[w] = f2bf(e);
+      __syncwarp();
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      ml[2 * qh] = (nslots + nkeys) > 0 ? mx : -INFINITY;
+      ml[2 * qh + 1] = sum;
+    }
+  }
+  __syncthreads();
+
+  // ---- value stages: O += P V, one 16-column tile of the output per warp, accumulated in registers -------------
+  fragment<accumulator, 16, 16, 16, float> oacc;
+  fill_fragment(oacc, 0.f);
+  const bf16* P = reinterpret_cast<const bf16*>(S);
+  const int ldp = 2 * lds;
+  for (int st = 0; st < nst; ++st) {
+    const int j = nst + st, slot = j % kStrSlots;
+    const bf16* vst = reinterpret_cast<const bf16*>(ring + slot * kSlotBytes);
+    NHA_WAIT_LOAD(j, min(nloads, kStrSlots + j));
+    __syncthreads();
+    if (warp < V / 16) {
+#pragma unroll
+      for (int kt = 0; kt < kStrStage / 16; ++kt) {
+        fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
+        fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+        load_matrix_sync(fa, P + st * kStrStage + 16 * kt, ldp);
+        load_matrix_sync(fb, vst + (size_t)16 * kt * ldk + 16 * warp, ldk);
+        mma_sync(oacc, fa, fb, oacc);
+      }
+    }
+    if (j + kStrSlots < nloads) {
+      __syncthreads();                                             // every warp is done with the slot
+      NHA_ISSUE_LOAD(j + kStrSlots);
+    }
+  }
+#undef NHA_ISSUE_LOAD
+#undef NHA_WAIT_LOAD
+  __syncthreads();                                                 // the logits / weights and the ring are dead
+  float* osm = reinterpret_cast<float*>(ring);                     // [16][V+8] window part of the output
+  if (warp < V / 16) store_matrix_sync(osm + 16 * warp, oacc, ldo, mem_row_major);
+
+  // ---- my rows of hv <- diag(exp(g)) hv + s v^T (in place), slot readout -----------------------------------------
+  constexpr int V4 = V >> 2;
+  if (nslots > 0) {
+    if (!a.zero_state && !umma::mbar_wait(&bars[kStrSlots], 0)) failed = true;
+    float4* hg = reinterpret_cast<float4*>(a.hv + ((size_t)bh * M + m0) * V);
+    for (int i = tid; i < nslots * V4; i += kStrThreads) {
+      const int m = i / V4, c = i - m * V4;
+      float4 hh = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+      const float4 vp4 = *reinterpret_cast<const float4*>(vpop + 4 * c);
+      const float e = eg[m], sm = sv[m];
+      hh.x = hh.x * e + sm * vp4.x;
+      hh.y = hh.y * e + sm * vp4.y;
+      hh.z = hh.z * e + sm * vp4.z;
+      hh.w = hh.w * e + sm * vp4.w;
+      *reinterpret_cast<float4*>(hvS + m * V + 4 * c) = hh;
+      hg[i] = hh;
+    }
+  }
+  __syncthreads();
+  // partial output of this split: slot part + window part, unnormalised
+  float* po = a.part_o + ((size_t)bh * SPL + sp) * NG * V;
+  for (int i = tid; i < NG * V4; i += kStrThreads) {
+    const int qh = i / V4, c = i - qh * V4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int m = 0; m < nslots; ++m) {
+      const float pm = oks[qh * MQ + m];
+      const float4 hh = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+      acc.x += pm * hh.x; acc.y += pm * hh.y; acc.z += pm * hh.z; acc.w += pm * hh.w;
+    }
+    if (nkeys > 0) {
+      const float4 wv = *reinterpret_cast<const float4*>(osm + qh * ldo + 4 * c);
+      acc.x += wv.x; acc.y += wv.y; acc.z += wv.z; acc.w += wv.w;
+    }
+    if (SPL == 1) {
+      const float inv = 1.0f / ml[2 * qh + 1];
+      bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
+      orow[0] = f2bf(acc.x * inv); orow[1] = f2bf(acc.y * inv); orow[2] = f2bf(acc.z * inv); orow[3] = f2bf(acc.w * inv);
+    } else {
+      *reinterpret_cast<float4*>(po + qh * V + 4 * c) = acc;
+    }
+  }
+  if (failed && tid == 0 && a.err) atomicExch(a.err, 1);
+  if (SPL == 1) return;
+
+  // ---- merge: the last split of this (sequence, kv head) to arrive combines all partials ------------
+  float* pml = a.part_ml + ((size_t)bh * SPL + sp) * NG * 2;
+  for (int i = tid; i < NG * 2; i += kStrThreads) pml[i] = ml[i];
+  __syncthreads();
+  __shared__ int s_last;
+  if (tid == 0) {
+    __threadfence();                    // the partials of this CTA are visible before its ticket
+    const int t = atomicAdd(a.tickets + bh, 1);
+    s_last = (t == SPL - 1);
+    if (s_last) a.tickets[bh] = 0;      // leave the counter at zero for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* all_ml = a.part_ml + (size_t)bh * SPL * NG * 2;
+  float* wgt = red;                     // [SPL][NG] merge weights exp(m_s - m) / denominator
+  for (int qh = tid; qh < NG; qh += kStrThreads) {
+    float mx = -INFINITY;
+    for (int s2 = 0; s2 < SPL; ++s2) mx = fmaxf(mx, __ldcg(all_ml + ((size_t)s2 * NG + qh) * 2));
+    float den = 0.f;
+    for (int s2 = 0; s2 < SPL; ++s2) {
+      const float m2 = __ldcg(all_ml + ((size_t)s2 * NG + qh) * 2);
+      const float l2 = __ldcg(all_ml + ((size_t)s2 * NG + qh) * 2 + 1);
+      den += m2 > -INFINITY ? l2 * __expf(m2 - mx) : 0.f;
+    }
+    for (int s2 = 0; s2 < SPL; ++s2) {
+      const float m2 = __ldcg(all_ml + ((size_t)s2 * NG + qh) * 2);
+      wgt[s2 * NG + qh] = m2 > -INFINITY ? __expf(m2 - mx) / den : 0.f;
+    }
+  }
+  __syncthreads();
+  const float* all_o = a.part_o + (size_t)bh * SPL * NG * V;
+  for (int i = tid; i < NG * V4; i += kStrThreads) {
+    const int qh = i / V4, c = i - qh * V4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = 0; s2 < SPL; ++s2) {
+      const float wq = wgt[s2 * NG + qh];
+      const float4 pv = __ldcg(reinterpret_cast<const float4*>(all_o + ((size_t)s2 * NG + qh) * V + 4 * c));
+      acc.x += wq * pv.x; acc.y += wq * pv.y; acc.z += wq * pv.z; acc.w += wq * pv.w;
+    }
+    bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
+    orow[0] = f2bf(acc.x); orow[1] = f2bf(acc.y); orow[2] = f2bf(acc.z); orow[3] = f2bf(acc.w);
+  }
+}
+
+static int stream_layout(DecodeStreamArgs& a, int D, int nkp) {
+  const int NG = a.NG, MQ = a.MQ;
+  int off = 0;
+  auto take = [&](int bytes) { int o = off; off = (off + bytes + 127) / 128 * 128; return o; };
+  a.off_ring = take(kStrSlots * kStrStage * (D + 8) * 2);
+  a.off_hv = take(MQ * D * 4);
+  const int s_bytes = 16 * (nkp + 8) * 4, red_bytes = kStrWarps * NG * 32 * 4;
+  a.off_S = take(s_bytes > red_bytes ? s_bytes : red_bytes);
+  a.off_red = a.off_S;                               // the partial slot logits are summed before the first S tile lands
+  a.off_q = take(NG * D * 2);
+  a.off_sqA = take(16 * (D + 8) * 2);
+  a.off_oks = take(NG * MQ * 4);
+  a.off_eg = take(MQ * 4);
+  a.off_sv = take(MQ * 4);
+  a.off_kpop = take(D * 4);
+  a.off_vpop = take(D * 4);
+  a.off_ml = take(NG * 2 * 4);
+  a.off_bar = take((kStrSlots + 1) * 8);
+  return off;
+}
+
+// Splits of a (sequence, kv head) for the streaming kernel: as many as keep the whole grid in one wave of two
+// CTAs per SM, each split keeping at least 64 keys and 4 slots.
+int decode_stream_splits(int B, int H, int W, int M) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int spl = 1;
+  while (spl < 16 && (int64_t)B * H * spl * 2 <= 2 * (int64_t)sms && W / (spl * 2) >= kStrStage && M / (spl * 2) >= 4 &&
+         M % (spl * 2 * 4) == 0)
+    spl *= 2;
+  return spl;
+}
+
+bool decode_stream_supported(int K, int V, int M, int W, int NG, bool logits_mode) {
+  return !logits_mode && K == V && (K == 64 || K == 128) && M % 4 == 0 && M <= 128 && NG <= 16 && W >= 1;
+}
+
+// The caller has checked decode_stream_supported() and sized the workspace for `splits`.
+int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
+  DecodeStreamArgs a = in;
+  a.KSPL = ((a.W + a.SPLITS - 1) / a.SPLITS + kStrStage - 1) / kStrStage * kStrStage;
+  a.MQ = ((a.M + a.SPLITS - 1) / a.SPLITS + 3) / 4 * 4;
+  const int nkp = a.KSPL;
+  const int smem = stream_layout(a, D, nkp);
+  if (smem > kMaxSmem) return NHA_ERR_SMEM;
+  dim3 grid(a.B * a.H * a.SPLITS), block(kStrThreads);
+  cudaError_t e;
+  if (D == 128) {
+    e = cudaFuncSetAttribute(nha_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    nha_decode_stream_kernel<128><<<grid, block, smem, st>>>(a);
+  } else {
+    e = cudaFuncSetAttribute(nha_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    nha_decode_stream_kernel<64><<<grid, block, smem, st>>>(a);
+  }
+  return check_launch();
+}
+
+// Runs the streaming kernel when the shape has one; *used tells the caller whether it did.
+int decode_stream_try(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
+                      const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
+                      int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
+                      float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
+                      cudaStream_t st) {
+  DecodeStreamArgs a;
+  a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
+  a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
+  a.sinp = (const bf16*)sinp;
+  a.hk = hk; a.hv = hv; a.o = (bf16*)o;
+  a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.err = err;
+  a.cs_batch = cs_batch; a.cs_row = cs_row;
+  a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
+  a.zero_state = zero_state; a.scale = scale;
+  return decode_stream_launch(a, D, st);
+}
+
+}  // namespace nha

@@ -24,11 +24,11 @@ _WORKSPACES = {}
 
 
 def _decode_workspace(device, B, HQ, H, V, W):
-    """Zero-initialised scratch for the split decode kernel, one per (device, stream); the kernel
-    leaves its counters at zero, so the buffer is reused by later calls on the same stream."""
+    """Zero-initialised scratch for the split decode kernels, one per (device, stream, B * H); the
+    kernels leave their counters at zero, so the buffer is reused by later calls on the same stream."""
     lib = _lib.load()
     need = int(lib.nha_decode_workspace_bytes(B, HQ, H, V, W))
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, B * H)   # the layout depends on B * H
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(need, dtype=torch.uint8, device=device)
