@@ -179,11 +179,13 @@ int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
 int64_t nha_chunk_state_pass_static_max_bytes(void);
 int nha_chunk_state_pass_static(const nha_chunk_desc* d, void* stream);
 
-/* one stage of nha_chunk_bwd on its own, so a harness can time each kernel with events on the
-   launching stream: 0 = window rows (delta, joint LSE, dq_swa), 1 = window columns (dk_swa, window
-   part of dv), 2 = slot pass (dq_gsa, intra-chunk parts), 3 = reverse march (dk_gsa, dv, ds, dg,
-   dhk0/dhv0).  The stages of one backward must run in this order; running all four equals
-   nha_chunk_bwd.  No counterpart in the reference (it has no timing hooks). */
+/* one stage of nha_chunk_bwd on its own, so a harness can time each part with events on the
+   launching stream: 0 = query-row side (delta, joint LSE, dq_gsa, dq_swa, gate terms, bf16 copies of
+   dz and p, the chunks' own state-gradient terms), 1 = key side of the window (dk_swa, window part
+   of dv), 2 = general slot kernel (chunks flagged by the forward only), 3 = scan of the state
+   gradients over the chunks (dhk0/dhv0), 4 = gate carry and key-row side of the slot branch
+   (dk_gsa, dv, ds, dg).  The stages of one backward must run in this order; running all five
+   equals nha_chunk_bwd.  No counterpart in the reference (it has no timing hooks). */
 int nha_chunk_bwd_stage(const nha_chunk_desc* d, int stage, void* stream);
 
 #ifdef __cplusplus

@@ -1022,6 +1022,8 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     nha_bwd_state_scan_kernel<<<dim3((SD / 4 + 255) / 256, d->N * d->H), 256, 0, cs>>>(*d, w);
     st = check_launch();
     if (st != NHA_OK) return st;
+  }
+  if (stage_mask & 16) {
     if (umma) {
       st = bwd_umma_launch(d, wu, 1, err, cs);
       if (st != NHA_OK) return st;
@@ -1032,9 +1034,9 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   return st;
 }
 
-extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) { return bwd_run(d, 15, stream); }
+extern "C" int nha_chunk_bwd(const nha_chunk_desc* d, void* stream) { return bwd_run(d, 31, stream); }
 
 extern "C" int nha_chunk_bwd_stage(const nha_chunk_desc* d, int stage, void* stream) {
-  if (stage < 0 || stage > 3) return NHA_ERR_BAD_ARG;
+  if (stage < 0 || stage > 4) return NHA_ERR_BAD_ARG;
   return bwd_run(d, 1 << stage, stream);
 }

@@ -125,3 +125,29 @@ def test_decode_headline_shape():
     assert_close(o, ref[0], TOL_OUT, 'o')
     assert_close(hk, ref[1], 1e-5, 'hkt')
     assert_close(hv, ref[2], 1e-5, 'hvt')
+
+
+@pytest.mark.parametrize('B', [1, 3, 40])
+def test_decode_general_kernel_matches_streaming_kernel(B, monkeypatch):
+    """K == V in {64, 128} normally takes the streaming kernel; NHA_B200_DECODE_GENERAL=1 forces the
+    general one.  Both must agree with the oracle on the headline layer shape at batch sizes that give
+    different split counts (few sequences: many splits per kv head; many: none)."""
+    from nha_b200 import fused_recurrent_nha_decode
+    H, NG, K, M, W = 4, 8, 128, 64, 512
+    d = gen.decode_inputs(70 + B, B, H, NG, K, K, M, W)
+    d['cos'], d['sin'] = gen.rope_tables(W, K, first_pos=32768 - W + 1)
+    ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'],
+                          sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    c = cuda(d)
+    outs = []
+    for force in ('0', '1'):
+        monkeypatch.setenv('NHA_B200_DECODE_GENERAL', force)
+        o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'],
+                                                 sw_v=c['vw'], cos=c['cos'], sin=c['sin'],
+                                                 initial_state=(c['hk0'].clone(), c['hv0'].clone()),
+                                                 output_final_state=True)
+        assert_close(o, ref[0], TOL_OUT, f'o (general={force})')
+        assert_close(hk, ref[1], 1e-5, f'hkt (general={force})')
+        assert_close(hv, ref[2], 1e-5, f'hvt (general={force})')
+        outs.append(o.float())
+    assert (outs[0] - outs[1]).abs().max() < 2e-2
