@@ -1,8 +1,8 @@
 // Output pass of the chunked NHA forward on the sm_100a tensor-core path: tcgen05.mma with operands in
-// 128-byte-swizzled shared memory, accumulators in tensor memory (TMEM), two threads per query row
-// for the softmax: tcgen05.ld hands a thread 32 columns of its row, the two warps that share a TMEM
-// lane quarter (warp w and w + 4) take alternate halves of the columns and swap row maxima and sums
-// through shared memory.  Eight warps per CTA keep the element-wise phases, which are bound by
+// 128-byte-swizzled shared memory, accumulators in tensor memory (TMEM), two (D = 64) or four (D = 128)
+// threads per query row for the softmax: tcgen05.ld hands a thread 32 or 16 columns of its row, the warps
+// that share a TMEM lane quarter (w, w + 4, ...) take alternate parts of the columns and combine row maxima
+// and sums through shared memory.  Eight or sixteen warps per CTA keep the element-wise phases, which are bound by
 // instruction issue, from stalling on their own dependencies.  One CTA per (chunk, kv head); an MMA tile is 64 tokens x 1 head (R = 64, for
 // HQ == H) or 64 tokens x 2 heads of the group (R = 128), and the CTA walks the heads of the group
 // reusing the chunk's k', v', gates and chunk-start states.
@@ -31,13 +31,14 @@ namespace nha {
 
 using namespace umma;
 
-constexpr int kUThreads = 256;
 constexpr float kUmmaDecayLimit = 140.0f;
 
 template <int D, int R>
 struct UmmaLayout {
   static constexpr int KT = D / 64;
   static constexpr int TP = D == 64 ? 2 : 1;          // 64-key tiles per window step
+  static constexpr int NS = D == 64 ? 2 : 4;          // threads per row (D = 128 runs one CTA per SM: more warps)
+  static constexpr int kThreads = 128 * NS;
   static constexpr int kATile = R * 128;              // one 64-wide k tile of an R-row A operand
   static constexpr int kWTile = TP * 8192;            // one 64-wide k tile of a window-step operand (64 TP rows)
   static constexpr bool kAlias = R == 64;             // one head per CTA: k' and Hk are dead after round 1
@@ -59,8 +60,8 @@ struct UmmaLayout {
   static constexpr int end2 = kAlias ? end1 : end1 + 2 * kATile;
   static constexpr int oA = end2;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
   static constexpr int oR = oA + 64 * 65 * 4;         // fp32 [64] exp(R)
-  static constexpr int oX = oR + 256;                 // fp32 [4][2][128] row statistics swapped between the column halves
-  static constexpr int oBar = oX + 4096;              // mbarrier + TMEM slot
+  static constexpr int oX = oR + 256;                 // fp32 [4][NS][128] row statistics swapped between the column parts
+  static constexpr int oBar = oX + 4 * NS * 128 * 4;              // mbarrier + TMEM slot
   static constexpr int total = oBar + 64 + 1024;      // + slack for the 1024-byte alignment of the base
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
   // O reuses QH's columns at D = 64 (QH has been read by then)
@@ -69,10 +70,14 @@ struct UmmaLayout {
 };
 
 template <int D, int R>
-__global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
+__global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 64) ? 2 : 1) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
                                                                   int* __restrict__ err) {
   typedef UmmaLayout<D, R> L;
   constexpr int KT = L::KT, TH = R / 64, M = 64, TP = L::TP, WK = 64 * TP;
+  constexpr int NS = L::NS, kUThreads = L::kThreads;
+  constexpr int CW = 64 / NS;                       // columns of a 64-column accumulator per thread
+  constexpr int KW = WK / NS;                       // keys of a window step per thread
+  constexpr int LW = KW < 32 ? KW : 32;             // columns per tensor-memory load of the window logits
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
@@ -148,23 +153,24 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
   }
   if (tid == 0) mbar_init(mbar, 1);
   __syncthreads();
-  // inclusive scan along the rows: four threads per column (16 rows each), then the totals of the earlier
-  // quarters are added
+  // inclusive scan along the rows: kUThreads / 64 threads per column (a segment of rows each), then the totals
+  // of the earlier segments are added
   {
+    constexpr int NSEG = kUThreads / 64, RS = 64 / NSEG;
     const int m = tid & 63, seg = tid >> 6;
     float run = 0.f;
 #pragma unroll
-    for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
+    for (int r = RS * seg; r < RS * seg + RS; ++r) {
       run += As[r * 65 + m];
       As[r * 65 + m] = run;
     }
     __syncthreads();
     float add = 0.f;
-    for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * 65 + m];
+    for (int s2 = 0; s2 < seg; ++s2) add += As[(RS * s2 + RS - 1) * 65 + m];
     __syncthreads();                                  // every total is read before any of them changes
     if (seg > 0) {
 #pragma unroll
-      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * 65 + m] += add;
+      for (int r = RS * seg; r < RS * seg + RS; ++r) As[r * 65 + m] += add;
     }
     __syncthreads();
   }
@@ -207,19 +213,19 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const int quarter = warp & 3, half = warp >> 2;   // TMEM lane quarter of this warp; column half it works on
+  const int quarter = warp & 3, cpart = warp >> 2;  // TMEM lane quarter of this warp; column part it works on
   const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
   uint32_t phase = 0;
   bool failed = false;
 
-  // row of this thread inside the tile (two threads, one per column half, share a row)
+  // row of this thread inside the tile (NS threads, one per column part, share a row)
   const bool active = R == 128 ? true : lane < 16;
   const int row = R == 128 ? quarter * 32 + lane : quarter * 16 + (lane & 15);
   const int tk = row & 63;                          // token inside the chunk
   const int th = row >> 6;                          // head inside the tile
   const int pos = c0 + tk;
   const bool in_seq = pos < len;
-  float* xch = (float*)(sm + L::oX);                // [4 exchange points][2 halves][128 rows]
+  float* xch = (float*)(sm + L::oX);                // [4 exchange points][NS parts][128 rows]
   // visible keys of this row: klo <= key <= pos, tested as (unsigned)(key - klo) <= kspan; a row past the
   // sequence end sees nothing
   constexpr float kLog2e = 1.4426950408889634f;
@@ -245,34 +251,34 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
     __syncthreads();                                     \
     tc_fence_after();                                    \
   } while (0)
-// this thread's half of tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 A-operand tile
+// this thread's part of tril of a [R][64] accumulator (row token tk keeps columns i <= tk) -> bf16 A-operand tile
 #define NHA_TRIL_TO_SMEM(col0, dst_off)                                                          \
   do {                                                                                           \
-    float tv_[32];                                                                               \
-    tmem_ld32(tlane + (col0) + 32 * half, tv_);                                                  \
+    float tv_[CW];                                                                               \
+    tmem_ldw<CW>(tlane + (col0) + CW * cpart, tv_);                                              \
     if (active) {                                                                                \
-      _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                         \
+      _Pragma("unroll") for (int c8 = 0; c8 < CW / 8; ++c8) {                                    \
         float o8[8];                                                                             \
         _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                          \
-          const int i_ = 32 * half + 8 * c8 + e;                                                 \
+          const int i_ = CW * cpart + 8 * c8 + e;                                                \
           o8[e] = i_ <= tk ? tv_[8 * c8 + e] : 0.f;                                              \
         }                                                                                        \
-        *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, 4 * half + c8)) = pack8(o8);      \
+        *reinterpret_cast<uint4*>(sm + (dst_off) + sw_off(row, (CW / 8) * cpart + c8)) = pack8(o8); \
       }                                                                                          \
     }                                                                                            \
   } while (0)
 // S = q_swa (window keys of one step)^T
 #define NHA_ISSUE_S() mma_tile(tbase + L::cS, aQS, L::kATile, aW, L::kWTile, R, WK, D / 16, 0, false)
-// this thread's 32 TP keys of a window step: keys kb_ + 32 TP half + [0, 32 TP)
+// this thread's KW keys of a window step: keys kb_ + KW cpart + [0, KW)
 #define NHA_STEP_MAX(kb_)                                                                        \
   do {                                                                                           \
-    float sv_[32];                                                                               \
-    _Pragma("unroll") for (int pp = 0; pp < TP; ++pp) {                                          \
-      const int part = TP * half + pp;                                                           \
-      tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
-      const int off_ = (kb_) + 32 * part - klo;                                                  \
+    float sv_[LW];                                                                               \
+    _Pragma("unroll") for (int pp = 0; pp < KW / LW; ++pp) {                                     \
+      const int key0 = KW * cpart + LW * pp;                                                     \
+      tmem_ldw<LW>(tlane + L::cS + key0, sv_);                                                   \
+      const int off_ = (kb_) + key0 - klo;                                                       \
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};                                \
-      _Pragma("unroll") for (int e = 0; e < 32; ++e)                                             \
+      _Pragma("unroll") for (int e = 0; e < LW; ++e)                                             \
         m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off_ + e) <= kspan ? sv_[e] : -INFINITY);        \
       ms = fmaxf(ms, d.scale * fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));                 \
     }                                                                                            \
@@ -280,15 +286,15 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
 // P~ = exp(scale S - ms) cw of this thread's keys of a step, into the swizzled tile; row sum into ls
 #define NHA_STEP_PROB(kb_)                                                                       \
   do {                                                                                           \
-    float sv_[32];                                                                               \
+    float sv_[LW];                                                                               \
     const float nms_ = -ms * kLog2e;                                                             \
-    _Pragma("unroll") for (int pp = 0; pp < TP; ++pp) {                                          \
-      const int part = TP * half + pp;                                                           \
-      tmem_ld32(tlane + L::cS + 32 * part, sv_);                                                 \
-      const int off_ = (kb_) + 32 * part - klo;                                                  \
+    _Pragma("unroll") for (int pp = 0; pp < KW / LW; ++pp) {                                     \
+      const int key0 = KW * cpart + LW * pp;                                                     \
+      tmem_ldw<LW>(tlane + L::cS + key0, sv_);                                                   \
+      const int off_ = (kb_) + key0 - klo;                                                       \
       if (active) {                                                                              \
         float l4[4] = {0.f, 0.f, 0.f, 0.f};                                                      \
-        _Pragma("unroll") for (int c8 = 0; c8 < 4; ++c8) {                                       \
+        _Pragma("unroll") for (int c8 = 0; c8 < LW / 8; ++c8) {                                  \
           float o8[8];                                                                           \
           _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                        \
             const float pe = (unsigned)(off_ + 8 * c8 + e) <= kspan                              \
@@ -296,8 +302,9 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
             l4[e & 3] += pe;                                                                     \
             o8[e] = pe * cw;                                                                     \
           }                                                                                      \
-          *reinterpret_cast<uint4*>(sm + L::tP + (part >> 1) * L::kATile +                       \
-                                    sw_off(row, 4 * (part & 1) + c8)) = pack8(o8);               \
+          const int kk_ = key0 + 8 * c8;                                                         \
+          *reinterpret_cast<uint4*>(sm + L::tP + (kk_ >> 6) * L::kATile +                        \
+                                    sw_off(row, (kk_ & 63) >> 3)) = pack8(o8);                   \
         }                                                                                        \
         ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);                                                 \
       }                                                                                          \
@@ -309,14 +316,17 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
     _Pragma("unroll") for (int ct = 0; ct < KT; ++ct)                                            \
       mma_tile(tbase + L::cO + 64 * ct, aP, L::kATile, aWV + ct * L::kWTile, 0, R, 64, 4 * TP, 1, true); \
   } while (0)
-// swap a row statistic with the thread that owns the other column half (slot_: exchange point 0..3);
+// combine a row statistic over the NS threads of the row (slot_: exchange point 0..3; OP_: fmaxf or addf);
 // the barrier inside is reached by every thread of the CTA
-#define NHA_SWAP(slot_, mine_, other_)                                                           \
+#define NHA_XCHG(slot_, v_, OP_)                                                                 \
   do {                                                                                           \
-    xch[((slot_) * 2 + half) * 128 + row] = (mine_);                                             \
+    xch[((slot_) * NS + cpart) * 128 + row] = (v_);                                              \
     __syncthreads();                                                                             \
-    (other_) = xch[((slot_) * 2 + (half ^ 1)) * 128 + row];                                      \
+    float r_ = xch[((slot_) * NS) * 128 + row];                                                  \
+    _Pragma("unroll") for (int p_ = 1; p_ < NS; ++p_) r_ = OP_(r_, xch[((slot_) * NS + p_) * 128 + row]); \
+    (v_) = r_;                                                                                   \
   } while (0)
+  auto addf = [](float x, float y) { return x + y; };
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
     const int hq0 = h * NG + ht * TH;
@@ -339,34 +349,30 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
     NHA_STEP_MAX(NHA_KBASE(nsteps - 1));
     NHA_MMA_WAIT();
     // ---- this thread's 32 slot logits ok = scale a .* (e^R .* QH + X), kept in registers --------------------------
-    float ok[32];
+    float ok[CW];
     float mg = -INFINITY;
     {
-      float qh[32];
-      tmem_ld32(tlane + L::cQH + 32 * half, qh);
-      tmem_ld32(tlane + L::cA + 32 * half, ok);
+      float qh[CW];
+      tmem_ldw<CW>(tlane + L::cQH + CW * cpart, qh);
+      tmem_ldw<CW>(tlane + L::cA + CW * cpart, ok);
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const int m = 32 * half + e;
+      for (int e = 0; e < CW; ++e) {
+        const int m = CW * cpart + e;
         const float v = d.scale * As[tk * 65 + m] * (ER[m] * qh[e] + ok[e]);
         ok[e] = v;
         m4[e & 3] = fmaxf(m4[e & 3], v);
       }
       mg = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
     }
-    {
-      float other;
-      NHA_SWAP(0, mg, other);
-      mg = fmaxf(mg, other);
-    }
+    NHA_XCHG(0, mg, fmaxf);
     float lg = 0.f;
     {
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       const float nmg = -mg * kLog2e;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
+      for (int e = 0; e < CW; ++e) {
         ok[e] = exp2f(fmaf(ok[e], kLog2e, nmg));      // from here on ok holds exp(ok - mg)
         l4[e & 3] += ok[e];
       }
@@ -387,27 +393,24 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
     }
     // ---- joint maximum; unnormalised slot probabilities as bf16 A operands -----------------------------------------
     tc_fence_before();
-    {
-      float other;
-      NHA_SWAP(1, ms, other);                         // its barrier also puts every thread past its reads of QH / X
-      ms = fmaxf(ms, other);                          // and of the products that read tQ
-    }
+    NHA_XCHG(1, ms, fmaxf);                           // its barrier also puts every thread past its reads of QH / X
+                                                      // and of the products that read tQ
     const float mx = fmaxf(mg, ms);
     const float cgs = __expf(mg - mx);               // slot entries:   p~ = exp(ok - mg) cgs
     const float cw = __expf(ms - mx);                // window entries: p~ = exp(s  - ms) cw
     if (active) {
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {
+      for (int c8 = 0; c8 < CW / 8; ++c8) {
         float pg8[8], pa8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int m = 32 * half + 8 * c8 + e;
+          const int m = CW * cpart + 8 * c8 + e;
           const float pa = in_seq ? ok[8 * c8 + e] * cgs * As[tk * 65 + m] : 0.f;
           pa8[e] = pa;
           pg8[e] = pa * ER[m];
         }
-        *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, 4 * half + c8)) = pack8(pg8);
-        *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, 4 * half + c8)) = pack8(pa8);
+        *reinterpret_cast<uint4*>(sm + L::tPG + sw_off(row, (CW / 8) * cpart + c8)) = pack8(pg8);
+        *reinterpret_cast<uint4*>(sm + L::tQ + sw_off(row, (CW / 8) * cpart + c8)) = pack8(pa8);
       }
     }
     NHA_SMEM_TO_MMA();
@@ -447,36 +450,36 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
       if (tid == 0) NHA_ISSUE_PV();
       NHA_MMA_WAIT();
     }
-    // ---- row sums of both halves, normalise and store ----------------------------------------------------------------------
+    // ---- row sums of all column parts, normalise and store ----------------------------------------------------------------
     {
-      float other_g, other_s;
-      xch[(2 * 2 + half) * 128 + row] = lg;
-      xch[(3 * 2 + half) * 128 + row] = ls;
+      xch[(2 * NS + cpart) * 128 + row] = lg;
+      xch[(3 * NS + cpart) * 128 + row] = ls;
       __syncthreads();
-      other_g = xch[(2 * 2 + (half ^ 1)) * 128 + row];
-      other_s = xch[(3 * 2 + (half ^ 1)) * 128 + row];
-      lg += other_g;
-      ls += other_s;
+      lg = 0.f;
+      ls = 0.f;
+#pragma unroll
+      for (int p2 = 0; p2 < NS; ++p2) {
+        lg += xch[(2 * NS + p2) * 128 + row];
+        ls += xch[(3 * NS + p2) * 128 + row];
+      }
     }
     const float lsum = lg * cgs + ls * cw;
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-    if (active && in_seq && half == 0) {
+    if (active && in_seq && cpart == 0) {
       d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg);
       d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = ms + __logf(ls);
     }
     {
+      // D / NS = 32 output columns per thread
+      static_assert(D / NS == 32, "output columns per thread");
       float ov[32];
+      tmem_ld32(tlane + L::cO + 32 * cpart, ov);
+      if (active && in_seq) {
 #pragma unroll
-      for (int pp = 0; pp < D / 64; ++pp) {
-        const int part = (D / 64) * half + pp;        // this thread's half of the output columns
-        tmem_ld32(tlane + L::cO + 32 * part, ov);
-        if (active && in_seq) {
+        for (int e = 0; e < 32; ++e) ov[e] *= inv;
+        bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D + 32 * cpart;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ov[e] *= inv;
-          bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D + 32 * part;
-#pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
-        }
+        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
       }
     }
     tc_fence_before();
@@ -490,7 +493,7 @@ __global__ void __launch_bounds__(kUThreads, (D == 64 && R == 64) ? 2 : 1) nha_f
 #undef NHA_STEP_MAX
 #undef NHA_STEP_PROB
 #undef NHA_ISSUE_PV
-#undef NHA_SWAP
+#undef NHA_XCHG
 #undef NHA_LOAD_HEAD_TILE
 #undef NHA_KBASE
   if (failed && tid == 0) atomicExch(err, 1);
@@ -506,7 +509,7 @@ static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream
   cudaError_t e = cudaFuncSetAttribute(nha_fwd_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), kUThreads, L::total, cs>>>(*d, flags, err);
+  nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), L::kThreads, L::total, cs>>>(*d, flags, err);
   return check_launch();
 }
 

@@ -147,6 +147,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* out) {
   for (int i = 0; i < 16; ++i) out[i] = __uint_as_float(r[i]);
 }
 
+// W consecutive fp32 columns (W = 16 or 32)
+template <int W>
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, float* out) {
+  if constexpr (W == 32) tmem_ld32(taddr, out);
+  else tmem_ld16(taddr, out);
+}
+
 // ---- asynchronous 16-byte copies into swizzled tiles (NT-thread CTAs) ------------------------------
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
