@@ -333,18 +333,21 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     }
     // ---- A = q k'^T, Av = do v'^T, QH = q Hk, Y0 = do Hv^T ---------------------------------------------------
     if (tid == 0) {
-      mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
-      mma_tile(tbase + L::cAv, aDO, L::kATile, aV, 8192, R, 64, D / 16, 0, false);
-      mma_tile(tbase + L::cQH, aQ, L::kATile, aHk, 0, R, 64, D / 16, 1, false);
-      mma_tile(tbase + L::cY, aDO, L::kATile, aHv, 8192, R, 64, D / 16, 0, false);      // Hv tiles as K-major [m][v]
+      const MmaOp ops[4] = {
+          {tbase + L::cA, aQ, aK, L::kATile, 8192, 0, 0, 64, D / 16, false},
+          {tbase + L::cAv, aDO, aV, L::kATile, 8192, 0, 0, 64, D / 16, false},
+          {tbase + L::cQH, aQ, aHk, L::kATile, 0, 0, 1, 64, D / 16, false},
+          {tbase + L::cY, aDO, aHv, L::kATile, 8192, 0, 0, 64, D / 16, false}};   // Hv tiles as K-major [m][v]
+      mma_interleaved(ops, R);
     }
     NHA_MMA_WAIT();
     NHA_TRIL_TO_SMEM(L::cA, L::bufA);
     NHA_TRIL_TO_SMEM(L::cAv, L::bufB);
     NHA_SMEM_TO_MMA();
     if (tid == 0) {
-      mma_tile(tbase + L::cA, aA, L::kATile, aSB, 0, R, 64, 4, 1, false);               // X  = tril(A)  SB
-      mma_tile(tbase + L::cAv, aB, L::kATile, aSB, 0, R, 64, 4, 1, false);              // X2 = tril(Av) SB
+      const MmaOp ops[2] = {{tbase + L::cA, aA, aSB, L::kATile, 0, 0, 1, 64, 4, false},      // X  = tril(A)  SB
+                            {tbase + L::cAv, aB, aSB, L::kATile, 0, 0, 1, 64, 4, false}};    // X2 = tril(Av) SB
+      mma_interleaved(ops, R);
     }
     NHA_MMA_WAIT();
     // ---- slot part of dz (this thread's 32 slots, 16 at a time); decayed bf16 copies; gate terms -------------------
@@ -531,8 +534,9 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
       }
       NHA_SMEM_TO_MMA();
       if (tid == 0) {
-        mma_tile(tbase + L::cS, aQS, L::kATile, aW, 8192, R, 64, D / 16, 0, false);      // S  = q_swa k^T
-        mma_tile(tbase + L::cDP, aDO, L::kATile, aWV, 8192, R, 64, D / 16, 0, false);    // dP = do v^T
+        const MmaOp ops[2] = {{tbase + L::cS, aQS, aW, L::kATile, 8192, 0, 0, 64, D / 16, false},     // S  = q_swa k^T
+                              {tbase + L::cDP, aDO, aWV, L::kATile, 8192, 0, 0, 64, D / 16, false}};  // dP = do v^T
+        mma_interleaved(ops, R);
       }
       NHA_MMA_WAIT();
       {

@@ -24,6 +24,9 @@
 //
 // Replaces chunk_nha_fused_o_kernel (nha_fla/ops/nha/chunk_fused.py:117-283) and, for chunk_nha, the
 // flash-attn varlen forward + fla chunk_gsa forward + log-sum-exp merge (nha_fla/ops/nha/chunk.py:423-470).
+#include <cuda.h>
+#include <string.h>
+
 #include "nha_common.cuh"
 #include "nha_umma.cuh"
 
@@ -32,6 +35,27 @@ namespace nha {
 using namespace umma;
 
 constexpr float kUmmaDecayLimit = 140.0f;
+
+// Tensor maps of the window keys (k_swa) and values (v) seen as [Ttot][H][D] bf16: a box is the 64-column half of
+// 64 consecutive tokens of one kv head and lands as one 128-byte-swizzled [64][64] operand tile.
+struct WindowMaps {
+  CUtensorMap k, v;
+  int use;                                            // 0: no tensor maps (copies go through cp.async)
+};
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(mbar))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(mbar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(mbar)) : "memory");
+}
 
 template <int D, int R>
 struct UmmaLayout {
@@ -58,20 +82,29 @@ struct UmmaLayout {
   static constexpr int tAB = kAlias ? tHk : end1;     // tril(A) / tril(Bv)  [R][64]
   static constexpr int tPG = kAlias ? tK : end1 + kATile;   // p~ .* a .* e^R   [R][64]
   static constexpr int end2 = kAlias ? end1 : end1 + 2 * kATile;
-  static constexpr int oA = end2;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
+  // D = 128 runs one CTA per SM, so the window loops are pipelined inside the CTA: a second set of window
+  // buffers (behind k' and Hk, which are dead after round 1 and fetched again for the next head tile; with one
+  // head per CTA those tiles hold p~ and tril(A), so the set gets room of its own) and a second S accumulator.
+  static constexpr bool kPipe = D == 128;
+  static constexpr int end3 = (kPipe && kAlias) ? end2 + 2 * KT * kWTile : end2;
+  static constexpr int tW2 = !kPipe ? tW : (kAlias ? end2 : tK);
+  static constexpr int tWV2 = !kPipe ? tWV : (kAlias ? end2 + KT * kWTile : tHk);
+  static constexpr int oA = end3;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
   static constexpr int oR = oA + 64 * 65 * 4;         // fp32 [64] exp(R)
   static constexpr int oX = oR + 256;                 // fp32 [4][NS][128] row statistics swapped between the column parts
-  static constexpr int oBar = oX + 4 * NS * 128 * 4;              // mbarrier + TMEM slot
-  static constexpr int total = oBar + 64 + 1024;      // + slack for the 1024-byte alignment of the base
+  static constexpr int oBar = oX + 4 * NS * 128 * 4;  // mbarriers (MMA rounds; loads, S and PV of the pipelined loops) + TMEM slot              // mbarrier + TMEM slot
+  static constexpr int total = oBar + 128 + 1024;     // + slack for the 1024-byte alignment of the base
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
   // O reuses QH's columns at D = 64 (QH has been read by then)
   static constexpr int cA = 0, cQH = 64, cS = 128, cO = D == 64 ? 64 : 256;
+  static constexpr int cS2 = kPipe ? 192 : cS;        // second S accumulator of the pipelined loops
   static_assert(total <= 227 * 1024, "shared memory of the output pass");
 };
 
 template <int D, int R>
 __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 64) ? 2 : 1) nha_fwd_umma_kernel(const nha_chunk_desc d, int* __restrict__ flags,
-                                                                  int* __restrict__ err) {
+                                                                  int* __restrict__ err,
+                                                                  const __grid_constant__ WindowMaps maps) {
   typedef UmmaLayout<D, R> L;
   constexpr int KT = L::KT, TH = R / 64, M = 64, TP = L::TP, WK = 64 * TP;
   constexpr int NS = L::NS, kUThreads = L::kThreads;
@@ -96,6 +129,9 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
   float* ER = (float*)(sm + L::oR);
   uint64_t* mbar = (uint64_t*)(sm + L::oBar);
   uint32_t* tslot = (uint32_t*)(sm + L::oBar + 16);
+  uint64_t* bl = (uint64_t*)(sm + L::oBar + 32);     // [2] window loads of the two buffer sets
+  uint64_t* bs = bl + 2;                              // [2] S products of the two accumulators
+  uint64_t* bpv = bl + 4;                             // P~ V product of the pipelined loop
 
   // window steps, newest first: step p covers the keys [kbase(p), kbase(p) + WK)
   const int jt_hi = ci;
@@ -136,6 +172,12 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       load_sw<D, kUThreads>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq0_ + t2) * D, (int64_t)HQ * D,   \
                  c0, 0, len, 64, 64 * t2, tid);                                                                       \
     }                                                                                                                 \
+    if (L::kPipe && !L::kAlias && (ht_) > 0) {     /* the second window buffer set has overwritten k' and Hk */       \
+      load_sw<D, kUThreads>(sm + L::tK, 8192, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * D, (int64_t)H * D,          \
+                            c0 - shift, lo, hi, 64, 0, tid);                                                            \
+      load_sw<64, kUThreads>(sm + L::tHk, 0, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * D * M, M, 0, 0, D, D,    \
+                             0, tid);                                                                                   \
+    }                                                                                                                 \
     /* keys of the OLDEST step (the first one the maxima sweep needs); with a single step also its values */         \
     load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(nsteps - 1), 0, len, WK, 0, tid);                \
     if (nsteps == 1) load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);       \
@@ -151,7 +193,10 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 #pragma unroll
     for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
   }
-  if (tid == 0) mbar_init(mbar, 1);
+  if (tid == 0) {
+    mbar_init(mbar, 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&bl[i], 1);
+  }
   __syncthreads();
   // inclusive scan along the rows: kUThreads / 64 threads per column (a segment of rows each), then the totals
   // of the earlier segments are added
@@ -268,14 +313,16 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     }                                                                                            \
   } while (0)
 // S = q_swa (window keys of one step)^T
-#define NHA_ISSUE_S() mma_tile(tbase + L::cS, aQS, L::kATile, aW, L::kWTile, R, WK, D / 16, 0, false)
+#define NHA_ISSUE_S_AT(cs_, aw_) mma_tile(tbase + (cs_), aQS, L::kATile, (aw_), L::kWTile, R, WK, D / 16, 0, false)
+#define NHA_ISSUE_S() NHA_ISSUE_S_AT(L::cS, aW)
 // this thread's KW keys of a window step: keys kb_ + KW cpart + [0, KW)
-#define NHA_STEP_MAX(kb_)                                                                        \
+#define NHA_STEP_MAX(kb_) NHA_STEP_MAX_AT(kb_, L::cS)
+#define NHA_STEP_MAX_AT(kb_, cs_)                                                                \
   do {                                                                                           \
     float sv_[LW];                                                                               \
     _Pragma("unroll") for (int pp = 0; pp < KW / LW; ++pp) {                                     \
       const int key0 = KW * cpart + LW * pp;                                                     \
-      tmem_ldw<LW>(tlane + L::cS + key0, sv_);                                                   \
+      tmem_ldw<LW>(tlane + (cs_) + key0, sv_);                                                   \
       const int off_ = (kb_) + key0 - klo;                                                       \
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};                                \
       _Pragma("unroll") for (int e = 0; e < LW; ++e)                                             \
@@ -284,13 +331,14 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     }                                                                                            \
   } while (0)
 // P~ = exp(scale S - ms) cw of this thread's keys of a step, into the swizzled tile; row sum into ls
-#define NHA_STEP_PROB(kb_)                                                                       \
+#define NHA_STEP_PROB(kb_) NHA_STEP_PROB_AT(kb_, L::cS, L::tP)
+#define NHA_STEP_PROB_AT(kb_, cs_, tp_)                                                          \
   do {                                                                                           \
     float sv_[LW];                                                                               \
     const float nms_ = -ms * kLog2e;                                                             \
     _Pragma("unroll") for (int pp = 0; pp < KW / LW; ++pp) {                                     \
       const int key0 = KW * cpart + LW * pp;                                                     \
-      tmem_ldw<LW>(tlane + L::cS + key0, sv_);                                                   \
+      tmem_ldw<LW>(tlane + (cs_) + key0, sv_);                                                   \
       const int off_ = (kb_) + key0 - klo;                                                       \
       if (active) {                                                                              \
         float l4[4] = {0.f, 0.f, 0.f, 0.f};                                                      \
@@ -303,7 +351,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
             o8[e] = pe * cw;                                                                     \
           }                                                                                      \
           const int kk_ = key0 + 8 * c8;                                                         \
-          *reinterpret_cast<uint4*>(sm + L::tP + (kk_ >> 6) * L::kATile +                        \
+          *reinterpret_cast<uint4*>(sm + (tp_) + (kk_ >> 6) * L::kATile +                        \
                                     sw_off(row, (kk_ & 63) >> 3)) = pack8(o8);                   \
         }                                                                                        \
         ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);                                                 \
@@ -311,10 +359,11 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     }                                                                                            \
   } while (0)
 // O += P~ (window values of one step)
-#define NHA_ISSUE_PV()                                                                           \
+#define NHA_ISSUE_PV() NHA_ISSUE_PV_AT(aP, aWV)
+#define NHA_ISSUE_PV_AT(ap_, awv_)                                                               \
   do {                                                                                           \
     _Pragma("unroll") for (int ct = 0; ct < KT; ++ct)                                            \
-      mma_tile(tbase + L::cO + 64 * ct, aP, L::kATile, aWV + ct * L::kWTile, 0, R, 64, 4 * TP, 1, true); \
+      mma_tile(tbase + L::cO + 64 * ct, (ap_), L::kATile, (awv_) + ct * L::kWTile, 0, R, 64, 4 * TP, 1, true); \
   } while (0)
 // combine a row statistic over the NS threads of the row (slot_: exchange point 0..3; OP_: fmaxf or addf);
 // the barrier inside is reached by every thread of the CTA
@@ -327,6 +376,44 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     (v_) = r_;                                                                                   \
   } while (0)
   auto addf = [](float x, float y) { return x + y; };
+
+// pipelined loops (D = 128): window step p_ into buffer set set_ (its keys, with wv_ also its values).  A step whose
+// 64 keys lie inside the sequence comes by TMA (one thread, two or four boxes, bytes counted on the set's mbarrier);
+// a step that sticks out of the sequence is copied with zero fill by every thread and then arrives on the same
+// barrier.  Every thread of the CTA runs the macro.  Issue work is spread over three threads of three warps so that
+// it does not queue behind one thread: thread 0 the MMA rounds and P~ V, thread 32 the TMA loads, thread 64 the S
+// products of the loops.
+#define NHA_LOAD_STEP(set_, p_, wv_)                                                                                \
+  do {                                                                                                              \
+    const int kb__ = NHA_KBASE(p_);                                                                                 \
+    unsigned char* w__ = sm + ((set_) ? L::tW2 : L::tW);                                                            \
+    unsigned char* v__ = sm + ((set_) ? L::tWV2 : L::tWV);                                                          \
+    if (maps.use && kb__ >= 0 && kb__ + WK <= len) {                                                                \
+      if (tid == 32) {                                                                                              \
+        mbar_expect_tx(&bl[set_], (uint32_t)((wv_) ? 2 : 1) * WK * D * 2);                                          \
+        _Pragma("unroll") for (int kt = 0; kt < KT; ++kt) {                                                         \
+          tma_load_3d(w__ + kt * L::kWTile, &maps.k, 64 * kt, h, t0 + kb__, &bl[set_]);                             \
+          if (wv_) tma_load_3d(v__ + kt * L::kWTile, &maps.v, 64 * kt, h, t0 + kb__, &bl[set_]);                    \
+        }                                                                                                           \
+      }                                                                                                             \
+    } else {                                                                                                        \
+      load_sw<D, kUThreads>(w__, L::kWTile, ksw, (int64_t)H * D, kb__, 0, len, WK, 0, tid);                         \
+      if (wv_) load_sw<D, kUThreads>(v__, L::kWTile, vsw, (int64_t)H * D, kb__, 0, len, WK, 0, tid);                \
+      cp_commit();                                                                                                  \
+      cp_wait_all();                                                                                                \
+      fence_async_smem();                                                                                           \
+      __syncthreads();                                                                                              \
+      if (tid == 32) mbar_arrive(&bl[set_]);                                                                        \
+    }                                                                                                               \
+  } while (0)
+// bounded wait on one of the pipeline's mbarriers; bit_ of `phases` holds its parity
+#define NHA_WAIT_BAR(bar_, bit_)                                                                                    \
+  do {                                                                                                              \
+    if (!mbar_wait((bar_), (phases >> (bit_)) & 1u)) failed = true;                                                 \
+    phases ^= 1u << (bit_);                                                                                         \
+    tc_fence_after();                                                                                               \
+  } while (0)
+  uint32_t phases = 0u;                               // parities: bits 0-1 loads, 2-3 S products, 4 P~ V product
 
   for (int ht = 0; ht < NG / TH && !failed; ++ht) {
     const int hq0 = h * NG + ht * TH;
@@ -379,17 +466,51 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       lg = (l4[0] + l4[1]) + (l4[2] + l4[3]);
     }
     // ---- maxima of the newer window steps (the newest one last: its S stays in TMEM) -----------------------------
-    for (int p = nsteps - 2; p >= 0 && !failed; --p) {
-      tc_fence_before();
-      __syncthreads();
-      load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
-      if (p == 0) load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);
-      cp_commit();
-      cp_wait_all();
-      NHA_SMEM_TO_MMA();
-      if (tid == 0) NHA_ISSUE_S();
-      NHA_MMA_WAIT();
-      NHA_STEP_MAX(NHA_KBASE(p));
+    int rset = 0;                                      // buffer set / accumulator that hold the newest step afterwards
+    if constexpr (L::kPipe) {
+      // step index i counts from the oldest step (i = 0: loaded with the head tile, S formed in round 1); step i uses
+      // buffer set and accumulator i & 1.  The load of step i + 1 and the maximum of step i - 1 overlap S of step i.
+      if (nsteps > 1) NHA_LOAD_STEP(1, nsteps - 2, nsteps - 2 == 0);
+      for (int i = 1; i < nsteps && !failed; ++i) {
+        const int b = i & 1, p = nsteps - 1 - i;
+        NHA_WAIT_BAR(&bl[b], b);
+        tc_fence_before();
+        __syncthreads();                               // every thread has read the maxima of step i - 2 from this accumulator
+        tc_fence_after();
+        if (tid == 64) {
+          NHA_ISSUE_S_AT(b ? L::cS2 : L::cS, smem_u32(sm + (b ? L::tW2 : L::tW)));
+          commit(&bs[b]);
+        }
+        // the other set's keys were read by S of step i - 1, which has completed
+        if (i + 1 < nsteps) {
+          if (b) NHA_LOAD_STEP(0, p - 1, p - 1 == 0); else NHA_LOAD_STEP(1, p - 1, p - 1 == 0);
+        }
+        if (i >= 2) {
+          if (b) NHA_STEP_MAX_AT(NHA_KBASE(p + 1), L::cS); else NHA_STEP_MAX_AT(NHA_KBASE(p + 1), L::cS2);
+        }
+        NHA_WAIT_BAR(&bs[b], 2 + b);
+      }
+      if (nsteps > 1) {
+        rset = (nsteps - 1) & 1;
+        if (rset) NHA_STEP_MAX_AT(NHA_KBASE(0), L::cS2); else NHA_STEP_MAX_AT(NHA_KBASE(0), L::cS);
+        // the other set is free: the first older step of the probability sweep goes in flight now
+        tc_fence_before();
+        __syncthreads();
+        if (rset) NHA_LOAD_STEP(0, 1, true); else NHA_LOAD_STEP(1, 1, true);
+      }
+    } else {
+      for (int p = nsteps - 2; p >= 0 && !failed; --p) {
+        tc_fence_before();
+        __syncthreads();
+        load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+        if (p == 0) load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(0), 0, len, WK, 0, tid);
+        cp_commit();
+        cp_wait_all();
+        NHA_SMEM_TO_MMA();
+        if (tid == 0) NHA_ISSUE_S();
+        NHA_MMA_WAIT();
+        NHA_STEP_MAX(NHA_KBASE(p));
+      }
     }
     // ---- joint maximum; unnormalised slot probabilities as bf16 A operands -----------------------------------------
     tc_fence_before();
@@ -422,7 +543,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       mma_tile(tbase + L::cA, aPA, L::kATile, aSB, 0, R, 64, 4, 0, false);
     }
     float ls = 0.f;
-    NHA_STEP_PROB(NHA_KBASE(0));
+    if (rset) NHA_STEP_PROB_AT(NHA_KBASE(0), L::cS2, L::tW2); else NHA_STEP_PROB(NHA_KBASE(0));
     NHA_MMA_WAIT();
     NHA_TRIL_TO_SMEM(L::cA, L::tAB);
     NHA_SMEM_TO_MMA();
@@ -431,24 +552,53 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 #pragma unroll
       for (int ct = 0; ct < KT; ++ct)
         mma_tile(tbase + L::cO + 64 * ct, aAB, L::kATile, aV + ct * 8192, 0, R, 64, 4, 1, true);
-      NHA_ISSUE_PV();
+      if (rset) NHA_ISSUE_PV_AT(smem_u32(sm + L::tW2), smem_u32(sm + L::tWV2)); else NHA_ISSUE_PV();
     }
     NHA_MMA_WAIT();
     // ---- older window steps ------------------------------------------------------------------------------------------------
-    for (int p = 1; p < nsteps && !failed; ++p) {
-      tc_fence_before();
-      __syncthreads();
-      load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
-      load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
-      cp_commit();
-      cp_wait_all();
-      NHA_SMEM_TO_MMA();
-      if (tid == 0) NHA_ISSUE_S();
-      NHA_MMA_WAIT();
-      NHA_STEP_PROB(NHA_KBASE(p));
-      NHA_SMEM_TO_MMA();
-      if (tid == 0) NHA_ISSUE_PV();
-      NHA_MMA_WAIT();
+    if constexpr (L::kPipe) {
+      // step j (j = 1: the first older one) uses buffer set and accumulator (rset + j) & 1; its load was issued one
+      // step ahead, P~ V of step j runs while step j + 1 is prepared
+      for (int j = 1; j < nsteps && !failed; ++j) {
+        const int b = (rset + j) & 1;
+        NHA_WAIT_BAR(&bl[b], b);
+        tc_fence_before();
+        __syncthreads();                               // every thread has read S of step j - 2 from this accumulator
+        tc_fence_after();
+        if (tid == 64) {
+          NHA_ISSUE_S_AT(b ? L::cS2 : L::cS, smem_u32(sm + (b ? L::tW2 : L::tW)));
+          commit(&bs[b]);
+        }
+        if (j >= 2) NHA_WAIT_BAR(bpv, 4);              // P~ V of step j - 1 has completed: the other set is free
+        if (j + 1 < nsteps) {
+          if (b) NHA_LOAD_STEP(0, j + 1, true); else NHA_LOAD_STEP(1, j + 1, true);
+        }
+        NHA_WAIT_BAR(&bs[b], 2 + b);
+        if (b) NHA_STEP_PROB_AT(NHA_KBASE(j), L::cS2, L::tW2); else NHA_STEP_PROB_AT(NHA_KBASE(j), L::cS, L::tW);
+        NHA_SMEM_TO_MMA();
+        if (tid == 0) {
+          if (b) NHA_ISSUE_PV_AT(smem_u32(sm + L::tW2), smem_u32(sm + L::tWV2));
+          else NHA_ISSUE_PV_AT(smem_u32(sm + L::tW), smem_u32(sm + L::tWV));
+          commit(bpv);
+        }
+      }
+      if (nsteps > 1) NHA_WAIT_BAR(bpv, 4);
+    } else {
+      for (int p = 1; p < nsteps && !failed; ++p) {
+        tc_fence_before();
+        __syncthreads();
+        load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+        load_sw<D, kUThreads>(sm + L::tWV, L::kWTile, vsw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
+        cp_commit();
+        cp_wait_all();
+        NHA_SMEM_TO_MMA();
+        if (tid == 0) NHA_ISSUE_S();
+        NHA_MMA_WAIT();
+        NHA_STEP_PROB(NHA_KBASE(p));
+        NHA_SMEM_TO_MMA();
+        if (tid == 0) NHA_ISSUE_PV();
+        NHA_MMA_WAIT();
+      }
     }
     // ---- row sums of all column parts, normalise and store ----------------------------------------------------------------
     {
@@ -490,6 +640,12 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 #undef NHA_SMEM_TO_MMA
 #undef NHA_TRIL_TO_SMEM
 #undef NHA_ISSUE_S
+#undef NHA_ISSUE_S_AT
+#undef NHA_STEP_MAX_AT
+#undef NHA_STEP_PROB_AT
+#undef NHA_ISSUE_PV_AT
+#undef NHA_LOAD_STEP
+#undef NHA_WAIT_BAR
 #undef NHA_STEP_MAX
 #undef NHA_STEP_PROB
 #undef NHA_ISSUE_PV
@@ -503,13 +659,48 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
   if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    return (e == cudaSuccess && q == cudaDriverEntryPointSuccess) ? (EncodeTiledFn)p : (EncodeTiledFn) nullptr;
+  }();
+  return fn;
+}
+
+// [Ttot][H][D] bf16 seen as a 3-d tensor (D innermost); box = 64 columns x 1 head x 64 tokens, 128-byte swizzle
+static bool make_window_map(CUtensorMap* m, const void* base, int64_t Ttot, int H, int D) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || Ttot <= 0 || ((uintptr_t)base & 15)) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)Ttot};
+  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2};
+  const cuuint32_t box[3] = {64, 1, 64};
+  const cuuint32_t es[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int D, int R>
 static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
   typedef UmmaLayout<D, R> L;
   cudaError_t e = cudaFuncSetAttribute(nha_fwd_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
+  WindowMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (L::kPipe) {
+    const char* off = getenv("NHA_B200_NO_TMA");
+    maps.use = !(off && off[0] == '1') && make_window_map(&maps.k, d->k_swa, d->Ttot, d->H, D) &&
+               make_window_map(&maps.v, d->v, d->Ttot, d->H, D);
+  }
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), L::kThreads, L::total, cs>>>(*d, flags, err);
+  nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), L::kThreads, L::total, cs>>>(*d, flags, err, maps);
   return check_launch();
 }
 

@@ -78,6 +78,41 @@ __device__ __forceinline__ void mma_tile_ex(uint32_t d_tmem, uint32_t a_addr, in
   }
 }
 
+// Several products issued with their k steps interleaved.  The k steps of ONE product accumulate into the same
+// tensor-memory columns, so each waits for the one before it; a product of a few small k steps is therefore bound
+// by the latency of the instruction, not by the tensor pipe, and independent products issued one after the other
+// add their latencies up.  Issuing step ks of every product before step ks + 1 of any lets the chains overlap.
+// (Products that accumulate into the same columns must be given as ONE chain: list them in order with the same d
+// and accumulate = true on the later ones; they are issued in list order within each step, which keeps them
+// ordered because the hardware executes one thread's MMAs in issue order.)
+struct MmaOp {
+  uint32_t d;        // tensor-memory column address of the accumulator
+  uint32_t a, b;     // shared-memory addresses of the operands
+  int a_tile, b_tile;   // bytes between consecutive 64-wide k tiles of a K-major operand
+  int a_mn, b_mn;    // 1: operand is MN-major (16 k rows = 2048 bytes per k step)
+  int N, ksteps;
+  bool acc;          // accumulate onto what the columns already hold
+};
+
+template <int NOPS>
+__device__ __forceinline__ void mma_interleaved(const MmaOp (&ops)[NOPS], int M) {
+  int kmax = 0;
+#pragma unroll
+  for (int i = 0; i < NOPS; ++i) kmax = ops[i].ksteps > kmax ? ops[i].ksteps : kmax;
+  for (int ks = 0; ks < kmax; ++ks) {
+    const int kt = ks >> 2, kin = ks & 3;
+#pragma unroll
+    for (int i = 0; i < NOPS; ++i) {
+      if (ks < ops[i].ksteps) {
+        const uint32_t idesc = make_idesc(M, ops[i].N, ops[i].b_mn) | ((uint32_t)ops[i].a_mn << 15);
+        const uint64_t da = ops[i].a_mn ? make_desc(ops[i].a + ks * 2048) : make_desc(ops[i].a + kt * ops[i].a_tile + kin * 32);
+        const uint64_t db = ops[i].b_mn ? make_desc(ops[i].b + ks * 2048) : make_desc(ops[i].b + kt * ops[i].b_tile + kin * 32);
+        mma_f16(ops[i].d, da, db, idesc, ops[i].acc || ks > 0);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void commit(uint64_t* mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(mbar))
                : "memory");
