@@ -151,9 +151,10 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
 }
 
 // Forward scan over the chunks of one (sequence, kv head): stores the state at every chunk start and
-// the final state.  One thread owns eight consecutive state elements (one 16-byte bf16 store per
-// chunk) and fetches kStScanBatch chunks of L ahead of the serial recurrence.
-constexpr int kStScanBatch = 4;
+// the final state.  One thread owns four consecutive state elements (one 8-byte bf16 store per chunk) and
+// fetches kStScanBatch chunks of L ahead of the serial recurrence, so that a long sequence with few heads
+// still keeps enough loads in flight.
+constexpr int kStScanBatch = 8;
 __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w) {
   const int K = d.K, V = d.V, M = d.M, H = d.H;
   const int KM = K * M, MV = M * V;
@@ -163,35 +164,28 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int chunk0 = d.plan[n];
-  const int el = 8 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int el = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (el >= KM + MV) return;
   const bool is_k = el < KM;
   const int e = is_k ? el : el - KM;
   const int m = is_k ? e % M : e / V;
   const size_t per = is_k ? KM : MV;
   bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
-  float run[8];
+  float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
   {
     const float* h0 = is_k ? d.hk0 : d.hv0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) run[i] = h0 ? h0[nh * per + e + i] : 0.f;
+    if (h0) run = *reinterpret_cast<const float4*>(h0 + nh * per + e);
   }
   for (int lo = 0; lo < nchunks; lo += kStScanBatch) {
-    float4 la[kStScanBatch], lb[kStScanBatch], da[kStScanBatch], db[kStScanBatch];
+    float4 la[kStScanBatch], da[kStScanBatch];
 #pragma unroll
     for (int u = 0; u < kStScanBatch; ++u) {
       const int ci = lo + u;
       if (ci < nchunks) {
         const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-        const float* src = w.local + cgi * SD + el;
-        la[u] = __ldcs((const float4*)src);
-        lb[u] = __ldcs((const float4*)(src + 4));
-        if (is_k) {
-          da[u] = *(const float4*)(w.gend + cgi * M + m);
-          db[u] = *(const float4*)(w.gend + cgi * M + m + 4);
-        } else {
-          da[u].x = w.gend[cgi * M + m];
-        }
+        la[u] = __ldcs((const float4*)(w.local + cgi * SD + el));
+        if (is_k) da[u] = *(const float4*)(w.gend + cgi * M + m);
+        else da[u].x = w.gend[cgi * M + m];
       }
     }
 #pragma unroll
@@ -199,28 +193,20 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
       const int ci = lo + u;
       if (ci < nchunks) {
         const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-        *reinterpret_cast<uint4*>(out + cgi * per + e) = pack8(run);
-        float a[8];
-        if (is_k) {
-          a[0] = __expf(da[u].x); a[1] = __expf(da[u].y); a[2] = __expf(da[u].z); a[3] = __expf(da[u].w);
-          a[4] = __expf(db[u].x); a[5] = __expf(db[u].y); a[6] = __expf(db[u].z); a[7] = __expf(db[u].w);
-        } else {
-          const float x = __expf(da[u].x);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) a[i] = x;
-        }
-        run[0] = run[0] * a[0] + la[u].x; run[1] = run[1] * a[1] + la[u].y;
-        run[2] = run[2] * a[2] + la[u].z; run[3] = run[3] * a[3] + la[u].w;
-        run[4] = run[4] * a[4] + lb[u].x; run[5] = run[5] * a[5] + lb[u].y;
-        run[6] = run[6] * a[6] + lb[u].z; run[7] = run[7] * a[7] + lb[u].w;
+        uint2 o;
+        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(run.x, run.y);
+        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(run.z, run.w);
+        *reinterpret_cast<uint2*>(out + cgi * per + e) = o;
+        float4 a;
+        if (is_k) a = make_float4(__expf(da[u].x), __expf(da[u].y), __expf(da[u].z), __expf(da[u].w));
+        else { const float x = __expf(da[u].x); a = make_float4(x, x, x, x); }
+        run.x = run.x * a.x + la[u].x; run.y = run.y * a.y + la[u].y;
+        run.z = run.z * a.z + la[u].z; run.w = run.w * a.w + la[u].w;
       }
     }
   }
   float* ht = is_k ? d.hkt : d.hvt;
-  if (ht) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ht[nh * per + e + i] = run[i];
-  }
+  if (ht) *reinterpret_cast<float4*>(ht + nh * per + e) = run;
 }
 
 int64_t state_workspace_bytes(const nha_chunk_desc* d) {
@@ -243,7 +229,7 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
   int st = check_launch();
   if (st != NHA_OK) return st;
-  nha_state_scan_kernel<<<dim3((unsigned)((SD / 8 + 255) / 256), d->N * d->H), 256, 0, cs>>>(*d, w);
+  nha_state_scan_kernel<<<dim3((unsigned)((SD / 4 + 255) / 256), d->N * d->H), 256, 0, cs>>>(*d, w);
   return check_launch();
 }
 
