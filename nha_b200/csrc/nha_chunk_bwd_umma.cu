@@ -629,8 +629,13 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int tid = threadIdx.x, lane = tid & 31;
   const size_t nh = (size_t)n * H + h, ch = (size_t)cg * H + h;
-  __shared__ float acc_s[M];
-  if (tid < M) acc_s[tid] = 0.f;
+  // per-warp partial sums, added in a fixed order afterwards (no floating-point atomics: the result must not
+  // depend on the order in which warps arrive)
+  constexpr int kCW = kCarryThreads / 32;
+  __shared__ float part_k[kCW][M];
+  __shared__ float part_v[kCarryThreads / 32][M];
+  const int warp = tid >> 5;
+  for (int i = tid; i < kCW * M; i += kCarryThreads) (&part_v[0][0])[i] = 0.f;
   __syncthreads();
   const bool last = ci >= nchunks - 1;
   const bool have_next = !last || (d.d_hkt && d.hkt && d.hvt);
@@ -667,7 +672,7 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
   for (int e = 0; e < 4; ++e) ck[e] += __shfl_xor_sync(0xffffffffu, ck[e], 16);
   if (lane < 16) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) atomicAdd(&acc_s[4 * lane + e], ck[e]);
+    for (int e = 0; e < 4; ++e) part_k[warp][4 * lane + e] = ck[e];
   }
   // DV [64][V]: a slot's row is spread over V/4 neighbouring lanes
   const int C4 = V / 4;
@@ -691,10 +696,17 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
     *reinterpret_cast<uint2*>(dvb + 4 * (size_t)i) = o;
     float acc = f.x * nx.x + f.y * nx.y + f.z * nx.z + f.w * nx.w;
     for (int o2 = 1; o2 < C4 && o2 < 32; o2 <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-    if (c == 0) atomicAdd(&acc_s[r], acc);
+    if (c == 0) part_v[warp][r] = acc;                 // one writer per (warp, slot): row r belongs to one warp only
   }
   __syncthreads();
-  if (tid < M) w.gcarry[ch * M + tid] = acc_s[tid];
+  if (tid < M) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < kCW; ++w8) sum += part_k[w8][tid];
+#pragma unroll
+    for (int w8 = 0; w8 < kCW; ++w8) sum += part_v[w8][tid];
+    w.gcarry[ch * M + tid] = sum;
+  }
 }
 
 // ================================================================================================
