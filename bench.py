@@ -357,8 +357,8 @@ def main():
         # q_gsa, q_swa, k_gsa, k_swa, v, s, g, states in; o and both log-sum-exps out
         'output_pass': H * ((5 * D + 2 * M) * e + st * e + D * e + 2 * f),
         # q_gsa, q_swa, do, o, k_gsa, k_swa, v, s, g, states, log-sum-exps in; dq_gsa, dq_swa, delta, joint LSE,
-        # gate terms (fp32), four bf16 copies of dz / p, the chunk's state-gradient terms (fp32) out
-        'bwd_rows': H * ((7 * D + 2 * M) * e + st * e + 2 * f + 2 * D * e + 2 * f + M * f + 4 * M * e + st * f),
+        # gate terms (fp32), two bf16 copies of dz / p, the chunk's state-gradient terms (fp32) out
+        'bwd_rows': H * ((7 * D + 2 * M) * e + st * e + 2 * f + 2 * D * e + 2 * f + M * f + 2 * M * e + st * f),
         # k_swa, v, q_swa, do, joint LSE, delta in; dk_swa and the fp32 window part of dv out
         'bwd_window_cols': H * (4 * D * e + 2 * f + D * e + D * f),
         # general kernel of the slot branch: runs only on chunks flagged by the forward (none here)

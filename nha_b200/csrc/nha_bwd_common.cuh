@@ -14,8 +14,8 @@ struct BwdWs {
   float* dvp;     // [Ttot, H, V]    intra-chunk part of dv'
   float* dsp;     // [Ttot, H, M]    intra-chunk part of ds'
   float* dga;     // [Ttot, H, M]    ok .* dz + p .* dp summed over the group
-  bf16* dzg;      // [Ttot, HQ, M]   scale * dz_slot .* exp(G)
-  bf16* pgq;      // [Ttot, HQ, M]   p_slot .* exp(G)
+  bf16* dzg;      // [Ttot, HQ, M]   scale * dz_slot .* exp(G)   (general kernels; the tensor-memory rows pass keeps it on chip)
+  bf16* pgq;      // [Ttot, HQ, M]   p_slot .* exp(G)            (general kernels, and the two-heads-per-tile rows pass)
   float* dkc;     // [NC, H, K, M]   first the chunk's own term q^T (scale dz exp G), then (after the scan)
                   //                 the gradient of hk at the END of the chunk
   float* dvc;     // [NC, H, M, V]   likewise (p exp G)^T do, then the gradient of hv at the chunk end

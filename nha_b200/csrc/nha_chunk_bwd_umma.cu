@@ -402,7 +402,6 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
               *reinterpret_cast<uint4*>(sm + L::tPA + sw_off(row, ch)) = pa;
             } else if (in_seq) {
               const size_t gi = rowq * M + 8 * ch;
-              *reinterpret_cast<uint4*>(w.dzg + gi) = zg;
               *reinterpret_cast<uint4*>(w.dza + gi) = za;
               *reinterpret_cast<uint4*>(w.pgq + gi) = pg;
               *reinterpret_cast<uint4*>(w.paq + gi) = pa;
@@ -414,12 +413,12 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     NHA_SMEM_TO_MMA();
     if (tid == 0) mma_tile(tbase + L::cA, aA, L::kATile, aSB, 0, R, 64, 4, 0, false);  // E = (scale dz a) SB^T
     if constexpr (L::kAlias) {
-      // while E runs: the four bf16 copies leave through coalesced 128-byte rows
-      const bf16* tiles[4] = {(const bf16*)(sm + L::bufB), (const bf16*)(sm + L::bufA), (const bf16*)(sm + L::tPG),
-                              (const bf16*)(sm + L::tPA)};
-      bf16* dsts[4] = {w.dzg, w.dza, w.pgq, w.paq};
+      // while E runs: the two bf16 copies the columns pass reads (scale dz a, p a) leave through coalesced
+      // 128-byte rows; the copies decayed by exp(G) are used inside this CTA only
+      const bf16* tiles[2] = {(const bf16*)(sm + L::bufA), (const bf16*)(sm + L::tPA)};
+      bf16* dsts[2] = {w.dza, w.paq};
 #pragma unroll
-      for (int t4 = 0; t4 < 4; ++t4) {
+      for (int t4 = 0; t4 < 2; ++t4) {
 #pragma unroll
         for (int j = 0; j < 512 / NT; ++j) {
           const int i = tid + NT * j;
