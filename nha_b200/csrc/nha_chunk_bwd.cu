@@ -53,10 +53,10 @@ __host__ __device__ inline WRowLayout wrow_layout(int K, int V) {
   return L;
 }
 
-__global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const nha_chunk_desc d, const BwdWs w) {
+__device__ __forceinline__ void nha_bwd_window_rows_kernel_body(const nha_chunk_desc d, const BwdWs w, const int cgb) {
   ChunkCtx c;
-  if (!chunk_ctx(d, blockIdx.x, c)) return;
-  if (!chunk_gate(w, blockIdx.x, blockIdx.y, d.H)) return;
+  if (!chunk_ctx(d, cgb, c)) return;
+  if (!chunk_gate(w, cgb, blockIdx.y, d.H)) return;
   const int K = d.K, V = d.V, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -144,6 +144,18 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const n
       if (pq < c.len)
         *reinterpret_cast<uint4*>((bf16*)d.dq_swa + ((size_t)(c.t0 + pq) * HQ + hq) * K + 8 * c8) = pack8(DQ + r * ldq + 8 * c8);
     }
+  }
+}
+
+// One CTA walks `cpc` consecutive chunks (1 when the kernel handles every chunk; more when it is launched gated
+// on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  for (int i = 0; i < cpc; ++i) {
+    const int cgb = blockIdx.x * cpc + i;
+    if (cgb >= ncb) return;
+    nha_bwd_window_rows_kernel_body(d, w, cgb);
+    __syncthreads();
   }
 }
 
@@ -327,10 +339,10 @@ __device__ __forceinline__ void rows_times_sbT(float* Y, int ldy, const bf16* PA
   }
 }
 
-__global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chunk_desc d, const BwdWs w) {
+__device__ __forceinline__ void nha_bwd_slot_kernel_body(const nha_chunk_desc d, const BwdWs w, const int cgb) {
   using namespace nvcuda::wmma;
   ChunkCtx c;
-  const int cg = blockIdx.x;
+  const int cg = cgb;
   if (!chunk_ctx(d, cg, c)) return;
   if (!chunk_gate(w, cg, blockIdx.y, d.H)) return;
   const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
@@ -576,6 +588,18 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chun
   }
 }
 
+// One CTA walks `cpc` consecutive chunks (1 when the kernel handles every chunk; more when it is launched gated
+// on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  for (int i = 0; i < cpc; ++i) {
+    const int cgb = blockIdx.x * cpc + i;
+    if (cgb >= ncb) return;
+    nha_bwd_slot_kernel_body(d, w, cgb);
+    __syncthreads();
+  }
+}
+
 // ================================================================================================
 // 4a. state gradients at every chunk end.  The gradient D of the slot memory obeys, last chunk first,
 //         D_end[c-1] = D_end[c] .* exp(Gend_c) + L_c,
@@ -598,9 +622,9 @@ __host__ __device__ inline LocalLayout local_layout(int K, int V, int M) {
   return L;
 }
 
-__global__ void __launch_bounds__(kBwThreads) nha_bwd_local_terms_kernel(const nha_chunk_desc d, const BwdWs w) {
+__device__ __forceinline__ void nha_bwd_local_terms_kernel_body(const nha_chunk_desc d, const BwdWs w, const int cgb) {
   ChunkCtx c;
-  const int cg = blockIdx.x;
+  const int cg = cgb;
   if (!chunk_ctx(d, cg, c)) return;
   if (!chunk_gate(w, cg, blockIdx.y, d.H)) return;
   const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H, h = blockIdx.y;
@@ -647,6 +671,18 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_local_terms_kernel(const n
   float* dv = w.dvc + ((size_t)cg * H + h) * M * V;
   for (int i = tid; i < K * M; i += kBwThreads) dk[i] = OK[(i / M) * ldok + (i % M)];
   for (int i = tid; i < M * V; i += kBwThreads) dv[i] = OV[(i / V) * ldov + (i % V)];
+}
+
+// One CTA walks `cpc` consecutive chunks (1 when the kernel handles every chunk; more when it is launched gated
+// on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_local_terms_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  for (int i = 0; i < cpc; ++i) {
+    const int cgb = blockIdx.x * cpc + i;
+    if (cgb >= ncb) return;
+    nha_bwd_local_terms_kernel_body(d, w, cgb);
+    __syncthreads();
+  }
 }
 
 // In-place reverse scan over the chunks of one (sequence, kv head): on entry dkc/dvc hold L_c, on exit
@@ -730,9 +766,9 @@ __host__ __device__ inline MarchLayout march_layout(int K, int V, int M) {
   return L;
 }
 
-__global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chunk_desc d, const BwdWs w) {
+__device__ __forceinline__ void nha_bwd_inter_kernel_body(const nha_chunk_desc d, const BwdWs w, const int cgb) {
   ChunkCtx c;
-  const int cgx = blockIdx.x;
+  const int cgx = cgb;
   if (!chunk_ctx(d, cgx, c)) return;
   // a chunk that another kernel handles is skipped, except that the CTA of a sequence's first chunk
   // always finishes the tail rows at the end of this kernel
@@ -923,6 +959,18 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chu
   }
 }
 
+// One CTA walks `cpc` consecutive chunks (1 when the kernel handles every chunk; more when it is launched gated
+// on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
+__global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  for (int i = 0; i < cpc; ++i) {
+    const int cgb = blockIdx.x * cpc + i;
+    if (cgb >= ncb) return;
+    nha_bwd_inter_kernel_body(d, w, cgb);
+    __syncthreads();
+  }
+}
+
 
 int check_chunk_desc(const nha_chunk_desc* d);
 bool bwd_umma_supported(const nha_chunk_desc* d);
@@ -973,6 +1021,9 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kBwThreads);
+  // gated launches (only the chunks the forward flagged do work): sixteen chunks per CTA
+  const int cpc = 16;
+  dim3 ggrid((NCB + cpc - 1) / cpc, d->H);
   // Shapes with tensor-memory kernels: those handle every chunk the forward did not flag, the general
   // kernels below are launched gated on the flags and pick up the rest.
   const char* off = getenv("NHA_B200_NO_UMMA");
@@ -994,7 +1045,8 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
       st = bwd_umma_launch(d, wu, 0, err, cs);
       if (st != NHA_OK) return st;
     }
-    nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, wg);
+    if (umma) nha_bwd_window_rows_kernel<<<ggrid, block, L1.total, cs>>>(*d, wg, cpc);
+    else nha_bwd_window_rows_kernel<<<grid, block, L1.total, cs>>>(*d, wg, 1);
     st = check_launch();
     if (st != NHA_OK) return st;
   }
@@ -1010,12 +1062,14 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 4) {
-    nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, wg);
+    if (umma) nha_bwd_slot_kernel<<<ggrid, block, L3.total, cs>>>(*d, wg, cpc);
+    else nha_bwd_slot_kernel<<<grid, block, L3.total, cs>>>(*d, wg, 1);
     st = check_launch();
     if (st != NHA_OK) return st;
   }
   if (stage_mask & 8) {
-    nha_bwd_local_terms_kernel<<<grid, block, L5.total, cs>>>(*d, wg);
+    if (umma) nha_bwd_local_terms_kernel<<<ggrid, block, L5.total, cs>>>(*d, wg, cpc);
+    else nha_bwd_local_terms_kernel<<<grid, block, L5.total, cs>>>(*d, wg, 1);
     st = check_launch();
     if (st != NHA_OK) return st;
     const int SD = d->K * d->M + d->M * d->V;
@@ -1028,7 +1082,8 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
       st = bwd_umma_launch(d, wu, 1, err, cs);
       if (st != NHA_OK) return st;
     }
-    nha_bwd_inter_kernel<<<grid, block, L4.total, cs>>>(*d, wg);
+    if (umma) nha_bwd_inter_kernel<<<ggrid, block, L4.total, cs>>>(*d, wg, cpc);
+    else nha_bwd_inter_kernel<<<grid, block, L4.total, cs>>>(*d, wg, 1);
     st = check_launch();
   }
   return st;

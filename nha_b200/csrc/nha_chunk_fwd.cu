@@ -109,11 +109,11 @@ __device__ __forceinline__ void tril_to_bf16(bf16* AB, int ldab, const float* SA
 
 // `only_flagged` (optional): [chunks, H] flags; when given, a CTA whose flag is zero has nothing to do
 // (the tensor-memory kernel already produced that chunk).
-__global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_chunk_desc d, const int* __restrict__ only_flagged) {
+__device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d, const int* __restrict__ only_flagged, const int cgb) {
   using namespace nvcuda::wmma;
   const int K = d.K, V = d.V, M = d.M, H = d.H, HQ = d.HQ, NG = HQ / H;
   const int N = d.N;
-  const int cg = blockIdx.x;                       // global chunk index
+  const int cg = cgb;                       // global chunk index
   const int h = blockIdx.y;
   const int n = d.plan[N + 1 + cg];
   if (n < 0) return;
@@ -376,6 +376,18 @@ __global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_ch
   }
 }
 
+// One CTA walks `cpc` consecutive chunks (1 when the kernel handles every chunk; more when it is launched gated
+// on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
+__global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_chunk_desc d, const int* __restrict__ only_flagged, const int cpc) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  for (int i = 0; i < cpc; ++i) {
+    const int cgb = blockIdx.x * cpc + i;
+    if (cgb >= ncb) return;
+    nha_chunk_fwd_kernel_body(d, only_flagged, cgb);
+    __syncthreads();
+  }
+}
+
 int64_t state_workspace_bytes(const nha_chunk_desc* d);
 int check_chunk_desc(const nha_chunk_desc* d);
 int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs);
@@ -417,7 +429,13 @@ extern "C" int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream) {
   cudaError_t e = cudaFuncSetAttribute(nha_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   dim3 grid(NCB, d->H), block(kFwdThreads);
-  nha_chunk_fwd_kernel<<<grid, block, L.total, cs>>>(*d, umma_done ? flags : nullptr);
+  if (umma_done) {
+    // only the flagged chunks do work: sixteen chunks per CTA keep an all-clear launch short
+    const int cpc = 16;
+    nha_chunk_fwd_kernel<<<dim3((grid.x + cpc - 1) / cpc, grid.y), block, L.total, cs>>>(*d, flags, cpc);
+  } else {
+    nha_chunk_fwd_kernel<<<grid, block, L.total, cs>>>(*d, nullptr, 1);
+  }
   return check_launch();
 }
 
