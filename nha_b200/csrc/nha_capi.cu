@@ -1,6 +1,10 @@
 // Status plumbing and size helpers of the C ABI.
 #include <string.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "nha_common.cuh"
 
 namespace nha {
@@ -17,6 +21,20 @@ int check_launch() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return record_cuda_error(e);
   return NHA_OK;
+}
+
+cudaError_t set_max_smem(const void* func, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> granted;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = granted.find({dev, func});
+  if (it != granted.end() && it->second >= bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) granted[{dev, func}] = bytes;
+  return e;
 }
 
 }  // namespace nha

@@ -151,10 +151,20 @@ __device__ __forceinline__ void nha_bwd_window_rows_kernel_body(const nha_chunk_
 // on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
 __global__ void __launch_bounds__(kBwThreads) nha_bwd_window_rows_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
   const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
-  for (int i = 0; i < cpc; ++i) {
-    const int cgb = blockIdx.x * cpc + i;
-    if (cgb >= ncb) return;
-    nha_bwd_window_rows_kernel_body(d, w, cgb);
+  // which of my chunks have work: one flag load per chunk, all at once (cpc <= 32)
+  __shared__ unsigned todo;
+  if (threadIdx.x < 32) {
+    const int cgl = blockIdx.x * cpc + threadIdx.x;
+    const bool mine = (int)threadIdx.x < cpc && cgl < ncb && chunk_gate(w, cgl, blockIdx.y, d.H);
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (threadIdx.x == 0) todo = m;
+  }
+  __syncthreads();
+  unsigned left = todo;
+  while (left) {
+    const int i = __ffs(left) - 1;
+    left &= left - 1;
+    nha_bwd_window_rows_kernel_body(d, w, blockIdx.x * cpc + i);
     __syncthreads();
   }
 }
@@ -592,10 +602,20 @@ __device__ __forceinline__ void nha_bwd_slot_kernel_body(const nha_chunk_desc d,
 // on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
 __global__ void __launch_bounds__(kBwThreads) nha_bwd_slot_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
   const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
-  for (int i = 0; i < cpc; ++i) {
-    const int cgb = blockIdx.x * cpc + i;
-    if (cgb >= ncb) return;
-    nha_bwd_slot_kernel_body(d, w, cgb);
+  // which of my chunks have work: one flag load per chunk, all at once (cpc <= 32)
+  __shared__ unsigned todo;
+  if (threadIdx.x < 32) {
+    const int cgl = blockIdx.x * cpc + threadIdx.x;
+    const bool mine = (int)threadIdx.x < cpc && cgl < ncb && chunk_gate(w, cgl, blockIdx.y, d.H);
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (threadIdx.x == 0) todo = m;
+  }
+  __syncthreads();
+  unsigned left = todo;
+  while (left) {
+    const int i = __ffs(left) - 1;
+    left &= left - 1;
+    nha_bwd_slot_kernel_body(d, w, blockIdx.x * cpc + i);
     __syncthreads();
   }
 }
@@ -677,10 +697,20 @@ __device__ __forceinline__ void nha_bwd_local_terms_kernel_body(const nha_chunk_
 // on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
 __global__ void __launch_bounds__(kBwThreads) nha_bwd_local_terms_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
   const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
-  for (int i = 0; i < cpc; ++i) {
-    const int cgb = blockIdx.x * cpc + i;
-    if (cgb >= ncb) return;
-    nha_bwd_local_terms_kernel_body(d, w, cgb);
+  // which of my chunks have work: one flag load per chunk, all at once (cpc <= 32)
+  __shared__ unsigned todo;
+  if (threadIdx.x < 32) {
+    const int cgl = blockIdx.x * cpc + threadIdx.x;
+    const bool mine = (int)threadIdx.x < cpc && cgl < ncb && chunk_gate(w, cgl, blockIdx.y, d.H);
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (threadIdx.x == 0) todo = m;
+  }
+  __syncthreads();
+  unsigned left = todo;
+  while (left) {
+    const int i = __ffs(left) - 1;
+    left &= left - 1;
+    nha_bwd_local_terms_kernel_body(d, w, blockIdx.x * cpc + i);
     __syncthreads();
   }
 }
@@ -963,10 +993,25 @@ __device__ __forceinline__ void nha_bwd_inter_kernel_body(const nha_chunk_desc d
 // on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
 __global__ void __launch_bounds__(kBwThreads) nha_bwd_inter_kernel(const nha_chunk_desc d, const BwdWs w, const int cpc) {
   const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
-  for (int i = 0; i < cpc; ++i) {
-    const int cgb = blockIdx.x * cpc + i;
-    if (cgb >= ncb) return;
-    nha_bwd_inter_kernel_body(d, w, cgb);
+  // which of my chunks have work: one flag load per chunk, all at once (cpc <= 32)
+  __shared__ unsigned todo;
+  if (threadIdx.x < 32) {
+    const int cgl = blockIdx.x * cpc + threadIdx.x;
+    // (the CTA of a sequence's first chunk always runs: it finishes the sequence's tail rows)
+    bool mine = (int)threadIdx.x < cpc && cgl < ncb;
+    if (mine && !chunk_gate(w, cgl, blockIdx.y, d.H)) {
+      const int n = d.plan[d.N + 1 + cgl];
+      mine = n >= 0 && d.plan[n] == cgl;
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (threadIdx.x == 0) todo = m;
+  }
+  __syncthreads();
+  unsigned left = todo;
+  while (left) {
+    const int i = __ffs(left) - 1;
+    left &= left - 1;
+    nha_bwd_inter_kernel_body(d, w, blockIdx.x * cpc + i);
     __syncthreads();
   }
 }
@@ -1007,17 +1052,17 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   if (L1.total > kMaxSmem || L2.total > kMaxSmem || L3.total > kMaxSmem || L4.total > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t cs = (cudaStream_t)stream;
   cudaError_t e;
-  e = cudaFuncSetAttribute(nha_bwd_window_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L1.total);
+  e = set_max_smem((const void*)nha_bwd_window_rows_kernel, L1.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  e = cudaFuncSetAttribute(nha_bwd_window_cols_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L2.total);
+  e = set_max_smem((const void*)nha_bwd_window_cols_kernel, L2.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  e = cudaFuncSetAttribute(nha_bwd_slot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L3.total);
+  e = set_max_smem((const void*)nha_bwd_slot_kernel, L3.total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  e = cudaFuncSetAttribute(nha_bwd_inter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L4.total);
+  e = set_max_smem((const void*)nha_bwd_inter_kernel, L4.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const LocalLayout L5 = local_layout(d->K, d->V, d->M);
   if (L5.total > kMaxSmem) return NHA_ERR_SMEM;
-  e = cudaFuncSetAttribute(nha_bwd_local_terms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L5.total);
+  e = set_max_smem((const void*)nha_bwd_local_terms_kernel, L5.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   dim3 grid(NCB, d->H), block(kBwThreads);

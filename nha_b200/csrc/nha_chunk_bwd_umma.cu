@@ -1116,7 +1116,7 @@ __global__ void __launch_bounds__(kColsThreads, (D == 64 && R == 64) ? 2 : 1)
 template <int D, int R>
 static int launch_rows(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs) {
   typedef RowsLayout<D, R> L;
-  cudaError_t e = cudaFuncSetAttribute(nha_bwd_rows_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  cudaError_t e = set_max_smem((const void*)nha_bwd_rows_umma_kernel<D, R>, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   nha_bwd_rows_umma_kernel<D, R><<<dim3(NCB, d->H), kRowsThreads, L::total, cs>>>(*d, w, err);
@@ -1126,7 +1126,7 @@ static int launch_rows(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaSt
 template <int D, int R>
 static int launch_cols(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs) {
   typedef ColsLayout<D, R> L;
-  cudaError_t e = cudaFuncSetAttribute(nha_bwd_cols_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  cudaError_t e = set_max_smem((const void*)nha_bwd_cols_umma_kernel<D, R>, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   nha_bwd_gate_carry_kernel<<<dim3(NCB, d->H), kCarryThreads, 0, cs>>>(*d, w);

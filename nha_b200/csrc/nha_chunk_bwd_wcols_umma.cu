@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nh
 template <int D>
 static int launch_wcols(const nha_chunk_desc* d, const BwdWs& w, int* err, cudaStream_t cs) {
   typedef WColsLayout<D> L;
-  cudaError_t e = cudaFuncSetAttribute(nha_bwd_wcols_umma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  cudaError_t e = set_max_smem((const void*)nha_bwd_wcols_umma_kernel<D>, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   nha_bwd_wcols_umma_kernel<D><<<dim3(NCB, d->H), kWCThreads, L::total, cs>>>(*d, w, err);

@@ -380,10 +380,21 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
 // on the chunk flags and most chunks return at once, so that an all-clear launch costs few CTAs).
 __global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_chunk_desc d, const int* __restrict__ only_flagged, const int cpc) {
   const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
-  for (int i = 0; i < cpc; ++i) {
-    const int cgb = blockIdx.x * cpc + i;
-    if (cgb >= ncb) return;
-    nha_chunk_fwd_kernel_body(d, only_flagged, cgb);
+  // which of my chunks have work: one flag load per chunk, all at once (cpc <= 32)
+  __shared__ unsigned todo;
+  if (threadIdx.x < 32) {
+    const int cgl = blockIdx.x * cpc + threadIdx.x;
+    const bool mine = (int)threadIdx.x < cpc && cgl < ncb &&
+                      (only_flagged == nullptr || only_flagged[(size_t)cgl * d.H + blockIdx.y] != 0);
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (threadIdx.x == 0) todo = m;
+  }
+  __syncthreads();
+  unsigned left = todo;
+  while (left) {
+    const int i = __ffs(left) - 1;
+    left &= left - 1;
+    nha_chunk_fwd_kernel_body(d, only_flagged, blockIdx.x * cpc + i);
     __syncthreads();
   }
 }
@@ -426,7 +437,7 @@ extern "C" int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream) {
   }
   const FwdLayout L = fwd_layout(d->K, d->V, d->M);
   if (L.total > kMaxSmem) return umma_done ? NHA_OK : NHA_ERR_SMEM;
-  cudaError_t e = cudaFuncSetAttribute(nha_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+  cudaError_t e = set_max_smem((const void*)nha_chunk_fwd_kernel, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   dim3 grid(NCB, d->H), block(kFwdThreads);
   if (umma_done) {

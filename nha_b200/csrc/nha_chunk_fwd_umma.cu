@@ -690,7 +690,7 @@ static bool make_window_map(CUtensorMap* m, const void* base, int64_t Ttot, int 
 template <int D, int R>
 static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
   typedef UmmaLayout<D, R> L;
-  cudaError_t e = cudaFuncSetAttribute(nha_fwd_umma_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+  cudaError_t e = set_max_smem((const void*)nha_fwd_umma_kernel<D, R>, L::total);
   if (e != cudaSuccess) return record_cuda_error(e);
   WindowMaps maps;
   memset(&maps, 0, sizeof(maps));

@@ -224,7 +224,7 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   w.local = (float*)scratch;
   w.gend = w.local + (int64_t)NCB * d->H * SD;
   const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
-  cudaError_t e = cudaFuncSetAttribute(nha_state_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+  cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
   int st = check_launch();

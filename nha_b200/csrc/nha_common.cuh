@@ -20,6 +20,9 @@ constexpr int kMaxSmem = 227 * 1024;
 // ---- status plumbing -------------------------------------------------------------------------
 int record_cuda_error(cudaError_t e);   // stores the text for nha_last_cuda_error(), returns NHA_ERR_LAUNCH
 int check_launch();                     // cudaGetLastError() -> status
+// raises a kernel's dynamic shared-memory limit; remembered per (device, kernel), so the runtime is asked only
+// the first time or when more is needed
+cudaError_t set_max_smem(const void* func, int bytes);
 
 // ---- small device utilities ------------------------------------------------------------------
 __device__ __forceinline__ float bf2f(bf16 x) { return __bfloat162float(x); }

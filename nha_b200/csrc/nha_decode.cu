@@ -553,7 +553,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   dim3 grid(B * H * a.SPLITS), block(kDecThreads);
 #define NHA_LAUNCH_DECODE(KT_, VT_)                                                                               \
   do {                                                                                                            \
-    cudaError_t e = cudaFuncSetAttribute(nha_decode_kernel<KT_, VT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+    cudaError_t e = set_max_smem((const void*)nha_decode_kernel<KT_, VT_>, \
                                          smem);                                                                   \
     if (e != cudaSuccess) return record_cuda_error(e);                                                            \
     nha_decode_kernel<KT_, VT_><<<grid, block, smem, st>>>(a);                                                    \

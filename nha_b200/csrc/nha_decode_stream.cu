@@ -512,11 +512,11 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   dim3 grid(a.B * a.H * a.SPLITS), block(kStrThreads);
   cudaError_t e;
   if (D == 128) {
-    e = cudaFuncSetAttribute(nha_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = set_max_smem((const void*)nha_decode_stream_kernel<128>, smem);
     if (e != cudaSuccess) return record_cuda_error(e);
     nha_decode_stream_kernel<128><<<grid, block, smem, st>>>(a);
   } else {
-    e = cudaFuncSetAttribute(nha_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = set_max_smem((const void*)nha_decode_stream_kernel<64>, smem);
     if (e != cudaSuccess) return record_cuda_error(e);
     nha_decode_stream_kernel<64><<<grid, block, smem, st>>>(a);
   }
