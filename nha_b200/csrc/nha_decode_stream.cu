@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);
     bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);
   }
-  // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = warp + 8 j.  The first
+  // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = kRowsPer warp + j.  The first
   // block of columns (all of them unless the split owns more than 32 slots) is fetched now.
   constexpr int kRowsPer = K / kStrWarps;
   float hreg[kRowsPer];
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   if (!a.zero_state && nslots > 0) {
 #pragma unroll
     for (int j = 0; j < kRowsPer; ++j)
-      hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + warp + kStrWarps * j) * M + m0 + lane] : 0.f;
+      hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane] : 0.f;
   }
   // ---- the popped token, the gates and the queries: disjoint groups of threads, so that the loads of the four
   //      small inputs overlap instead of queueing behind one another --------------------------------------------
@@ -209,24 +209,31 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     if (cb > 0 && !a.zero_state) {
 #pragma unroll
       for (int j = 0; j < kRowsPer; ++j)
-        hreg[j] = m < nslots ? a.hk[((size_t)bh * K + warp + kStrWarps * j) * M + m0 + m] : 0.f;
+        hreg[j] = m < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + m] : 0.f;
     }
     const float e = m < MQ ? eg[m] : 1.f, sm = m < MQ ? sv[m] : 0.f;
-    float acc[16];
-#pragma unroll
-    for (int qh = 0; qh < 16; ++qh) acc[qh] = 0.f;
+    float hval[kRowsPer];
 #pragma unroll
     for (int j = 0; j < kRowsPer; ++j) {
-      const int kk = warp + kStrWarps * j;
-      const float hval = (a.zero_state ? 0.f : hreg[j]) * e + kpop[kk] * sm;
-      if (m < nslots) a.hk[((size_t)bh * K + kk) * M + m0 + m] = hval;
-#pragma unroll
-      for (int qh = 0; qh < 16; ++qh)
-        if (qh < NG) acc[qh] += bf2f(qs[qh * K + kk]) * hval;
+      const int kk = kRowsPer * warp + j;
+      hval[j] = (a.zero_state ? 0.f : hreg[j]) * e + kpop[kk] * sm;
+      if (m < nslots) a.hk[((size_t)bh * K + kk) * M + m0 + m] = hval[j];
     }
+    // this warp's rows of every query head: 16-byte loads of the raw query (the same address for all lanes)
 #pragma unroll
-    for (int qh = 0; qh < 16; ++qh)
-      if (qh < NG) red[(warp * NG + qh) * 32 + lane] = acc[qh];
+    for (int qh = 0; qh < 16; ++qh) {
+      if (qh < NG) {
+        float acc = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < kRowsPer / 8; ++c8) {
+          float q8[8];
+          unpack8(*reinterpret_cast<const uint4*>(qs + qh * K + kRowsPer * warp + 8 * c8), q8);
+#pragma unroll
+          for (int e8 = 0; e8 < 8; ++e8) acc += q8[e8] * hval[8 * c8 + e8];
+        }
+        red[(warp * NG + qh) * 32 + lane] = acc;
+      }
+    }
     __syncthreads();
     for (int i = tid; i < NG * 32; i += kStrThreads) {
       const int qh = i >> 5, l = i & 31;
