@@ -377,9 +377,9 @@ def main():
     top = max(kernels, key=lambda k: kernels[k]['ms'])
     peak, how = peaks()
     # DRAM bytes per token of the stage's dominant kernel from the committed ncu capture (B=4 case; traffic grows
-    # in proportion to the tokens): profiles/bwd_rows_umma_B4_T2048.md 341.2 MB, profiles/fwd_umma_B4_T2048.md
-    # 162.3 MB, each for 8192 tokens
-    ncu_traffic_per_tok = {'bwd_rows': 341.2e6 / 8192, 'output_pass': 162.3e6 / 8192}
+    # in proportion to the tokens): profiles/bwd_rows_umma_B4_T2048.md 311.0 MB, profiles/fwd_umma_B4_T2048.md
+    # 161.4 MB, each for 8192 tokens
+    ncu_traffic_per_tok = {'bwd_rows': 311.0e6 / 8192, 'output_pass': 161.4e6 / 8192}
     traffic = ncu_traffic_per_tok[top] * tokens if top in ncu_traffic_per_tok else None
     roofline = {'bound': 'hbm', 'kernel': top, 'achieved': kernels[top]['gbs'], 'peak': peak, 'unit': 'GB/s',
                 'frac': kernels[top]['gbs'] / peak, 'traffic': traffic, 'peak_source': how,
