@@ -2,8 +2,8 @@
 // dv.  One CTA per (key chunk, kv head).  The query rows that can see the chunk - every (query chunk,
 // query head of the group) pair - are taken two 64-row blocks at a time as the 128 rows of
 //     S = q_swa k_swa^T,   dP = do v^T                           (tcgen05.mma, accumulators in TMEM)
-// with one thread per query row for p = exp(scale S - L) and dz = scale p (dP - delta): the row's joint
-// log-sum-exp L and delta = <do, o> sit in registers.  The transposed products
+// with two threads per query row (alternate 32-key halves) for p = exp(scale S - L) and dz = scale p (dP - delta):
+// the row's joint log-sum-exp L and delta = <do, o> sit in registers.  The transposed products
 //     dv_win += p^T do,   dk_swa += dz^T q_swa
 // read p, dz, do and q_swa through MN-major descriptors (k = query row), so nothing is transposed in
 // memory.  The window part does not depend on the gates, so every chunk takes this path.
@@ -18,7 +18,7 @@ namespace nha {
 
 using namespace umma;
 
-constexpr int kWCThreads = 128;
+constexpr int kWCThreads = 256;          // two threads per query row (alternate 32-key halves)
 
 template <int D>
 struct WColsLayout {
@@ -37,7 +37,7 @@ struct WColsLayout {
 };
 
 template <int D>
-__global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nha_chunk_desc d, const BwdWs w,
+__global__ void __launch_bounds__(kWCThreads, D == 64 ? 2 : 1) nha_bwd_wcols_umma_kernel(const nha_chunk_desc d, const BwdWs w,
                                                                         int* __restrict__ err) {
   typedef WColsLayout<D> L;
   constexpr int KT = L::KT;
@@ -64,20 +64,24 @@ __global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nh
   const int nblk = (qi_hi - qi_lo + 1) * NG;
   const int npairs = (nblk + 1) >> 1;
 
-  load_sw<D>(sm + L::tK, 8192, (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0, 0, len, 64, 0, tid);
-  load_sw<D>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0, 0, len, 64, 0, tid);
+  load_sw<D, kWCThreads>(sm + L::tK, 8192, (const bf16*)d.k_swa + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0, 0, len, 64, 0, tid);
+  load_sw<D, kWCThreads>(sm + L::tV, 8192, (const bf16*)d.v + ((size_t)t0 * H + h) * D, (int64_t)H * D, c0, 0, len, 64, 0, tid);
   if (tid == 0) mbar_init(mbar, 1);
   if (warp == 0) tmem_alloc(tslot, L::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tbase = *tslot;
-  const uint32_t tlane = tbase + ((uint32_t)(warp * 32) << 16);
+  const int quarter = warp & 3, chalf = warp >> 2;    // TMEM lane quarter of this warp; key half it works on
+  const uint32_t tlane = tbase + ((uint32_t)(quarter * 32) << 16);
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float sc2 = d.scale * kLog2e;
   uint32_t phase = 0;
   bool failed = false;
   const uint32_t aK = smem_u32(sm + L::tK), aV = smem_u32(sm + L::tV), aQS = smem_u32(sm + L::tQS);
   const uint32_t aDO = smem_u32(sm + L::tDO), aP = smem_u32(sm + L::tP), aZ = smem_u32(sm + L::tZ);
-  const int half = tid >> 6, tk = tid & 63;            // this thread's row: block of the pair, query inside the chunk
+  const int row = quarter * 32 + lane;                // this thread's row of the 128-row products
+  const int half = row >> 6, tk = row & 63;           // block of the pair, query inside the chunk
 
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
@@ -101,9 +105,9 @@ __global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nh
       const int b = 2 * pr + t2;
       const bool valid = b < nblk;
       const int qi = qi_lo + (valid ? b / NG : 0), hq = h * NG + (valid ? b % NG : 0);
-      load_sw<D>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq) * D, (int64_t)HQ * D, qi * kChunk, 0,
+      load_sw<D, kWCThreads>(sm + L::tQS, L::kATile, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq) * D, (int64_t)HQ * D, qi * kChunk, 0,
                  valid ? len : 0, 64, 64 * t2, tid);
-      load_sw<D>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * D, (int64_t)HQ * D, qi * kChunk, 0,
+      load_sw<D, kWCThreads>(sm + L::tDO, L::kATile, (const bf16*)d.d_o + ((size_t)t0 * HQ + hq) * D, (int64_t)HQ * D, qi * kChunk, 0,
                  valid ? len : 0, 64, 64 * t2, tid);
     }
     cp_commit();
@@ -124,25 +128,25 @@ __global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nh
     }
     NHA_MMA_WAIT();
     {
+      // visible keys of this query row: klo <= key <= pq, tested as (unsigned)(key - klo) <= kspan
+      const int klo = live ? (wl < 0 ? 0 : max(0, pq - wl)) : (1 << 30);
+      const unsigned kspan = live ? (unsigned)(pq - klo) : 0u;
+      const float nLj = -Lj * kLog2e;
+      const int off = c0 + 32 * chalf - klo;
       float sv[32], dp[32];
+      tmem_ld32(tlane + L::cS + 32 * chalf, sv);
+      tmem_ld32(tlane + L::cDP + 32 * chalf, dp);
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        tmem_ld32(tlane + L::cS + 32 * part, sv);
-        tmem_ld32(tlane + L::cDP + 32 * part, dp);
+      for (int c8 = 0; c8 < 4; ++c8) {
+        float p8[8], z8[8];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          float p8[8], z8[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int key = c0 + 32 * part + 8 * c8 + e;
-            const bool vis = live && key <= pq && (wl < 0 || key >= pq - wl);
-            const float p = vis ? __expf(sv[8 * c8 + e] * d.scale - Lj) : 0.f;
-            p8[e] = p;
-            z8[e] = p * (dp[8 * c8 + e] - delta) * d.scale;
-          }
-          *reinterpret_cast<uint4*>(sm + L::tP + sw_off(tid, 4 * part + c8)) = pack8(p8);
-          *reinterpret_cast<uint4*>(sm + L::tZ + sw_off(tid, 4 * part + c8)) = pack8(z8);
+        for (int e = 0; e < 8; ++e) {
+          const float p = (unsigned)(off + 8 * c8 + e) <= kspan ? exp2f(fmaf(sv[8 * c8 + e], sc2, nLj)) : 0.f;
+          p8[e] = p;
+          z8[e] = p * (dp[8 * c8 + e] - delta) * d.scale;
         }
+        *reinterpret_cast<uint4*>(sm + L::tP + sw_off(row, 4 * chalf + c8)) = pack8(p8);
+        *reinterpret_cast<uint4*>(sm + L::tZ + sw_off(row, 4 * chalf + c8)) = pack8(z8);
       }
     }
     NHA_SMEM_TO_MMA();
@@ -161,33 +165,28 @@ __global__ void __launch_bounds__(kWCThreads) nha_bwd_wcols_umma_kernel(const nh
   }
 #undef NHA_MMA_WAIT
 #undef NHA_SMEM_TO_MMA
-  // ---- one thread per key row: rows of a 64-row product sit in the first 16 lanes of each warp ---------------
+  // ---- two threads per key row (rows of a 64-row product sit in the first 16 lanes of each quarter), each its half
+  //      of the columns
   {
     const bool kactive = lane < 16;
-    const int krow = warp * 16 + (lane & 15);
+    const int krow = quarter * 16 + (lane & 15);
     const int pk = c0 + krow;
     const bool keep = kactive && pk < len && !failed;
     float ov[32];
 #pragma unroll
-    for (int part = 0; part < D / 32; ++part) {
+    for (int pp = 0; pp < D / 64; ++pp) {
+      const int part = (D / 64) * chalf + pp;
       tmem_ld32(tlane + L::cDK + 32 * part, ov);
       if (keep) {
         bf16* orow = (bf16*)d.dk_swa + ((size_t)(t0 + pk) * H + h) * D + 32 * part;
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          float o8[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) o8[e] = npairs > 0 ? ov[8 * c8 + e] : 0.f;
-          *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(o8);
-        }
+        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 8 * c8) = pack8(ov + 8 * c8);
       }
       tmem_ld32(tlane + L::cDV + 32 * part, ov);
       if (keep) {
         float* orow = w.dvacc + ((size_t)(t0 + pk) * H + h) * D + 32 * part;
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          *reinterpret_cast<float4*>(orow + e) = npairs > 0 ? make_float4(ov[e], ov[e + 1], ov[e + 2], ov[e + 3])
-                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(orow + e) = make_float4(ov[e], ov[e + 1], ov[e + 2], ov[e + 3]);
       }
     }
   }
