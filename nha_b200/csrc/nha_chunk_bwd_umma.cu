@@ -55,7 +55,7 @@ struct RowsLayout {
   static constexpr int oBar = oX + 1024;
   static constexpr int total = oBar + 64 + 1024;
   // One head per CTA (R == 64): tiles are reused as soon as the last product that reads them has completed.
-  //   v' and Hv are read by round 1 only      -> p .* a and p .* exp(G) (operands of the local terms, and the
+  //   v' and Hv are read by MMA group 1 only      -> p .* a and p .* exp(G) (operands of the local terms, and the
   //                                              source of the coalesced copy-out of the four bf16 copies)
   //   k' and Hk are dead after dq_gsa          -> window keys / values of the even window tiles
   //   q_gsa is dead after the local terms     -> window keys of the odd window tiles (values: tWVx)
@@ -770,7 +770,7 @@ struct ColsLayout {
   static constexpr int eS = eV + 64 * kLdV * 4;         // [64][72] bf16 s'
   static_assert(eS + 64 * kLdS * 2 <= tK, "the staged epilogue inputs must fit in the per-head tiles");
   // D == 64 with one query head per kv head: 256 columns, so two CTAs share an SM; the intra-chunk ds'
-  // accumulator then borrows the dk' columns for one round and waits in registers
+  // accumulator then borrows the dk' columns for one MMA group and waits in registers
   static constexpr bool kDsInRegs = D == 64 && R == 64;
   static constexpr int kTmemCols = kDsInRegs ? 256 : 512;
   static constexpr int cA = 0, cAv = 64, cDK = 128, cDV = 128 + D, cDS = kDsInRegs ? cDK : 128 + 2 * D, cDS2 = cA;

@@ -7,11 +7,11 @@
 // HQ == H) or 64 tokens x 2 heads of the group (R = 128), and the CTA walks the heads of the group
 // reusing the chunk's k', v', gates and chunk-start states.
 //
-// Per tile:   A  = q k'^T,  QH = q Hk,  S = q_swa k_swa^T (newest window step)           round 1
-//             X  = tril(A) (s' .* b)                                                      round 2
+// Per tile:   A  = q k'^T,  QH = q Hk,  S = q_swa k_swa^T (newest window step)           MMA group 1
+//             X  = tril(A) (s' .* b)                                                      MMA group 2
 //             ok = scale a .* (e^R .* QH + X);   window maxima step by step (older steps: load, S, max)
-//             O  = (p~ a e^R) Hv,  Bv = (p~ a)(s' .* b)^T                                  round 3
-//             O += tril(Bv) v' + P~ v_win (newest step, its S still in TMEM)              round 4
+//             O  = (p~ a e^R) Hv,  Bv = (p~ a)(s' .* b)^T                                  MMA group 3
+//             O += tril(Bv) v' + P~ v_win (newest step, its S still in TMEM)              MMA group 4
 //             older window steps: load, S, P~, O += P~ v_win
 // a = exp(G - R), b = exp(R - G) with ONE reference R[m] = Gend[m] / 2 per chunk and slot, kept as a
 // shared fp32 table so the row threads spend no exponentials on the decay.  That keeps every factor
@@ -65,7 +65,7 @@ struct UmmaLayout {
   static constexpr int kThreads = 128 * NS;
   static constexpr int kATile = R * 128;              // one 64-wide k tile of an R-row A operand
   static constexpr int kWTile = TP * 8192;            // one 64-wide k tile of a window-step operand (64 TP rows)
-  static constexpr bool kAlias = R == 64;             // one head per CTA: k' and Hk are dead after round 1
+  static constexpr bool kAlias = R == 64;             // one head per CTA: k' and Hk are dead after MMA group 1
   static constexpr bool kPOverW = R <= D;             // P~ fits over the window keys it was computed from
   static constexpr int tQ = 0;                        // q_gsa; later p~ .* a
   static constexpr int tQS = tQ + KT * kATile;        // q_swa
@@ -83,7 +83,7 @@ struct UmmaLayout {
   static constexpr int tPG = kAlias ? tK : end1 + kATile;   // p~ .* a .* e^R   [R][64]
   static constexpr int end2 = kAlias ? end1 : end1 + 2 * kATile;
   // D = 128 runs one CTA per SM, so the window loops are pipelined inside the CTA: a second set of window
-  // buffers (behind k' and Hk, which are dead after round 1 and fetched again for the next head tile; with one
+  // buffers (behind k' and Hk, which are dead after MMA group 1 and fetched again for the next head tile; with one
   // head per CTA those tiles hold p~ and tril(A), so the set gets room of its own) and a second S accumulator.
   static constexpr bool kPipe = D == 128;
   static constexpr int end3 = (kPipe && kAlias) ? end2 + 2 * KT * kWTile : end2;
@@ -92,7 +92,7 @@ struct UmmaLayout {
   static constexpr int oA = end3;                     // fp32 [64][65]: cumulative gates, then a = exp(G - R)
   static constexpr int oR = oA + 64 * 65 * 4;         // fp32 [64] exp(R)
   static constexpr int oX = oR + 256;                 // fp32 [4][NS][128] row statistics swapped between the column parts
-  static constexpr int oBar = oX + 4 * NS * 128 * 4;  // mbarriers (MMA rounds; loads, S and PV of the pipelined loops) + TMEM slot              // mbarrier + TMEM slot
+  static constexpr int oBar = oX + 4 * NS * 128 * 4;  // mbarriers (MMA groups; loads, S and PV of the pipelined loops) + TMEM slot              // mbarrier + TMEM slot
   static constexpr int total = oBar + 128 + 1024;     // + slack for the 1024-byte alignment of the base
   static constexpr int kTmemCols = D == 64 ? 256 : 512;
   // O reuses QH's columns at D = 64 (QH has been read by then)
@@ -381,7 +381,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 // 64 keys lie inside the sequence comes by TMA (one thread, two or four boxes, bytes counted on the set's mbarrier);
 // a step that sticks out of the sequence is copied with zero fill by every thread and then arrives on the same
 // barrier.  Every thread of the CTA runs the macro.  Issue work is spread over three threads of three warps so that
-// it does not queue behind one thread: thread 0 the MMA rounds and P~ V, thread 32 the TMA loads, thread 64 the S
+// it does not queue behind one thread: thread 0 the MMA groups and P~ V, thread 32 the TMA loads, thread 64 the S
 // products of the loops.
 #define NHA_LOAD_STEP(set_, p_, wv_)                                                                                \
   do {                                                                                                              \
@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
     cp_wait_all();
     NHA_SMEM_TO_MMA();
-    // ---- round 1: A = q k'^T, QH = q Hk, S of the oldest window step --------------------------------------
+    // ---- MMA group 1: A = q k'^T, QH = q Hk, S of the oldest window step --------------------------------------
     if (tid == 0) {
       mma_tile(tbase + L::cA, aQ, L::kATile, aK, 8192, R, 64, D / 16, 0, false);
       mma_tile(tbase + L::cQH, aQ, L::kATile, aHk, 0, R, 64, D / 16, 1, false);
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     NHA_MMA_WAIT();
     NHA_TRIL_TO_SMEM(L::cA, L::tAB);
     NHA_SMEM_TO_MMA();
-    // ---- round 2: X = tril(A) SB; the window maxima are taken while it runs ---------------------------------
+    // ---- MMA group 2: X = tril(A) SB; the window maxima are taken while it runs ---------------------------------
     if (tid == 0) mma_tile(tbase + L::cA, aAB, L::kATile, aSB, 0, R, 64, 4, 1, false);
     float ms = -INFINITY;
     NHA_STEP_MAX(NHA_KBASE(nsteps - 1));
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     // ---- maxima of the newer window steps (the newest one last: its S stays in TMEM) -----------------------------
     int rset = 0;                                      // buffer set / accumulator that hold the newest step afterwards
     if constexpr (L::kPipe) {
-      // step index i counts from the oldest step (i = 0: loaded with the head tile, S formed in round 1); step i uses
+      // step index i counts from the oldest step (i = 0: loaded with the head tile, S formed in MMA group 1); step i uses
       // buffer set and accumulator i & 1.  The load of step i + 1 and the maximum of step i - 1 overlap S of step i.
       if (nsteps > 1) NHA_LOAD_STEP(1, nsteps - 2, nsteps - 2 == 0);
       for (int i = 1; i < nsteps && !failed; ++i) {
@@ -535,7 +535,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       }
     }
     NHA_SMEM_TO_MMA();
-    // ---- round 3: O = (p~ a e^R) Hv, Bv = (p~ a) SB^T; the newest step's P~ is formed while it runs ---------------
+    // ---- MMA group 3: O = (p~ a e^R) Hv, Bv = (p~ a) SB^T; the newest step's P~ is formed while it runs ---------------
     if (tid == 0) {
 #pragma unroll
       for (int ct = 0; ct < KT; ++ct)
@@ -547,7 +547,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     NHA_MMA_WAIT();
     NHA_TRIL_TO_SMEM(L::cA, L::tAB);
     NHA_SMEM_TO_MMA();
-    // ---- round 4: O += tril(Bv) v' + P~ v_win (newest step) -------------------------------------------------------------
+    // ---- MMA group 4: O += tril(Bv) v' + P~ v_win (newest step) -------------------------------------------------------------
     if (tid == 0) {
 #pragma unroll
       for (int ct = 0; ct < KT; ++ct)

@@ -294,7 +294,7 @@ def run_training(ref_chunk, naive_gsa):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference')
+    ap.add_argument('--reference', required=True, help='path of a checkout of the reference project')
     ap.add_argument('--skip-grids', action='store_true')
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, 'scripts'))
