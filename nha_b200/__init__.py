@@ -6,6 +6,8 @@ reference's layers and model classes can call them unchanged.
 from .chunk import chunk_nha
 from .chunk_fused import fused_chunk_nha_prefill
 from .fused_recurrent import fused_recurrent_nha, fused_recurrent_nha_decode
+from .ring_cache import NHARingCache, fused_recurrent_nha_decode_ring
 
-__all__ = ['chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode']
+__all__ = ['chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode',
+           'fused_recurrent_nha_decode_ring', 'NHARingCache']
 __version__ = '0.1.0'

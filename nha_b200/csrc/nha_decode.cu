@@ -464,7 +464,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st);
+                      cudaStream_t st, const int* head, const void* ring_g);
 
 // Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
 // every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
@@ -546,7 +546,8 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   }
   if (stream_ok)
     return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
-                             errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream);
+                             errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, nullptr,
+                             nullptr);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;
@@ -562,5 +563,60 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   else if (K == 64 && V == 64) NHA_LAUNCH_DECODE(64, 64);
   else NHA_LAUNCH_DECODE(0, 0);
 #undef NHA_LAUNCH_DECODE
+  return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode on a device-resident ring buffer: the window keys / values / gate rows of a sequence live in rings of
+// W rows whose oldest entry sits at row head[b].  One step = nha_decode_step_ring (the oldest entry enters the
+// slot memory, the new token is the newest window entry) followed by nha_ring_append (the new token's rows
+// overwrite the oldest entry, head advances) - no window is ever shifted in memory.
+namespace nha {
+
+__global__ void nha_ring_append_kernel(bf16* ring_k, bf16* ring_v, bf16* ring_g, const bf16* k, const bf16* v, const bf16* g,
+                                       int* head, int H, int K, int V, int M, int W) {
+  const int b = blockIdx.x;
+  const int hd = head[b];
+  const size_t row = (size_t)b * W + hd;
+  for (int i = threadIdx.x; i < H * K / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_k + row * H * K)[i] = reinterpret_cast<const uint4*>(k + (size_t)b * H * K)[i];
+  for (int i = threadIdx.x; i < H * V / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_v + row * H * V)[i] = reinterpret_cast<const uint4*>(v + (size_t)b * H * V)[i];
+  for (int i = threadIdx.x; i < H * M / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_g + row * H * M)[i] = reinterpret_cast<const uint4*>(g + (size_t)b * H * M)[i];
+  __syncthreads();
+  if (threadIdx.x == 0) head[b] = hd + 1 == W ? 0 : hd + 1;
+}
+
+}  // namespace nha
+
+extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void* v_new, const void* ring_k,
+                                    const void* ring_v, const void* ring_g, const int32_t* head, const void* cosp,
+                                    const void* sinp, int64_t cs_batch, int64_t cs_row, float* hk, float* hv, void* o,
+                                    void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M,
+                                    int W, float scale, void* stream) {
+  if (!q || !k_new || !v_new || !ring_k || !ring_v || !ring_g || !head || !cosp || !sinp || !hk || !hv || !o)
+    return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1) return NHA_ERR_BAD_ARG;
+  const int NG = HQ / H;
+  if (!decode_stream_supported(K, V, M, W, NG, false) || M % 8) return NHA_ERR_UNSUPPORTED;
+  const int splits = decode_stream_splits(B, H, W, M);
+  if (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W)) return NHA_ERR_WORKSPACE;
+  int* tickets = (int*)workspace;
+  int* errw = tickets + (size_t)B * H;
+  char* base = (char*)workspace + align_up((B * H + 1) * 4, 256);
+  float* part_ml = (float*)base;
+  float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
+  return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
+                           o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, head,
+                           ring_g);
+}
+
+extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
+                               const void* g_new, int32_t* head, int B, int H, int K, int V, int M, int W, void* stream) {
+  if (!ring_k || !ring_v || !ring_g || !k_new || !v_new || !g_new || !head) return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || W < 1 || (H * K) % 8 || (H * V) % 8 || (H * M) % 8) return NHA_ERR_BAD_ARG;
+  nha_ring_append_kernel<<<B, 128, 0, (cudaStream_t)stream>>>((bf16*)ring_k, (bf16*)ring_v, (bf16*)ring_g, (const bf16*)k_new,
+                                                              (const bf16*)v_new, (const bf16*)g_new, head, H, K, V, M, W);
   return check_launch();
 }

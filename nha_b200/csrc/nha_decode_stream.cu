@@ -35,6 +35,11 @@ struct DecodeStreamArgs {
   float* part_ml;     // [B*H, SPLITS, NG, 2] maximum and sum of each split
   int* tickets;       // [B*H] arrival counters, zero between calls
   int* err;           // device error word (a bounded wait ran out)
+  // ring mode (head != NULL): sw_k / sw_v are rings of W physical rows per sequence whose oldest entry sits at
+  // row head[b]; that entry is the token that leaves the window and enters the slot memory in this step (its
+  // gate row comes from ring_g, the popped k / v from the rings), the token of this step (k, v: not yet in the
+  // ring) is the newest window entry
+  const int* head; const bf16* ring_g;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   float scale;
@@ -84,6 +89,12 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   const int m0 = sp * MQ;
   const int nslots = max(0, min(MQ, M - m0));
   const int nloads = 2 * nst;                                      // key stages, then value stages
+  const bool isring = a.head != nullptr;
+  const int hd = isring ? a.head[b] : 0;                             // physical row of the oldest ring entry
+  // the token that enters the slot memory: separate small tensors, or the oldest ring entry
+  const bf16* kpop_g = isring ? a.sw_k + (((size_t)b * W + hd) * a.H + h) * D : a.k + (size_t)bh * D;
+  const bf16* vpop_g = isring ? a.sw_v + (((size_t)b * W + hd) * a.H + h) * D : a.v + (size_t)bh * D;
+  const bf16* gpop_g = isring ? a.ring_g + (((size_t)b * W + hd) * a.H + h) * M : a.g + (size_t)bh * M;
   bool failed = false;
 
   if (tid == 0) {
@@ -103,13 +114,18 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   do {                                                                                              \
     const int j__ = (j_);                                                                           \
     const int st__ = j__ < nst ? j__ : j__ - nst;                                                   \
-    const bf16* src__ = (j__ < nst ? a.sw_k : a.sw_v) +                                             \
-                        (((size_t)b * W + w0 + st__ * kStrStage) * a.H + h) * D + 8 * lc;           \
+    const bf16* base__ = (j__ < nst ? a.sw_k : a.sw_v) + ((size_t)b * W * a.H + h) * D + 8 * lc;    \
+    const bf16* new__ = (j__ < nst ? a.k : a.v) + (size_t)bh * D + 8 * lc;                          \
     unsigned char* dst__ = ring + (j__ % kStrSlots) * kSlotBytes + 16 * lc;                         \
     const int rows__ = min(kStrStage, nkeys - st__ * kStrStage);                                    \
     _Pragma("unroll") for (int r__ = lr; r__ < kStrStage; r__ += kRStep) {                          \
       const bool ok__ = r__ < rows__;                                                               \
-      umma::cp16(dst__ + r__ * ldk * 2, src__ + (size_t)(ok__ ? r__ : 0) * a.H * D, ok__);          \
+      const int lw__ = w0 + st__ * kStrStage + (ok__ ? r__ : 0);      /* logical window index */    \
+      const bf16* src__;                                                                            \
+      if (!isring) src__ = base__ + (size_t)lw__ * a.H * D;                                         \
+      else if (lw__ == W - 1) src__ = new__;                          /* the token of this step */  \
+      else { int pr__ = hd + 1 + lw__; if (pr__ >= W) pr__ -= W; src__ = base__ + (size_t)pr__ * a.H * D; } \
+      umma::cp16(dst__ + r__ * ldk * 2, src__, ok__);                                               \
     }                                                                                               \
     umma::cp_commit();                                                                              \
   } while (0)
@@ -145,7 +161,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     for (int m = tid; m < MQ; m += 64) {
       float e = 1.f, sm = 0.f;
       if (m < nslots) {
-        e = __expf(bf2f(a.g[(size_t)bh * M + m0 + m]));
+        e = __expf(bf2f(gpop_g[m0 + m]));
         sm = a.s ? bf2f(a.s[(size_t)bh * M + m0 + m]) : 1.0f - e;
       }
       eg[m] = e;
@@ -154,14 +170,14 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   } else if (tid < 96) {
     for (int i = tid - 64; i < (K >> 3); i += 32) {
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(a.k + (size_t)bh * K + 8 * i), f);
+      unpack8(*reinterpret_cast<const uint4*>(kpop_g + 8 * i), f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) kpop[8 * i + e] = f[e];
     }
   } else if (tid < 128) {
     for (int i = tid - 96; i < (V >> 3); i += 32) {
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(a.v + (size_t)bh * V + 8 * i), f);
+      unpack8(*reinterpret_cast<const uint4*>(vpop_g + 8 * i), f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) vpop[8 * i + e] = f[e];
     }
@@ -535,13 +551,14 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st) {
+                      cudaStream_t st, const int* head, const void* ring_g) {
   DecodeStreamArgs a;
   a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
   a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
   a.sinp = (const bf16*)sinp;
   a.hk = hk; a.hv = hv; a.o = (bf16*)o;
   a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.err = err;
+  a.head = head; a.ring_g = (const bf16*)ring_g;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
   a.zero_state = zero_state; a.scale = scale;
