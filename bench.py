@@ -201,7 +201,45 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     ms = timed(step, 10) / 10
     per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
     gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
+    # the same stack with the cache maintenance of one generated token inside the timed region: the reference's
+    # NHACache shifts each layer's window with torch.cat (keys, values, gate rows) and pops the oldest entry; the
+    # ring cache replaces that with nha_decode_step_ring + nha_ring_append
+    gnew = [(F.logsigmoid(mk(B, H, M)) / 8).bfloat16() for _ in range(LAYERS)]
+    gwin = [(F.logsigmoid(mk(B, W, H, M)) / 8).bfloat16() for _ in range(LAYERS)]
+
+    def step_shift():
+        for d, gn, li in zip(layers, gnew, range(LAYERS)):
+            pk, pv, pg = d['sw_k'][:, :1].contiguous(), d['sw_v'][:, :1].contiguous(), gwin[li][:, :1].contiguous()
+            d['sw_k'] = torch.cat([d['sw_k'][:, 1:], d['k'][:, None]], 1)
+            d['sw_v'] = torch.cat([d['sw_v'][:, 1:], d['v'][:, None]], 1)
+            gwin[li] = torch.cat([gwin[li][:, 1:], gn[:, None]], 1)
+            st = lib.nha_decode_step(d['q'].data_ptr(), None, pk.data_ptr(), pv.data_ptr(), pg.data_ptr(), None,
+                                     d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), cos.data_ptr(), sin.data_ptr(), 0,
+                                     cos.stride(1), None, d['hk'].data_ptr(), d['hv'].data_ptr(), 0, d['o'].data_ptr(), None,
+                                     ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, K ** -0.5, stream)
+            assert st == 0
+    heads = [torch.zeros(B, dtype=torch.int32, device=dev) for _ in range(LAYERS)]
+
+    def step_ring():
+        for d, gn, gw, hd in zip(layers, gnew, gwin, heads):
+            st = lib.nha_decode_step_ring(d['q'].data_ptr(), d['k'].data_ptr(), d['v'].data_ptr(), d['sw_k'].data_ptr(),
+                                          d['sw_v'].data_ptr(), gw.data_ptr(), hd.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                          0, cos.stride(1), d['hk'].data_ptr(), d['hv'].data_ptr(), d['o'].data_ptr(),
+                                          ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, K ** -0.5, stream)
+            assert st == 0
+            st = lib.nha_ring_append(d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), d['k'].data_ptr(),
+                                     d['v'].data_ptr(), gn.data_ptr(), hd.data_ptr(), B, H, K, K, M, W, stream)
+            assert st == 0
+    for _ in range(2):
+        step_shift()
+        step_ring()
+    ms_shift = timed(step_shift, 5) / 5
+    ms_ring = timed(step_ring, 5) / 5
+    with_cache = {'shifted_window_us_per_layer': 1e3 * ms_shift / LAYERS, 'ring_us_per_layer': 1e3 * ms_ring / LAYERS,
+                  'ring_tokens_per_s': world * B / (ms_ring * 1e-3),
+                  'note': 'one generated token per sequence including the window cache update of every layer'}
     return {'workload': 'decode 48 layers x 32 seq/GPU HQ32 H4 D128 M64 W512 bf16, fp32 state', 'ms_per_token_step': ms,
+            'with_cache_update': with_cache,
             'tokens_per_s': world * B / (ms * 1e-3), 'us_per_layer': 1e3 * ms / LAYERS,
             'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': peak, 'unit': 'GB/s', 'frac': gbs / peak,
                          'algorithmic_bytes_per_launch': per_seq_layer * B}, 'gpu_launches_per_step': LAYERS}
