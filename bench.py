@@ -275,6 +275,45 @@ def bench_prefill(dev, rank, world, dist, timed):
                          'frac': flops / (ms * 1e-3) / 1e12 / world / tensor_peak()}}
 
 
+def bench_varlen(dev, rank, timed):
+    """Varlen packed forward + backward: 32768 tokens per GPU, sequence lengths uniform[128, 8192], per-sequence
+    window from {32, 64, 128, 256, 512}, H16 D64 M64, through the public chunk_nha op."""
+    import nha_b200
+    H, D, M, total = 16, 64, 64, 32768
+    g = torch.Generator().manual_seed(7 + rank)
+    lens = []
+    while sum(lens) < total:
+        lens.append(int(torch.randint(128, 8193, (1,), generator=g)))
+    lens[-1] -= sum(lens) - total
+    if lens[-1] < 1:
+        lens[-2] += lens[-1] - 1
+        lens[-1] = 1
+    wins = [int([32, 64, 128, 256, 512][int(torch.randint(0, 5, (1,), generator=g))]) for _ in lens]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    wl = torch.tensor(wins, dtype=torch.int32, device=dev)
+    sh = torch.zeros(len(lens), dtype=torch.int32, device=dev)
+    gd = torch.Generator(device=dev).manual_seed(17 + rank)
+    r = lambda *s: torch.randn(*s, generator=gd, device=dev)
+    x = {n: (r(1, total, H, D) * D ** -0.5).bfloat16().requires_grad_(True) for n in ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v')}
+    gg = F.logsigmoid(r(1, total, H, M)).bfloat16()
+    x['s'] = (1 - gg.float().exp()).bfloat16().detach().requires_grad_(True)
+    x['g'] = gg.detach().requires_grad_(True)
+    do = r(1, total, H, D).bfloat16()
+
+    def step():
+        for t in x.values():
+            t.grad = None
+        o, _, _ = nha_b200.chunk_nha(x['q_swa'], x['k_swa'], x['q_gsa'], x['k_gsa'], x['v'], x['s'], x['g'], cu_seqlens=cu,
+                                     max_seqlen=max(lens), scale=D ** -0.5, window_size_left=wl, window_size_right=0,
+                                     gsa_kv_shift=sh)
+        o.backward(do)
+    for _ in range(3):
+        step()
+    ms = timed(step, 10) / 10
+    return {'workload': f'varlen fwd+bwd, {total} packed tokens in {len(lens)} sequences of 128-8192, windows 32-512, '
+                        f'H16 D64 M64 bf16', 'ms': ms, 'tokens_per_s_per_gpu': total / (ms * 1e-3)}
+
+
 def tensor_peak():
     p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(p):
@@ -495,7 +534,8 @@ def main():
     extras = None
     if not args.no_extras and not args.small:
         extras = {'decode': bench_decode(lib, dev, rank, world, timed, peak),
-                  'prefill': bench_prefill(dev, rank, world, dist, timed)}
+                  'prefill': bench_prefill(dev, rank, world, dist, timed),
+                  'varlen': bench_varlen(dev, rank, timed)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
