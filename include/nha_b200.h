@@ -135,8 +135,9 @@ typedef struct nha_chunk_desc {
   void* hv_chunks;              /* [NC, H, M, V] bf16 */
   /* plan (int32 workspace of nha_chunk_plan_ints(Ttot, N, H) entries, written by nha_chunk_plan):
      [0..N] first chunk of each sequence, [N+1 .. N+1+NC) the sequence of each chunk, then NC*H
-     per-(chunk, head) flags and a device error word used by the output pass;
-     NC = nha_chunk_count_bound(Ttot, N) */
+     per-(chunk, head) flags and a device error word used by the output pass, then (at the next
+     multiple of four ints) one record {sequence, chunk in sequence, first token, length} per chunk;
+     NC = nha_chunk_count_bound(Ttot, N).  The buffer must be 16-byte aligned. */
   int32_t* plan;
   void* workspace;              /* scratch, see nha_chunk_*_workspace_bytes */
   size_t workspace_bytes;

@@ -69,11 +69,12 @@ __device__ __forceinline__ bool chunk_gate(const BwdWs& w, int cg, int h, int H)
 }
 
 __device__ __forceinline__ bool chunk_ctx(const nha_chunk_desc& d, int cg, ChunkCtx& c) {
-  c.n = d.plan[d.N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  c.n = rc.n;
   if (c.n < 0) return false;
-  c.ci = cg - d.plan[c.n];
-  c.t0 = d.cu_seqlens[c.n];
-  c.len = d.cu_seqlens[c.n + 1] - c.t0;
+  c.ci = rc.ci;
+  c.t0 = rc.t0;
+  c.len = rc.len;
   c.c0 = c.ci * kChunk;
   c.wl = seq_window(d, c.n);
   c.shift = seq_shift(d, c.n);

@@ -87,12 +87,13 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
   constexpr float kLog2e = 1.4426950408889634f;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
   if (!chunk_gate(w, cg, h, H)) return;
-  const int ci = cg - d.plan[n];
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
+  const int ci = rc.ci;
+  const int t0 = rc.t0;
+  const int len = rc.len;
   const int c0 = ci * kChunk;
   const int wl = seq_window(d, n);
   const int shift = seq_shift(d, n);
@@ -620,11 +621,12 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
   constexpr int M = 64;
   const int H = d.H, N = d.N, K = d.K, V = d.V;
   const int cg = blockIdx.x, h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
   if (!chunk_gate(w, cg, h, H)) return;
-  const int ci = cg - d.plan[n];
-  const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
+  const int ci = rc.ci;
+  const int len = rc.len;
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int tid = threadIdx.x, lane = tid & 31;
   const size_t nh = (size_t)n * H + h, ch = (size_t)cg * H + h;
@@ -785,12 +787,13 @@ __global__ void __launch_bounds__(kColsThreads, (D == 64 && R == 64) ? 2 : 1)
   constexpr int KT = L::KT, TH = R / 64, M = 64, NT = kColsThreads;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
   if (!chunk_gate(w, cg, h, H)) return;
-  const int ci = cg - d.plan[n];
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
+  const int ci = rc.ci;
+  const int t0 = rc.t0;
+  const int len = rc.len;
   const int c0 = ci * kChunk;
   const int shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

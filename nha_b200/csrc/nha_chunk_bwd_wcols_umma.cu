@@ -43,11 +43,12 @@ __global__ void __launch_bounds__(kWCThreads, D == 64 ? 2 : 1) nha_bwd_wcols_umm
   constexpr int KT = L::KT;
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
-  const int ci = cg - d.plan[n];
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
+  const int ci = rc.ci;
+  const int t0 = rc.t0;
+  const int len = rc.len;
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int c0 = ci * kChunk;
   const int wl = seq_window(d, n);

@@ -115,12 +115,13 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
   const int N = d.N;
   const int cg = cgb;                       // global chunk index
   const int h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
   if (only_flagged && only_flagged[(size_t)cg * H + h] == 0) return;
-  const int ci = cg - d.plan[n];
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
+  const int ci = rc.ci;
+  const int t0 = rc.t0;
+  const int len = rc.len;
   const int c0 = ci * kChunk;
   const int wl = seq_window(d, n);
   const int shift = seq_shift(d, n);

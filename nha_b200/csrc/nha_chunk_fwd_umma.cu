@@ -113,11 +113,12 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
   constexpr int LW = KW < 32 ? KW : 32;             // columns per tensor-memory load of the window logits
   const int H = d.H, HQ = d.HQ, NG = HQ / H, N = d.N;
   const int cg = blockIdx.x, h = blockIdx.y;
-  const int n = d.plan[N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
-  const int ci = cg - d.plan[n];
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
+  const int ci = rc.ci;
+  const int t0 = rc.t0;
+  const int len = rc.len;
   const int c0 = ci * kChunk;
   const int wl = seq_window(d, n);
   const int shift = seq_shift(d, n);

@@ -39,9 +39,14 @@ __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restr
   }
   __syncthreads();
   for (int c = total + threadIdx.x; c < NCB; c += blockDim.x) plan[N + 1 + c] = -1;
+  int4* rec = reinterpret_cast<int4*>(plan + plan_rec_offset(N, NCB, H));
+  for (int c = total + threadIdx.x; c < NCB; c += blockDim.x) rec[c] = make_int4(-1, 0, 0, 0);
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     const int c0 = plan[n], c1 = plan[n + 1];
-    for (int c = c0; c < c1; ++c) plan[N + 1 + c] = n;
+    for (int c = c0; c < c1; ++c) {
+      plan[N + 1 + c] = n;
+      rec[c] = make_int4(n, c - c0, cu[n], cu[n + 1] - cu[n]);
+    }
   }
 }
 
@@ -68,12 +73,13 @@ __host__ __device__ inline StLocalLayout st_local_layout(int K, int V, int M) {
 __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_chunk_desc d, const StateWs w) {
   const int cg = blockIdx.x, h = blockIdx.y;
   const int NCB = gridDim.x;
-  const int n = d.plan[d.N + 1 + cg];
+  const ChunkRec rc = chunk_rec(d, cg);
+  const int n = rc.n;
   if (n < 0) return;
   const int K = d.K, V = d.V, M = d.M, H = d.H;
-  const int t0 = d.cu_seqlens[n];
-  const int len = d.cu_seqlens[n + 1] - t0;
-  const int p0 = (cg - d.plan[n]) * kChunk;       // shifted position of row 0
+  const int t0 = rc.t0;
+  const int len = rc.len;
+  const int p0 = rc.ci * kChunk;                  // shifted position of row 0
   const int shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5;
   (void)NCB;
@@ -253,7 +259,8 @@ using namespace nha;
 extern "C" int64_t nha_chunk_count_bound(int64_t Ttot, int64_t N) { return (Ttot + kChunk - 1) / kChunk + N; }
 extern "C" int64_t nha_chunk_plan_ints(int64_t Ttot, int64_t N, int64_t H) {
   const int64_t ncb = nha_chunk_count_bound(Ttot, N);
-  return N + 1 + ncb + ncb * H + 4;     // offsets, chunk -> sequence, per-(chunk, head) flags, error word
+  // offsets, chunk -> sequence, per-(chunk, head) flags, error word; then one 4-int record per chunk
+  return plan_rec_offset(N, ncb, H) + 4 * ncb;
 }
 
 extern "C" int nha_chunk_plan(const nha_chunk_desc* d, void* stream) {

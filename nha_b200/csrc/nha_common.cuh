@@ -120,6 +120,21 @@ struct SeqInfo {
   int shift;    // gsa_kv_shift
 };
 
+// Per-chunk record of the plan: {sequence (-1 = unused chunk), chunk index inside the sequence, first packed token of
+// the sequence, length of the sequence}, one 16-byte load instead of a chain of dependent ones.  The records follow
+// the plan's other tables (offsets, chunk -> sequence, flags, error word) at the next multiple of four ints.
+__host__ __device__ __forceinline__ int64_t plan_rec_offset(int64_t N, int64_t NCB, int64_t H) {
+  return (N + 1 + NCB + NCB * H + 4 + 3) & ~(int64_t)3;
+}
+struct ChunkRec { int n, ci, t0, len; };
+__device__ __forceinline__ ChunkRec chunk_rec(const nha_chunk_desc& d, int cg) {
+  const int ncb = (int)((d.Ttot + kChunk - 1) / kChunk + d.N);
+  const int4 r = __ldg(reinterpret_cast<const int4*>(d.plan + plan_rec_offset(d.N, ncb, d.H)) + cg);
+  ChunkRec c;
+  c.n = r.x; c.ci = r.y; c.t0 = r.z; c.len = r.w;
+  return c;
+}
+
 __device__ __forceinline__ int seq_window(const nha_chunk_desc& d, int n) {
   return d.window_left ? d.window_left[n] : d.window_left_all;
 }

@@ -30,7 +30,8 @@ def test_desc_layout_and_status_strings():
     assert lib.nha_status_string(0) == b'ok'
     assert b'unsupported' in lib.nha_status_string(2)
     assert lib.nha_chunk_count_bound(130, 2) == 3 + 2
-    assert lib.nha_chunk_plan_ints(130, 2, 3) == 3 + 5 + 5 * 3 + 4
+    # offsets, chunk -> sequence, flags, error word, padded to a multiple of four ints, then 4 ints per chunk
+    assert lib.nha_chunk_plan_ints(130, 2, 3) == (3 + 5 + 5 * 3 + 4 + 3) // 4 * 4 + 4 * 5
 
 
 def test_argument_validation_needs_no_gpu():
