@@ -76,7 +76,7 @@ class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
     Q = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,'
          'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
-         'clocks_event_reasons.sw_power_cap')
+         'clocks_event_reasons.sw_power_cap,utilization.gpu')
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
@@ -106,7 +106,8 @@ class ClockSampler:
 
     def summary(self):
         sm, mx, reasons = [], 0.0, set()
-        for r in self.rows:
+        loaded = [r for r in self.rows if len(r) > 7 and r[7].replace('.', '').isdigit() and float(r[7]) >= 50]
+        for r in (loaded or self.rows):                  # samples taken under load (GPU utilisation >= 50 %)
             try:
                 sm.append(float(r[0])); mx = max(mx, float(r[1]))
             except Exception:
@@ -117,6 +118,12 @@ class ClockSampler:
         busy = [x for x in sm if x > 0]
         return {'sm_mhz': statistics.median(busy) if busy else None, 'sm_max_mhz': mx or None,
                 'reasons': sorted(reasons), 'samples': len(sm)}
+
+    def start(self):
+        return self.__enter__()
+
+    def stop(self):
+        self.__exit__()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -392,10 +399,12 @@ def main():
             ms = float(t.item())
         return ms
 
+    # clocks and throttle reasons are sampled from the warm-up to the last measurement of this process (the timed
+    # region itself lasts tens of milliseconds, less than one sampling period)
+    clk = ClockSampler(local).start()
     for _ in range(args.warmup):
         step()
-    with ClockSampler(local) as clk:
-        ms = timed(step, args.steps)
+    ms = timed(step, args.steps)
     value = world * tokens * args.steps / (ms * 1e-3)
     # plan, state pass (2), output pass (2), backward: rows (2), window columns (1), slot (1), state-gradient terms +
     # scan + gate carry + columns + general inter-chunk kernel (5); the general kernels run gated on the chunk flags
@@ -544,6 +553,7 @@ def main():
         cpu = {'value': tps, 'unit': UNIT, 'cores': os.cpu_count(), 'kind': 'port',
                'sample': f'B=1 T={Ts} slice of the workload, fp64 oracle fwd + autograd bwd, {secs:.1f} s'}
 
+    clk.stop()
     if rank == 0:
         line = {
             'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
