@@ -56,6 +56,31 @@ __device__ __forceinline__ void mbar_expect(uint64_t* mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(umma::smem_u32(mbar)), "r"(bytes) : "memory");
 }
 
+// warp-level matrix fragments straight from shared memory, and the two mma.sync shapes the kernel uses
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(umma::smem_u32(p)) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(umma::smem_u32(p)) : "memory");
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1]) : "r"(umma::smem_u32(p)) : "memory");
+}
+// c[16x8] += a[16x16] b[16x8]
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// c[16x8] += a[16x8] b[8x8]
+__device__ __forceinline__ void mma_1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
+}
+
 template <int D>
 __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const DecodeStreamArgs a) {
   using namespace nvcuda::wmma;
@@ -103,13 +128,15 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   }
   __syncthreads();
 
-  // ring load j (j < nst: keys of stage j; else values of stage j - nst) into slot j % 4: 16-byte asynchronous
-  // copies, a thread always copies the same 16-byte column of rows 256 / (D / 8) apart, so the address
-  // arithmetic is one add per copy; rows past the end of the split are zero-filled.  One commit group per
-  // load and thread: groups complete in order, which is the order the stages are consumed in.
+  // ring load j (j < nst: keys of stage j; else values of stage j - nst) into slot j % 4 by 16-byte asynchronous
+  // copies.  A warp copies, rotates and multiplies only ITS OWN eight rows of every stage (rows 8 warp .. 8 warp + 7),
+  // so a stage is handed from the copies to the arithmetic by cp.async.wait_group + __syncwarp alone and the loops
+  // below hold no block-wide barrier.  A lane always copies the same 16-byte column, so the address arithmetic
+  // is one add per copy; rows past the end of the split are zero-filled.  One commit group per load and thread:
+  // groups complete in order, which is the order the stages are consumed in.
   constexpr int kC8 = D / 8;                                       // 16-byte columns of a row
-  constexpr int kRStep = kStrThreads / kC8;                        // rows between two copies of a thread
-  const int lc = tid % kC8, lr = tid / kC8;
+  constexpr int kRStep = 32 / kC8;                                 // rows between two copies of a lane
+  const int lc = lane % kC8, lr = 8 * warp + lane / kC8;
 #define NHA_ISSUE_LOAD(j_)                                                                          \
   do {                                                                                              \
     const int j__ = (j_);                                                                           \
@@ -118,7 +145,8 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     const bf16* new__ = (j__ < nst ? a.k : a.v) + (size_t)bh * D + 8 * lc;                          \
     unsigned char* dst__ = ring + (j__ % kStrSlots) * kSlotBytes + 16 * lc;                         \
     const int rows__ = min(kStrStage, nkeys - st__ * kStrStage);                                    \
-    _Pragma("unroll") for (int r__ = lr; r__ < kStrStage; r__ += kRStep) {                          \
+    _Pragma("unroll") for (int i__ = 0; i__ < kC8 / 4; ++i__) {                                     \
+      const int r__ = lr + i__ * kRStep;                                                            \
       const bool ok__ = r__ < rows__;                                                               \
       const int lw__ = w0 + st__ * kStrStage + (ok__ ? r__ : 0);      /* logical window index */    \
       const bf16* src__;                                                                            \
@@ -261,79 +289,78 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     __syncthreads();
   }
 
-  // ---- key stages: wait, rotate-half in place, S = sq K^T; the freed slot takes the next ring load ------------
+  // ---- key stages, warp-private: wait for my rows, rotate-half in place, S[:, my 8 keys] = sq K^T by m16n8k16 MMAs
+  //      with the query fragments held in registers; the freed rows take the next ring load -------------------------
   constexpr int c8h = K >> 4;
-  constexpr int kTasks = kStrStage * c8h / kStrThreads;            // rotary tasks per thread (8 values x 2 halves each)
+  constexpr int kTasks = 8 * c8h / 32;                             // rotary tasks per lane (8 values x 2 halves each)
+  const int gq = lane >> 2, tq = lane & 3;                         // fragment coordinates of the lane
+  uint32_t afr[K / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < K / 16; ++ks) ldsm_x4(afr[ks], sqA + (lane & 15) * ldq + 16 * ks + 8 * (lane >> 4));
   uint4 cs[kTasks][4];                                             // rotate-half table entries of the stage being rotated
+#define NHA_LOAD_TABLE(st_)                                                                         \
+  _Pragma("unroll") for (int u = 0; u < kTasks; ++u) {                                              \
+    const int i = lane + 32 * u;                                                                    \
+    const int r = i / c8h, c = i - r * c8h;                                                         \
+    const int wpos = min(w0 + (st_) * kStrStage + 8 * warp + r, W - 1);                             \
+    const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                          \
+    const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                          \
+    cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));                                 \
+    cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));                                 \
+    cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));                         \
+    cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));                         \
+  }
+  if (rotary && nst > 0) { NHA_LOAD_TABLE(0) }
   for (int st = 0; st < nst; ++st) {
     const int slot = st % kStrSlots;
-    bf16* kst = reinterpret_cast<bf16*>(ring + slot * kSlotBytes);
-    if (rotary && st == 0) {
-#pragma unroll
-      for (int u = 0; u < kTasks; ++u) {
-        const int i = tid + u * kStrThreads;
-        const int r = i / c8h, c = i - r * c8h;
-        const int wpos = min(w0 + r, W - 1);
-        const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
-        const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
-        cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));
-        cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));
-        cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));
-        cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));
-      }
-    }
+    bf16* kst = reinterpret_cast<bf16*>(ring + slot * kSlotBytes) + (size_t)8 * warp * ldk;   // my rows of the stage
     NHA_WAIT_LOAD(st, min(nloads, kStrSlots + st));
-    __syncthreads();                                               // every thread's copies of the stage have landed
+    __syncwarp();                                                  // every lane's copies of my rows have landed
     if (rotary) {
 #pragma unroll
       for (int u = 0; u < kTasks; ++u) {
-        const int i = tid + u * kStrThreads;
+        const int i = lane + 32 * u;
         const int r = i / c8h, c = i - r * c8h;
-        float x[8], y[8], c1[8], s1[8], c2[8], s2[8], o1[8], o2[8];
-        unpack8(*reinterpret_cast<const uint4*>(kst + r * ldk + 8 * c), x);
-        unpack8(*reinterpret_cast<const uint4*>(kst + r * ldk + 8 * (c + c8h)), y);
-        unpack8(cs[u][0], c1); unpack8(cs[u][1], s1); unpack8(cs[u][2], c2); unpack8(cs[u][3], s2);
+        // packed bf16 arithmetic: x c1 - y s1 and y c2 + x s2 on pairs, the first product rounded to bf16
+        uint4 xu = *reinterpret_cast<const uint4*>(kst + r * ldk + 8 * c);
+        uint4 yu = *reinterpret_cast<const uint4*>(kst + r * ldk + 8 * (c + c8h));
+        uint4 o1u, o2u;
+        const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(&xu);
+        const __nv_bfloat162* yv = reinterpret_cast<const __nv_bfloat162*>(&yu);
+        const __nv_bfloat162* c1v = reinterpret_cast<const __nv_bfloat162*>(&cs[u][0]);
+        const __nv_bfloat162* s1v = reinterpret_cast<const __nv_bfloat162*>(&cs[u][1]);
+        const __nv_bfloat162* c2v = reinterpret_cast<const __nv_bfloat162*>(&cs[u][2]);
+        const __nv_bfloat162* s2v = reinterpret_cast<const __nv_bfloat162*>(&cs[u][3]);
+        __nv_bfloat162* o1v = reinterpret_cast<__nv_bfloat162*>(&o1u);
+        __nv_bfloat162* o2v = reinterpret_cast<__nv_bfloat162*>(&o2u);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          o1[e] = x[e] * c1[e] - y[e] * s1[e];
-          o2[e] = y[e] * c2[e] + x[e] * s2[e];
+        for (int e = 0; e < 4; ++e) {
+          o1v[e] = __hfma2(xv[e], c1v[e], __hneg2(__hmul2(yv[e], s1v[e])));
+          o2v[e] = __hfma2(yv[e], c2v[e], __hmul2(xv[e], s2v[e]));
         }
-        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * c) = pack8(o1);
-        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * (c + c8h)) = pack8(o2);
+        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * c) = o1u;
+        *reinterpret_cast<uint4*>(kst + r * ldk + 8 * (c + c8h)) = o2u;
       }
-      if (st + 1 < nst) {
-        // the next stage's table entries travel while this stage's logits are formed
-#pragma unroll
-        for (int u = 0; u < kTasks; ++u) {
-          const int i = tid + u * kStrThreads;
-          const int r = i / c8h, c = i - r * c8h;
-          const int wpos = min(w0 + (st + 1) * kStrStage + r, W - 1);
-          const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
-          const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;
-          cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));
-          cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));
-          cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));
-          cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));
-        }
-      }
+      // the next stage's table entries travel while this stage's logits are formed
+      if (st + 1 < nst) { NHA_LOAD_TABLE(st + 1) }
+      __syncwarp();
     }
-    __syncthreads();
-    if (warp < kStrStage / 16) {
-      fragment<accumulator, 16, 16, 16, float> acc;
-      fill_fragment(acc, 0.f);
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ks = 0; ks < K / 16; ++ks) {
-        fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
-        fragment<matrix_b, 16, 16, 16, bf16, col_major> fb;
-        load_matrix_sync(fa, sqA + 16 * ks, ldq);
-        load_matrix_sync(fb, kst + (size_t)16 * warp * ldk + 16 * ks, ldk);
-        mma_sync(acc, fa, fb, acc);
-      }
-      store_matrix_sync(S + st * kStrStage + 16 * warp, acc, lds, mem_row_major);
+    for (int k2 = 0; k2 < K / 32; ++k2) {
+      uint32_t bfr[4];                                             // my 8 keys x 32 features: two k-steps
+      ldsm_x4(bfr, kst + (lane & 7) * ldk + 32 * k2 + 8 * (lane >> 3));
+      mma_16816(c0, afr[2 * k2], bfr[0], bfr[1]);
+      mma_16816(c1, afr[2 * k2 + 1], bfr[2], bfr[3]);
     }
-    __syncthreads();
+    float* sdst = S + st * kStrStage + 8 * warp + 2 * tq;
+    *reinterpret_cast<float2*>(sdst + (size_t)gq * lds) = make_float2(c0[0] + c1[0], c0[1] + c1[1]);
+    *reinterpret_cast<float2*>(sdst + (size_t)(gq + 8) * lds) = make_float2(c0[2] + c1[2], c0[3] + c1[3]);
+    __syncwarp();                                                  // every lane is done with my rows of the slot
     if (st + kStrSlots < nloads) NHA_ISSUE_LOAD(st + kStrSlots);
   }
+#undef NHA_LOAD_TABLE
+  __syncthreads();                                                 // all logits of the CTA are in S
 
   // ---- partial softmax over [my slots | my keys], one warp per query head; weights replace the logits in place ---
   for (int qh = warp; qh < NG; qh += kStrWarps) {
@@ -367,36 +394,42 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   }
   __syncthreads();
 
-  // ---- value stages: O += P V, one 16-column tile of the output per warp, accumulated in registers -------------
-  fragment<accumulator, 16, 16, 16, float> oacc;
-  fill_fragment(oacc, 0.f);
+  // ---- value stages, warp-private: O_w += P[:, my 8 keys] V[my 8 keys, :] by m16n8k8 MMAs, all V columns per warp,
+  //      accumulated in registers; the partial outputs of the eight warps are summed at the end ---------------------
+  float oacc[V / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < V / 8; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;
   const bf16* P = reinterpret_cast<const bf16*>(S);
   const int ldp = 2 * lds;
   for (int st = 0; st < nst; ++st) {
     const int j = nst + st, slot = j % kStrSlots;
-    const bf16* vst = reinterpret_cast<const bf16*>(ring + slot * kSlotBytes);
+    const bf16* vst = reinterpret_cast<const bf16*>(ring + slot * kSlotBytes) + (size_t)8 * warp * ldk;
     NHA_WAIT_LOAD(j, min(nloads, kStrSlots + j));
-    __syncthreads();
-    if (warp < V / 16) {
+    __syncwarp();
+    uint32_t pa[2];
+    ldsm_x2(pa, P + (size_t)(lane & 15) * ldp + st * kStrStage + 8 * warp);
 #pragma unroll
-      for (int kt = 0; kt < kStrStage / 16; ++kt) {
-        fragment<matrix_a, 16, 16, 16, bf16, row_major> fa;
-        fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
-        load_matrix_sync(fa, P + st * kStrStage + 16 * kt, ldp);
-        load_matrix_sync(fb, vst + (size_t)16 * kt * ldk + 16 * warp, ldk);
-        mma_sync(oacc, fa, fb, oacc);
-      }
+    for (int n4 = 0; n4 < V / 32; ++n4) {
+      uint32_t vb[4];                                              // my 8 keys x 32 value columns, transposed
+      ldsm_x4_trans(vb, vst + (lane & 7) * ldk + 32 * n4 + 8 * (lane >> 3));
+#pragma unroll
+      for (int t = 0; t < 4; ++t) mma_1688(oacc[4 * n4 + t], pa[0], pa[1], vb[t]);
     }
-    if (j + kStrSlots < nloads) {
-      __syncthreads();                                             // every warp is done with the slot
-      NHA_ISSUE_LOAD(j + kStrSlots);
-    }
+    __syncwarp();
+    if (j + kStrSlots < nloads) NHA_ISSUE_LOAD(j + kStrSlots);
   }
 #undef NHA_ISSUE_LOAD
 #undef NHA_WAIT_LOAD
   __syncthreads();                                                 // the logits / weights and the ring are dead
-  float* osm = reinterpret_cast<float*>(ring);                     // [16][V+8] window part of the output
-  if (warp < V / 16) store_matrix_sync(osm + 16 * warp, oacc, ldo, mem_row_major);
+  float* osm = reinterpret_cast<float*>(ring);                     // [8 warps][16][V+8] window parts of the output
+  {
+    float* ow = osm + (size_t)warp * 16 * ldo + 2 * tq;
+#pragma unroll
+    for (int nt = 0; nt < V / 8; ++nt) {
+      *reinterpret_cast<float2*>(ow + gq * ldo + 8 * nt) = make_float2(oacc[nt][0], oacc[nt][1]);
+      *reinterpret_cast<float2*>(ow + (gq + 8) * ldo + 8 * nt) = make_float2(oacc[nt][2], oacc[nt][3]);
+    }
+  }
 
   // ---- my rows of hv <- diag(exp(g)) hv + s v^T (in place), slot readout -----------------------------------------
   constexpr int V4 = V >> 2;
@@ -428,8 +461,11 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       acc.x += pm * hh.x; acc.y += pm * hh.y; acc.z += pm * hh.z; acc.w += pm * hh.w;
     }
     if (nkeys > 0) {
-      const float4 wv = *reinterpret_cast<const float4*>(osm + qh * ldo + 4 * c);
-      acc.x += wv.x; acc.y += wv.y; acc.z += wv.z; acc.w += wv.w;
+#pragma unroll
+      for (int w8 = 0; w8 < kStrWarps; ++w8) {
+        const float4 wv = *reinterpret_cast<const float4*>(osm + ((size_t)w8 * 16 + qh) * ldo + 4 * c);
+        acc.x += wv.x; acc.y += wv.y; acc.z += wv.z; acc.w += wv.w;
+      }
     }
     if (SPL == 1) {
       const float inv = 1.0f / ml[2 * qh + 1];
