@@ -167,11 +167,30 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     else asm volatile("cp.async.wait_group 0;\n" ::);                                               \
   } while (0)
 
-  // ---- everything that fits goes in flight: the first ring loads and my rows of hv -----------------------
-  for (int j = 0; j < min(nloads, kStrSlots); ++j) NHA_ISSUE_LOAD(j);
-  if (nslots > 0 && !a.zero_state && tid == 0) {
-    mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);
-    bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);
+  // ---- the small inputs first, into registers, so that they are not queued behind the window in the memory system;
+  //      then everything that fits goes in flight: my columns of hk, the first ring loads, my rows of hv.
+  //      Disjoint groups of threads fetch the four small inputs, so that their loads overlap. ----------------------
+  constexpr int c8h = K >> 4;
+  const int qi = tid - 128, q_r = qi / c8h, q_c = qi - q_r * c8h;
+  const bool qthread = tid >= 128 && qi < 16 * c8h, qlive = qthread && q_r < NG;
+  uint4 rq_x = make_uint4(0u, 0u, 0u, 0u), rq_y = rq_x, rq_c1 = rq_x, rq_s1 = rq_x, rq_c2 = rq_x, rq_s2 = rq_x;
+  if (qlive) {
+    const bf16* qrow = a.q + ((size_t)b * a.HQ + h * NG + q_r) * K;
+    rq_x = __ldg(reinterpret_cast<const uint4*>(qrow + 8 * q_c));
+    rq_y = __ldg(reinterpret_cast<const uint4*>(qrow + 8 * (q_c + c8h)));
+    if (rotary) {
+      // the query position is the last row of the window tables
+      const bf16* cq = a.cosp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row;
+      const bf16* sn = a.sinp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row;
+      rq_c1 = __ldg(reinterpret_cast<const uint4*>(cq + 8 * q_c));
+      rq_s1 = __ldg(reinterpret_cast<const uint4*>(sn + 8 * q_c));
+      rq_c2 = __ldg(reinterpret_cast<const uint4*>(cq + 8 * (q_c + c8h)));
+      rq_s2 = __ldg(reinterpret_cast<const uint4*>(sn + 8 * (q_c + c8h)));
+    } else {
+      const bf16* srow = a.sq + ((size_t)b * a.HQ + h * NG + q_r) * K;
+      rq_c1 = __ldg(reinterpret_cast<const uint4*>(srow + 8 * q_c));
+      rq_c2 = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (q_c + c8h)));
+    }
   }
   // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = kRowsPer warp + j.  The first
   // block of columns (all of them unless the split owns more than 32 slots) is fetched now.
@@ -183,67 +202,74 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     for (int j = 0; j < kRowsPer; ++j)
       hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane] : 0.f;
   }
-  // ---- the popped token, the gates and the queries: disjoint groups of threads, so that the loads of the four
-  //      small inputs overlap instead of queueing behind one another --------------------------------------------
+  // the gates (threads 0..63) and the popped token (one warp each for k and v)
+  bf16 gb[2], sb[2];
+  gb[0] = gb[1] = sb[0] = sb[1] = f2bf(0.f);
+  uint4 rpop = make_uint4(0u, 0u, 0u, 0u);
   if (tid < 64) {
-    for (int m = tid; m < MQ; m += 64) {
-      float e = 1.f, sm = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int m = tid + 64 * u;
       if (m < nslots) {
-        e = __expf(bf2f(gpop_g[m0 + m]));
-        sm = a.s ? bf2f(a.s[(size_t)bh * M + m0 + m]) : 1.0f - e;
+        gb[u] = gpop_g[m0 + m];
+        if (a.s) sb[u] = a.s[(size_t)bh * M + m0 + m];
       }
-      eg[m] = e;
-      sv[m] = sm;
     }
   } else if (tid < 96) {
-    for (int i = tid - 64; i < (K >> 3); i += 32) {
-      float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(kpop_g + 8 * i), f);
+    if (tid - 64 < (K >> 3)) rpop = __ldg(reinterpret_cast<const uint4*>(kpop_g + 8 * (tid - 64)));
+  } else if (tid < 128) {
+    if (tid - 96 < (V >> 3)) rpop = __ldg(reinterpret_cast<const uint4*>(vpop_g + 8 * (tid - 96)));
+  }
+  for (int j = 0; j < min(nloads, kStrSlots); ++j) NHA_ISSUE_LOAD(j);
+  if (nslots > 0 && !a.zero_state && tid == 0) {
+    mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);
+    bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);
+  }
+  // registers -> shared memory
+  if (tid < 64) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) kpop[8 * i + e] = f[e];
+    for (int u = 0; u < 2; ++u) {
+      const int m = tid + 64 * u;
+      if (m < MQ) {
+        float e = 1.f, sm = 0.f;
+        if (m < nslots) {
+          e = __expf(bf2f(gb[u]));
+          sm = a.s ? bf2f(sb[u]) : 1.0f - e;
+        }
+        eg[m] = e;
+        sv[m] = sm;
+      }
     }
   } else if (tid < 128) {
-    for (int i = tid - 96; i < (V >> 3); i += 32) {
+    const int i = (tid - 64) & 31;
+    if (i < (K >> 3)) {
       float f[8];
-      unpack8(*reinterpret_cast<const uint4*>(vpop_g + 8 * i), f);
+      unpack8(rpop, f);
+      float* dstp = tid < 96 ? kpop : vpop;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) vpop[8 * i + e] = f[e];
+      for (int e = 0; e < 8; ++e) dstp[8 * i + e] = f[e];
     }
-  } else {
-    constexpr int c8h = K >> 4;
-    const bf16* cq = rotary ? a.cosp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row : nullptr;
-    const bf16* sn = rotary ? a.sinp + b * a.cs_batch + (int64_t)(W - 1) * a.cs_row : nullptr;
-    for (int i = tid - 128; i < 16 * c8h; i += 128) {
-      const int r = i / c8h, c = i - r * c8h;
-      uint4 o1 = make_uint4(0u, 0u, 0u, 0u), o2 = o1;
-      if (r < NG) {
-        const bf16* qrow = a.q + ((size_t)b * a.HQ + h * NG + r) * K;
-        const uint4 xu = *reinterpret_cast<const uint4*>(qrow + 8 * c);
-        const uint4 yu = *reinterpret_cast<const uint4*>(qrow + 8 * (c + c8h));
-        if (rotary) {
-          const uint4 c1u = *reinterpret_cast<const uint4*>(cq + 8 * c), s1u = *reinterpret_cast<const uint4*>(sn + 8 * c);
-          const uint4 c2u = *reinterpret_cast<const uint4*>(cq + 8 * (c + c8h));
-          const uint4 s2u = *reinterpret_cast<const uint4*>(sn + 8 * (c + c8h));
-          float x[8], y[8], c1[8], s1[8], c2[8], s2[8], p1[8], p2[8];
-          unpack8(xu, x); unpack8(yu, y);
-          unpack8(c1u, c1); unpack8(s1u, s1); unpack8(c2u, c2); unpack8(s2u, s2);
+  } else if (qthread) {
+    uint4 o1 = make_uint4(0u, 0u, 0u, 0u), o2 = o1;
+    if (qlive) {
+      if (rotary) {
+        float x[8], y[8], c1[8], s1[8], c2[8], s2[8], p1[8], p2[8];
+        unpack8(rq_x, x); unpack8(rq_y, y);
+        unpack8(rq_c1, c1); unpack8(rq_s1, s1); unpack8(rq_c2, c2); unpack8(rq_s2, s2);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p1[e] = x[e] * c1[e] - y[e] * s1[e];
-            p2[e] = y[e] * c2[e] + x[e] * s2[e];
-          }
-          o1 = pack8(p1); o2 = pack8(p2);
-        } else {
-          const bf16* srow = a.sq + ((size_t)b * a.HQ + h * NG + r) * K;
-          o1 = *reinterpret_cast<const uint4*>(srow + 8 * c);
-          o2 = *reinterpret_cast<const uint4*>(srow + 8 * (c + c8h));
+        for (int e = 0; e < 8; ++e) {
+          p1[e] = x[e] * c1[e] - y[e] * s1[e];
+          p2[e] = y[e] * c2[e] + x[e] * s2[e];
         }
-        *reinterpret_cast<uint4*>(qs + r * K + 8 * c) = xu;
-        *reinterpret_cast<uint4*>(qs + r * K + 8 * (c + c8h)) = yu;
+        o1 = pack8(p1); o2 = pack8(p2);
+      } else {
+        o1 = rq_c1; o2 = rq_c2;
       }
-      *reinterpret_cast<uint4*>(sqA + r * ldq + 8 * c) = o1;
-      *reinterpret_cast<uint4*>(sqA + r * ldq + 8 * (c + c8h)) = o2;
+      *reinterpret_cast<uint4*>(qs + q_r * K + 8 * q_c) = rq_x;
+      *reinterpret_cast<uint4*>(qs + q_r * K + 8 * (q_c + c8h)) = rq_y;
     }
+    *reinterpret_cast<uint4*>(sqA + q_r * ldq + 8 * q_c) = o1;
+    *reinterpret_cast<uint4*>(sqA + q_r * ldq + 8 * (q_c + c8h)) = o2;
   }
   __syncthreads();
 
@@ -291,7 +317,6 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
 
   // ---- key stages, warp-private: wait for my rows, rotate-half in place, S[:, my 8 keys] = sq K^T by m16n8k16 MMAs
   //      with the query fragments held in registers; the freed rows take the next ring load -------------------------
-  constexpr int c8h = K >> 4;
   constexpr int kTasks = 8 * c8h / 32;                             // rotary tasks per lane (8 values x 2 halves each)
   const int gq = lane >> 2, tq = lane & 3;                         // fragment coordinates of the lane
   uint32_t afr[K / 16][4];
