@@ -387,13 +387,39 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
 #undef NHA_LOAD_TABLE
   __syncthreads();                                                 // all logits of the CTA are in S
 
+  // ---- my rows of hv <- diag(exp(g)) hv + s v^T (in place; they arrived behind the keys) ----------------------------
+  constexpr int V4 = V >> 2;
+  if (nslots > 0) {
+    if (!a.zero_state && !umma::mbar_wait(&bars[kStrSlots], 0)) failed = true;
+    float4* hg = reinterpret_cast<float4*>(a.hv + ((size_t)bh * M + m0) * V);
+    for (int i = tid; i < nslots * V4; i += kStrThreads) {
+      const int m = i / V4, c = i - m * V4;
+      float4 hh = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+      const float4 vp4 = *reinterpret_cast<const float4*>(vpop + 4 * c);
+      const float e = eg[m], sm = sv[m];
+      hh.x = hh.x * e + sm * vp4.x;
+      hh.y = hh.y * e + sm * vp4.y;
+      hh.z = hh.z * e + sm * vp4.z;
+      hh.w = hh.w * e + sm * vp4.w;
+      *reinterpret_cast<float4*>(hvS + m * V + 4 * c) = hh;
+      hg[i] = hh;
+    }
+  }
+
   // ---- partial softmax over [my slots | my keys], one warp per query head; weights replace the logits in place ---
   for (int qh = warp; qh < NG; qh += kStrWarps) {
     float* srow = S + (size_t)qh * lds;
     bf16* prow = reinterpret_cast<bf16*>(srow);
     float mx = -INFINITY;
     for (int m = lane; m < nslots; m += 32) mx = fmaxf(mx, oks[qh * MQ + m]);
-    for (int w = lane; w < nkeys; w += 32) mx = fmaxf(mx, srow[w] * a.scale);
+    // a lane takes 8 consecutive keys of every block of 256
+    for (int w8 = 8 * lane; w8 < nkp; w8 += 256) {
+      const float4 x0 = *reinterpret_cast<const float4*>(srow + w8), x1 = *reinterpret_cast<const float4*>(srow + w8 + 4);
+      const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int e8 = 0; e8 < 8; ++e8)
+        if (w8 + e8 < nkeys) mx = fmaxf(mx, xs[e8] * a.scale);
+    }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int m = lane; m < nslots; m += 32) {
@@ -401,14 +427,22 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       oks[qh * MQ + m] = e;
       sum += e;
     }
-    // the bf16 weight of key w lands inside the fp32 logit of key w / 2: convert 32 keys at a time, reading
-    // all of them before any is written
-    for (int w32 = 0; w32 < nkp; w32 += 32) {
-      const int w = w32 + lane;
-      const float e = w < nkeys ? __expf(srow[w] * a.scale - mx) : 0.f;
-      sum += e;
+    // the bf16 weight of key w lands inside the fp32 logit of key w / 2: convert a block of 256 keys at a time,
+    // blocks in ascending order, reading all of a block before any of it is written
+    for (int blk = 0; blk < nkp; blk += 256) {
+      const int w8 = blk + 8 * lane;
+      float es[8];
+      if (w8 < nkp) {
+        const float4 x0 = *reinterpret_cast<const float4*>(srow + w8), x1 = *reinterpret_cast<const float4*>(srow + w8 + 4);
+        const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int e8 = 0; e8 < 8; ++e8) {
+          es[e8] = w8 + e8 < nkeys ? __expf(xs[e8] * a.scale - mx) : 0.f;
+          sum += es[e8];
+        }
+      }
       __syncwarp();
-      prow[w] = f2bf(e);
+      if (w8 < nkp) *reinterpret_cast<uint4*>(prow + w8) = pack8(es);
       __syncwarp();
     }
     sum = warp_sum(sum);
@@ -418,6 +452,22 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     }
   }
   __syncthreads();
+
+  // ---- slot readout of my output elements, kept in registers while the values stream in ---------------------------
+  float4 sacc[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    sacc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int i = tid + u * kStrThreads;
+    if (i < NG * V4) {
+      const int qh = i / V4, c = i - qh * V4;
+      for (int m = 0; m < nslots; ++m) {
+        const float pm = oks[qh * MQ + m];
+        const float4 hh = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+        sacc[u].x += pm * hh.x; sacc[u].y += pm * hh.y; sacc[u].z += pm * hh.z; sacc[u].w += pm * hh.w;
+      }
+    }
+  }
 
   // ---- value stages, warp-private: O_w += P[:, my 8 keys] V[my 8 keys, :] by m16n8k8 MMAs, all V columns per warp,
   //      accumulated in registers; the partial outputs of the eight warps are summed at the end ---------------------
@@ -456,48 +506,29 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     }
   }
 
-  // ---- my rows of hv <- diag(exp(g)) hv + s v^T (in place), slot readout -----------------------------------------
-  constexpr int V4 = V >> 2;
-  if (nslots > 0) {
-    if (!a.zero_state && !umma::mbar_wait(&bars[kStrSlots], 0)) failed = true;
-    float4* hg = reinterpret_cast<float4*>(a.hv + ((size_t)bh * M + m0) * V);
-    for (int i = tid; i < nslots * V4; i += kStrThreads) {
-      const int m = i / V4, c = i - m * V4;
-      float4 hh = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
-      const float4 vp4 = *reinterpret_cast<const float4*>(vpop + 4 * c);
-      const float e = eg[m], sm = sv[m];
-      hh.x = hh.x * e + sm * vp4.x;
-      hh.y = hh.y * e + sm * vp4.y;
-      hh.z = hh.z * e + sm * vp4.z;
-      hh.w = hh.w * e + sm * vp4.w;
-      *reinterpret_cast<float4*>(hvS + m * V + 4 * c) = hh;
-      hg[i] = hh;
-    }
-  }
   __syncthreads();
   // partial output of this split: slot part + window part, unnormalised
   float* po = a.part_o + ((size_t)bh * SPL + sp) * NG * V;
-  for (int i = tid; i < NG * V4; i += kStrThreads) {
-    const int qh = i / V4, c = i - qh * V4;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int m = 0; m < nslots; ++m) {
-      const float pm = oks[qh * MQ + m];
-      const float4 hh = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
-      acc.x += pm * hh.x; acc.y += pm * hh.y; acc.z += pm * hh.z; acc.w += pm * hh.w;
-    }
-    if (nkeys > 0) {
 #pragma unroll
-      for (int w8 = 0; w8 < kStrWarps; ++w8) {
-        const float4 wv = *reinterpret_cast<const float4*>(osm + ((size_t)w8 * 16 + qh) * ldo + 4 * c);
-        acc.x += wv.x; acc.y += wv.y; acc.z += wv.z; acc.w += wv.w;
+  for (int u = 0; u < 2; ++u) {
+    const int i = tid + u * kStrThreads;
+    if (i < NG * V4) {
+      const int qh = i / V4, c = i - qh * V4;
+      float4 acc = sacc[u];
+      if (nkeys > 0) {
+#pragma unroll
+        for (int w8 = 0; w8 < kStrWarps; ++w8) {
+          const float4 wv = *reinterpret_cast<const float4*>(osm + ((size_t)w8 * 16 + qh) * ldo + 4 * c);
+          acc.x += wv.x; acc.y += wv.y; acc.z += wv.z; acc.w += wv.w;
+        }
       }
-    }
-    if (SPL == 1) {
-      const float inv = 1.0f / ml[2 * qh + 1];
-      bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
-      orow[0] = f2bf(acc.x * inv); orow[1] = f2bf(acc.y * inv); orow[2] = f2bf(acc.z * inv); orow[3] = f2bf(acc.w * inv);
-    } else {
-      *reinterpret_cast<float4*>(po + qh * V + 4 * c) = acc;
+      if (SPL == 1) {
+        const float inv = 1.0f / ml[2 * qh + 1];
+        bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
+        orow[0] = f2bf(acc.x * inv); orow[1] = f2bf(acc.y * inv); orow[2] = f2bf(acc.z * inv); orow[3] = f2bf(acc.w * inv);
+      } else {
+        *reinterpret_cast<float4*>(po + qh * V + 4 * c) = acc;
+      }
     }
   }
   if (failed && tid == 0 && a.err) atomicExch(a.err, 1);
@@ -518,6 +549,47 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   if (!s_last) return;
   __threadfence();
   const float* all_ml = a.part_ml + (size_t)bh * SPL * NG * 2;
+  const float* all_o = a.part_o + (size_t)bh * SPL * NG * V;
+  if (SPL <= 4) {
+    // few splits: a thread fetches the maxima, sums and partial outputs of its element in one go (one trip to L2)
+    // and forms the merge weights itself
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = tid + u * kStrThreads;
+      if (i < NG * V4) {
+        const int qh = i / V4, c = i - qh * V4;
+        float4 pv[4];
+        float m2[4], l2[4];
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          if (s2 < SPL) {
+            pv[s2] = __ldcg(reinterpret_cast<const float4*>(all_o + ((size_t)s2 * NG + qh) * V + 4 * c));
+            const float2 t2 = __ldcg(reinterpret_cast<const float2*>(all_ml + ((size_t)s2 * NG + qh) * 2));
+            m2[s2] = t2.x; l2[s2] = t2.y;
+          } else {
+            pv[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+            m2[s2] = -INFINITY; l2[s2] = 0.f;
+          }
+        }
+        const float mx = fmaxf(fmaxf(m2[0], m2[1]), fmaxf(m2[2], m2[3]));
+        float wq[4], den = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          wq[s2] = m2[s2] > -INFINITY ? __expf(m2[s2] - mx) : 0.f;
+          den += l2[s2] * wq[s2];
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s2 = 0; s2 < 4; ++s2) {
+          const float w2 = wq[s2] / den;
+          acc.x += w2 * pv[s2].x; acc.y += w2 * pv[s2].y; acc.z += w2 * pv[s2].z; acc.w += w2 * pv[s2].w;
+        }
+        bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
+        orow[0] = f2bf(acc.x); orow[1] = f2bf(acc.y); orow[2] = f2bf(acc.z); orow[3] = f2bf(acc.w);
+      }
+    }
+    return;
+  }
   float* wgt = red;                     // [SPL][NG] merge weights exp(m_s - m) / denominator
   for (int qh = tid; qh < NG; qh += kStrThreads) {
     float mx = -INFINITY;
@@ -534,7 +606,6 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     }
   }
   __syncthreads();
-  const float* all_o = a.part_o + (size_t)bh * SPL * NG * V;
   for (int i = tid; i < NG * V4; i += kStrThreads) {
     const int qh = i / V4, c = i - qh * V4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
