@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   float* hvS = reinterpret_cast<float*>(smem + a.off_hv);          // [MQ][V] my rows of hv
   float* S = reinterpret_cast<float*>(smem + a.off_S);             // [16][nkp+8] logits, then bf16 weights in place
   float* red = reinterpret_cast<float*>(smem + a.off_red);         // [warps][NG][32] partial slot logits
-  bf16* qs = reinterpret_cast<bf16*>(smem + a.off_q);              // [NG][K] raw query
+  float* qs = reinterpret_cast<float*>(smem + a.off_q);            // [NG][K] raw query, fp32
   bf16* sqA = reinterpret_cast<bf16*>(smem + a.off_sqA);           // [16][K+8] rotated query (rows >= NG zero)
   float* oks = reinterpret_cast<float*>(smem + a.off_oks);         // [NG][MQ] slot logits -> unnormalised weights
   float* eg = reinterpret_cast<float*>(smem + a.off_eg);
@@ -265,14 +265,19 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       } else {
         o1 = rq_c1; o2 = rq_c2;
       }
-      *reinterpret_cast<uint4*>(qs + q_r * K + 8 * q_c) = rq_x;
-      *reinterpret_cast<uint4*>(qs + q_r * K + 8 * (q_c + c8h)) = rq_y;
+      float fx[8], fy[8];
+      unpack8(rq_x, fx); unpack8(rq_y, fy);
+      float4* qd = reinterpret_cast<float4*>(qs + q_r * K + 8 * q_c);
+      qd[0] = make_float4(fx[0], fx[1], fx[2], fx[3]);
+      qd[1] = make_float4(fx[4], fx[5], fx[6], fx[7]);
+      qd = reinterpret_cast<float4*>(qs + q_r * K + 8 * (q_c + c8h));
+      qd[0] = make_float4(fy[0], fy[1], fy[2], fy[3]);
+      qd[1] = make_float4(fy[4], fy[5], fy[6], fy[7]);
     }
     *reinterpret_cast<uint4*>(sqA + q_r * ldq + 8 * q_c) = o1;
     *reinterpret_cast<uint4*>(sqA + q_r * ldq + 8 * (q_c + c8h)) = o2;
   }
   __syncthreads();
-
   // ---- my columns of hk <- hk exp(g) + k s^T (registers -> global), partial slot logits of every query head ----
   for (int cb = 0; cb < ncb; ++cb) {
     const int m = 32 * cb + lane;
@@ -289,17 +294,15 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       hval[j] = (a.zero_state ? 0.f : hreg[j]) * e + kpop[kk] * sm;
       if (m < nslots) a.hk[((size_t)bh * K + kk) * M + m0 + m] = hval[j];
     }
-    // this warp's rows of every query head: 16-byte loads of the raw query (the same address for all lanes)
+    // this warp's rows of every query head: 16-byte loads of the query (the same address for all lanes)
 #pragma unroll
     for (int qh = 0; qh < 16; ++qh) {
       if (qh < NG) {
         float acc = 0.f;
 #pragma unroll
-        for (int c8 = 0; c8 < kRowsPer / 8; ++c8) {
-          float q8[8];
-          unpack8(*reinterpret_cast<const uint4*>(qs + qh * K + kRowsPer * warp + 8 * c8), q8);
-#pragma unroll
-          for (int e8 = 0; e8 < 8; ++e8) acc += q8[e8] * hval[8 * c8 + e8];
+        for (int c4 = 0; c4 < kRowsPer / 4; ++c4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + qh * K + kRowsPer * warp + 4 * c4);
+          acc += q4.x * hval[4 * c4] + q4.y * hval[4 * c4 + 1] + q4.z * hval[4 * c4 + 2] + q4.w * hval[4 * c4 + 3];
         }
         red[(warp * NG + qh) * 32 + lane] = acc;
       }
@@ -628,7 +631,7 @@ static int stream_layout(DecodeStreamArgs& a, int D, int nkp) {
   const int s_bytes = 16 * (nkp + 8) * 4, red_bytes = kStrWarps * NG * 32 * 4;
   a.off_S = take(s_bytes > red_bytes ? s_bytes : red_bytes);
   a.off_red = a.off_S;                               // the partial slot logits are summed before the first S tile lands
-  a.off_q = take(NG * D * 2);
+  a.off_q = take(NG * D * 4);
   a.off_sqA = take(16 * (D + 8) * 2);
   a.off_oks = take(NG * MQ * 4);
   a.off_eg = take(MQ * 4);
