@@ -5,18 +5,28 @@
 //
 //   * a (sequence, kv head) is cut into SPLITS CTAs chosen so that B*H*SPLITS CTAs fit the GPU in ONE
 //     wave (two CTAs per SM); split s owns a contiguous range of window keys and of slots;
+//   * the small inputs (queries, gates, the token that enters the slot memory, the rotary row of the query) and the
+//     CTA's hk columns are requested first, into registers, so that they are not queued behind the window;
 //   * window keys and values stream through a ring of four 64-key slots filled by 16-byte asynchronous
 //     copies with one commit group per stage (the rows of one kv head are 2 D bytes long and H times that
 //     apart, too short for bulk copies to pay: one cp.async.bulk per row measured slower): first every key
-//     stage, then - into slots as their keys have been used - the value stages.  All logits of
-//     the CTA are kept ([16][keys] fp32), so the softmax is exact in one pass and the value readout
-//     accumulates in registers without rescaling;
+//     stage, then - into slots as their keys have been used - the value stages.  A warp owns eight rows of every
+//     stage: it copies them, rotates them in place (rotate-half on packed bf16 pairs), multiplies them
+//     (ldmatrix + mma.sync m16n8k16 for the logits, m16n8k8 over its eight keys for the value readout) and refills
+//     them, so the stage loops synchronise with cp.async.wait_group and __syncwarp only - no block-wide barrier.
+//     All logits of the CTA are kept ([16][keys] fp32), so the softmax is exact in one pass and the value readout
+//     accumulates in registers without rescaling; the eight warps' partial outputs are summed at the end;
 //   * the hk columns of the split never touch shared memory: a thread updates its elements in registers,
 //     stores them back and contributes to the slot logits of all query heads, which are then summed over
-//     the warps; the hv rows, contiguous in memory, arrive by ONE bulk copy (cp.async.bulk on an mbarrier).
+//     the warps; the hv rows, contiguous in memory, arrive by ONE bulk copy (cp.async.bulk on an mbarrier)
+//     and are updated and read out before the value stages, while those stream in;
+//   * splits are merged by the last CTA of a (sequence, kv head) to arrive (a ticket in global memory); with up
+//     to four splits every thread fetches the partial results of its output element in one trip to L2.
 //
 // Replaces the two Triton launches of fused_recurrent_nha_decode
 // (nha_fla/ops/nha/fused_recurrent.py:229-353 k-kernel, :356-428 v-kernel).
+#include <string.h>
+
 #include "nha_common.cuh"
 #include "nha_umma.cuh"
 
@@ -42,6 +52,7 @@ struct DecodeStreamArgs {
   const int* head; const bf16* ring_g;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
+  int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
   float scale;
   int off_ring, off_hv, off_S, off_red, off_q, off_sqA, off_oks, off_eg, off_sv, off_kpop, off_vpop, off_ml, off_bar;
 };
@@ -69,6 +80,26 @@ __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
                : "=r"(r[0]), "=r"(r[1]) : "r"(umma::smem_u32(p)) : "memory");
 }
+// thread-block cluster: barrier over all threads of all CTAs, and loads from another CTA's shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(umma::smem_u32(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+
 // c[16x8] += a[16x16] b[16x8]
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -529,6 +560,8 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
         const float inv = 1.0f / ml[2 * qh + 1];
         bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
         orow[0] = f2bf(acc.x * inv); orow[1] = f2bf(acc.y * inv); orow[2] = f2bf(acc.z * inv); orow[3] = f2bf(acc.w * inv);
+      } else if (a.cluster) {
+        *reinterpret_cast<float4*>(hvS + qh * V + 4 * c) = acc;      // my rows of hv are dead: the partial output goes there
       } else {
         *reinterpret_cast<float4*>(po + qh * V + 4 * c) = acc;
       }
@@ -536,6 +569,37 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   }
   if (failed && tid == 0 && a.err) atomicExch(a.err, 1);
   if (SPL == 1) return;
+
+  if (a.cluster) {
+    // ---- merge inside the cluster: CTA 0 reads the partial outputs, maxima and sums of its peers from their shared
+    //      memory; the second barrier keeps the peers' memory alive until it has ----------------------------------
+    cluster_sync_all();
+    if (sp == 0) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = tid + u * kStrThreads;
+        if (i < NG * V4) {
+          const int qh = i / V4, c = i - qh * V4;
+          float mx = -INFINITY;
+          for (int s2 = 0; s2 < SPL; ++s2) mx = fmaxf(mx, ld_cluster_f2(cluster_map(ml + 2 * qh, s2)).x);
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          float den = 0.f;
+          for (int s2 = 0; s2 < SPL; ++s2) {
+            const float2 t2 = ld_cluster_f2(cluster_map(ml + 2 * qh, s2));
+            const float4 pv = ld_cluster_f4(cluster_map(hvS + qh * V + 4 * c, s2));
+            const float w2 = t2.x > -INFINITY ? __expf(t2.x - mx) : 0.f;
+            den += t2.y * w2;
+            acc.x += w2 * pv.x; acc.y += w2 * pv.y; acc.z += w2 * pv.z; acc.w += w2 * pv.w;
+          }
+          const float inv = 1.0f / den;
+          bf16* orow = a.o + ((size_t)b * a.HQ + h * NG + qh) * V + 4 * c;
+          orow[0] = f2bf(acc.x * inv); orow[1] = f2bf(acc.y * inv); orow[2] = f2bf(acc.z * inv); orow[3] = f2bf(acc.w * inv);
+        }
+      }
+    }
+    cluster_sync_all();
+    return;
+  }
 
   // ---- merge: the last split of this (sequence, kv head) to arrive combines all partials ------------
   float* pml = a.part_ml + ((size_t)bh * SPL + sp) * NG * 2;
@@ -668,16 +732,27 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   const int smem = stream_layout(a, D, nkp);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   dim3 grid(a.B * a.H * a.SPLITS), block(kStrThreads);
-  cudaError_t e;
-  if (D == 128) {
-    e = set_max_smem((const void*)nha_decode_stream_kernel<128>, smem);
-    if (e != cudaSuccess) return record_cuda_error(e);
-    nha_decode_stream_kernel<128><<<grid, block, smem, st>>>(a);
-  } else {
-    e = set_max_smem((const void*)nha_decode_stream_kernel<64>, smem);
-    if (e != cudaSuccess) return record_cuda_error(e);
-    nha_decode_stream_kernel<64><<<grid, block, smem, st>>>(a);
-  }
+  // 2, 4 or 8 splits whose partial outputs fit the (dead) hv rows merge through the cluster's shared memory
+  a.cluster = (a.SPLITS == 2 || a.SPLITS == 4 || a.SPLITS == 8) && a.NG <= a.MQ;
+  const void* fn = D == 128 ? (const void*)nha_decode_stream_kernel<128> : (const void*)nha_decode_stream_kernel<64>;
+  cudaError_t e = set_max_smem(fn, smem);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = a.cluster ? a.SPLITS : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[1] = {(void*)&a};
+  e = cudaLaunchKernelExC(&cfg, fn, args);
+  if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
 
