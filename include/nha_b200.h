@@ -69,8 +69,10 @@ int nha_abi_version(void);
  *            first call and every call leaves the counters zero, so one zero-initialised buffer can
  *            be reused by all calls with the same B*H that do not overlap on the GPU.  May be NULL
  *            for W <= 64.
- * K == V in {64, 128} with window keys takes a streaming kernel (ring of cp.async.bulk copies, whole
- * grid resident in one wave); other shapes and the win_logits mode take the general kernel.
+ * K == V in {64, 128} with window keys takes a streaming kernel (ring of asynchronous copies, whole
+ * grid resident in one wave; 2, 4 or 8 splits run as a thread-block cluster and merge through shared
+ * memory without touching the workspace, which must be passed all the same); other shapes and the
+ * win_logits mode take the general kernel.
  */
 int64_t nha_decode_workspace_bytes(int B, int HQ, int H, int V, int W);
 int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
