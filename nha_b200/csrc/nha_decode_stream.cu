@@ -426,17 +426,32 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   if (nslots > 0) {
     if (!a.zero_state && !umma::mbar_wait(&bars[kStrSlots], 0)) failed = true;
     float4* hg = reinterpret_cast<float4*>(a.hv + ((size_t)bh * M + m0) * V);
-    for (int i = tid; i < nslots * V4; i += kStrThreads) {
-      const int m = i / V4, c = i - m * V4;
-      float4 hh = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
-      const float4 vp4 = *reinterpret_cast<const float4*>(vpop + 4 * c);
-      const float e = eg[m], sm = sv[m];
-      hh.x = hh.x * e + sm * vp4.x;
-      hh.y = hh.y * e + sm * vp4.y;
-      hh.z = hh.z * e + sm * vp4.z;
-      hh.w = hh.w * e + sm * vp4.w;
-      *reinterpret_cast<float4*>(hvS + m * V + 4 * c) = hh;
-      hg[i] = hh;
+    // four elements per thread and round: all loads of a round before its stores
+    for (int i0 = tid; i0 < nslots * V4; i0 += 4 * kStrThreads) {
+      float4 hh[4], vp4[4];
+      float e[4], sm[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kStrThreads;
+        if (i < nslots * V4) {
+          const int m = i / V4, c = i - m * V4;
+          hh[u] = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+          vp4[u] = *reinterpret_cast<const float4*>(vpop + 4 * c);
+          e[u] = eg[m]; sm[u] = sv[m];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kStrThreads;
+        if (i < nslots * V4) {
+          hh[u].x = hh[u].x * e[u] + sm[u] * vp4[u].x;
+          hh[u].y = hh[u].y * e[u] + sm[u] * vp4[u].y;
+          hh[u].z = hh[u].z * e[u] + sm[u] * vp4[u].z;
+          hh[u].w = hh[u].w * e[u] + sm[u] * vp4[u].w;
+          reinterpret_cast<float4*>(hvS)[i] = hh[u];
+          hg[i] = hh[u];
+        }
+      }
     }
   }
 
@@ -495,10 +510,18 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     const int i = tid + u * kStrThreads;
     if (i < NG * V4) {
       const int qh = i / V4, c = i - qh * V4;
-      for (int m = 0; m < nslots; ++m) {
-        const float pm = oks[qh * MQ + m];
-        const float4 hh = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
-        sacc[u].x += pm * hh.x; sacc[u].y += pm * hh.y; sacc[u].z += pm * hh.z; sacc[u].w += pm * hh.w;
+      // nslots is a multiple of four: four slots at a time, all loads of a block before its arithmetic
+#pragma unroll 2
+      for (int m = 0; m < nslots; m += 4) {
+        const float4 pm = *reinterpret_cast<const float4*>(oks + qh * MQ + m);
+        const float4 h0 = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+        const float4 h1 = *reinterpret_cast<const float4*>(hvS + (m + 1) * V + 4 * c);
+        const float4 h2 = *reinterpret_cast<const float4*>(hvS + (m + 2) * V + 4 * c);
+        const float4 h3 = *reinterpret_cast<const float4*>(hvS + (m + 3) * V + 4 * c);
+        sacc[u].x += pm.x * h0.x; sacc[u].y += pm.x * h0.y; sacc[u].z += pm.x * h0.z; sacc[u].w += pm.x * h0.w;
+        sacc[u].x += pm.y * h1.x; sacc[u].y += pm.y * h1.y; sacc[u].z += pm.y * h1.z; sacc[u].w += pm.y * h1.w;
+        sacc[u].x += pm.z * h2.x; sacc[u].y += pm.z * h2.y; sacc[u].z += pm.z * h2.z; sacc[u].w += pm.z * h2.w;
+        sacc[u].x += pm.w * h3.x; sacc[u].y += pm.w * h3.y; sacc[u].z += pm.w * h3.z; sacc[u].w += pm.w * h3.w;
       }
     }
   }
