@@ -170,7 +170,7 @@ def run_reference(args):
         'e2e': {'value': val, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 
@@ -328,6 +328,26 @@ def tensor_peak():
     return 1590.0
 
 
+_RESULT_OUT = None
+
+
+def claim_stdout():
+    """Keep the process's stdout for the one JSON line: file descriptor 1 is pointed at stderr, so that
+    whatever a library writes there (NCCL's version banner, for one) cannot land beside the result."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), 'w')
+        os.dup2(2, 1)
+    return _RESULT_OUT
+
+
+def emit(line):
+    out = claim_stdout()
+    out.write(json.dumps(line) + '\n')
+    out.flush()
+
+
 # ---------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -340,6 +360,7 @@ def main():
     ap.add_argument('--no-extras', action='store_true', help='skip the decode and long-context prefill side measurements')
     ap.add_argument('--small', action='store_true', help='B=4 instead of 16 (profiling captures)')
     args = ap.parse_args()
+    claim_stdout()
     args.warmup = max(args.warmup, 3)
     if args.impl == 'reference':
         return run_reference(args)
@@ -567,7 +588,7 @@ def main():
             'cpu_baseline': cpu, 'e2e': e2e, 'gpu_launches': launches_per_step * args.steps, 'extras': extras,
             'clocks': clk.summary(),
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
