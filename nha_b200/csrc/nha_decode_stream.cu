@@ -775,6 +775,13 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   cfg.numAttrs = 1;
   void* args[1] = {(void*)&a};
   e = cudaLaunchKernelExC(&cfg, fn, args);
+  if (e != cudaSuccess && a.cluster) {
+    // the device could not place the cluster (partitioned GPU, ...): the same kernel merges through the workspace
+    (void)cudaGetLastError();
+    a.cluster = 0;
+    attr[0].val.clusterDim.x = 1;
+    e = cudaLaunchKernelExC(&cfg, fn, args);
+  }
   if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
