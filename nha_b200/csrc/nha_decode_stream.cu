@@ -25,6 +25,7 @@
 //
 // Replaces the two Triton launches of fused_recurrent_nha_decode
 // (nha_fla/ops/nha/fused_recurrent.py:229-353 k-kernel, :356-428 v-kernel).
+#include <stdlib.h>
 #include <string.h>
 
 #include "nha_common.cuh"
@@ -757,6 +758,9 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   dim3 grid(a.B * a.H * a.SPLITS), block(kStrThreads);
   // 2, 4 or 8 splits whose partial outputs fit the (dead) hv rows merge through the cluster's shared memory
   a.cluster = (a.SPLITS == 2 || a.SPLITS == 4 || a.SPLITS == 8) && a.NG <= a.MQ;
+  if (const char* nc = getenv("NHA_B200_DECODE_NO_CLUSTER")) {
+    if (nc[0] == '1') a.cluster = 0;                 // merge through the workspace instead
+  }
   const void* fn = D == 128 ? (const void*)nha_decode_stream_kernel<128> : (const void*)nha_decode_stream_kernel<64>;
   cudaError_t e = set_max_smem(fn, smem);
   if (e != cudaSuccess) return record_cuda_error(e);

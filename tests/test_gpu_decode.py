@@ -151,3 +151,30 @@ def test_decode_general_kernel_matches_streaming_kernel(B, monkeypatch):
         assert_close(hv, ref[2], 1e-5, f'hvt (general={force})')
         outs.append(o.float())
     assert (outs[0] - outs[1]).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize('B', [2, 32])
+def test_decode_cluster_merge_matches_workspace_merge(B, monkeypatch):
+    """The splits of a (sequence, kv head) merge through the cluster's shared memory; NHA_B200_DECODE_NO_CLUSTER=1
+    makes the same kernel merge through the workspace (the path taken when a cluster cannot be launched or the
+    split count is not 2, 4 or 8).  Same partial results, so the states agree bit for bit and the outputs to
+    rounding of the merge weights."""
+    from nha_b200 import fused_recurrent_nha_decode
+    H, NG, K, M, W = 4, 8, 128, 64, 512
+    d = gen.decode_inputs(90 + B, B, H, NG, K, K, M, W)
+    d['cos'], d['sin'] = gen.rope_tables(W, K, first_pos=32768 - W + 1)
+    ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'],
+                          sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    c = cuda(d)
+    res = []
+    for off in ('0', '1'):
+        monkeypatch.setenv('NHA_B200_DECODE_NO_CLUSTER', off)
+        o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'],
+                                                 sw_v=c['vw'], cos=c['cos'], sin=c['sin'],
+                                                 initial_state=(c['hk0'].clone(), c['hv0'].clone()),
+                                                 output_final_state=True)
+        assert_close(o, ref[0], TOL_OUT, f'o (no_cluster={off})')
+        res.append((o.float(), hk, hv))
+    monkeypatch.setenv('NHA_B200_DECODE_NO_CLUSTER', '0')
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2])
+    assert (res[0][0] - res[1][0]).abs().max() < 1e-2
