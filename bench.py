@@ -232,10 +232,10 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             st = lib.nha_decode_step_ring(d['q'].data_ptr(), d['k'].data_ptr(), d['v'].data_ptr(), d['sw_k'].data_ptr(),
                                           d['sw_v'].data_ptr(), gw.data_ptr(), hd.data_ptr(), cos.data_ptr(), sin.data_ptr(),
                                           0, cos.stride(1), d['hk'].data_ptr(), d['hv'].data_ptr(), d['o'].data_ptr(),
-                                          ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, K ** -0.5, stream)
+                                          ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, W, K ** -0.5, stream)
             assert st == 0
             st = lib.nha_ring_append(d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), d['k'].data_ptr(),
-                                     d['v'].data_ptr(), gn.data_ptr(), hd.data_ptr(), B, H, K, K, M, W, stream)
+                                     d['v'].data_ptr(), gn.data_ptr(), hd.data_ptr(), B, H, K, K, M, W, W, stream)
             assert st == 0
     for _ in range(2):
         step_shift()

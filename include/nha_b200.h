@@ -88,22 +88,27 @@ int nha_decode_device_error(const void* workspace, int B, int H, void* stream);
  * nha_fla/models/nha_cache.py:105-126, without its per-step torch.cat shift; pop and rope plumbing of the
  * callers: nha_fla/models/qwennha.py:149-176,207-218).  Per sequence the window keys, values and gate rows
  * live in rings `ring_k [B,W,H,K]`, `ring_v [B,W,H,V]`, `ring_g [B,W,H,M]` (bf16) of W physical rows; `head [B]`
- * (int32, device) is the row of the OLDEST entry.  The rings must be full (W entries, e.g. the last W tokens of
- * the prefill).
+ * (int32, device) is the row of the OLDEST entry.  `fill` is the number of entries the rings hold: W once they
+ * are full (e.g. the last W tokens of the prefill); while a short prompt is still filling them, the entries sit
+ * in rows 0 .. fill-1 in time order and head[b] stays 0.
  *   nha_decode_step_ring: one decode step.  The oldest entry (k, v, g = log decay, s = 1 - exp(g)) enters the
  *     slot memory; the window is the other W-1 entries followed by the token of this step (`k_new [B,H,K]`,
  *     `v_new [B,H,V]`, raw keys, not yet in the ring); cos/sin as for nha_decode_step (row w = logical window
  *     position, row W-1 = query).  hk, hv updated in place; `o [B,HQ,V]`.  K == V in {64, 128}; other shapes
- *     return NHA_ERR_UNSUPPORTED.  Rings and head are only read.
+ *     return NHA_ERR_UNSUPPORTED.  Rings and head are only read.  With fill < W nothing leaves the window and the
+ *     slot memory keeps its value (the reference's callers pass an all-zero entry then, qwennha.py:152-160); the
+ *     window is the `fill` entries and the new token, and cos/sin hold fill+1 rows (row fill = query).
  *   nha_ring_append: after the step, in stream order: the new token's rows (`g_new [B,H,M]` = its log decay)
- *     overwrite the oldest entry and head[b] advances by one (mod W).
- * Both are plain launches on `stream` with no host-side state, so a step can be captured once and replayed. */
+ *     overwrite the oldest entry and head[b] advances by one (mod W); with fill < W they go to row `fill` and
+ *     head is left alone (the caller passes fill+1 next time).
+ * Both are plain launches on `stream`; once the rings are full they carry no host-side state, so a step can be
+ * captured once and replayed. */
 int nha_decode_step_ring(const void* q, const void* k_new, const void* v_new, const void* ring_k, const void* ring_v,
                          const void* ring_g, const int32_t* head, const void* cos, const void* sin, int64_t cs_batch,
                          int64_t cs_row, float* hk, float* hv, void* o, void* workspace, int64_t workspace_bytes, int B,
-                         int HQ, int H, int K, int V, int M, int W, float scale, void* stream);
+                         int HQ, int H, int K, int V, int M, int W, int fill, float scale, void* stream);
 int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new, const void* g_new,
-                    int32_t* head, int B, int H, int K, int V, int M, int W, void* stream);
+                    int32_t* head, int B, int H, int K, int V, int M, int W, int fill, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Chunked prefill / training.  One descriptor serves the state pass, the output pass and the

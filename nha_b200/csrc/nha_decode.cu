@@ -464,7 +464,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st, const int* head, const void* ring_g);
+                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop);
 
 // Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
 // every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
@@ -547,7 +547,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   if (stream_ok)
     return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
                              errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, nullptr,
-                             nullptr);
+                             nullptr, W, 0);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;
@@ -574,9 +574,9 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
 namespace nha {
 
 __global__ void nha_ring_append_kernel(bf16* ring_k, bf16* ring_v, bf16* ring_g, const bf16* k, const bf16* v, const bf16* g,
-                                       int* head, int H, int K, int V, int M, int W) {
+                                       int* head, int H, int K, int V, int M, int W, int fill) {
   const int b = blockIdx.x;
-  const int hd = head[b];
+  const int hd = fill < W ? fill : head[b];        // a ring that is still filling takes the token in its next free row
   const size_t row = (size_t)b * W + hd;
   for (int i = threadIdx.x; i < H * K / 8; i += blockDim.x)
     reinterpret_cast<uint4*>(ring_k + row * H * K)[i] = reinterpret_cast<const uint4*>(k + (size_t)b * H * K)[i];
@@ -585,7 +585,7 @@ __global__ void nha_ring_append_kernel(bf16* ring_k, bf16* ring_v, bf16* ring_g,
   for (int i = threadIdx.x; i < H * M / 8; i += blockDim.x)
     reinterpret_cast<uint4*>(ring_g + row * H * M)[i] = reinterpret_cast<const uint4*>(g + (size_t)b * H * M)[i];
   __syncthreads();
-  if (threadIdx.x == 0) head[b] = hd + 1 == W ? 0 : hd + 1;
+  if (threadIdx.x == 0 && fill >= W) head[b] = hd + 1 == W ? 0 : hd + 1;
 }
 
 }  // namespace nha
@@ -594,13 +594,15 @@ extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void
                                     const void* ring_v, const void* ring_g, const int32_t* head, const void* cosp,
                                     const void* sinp, int64_t cs_batch, int64_t cs_row, float* hk, float* hv, void* o,
                                     void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M,
-                                    int W, float scale, void* stream) {
+                                    int W, int fill, float scale, void* stream) {
   if (!q || !k_new || !v_new || !ring_k || !ring_v || !ring_g || !head || !cosp || !sinp || !hk || !hv || !o)
     return NHA_ERR_BAD_ARG;
-  if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1) return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1 || fill < 0 || fill > W) return NHA_ERR_BAD_ARG;
   const int NG = HQ / H;
-  if (!decode_stream_supported(K, V, M, W, NG, false) || M % 8) return NHA_ERR_UNSUPPORTED;
-  const int splits = decode_stream_splits(B, H, W, M);
+  // a full ring: W window entries (the oldest leaves); a filling ring: its `fill` rows and the new token
+  const int nopop = fill < W, Weff = nopop ? fill + 1 : W;
+  if (!decode_stream_supported(K, V, M, Weff, NG, false) || M % 8) return NHA_ERR_UNSUPPORTED;
+  const int splits = decode_stream_splits(B, H, Weff, M);
   if (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W)) return NHA_ERR_WORKSPACE;
   int* tickets = (int*)workspace;
   int* errw = tickets + (size_t)B * H;
@@ -608,15 +610,16 @@ extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void
   float* part_ml = (float*)base;
   float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
-                           o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, head,
-                           ring_g);
+                           o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
+                           ring_g, W, nopop);
 }
 
 extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
-                               const void* g_new, int32_t* head, int B, int H, int K, int V, int M, int W, void* stream) {
+                               const void* g_new, int32_t* head, int B, int H, int K, int V, int M, int W, int fill,
+                               void* stream) {
   if (!ring_k || !ring_v || !ring_g || !k_new || !v_new || !g_new || !head) return NHA_ERR_BAD_ARG;
-  if (B <= 0 || H <= 0 || W < 1 || (H * K) % 8 || (H * V) % 8 || (H * M) % 8) return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || W < 1 || fill < 0 || fill > W || (H * K) % 8 || (H * V) % 8 || (H * M) % 8) return NHA_ERR_BAD_ARG;
   nha_ring_append_kernel<<<B, 128, 0, (cudaStream_t)stream>>>((bf16*)ring_k, (bf16*)ring_v, (bf16*)ring_g, (const bf16*)k_new,
-                                                              (const bf16*)v_new, (const bf16*)g_new, head, H, K, V, M, W);
+                                                              (const bf16*)v_new, (const bf16*)g_new, head, H, K, V, M, W, fill);
   return check_launch();
 }

@@ -51,6 +51,9 @@ struct DecodeStreamArgs {
   // gate row comes from ring_g, the popped k / v from the rings), the token of this step (k, v: not yet in the
   // ring) is the newest window entry
   const int* head; const bf16* ring_g;
+  // WR: rows of a ring (W outside ring mode).  nopop != 0: the rings are still filling - they hold the W - 1 oldest
+  // window entries in rows 0 .. W - 2, nothing leaves the window and the slot memory keeps its value
+  int WR, nopop;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
@@ -147,11 +150,12 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   const int nslots = max(0, min(MQ, M - m0));
   const int nloads = 2 * nst;                                      // key stages, then value stages
   const bool isring = a.head != nullptr;
-  const int hd = isring ? a.head[b] : 0;                             // physical row of the oldest ring entry
+  const int WR = a.WR;
+  const int hd = isring ? (a.nopop ? -1 : a.head[b]) : 0;              // physical row of the oldest ring entry
   // the token that enters the slot memory: separate small tensors, or the oldest ring entry
-  const bf16* kpop_g = isring ? a.sw_k + (((size_t)b * W + hd) * a.H + h) * D : a.k + (size_t)bh * D;
-  const bf16* vpop_g = isring ? a.sw_v + (((size_t)b * W + hd) * a.H + h) * D : a.v + (size_t)bh * D;
-  const bf16* gpop_g = isring ? a.ring_g + (((size_t)b * W + hd) * a.H + h) * M : a.g + (size_t)bh * M;
+  const bf16* kpop_g = isring ? a.sw_k + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D : a.k + (size_t)bh * D;
+  const bf16* vpop_g = isring ? a.sw_v + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D : a.v + (size_t)bh * D;
+  const bf16* gpop_g = isring ? a.ring_g + (((size_t)b * WR + max(hd, 0)) * a.H + h) * M : a.g + (size_t)bh * M;
   bool failed = false;
 
   if (tid == 0) {
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   do {                                                                                              \
     const int j__ = (j_);                                                                           \
     const int st__ = j__ < nst ? j__ : j__ - nst;                                                   \
-    const bf16* base__ = (j__ < nst ? a.sw_k : a.sw_v) + ((size_t)b * W * a.H + h) * D + 8 * lc;    \
+    const bf16* base__ = (j__ < nst ? a.sw_k : a.sw_v) + ((size_t)b * WR * a.H + h) * D + 8 * lc;   \
     const bf16* new__ = (j__ < nst ? a.k : a.v) + (size_t)bh * D + 8 * lc;                          \
     unsigned char* dst__ = ring + (j__ % kStrSlots) * kSlotBytes + 16 * lc;                         \
     const int rows__ = min(kStrStage, nkeys - st__ * kStrStage);                                    \
@@ -184,7 +188,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       const bf16* src__;                                                                            \
       if (!isring) src__ = base__ + (size_t)lw__ * a.H * D;                                         \
       else if (lw__ == W - 1) src__ = new__;                          /* the token of this step */  \
-      else { int pr__ = hd + 1 + lw__; if (pr__ >= W) pr__ -= W; src__ = base__ + (size_t)pr__ * a.H * D; } \
+      else { int pr__ = hd + 1 + lw__; if (pr__ >= WR) pr__ -= WR; src__ = base__ + (size_t)pr__ * a.H * D; } \
       umma::cp16(dst__ + r__ * ldk * 2, src__, ok__);                                               \
     }                                                                                               \
     umma::cp_commit();                                                                              \
@@ -242,15 +246,15 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int m = tid + 64 * u;
-      if (m < nslots) {
+      if (m < nslots && !a.nopop) {
         gb[u] = gpop_g[m0 + m];
         if (a.s) sb[u] = a.s[(size_t)bh * M + m0 + m];
       }
     }
   } else if (tid < 96) {
-    if (tid - 64 < (K >> 3)) rpop = __ldg(reinterpret_cast<const uint4*>(kpop_g + 8 * (tid - 64)));
+    if (tid - 64 < (K >> 3) && !a.nopop) rpop = __ldg(reinterpret_cast<const uint4*>(kpop_g + 8 * (tid - 64)));
   } else if (tid < 128) {
-    if (tid - 96 < (V >> 3)) rpop = __ldg(reinterpret_cast<const uint4*>(vpop_g + 8 * (tid - 96)));
+    if (tid - 96 < (V >> 3) && !a.nopop) rpop = __ldg(reinterpret_cast<const uint4*>(vpop_g + 8 * (tid - 96)));
   }
   for (int j = 0; j < min(nloads, kStrSlots); ++j) NHA_ISSUE_LOAD(j);
   if (nslots > 0 && !a.zero_state && tid == 0) {
@@ -795,7 +799,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st, const int* head, const void* ring_g) {
+                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop) {
   DecodeStreamArgs a;
   a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
   a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
@@ -803,6 +807,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
   a.hk = hk; a.hv = hv; a.o = (bf16*)o;
   a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.err = err;
   a.head = head; a.ring_g = (const bf16*)ring_g;
+  a.WR = head ? ring_rows : W; a.nopop = head ? nopop : 0;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
   a.zero_state = zero_state; a.scale = scale;

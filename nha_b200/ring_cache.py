@@ -4,8 +4,10 @@ The reference keeps the sliding window of a layer as three tensors that it shift
 on every generated token (``NHACache.update``, nha_fla/models/nha_cache.py:105-126) and hands the
 oldest entry to the layer with ``get_pop_kvf`` (:143-154).  Here the window lives in rings of ``W``
 rows per sequence and a per-sequence head index, all on the device; a decode step is two launches
-(``nha_decode_step_ring`` + ``nha_ring_append``) with no host-side state, so it can be captured in a
-CUDA graph.  The rings hold the raw (un-rotated) keys, the values and the log-decay rows ``g`` of the
+(``nha_decode_step_ring`` + ``nha_ring_append``).  Once the rings are full the launches carry no
+host-side state, so a step can be captured in a CUDA graph; while a short prompt is still filling them
+the host passes the fill level (one integer per layer) and nothing leaves the window, as in the
+reference, whose callers feed the op an all-zero entry then (qwennha.py:152-160).  The rings hold the raw (un-rotated) keys, the values and the log-decay rows ``g`` of the
 window tokens; the layer computes ``g = logsigmoid(f) / 8`` exactly as it does for the reference op.
 
 :class:`NHARingCache` keeps one ring set per layer and mirrors the parts of the ``NHACache`` surface
@@ -26,12 +28,20 @@ _BF16 = torch.bfloat16
 class RingLayer:
     """Rings, head indices and slot memory of one layer."""
 
-    def __init__(self, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor):
-        # k [B,W,H,K], v [B,W,H,V], g [B,W,H,M]: the last W tokens, oldest first; hk [B,H,K,M], hv [B,H,M,V] fp32
+    def __init__(self, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor,
+                 window_size: Optional[int] = None):
+        # k [B,T,H,K], v [B,T,H,V], g [B,T,H,M]: the last T <= W tokens, oldest first; hk [B,H,K,M], hv [B,H,M,V] fp32.
+        # With T < W the rings are still filling: entries in rows 0 .. T-1, `fill` counts them (host side).
         assert k.dim() == 4 and v.dim() == 4 and g.dim() == 4 and k.shape[:3] == v.shape[:3] == g.shape[:3]
-        self.ring_k = k.to(_BF16).contiguous().clone()
-        self.ring_v = v.to(_BF16).contiguous().clone()
-        self.ring_g = g.to(_BF16).contiguous().clone()
+        W = k.shape[1] if window_size is None else int(window_size)
+        assert k.shape[1] <= W
+        self.fill = k.shape[1]
+
+        def ring(x):
+            r = torch.zeros(x.shape[0], W, *x.shape[2:], dtype=_BF16, device=x.device)
+            r[:, :x.shape[1]] = x.to(_BF16)
+            return r
+        self.ring_k, self.ring_v, self.ring_g = ring(k), ring(v), ring(g)
         self.head = torch.zeros(k.shape[0], dtype=torch.int32, device=k.device)
         self.hk = hk.float().contiguous().clone()
         self.hv = hv.float().contiguous().clone()
@@ -43,6 +53,8 @@ class RingLayer:
     def ordered(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """The window in time order (oldest first), as the reference cache would hold it (copies)."""
         W = self.window
+        if self.fill < W:
+            return self.ring_k[:, :self.fill].clone(), self.ring_v[:, :self.fill].clone(), self.ring_g[:, :self.fill].clone()
         idx = (self.head.long()[:, None] + torch.arange(W, device=self.head.device)[None]) % W
         gather = lambda r: torch.gather(r, 1, idx[:, :, None, None].expand(-1, -1, *r.shape[2:]))
         return gather(self.ring_k), gather(self.ring_v), gather(self.ring_g)
@@ -53,14 +65,17 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
     """One decode step on a ring cache: returns ``o [B,1,HQ,V]``; the layer's state and rings are updated.
 
     ``q [B,1,HQ,K]``, ``k [B,1,H,K]`` (raw), ``v [B,1,H,V]``, ``g [B,1,H,M]`` (log decay of the new token),
-    ``cos/sin [1|B, W, K]`` for the W window positions (row W-1 = the query's position).
+    ``cos/sin [1|B, W, K]`` for the W window positions (row W-1 = the query's position); while the rings are
+    still filling (``layer.fill < W``) the window is ``layer.fill + 1`` long and so are the tables.
     """
     lib = _lib.load()
     B, one, HQ, K = q.shape
     if one != 1:
         raise ValueError('decode takes one token per sequence')
     H, V, M, W = k.shape[2], v.shape[3], g.shape[3], layer.window
-    assert cos.shape[-2] == W and cos.shape[-1] == K, 'cos/sin must cover the W window positions'
+    fill = layer.fill
+    wlen = W if fill >= W else fill + 1
+    assert cos.shape[-2] == wlen and cos.shape[-1] == K, 'cos/sin must cover the window positions'
     dev = q.device
     qc, kc, vc, gc = (x.to(_BF16).contiguous() for x in (q, k, v, g))
     cosc, sinc = cos.to(_BF16).contiguous(), sin.to(_BF16).contiguous()
@@ -73,10 +88,11 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
                                         layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), layer.head.data_ptr(),
                                         cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2), layer.hk.data_ptr(),
                                         layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(), ws.numel(), B, HQ, H, K, V, M, W,
-                                        sc, st), 'nha_decode_step_ring')
+                                        fill, sc, st), 'nha_decode_step_ring')
     _lib.check(lib.nha_ring_append(layer.ring_k.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), kc.data_ptr(),
-                                   vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M, W, st),
+                                   vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M, W, fill, st),
                'nha_ring_append')
+    layer.fill = min(fill + 1, W)
     return o
 
 
@@ -97,12 +113,13 @@ class NHARingCache:
 
     def init_layer(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, window_size: int,
                    recurrent_state: Tuple[torch.Tensor, torch.Tensor]) -> RingLayer:
-        """Fill a layer from its prefill: ``k, v, g [B,T,H,*]`` with ``T >= window_size`` (the last
-        ``window_size`` tokens are kept, as ``NHACache.update`` does) and the slot memory after the prefill."""
-        assert k.shape[1] >= window_size, 'the ring must be full: prefill at least window_size tokens'
+        """Fill a layer from its prefill: ``k, v, g [B,T,H,*]`` (the last ``window_size`` tokens are kept, as
+        ``NHACache.update`` does; a shorter prompt leaves the rings partly filled) and the slot memory after the
+        prefill."""
         while len(self.layers) <= layer_idx:
             self.layers.append(None)
-        layer = RingLayer(k[:, -window_size:], v[:, -window_size:], g[:, -window_size:], *recurrent_state)
+        layer = RingLayer(k[:, -window_size:], v[:, -window_size:], g[:, -window_size:], *recurrent_state,
+                          window_size=window_size)
         self.layers[layer_idx] = layer
         return layer
 
@@ -119,6 +136,8 @@ class NHARingCache:
         if layer_idx >= len(self.layers) or self.layers[layer_idx] is None:
             return (None, None, None)
         L = self.layers[layer_idx]
+        if L.fill < L.window:
+            return (None, None, None)                 # as NHACache: nothing leaves a window that is not full
         b = torch.arange(L.head.shape[0], device=L.head.device)
         pick = lambda r: r[b, L.head.long()].reshape(r.shape[0], 1, -1)
         return pick(L.ring_k), pick(L.ring_v), pick(L.ring_g)

@@ -60,3 +60,53 @@ def test_ring_decode_matches_shifted_window(B, H, NG, D, M, W, steps):
     ok, ov, og = cache[0].ordered()
     assert torch.equal(ok, ref_k) and torch.equal(ov, ref_v) and torch.equal(og, ref_g)
     assert cache.get_seq_length() == steps
+
+
+@pytest.mark.parametrize('B,H,NG,D,M,W,T0,steps', [(2, 2, 4, 64, 32, 16, 0, 40), (2, 4, 8, 128, 64, 64, 5, 80)])
+def test_ring_decode_warm_up_matches_growing_window(B, H, NG, D, M, W, T0, steps):
+    """A prompt shorter than the window: the rings fill up step by step.  Until they are full nothing leaves the
+    window; the reference's callers hand the op an all-zero entry then (qwennha.py:152-160) and a window that grows
+    by one token per step (NHACache.update).  Same flow here with the shifted-window decode as the reference arm."""
+    from nha_b200 import NHARingCache, fused_recurrent_nha_decode
+    dev = 'cuda'
+    g0 = torch.Generator().manual_seed(300 + W)
+    r = lambda *s: torch.randn(*s, generator=g0)
+    HQ = H * NG
+    win_k = (r(B, T0, H, D) * D ** -0.5).bfloat16().to(dev)
+    win_v = (r(B, T0, H, D) * D ** -0.5).bfloat16().to(dev)
+    win_g = (F.logsigmoid(r(B, T0, H, M)) / 8).bfloat16().to(dev)
+    hk = (r(B, H, D, M) * 0.5).to(dev)
+    hv = (r(B, H, M, D) * 0.5).to(dev)
+    cache = NHARingCache()
+    cache.init_layer(0, win_k, win_v, win_g, W, (hk, hv))
+    ref_k, ref_v, ref_g = win_k.clone(), win_v.clone(), win_g.clone()
+    ref_hk, ref_hv = hk.clone(), hv.clone()
+    for t in range(steps):
+        q = (r(B, 1, HQ, D) * D ** -0.5).bfloat16().to(dev)
+        k = (r(B, 1, H, D) * D ** -0.5).bfloat16().to(dev)
+        v = (r(B, 1, H, D) * D ** -0.5).bfloat16().to(dev)
+        g = (F.logsigmoid(r(B, 1, H, M)) / 8).bfloat16().to(dev)
+        full = ref_k.shape[1] >= W
+        pk, pv, pg = cache.get_pop_kvf(0, W)
+        assert (pk is not None) == full
+        if full:
+            pop_k, pop_v, pop_g = ref_k[:, :1].contiguous(), ref_v[:, :1].contiguous(), ref_g[:, :1].contiguous()
+            ref_k, ref_v, ref_g = ref_k[:, 1:], ref_v[:, 1:], ref_g[:, 1:]
+        else:
+            pop_k, pop_v, pop_g = torch.zeros_like(k), torch.zeros_like(v), torch.zeros_like(g)
+        ref_k, ref_v, ref_g = torch.cat([ref_k, k], 1), torch.cat([ref_v, v], 1), torch.cat([ref_g, g], 1)
+        wlen = ref_k.shape[1]
+        cos, sin = gen.rope_tables(wlen, D, first_pos=T0 + t - wlen + 1)
+        cos, sin = cos.to(dev), sin.to(dev)
+        o_ref, (ref_hk, ref_hv) = fused_recurrent_nha_decode(q=q, k=pop_k, v=pop_v, g=pop_g, sw_k=ref_k.contiguous(),
+                                                             sw_v=ref_v.contiguous(), cos=cos, sin=sin,
+                                                             initial_state=(ref_hk, ref_hv), output_final_state=True)
+        o = cache.decode(0, q, k, v, g, cos, sin)
+        assert torch.equal(o, o_ref), f'step {t} (window {wlen}): output differs from the growing-window decode'
+        assert torch.equal(cache[0].hk, ref_hk) and torch.equal(cache[0].hv, ref_hv), f'step {t}: state differs'
+        if t == 0:
+            want = orc.decode_step(q.cpu(), pop_k.cpu(), pop_v.cpu(), pop_g.cpu(), ref_k.cpu(), ref_v.cpu(), D ** -0.5,
+                                   cos=cos.cpu(), sin=sin.cpu(), hk0=hk.cpu(), hv0=hv.cpu())
+            assert_close(o, want[0], TOL_OUT, 'o (first step vs oracle)')
+    ok, ov, og = cache[0].ordered()
+    assert torch.equal(ok, ref_k) and torch.equal(ov, ref_v) and torch.equal(og, ref_g)
