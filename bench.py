@@ -321,6 +321,43 @@ def bench_varlen(dev, rank, timed):
                         f'H16 D64 M64 bf16', 'ms': ms, 'tokens_per_s_per_gpu': total / (ms * 1e-3)}
 
 
+def bench_gates(lib, dev, rank, timed, peak):
+    """The callers' gate chain at the bench workload's gate shape (B16 T2048 H16 M64): g = logsigmoid(f) / 8 and
+    s = 1 - exp(g) from one pass over f (nha_slot_gates_fwd) and df from dg, ds (nha_slot_gates_bwd), beside the
+    layer's own chain of element-wise torch kernels (nha_fla/layers/nha.py:229-231) with autograd."""
+    n = 16 * 2048 * 16 * 64
+    gd = torch.Generator(device=dev).manual_seed(23 + rank)
+    f = (torch.randn(n, generator=gd, device=dev) * 2).bfloat16()
+    dg = torch.randn(n, generator=gd, device=dev).bfloat16()
+    ds = torch.randn(n, generator=gd, device=dev).bfloat16()
+    g, s, df = torch.empty_like(f), torch.empty_like(f), torch.empty_like(f)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def fwd():
+        assert lib.nha_slot_gates_fwd(f.data_ptr(), g.data_ptr(), s.data_ptr(), n, 8.0, stream) == 0
+
+    def bwd():
+        assert lib.nha_slot_gates_bwd(f.data_ptr(), dg.data_ptr(), ds.data_ptr(), df.data_ptr(), n, 8.0, stream) == 0
+    ft = f.clone().requires_grad_(True)
+
+    def chain():
+        ft.grad = None
+        g1 = F.logsigmoid(ft) / 8.0
+        s1 = (1 - g1.exp()).to(g1.dtype)
+        torch.autograd.backward([g1, s1], [dg, ds])
+    for fn in (fwd, bwd, chain):
+        for _ in range(3):
+            fn()
+    ms_f, ms_b, ms_c = timed(fwd, 20) / 20, timed(bwd, 20) / 20, timed(chain, 10) / 10
+    bytes_f, bytes_b = n * 6, n * 8                       # f read, g and s written; f, dg, ds read, df written
+    return {'workload': 'slot gates g = logsigmoid(f)/8, s = 1 - exp(g): B16 T2048 H16 M64 bf16 (201 MB forward, 268 MB '
+                        'backward: larger than L2)',
+            'fwd_ms': ms_f, 'bwd_ms': ms_b, 'torch_chain_fwd_bwd_ms': ms_c, 'gpu_launches_fwd_bwd': 2,
+            'roofline': {'bound': 'hbm', 'achieved': (bytes_f + bytes_b) / ((ms_f + ms_b) * 1e-3) / 1e9, 'peak': peak,
+                         'unit': 'GB/s', 'frac': (bytes_f + bytes_b) / ((ms_f + ms_b) * 1e-3) / 1e9 / peak,
+                         'fwd_gbs': bytes_f / (ms_f * 1e-3) / 1e9, 'bwd_gbs': bytes_b / (ms_b * 1e-3) / 1e9}}
+
+
 def tensor_peak():
     p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(p):
@@ -565,7 +602,8 @@ def main():
     if not args.no_extras and not args.small:
         extras = {'decode': bench_decode(lib, dev, rank, world, timed, peak),
                   'prefill': bench_prefill(dev, rank, world, dist, timed),
-                  'varlen': bench_varlen(dev, rank, timed)}
+                  'varlen': bench_varlen(dev, rank, timed),
+                  'gates': bench_gates(lib, dev, rank, timed, peak)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -217,6 +217,19 @@ int nha_chunk_state_pass_static(const nha_chunk_desc* d, void* stream);
    equals nha_chunk_bwd.  No counterpart in the reference (it has no timing hooks). */
 int nha_chunk_bwd_stage(const nha_chunk_desc* d, int stage, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Slot gates of the callers, fused.  The layers turn the gate projection f [.., H, M] into the
+ * operator's two gate inputs with a chain of element-wise torch kernels
+ * (nha_fla/layers/nha.py:229-231; hybrid models nha_fla/models/qwen3_nha/qwennha.py:116):
+ *     g = logsigmoid(f) / normalizer,   s = 1 - exp(g).
+ *   nha_slot_gates_fwd: f, g, s bf16 with n elements each (any shape, contiguous, 16-byte aligned);
+ *     s may be NULL.  s is computed from the bf16-rounded g, as the reference does.
+ *   nha_slot_gates_bwd: df = (dg - ds * exp(g)) * sigmoid(-f) / normalizer; dg or ds may be NULL.
+ * One launch each on `stream`, no workspace. */
+int nha_slot_gates_fwd(const void* f, void* g, void* s, int64_t n, float normalizer, void* stream);
+int nha_slot_gates_bwd(const void* f, const void* dg, const void* ds, void* df, int64_t n, float normalizer,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

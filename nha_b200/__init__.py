@@ -6,8 +6,9 @@ reference's layers and model classes can call them unchanged.
 from .chunk import chunk_nha
 from .chunk_fused import fused_chunk_nha_prefill
 from .fused_recurrent import fused_recurrent_nha, fused_recurrent_nha_decode
+from .gates import slot_gates
 from .ring_cache import NHARingCache, fused_recurrent_nha_decode_ring
 
 __all__ = ['chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode',
-           'fused_recurrent_nha_decode_ring', 'NHARingCache']
+           'fused_recurrent_nha_decode_ring', 'NHARingCache', 'slot_gates']
 __version__ = '0.1.0'

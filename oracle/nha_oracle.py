@@ -46,6 +46,7 @@ __all__ = [
     "prefill",
     "decode_step",
     "recurrent_step",
+    "slot_gates",
     "rel_l2",
 ]
 
@@ -234,3 +235,10 @@ def recurrent_step(q, k, v, sliding_window, s, g, scale: float, hk0=None, hv0=No
     ps, pw = p[..., :M], p[..., M:]
     o = torch.einsum('bqm,bqmv->bqv', ps, hv1.repeat_interleave(NG, dim=1))
     return o[:, None], pw[:, None], hk1, hv1
+
+
+def slot_gates(f: torch.Tensor, normalizer: float = 8.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The callers' gate chain in fp64: ``g = logsigmoid(f) / normalizer``, ``s = 1 - exp(g)``
+    (nha_fla/layers/nha.py:229-231; differentiable through autograd)."""
+    g = torch.nn.functional.logsigmoid(f.double()) / normalizer
+    return g, -torch.expm1(g)

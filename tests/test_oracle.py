@@ -123,3 +123,21 @@ def test_lse_merge_equals_joint_softmax():
         ws, wg = (ls[t] - mx).exp(), (lg[t] - mx).exp()
         merged = (ws[:, None] * osw + wg[:, None] * og) / (ws + wg)[:, None]
         assert torch.allclose(merged, o[t], atol=1e-12)
+
+
+def test_slot_gates_against_the_layer_chain():
+    """The oracle's gate function against the layer's own three lines (nha_fla/layers/nha.py:229-231) run
+    literally in fp64 and in bf16: identical in fp64, within bf16 rounding of the chain's three roundings in bf16."""
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    f = torch.randn(4, 33, 2, 16, dtype=torch.float64) * 3
+    for norm in (1.0, 8.0):
+        g, s = orc.slot_gates(f, norm)
+        f1 = F.logsigmoid(f) / norm                       # the chain, as written in the layer
+        s1 = (1 - f1.exp()).to(f1.dtype)
+        assert torch.allclose(g, f1, rtol=0, atol=1e-15) and torch.allclose(s, s1, rtol=0, atol=1e-14)
+        fb = f.bfloat16()
+        f2 = F.logsigmoid(fb) / norm
+        s2 = (1 - f2.exp()).to(f2.dtype)
+        gb, sb = orc.slot_gates(fb, norm)
+        assert orc.rel_l2(f2.double(), gb) < 1e-2 and orc.rel_l2(s2.double(), sb) < 1e-2
