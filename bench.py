@@ -358,6 +358,32 @@ def bench_gates(lib, dev, rank, timed, peak):
                          'fwd_gbs': bytes_f / (ms_f * 1e-3) / 1e9, 'bwd_gbs': bytes_b / (ms_b * 1e-3) / 1e9}}
 
 
+def bench_rotary(lib, dev, rank, timed, peak):
+    """The layer's rotary call at the bench workload's shape (B16 T2048 H16 D64): q and k rotated by one launch
+    (nha_rope_pair), 268 MB read + written."""
+    B, T, H, K = 16, 2048, 16, 64
+    gd = torch.Generator(device=dev).manual_seed(29 + rank)
+    q = torch.randn(B * T, H, K, generator=gd, device=dev).bfloat16()
+    k = torch.randn(B * T, H, K, generator=gd, device=dev).bfloat16()
+    qo, ko = torch.empty_like(q), torch.empty_like(k)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, K, 2, dtype=torch.float32) / K))
+    fr = torch.outer(torch.arange(T, dtype=torch.float32), inv)
+    cos, sin = fr.cos().bfloat16().to(dev).contiguous(), fr.sin().bfloat16().to(dev).contiguous()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        assert lib.nha_rope_pair(q.data_ptr(), k.data_ptr(), qo.data_ptr(), ko.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                 cos.stride(0), T, None, 0, T, B * T, H, H, K, 0, 0, stream) == 0
+    for _ in range(3):
+        step()
+    ms = timed(step, 20) / 20
+    nbytes = 4 * q.numel() * 2
+    return {'workload': 'rotary of q and k, B16 T2048 H16 D64 bf16, one launch (268 MB: larger than L2)', 'ms': ms,
+            'gpu_launches': 1,
+            'roofline': {'bound': 'hbm', 'achieved': nbytes / (ms * 1e-3) / 1e9, 'peak': peak, 'unit': 'GB/s',
+                         'frac': nbytes / (ms * 1e-3) / 1e9 / peak}}
+
+
 def tensor_peak():
     p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(p):
@@ -603,7 +629,8 @@ def main():
         extras = {'decode': bench_decode(lib, dev, rank, world, timed, peak),
                   'prefill': bench_prefill(dev, rank, world, dist, timed),
                   'varlen': bench_varlen(dev, rank, timed),
-                  'gates': bench_gates(lib, dev, rank, timed, peak)}
+                  'gates': bench_gates(lib, dev, rank, timed, peak),
+                  'rotary': bench_rotary(lib, dev, rank, timed, peak)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

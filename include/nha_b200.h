@@ -230,6 +230,21 @@ int nha_slot_gates_fwd(const void* f, void* g, void* s, int64_t n, float normali
 int nha_slot_gates_bwd(const void* f, const void* dg, const void* ds, void* df, int64_t n, float normalizer,
                        void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Rotary embedding of the callers' queries and keys, both tensors in one launch (the layer's
+ * RotaryEmbedding call, nha_fla/layers/nha.py:145,235: non-interleaved halves, positions restart
+ * at every packed sequence; the hybrid models' rotate-half on duplicated-halves tables,
+ * nha_fla/models/qwen3_nha/qwennha.py:240-244, is the same arithmetic on the first K/2 columns).
+ *   q [Ttot,HQ,K], k [Ttot,H,K] (k and k_out may be NULL), outputs of the same shape (may alias
+ *   the inputs), bf16.  cos, sin: bf16 tables of `table_rows` rows, `cs_row` elements apart, of
+ *   which the first K/2 columns are read; row = offset + position of the token in its sequence.
+ *   Sequences: cu_seqlens [N+1] (device) or, when NULL, Ttot / T sequences of T tokens each.
+ *   The caller guarantees offset + longest sequence <= table_rows.  inverse != 0 rotates by the
+ *   opposite angle (the backward).  K % 16 == 0, cs_row % 8 == 0, 16-byte aligned pointers. */
+int nha_rope_pair(const void* q, const void* k, void* q_out, void* k_out, const void* cos, const void* sin,
+                  int64_t cs_row, int table_rows, const int32_t* cu_seqlens, int N, int T, int64_t Ttot, int HQ,
+                  int H, int K, int offset, int inverse, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

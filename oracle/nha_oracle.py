@@ -47,6 +47,7 @@ __all__ = [
     "decode_step",
     "recurrent_step",
     "slot_gates",
+    "rotary_positions",
     "rel_l2",
 ]
 
@@ -242,3 +243,16 @@ def slot_gates(f: torch.Tensor, normalizer: float = 8.0) -> Tuple[torch.Tensor, 
     (nha_fla/layers/nha.py:229-231; differentiable through autograd)."""
     g = torch.nn.functional.logsigmoid(f.double()) / normalizer
     return g, -torch.expm1(g)
+
+
+def rotary_positions(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """Non-interleaved rotary of ``x [T, H, K]`` in fp64 with tables ``cos, sin [P, K/2]`` and one table row per
+    token (``positions [T]``): the layer's ``self.rotary(q, k, seqlen_offset)`` (nha_fla/layers/nha.py:145,235), whose
+    arithmetic is the third-party ``fla.modules.rotary.rotary_embedding_ref`` (flash-linear-attention 0.5.1):
+    ``o[:K/2] = x[:K/2] cos - x[K/2:] sin``, ``o[K/2:] = x[:K/2] sin + x[K/2:] cos``."""
+    x = x.double()
+    R = x.shape[-1] // 2
+    c = cos.double()[positions, None, :R]
+    s = sin.double()[positions, None, :R]
+    x0, x1 = x[..., :R], x[..., R:]
+    return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], -1)

@@ -141,3 +141,22 @@ def test_slot_gates_against_the_layer_chain():
         s2 = (1 - f2.exp()).to(f2.dtype)
         gb, sb = orc.slot_gates(fb, norm)
         assert orc.rel_l2(f2.double(), gb) < 1e-2 and orc.rel_l2(s2.double(), sb) < 1e-2
+
+
+def test_rotary_positions_against_fla_reference_and_rotate_half():
+    """The oracle's rotary against the third-party PyTorch reference the layer's RotaryEmbedding stands on
+    (fla.modules.rotary.rotary_embedding_ref, flash-linear-attention 0.5.1) and against the oracle's own HF-style
+    rotate-half on duplicated-halves tables (scripts/verify_opt_parity.py:48-54)."""
+    torch.manual_seed(4)
+    T, H, K, P = 37, 3, 32, 64
+    x = torch.randn(T, H, K, dtype=torch.float64)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, K, 2, dtype=torch.float64) / K))
+    fr = torch.outer(torch.arange(P, dtype=torch.float64), inv)
+    cos, sin = fr.cos(), fr.sin()
+    pos = torch.arange(5, 5 + T)
+    got = orc.rotary_positions(x, cos, sin, pos)
+    hf = orc.rope_rotate_half(x, torch.cat([cos, cos], -1)[pos], torch.cat([sin, sin], -1)[pos])
+    assert torch.allclose(got, hf, rtol=0, atol=1e-14)
+    rot = pytest.importorskip('fla.modules.rotary')
+    want = rot.rotary_embedding_ref(x[None], cos[pos], sin[pos])[0]
+    assert torch.allclose(got, want, rtol=0, atol=1e-14)
