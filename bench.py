@@ -422,6 +422,8 @@ def main():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='skip the decode and long-context prefill side measurements')
     ap.add_argument('--small', action='store_true', help='B=4 instead of 16 (profiling captures)')
+    ap.add_argument('--pre-op', action='store_true', help='only the slot-gate and rotary side measurements (profiling '
+                    'captures of those kernels; prints their JSON, not the bench line)')
     args = ap.parse_args()
     claim_stdout()
     args.warmup = max(args.warmup, 3)
@@ -482,6 +484,13 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
+
+    if args.pre_op:
+        pk = peaks()[0]
+        out = {'gates': bench_gates(lib, dev, rank, timed, pk), 'rotary': bench_rotary(lib, dev, rank, timed, pk)}
+        if rank == 0:
+            emit(out)
+        return 0
 
     # clocks and throttle reasons are sampled from the warm-up to the last measurement of this process (the timed
     # region itself lasts tens of milliseconds, less than one sampling period)
