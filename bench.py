@@ -237,13 +237,40 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             st = lib.nha_ring_append(d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), d['k'].data_ptr(),
                                      d['v'].data_ptr(), gn.data_ptr(), hd.data_ptr(), B, H, K, K, M, W, W, stream)
             assert st == 0
+    # rings whose keys were rotated when they entered (absolute positions): the step rotates only its own token
+    kr = [torch.empty_like(d['sw_k']) for d in layers]
+    for d, x in zip(layers, kr):
+        assert lib.nha_ring_rotate_rows(d['sw_k'].data_ptr(), x.data_ptr(), cos.data_ptr(), sin.data_ptr(), 0,
+                                        cos.stride(1), B, H, K, W, W, stream) == 0
+    cosq, sinq = cos[:, -1].contiguous(), sin[:, -1].contiguous()
+
+    def step_ring_rot(append=True):
+        for d, x, gn, gw, hd in zip(layers, kr, gnew, gwin, heads):
+            st = lib.nha_decode_step_ring_rot(d['q'].data_ptr(), d['k'].data_ptr(), d['v'].data_ptr(), d['sw_k'].data_ptr(),
+                                              x.data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), hd.data_ptr(),
+                                              cosq.data_ptr(), sinq.data_ptr(), 0, d['hk'].data_ptr(), d['hv'].data_ptr(),
+                                              d['o'].data_ptr(), ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, W,
+                                              K ** -0.5, stream)
+            assert st == 0
+            if append:
+                st = lib.nha_ring_append_rot(d['sw_k'].data_ptr(), x.data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(),
+                                             d['k'].data_ptr(), d['v'].data_ptr(), gn.data_ptr(), cosq.data_ptr(),
+                                             sinq.data_ptr(), 0, hd.data_ptr(), B, H, K, K, M, W, W, stream)
+                assert st == 0
     for _ in range(2):
         step_shift()
         step_ring()
+        step_ring_rot()
     ms_shift = timed(step_shift, 5) / 5
     ms_ring = timed(step_ring, 5) / 5
+    ms_rot = timed(step_ring_rot, 5) / 5
+    ms_rot_only = timed(lambda: step_ring_rot(False), 10) / 10
     with_cache = {'shifted_window_us_per_layer': 1e3 * ms_shift / LAYERS, 'ring_us_per_layer': 1e3 * ms_ring / LAYERS,
                   'ring_tokens_per_s': world * B / (ms_ring * 1e-3),
+                  'ring_rotated_keys_us_per_layer': 1e3 * ms_rot / LAYERS,
+                  'ring_rotated_keys_tokens_per_s': world * B / (ms_rot * 1e-3),
+                  'ring_rotated_keys_decode_only_us_per_layer': 1e3 * ms_rot_only / LAYERS,
+                  'ring_rotated_keys_decode_only_gbs': per_seq_layer * B * LAYERS / (ms_rot_only * 1e-3) / 1e9,
                   'note': 'one generated token per sequence including the window cache update of every layer'}
     return {'workload': 'decode 48 layers x 32 seq/GPU HQ32 H4 D128 M64 W512 bf16, fp32 state', 'ms_per_token_step': ms,
             'with_cache_update': with_cache,

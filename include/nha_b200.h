@@ -110,6 +110,27 @@ int nha_decode_step_ring(const void* q, const void* k_new, const void* v_new, co
 int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new, const void* g_new,
                     int32_t* head, int B, int H, int K, int V, int M, int W, int fill, void* stream);
 
+/* Rings with keys rotated on entry (optional layout of the ring cache above).  Rotary by absolute position does
+ * not change while the window slides, so a key is rotated once, when it enters the ring, and the decode step no
+ * longer rotates (or reads tables for) the W-1 old window keys; the reference rotates the whole window at every
+ * step (nha_fla/models/qwen3_moe_nha/qwennha.py:207-226).  `ring_k` keeps the raw keys (a token's raw key enters the
+ * slot memory when it leaves the window), `ring_kr [B,W,H,K]` the rotated ones.  `cos_q, sin_q [1|B, K]` (bf16,
+ * duplicated halves; `cs_batch` elements between sequences, 0 when shared) are the table row of the position of
+ * this step's token.  Same results, bit for bit, as nha_decode_step_ring on raw keys with absolute-position tables.
+ *   nha_ring_rotate_rows: fills rows 0 .. rows-1 of ring_kr from ring_k with table rows 0 .. rows-1 (after the
+ *     prefill, rings in time order, head == 0).
+ *   nha_decode_step_ring_rot / nha_ring_append_rot: as nha_decode_step_ring / nha_ring_append. */
+int nha_ring_rotate_rows(const void* ring_k, void* ring_kr, const void* cos, const void* sin, int64_t cs_batch,
+                         int64_t cs_row, int B, int H, int K, int W, int rows, void* stream);
+int nha_decode_step_ring_rot(const void* q, const void* k_new, const void* v_new, const void* ring_k, const void* ring_kr,
+                             const void* ring_v, const void* ring_g, const int32_t* head, const void* cos_q,
+                             const void* sin_q, int64_t cs_batch, float* hk, float* hv, void* o, void* workspace,
+                             int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M, int W, int fill,
+                             float scale, void* stream);
+int nha_ring_append_rot(void* ring_k, void* ring_kr, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
+                        const void* g_new, const void* cos_q, const void* sin_q, int64_t cs_batch, int32_t* head, int B,
+                        int H, int K, int V, int M, int W, int fill, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Chunked prefill / training.  One descriptor serves the state pass, the output pass and the
  * backward.  Replaces chunk_nha (nha_fla/ops/nha/chunk.py:568-690; autograd node :352-564,

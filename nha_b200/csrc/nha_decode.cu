@@ -464,7 +464,8 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop);
+                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
+                      const void* ring_kraw);
 
 // Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
 // every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
@@ -547,7 +548,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   if (stream_ok)
     return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
                              errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, nullptr,
-                             nullptr, W, 0);
+                             nullptr, W, 0, nullptr);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;
@@ -611,7 +612,7 @@ extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void
   float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop);
+                           ring_g, W, nopop, nullptr);
 }
 
 extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
@@ -621,5 +622,125 @@ extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const v
   if (B <= 0 || H <= 0 || W < 1 || fill < 0 || fill > W || (H * K) % 8 || (H * V) % 8 || (H * M) % 8) return NHA_ERR_BAD_ARG;
   nha_ring_append_kernel<<<B, 128, 0, (cudaStream_t)stream>>>((bf16*)ring_k, (bf16*)ring_v, (bf16*)ring_g, (const bf16*)k_new,
                                                               (const bf16*)v_new, (const bf16*)g_new, head, H, K, V, M, W, fill);
+  return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rings with keys rotated on entry.  Rotary by absolute position does not change while the window slides, so a
+// key can be rotated once, when it enters the ring, instead of at every step it stays in the window (the
+// reference rotates the whole window every step, nha_fla/models/qwen3_moe_nha/qwennha.py:207-226, with a memo for
+// the tables only).  The raw key is still needed once more, when the token leaves the window and enters the
+// slot memory, so the cache keeps both rings.  The rotation below is the packed bf16 arithmetic of the streaming
+// decode kernel, operation for operation, so that both layouts give the same bits.
+namespace nha {
+
+__device__ __forceinline__ void rotate_half_row(bf16* dst, const bf16* src, const bf16* crow, const bf16* srow, int H, int K,
+                                                int tid, int nthreads) {
+  const int c8h = K >> 4;
+  for (int i = tid; i < H * c8h; i += nthreads) {
+    const int hh = i / c8h, c = i - hh * c8h;
+    const uint4 xu = *reinterpret_cast<const uint4*>(src + hh * K + 8 * c);
+    const uint4 yu = *reinterpret_cast<const uint4*>(src + hh * K + 8 * (c + c8h));
+    const uint4 c1u = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));
+    const uint4 s1u = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));
+    const uint4 c2u = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));
+    const uint4 s2u = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));
+    uint4 o1u, o2u;
+    const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(&xu);
+    const __nv_bfloat162* yv = reinterpret_cast<const __nv_bfloat162*>(&yu);
+    const __nv_bfloat162* c1v = reinterpret_cast<const __nv_bfloat162*>(&c1u);
+    const __nv_bfloat162* s1v = reinterpret_cast<const __nv_bfloat162*>(&s1u);
+    const __nv_bfloat162* c2v = reinterpret_cast<const __nv_bfloat162*>(&c2u);
+    const __nv_bfloat162* s2v = reinterpret_cast<const __nv_bfloat162*>(&s2u);
+    __nv_bfloat162* o1v = reinterpret_cast<__nv_bfloat162*>(&o1u);
+    __nv_bfloat162* o2v = reinterpret_cast<__nv_bfloat162*>(&o2u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      o1v[e] = __hfma2(xv[e], c1v[e], __hneg2(__hmul2(yv[e], s1v[e])));
+      o2v[e] = __hfma2(yv[e], c2v[e], __hmul2(xv[e], s2v[e]));
+    }
+    *reinterpret_cast<uint4*>(dst + hh * K + 8 * c) = o1u;
+    *reinterpret_cast<uint4*>(dst + hh * K + 8 * (c + c8h)) = o2u;
+  }
+}
+
+// one CTA per (sequence, ring row): ring_kr[b, r] = rotate(ring_k[b, r]) with table row r
+__global__ void nha_ring_rotate_rows_kernel(const bf16* ring_k, bf16* ring_kr, const bf16* cosp, const bf16* sinp,
+                                            int64_t cs_batch, int64_t cs_row, int H, int K, int W) {
+  const int b = blockIdx.y, r = blockIdx.x;
+  const size_t row = ((size_t)b * W + r) * H * K;
+  rotate_half_row(ring_kr + row, ring_k + row, cosp + b * cs_batch + r * cs_row, sinp + b * cs_batch + r * cs_row, H, K,
+                  threadIdx.x, blockDim.x);
+}
+
+__global__ void nha_ring_append_rot_kernel(bf16* ring_k, bf16* ring_kr, bf16* ring_v, bf16* ring_g, const bf16* k,
+                                           const bf16* v, const bf16* g, const bf16* cosq, const bf16* sinq, int64_t cs_batch,
+                                           int* head, int H, int K, int V, int M, int W, int fill) {
+  const int b = blockIdx.x;
+  const int hd = fill < W ? fill : head[b];
+  const size_t row = (size_t)b * W + hd;
+  for (int i = threadIdx.x; i < H * K / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_k + row * H * K)[i] = reinterpret_cast<const uint4*>(k + (size_t)b * H * K)[i];
+  rotate_half_row(ring_kr + row * H * K, k + (size_t)b * H * K, cosq + b * cs_batch, sinq + b * cs_batch, H, K, threadIdx.x,
+                  blockDim.x);
+  for (int i = threadIdx.x; i < H * V / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_v + row * H * V)[i] = reinterpret_cast<const uint4*>(v + (size_t)b * H * V)[i];
+  for (int i = threadIdx.x; i < H * M / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(ring_g + row * H * M)[i] = reinterpret_cast<const uint4*>(g + (size_t)b * H * M)[i];
+  __syncthreads();
+  if (threadIdx.x == 0 && fill >= W) head[b] = hd + 1 == W ? 0 : hd + 1;
+}
+
+}  // namespace nha
+
+extern "C" int nha_ring_rotate_rows(const void* ring_k, void* ring_kr, const void* cosp, const void* sinp, int64_t cs_batch,
+                                    int64_t cs_row, int B, int H, int K, int W, int rows, void* stream) {
+  if (!ring_k || !ring_kr || !cosp || !sinp) return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || W < 1 || rows < 0 || rows > W) return NHA_ERR_BAD_ARG;
+  if (K <= 0 || K % 16 || cs_row % 8 || cs_batch % 8) return NHA_ERR_UNSUPPORTED;
+  if (rows == 0) return NHA_OK;
+  nha_ring_rotate_rows_kernel<<<dim3(rows, B), 128, 0, (cudaStream_t)stream>>>((const bf16*)ring_k, (bf16*)ring_kr,
+                                                                             (const bf16*)cosp, (const bf16*)sinp, cs_batch,
+                                                                             cs_row, H, K, W);
+  return check_launch();
+}
+
+extern "C" int nha_decode_step_ring_rot(const void* q, const void* k_new, const void* v_new, const void* ring_k,
+                                        const void* ring_kr, const void* ring_v, const void* ring_g, const int32_t* head,
+                                        const void* cos_q, const void* sin_q, int64_t cs_batch, float* hk, float* hv, void* o,
+                                        void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M,
+                                        int W, int fill, float scale, void* stream) {
+  if (!q || !k_new || !v_new || !ring_k || !ring_kr || !ring_v || !ring_g || !head || !cos_q || !sin_q || !hk || !hv || !o)
+    return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1 || fill < 0 || fill > W) return NHA_ERR_BAD_ARG;
+  const int NG = HQ / H;
+  const int nopop = fill < W, Weff = nopop ? fill + 1 : W;
+  if (!decode_stream_supported(K, V, M, Weff, NG, false) || M % 8) return NHA_ERR_UNSUPPORTED;
+  const int splits = decode_stream_splits(B, H, Weff, M);
+  if (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W)) return NHA_ERR_WORKSPACE;
+  int* tickets = (int*)workspace;
+  int* errw = tickets + (size_t)B * H;
+  char* base = (char*)workspace + align_up((B * H + 1) * (int)sizeof(int), 256);
+  float* part_ml = (float*)base;
+  float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
+  // a table row stride of 0: every window position reads the query's row; the kernel rotates only the query and the
+  // token of this step
+  return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_kr, ring_v, cos_q, sin_q, cs_batch, 0, hk, hv, 0,
+                           o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
+                           ring_g, W, nopop, ring_k);
+}
+
+extern "C" int nha_ring_append_rot(void* ring_k, void* ring_kr, void* ring_v, void* ring_g, const void* k_new,
+                                   const void* v_new, const void* g_new, const void* cos_q, const void* sin_q,
+                                   int64_t cs_batch, int32_t* head, int B, int H, int K, int V, int M, int W, int fill,
+                                   void* stream) {
+  if (!ring_k || !ring_kr || !ring_v || !ring_g || !k_new || !v_new || !g_new || !cos_q || !sin_q || !head)
+    return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || W < 1 || fill < 0 || fill > W || K % 16 || (H * V) % 8 || (H * M) % 8 || cs_batch % 8)
+    return NHA_ERR_BAD_ARG;
+  nha_ring_append_rot_kernel<<<B, 128, 0, (cudaStream_t)stream>>>((bf16*)ring_k, (bf16*)ring_kr, (bf16*)ring_v, (bf16*)ring_g,
+                                                                  (const bf16*)k_new, (const bf16*)v_new, (const bf16*)g_new,
+                                                                  (const bf16*)cos_q, (const bf16*)sin_q, cs_batch, head, H, K,
+                                                                  V, M, W, fill);
   return check_launch();
 }

@@ -54,6 +54,10 @@ struct DecodeStreamArgs {
   // WR: rows of a ring (W outside ring mode).  nopop != 0: the rings are still filling - they hold the W - 1 oldest
   // window entries in rows 0 .. W - 2, nothing leaves the window and the slot memory keeps its value
   int WR, nopop;
+  // ring_kraw != NULL (ring mode only): sw_k is a ring of keys that were rotated when they entered it (rotary by
+  // absolute position does not change while the window slides), so only the token of this step is rotated here;
+  // the raw key that enters the slot memory comes from ring_kraw
+  const bf16* ring_kraw;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
@@ -153,7 +157,9 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   const int WR = a.WR;
   const int hd = isring ? (a.nopop ? -1 : a.head[b]) : 0;              // physical row of the oldest ring entry
   // the token that enters the slot memory: separate small tensors, or the oldest ring entry
-  const bf16* kpop_g = isring ? a.sw_k + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D : a.k + (size_t)bh * D;
+  const bool prerot = a.ring_kraw != nullptr;
+  const bf16* kpop_g = isring ? (prerot ? a.ring_kraw : a.sw_k) + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D
+                              : a.k + (size_t)bh * D;
   const bf16* vpop_g = isring ? a.sw_v + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D : a.v + (size_t)bh * D;
   const bf16* gpop_g = isring ? a.ring_g + (((size_t)b * WR + max(hd, 0)) * a.H + h) * M : a.g + (size_t)bh * M;
   bool failed = false;
@@ -366,13 +372,16 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   _Pragma("unroll") for (int u = 0; u < kTasks; ++u) {                                              \
     const int i = lane + 32 * u;                                                                    \
     const int r = i / c8h, c = i - r * c8h;                                                         \
-    const int wpos = min(w0 + (st_) * kStrStage + 8 * warp + r, W - 1);                             \
-    const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                          \
-    const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                          \
-    cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));                                 \
-    cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));                                 \
-    cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));                         \
-    cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));                         \
+    const int wraw = w0 + (st_) * kStrStage + 8 * warp + r;                                         \
+    const int wpos = min(wraw, W - 1);                                                              \
+    if (!prerot || wraw == W - 1) {                     /* rotated ring: only the token of this step */ \
+      const bf16* crow = a.cosp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                        \
+      const bf16* srow = a.sinp + b * a.cs_batch + (int64_t)wpos * a.cs_row;                        \
+      cs[u][0] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * c));                               \
+      cs[u][1] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * c));                               \
+      cs[u][2] = __ldg(reinterpret_cast<const uint4*>(crow + 8 * (c + c8h)));                       \
+      cs[u][3] = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (c + c8h)));                       \
+    }                                                                                               \
   }
   if (rotary && nst > 0) { NHA_LOAD_TABLE(0) }
   for (int st = 0; st < nst; ++st) {
@@ -385,6 +394,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       for (int u = 0; u < kTasks; ++u) {
         const int i = lane + 32 * u;
         const int r = i / c8h, c = i - r * c8h;
+        if (prerot && w0 + st * kStrStage + 8 * warp + r != W - 1) continue;
         // packed bf16 arithmetic: x c1 - y s1 and y c2 + x s2 on pairs, the first product rounded to bf16
         uint4 xu = *reinterpret_cast<const uint4*>(kst + r * ldk + 8 * c);
         uint4 yu = *reinterpret_cast<const uint4*>(kst + r * ldk + 8 * (c + c8h));
@@ -799,7 +809,8 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
-                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop) {
+                      cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
+                      const void* ring_kraw) {
   DecodeStreamArgs a;
   a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
   a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
@@ -808,6 +819,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
   a.part_o = part_o; a.part_ml = part_ml; a.tickets = tickets; a.err = err;
   a.head = head; a.ring_g = (const bf16*)ring_g;
   a.WR = head ? ring_rows : W; a.nopop = head ? nopop : 0;
+  a.ring_kraw = head ? (const bf16*)ring_kraw : nullptr;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
   a.zero_state = zero_state; a.scale = scale;

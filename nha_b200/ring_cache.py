@@ -29,7 +29,7 @@ class RingLayer:
     """Rings, head indices and slot memory of one layer."""
 
     def __init__(self, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor,
-                 window_size: Optional[int] = None):
+                 window_size: Optional[int] = None, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
         # k [B,T,H,K], v [B,T,H,V], g [B,T,H,M]: the last T <= W tokens, oldest first; hk [B,H,K,M], hv [B,H,M,V] fp32.
         # With T < W the rings are still filling: entries in rows 0 .. T-1, `fill` counts them (host side).
         assert k.dim() == 4 and v.dim() == 4 and g.dim() == 4 and k.shape[:3] == v.shape[:3] == g.shape[:3]
@@ -45,6 +45,21 @@ class RingLayer:
         self.head = torch.zeros(k.shape[0], dtype=torch.int32, device=k.device)
         self.hk = hk.float().contiguous().clone()
         self.hv = hv.float().contiguous().clone()
+        # rope = (cos, sin) [1|B, T, K] of the T kept tokens' absolute positions: a second key ring holds the keys
+        # rotated on entry, and a decode step then rotates only its own token (rotary by absolute position does
+        # not change while the window slides)
+        self.ring_kr = None
+        if rope is not None:
+            cos, sin = (t.to(_BF16).contiguous() for t in rope)
+            assert cos.dim() == 3 and cos.shape == sin.shape and cos.shape[1] == self.fill and cos.shape[2] == k.shape[3]
+            self.ring_kr = torch.zeros_like(self.ring_k)
+            if self.fill:
+                cs_batch = cos.stride(0) if cos.shape[0] > 1 else 0
+                with torch.cuda.device(k.device):
+                    _lib.check(_lib.load().nha_ring_rotate_rows(
+                        self.ring_k.data_ptr(), self.ring_kr.data_ptr(), cos.data_ptr(), sin.data_ptr(), cs_batch,
+                        cos.stride(1), k.shape[0], k.shape[2], k.shape[3], W, self.fill,
+                        torch.cuda.current_stream(k.device).cuda_stream), 'nha_ring_rotate_rows')
 
     @property
     def window(self) -> int:
@@ -75,6 +90,8 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
     H, V, M, W = k.shape[2], v.shape[3], g.shape[3], layer.window
     fill = layer.fill
     wlen = W if fill >= W else fill + 1
+    if layer.ring_kr is not None:
+        return _decode_ring_rot(q, k, v, g, layer, cos, sin, scale)
     assert cos.shape[-2] == wlen and cos.shape[-1] == K, 'cos/sin must cover the window positions'
     dev = q.device
     qc, kc, vc, gc = (x.to(_BF16).contiguous() for x in (q, k, v, g))
@@ -96,6 +113,35 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
     return o
 
 
+def _decode_ring_rot(q, k, v, g, layer: RingLayer, cos, sin, scale) -> torch.Tensor:
+    """Decode step on rings whose keys were rotated on entry: only the last row of ``cos/sin [1|B, >=1, K]`` (the
+    position of this step's token) is read."""
+    lib = _lib.load()
+    B, _, HQ, K = q.shape
+    H, V, M, W = k.shape[2], v.shape[3], g.shape[3], layer.window
+    assert cos.shape[-1] == K and cos.shape == sin.shape
+    dev = q.device
+    qc, kc, vc, gc = (x.to(_BF16).contiguous() for x in (q, k, v, g))
+    cosq, sinq = cos[:, -1].to(_BF16).contiguous(), sin[:, -1].to(_BF16).contiguous()        # [1|B, K]
+    cs_batch = cosq.stride(0) if cosq.shape[0] > 1 else 0
+    sc = float(scale) if scale is not None else K ** -0.5
+    o = torch.empty(B, 1, HQ, V, device=dev, dtype=_BF16)
+    ws = _decode_workspace(dev, B, HQ, H, V, W)
+    st = _stream(dev)
+    fill = layer.fill
+    _lib.check(lib.nha_decode_step_ring_rot(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
+                                            layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
+                                            layer.head.data_ptr(), cosq.data_ptr(), sinq.data_ptr(), cs_batch,
+                                            layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
+                                            ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st), 'nha_decode_step_ring_rot')
+    _lib.check(lib.nha_ring_append_rot(layer.ring_k.data_ptr(), layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(),
+                                       layer.ring_g.data_ptr(), kc.data_ptr(), vc.data_ptr(), gc.data_ptr(),
+                                       cosq.data_ptr(), sinq.data_ptr(), cs_batch, layer.head.data_ptr(), B, H, K, V, M, W,
+                                       fill, st), 'nha_ring_append_rot')
+    layer.fill = min(fill + 1, W)
+    return o
+
+
 class NHARingCache:
     """Per-layer ring caches with the read-side surface of the reference's ``NHACache``."""
 
@@ -112,14 +158,19 @@ class NHARingCache:
         raise KeyError(f'Cache only has {len(self)} layers, attempted to access layer with index {layer_idx}')
 
     def init_layer(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, window_size: int,
-                   recurrent_state: Tuple[torch.Tensor, torch.Tensor]) -> RingLayer:
+                   recurrent_state: Tuple[torch.Tensor, torch.Tensor],
+                   rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> RingLayer:
         """Fill a layer from its prefill: ``k, v, g [B,T,H,*]`` (the last ``window_size`` tokens are kept, as
         ``NHACache.update`` does; a shorter prompt leaves the rings partly filled) and the slot memory after the
-        prefill."""
+        prefill.  With ``rope = (cos, sin) [1|B, T, K]`` (tables of the T tokens' absolute positions) the layer also
+        keeps the keys rotated on entry, and ``decode`` then needs only the table row of the new token's position
+        (the last row of what it is given); rotary positions must be absolute for this layout."""
+        if rope is not None:
+            rope = tuple(t[:, -window_size:] for t in rope)
         while len(self.layers) <= layer_idx:
             self.layers.append(None)
         layer = RingLayer(k[:, -window_size:], v[:, -window_size:], g[:, -window_size:], *recurrent_state,
-                          window_size=window_size)
+                          window_size=window_size, rope=rope)
         self.layers[layer_idx] = layer
         return layer
 
