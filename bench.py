@@ -411,6 +411,39 @@ def bench_rotary(lib, dev, rank, timed, peak):
                          'frac': nbytes / (ms * 1e-3) / 1e9 / peak}}
 
 
+def bench_lse_stats(lib, dev, rank, timed):
+    """The training layer's aux loss and compression statistic at the bench shape (T*HQ = 524288 log-sum-exp pairs,
+    4 MB): one launch for both means plus one for the gradient, beside the layer's chain of torch kernels with
+    autograd and its .item() (nha_fla/layers/nha.py:255-264, 288-323)."""
+    n = 16 * 2048 * 16
+    gd = torch.Generator(device=dev).manual_seed(37 + rank)
+    ls = torch.randn(n, generator=gd, device=dev) * 3
+    lg = torch.randn(n, generator=gd, device=dev) * 3
+    out, d = torch.empty(2, device=dev), torch.empty(n, device=dev)
+    one = torch.ones(1, device=dev)
+    scratch = torch.zeros(int(lib.nha_lse_stats_scratch_bytes()), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def ours():
+        assert lib.nha_lse_stats(ls.data_ptr(), lg.data_ptr(), n, 0.3, out.data_ptr(), scratch.data_ptr(), stream) == 0
+        assert lib.nha_lse_aux_grad(ls.data_ptr(), lg.data_ptr(), one.data_ptr(), n, 0.3, d.data_ptr(), stream) == 0
+    lgt = lg.clone().requires_grad_(True)
+
+    def chain():
+        lgt.grad = None
+        mx = torch.maximum(ls, lgt)
+        w_swa, w_gsa = torch.exp(ls - mx), torch.exp(lgt - mx)
+        with torch.no_grad():
+            (w_gsa / (w_swa + w_gsa)).mean().item()
+        delta = lgt.float() - ls.detach().float()
+        F.binary_cross_entropy_with_logits(delta, torch.full_like(delta, 0.3), reduction='mean').backward()
+    for fn in (ours, chain):
+        for _ in range(3):
+            fn()
+    return {'workload': 'aux loss + slot-branch share from 524288 lse pairs, forward and gradient', 'ms': timed(ours, 20) / 20,
+            'torch_chain_ms': timed(chain, 10) / 10, 'gpu_launches': 2}
+
+
 def tensor_peak():
     p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(p):
@@ -514,7 +547,8 @@ def main():
 
     if args.pre_op:
         pk = peaks()[0]
-        out = {'gates': bench_gates(lib, dev, rank, timed, pk), 'rotary': bench_rotary(lib, dev, rank, timed, pk)}
+        out = {'gates': bench_gates(lib, dev, rank, timed, pk), 'rotary': bench_rotary(lib, dev, rank, timed, pk),
+               'lse_stats': bench_lse_stats(lib, dev, rank, timed)}
         if rank == 0:
             emit(out)
         return 0
@@ -666,7 +700,8 @@ def main():
                   'prefill': bench_prefill(dev, rank, world, dist, timed),
                   'varlen': bench_varlen(dev, rank, timed),
                   'gates': bench_gates(lib, dev, rank, timed, peak),
-                  'rotary': bench_rotary(lib, dev, rank, timed, peak)}
+                  'rotary': bench_rotary(lib, dev, rank, timed, peak),
+                  'lse_stats': bench_lse_stats(lib, dev, rank, timed)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -266,6 +266,23 @@ int nha_rope_pair(const void* q, const void* k, void* q_out, void* k_out, const 
                   int64_t cs_row, int table_rows, const int32_t* cu_seqlens, int N, int T, int64_t Ttot, int HQ,
                   int H, int K, int offset, int inverse, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Layer-side consumers of lse_swa / lse_gsa, fused (the training layer's aux loss and compression
+ * statistic, nha_fla/layers/nha.py:255-264, 288-323): with delta = lse_gsa - lse_swa over n = T*HQ
+ * elements (fp32),
+ *     out[0] = mean(binary_cross_entropy_with_logits(delta, target)),   out[1] = mean(sigmoid(delta))
+ * (the latter is the reference's gsa_ratio = mean(w_gsa / (w_swa + w_gsa))).  Results stay on the device.
+ *   nha_lse_stats: one launch; `scratch` of nha_lse_stats_scratch_bytes() bytes, zeroed ONCE by the caller
+ *     before its first use (the kernel leaves it ready for the next call; calls sharing a scratch must be
+ *     in stream order).  The sum order is fixed: equal inputs give equal bits.
+ *   nha_lse_aux_grad: d_lse_gsa[i] = dloss[0] * (sigmoid(delta_i) - target) / n, the gradient the layer's
+ *     autograd sends into the operator (lse_swa is detached there, :303). */
+int64_t nha_lse_stats_scratch_bytes(void);
+int nha_lse_stats(const float* lse_swa, const float* lse_gsa, int64_t n, float target, float* out, void* scratch,
+                  void* stream);
+int nha_lse_aux_grad(const float* lse_swa, const float* lse_gsa, const float* dloss, int64_t n, float target,
+                     float* d_lse_gsa, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

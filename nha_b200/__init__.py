@@ -7,9 +7,10 @@ from .chunk import chunk_nha
 from .chunk_fused import fused_chunk_nha_prefill
 from .fused_recurrent import fused_recurrent_nha, fused_recurrent_nha_decode
 from .gates import slot_gates
+from .lse_stats import gsa_aux_loss
 from .rotary import rotary_pair
 from .ring_cache import NHARingCache, fused_recurrent_nha_decode_ring
 
 __all__ = ['chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode',
-           'fused_recurrent_nha_decode_ring', 'NHARingCache', 'slot_gates', 'rotary_pair']
+           'fused_recurrent_nha_decode_ring', 'NHARingCache', 'slot_gates', 'rotary_pair', 'gsa_aux_loss']
 __version__ = '0.1.0'

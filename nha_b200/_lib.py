@@ -70,6 +70,9 @@ SYMBOLS = {
     'nha_slot_gates_fwd': (C.c_int, [c_void_p, c_void_p, c_void_p, C.c_int64, C.c_float, c_void_p]),
     'nha_rope_pair': (C.c_int, [c_void_p] * 6 + [C.c_int64, C.c_int, c_void_p, C.c_int, C.c_int, C.c_int64] + [C.c_int] * 5
                       + [c_void_p]),
+    'nha_lse_stats_scratch_bytes': (C.c_int64, []),
+    'nha_lse_stats': (C.c_int, [c_void_p, c_void_p, C.c_int64, C.c_float, c_void_p, c_void_p, c_void_p]),
+    'nha_lse_aux_grad': (C.c_int, [c_void_p, c_void_p, c_void_p, C.c_int64, C.c_float, c_void_p, c_void_p]),
     'nha_slot_gates_bwd': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, C.c_int64, C.c_float, c_void_p]),
 }
 

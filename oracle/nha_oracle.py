@@ -48,6 +48,7 @@ __all__ = [
     "recurrent_step",
     "slot_gates",
     "rotary_positions",
+    "gsa_aux",
     "rel_l2",
 ]
 
@@ -256,3 +257,15 @@ def rotary_positions(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     s = sin.double()[positions, None, :R]
     x0, x1 = x[..., :R], x[..., R:]
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], -1)
+
+
+def gsa_aux(lse_swa: torch.Tensor, lse_gsa: torch.Tensor, target: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The training layer's two scalars in fp64 (nha_fla/layers/nha.py:255-264, 288-313): the aux loss
+    ``mean(BCE_with_logits(lse_gsa - lse_swa.detach(), target))`` (differentiable in ``lse_gsa``) and the monitoring
+    ratio ``mean(w_gsa / (w_swa + w_gsa))`` with ``w_x = exp(lse_x - max(lse_swa, lse_gsa))``."""
+    ls, lg = lse_swa.double().detach(), lse_gsa.double()
+    d = lg - ls
+    loss = (d.clamp(min=0) - d * target + torch.log1p(torch.exp(-d.abs()))).mean()
+    mx = torch.maximum(ls, lg.detach())
+    ws, wg = (ls - mx).exp(), (lg.detach() - mx).exp()
+    return loss, (wg / (ws + wg)).mean()

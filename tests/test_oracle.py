@@ -160,3 +160,24 @@ def test_rotary_positions_against_fla_reference_and_rotate_half():
     rot = pytest.importorskip('fla.modules.rotary')
     want = rot.rotary_embedding_ref(x[None], cos[pos], sin[pos])[0]
     assert torch.allclose(got, want, rtol=0, atol=1e-14)
+
+
+def test_gsa_aux_against_the_layer_chain():
+    """The oracle's aux-loss function against the layer's own lines run literally
+    (nha_fla/layers/nha.py:257-259, 291-292, 308-312)."""
+    import torch.nn.functional as F
+    torch.manual_seed(5)
+    ls = torch.randn(3, 50, 4, dtype=torch.float64) * 3
+    lg = (torch.randn(3, 50, 4, dtype=torch.float64) * 3).requires_grad_(True)
+    loss, ratio = orc.gsa_aux(ls, lg, 0.3)
+    lse_max = torch.maximum(ls, lg)
+    w_swa, w_gsa = torch.exp(ls - lse_max), torch.exp(lg - lse_max)
+    want_ratio = (w_gsa / (w_swa + w_gsa)).mean()
+    delta = lg - ls.detach()                        # the layer writes .float() here: its lse tensors are fp32
+    want = F.binary_cross_entropy_with_logits(delta, torch.full_like(delta, 0.3), reduction='mean')
+    assert torch.allclose(loss, want, rtol=0, atol=1e-14) and torch.allclose(ratio, want_ratio.detach(), rtol=0, atol=1e-14)
+    (g1,) = torch.autograd.grad(loss, lg, retain_graph=True)
+    lg2 = lg.detach().clone().requires_grad_(True)
+    d2 = lg2 - ls
+    (g2,) = torch.autograd.grad(F.binary_cross_entropy_with_logits(d2, torch.full_like(d2, 0.3)), lg2)
+    assert torch.allclose(g1, g2, rtol=0, atol=1e-15)
