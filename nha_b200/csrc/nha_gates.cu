@@ -27,21 +27,9 @@ __device__ __forceinline__ float log_sigmoid(float x) {
   // min(x, 0) - log1p(exp(-|x|)); accurate for both tails
   return fminf(x, 0.0f) - log1p_unit(__expf(-fabsf(x)));
 }
-// exp(g) for g <= 0 on the FMA and integer pipes (the special-function unit is the busiest pipe of these kernels):
-// g log2(e) = n + f with n the nearest integer and |f| <= 1/2, 2^f by a degree-4 polynomial (4e-5 relative, far inside
-// the bf16 rounding of the result), 2^n by an add into the exponent field.
-__device__ __forceinline__ float exp_nonpos_fma(float g) {
-  const float t = fmaxf(g * 1.4426950408889634f, -125.0f);
-  const float magic = 12582912.0f;                           // 1.5 * 2^23: adding it rounds t to the nearest integer
-  const float r = t + magic;
-  const float f = (t - (r - magic)) * 0.6931471805599453f;   // f ln 2, |.| <= 0.347
-  const float p = 1.0f + f * (1.0f + f * (0.5f + f * (0.16666667f + f * 0.041666668f)));
-  const int n = __float_as_int(r) - __float_as_int(magic);
-  return __int_as_float(__float_as_int(p) + (n << 23));
-}
 // 1 - exp(g) for g <= 0 without cancellation near 0
 __device__ __forceinline__ float one_minus_exp(float g) {
-  return g > -1e-2f ? -g * (1.0f + g * (0.5f + g * (1.0f / 6.0f))) : 1.0f - exp_nonpos_fma(g);
+  return g > -1e-2f ? -g * (1.0f + g * (0.5f + g * (1.0f / 6.0f))) : 1.0f - __expf(g);
 }
 
 __device__ __forceinline__ void gate_of(float f, float inv_norm, bf16& g_out, bf16& s_out) {
@@ -93,7 +81,7 @@ __global__ void __launch_bounds__(kGateThreads) nha_slot_gates_fwd_kernel(const 
 __device__ __forceinline__ float gate_grad(float f, float dg, float ds, float inv_norm) {
   const float g = log_sigmoid(f) * inv_norm;
   const float sig = __fdividef(1.0f, 1.0f + __expf(fminf(f, 80.0f)));   // sigmoid(-f); the clamp keeps the divisor finite
-  return (dg - ds * exp_nonpos_fma(g)) * sig * inv_norm;
+  return (dg - ds * __expf(g)) * sig * inv_norm;
 }
 
 __global__ void __launch_bounds__(kGateThreads) nha_slot_gates_bwd_kernel(const bf16* __restrict__ f, const bf16* __restrict__ dg,
