@@ -8,18 +8,14 @@ Two modes, following how the operator shards:
   ``[r*T/P, (r+1)*T/P)``) has exactly one exchange step, implemented by
   :func:`sequence_parallel_prefill`:
 
-    1. every rank summarises its own tokens from a zero start, in two parts (all but the last ``W``
-       tokens, and the last ``W``): the slot memory ``L`` they would leave and their total log decay
-       ``G`` - the recurrence is linear, so ``S_after = S_before * exp(G) + L``;
-    2. halo: rank r receives from rank r-1 the last ``W`` tokens of ``k, rotary_k, v, s, g`` (the
-       keys/values its first ``W`` queries still see, and the tokens that enter the slot memory during
-       them because of the shift by ``W``) - one point-to-point message - and one all-gather of the
-       summaries;
-    3. every rank folds the parts before it: the state before its first token, and the state ``W``
-       tokens earlier;
-    4. the rank's forward runs on its own tensors (no copy of the segment) from the state before its
-       first token, fully parallel with the other ranks; its first ``W`` rows, which need the halo, are
-       recomputed by a second, small forward over the ``2W`` tokens around the boundary.
+    1. halo: rank r receives from rank r-1 the last ``W`` tokens of ``k, rotary_k, v, s, g`` (the
+       keys/values its first queries still see, and the tokens that enter its slot memory late
+       because of the shift by ``W``) - one point-to-point message;
+    2. every rank summarises its segment: the slot memory it would end with from a zero start,
+       ``L_r``, and the total log decay ``G_r`` of the tokens that enter - the recurrence is linear,
+       so ``S_start(r+1) = S_start(r) * exp(G_r) + L_r``;
+    3. one all-gather of ``(L_r, G_r)``; every rank folds the ranks before it;
+    4. the rank's forward runs from its true start state, fully parallel with the other ranks.
 
   The reference has no distributed code at all (its long-context story is the O(1) state plus
   ``initial_state`` resumption, nha_fla/ops/nha/chunk_fused.py:337-342); the single-device op is the
@@ -76,22 +72,7 @@ def sequence_parallel_prefill(
         scale = q.shape[-1] ** -0.5
     dev = k.device
 
-    H, K, M, V = k.shape[2], k.shape[3], s.shape[3], v.shape[3]
-    nk, nv = H * K * M, H * M * V
-
-    # ---- 1. summaries of this rank's own tokens from a zero start, in two parts: A = all but the last W tokens,
-    #         B = the last W.  They need nothing from another rank.  `local_state` absorbs all but the last W
-    #         tokens of what it is given, so B is followed by W tokens of padding. -----------------------------------
-    LkA, LvA = local_state(k, v, s, g, W)
-    tail = lambda x: torch.cat([x[:, Tr - W:], torch.zeros_like(x[:, :W])], 1)
-    LkB, LvB = local_state(tail(k), tail(v), tail(s), tail(g), W)
-    GA = g[:, :Tr - W].sum(1, dtype=torch.float32)                         # [B,H,M] total log decay of each part
-    GB = g[:, Tr - W:].sum(1, dtype=torch.float32)
-    part = lambda lk, lv, G: torch.cat([lk.reshape(B, -1).float(), lv.reshape(B, -1).float(), G.reshape(B, -1)], 1)
-    pack = torch.stack([part(LkA, LvA, GA), part(LkB, LvB, GB)]).contiguous()   # [2, B, nk + nv + H*M]
-
-    # ---- 2. the exchange: halo of W tokens from the left neighbour (kv-head tensors only) and the all-gather of
-    #         the summaries ---------------------------------------------------------------------------------------
+    # ---- 1. halo of W tokens from the left neighbour (kv-head tensors only) ---------------------------
     send = [x[:, Tr - W:].contiguous() for x in (k, rotary_k, v, s, g)]
     recv = [torch.empty_like(x) for x in send]
     ops = []
@@ -99,42 +80,46 @@ def sequence_parallel_prefill(
         ops += [dist.P2POp(dist.isend, x, dist.get_global_rank(group, rank + 1) if group else rank + 1, group) for x in send]
     if rank > 0:
         ops += [dist.P2POp(dist.irecv, x, dist.get_global_rank(group, rank - 1) if group else rank - 1, group) for x in recv]
-    works = dist.batch_isend_irecv(ops) if ops else []
-    allp = [torch.empty_like(pack) for _ in range(world)]
-    dist.all_gather(allp, pack, group=group)
-    for w in works:
-        w.wait()
-
-    # ---- 3. fold the parts before this rank: the recurrence is linear, S_after = S_before * exp(G) + L.  Parts in
-    #         time order are A_0, B_0, A_1, B_1, ...; the state before this rank's first token has absorbed the first
-    #         2*rank of them, the state W tokens earlier one part less. ------------------------------------------------
-    if initial_state is not None and initial_state != (None, None):
-        S0k, S0v = initial_state[0].float(), initial_state[1].float()
-    else:
-        S0k = torch.zeros(B, H, K, M, dtype=torch.float32, device=dev)
-        S0v = torch.zeros(B, H, M, V, dtype=torch.float32, device=dev)
-
-    def fold(n):
-        if n == 0:
-            return S0k.clone(), S0v.clone()
-        P = torch.cat(allp[:(n + 1) // 2])[:n]                             # [n, B, nk + nv + H*M], time order
-        Gs = P[:, :, nk + nv:].reshape(n, B, H, M)
-        after = Gs.flip(0).cumsum(0).flip(0) - Gs                          # total log decay of the parts after each
-        wgt, tot = after.exp(), Gs.sum(0).exp()
-        Sk = S0k * tot[:, :, None, :] + (P[:, :, :nk].reshape(n, B, H, K, M) * wgt[:, :, :, None, :]).sum(0)
-        Sv = S0v * tot[:, :, :, None] + (P[:, :, nk:nk + nv].reshape(n, B, H, M, V) * wgt[:, :, :, :, None]).sum(0)
-        return Sk, Sv
-
-    # ---- 4. the rank's own tokens from the state before its first token: no copies of the segment.  Rows >= W are
-    #         final; the first W rows lack the neighbour's keys and are recomputed below. ------------------------------
-    o, hk, hv = forward(q, k, v, rotary_q, rotary_k, s, g, W, scale, fold(2 * rank))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
     if rank > 0:
-        # ---- 5. the first W rows: the 2W tokens around the boundary (halo + own first W), queries of the halo
-        #         rows zero, from the state W tokens before the boundary ------------------------------------------------
         hk_, hrk, hv_, hs, hg = recv
         zq = q.new_zeros(B, W, *q.shape[2:])
-        head = lambda h, x: torch.cat([h, x[:, :W]], 1)
-        oh, _, _ = forward(head(zq, q), head(hk_, k), head(hv_, v), head(zq, rotary_q), head(hrk, rotary_k), head(hs, s),
-                           head(hg, g), W, scale, fold(2 * rank - 1))
-        o[:, :W] = oh[:, W:]
+        q_e, rq_e = torch.cat([zq, q], 1), torch.cat([zq, rotary_q], 1)
+        k_e, rk_e = torch.cat([hk_, k], 1), torch.cat([hrk, rotary_k], 1)
+        v_e, s_e, g_e = torch.cat([hv_, v], 1), torch.cat([hs, s], 1), torch.cat([hg, g], 1)
+    else:
+        q_e, rq_e, k_e, rk_e, v_e, s_e, g_e = q, rotary_q, k, rotary_k, v, s, g
+
+    # ---- 2. segment summary from a zero start --------------------------------------------------------------
+    # tokens entering the slot memory during this rank's steps: all of the extended segment but its last W
+    n_enter = k_e.shape[1] - W
+    Lk, Lv = local_state(k_e, v_e, s_e, g_e, W)
+    G = g_e[:, :n_enter].float().sum(1)                                   # [B,H,M] total log decay
+
+    # ---- 3. all-gather of the summaries, fold the ranks before this one ------------------------------------------
+    pack = torch.cat([Lk.reshape(B, -1).float(), Lv.reshape(B, -1).float(), G.reshape(B, -1)], 1).contiguous()
+    allp = [torch.empty_like(pack) for _ in range(world)]
+    dist.all_gather(allp, pack, group=group)
+    H, K, M = Lk.shape[1], Lk.shape[2], Lk.shape[3]
+    V = Lv.shape[3]
+    nk, nv = H * K * M, H * M * V
+    if initial_state is not None and initial_state != (None, None):
+        Sk, Sv = initial_state[0].float().clone(), initial_state[1].float().clone()
+    else:
+        Sk = torch.zeros(B, H, K, M, dtype=torch.float32, device=dev)
+        Sv = torch.zeros(B, H, M, V, dtype=torch.float32, device=dev)
+    for r in range(rank):
+        pr = allp[r]
+        lk = pr[:, :nk].reshape(B, H, K, M)
+        lv = pr[:, nk:nk + nv].reshape(B, H, M, V)
+        dec = pr[:, nk + nv:].reshape(B, H, M).exp()
+        Sk = Sk * dec[:, :, None, :] + lk
+        Sv = Sv * dec[:, :, :, None] + lv
+
+    # ---- 4. forward from the true start state -----------------------------------------------------------------------
+    o, hk, hv = forward(q_e, k_e, v_e, rq_e, rk_e, s_e, g_e, W, scale, (Sk, Sv))
+    if rank > 0:
+        o = o[:, W:]
     return o, (hk, hv)
