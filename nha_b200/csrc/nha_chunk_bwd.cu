@@ -275,28 +275,37 @@ __global__ void __launch_bounds__(kBwThreads) nha_bwd_window_cols_kernel(const n
 // ================================================================================================
 // 3. slot pass: everything of the slot branch that stays inside a chunk
 // ================================================================================================
-struct SlotLayout { int kp, vp, G, Hk, Hv, SB, qb, dob, OK, Y, SA, AB, AvB, dzg, dza, paq, DQ, rows, total; };
+// Two tiles share storage with tiles that are dead while they are live, where the sizes allow it (this is what lets
+// K = V = 128 with M = 64 fit the 227 KB): Hv is only read by the first product of a head (do Hv^T), before tril(A)
+// and tril(Av) are written, so it may sit in their two tiles and is then fetched again for every query head; DQ is
+// written after the last read of OK and Y (step 3) and may lie over that pair.
+struct SlotLayout { int kp, vp, G, Hk, Hv, SB, qb, dob, OK, Y, SA, AB, AvB, dzg, dza, paq, DQ, rows, total, hv_alias; };
 __host__ __device__ inline SlotLayout slot_layout(int K, int V, int M) {
   SlotLayout L; int off = 0;
   const int KV = K > V ? K : V;
+  const int sz_hv = bup128(M * (V + 8) * 2), sz_ab = bup128(kChunk * (kChunk + 8) * 2);
+  const int sz_ok = bup128(kChunk * (M + 4) * 4), sz_dq = bup128(kChunk * (KV + 4) * 4);
+  L.hv_alias = sz_hv <= 2 * sz_ab;
   L.kp = off; off = bup128(off + kChunk * (K + 8) * 2);
   L.vp = off; off = bup128(off + kChunk * (V + 8) * 2);
   L.G = off; off = bup128(off + kChunk * (M + 4) * 4);
   L.Hk = off; off = bup128(off + K * (M + 8) * 2);
-  L.Hv = off; off = bup128(off + M * (V + 8) * 2);
+  L.Hv = off; if (!L.hv_alias) off += sz_hv;
   L.SB = off; off = bup128(off + 160 * (M + 8) * 2);
   L.qb = off; off = bup128(off + kChunk * (K + 8) * 2);
   L.dob = off; off = bup128(off + kChunk * (V + 8) * 2);
-  L.OK = off; off = bup128(off + kChunk * (M + 4) * 4);
-  L.Y = off; off = bup128(off + kChunk * (M + 4) * 4);
+  L.OK = off; off += sz_ok;
+  L.Y = off; off += sz_ok;
   const int sa_cols = M > kChunk ? M : kChunk;
   L.SA = off; off = bup128(off + kChunk * (sa_cols + 4) * 4);
-  L.AB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
-  L.AvB = off; off = bup128(off + kChunk * (kChunk + 8) * 2);
+  L.AB = off; off += sz_ab;
+  L.AvB = off; off += sz_ab;
+  if (L.hv_alias) L.Hv = L.AB;
   L.dzg = off; off = bup128(off + kChunk * (M + 8) * 2);
   L.dza = off; off = bup128(off + kChunk * (M + 8) * 2);
   L.paq = off; off = bup128(off + kChunk * (M + 8) * 2);
-  L.DQ = off; off = bup128(off + kChunk * (KV + 4) * 4);
+  if (sz_dq <= 2 * sz_ok) L.DQ = L.OK;
+  else { L.DQ = off; off += sz_dq; }
   L.rows = off; off = bup128(off + 4 * kChunk * 4);
   L.total = off;
   return L;
@@ -403,7 +412,8 @@ __device__ __forceinline__ void nha_bwd_slot_kernel_body(const nha_chunk_desc d,
       for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
     }
     load_tile_bf16(Hk, ldhk, (const bf16*)d.hk_chunks + ((size_t)cg * H + h) * K * M, M, 0, 0, K, K, M, tid, kBwThreads);
-    load_tile_bf16(Hv, ldhv, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * V, V, 0, 0, M, M, V, tid, kBwThreads);
+    if (!L.hv_alias)
+      load_tile_bf16(Hv, ldhv, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * V, V, 0, 0, M, M, V, tid, kBwThreads);
   }
   __syncthreads();
   for (int m = tid; m < M; m += kBwThreads) {
@@ -437,6 +447,8 @@ __device__ __forceinline__ void nha_bwd_slot_kernel_body(const nha_chunk_desc d,
                    tid, kBwThreads);
     load_tile_bf16(dob, ldv, (const bf16*)d.d_o + ((size_t)c.t0 * HQ + hq) * V, (int64_t)HQ * V, c.c0, 0, c.len, kChunk, V,
                    tid, kBwThreads);
+    if (L.hv_alias)                                    // tril(A) / tril(Av) of the previous head have been consumed
+      load_tile_bf16(Hv, ldhv, (const bf16*)d.hv_chunks + ((size_t)cg * H + h) * M * V, V, 0, 0, M, M, V, tid, kBwThreads);
     if (tid < kChunk) {
       const int pq = c.c0 + tid;
       const bool in = pq < c.len;

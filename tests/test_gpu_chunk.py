@@ -150,6 +150,55 @@ def test_varlen_with_per_sequence_windows():
     compare(o_g, g_g, o_o, g_o)
 
 
+# every tensor-memory backward instantiation (rows, columns and window-columns kernels): tile of 64 rows (one query
+# head per kv head) or 128 rows (two heads of a group), head dim 64 or 128; M = 64 selects those kernels
+UMMA_SHAPES = [(2, 2, 64), (4, 2, 64), (2, 2, 128), (8, 2, 128)]
+
+
+@pytest.mark.parametrize('no_umma', ['0', '1'])
+@pytest.mark.parametrize('HQ,H,K', UMMA_SHAPES)
+def test_backward_of_every_tile_shape(HQ, H, K, no_umma, monkeypatch):
+    """Gradients (all seven inputs, both initial states) for grouped query heads and head dim 128 with 64 slots: a
+    window wider than a chunk, a packing that holds a one-token sequence, initial states, gradients arriving on
+    lse_gsa and on the final states; with the tensor-memory kernels and with the general kernels forced."""
+    monkeypatch.setenv('NHA_B200_NO_UMMA', no_umma)
+    lens = [150, 1, 70]
+    cu = [0, 150, 151, 221]
+    T, N, M = cu[-1], len(lens), 64
+    d = gen.layer_inputs(7700 + HQ + K, 1, T, HQ, H, K, K, M, gate_div=2.0, val_scale=1.0)
+    x = flat_inputs(d, 1, T)
+    torch.manual_seed(HQ * K)
+    hk0 = torch.randn(N, H, K, M) * 0.5
+    hv0 = torch.randn(N, H, M, K) * 0.5
+    dlse = torch.randn(T, HQ) * 0.1
+    dhk, dhv = torch.randn(N, H, K, M) * 0.1, torch.randn(N, H, M, K) * 0.1
+    do = d['do'].reshape(T, HQ, K).float()
+    for wl, shift in ((100, 0), (95, 96)):
+        o_o, g_o = run_oracle(x, cu, K ** -0.5, wl, shift, hk0, hv0, do, dlse, dhk, dhv)
+        o_g, g_g = run_gpu(x, cu, max(lens), K ** -0.5, wl, shift, hk0, hv0, do, dlse, dhk, dhv)
+        compare(o_g, g_g, o_o, g_o)
+
+
+@pytest.mark.parametrize('HQ,H,K', [(2, 2, 64), (4, 2, 128)])
+def test_backward_with_strong_gates(HQ, H, K):
+    """Gates of about -3 nats per token: most chunks decay by more than the single-reference tensor-memory kernels
+    accept, so the forward flags them and the general kernels (one reference per 16 rows) produce their outputs AND
+    gradients; chunks of the same call that stay below the bound take the tensor-memory kernels."""
+    T, M = 260, 64
+    d = gen.layer_inputs(8800 + K, 1, T, HQ, H, K, K, M, gate_div=1.0, val_scale=1.0)
+    g = d['g'].float() * 3.0 - 1.0
+    g[:, 64:128] = d['g'][:, 64:128].float() / 8.0                  # one chunk with weak gates in the middle
+    d['g'] = g.to(torch.bfloat16)
+    d['s'] = (1 - d['g'].float().exp()).to(torch.bfloat16)
+    x = flat_inputs(d, 1, T)
+    do = d['do'].reshape(T, HQ, K).float()
+    o_o, g_o = run_oracle(x, [0, T], K ** -0.5, 63, 64, None, None, do, None)
+    o_g, g_g = run_gpu(x, [0, T], T, K ** -0.5, 63, 64, None, None, do, None)
+    for n in NAMES:
+        assert torch.isfinite(g_g[n].float()).all(), n
+    compare(o_g, g_g, o_o, g_o)
+
+
 def test_headline_shape_slice():
     """The fwd+bwd workload's shape (H=16, D=64, M=64, W=64, gates logsigmoid(N(0,1)), values N(0,1)/8)
     on a slice short enough for the oracle, both window conventions."""

@@ -73,24 +73,32 @@ def test_prefill_wide_window_and_head_dims(K, M, W, T, NG):
     assert_close(hv, ref_hv, TOL_OUT, 'hvt')
 
 
-def test_state_pass_segments_agree():
-    """Long sequences are cut into segments whose states are combined by a scan; any segment
-    length must give the same chunk-start and final states as a single march."""
+def test_chunk_start_states_against_the_oracle():
+    """The state pass alone: the chunk-start states it leaves for the output pass and the backward are the
+    oracle's slot memory at every 64th token (bf16 storage), and the final states its fp32 end value."""
     from nha_b200.chunk import chunk_forward
-    d = gen.prefill_inputs(4242, 2, 2, 2, 64, 64, 32, 16, 700, with_state=True)
+    B, T, H, K, M, W = 2, 300, 2, 64, 32, 16
+    d = gen.prefill_inputs(4242, B, H, 2, K, K, M, W, T, with_state=True)
     c = cuda(d)
-    B, T = 2, 700
     flat = lambda x: x.reshape(B * T, *x.shape[2:]).contiguous()
     cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device='cuda')
-    outs = []
-    for seg in (0, 1, 3, 4):
-        o, ls, lg, hk, hv, saved = chunk_forward(flat(c['q']), flat(c['rotary_q']), flat(c['k']), flat(c['rotary_k']),
-                                                 flat(c['v']), flat(c['s']), flat(c['g']), cu, T, d['scale'], 15, 16,
-                                                 c['hk0'], c['hv0'], True, seg_chunks=seg)
-        outs.append((o, hk, hv, saved['hk_chunks'][:22].float(), saved['hv_chunks'][:22].float()))
-    for other in outs[1:]:
-        for a, b, name in zip(outs[0], other, ('o', 'hkt', 'hvt', 'hk_chunks', 'hv_chunks')):
-            assert_close(b, a.cpu(), 5e-3, name)
+    o, ls, lg, hk, hv, saved = chunk_forward(flat(c['q']), flat(c['rotary_q']), flat(c['k']), flat(c['rotary_k']),
+                                             flat(c['v']), flat(c['s']), flat(c['g']), cu, T, d['scale'], W - 1, W,
+                                             c['hk0'], c['hv0'], True)
+    nc = (T + 63) // 64
+    for b in range(B):
+        hk_r, hv_r = d['hk0'][b].double(), d['hv0'][b].double()
+        for t in range(T + 1):
+            if t % 64 == 0 and t < T:
+                ci = b * nc + t // 64
+                assert_close(saved['hk_chunks'][ci], hk_r, TOL_OUT, f'hk_chunks[{b},{t // 64}]')
+                assert_close(saved['hv_chunks'][ci], hv_r, TOL_OUT, f'hv_chunks[{b},{t // 64}]')
+            j = t - W
+            if t < T and j >= 0:
+                hk_r, hv_r = orc.gsa_step(hk_r, hv_r, d['k'][b, j].double(), d['v'][b, j].double(),
+                                          d['s'][b, j].double(), d['g'][b, j].double())
+        assert_close(hk[b], hk_r, TOL_OUT, 'hkt')
+        assert_close(hv[b], hv_r, TOL_OUT, 'hvt')
 
 
 def test_strong_gates_stay_finite_and_exact():
