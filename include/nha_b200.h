@@ -39,6 +39,11 @@ enum {
 #define NHA_CHUNK 64         /* tokens per chunk of the chunked kernels */
 
 const char* nha_status_string(int status);
+/* Self test of the bounded waits.  Every wait of the tensor-core kernels on a completion barrier polls a limited
+   number of times, then sets a device error word and carries on to the kernel's end instead of spinning.  This
+   launches one small CTA that waits `polls` times (1 .. 65536) on a barrier that nothing ever completes and writes
+   1 into *err_word (device int32, zeroed by the caller) when the wait runs out.  No counterpart in the reference. */
+int nha_selftest_bounded_wait(int32_t* err_word, int polls, void* stream);
 /* last CUDA error text seen by this library on the calling thread ("" if none) */
 const char* nha_last_cuda_error(void);
 int nha_abi_version(void);

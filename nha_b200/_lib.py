@@ -41,6 +41,7 @@ SYMBOLS = {
     'nha_status_string': (C.c_char_p, [C.c_int]),
     'nha_last_cuda_error': (C.c_char_p, []),
     'nha_abi_version': (C.c_int, []),
+    'nha_selftest_bounded_wait': (C.c_int, [c_void_p, C.c_int, c_void_p]),
     'nha_decode_workspace_bytes': (C.c_int64, [C.c_int] * 5),
     'nha_decode_step': (C.c_int, [c_void_p] * 10 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, C.c_int,
                                                      c_void_p, c_void_p, c_void_p, C.c_int64] + [C.c_int] * 7
@@ -116,6 +117,28 @@ def check(status: int, what: str):
         msg = lib.nha_status_string(status).decode()
         detail = lib.nha_last_cuda_error().decode()
         raise NHALibraryError(f'{what}: {msg}' + (f' [{detail}]' if detail and status == 4 else ''))
+
+
+def check_device_words() -> bool:
+    """True when ``NHA_B200_CHECK=1``: the ops then read the kernels' device error word after every call (a bounded
+    wait that ran out leaves it non-zero) and raise.  Reading it synchronises the stream, so it is off by default."""
+    return os.environ.get('NHA_B200_CHECK') == '1'
+
+
+def check_chunk_device(lib, desc, stream, what: str):
+    if check_device_words():
+        e = lib.nha_chunk_device_error(desc, stream)
+        if e != 0:
+            raise NHALibraryError(f'{what}: device error word {e} (a bounded wait on a tensor-core completion ran out; '
+                                  f'the outputs of this call are invalid)')
+
+
+def check_decode_device(lib, ws, B, H, stream, what: str):
+    if ws is not None and check_device_words():
+        e = lib.nha_decode_device_error(ws.data_ptr(), B, H, stream)
+        if e != 0:
+            raise NHALibraryError(f'{what}: device error word {e} (a bounded wait in the decode kernel ran out; '
+                                  f'the outputs of this call are invalid)')
 
 
 def ptr(t):

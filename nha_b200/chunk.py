@@ -98,6 +98,7 @@ def chunk_forward(q_gsa, q_swa, k_gsa, k_swa, v, s, g, cu_seqlens, max_seqlen, s
         d = _fill_desc(geo, t, scale, wl_t, wl_all, sh_t, sh_all)
     with torch.cuda.device(dev):
         _lib.check(lib.nha_chunk_fwd(d, _stream(dev)), 'nha_chunk_fwd')
+        _lib.check_chunk_device(lib, d, _stream(dev), 'nha_chunk_fwd')
     saved = dict(geo=geo, wl=(wl_t, wl_all), sh=(sh_t, sh_all), hk_chunks=t['hk_chunks'], hv_chunks=t['hv_chunks'])
     return t['o'], t['lse_swa'], t['lse_gsa'], t.get('hkt'), t.get('hvt'), saved
 
@@ -127,6 +128,7 @@ def chunk_backward(q_gsa, q_swa, k_gsa, k_swa, v, s, g, cu_seqlens, scale, saved
     d = _fill_desc(geo, t, scale, wl_t, wl_all, sh_t, sh_all)
     with torch.cuda.device(dev):
         _lib.check(lib.nha_chunk_bwd(d, _stream(dev)), 'nha_chunk_bwd')
+        _lib.check_chunk_device(lib, d, _stream(dev), 'nha_chunk_bwd')
     return (t['dq_swa'], t['dk_swa'], t['dq_gsa'], t['dk_gsa'], t['dv'], t['ds'], t['dg'],
             t.get('dhk0'), t.get('dhv0'))
 

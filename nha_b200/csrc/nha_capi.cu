@@ -6,6 +6,7 @@
 #include <utility>
 
 #include "nha_common.cuh"
+#include "nha_umma.cuh"
 
 namespace nha {
 
@@ -37,7 +38,22 @@ cudaError_t set_max_smem(const void* func, int bytes) {
   return e;
 }
 
+// One CTA waits, with a poll limit, on an mbarrier phase that nobody completes: the wait must come back as "ran out"
+// and the kernel reports it in the error word, exactly as the tensor-core kernels report a completion that never came.
+__global__ void nha_selftest_wait_kernel(int* err, int limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) umma::mbar_init(&bar, 1);
+  __syncthreads();
+  if (!umma::mbar_wait_limit(&bar, 0, limit)) atomicExch(err, 1);
+}
+
 }  // namespace nha
+
+extern "C" int nha_selftest_bounded_wait(int* err_word, int polls, void* stream) {
+  if (!err_word || polls <= 0 || polls > (1 << 16)) return NHA_ERR_BAD_ARG;
+  nha::nha_selftest_wait_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(err_word, polls);
+  return nha::check_launch();
+}
 
 extern "C" const char* nha_status_string(int status) {
   switch (status) {

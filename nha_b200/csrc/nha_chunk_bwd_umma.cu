@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
     if (tid == 0) commit(mbar);                          \
-    if (!mbar_wait(mbar, phase)) failed = true;          \
+    if (!failed && !mbar_wait(mbar, phase)) failed = true;          \
     phase ^= 1;                                          \
     tc_fence_after();                                    \
   } while (0)
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     }                                                                                            \
   } while (0)
 
-  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+  for (int ht = 0; ht < NG / TH; ++ht) {
     const int hq0 = h * NG + ht * TH;
     const int hq = hq0 + th;
     const size_t rowq = (size_t)(t0 + pos) * HQ + hq;          // (token, query head) index of this thread's row
@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
     }
     // ---- window part: dz_win tile by tile, dq_swa --------------------------------------------------------------------
     const float nLjw = -Lj * kLog2e;
-    for (int jt = jt_lo; jt <= jt_hi && !failed; ++jt) {
+    for (int jt = jt_lo; jt <= jt_hi; ++jt) {
       const int wi = jt - jt_lo;
       const int set = L::kAlias ? (wi & 1) : 0;
       const uint32_t aW = smem_u32(sm + (set ? L::tW1 : L::tW0)), aWV = smem_u32(sm + (set ? L::tWV1 : L::tWV0));
@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(kRowsThreads, (D == 64 && R == 64) ? 2 : 1)
   }
 #undef NHA_LOAD_HEAD_TILE
 #undef NHA_ROW_SCALARS
-  if (failed && tid == 0) atomicExch(err, 1);
+  if (failed) atomicExch(err, 1);
   cp_wait_all();
   tc_fence_before();
   __syncthreads();
@@ -716,7 +716,7 @@ __global__ void __launch_bounds__(kCarryThreads) nha_bwd_gate_carry_kernel(const
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
     if (tid == 0) commit(mbar);                          \
-    if (!mbar_wait(mbar, phase)) failed = true;          \
+    if (!failed && !mbar_wait(mbar, phase)) failed = true;          \
     phase ^= 1;                                          \
     tc_fence_after();                                    \
   } while (0)
@@ -928,7 +928,7 @@ __global__ void __launch_bounds__(kColsThreads, (D == 64 && R == 64) ? 2 : 1)
   const uint32_t aDV = smem_u32(sm + L::tDV), aA = smem_u32(sm + L::bufA), aB = smem_u32(sm + L::bufB);
   float dsk[L::kDsInRegs ? 32 : 1];                   // this thread's half of the intra-chunk ds' accumulator
 
-  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+  for (int ht = 0; ht < NG / TH; ++ht) {
     if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
     cp_wait_all();
     NHA_SMEM_TO_MMA();
@@ -1110,7 +1110,7 @@ __global__ void __launch_bounds__(kColsThreads, (D == 64 && R == 64) ? 2 : 1)
       *reinterpret_cast<uint4*>((bf16*)d.dg + ((size_t)(t0 + kj) * H + h) * M + m0) = pack8(g8);
     }
   }
-  if (failed && tid == 0) atomicExch(err, 1);
+  if (failed) atomicExch(err, 1);
 }
 #undef NHA_MMA_WAIT
 #undef NHA_SMEM_TO_MMA

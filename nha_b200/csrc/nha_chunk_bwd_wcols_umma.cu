@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kWCThreads, D == 64 ? 2 : 1) nha_bwd_wcols_umm
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
     if (tid == 0) commit(mbar);                          \
-    if (!mbar_wait(mbar, phase)) failed = true;          \
+    if (!failed && !mbar_wait(mbar, phase)) failed = true;          \
     phase ^= 1;                                          \
     tc_fence_after();                                    \
   } while (0)
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kWCThreads, D == 64 ? 2 : 1) nha_bwd_wcols_umm
     tc_fence_after();                                    \
   } while (0)
 
-  for (int pr = 0; pr < npairs && !failed; ++pr) {
+  for (int pr = 0; pr < npairs; ++pr) {
     // ---- the two row blocks of this pair ---------------------------------------------------------------------
 #pragma unroll
     for (int t2 = 0; t2 < 2; ++t2) {
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kWCThreads, D == 64 ? 2 : 1) nha_bwd_wcols_umm
       }
     }
   }
-  if (failed && tid == 0) atomicExch(err, 1);
+  if (failed) atomicExch(err, 1);
   cp_wait_all();
   tc_fence_before();
   __syncthreads();

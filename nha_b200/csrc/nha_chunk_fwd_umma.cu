@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 #define NHA_MMA_WAIT()                                   \
   do {                                                   \
     if (tid == 0) commit(mbar);                          \
-    if (!mbar_wait(mbar, phase)) failed = true;          \
+    if (!failed && !mbar_wait(mbar, phase)) failed = true;          \
     phase ^= 1;                                          \
     tc_fence_after();                                    \
   } while (0)
@@ -410,13 +410,13 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 // bounded wait on one of the pipeline's mbarriers; bit_ of `phases` holds its parity
 #define NHA_WAIT_BAR(bar_, bit_)                                                                                    \
   do {                                                                                                              \
-    if (!mbar_wait((bar_), (phases >> (bit_)) & 1u)) failed = true;                                                 \
+    if (!failed && !mbar_wait((bar_), (phases >> (bit_)) & 1u)) failed = true;                                                 \
     phases ^= 1u << (bit_);                                                                                         \
     tc_fence_after();                                                                                               \
   } while (0)
   uint32_t phases = 0u;                               // parities: bits 0-1 loads, 2-3 S products, 4 P~ V product
 
-  for (int ht = 0; ht < NG / TH && !failed; ++ht) {
+  for (int ht = 0; ht < NG / TH; ++ht) {
     const int hq0 = h * NG + ht * TH;
     const int hq = hq0 + th;
     if (ht > 0) NHA_LOAD_HEAD_TILE(ht);
@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       // step index i counts from the oldest step (i = 0: loaded with the head tile, S formed in MMA group 1); step i uses
       // buffer set and accumulator i & 1.  The load of step i + 1 and the maximum of step i - 1 overlap S of step i.
       if (nsteps > 1) NHA_LOAD_STEP(1, nsteps - 2, nsteps - 2 == 0);
-      for (int i = 1; i < nsteps && !failed; ++i) {
+      for (int i = 1; i < nsteps; ++i) {
         const int b = i & 1, p = nsteps - 1 - i;
         NHA_WAIT_BAR(&bl[b], b);
         tc_fence_before();
@@ -500,7 +500,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
         if (rset) NHA_LOAD_STEP(0, 1, true); else NHA_LOAD_STEP(1, 1, true);
       }
     } else {
-      for (int p = nsteps - 2; p >= 0 && !failed; --p) {
+      for (int p = nsteps - 2; p >= 0; --p) {
         tc_fence_before();
         __syncthreads();
         load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
     if constexpr (L::kPipe) {
       // step j (j = 1: the first older one) uses buffer set and accumulator (rset + j) & 1; its load was issued one
       // step ahead, P~ V of step j runs while step j + 1 is prepared
-      for (int j = 1; j < nsteps && !failed; ++j) {
+      for (int j = 1; j < nsteps; ++j) {
         const int b = (rset + j) & 1;
         NHA_WAIT_BAR(&bl[b], b);
         tc_fence_before();
@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
       }
       if (nsteps > 1) NHA_WAIT_BAR(bpv, 4);
     } else {
-      for (int p = 1; p < nsteps && !failed; ++p) {
+      for (int p = 1; p < nsteps; ++p) {
         tc_fence_before();
         __syncthreads();
         load_sw<D, kUThreads>(sm + L::tW, L::kWTile, ksw, (int64_t)H * D, NHA_KBASE(p), 0, len, WK, 0, tid);
@@ -653,7 +653,7 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
 #undef NHA_XCHG
 #undef NHA_LOAD_HEAD_TILE
 #undef NHA_KBASE
-  if (failed && tid == 0) atomicExch(err, 1);
+  if (failed) atomicExch(err, 1);
   cp_wait_all();
   tc_fence_before();
   __syncthreads();

@@ -124,9 +124,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* mbar, int count) {
 
 // Bounded wait on an mbarrier phase; returns false when the limit is hit (the caller records an
 // error and leaves instead of spinning forever).
-__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* mbar, uint32_t parity, int limit) {
   uint32_t done = 0;
-  for (int it = 0; it < (1 << 22) && !done; ++it) {
+  for (int it = 0; it < limit && !done; ++it) {
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
@@ -135,6 +135,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) {
   }
   return done != 0;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) { return mbar_wait_limit(mbar, parity, 1 << 22); }
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

@@ -153,7 +153,8 @@ def fused_recurrent_nha_decode(
             cs_batch, cs_row, None, _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o), None,
             _lib.ptr(ws), 0 if ws is None else ws.numel(),
             B, HQ, H, K, V, M, W, float(scale), _stream(dev))
-    _lib.check(st, 'nha_decode_step')
+        _lib.check(st, 'nha_decode_step')
+        _lib.check_decode_device(lib, ws, B, H, _stream(dev), 'nha_decode_step')
     o = o.view(B, 1, HQ, V)
     if out_dtype != _BF16:
         o = o.to(out_dtype)

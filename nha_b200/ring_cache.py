@@ -98,17 +98,19 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
     cosc, sinc = cos.to(_BF16).contiguous(), sin.to(_BF16).contiguous()
     cs_batch = cosc.stride(0) if (cosc.dim() == 3 and cosc.shape[0] > 1) else 0
     o = torch.empty(B, 1, HQ, V, dtype=_BF16, device=dev)
-    ws = _decode_workspace(dev, B, HQ, H, V, W)
-    st = _stream(dev)
     sc = float(K ** -0.5 if scale is None else scale)
-    _lib.check(lib.nha_decode_step_ring(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
-                                        layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), layer.head.data_ptr(),
-                                        cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2), layer.hk.data_ptr(),
-                                        layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(), ws.numel(), B, HQ, H, K, V, M, W,
-                                        fill, sc, st), 'nha_decode_step_ring')
-    _lib.check(lib.nha_ring_append(layer.ring_k.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), kc.data_ptr(),
-                                   vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M, W, fill, st),
-               'nha_ring_append')
+    with torch.cuda.device(dev):                       # split count and launches follow the tensors' device
+        ws = _decode_workspace(dev, B, HQ, H, V, W)
+        st = _stream(dev)
+        _lib.check(lib.nha_decode_step_ring(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
+                                            layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), layer.head.data_ptr(),
+                                            cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2),
+                                            layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
+                                            ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st), 'nha_decode_step_ring')
+        _lib.check(lib.nha_ring_append(layer.ring_k.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
+                                       kc.data_ptr(), vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M,
+                                       W, fill, st), 'nha_ring_append')
+        _lib.check_decode_device(lib, ws, B, H, st, 'nha_decode_step_ring')
     layer.fill = min(fill + 1, W)
     return o
 
@@ -126,18 +128,21 @@ def _decode_ring_rot(q, k, v, g, layer: RingLayer, cos, sin, scale) -> torch.Ten
     cs_batch = cosq.stride(0) if cosq.shape[0] > 1 else 0
     sc = float(scale) if scale is not None else K ** -0.5
     o = torch.empty(B, 1, HQ, V, device=dev, dtype=_BF16)
-    ws = _decode_workspace(dev, B, HQ, H, V, W)
-    st = _stream(dev)
     fill = layer.fill
-    _lib.check(lib.nha_decode_step_ring_rot(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
-                                            layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
-                                            layer.head.data_ptr(), cosq.data_ptr(), sinq.data_ptr(), cs_batch,
-                                            layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
-                                            ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st), 'nha_decode_step_ring_rot')
-    _lib.check(lib.nha_ring_append_rot(layer.ring_k.data_ptr(), layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(),
-                                       layer.ring_g.data_ptr(), kc.data_ptr(), vc.data_ptr(), gc.data_ptr(),
-                                       cosq.data_ptr(), sinq.data_ptr(), cs_batch, layer.head.data_ptr(), B, H, K, V, M, W,
-                                       fill, st), 'nha_ring_append_rot')
+    with torch.cuda.device(dev):
+        ws = _decode_workspace(dev, B, HQ, H, V, W)
+        st = _stream(dev)
+        _lib.check(lib.nha_decode_step_ring_rot(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
+                                                layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
+                                                layer.head.data_ptr(), cosq.data_ptr(), sinq.data_ptr(), cs_batch,
+                                                layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
+                                                ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st),
+                   'nha_decode_step_ring_rot')
+        _lib.check(lib.nha_ring_append_rot(layer.ring_k.data_ptr(), layer.ring_kr.data_ptr(), layer.ring_v.data_ptr(),
+                                           layer.ring_g.data_ptr(), kc.data_ptr(), vc.data_ptr(), gc.data_ptr(),
+                                           cosq.data_ptr(), sinq.data_ptr(), cs_batch, layer.head.data_ptr(), B, H, K, V,
+                                           M, W, fill, st), 'nha_ring_append_rot')
+        _lib.check_decode_device(lib, ws, B, H, st, 'nha_decode_step_ring_rot')
     layer.fill = min(fill + 1, W)
     return o
 

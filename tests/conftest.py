@@ -8,6 +8,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# every op reads its kernels' device error word after each call and raises when a bounded wait ran out
+os.environ.setdefault('NHA_B200_CHECK', '1')
+
+
 def pytest_configure(config):
     config.addinivalue_line('markers', 'gpu: needs a CUDA device (B200); run with -m gpu')
 

@@ -42,3 +42,40 @@ def test_argument_validation_needs_no_gpu():
     assert st == 1
     d = _lib.ChunkDesc()
     assert lib.nha_chunk_fwd(ctypes.byref(d), None) == 1
+
+
+def test_operator_signatures_equal_the_reference():
+    """Parameter names, kinds and defaults of the four public ops against those of the reference's ops, read from its
+    sources by tests/golden/make_boundary.py (nha_fla/ops/nha/chunk.py:568-585, chunk_fused.py:291-303,
+    fused_recurrent.py:431-445, :588-598).  Callers pass keywords, so names and defaults are the contract."""
+    import inspect
+    import json
+    import nha_b200
+    want = json.load(open(os.path.join(ROOT, 'tests', 'golden', 'boundary.json')))['signatures']
+    assert set(want) == {'chunk_nha', 'fused_chunk_nha_prefill', 'fused_recurrent_nha', 'fused_recurrent_nha_decode'}
+    for name, params in want.items():
+        got = [[p.name, str(p.kind), None if p.default is inspect.Parameter.empty else repr(p.default)]
+               for p in inspect.signature(getattr(nha_b200, name)).parameters.values()]
+        assert got == params, f'{name}: {got} != {params}'
+
+
+def test_patch_reference_rebinds_every_import_site():
+    """With the reference package importable, patch_reference() must reach every module that bound an operator by
+    name, including the hybrid model file that imports fused_chunk_nha_prefill from its defining module."""
+    import pytest
+    nha_fla = pytest.importorskip('nha_fla', reason='reference package not importable here')
+    import nha_b200
+    done = nha_b200.patch_reference()
+    try:
+        import nha_fla.layers.nha as layer
+        import nha_fla.ops.nha as ops
+        assert layer.chunk_nha is nha_b200.chunk_nha and ops.chunk_nha is nha_b200.chunk_nha
+        assert ops.fused_recurrent_nha_decode is nha_b200.fused_recurrent_nha_decode
+        import nha_fla.models.qwen3_moe_nha.qwennha as moe
+        assert moe.fused_chunk_nha_prefill is nha_b200.fused_chunk_nha_prefill
+        assert moe.fused_recurrent_nha_decode is nha_b200.fused_recurrent_nha_decode
+        assert 'nha_fla.ops.nha.chunk_fused' in done['fused_chunk_nha_prefill']
+    finally:
+        nha_b200.unpatch_reference()
+    import nha_fla.ops.nha as ops
+    assert ops.chunk_nha is not nha_b200.chunk_nha
