@@ -16,9 +16,15 @@ One JSON line is printed by rank 0.  `value` times the C-ABI calls with inputs
 resident in HBM; `e2e` times the public `chunk_nha` call + autograd backward
 with pinned HOST buffers (host->device of the 8 inputs and device->host of the
 output, both LSEs and the 7 gradients inside the timed region).  `roofline`
-describes the kernel with the largest share of the step, timed on its own with
-CUDA events.  `cpu_baseline` is the CPU oracle (a port of the reference's naive
-PyTorch path) timed on this box's host cores on a bounded slice.
+is the whole step against the HBM roof: algorithmic bytes (every input read
+once per pass, every output written once, no intermediates: 49,344 B per token)
+divided by the step time; it names the kernel with the largest share, and
+`kernels` lists every stage timed on its own with CUDA events together with the
+bytes that stage moves by design (`stage_bytes`, hand-over scratch included).
+`cpu_baseline` is the CPU oracle (a port of the reference's naive PyTorch path)
+timed on this box's host cores on a bounded slice.  A timed region is repeated
+back to back until it lasts about half a second (`inner_repeats`), so that the
+sampled clocks describe it; `ms_per_step` stays the time of one step.
 
 `--impl reference` times that CPU oracle alone (rank 0 only), same metric/unit.
 """
@@ -26,6 +32,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -43,6 +50,10 @@ METRIC = 'NHA attn fwd+bwd tokens/s (bf16)'
 UNIT = 'tokens/s'
 CFG = dict(B=16, T=2048, H=16, D=64, M=64, W=64, shift=0)
 WORKLOAD = 'nha_attn_fwd_bwd B16 T2048 H16 D64 M64 W64 chunk64 bf16 (340M-layer shape)'
+CPU_SLICE_T = 512                             # tokens of the B=1 slice both CPU measurements run (cost grows with T)
+# dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one step per token, from the committed ncu captures
+# (None until a capture of the current kernels is committed)
+NCU_STEP_TRAFFIC_PER_TOKEN = None
 ALG_BYTES_PER_TOKEN = 16512 + 32832          # forward + backward, all 16 heads (each input read once per pass)
 NAMES = ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v', 's', 'g')
 
@@ -152,7 +163,7 @@ def run_reference(args):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    T = 256
+    T = CPU_SLICE_T
     for _ in range(min(args.warmup, 3)):
         cpu_oracle_tokens_per_s(T)
     t0 = time.perf_counter()
@@ -205,7 +216,7 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             assert st == 0
     for _ in range(3):
         step()
-    ms = timed(step, 10) / 10
+    ms = timed(step, 200) / 200
     per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
     gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
     # the same stack with the cache maintenance of one generated token inside the timed region: the reference's
@@ -261,10 +272,10 @@ def bench_decode(lib, dev, rank, world, timed, peak):
         step_shift()
         step_ring()
         step_ring_rot()
-    ms_shift = timed(step_shift, 5) / 5
-    ms_ring = timed(step_ring, 5) / 5
-    ms_rot = timed(step_ring_rot, 5) / 5
-    ms_rot_only = timed(lambda: step_ring_rot(False), 10) / 10
+    ms_shift = timed(step_shift, 10) / 10
+    ms_ring = timed(step_ring, 50) / 50
+    ms_rot = timed(step_ring_rot, 50) / 50
+    ms_rot_only = timed(lambda: step_ring_rot(False), 50) / 50
     with_cache = {'shifted_window_us_per_layer': 1e3 * ms_shift / LAYERS, 'ring_us_per_layer': 1e3 * ms_ring / LAYERS,
                   'ring_tokens_per_s': world * B / (ms_ring * 1e-3),
                   'ring_rotated_keys_us_per_layer': 1e3 * ms_rot / LAYERS,
@@ -300,7 +311,7 @@ def bench_prefill(dev, rank, world, dist, timed):
         return sequence_parallel_prefill(q, k, v, rq, rk, ss, gg, W)
     for _ in range(2):
         step()
-    ms = timed(step, 5) / 5
+    ms = timed(step, 30) / 30
     flops = T * 9699328.0
     return {'workload': f'prefill fwd B1 T131072 HQ32 H8 D128 M64 W512 bf16, sequence-parallel x{world}', 'ms': ms,
             'tokens_per_s': T / (ms * 1e-3), 'tflops': flops / (ms * 1e-3) / 1e12,
@@ -343,7 +354,7 @@ def bench_varlen(dev, rank, timed):
         o.backward(do)
     for _ in range(3):
         step()
-    ms = timed(step, 10) / 10
+    ms = timed(step, 100) / 100
     return {'workload': f'varlen fwd+bwd, {total} packed tokens in {len(lens)} sequences of 128-8192, windows 32-512, '
                         f'H16 D64 M64 bf16', 'ms': ms, 'tokens_per_s_per_gpu': total / (ms * 1e-3)}
 
@@ -558,8 +569,26 @@ def main():
     clk = ClockSampler(local).start()
     for _ in range(args.warmup):
         step()
-    ms = timed(step, args.steps)
+    # K steps are timed once to size the region, then K x inner_repeats steps back to back (about half a second, so
+    # that the clock samples fall inside it); `ms` is the time of K steps
+    ms_cal = timed(step, args.steps)
+    reps = max(1, int(math.ceil(500.0 / max(ms_cal, 1e-3))))
+    if dist is not None:
+        t_r = torch.tensor([reps], device=dev)
+        dist.all_reduce(t_r, op=dist.ReduceOp.MAX)
+        reps = int(t_r.item())
+    ms = timed(step, args.steps * reps) / reps
     value = world * tokens * args.steps / (ms * 1e-3)
+
+    def timed_avg(fn, min_ms=250.0):
+        """ms per call of `fn`, measured over a region of at least `min_ms`."""
+        cal = timed(fn, args.steps) / args.steps
+        n = max(args.steps, int(math.ceil(min_ms / max(cal, 1e-4))))
+        if dist is not None:
+            t_n = torch.tensor([n], device=dev)
+            dist.all_reduce(t_n, op=dist.ReduceOp.MAX)
+            n = int(t_n.item())
+        return timed(fn, n) / n
     # plan, state pass (2), output pass (2), backward: rows (2), window columns (1), slot (1), state-gradient terms +
     # scan + gate carry + columns + general inter-chunk kernel (5); the general kernels run gated on the chunk flags
     launches_per_step = 14
@@ -612,21 +641,21 @@ def main():
     for name, fn in calls.items():
         for _ in range(3):
             assert fn() == 0
-        kms = timed(fn, args.steps) / args.steps
-        kernels[name] = {'ms': kms, 'gbs': per_tok[name] * tokens / (kms * 1e-3) / 1e9}
+        kms = timed_avg(fn)
+        kernels[name] = {'ms': kms, 'stage_bytes': per_tok[name] * tokens, 'gbs': per_tok[name] * tokens / (kms * 1e-3) / 1e9}
     top = max(kernels, key=lambda k: kernels[k]['ms'])
+    stage_sum = sum(k['ms'] for k in kernels.values())
     peak, how = peaks()
-    # DRAM bytes per token of the stage's dominant kernel from the committed ncu capture (B=4 case; traffic grows
-    # in proportion to the tokens): profiles/bwd_rows_umma_B4_T2048.md 311.0 MB, profiles/fwd_umma_B4_T2048.md
-    # 161.4 MB, each for 8192 tokens
-    ncu_traffic_per_tok = {'bwd_rows': 311.0e6 / 8192, 'output_pass': 161.4e6 / 8192}
-    traffic = ncu_traffic_per_tok[top] * tokens if top in ncu_traffic_per_tok else None
-    roofline = {'bound': 'hbm', 'kernel': top, 'achieved': kernels[top]['gbs'], 'peak': peak, 'unit': 'GB/s',
-                'frac': kernels[top]['gbs'] / peak, 'traffic': traffic, 'peak_source': how,
-                'algorithmic_bytes_per_launch': per_tok[top] * tokens}
+    # DRAM bytes of one step: dram__bytes_read.sum + dram__bytes_write.sum of every kernel of a step, one ncu capture
+    # per kernel on the B=4 case (8192 tokens; traffic grows in proportion to the tokens), summed; the per-kernel
+    # figures are in profiles/step_traffic_chunk_fwd_bwd_B4_T2048.md
+    traffic = NCU_STEP_TRAFFIC_PER_TOKEN * tokens if NCU_STEP_TRAFFIC_PER_TOKEN else None
     step_gbs = ALG_BYTES_PER_TOKEN * tokens * args.steps / (ms * 1e-3) / 1e9
-    step_roofline = {'bound': 'hbm', 'achieved': step_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': step_gbs / peak,
-                     'algorithmic_bytes_per_step': ALG_BYTES_PER_TOKEN * tokens}
+    roofline = {'bound': 'hbm', 'achieved': step_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': step_gbs / peak,
+                'traffic': traffic, 'peak_source': how, 'algorithmic_bytes_per_step': ALG_BYTES_PER_TOKEN * tokens,
+                'scope': 'one forward + backward step (all kernels), algorithmic bytes = inputs once per pass + outputs once',
+                'kernel': top, 'kernel_share': kernels[top]['ms'] / stage_sum,
+                'stage_bytes_per_step': sum(k['stage_bytes'] for k in kernels.values())}
 
     # ---- end to end through the public API with host buffers -------------------------------------------
     # Every step copies its inputs from pinned host memory, runs chunk_nha forward + backward through the public
@@ -705,8 +734,8 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        Ts = 1024
-        tps, secs = cpu_oracle_tokens_per_s(Ts)
+        Ts = CPU_SLICE_T
+        tps, secs = cpu_oracle_tokens_per_s(Ts, repeats=3)
         cpu = {'value': tps, 'unit': UNIT, 'cores': os.cpu_count(), 'kind': 'port',
                'sample': f'B=1 T={Ts} slice of the workload, fp64 oracle fwd + autograd bwd, {secs:.1f} s'}
 
@@ -720,7 +749,7 @@ def main():
                        'tokens_per_gpu_per_step': tokens, 'window_left': W, 'gsa_kv_shift': shift,
                        'parallelism': f'batch-sharded x{world}, no collective',
                        'l2': 'inputs of one step (0.54 GB) exceed the 126 MB L2; no flush between steps'},
-            'roofline': roofline, 'step_roofline': step_roofline, 'kernels': kernels,
+            'inner_repeats': reps, 'roofline': roofline, 'kernels': kernels,
             'cpu_baseline': cpu, 'e2e': e2e, 'gpu_launches': launches_per_step * args.steps, 'extras': extras,
             'clocks': clk.summary(),
         }
