@@ -214,9 +214,16 @@ def bench_decode(lib, dev, rank, world, timed, peak):
                                      cos.stride(1), None, d['hk'].data_ptr(), d['hv'].data_ptr(), 0, d['o'].data_ptr(), None,
                                      ws.data_ptr(), ws.numel(), B, H * NG, H, K, K, M, W, K ** -0.5, stream)
             assert st == 0
-    for _ in range(3):
-        step()
-    ms = timed(step, 200) / 200
+    # programmatic dependent launch: 0 = plain launches, 1 = wait before the first read (the library's default),
+    # 2 = the layer's state and window are requested before the wait (valid for this stack: the kernel in front on
+    # the stream belongs to another layer and writes neither)
+    by_mode = {}
+    for mode in (0, 1, 2):
+        assert lib.nha_decode_set_pdl(mode) == 0
+        for _ in range(3):
+            step()
+        by_mode[mode] = timed(step, 200) / 200
+    ms = by_mode[2]
     per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
     gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
     # the same stack with the cache maintenance of one generated token inside the timed region: the reference's
@@ -286,6 +293,10 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     return {'workload': 'decode 48 layers x 32 seq/GPU HQ32 H4 D128 M64 W512 bf16, fp32 state', 'ms_per_token_step': ms,
             'with_cache_update': with_cache,
             'tokens_per_s': world * B / (ms * 1e-3), 'us_per_layer': 1e3 * ms / LAYERS,
+            'dependent_launch': {'us_per_layer_plain': 1e3 * by_mode[0] / LAYERS,
+                                 'us_per_layer_wait_first': 1e3 * by_mode[1] / LAYERS,
+                                 'us_per_layer_early_requests': 1e3 * by_mode[2] / LAYERS,
+                                 'headline_mode': 'early requests (mode 2)'},
             'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': peak, 'unit': 'GB/s', 'frac': gbs / peak,
                          'algorithmic_bytes_per_launch': per_seq_layer * B}, 'gpu_launches_per_step': LAYERS}
 

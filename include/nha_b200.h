@@ -85,6 +85,18 @@ int nha_decode_step(const void* q, const void* sq, const void* k, const void* v,
                     int64_t cs_row, const void* win_logits, float* hk, float* hv, int zero_state, void* o,
                     float* win_prob, void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V,
                     int M, int W, float scale, void* stream);
+/* Programmatic dependent launch of the streaming decode kernel (the reference chains its two decode kernels the same
+ * way and switches it with the environment variable NHA_PDL, nha_fla/ops/nha/fused_recurrent.py:13-44, 560-582).
+ *   0  plain launches.
+ *   1  (default; NHA_PDL unset or "1") the kernel may be scheduled while the kernel in front of it on the stream is
+ *      still draining and waits for that kernel before its first global read: always safe, hides the launch gap.
+ *   2  as 1, and the slot memory (hk, hv) and the window (sw_k / sw_v, or the rings and head) of the call are
+ *      requested BEFORE the wait; q, the popped or new token and the gates are read after it.  Only for callers who
+ *      know that the kernel immediately in front on the stream writes neither this call's slot memory nor its window
+ *      (a stack of layers with one cache per layer: the kernel in front works on another layer, or is a projection).
+ * The mode is process-wide; NHA_PDL ("0", "1", "2") gives the initial value. */
+int nha_decode_set_pdl(int mode);
+int nha_decode_get_pdl(void);
 /* reads the workspace's device error word (synchronises the stream): non-zero when a bounded wait
    inside the streaming decode kernel ran out.  No counterpart in the reference. */
 int nha_decode_device_error(const void* workspace, int B, int H, void* stream);

@@ -47,6 +47,8 @@ SYMBOLS = {
                                                      c_void_p, c_void_p, c_void_p, C.c_int64] + [C.c_int] * 7
                         + [C.c_float, c_void_p]),
     'nha_decode_device_error': (C.c_int, [c_void_p, C.c_int, C.c_int, c_void_p]),
+    'nha_decode_set_pdl': (C.c_int, [C.c_int]),
+    'nha_decode_get_pdl': (C.c_int, []),
     'nha_decode_step_ring': (C.c_int, [c_void_p] * 9 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                        C.c_int64] + [C.c_int] * 8 + [C.c_float, c_void_p]),
     'nha_ring_append': (C.c_int, [c_void_p] * 7 + [C.c_int] * 7 + [c_void_p]),

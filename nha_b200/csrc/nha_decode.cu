@@ -459,6 +459,8 @@ static int decode_splits(int W, bool logits_mode) {
 }
 
 int decode_stream_splits(int B, int H, int W, int M);
+int decode_pdl_mode();
+void decode_set_pdl_mode(int m);
 bool decode_stream_supported(int K, int V, int M, int W, int NG, bool logits_mode);
 int decode_stream_try(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
                       const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
@@ -484,6 +486,13 @@ extern "C" int64_t nha_decode_workspace_bytes(int B, int HQ, int H, int V, int W
   const int64_t NG = HQ / H;
   return (int64_t)B * H * spl * NG * (V + 2) * 4 + ((int64_t)B * H + 1) * 4 + 1024;
 }
+
+extern "C" int nha_decode_set_pdl(int mode) {
+  if (mode < 0 || mode > 2) return NHA_ERR_BAD_ARG;
+  decode_set_pdl_mode(mode);
+  return NHA_OK;
+}
+extern "C" int nha_decode_get_pdl(void) { return decode_pdl_mode(); }
 
 extern "C" int nha_decode_device_error(const void* workspace, int B, int H, void* stream) {
   if (!workspace || B <= 0 || H <= 0) return 0;

@@ -28,6 +28,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "nha_common.cuh"
 #include "nha_umma.cuh"
 
@@ -61,6 +63,10 @@ struct DecodeStreamArgs {
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
+  // programmatic dependent launch: 0 = plain launch; 1 = the grid may be scheduled before the kernel in front of it on
+  // the stream has finished and waits for it before its first global read; 2 = as 1, but the slot memory and the
+  // window of this call are requested BEFORE that wait (the caller asserts that the kernel in front writes neither)
+  int pdl;
   float scale;
   int off_ring, off_hv, off_S, off_red, off_q, off_sqA, off_oks, off_eg, off_sv, off_kpop, off_vpop, off_ml, off_bar;
 };
@@ -107,6 +113,11 @@ __device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
   asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
   return v;
 }
+
+// programmatic dependent launch: wait until the grids this one depends on have completed and their writes are
+// visible; let the grid behind this one on the stream be scheduled
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // c[16x8] += a[16x16] b[16x8]
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -155,6 +166,10 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   const int nloads = 2 * nst;                                      // key stages, then value stages
   const bool isring = a.head != nullptr;
   const int WR = a.WR;
+  if (a.pdl == 1) {                                                // before the first global read
+    grid_dep_wait();
+    grid_dep_launch();
+  }
   const int hd = isring ? (a.nopop ? -1 : a.head[b]) : 0;              // physical row of the oldest ring entry
   // the token that enters the slot memory: separate small tensors, or the oldest ring entry
   const bool prerot = a.ring_kraw != nullptr;
@@ -212,6 +227,40 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   // ---- the small inputs first, into registers, so that they are not queued behind the window in the memory system;
   //      then everything that fits goes in flight: my columns of hk, the first ring loads, my rows of hv.
   //      Disjoint groups of threads fetch the four small inputs, so that their loads overlap. ----------------------
+  // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = kRowsPer warp + j.  The first
+  // block of columns (all of them unless the split owns more than 32 slots) is fetched in the prologue.
+  constexpr int kRowsPer = K / kStrWarps;
+  float hreg[kRowsPer];
+  const int ncb = (nslots + 31) / 32;
+#define NHA_LOAD_HK_FIRST()                                                                         \
+  do {                                                                                              \
+    if (!a.zero_state && nslots > 0) {                                                              \
+      _Pragma("unroll") for (int j = 0; j < kRowsPer; ++j)                                          \
+        hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane] : 0.f; \
+    }                                                                                               \
+  } while (0)
+#define NHA_LOAD_HV_ROWS()                                                                          \
+  do {                                                                                              \
+    if (nslots > 0 && !a.zero_state && tid == 0) {                                                  \
+      mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);                                      \
+      bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);  \
+    }                                                                                               \
+  } while (0)
+  // Dependent launch with early requests (pdl == 2): the state and the window of this call do not depend on the
+  // kernel in front, so they go in flight before the wait.  In ring mode the newest window entry is the token of
+  // this step (a.k / a.v, written by the caller's projections): the ring loads from the first one that holds it on
+  // are issued after the wait, in the same order as always (groups complete in issue order).
+  const int ninit = min(nloads, kStrSlots);
+  int npre = 0;
+  if (a.pdl == 2) {
+    npre = ninit;
+    if (isring && w0 + nkeys == W && nst > 0) npre = min(npre, nst - 1);
+    NHA_LOAD_HK_FIRST();
+    for (int j = 0; j < npre; ++j) NHA_ISSUE_LOAD(j);
+    NHA_LOAD_HV_ROWS();
+    grid_dep_wait();
+    grid_dep_launch();
+  }
   constexpr int c8h = K >> 4;
   const int qi = tid - 128, q_r = qi / c8h, q_c = qi - q_r * c8h;
   const bool qthread = tid >= 128 && qi < 16 * c8h, qlive = qthread && q_r < NG;
@@ -234,16 +283,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
       rq_c2 = __ldg(reinterpret_cast<const uint4*>(srow + 8 * (q_c + c8h)));
     }
   }
-  // my columns of hk: thread -> column m = lane (+32 per block of columns), rows k = kRowsPer warp + j.  The first
-  // block of columns (all of them unless the split owns more than 32 slots) is fetched now.
-  constexpr int kRowsPer = K / kStrWarps;
-  float hreg[kRowsPer];
-  const int ncb = (nslots + 31) / 32;
-  if (!a.zero_state && nslots > 0) {
-#pragma unroll
-    for (int j = 0; j < kRowsPer; ++j)
-      hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane] : 0.f;
-  }
+  if (a.pdl != 2) NHA_LOAD_HK_FIRST();
   // the gates (threads 0..63) and the popped token (one warp each for k and v)
   bf16 gb[2], sb[2];
   gb[0] = gb[1] = sb[0] = sb[1] = f2bf(0.f);
@@ -262,11 +302,10 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   } else if (tid < 128) {
     if (tid - 96 < (V >> 3) && !a.nopop) rpop = __ldg(reinterpret_cast<const uint4*>(vpop_g + 8 * (tid - 96)));
   }
-  for (int j = 0; j < min(nloads, kStrSlots); ++j) NHA_ISSUE_LOAD(j);
-  if (nslots > 0 && !a.zero_state && tid == 0) {
-    mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);
-    bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);
-  }
+  for (int j = npre; j < ninit; ++j) NHA_ISSUE_LOAD(j);
+  if (a.pdl != 2) NHA_LOAD_HV_ROWS();
+#undef NHA_LOAD_HK_FIRST
+#undef NHA_LOAD_HV_ROWS
   // registers -> shared memory
   if (tid < 64) {
 #pragma unroll
@@ -757,6 +796,22 @@ int decode_stream_splits(int B, int H, int W, int M) {
   return spl;
 }
 
+// Mode of the programmatic dependent launch of the streaming kernel (see DecodeStreamArgs::pdl): set by
+// nha_decode_set_pdl(), else taken once from the environment variable NHA_PDL (the reference's switch of the same
+// name, nha_fla/ops/nha/fused_recurrent.py:32-34: "0" turns it off), default 1.
+static std::atomic<int> g_pdl_mode{-1};
+int decode_pdl_mode() {
+  int m = g_pdl_mode.load(std::memory_order_relaxed);
+  if (m < 0) {
+    const char* e = getenv("NHA_PDL");
+    m = 1;
+    if (e && e[0] >= '0' && e[0] <= '2' && e[1] == 0) m = e[0] - '0';
+    g_pdl_mode.store(m, std::memory_order_relaxed);
+  }
+  return m;
+}
+void decode_set_pdl_mode(int m) { g_pdl_mode.store(m, std::memory_order_relaxed); }
+
 bool decode_stream_supported(int K, int V, int M, int W, int NG, bool logits_mode) {
   return !logits_mode && K == V && (K == 64 || K == 128) && M % 4 == 0 && M <= 128 && NG <= 16 && W >= 1;
 }
@@ -784,13 +839,16 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = a.cluster ? a.SPLITS : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  a.pdl = decode_pdl_mode();
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = a.pdl ? 2 : 1;
   void* args[1] = {(void*)&a};
   e = cudaLaunchKernelExC(&cfg, fn, args);
   if (e != cudaSuccess && a.cluster) {

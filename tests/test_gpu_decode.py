@@ -178,3 +178,57 @@ def test_decode_cluster_merge_matches_workspace_merge(B, monkeypatch):
     monkeypatch.setenv('NHA_B200_DECODE_NO_CLUSTER', '0')
     assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][2], res[1][2])
     assert (res[0][0] - res[1][0]).abs().max() < 1e-2
+
+
+@pytest.fixture
+def pdl_mode():
+    """Sets the dependent-launch mode of the streaming decode kernel for a test and restores the default."""
+    from nha_b200 import _lib
+    lib = _lib.load()
+    before = lib.nha_decode_get_pdl()
+    yield lambda m: _lib.check(lib.nha_decode_set_pdl(m), 'nha_decode_set_pdl')
+    lib.nha_decode_set_pdl(before)
+
+
+@pytest.mark.parametrize('B', [3, 32])
+def test_dependent_launch_modes_agree_on_a_stack_of_layers(B, pdl_mode):
+    """Six layers with their own slot memory and window, decoded back to back for two tokens: plain launches (0),
+    dependent launches that wait before their first read (1), and dependent launches that request the layer's state
+    and window before the wait (2; allowed here because the kernel in front belongs to another layer).  Layer 0 of
+    the first token is checked against the oracle; all modes must give the same bits."""
+    from nha_b200 import NHARingCache, fused_recurrent_nha_decode
+    H, NG, K, M, W, L, STEPS = 4, 8, 128, 64, 512, 6, 2
+    layers = [gen.decode_inputs(300 + i, B, H, NG, K, K, M, W) for i in range(L)]
+    cos, sin = gen.rope_tables(W, K, first_pos=32768 - W + 1)
+    d0 = layers[0]
+    ref = orc.decode_step(d0['q'], d0['k'], d0['v'], d0['g'], d0['sw_k_raw'], d0['vw'], d0['scale'], cos=cos, sin=sin,
+                          hk0=d0['hk0'], hv0=d0['hv0'])
+    cl = [cuda(d) for d in layers]
+    cosd, sind = cos.cuda(), sin.cuda()
+    results = {}
+    for mode in (0, 1, 2):
+        pdl_mode(mode)
+        st = [(c['hk0'].clone(), c['hv0'].clone()) for c in cl]
+        outs = []
+        for _ in range(STEPS):
+            for i, c in enumerate(cl):
+                o, st[i] = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'],
+                                                      sw_v=c['vw'], cos=cosd, sin=sind, initial_state=st[i],
+                                                      output_final_state=True)
+                outs.append(o)
+        # the same stack on ring caches (decode + append per layer)
+        cache = NHARingCache()
+        for i, c in enumerate(cl):
+            cache.init_layer(i, c['sw_k_raw'], c['vw'], (c['g'].expand(B, W, H, M) * 0.5).contiguous(), W,
+                             (c['hk0'], c['hv0']))
+        routs = []
+        for _ in range(STEPS + 1):
+            for i, c in enumerate(cl):
+                routs.append(cache.decode(i, c['q'], c['k'], c['v'], c['g'], cosd, sind))
+        torch.cuda.synchronize()
+        results[mode] = (outs, [x for pair in st for x in pair], routs, [cache[i].hk for i in range(L)])
+    assert_close(results[0][0][0], ref[0], TOL_OUT, 'o of layer 0 (plain launches)')
+    for mode in (1, 2):
+        for part in range(4):
+            for a, b in zip(results[0][part], results[mode][part]):
+                assert torch.equal(a, b), f'mode {mode} differs from plain launches'
