@@ -1,0 +1,627 @@
+// Output pass of the chunked NHA forward for head dim 128 with four (or a multiple of four) query heads per kv head,
+// as a warp-specialised pipeline on the sm_100a tensor-core path.
+//
+// One CTA = one (64-token chunk, kv head, group of four query heads) = two 128-row tiles (two heads x 64 tokens each)
+// that share the chunk's slot operands (k', v', Hk, Hv, s' .* b) and every window key / value tile.  320 threads:
+//   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: ONE thread per row (tcgen05.ld gives it its row of the
+//                    accumulator), element-wise work only;
+//   warp 8           loads: all operand tiles by TMA (cp.async.bulk.tensor on maps of this GPU's own tensors, no
+//                    multicast) into 128-byte-swizzled tiles, bytes counted on mbarriers; the slot operands and the
+//                    window tiles stream through one ring of four 16 KB slots; a tile that sticks out of its
+//                    sequence is written by the warp itself with zero fill, so that no row of a neighbouring sequence
+//                    ever enters a product;
+//   warp 9           one thread issues every tcgen05.mma and commits completions to mbarriers.
+// The two tiles run the same chain half a step apart, so the tensor pipe works on one while the other's softmax
+// group does its element-wise step:
+//     G1  A = q k'^T, QH = q Hk                group: tril(A) -> bf16 operand
+//     G2  X = tril(A) (s' .* b)                group: slot logits ok = scale a .* (e^R .* QH + X), p~ = exp(ok - max),
+//                                                     operands p~ a e^R and p~ a
+//     G3  O = (p~ a e^R) Hv, Bv = (p~ a)(s' .* b)^T      group: tril(Bv) -> bf16 operand
+//     G4  O += tril(Bv) v'
+//     window steps, newest key tile first (64 keys each):   S_j = q_swa K_j^T (two accumulators, S_{j+2} is issued as
+//         soon as the group has read S_j);   group: P~_j = exp(scale S_j - m) -> bf16 operand;   O += P~_j V_j
+// ONE softmax over the slot logits and all window logits, in a single sweep: the running reference m of a row starts
+// as its slot maximum and is only raised when a window logit exceeds it by more than 8 ln 2 (probabilities then stay
+// below 256, exact in the fp32 accumulator); raising it rescales the row of O in tensor memory (tcgen05.ld / st by the
+// row's thread, after the products in flight on O have completed).  Decay factorisation, flags for chunks that decay
+// too fast for one reference per chunk, and the general kernel that takes those: as in nha_chunk_fwd_umma.cu.
+//
+// Replaces chunk_nha_fused_o_kernel (nha_fla/ops/nha/chunk_fused.py:117-283) at the long-context shape.
+#include <cuda.h>
+#include <string.h>
+
+#include "nha_common.cuh"
+#include "nha_tma.cuh"
+#include "nha_umma.cuh"
+
+namespace nha {
+
+using namespace umma;
+
+namespace pipe {
+constexpr int D = 128, M = 64;
+constexpr int kThreads = 320;
+constexpr int kQTile = 128 * 128;                 // one 64-wide k tile of a 128-row A operand
+constexpr int kSlot = 16384, kNSlot = 4;
+constexpr int oQG = 0;                            // q_gsa [2 tiles][2 k tiles][128][64]; later tril / p~ operands, P~
+constexpr int oQS = oQG + 4 * kQTile;             // q_swa, same shape
+constexpr int oRing = oQS + 4 * kQTile;
+constexpr int oSB = oRing + kNSlot * kSlot;       // s' .* b [64][64]
+constexpr int oA = oSB + 8192;                    // fp32 [64][65]: cumulative gates, then a = exp(G - R)
+constexpr int oER = oA + 64 * 65 * 4;             // fp32 [64] exp(R)
+constexpr int oBar = oER + 256;
+constexpr int total = oBar + 512 + 1024;          // + slack for the 1024-byte alignment of the base
+static_assert(total <= 227 * 1024, "shared memory of the pipelined output pass");
+// mbarriers
+constexpr int bQ = 0, bFull = 2, bEmpty = 6, bG = 10, bW = 12, bS = 14, bP = 18, bPV = 22, nBar = 26;
+constexpr int kPoll = 1 << 20;
+constexpr float kDecayLimit = 140.0f;
+constexpr float kRaise = 5.545177f;               // 8 ln 2
+}  // namespace pipe
+
+struct PipeMaps {
+  CUtensorMap qg, qs, kg, ks, v, hk, hv;
+};
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* in) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,"
+      "%31,%32};" ::"r"(taddr),
+      "r"(__float_as_uint(in[0])), "r"(__float_as_uint(in[1])), "r"(__float_as_uint(in[2])), "r"(__float_as_uint(in[3])),
+      "r"(__float_as_uint(in[4])), "r"(__float_as_uint(in[5])), "r"(__float_as_uint(in[6])), "r"(__float_as_uint(in[7])),
+      "r"(__float_as_uint(in[8])), "r"(__float_as_uint(in[9])), "r"(__float_as_uint(in[10])), "r"(__float_as_uint(in[11])),
+      "r"(__float_as_uint(in[12])), "r"(__float_as_uint(in[13])), "r"(__float_as_uint(in[14])), "r"(__float_as_uint(in[15])),
+      "r"(__float_as_uint(in[16])), "r"(__float_as_uint(in[17])), "r"(__float_as_uint(in[18])), "r"(__float_as_uint(in[19])),
+      "r"(__float_as_uint(in[20])), "r"(__float_as_uint(in[21])), "r"(__float_as_uint(in[22])), "r"(__float_as_uint(in[23])),
+      "r"(__float_as_uint(in[24])), "r"(__float_as_uint(in[25])), "r"(__float_as_uint(in[26])), "r"(__float_as_uint(in[27])),
+      "r"(__float_as_uint(in[28])), "r"(__float_as_uint(in[29])), "r"(__float_as_uint(in[30])), "r"(__float_as_uint(in[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(pipe::kThreads, 1)
+    nha_fwd_pipe_kernel(const nha_chunk_desc d, int* __restrict__ flags, int* __restrict__ err,
+                        const __grid_constant__ PipeMaps maps) {
+  using namespace pipe;
+  const int H = d.H, HQ = d.HQ, NG = HQ / H;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const ChunkRec rc = chunk_rec(d, cg);
+  if (rc.n < 0) return;
+  const int n = rc.n, ci = rc.ci, t0 = rc.t0, len = rc.len, c0 = ci * kChunk;
+  const int wl = seq_window(d, n), shift = seq_shift(d, n);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hq0 = h * NG + 4 * blockIdx.z;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* As = (float*)(sm + oA);
+  float* ER = (float*)(sm + oER);
+  uint64_t* bar = (uint64_t*)(sm + oBar);
+  uint32_t* tslot = (uint32_t*)(bar + nBar);
+  __shared__ int s_abort;
+
+  // window key tiles, newest first: step j covers the keys [64 (ci - j), 64 (ci - j) + 64)
+  const int jt_lo = wl < 0 ? 0 : max(0, c0 - wl) / kChunk;
+  const int nst = ci - jt_lo + 1;
+  const int nloads = 4 + 2 * nst;
+
+  if (tid == 0) {
+    s_abort = *(volatile int*)err;                    // an earlier CTA of this launch gave up on a wait: do not start
+    for (int i = 0; i < nBar; ++i) {
+      const bool many = (i >= bW && i < bW + 2) || (i >= bP && i < bP + 4);
+      mbar_init(&bar[i], many ? 128 : 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(tslot, 512);
+  // gates and write weights of the chunk's shifted rows through registers (threads 0..255: two 16-byte pieces each)
+  const int lo = 0, hi = len - shift;
+  uint4 sreg[2], greg[2];
+  if (tid < 256) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int i = tid + 256 * j;
+      const int r = i >> 3, c8 = i & 7;
+      const int src = c0 + r - shift;
+      sreg[j] = make_uint4(0u, 0u, 0u, 0u);
+      greg[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (src >= lo && src < hi) {
+        greg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+        sreg[j] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + src) * H + h) * M + 8 * c8);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = *tslot;
+  if (s_abort) {
+    if (warp == 0) tmem_dealloc(tbase, 512);
+    return;
+  }
+  bool failed = false;
+#define NHA_WAIT(idx_, par_)                                                       \
+  do {                                                                             \
+    if (!failed && !mbar_wait_limit(&bar[idx_], (uint32_t)(par_), kPoll)) failed = true; \
+  } while (0)
+
+  // ---- loads (warp 8) ---------------------------------------------------------------------------------------------
+  // load 0: k' (shifted un-rotated keys), 1: Hk, 2: Hv, 3: v' (shifted values), 4 + 2 j: window keys of step j,
+  // 5 + 2 j: window values of step j; load i goes to ring slot i % 4.
+  auto ragged_fill = [&](unsigned char* dst, const bf16* base, int r0, int rlo, int rhi) {
+    // [64 rows][128 columns] as two swizzled 64-column tiles; rows outside [rlo, rhi) become zeros
+#pragma unroll 1
+    for (int it = 0; it < 32; it += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = lane + 32 * (it + u);
+        const int r = i >> 4, c = i & 15;
+        const int gr = r0 + r;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (gr >= rlo && gr < rhi) v[u] = __ldg(reinterpret_cast<const uint4*>(base + (size_t)gr * H * D + 8 * c));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = lane + 32 * (it + u);
+        const int r = i >> 4, c = i & 15;
+        *reinterpret_cast<uint4*>(dst + (c >> 3) * 8192 + sw_off(r, c & 7)) = v[u];
+      }
+    }
+    fence_async_smem();
+    __syncwarp();
+  };
+  auto issue_load = [&](int idx) {
+    unsigned char* dst = sm + oRing + (idx & 3) * kSlot;
+    uint64_t* fb = &bar[bFull + (idx & 3)];
+    if (idx == 1) {
+      if (lane == 0) {
+        mbar_expect_tx(fb, 16384);
+        tma_load_2d(dst, &maps.hk, 0, (cg * H + h) * D, fb);
+      }
+      return;
+    }
+    if (idx == 2) {
+      if (lane == 0) {
+        mbar_expect_tx(fb, 16384);
+        tma_load_2d(dst, &maps.hv, 0, (cg * H + h) * M, fb);
+        tma_load_2d(dst + 8192, &maps.hv, 64, (cg * H + h) * M, fb);
+      }
+      return;
+    }
+    const CUtensorMap* mp;
+    const bf16* base;
+    int r0, rlo = 0, rhi;
+    if (idx == 0) { mp = &maps.kg; base = (const bf16*)d.k_gsa; r0 = c0 - shift; rhi = hi; }
+    else if (idx == 3) { mp = &maps.v; base = (const bf16*)d.v; r0 = c0 - shift; rhi = hi; }
+    else {
+      const int j = (idx - 4) >> 1;
+      r0 = (ci - j) * kChunk;
+      rhi = len;
+      if ((idx & 1) == 0) { mp = &maps.ks; base = (const bf16*)d.k_swa; }
+      else { mp = &maps.v; base = (const bf16*)d.v; }
+    }
+    if (r0 >= rlo && r0 + kChunk <= rhi) {
+      if (lane == 0) {
+        mbar_expect_tx(fb, 16384);
+        tma_load_3d(dst, mp, 0, h, t0 + r0, fb);
+        tma_load_3d(dst + 8192, mp, 64, h, t0 + r0, fb);
+      }
+    } else {
+      ragged_fill(dst, base + ((size_t)t0 * H + h) * D, r0, rlo, rhi);
+      if (lane == 0) mbar_arrive(fb);
+    }
+  };
+  if (warp == 8) {
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        mbar_expect_tx(&bar[bQ + t], 65536);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int kt = 0; kt < 2; ++kt) {
+            tma_load_3d(sm + oQG + (2 * t + kt) * kQTile + hh * 8192, &maps.qg, 64 * kt, hq0 + 2 * t + hh, t0 + c0, &bar[bQ + t]);
+            tma_load_3d(sm + oQS + (2 * t + kt) * kQTile + hh * 8192, &maps.qs, 64 * kt, hq0 + 2 * t + hh, t0 + c0, &bar[bQ + t]);
+          }
+      }
+    }
+    for (int idx = 0; idx < 4; ++idx) issue_load(idx);
+  }
+
+  // ---- decay tables (threads 0..255), as in nha_chunk_fwd_umma.cu -------------------------------------------------
+  if (tid < 256) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int i = tid + 256 * j;
+      const int r = i >> 3, c8 = i & 7;
+      float gv[8];
+      unpack8(greg[j], gv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
+    }
+  }
+  __syncthreads();
+  {
+    // inclusive scan along the rows: four threads per column (16 rows each), then the totals of the earlier segments
+    const int m = tid & 63, seg = tid >> 6;
+    if (tid < 256) {
+      float run = 0.f;
+#pragma unroll
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
+        run += As[r * 65 + m];
+        As[r * 65 + m] = run;
+      }
+    }
+    __syncthreads();
+    float add = 0.f;
+    if (tid < 256)
+      for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * 65 + m];
+    __syncthreads();
+    if (tid < 256 && seg > 0) {
+#pragma unroll
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * 65 + m] += add;
+    }
+    __syncthreads();
+  }
+  const bool mine_unsafe = tid < 64 && fabsf(As[63 * 65 + tid]) > kDecayLimit;
+  const int unsafe = __syncthreads_or(mine_unsafe ? 1 : 0);
+  if (tid == 0 && blockIdx.z == 0) flags[(size_t)cg * H + h] = unsafe;
+  if (unsafe) {
+    // the general kernel computes this chunk; the loads already in flight must land before the CTA may leave
+    if (warp == 8 && lane == 0) {
+      NHA_WAIT(bQ, 0);
+      NHA_WAIT(bQ + 1, 0);
+      for (int i = 0; i < 4; ++i) NHA_WAIT(bFull + i, 0);
+      if (failed) atomicExch(err, 1);
+    }
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tbase, 512);
+    return;
+  }
+  {
+    float rref[8];
+    const int c8 = tid & 7;
+    if (tid < 256) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) rref[e] = 0.5f * As[63 * 65 + 8 * c8 + e];
+    }
+    __syncthreads();                                  // every thread holds its references before the table changes
+    if (tid < 8) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ER[8 * tid + e] = __expf(rref[e]);
+    }
+    if (tid < 256) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int i = tid + 256 * j;
+        const int r = i >> 3;
+        float sv[8], out[8];
+        unpack8(sreg[j], sv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float x = As[r * 65 + 8 * c8 + e] - rref[e];
+          As[r * 65 + 8 * c8 + e] = __expf(x);
+          out[e] = sv[e] * __expf(-x);
+        }
+        *reinterpret_cast<uint4*>(sm + oSB + sw_off(r, c8)) = pack8(out);
+      }
+    }
+    fence_async_smem();
+    __syncthreads();
+  }
+
+  const uint32_t aSB = smem_u32(sm + oSB);
+  if (warp == 8) {
+    // ================= load warp: the rest of the ring ============================================================
+    for (int idx = 4; idx < nloads; ++idx) {
+      NHA_WAIT(bEmpty + (idx & 3), ((idx >> 2) - 1) & 1);
+      issue_load(idx);
+    }
+  } else if (warp == 9) {
+    // ================= MMA warp: one thread issues everything =====================================================
+    if (lane == 0) {
+      auto ring = [&](int idx) { return smem_u32(sm + oRing + (idx & 3) * kSlot); };
+      auto wait_full = [&](int idx) {
+        NHA_WAIT(bFull + (idx & 3), (idx >> 2) & 1);
+        tc_fence_after();
+      };
+      auto s_mma = [&](int t, int j) {   // S_j of tile t into accumulator j & 1 (window keys = load 4 + 2 j)
+        mma_tile(tbase + 256 * t + 64 * (j & 1), smem_u32(sm + oQS + 2 * t * kQTile), kQTile, ring(4 + 2 * j), 8192, 128, 64,
+                 8, 0, false);
+        commit(&bar[bS + 2 * t + (j & 1)]);
+      };
+      uint32_t wph[2] = {0u, 0u};
+      // G1
+      for (int t = 0; t < 2; ++t) {
+        NHA_WAIT(bQ + t, 0);
+        if (t == 0) { wait_full(0); wait_full(1); }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sm + oQG + 2 * t * kQTile);
+        mma_tile(tbase + 256 * t, aQ, kQTile, ring(0), 8192, 128, 64, 8, 0, false);
+        mma_tile(tbase + 256 * t + 64, aQ, kQTile, ring(1), 0, 128, 64, 8, 1, false);
+        commit(&bar[bG + t]);
+      }
+      commit(&bar[bEmpty + 0]);
+      commit(&bar[bEmpty + 1]);
+      // G2
+      for (int t = 0; t < 2; ++t) {
+        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
+        tc_fence_after();
+        mma_tile(tbase + 256 * t, smem_u32(sm + oQG + 2 * t * kQTile), kQTile, aSB, 0, 128, 64, 4, 1, false);
+        commit(&bar[bG + t]);
+      }
+      // G3 (+ S_0)
+      for (int t = 0; t < 2; ++t) {
+        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
+        if (t == 0) wait_full(2);
+        tc_fence_after();
+        const uint32_t aPA = smem_u32(sm + oQG + 2 * t * kQTile), aPG = aPA + kQTile;
+#pragma unroll
+        for (int ct = 0; ct < 2; ++ct)
+          mma_tile(tbase + 256 * t + 128 + 64 * ct, aPG, kQTile, ring(2) + ct * 8192, 0, 128, 64, 4, 1, false);
+        mma_tile(tbase + 256 * t + 64, aPA, kQTile, aSB, 0, 128, 64, 4, 0, false);
+        commit(&bar[bG + t]);
+        if (t == 0) wait_full(4);
+        s_mma(t, 0);
+      }
+      commit(&bar[bEmpty + 2]);
+      commit(&bar[bEmpty + 0]);                        // window keys of step 0 (load 4)
+      // G4 (+ S_1)
+      for (int t = 0; t < 2; ++t) {
+        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
+        if (t == 0) wait_full(3);
+        tc_fence_after();
+        const uint32_t aAB = smem_u32(sm + oQG + 2 * t * kQTile);
+#pragma unroll
+        for (int ct = 0; ct < 2; ++ct)
+          mma_tile(tbase + 256 * t + 128 + 64 * ct, aAB, kQTile, ring(3) + ct * 8192, 0, 128, 64, 4, 1, true);
+        commit(&bar[bG + t]);
+        if (nst > 1) {
+          if (t == 0) wait_full(6);
+          s_mma(t, 1);
+        }
+      }
+      commit(&bar[bEmpty + 3]);
+      if (nst > 1) commit(&bar[bEmpty + 2]);           // window keys of step 1 (load 6)
+      // window steps: O += P~_j V_j, then S_{j+2}
+      for (int j = 0; j < nst; ++j) {
+        const int b = j & 1;
+        for (int t = 0; t < 2; ++t) {
+          NHA_WAIT(bP + 2 * t + b, (j >> 1) & 1);
+          if (t == 0) wait_full(5 + 2 * j);
+          tc_fence_after();
+          const uint32_t aP = smem_u32(sm + oQG + (2 * t + b) * kQTile);
+#pragma unroll
+          for (int ct = 0; ct < 2; ++ct)
+            mma_tile(tbase + 256 * t + 128 + 64 * ct, aP, kQTile, ring(5 + 2 * j) + ct * 8192, 0, 128, 64, 4, 1, true);
+          commit(&bar[bPV + 2 * t + b]);
+          if (j + 2 < nst) {
+            if (t == 0) wait_full(4 + 2 * (j + 2));
+            s_mma(t, j + 2);
+          }
+        }
+        commit(&bar[bEmpty + ((5 + 2 * j) & 3)]);
+        if (j + 2 < nst) commit(&bar[bEmpty + ((4 + 2 * (j + 2)) & 3)]);
+      }
+    }
+  } else {
+    // ================= softmax groups: tile t = warp / 4, one thread per row =======================================
+    const int t = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int tk = row & 63, th = row >> 6;
+    const int pos = c0 + tk;
+    const bool in_seq = pos < len;
+    const int hq = hq0 + 2 * t + th;
+    const uint32_t tl = tbase + ((uint32_t)(quarter * 32) << 16) + 256 * t;   // S0 at +0, S1 at +64, O at +128
+    unsigned char* opA = sm + oQG + 2 * t * kQTile;      // tril(A) / p~ a / tril(Bv); P~ of even steps
+    unsigned char* opB = opA + kQTile;                   // p~ a e^R; P~ of odd steps
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int klo = in_seq ? (wl < 0 ? 0 : max(0, pos - wl)) : (1 << 30);
+    const unsigned kspan = in_seq ? (unsigned)(pos - klo) : 0u;
+    const float sc2 = d.scale * kLog2e;
+    uint32_t gph = 0u;
+    const float* arow = As + tk * 65;
+    // this thread's row of tril of a [128][64] accumulator (token tk keeps columns i <= tk) -> bf16 A-operand tile
+    auto tril_to = [&](uint32_t col0, unsigned char* dst) {
+      float v[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld32(tl + col0 + 32 * half, v);
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float o8[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o8[e] = (32 * half + 8 * c8 + e) <= tk ? v[8 * c8 + e] : 0.f;
+          *reinterpret_cast<uint4*>(dst + sw_off(row, 4 * half + c8)) = pack8(o8);
+        }
+      }
+    };
+    auto hand_over = [&](int b_) {
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bar[b_]);
+    };
+    // G1 -> tril(A)
+    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    tc_fence_after();
+    tril_to(0, opA);
+    hand_over(bW + t);
+    // G2 -> slot logits, p~, operands
+    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    tc_fence_after();
+    float mg, lg0;
+    {
+      float ok[64];
+      tmem_ld32(tl + 64, ok);
+      tmem_ld32(tl + 96, ok + 32);
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float x[32];
+        tmem_ld32(tl + 32 * half, x);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int m = 32 * half + e;
+          const float v = d.scale * arow[m] * (ER[m] * ok[m] + x[e]);
+          ok[m] = v;
+          m4[e & 3] = fmaxf(m4[e & 3], v);
+        }
+      }
+      mg = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      const float nmg = -mg * kLog2e;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        float pg8[8], pa8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int m = 8 * c8 + e;
+          const float p = exp2f(fmaf(ok[m], kLog2e, nmg));
+          l4[e & 3] += p;
+          const float pa = in_seq ? p * arow[m] : 0.f;
+          pa8[e] = pa;
+          pg8[e] = pa * ER[m];
+        }
+        *reinterpret_cast<uint4*>(opA + sw_off(row, c8)) = pack8(pa8);
+        *reinterpret_cast<uint4*>(opB + sw_off(row, c8)) = pack8(pg8);
+      }
+      lg0 = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+    }
+    hand_over(bW + t);
+    // G3 -> tril(Bv)
+    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    tc_fence_after();
+    tril_to(64, opA);
+    hand_over(bW + t);
+    // G4: the operand tiles are free for the P~ tiles from here on
+    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    tc_fence_after();
+
+    float mref = mg;            // reference of the unnormalised probabilities of this row
+    float lgs = lg0;            // slot sum, in units of exp(-mref)
+    float ls = 0.f;             // window sum, same units
+    int pvseen[2] = {0, 0};
+    // observe the completions of P~ V of steps 0 .. upto-1 (each of the two barriers is read phase by phase)
+    auto wait_pv = [&](int upto) {
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const int need = (upto + 1 - b) >> 1;
+        while (pvseen[b] < need) {
+          NHA_WAIT(bPV + 2 * t + b, pvseen[b] & 1);
+          ++pvseen[b];
+        }
+      }
+    };
+    for (int j = 0; j < nst; ++j) {
+      const int b = j & 1;
+      NHA_WAIT(bS + 2 * t + b, (j >> 1) & 1);
+      tc_fence_after();
+      float s[64];
+      tmem_ld32(tl + 64 * b, s);
+      tmem_ld32(tl + 64 * b + 32, s + 32);
+      const int off = (ci - j) * kChunk - klo;
+      {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off + e) <= kspan ? s[e] : -INFINITY);
+        const float mc = d.scale * fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        const bool raise = mc > mref + kRaise;
+        float f = 1.f;
+        if (raise) {
+          f = __expf(mref - mc);
+          mref = mc;
+        }
+        if (__any_sync(0xffffffffu, raise)) {
+          // rescale this warp's rows of O: everything issued on O so far must have completed
+          wait_pv(j);
+          tc_fence_after();
+#pragma unroll 1
+          for (int q4 = 0; q4 < 4; ++q4) {
+            float ov[32];
+            tmem_ld32(tl + 128 + 32 * q4, ov);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] *= f;
+            tmem_st32(tl + 128 + 32 * q4, ov);
+          }
+          tmem_st_wait();
+          lgs *= f;
+          ls *= f;
+        }
+      }
+      if (j >= 2) wait_pv(j - 1);                        // P~ V of step j - 2 has read this operand tile
+      unsigned char* pd = b ? opB : opA;
+      const float nm = -mref * kLog2e;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
+        float o8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float pe = (unsigned)(off + 8 * c8 + e) <= kspan ? exp2f(fmaf(s[8 * c8 + e], sc2, nm)) : 0.f;
+          l4[e & 3] += pe;
+          o8[e] = pe;
+        }
+        *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
+      }
+      ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      hand_over(bP + 2 * t + b);
+    }
+    wait_pv(nst);
+    tc_fence_after();
+    const float lsum = lgs + ls;
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    if (in_seq) {
+      d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg0);
+      d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = mref + __logf(ls);
+    }
+    bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D;
+#pragma unroll 1
+    for (int q4 = 0; q4 < 4; ++q4) {
+      float ov[32];
+      tmem_ld32(tl + 128 + 32 * q4, ov);
+      if (in_seq) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) ov[e] *= inv;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 32 * q4 + 8 * c8) = pack8(ov + 8 * c8);
+      }
+    }
+  }
+#undef NHA_WAIT
+  if (failed) atomicExch(err, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tbase, 512);
+}
+
+bool fwd_pipe_supported(const nha_chunk_desc* d) {
+  const int NG = d->HQ / d->H;
+  if (d->K != 128 || d->V != 128 || d->M != 64 || NG % 4 != 0 || !(d->scale > 0.f)) return false;
+  const char* off = getenv("NHA_B200_NO_PIPE");
+  return !(off && off[0] == '1');
+}
+
+// Launches the pipelined output pass; NHA_ERR_UNSUPPORTED when the tensor maps cannot be made (the caller then takes
+// the non-pipelined tensor-memory kernel).
+int fwd_pipe_launch(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
+  using namespace pipe;
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  PipeMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const bool ok = make_map_rows_heads(&maps.qg, d->q_gsa, d->Ttot, d->HQ, D) &&
+                  make_map_rows_heads(&maps.qs, d->q_swa, d->Ttot, d->HQ, D) &&
+                  make_map_rows_heads(&maps.kg, d->k_gsa, d->Ttot, d->H, D) &&
+                  make_map_rows_heads(&maps.ks, d->k_swa, d->Ttot, d->H, D) &&
+                  make_map_rows_heads(&maps.v, d->v, d->Ttot, d->H, D) &&
+                  make_map_matrix(&maps.hk, d->hk_chunks, (int64_t)NCB * d->H * D, M, 128) &&
+                  make_map_matrix(&maps.hv, d->hv_chunks, (int64_t)NCB * d->H * M, D, 64);
+  if (!ok) return NHA_ERR_UNSUPPORTED;
+  cudaError_t e = set_max_smem((const void*)nha_fwd_pipe_kernel, total);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  nha_fwd_pipe_kernel<<<dim3(NCB, d->H, d->HQ / d->H / 4), kThreads, total, cs>>>(*d, flags, err, maps);
+  return check_launch();
+}
+
+}  // namespace nha

@@ -29,6 +29,7 @@
 
 #include "nha_common.cuh"
 #include "nha_umma.cuh"
+#include "nha_tma.cuh"
 
 namespace nha {
 
@@ -42,20 +43,6 @@ struct WindowMaps {
   CUtensorMap k, v;
   int use;                                            // 0: no tensor maps (copies go through cp.async)
 };
-
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* mbar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-          smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(mbar))
-      : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* mbar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(mbar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* mbar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(mbar)) : "memory");
-}
 
 template <int D, int R>
 struct UmmaLayout {
@@ -660,34 +647,6 @@ __global__ void __launch_bounds__(UmmaLayout<D, R>::kThreads, (D == 64 && R == 6
   if (warp == 0) tmem_dealloc(tbase, L::kTmemCols);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
-    return (e == cudaSuccess && q == cudaDriverEntryPointSuccess) ? (EncodeTiledFn)p : (EncodeTiledFn) nullptr;
-  }();
-  return fn;
-}
-
-// [Ttot][H][D] bf16 seen as a 3-d tensor (D innermost); box = 64 columns x 1 head x 64 tokens, 128-byte swizzle
-static bool make_window_map(CUtensorMap* m, const void* base, int64_t Ttot, int H, int D) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn || Ttot <= 0 || ((uintptr_t)base & 15)) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)Ttot};
-  const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2};
-  const cuuint32_t box[3] = {64, 1, 64};
-  const cuuint32_t es[3] = {1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D, int R>
 static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
   typedef UmmaLayout<D, R> L;
@@ -697,8 +656,8 @@ static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream
   memset(&maps, 0, sizeof(maps));
   if (L::kPipe) {
     const char* off = getenv("NHA_B200_NO_TMA");
-    maps.use = !(off && off[0] == '1') && make_window_map(&maps.k, d->k_swa, d->Ttot, d->H, D) &&
-               make_window_map(&maps.v, d->v, d->Ttot, d->H, D);
+    maps.use = !(off && off[0] == '1') && make_map_rows_heads(&maps.k, d->k_swa, d->Ttot, d->H, D) &&
+               make_map_rows_heads(&maps.v, d->v, d->Ttot, d->H, D);
   }
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   nha_fwd_umma_kernel<D, R><<<dim3(NCB, d->H), L::kThreads, L::total, cs>>>(*d, flags, err, maps);
@@ -707,10 +666,18 @@ static int launch_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream
 
 // Runs the tensor-memory output pass when the shape has one (K == V in {64, 128}, M == 64, one or an
 // even number of query heads per kv head, positive scale).  Returns NHA_ERR_UNSUPPORTED otherwise.
+bool fwd_pipe_supported(const nha_chunk_desc* d);
+int fwd_pipe_launch(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs);
+
 int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs) {
   const int NG = d->HQ / d->H;
   if (d->K != d->V || d->M != 64) return NHA_ERR_UNSUPPORTED;
   if (!(d->scale > 0.f)) return NHA_ERR_UNSUPPORTED;     // row maxima are taken before scaling
+  // head dim 128 with groups of four query heads: the warp-specialised pipeline (nha_chunk_fwd_pipe.cu)
+  if (fwd_pipe_supported(d)) {
+    const int st = fwd_pipe_launch(d, flags, err, cs);
+    if (st != NHA_ERR_UNSUPPORTED) return st;
+  }
   if (d->K == 64 && NG == 1) return launch_umma<64, 64>(d, flags, err, cs);
   if (d->K == 64 && NG % 2 == 0) return launch_umma<64, 128>(d, flags, err, cs);
   if (d->K == 128 && NG == 1) return launch_umma<128, 64>(d, flags, err, cs);
