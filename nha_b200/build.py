@@ -54,7 +54,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.join(tmp, os.path.basename(src)[:-3] + '.o')
         objs.append(obj)
-        cmd = [nvcc] + [f for f in NVCC_FLAGS if f not in ('-shared',)] + ['-c', src, '-o', obj]
+        cmd = [nvcc] + [f for f in NVCC_FLAGS if f not in ('-shared',)] + os.environ.get('NHA_B200_NVCC_FLAGS', '').split() \
+            + ['-c', src, '-o', obj]
         if verbose:
             cmd.insert(1, '-Xptxas=-v')
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

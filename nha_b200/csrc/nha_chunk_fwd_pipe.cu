@@ -47,8 +47,9 @@ constexpr int oQG = 0;                            // q_gsa [2 tiles][2 k tiles][
 constexpr int oQS = oQG + 4 * kQTile;             // q_swa, same shape
 constexpr int oRing = oQS + 4 * kQTile;
 constexpr int oSB = oRing + kNSlot * kSlot;       // s' .* b [64][64]
-constexpr int oA = oSB + 8192;                    // fp32 [64][65]: cumulative gates, then a = exp(G - R)
-constexpr int oER = oA + 64 * 65 * 4;             // fp32 [64] exp(R)
+constexpr int kLdA = 68;                          // row pitch of the decay table: 16-byte aligned rows, conflict-free float4 reads
+constexpr int oA = oSB + 8192;                    // fp32 [64][kLdA]: cumulative gates, then a = exp(G - R)
+constexpr int oER = oA + 64 * kLdA * 4;           // fp32 [64] exp(R)
 constexpr int oBar = oER + 256;
 constexpr int total = oBar + 512 + 1024;          // + slack for the 1024-byte alignment of the base
 static_assert(total <= 227 * 1024, "shared memory of the pipelined output pass");
@@ -58,6 +59,30 @@ constexpr int kPoll = 1 << 20;
 constexpr float kDecayLimit = 140.0f;
 constexpr float kRaise = 5.545177f;               // 8 ln 2
 }  // namespace pipe
+
+// Phase clocks for tuning (a build with -DNHA_PIPE_PROF only): cycles per phase summed over all CTAs, read back with
+// nha_debug_pipe_prof().
+#ifdef NHA_PIPE_PROF
+__device__ unsigned long long g_pipe_prof[64];
+__device__ unsigned int g_pipe_trace[4 * 512];       // one CTA's events: (phase id << 24) | cycles since the CTA began
+#define PROF_INIT()                                                            \
+  long long tp_ = clock64();                                                   \
+  const long long tp0_ = tp_;                                                  \
+  int tn_ = 0;                                                                 \
+  const int trole_ = threadIdx.x == 0 ? 0 : (threadIdx.x == 128 ? 1 : (threadIdx.x == 256 ? 2 : 3));                \
+  const bool ttrace_ = blockIdx.x == 1000 && blockIdx.y == 0
+#define PROF(i_)                                                               \
+  do {                                                                         \
+    const long long n_ = clock64();                                            \
+    if (trole_ != 1) atomicAdd(&g_pipe_prof[i_], (unsigned long long)(n_ - tp_)); \
+    if (ttrace_ && tn_ < 511) g_pipe_trace[trole_ * 512 + 1 + tn_++] = ((unsigned)(i_) << 24) | (unsigned)((n_ - tp0_) & 0xffffff); \
+    if (ttrace_) g_pipe_trace[trole_ * 512] = tn_;                             \
+    tp_ = n_;                                                                  \
+  } while (0)
+#else
+#define PROF_INIT()
+#define PROF(i_)
+#endif
 
 struct PipeMaps {
   CUtensorMap qg, qs, kg, ks, v, hk, hv;
@@ -92,6 +117,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
   const int wl = seq_window(d, n), shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hq0 = h * NG + 4 * blockIdx.z;
+  PROF_INIT();
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -106,13 +132,13 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
   const int nst = ci - jt_lo + 1;
   const int nloads = 4 + 2 * nst;
 
-  if (tid == 0) {
-    s_abort = *(volatile int*)err;                    // an earlier CTA of this launch gave up on a wait: do not start
-    for (int i = 0; i < nBar; ++i) {
-      const bool many = (i >= bW && i < bW + 2) || (i >= bP && i < bP + 4);
-      mbar_init(&bar[i], many ? 128 : 1);
+  if (warp == 9) {
+    if (lane < nBar) {
+      const bool many = (lane >= bW && lane < bW + 2) || (lane >= bP && lane < bP + 4);
+      mbar_init(&bar[lane], many ? 128 : 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (lane == 31) s_abort = *(volatile int*)err;    // an earlier CTA of this launch gave up on a wait: do not start
   }
   if (warp == 0) tmem_alloc(tslot, 512);
   // gates and write weights of the chunk's shifted rows through registers (threads 0..255: two 16-byte pieces each)
@@ -140,6 +166,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     if (warp == 0) tmem_dealloc(tbase, 512);
     return;
   }
+  if (tid == 0 || tid == 128) PROF(0);
   bool failed = false;
 #define NHA_WAIT(idx_, par_)                                                       \
   do {                                                                             \
@@ -239,7 +266,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       float gv[8];
       unpack8(greg[j], gv);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) As[r * 65 + 8 * c8 + e] = gv[e];
+      for (int e = 0; e < 8; ++e) As[r * kLdA + 8 * c8 + e] = gv[e];
     }
   }
   __syncthreads();
@@ -250,22 +277,22 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       float run = 0.f;
 #pragma unroll
       for (int r = 16 * seg; r < 16 * seg + 16; ++r) {
-        run += As[r * 65 + m];
-        As[r * 65 + m] = run;
+        run += As[r * kLdA + m];
+        As[r * kLdA + m] = run;
       }
     }
     __syncthreads();
     float add = 0.f;
     if (tid < 256)
-      for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * 65 + m];
+      for (int s2 = 0; s2 < seg; ++s2) add += As[(16 * s2 + 15) * kLdA + m];
     __syncthreads();
     if (tid < 256 && seg > 0) {
 #pragma unroll
-      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * 65 + m] += add;
+      for (int r = 16 * seg; r < 16 * seg + 16; ++r) As[r * kLdA + m] += add;
     }
     __syncthreads();
   }
-  const bool mine_unsafe = tid < 64 && fabsf(As[63 * 65 + tid]) > kDecayLimit;
+  const bool mine_unsafe = tid < 64 && fabsf(As[63 * kLdA + tid]) > kDecayLimit;
   const int unsafe = __syncthreads_or(mine_unsafe ? 1 : 0);
   if (tid == 0 && blockIdx.z == 0) flags[(size_t)cg * H + h] = unsafe;
   if (unsafe) {
@@ -285,7 +312,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     const int c8 = tid & 7;
     if (tid < 256) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) rref[e] = 0.5f * As[63 * 65 + 8 * c8 + e];
+      for (int e = 0; e < 8; ++e) rref[e] = 0.5f * As[63 * kLdA + 8 * c8 + e];
     }
     __syncthreads();                                  // every thread holds its references before the table changes
     if (tid < 8) {
@@ -301,8 +328,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
         unpack8(sreg[j], sv);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float x = As[r * 65 + 8 * c8 + e] - rref[e];
-          As[r * 65 + 8 * c8 + e] = __expf(x);
+          const float x = As[r * kLdA + 8 * c8 + e] - rref[e];
+          As[r * kLdA + 8 * c8 + e] = __expf(x);
           out[e] = sv[e] * __expf(-x);
         }
         *reinterpret_cast<uint4*>(sm + oSB + sw_off(r, c8)) = pack8(out);
@@ -312,24 +339,63 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     __syncthreads();
   }
 
+  if (tid == 0 || tid == 128) PROF(1);
+  if (tid == 256) PROF(24);
+  if (tid == 288) PROF(16);
   const uint32_t aSB = smem_u32(sm + oSB);
   if (warp == 8) {
     // ================= load warp: the rest of the ring ============================================================
-    for (int idx = 4; idx < nloads; ++idx) {
-      NHA_WAIT(bEmpty + (idx & 3), ((idx >> 2) - 1) & 1);
-      issue_load(idx);
+    // Window keys go through slots 0 and 2, values through slots 1 and 3.  A key tile is released as soon as both
+    // tiles' S products have read it, long before the value tile of the same step, so the two sequences are polled
+    // side by side: whichever next load finds its slot free is issued.
+    int kn = 0, vn = 0, spins = 0;
+    while (kn < nst || vn < nst) {
+      bool did = false;
+      if (kn < nst) {
+        const int idx = 4 + 2 * kn;
+        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + (idx & 3)], ((idx >> 2) - 1) & 1) : 0;
+        if (__shfl_sync(0xffffffffu, free_, 0)) {
+          issue_load(idx);
+          ++kn;
+          did = true;
+        }
+      }
+      if (vn < nst) {
+        const int idx = 5 + 2 * vn;
+        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + (idx & 3)], ((idx >> 2) - 1) & 1) : 0;
+        if (__shfl_sync(0xffffffffu, free_, 0)) {
+          issue_load(idx);
+          ++vn;
+          did = true;
+        }
+      }
+      if (did) spins = 0;
+      else __nanosleep(64);
+      if (!did && ++spins > kPoll) {                        // nothing was released for a very long time: give up
+        failed = true;
+        break;
+      }
     }
+    if (lane == 0) PROF(25);
   } else if (warp == 9) {
     // ================= MMA warp: one thread issues everything =====================================================
     if (lane == 0) {
       auto ring = [&](int idx) { return smem_u32(sm + oRing + (idx & 3) * kSlot); };
+      constexpr uint32_t kT16 = kQTile >> 4;             // k-tile pitch of a 128-row A operand, in descriptor units
+      const uint32_t iK = make_idesc(128, 64, 0), iMN = make_idesc(128, 64, 1), iMN128 = make_idesc(128, 128, 1);
+      const uint64_t dSB = make_desc(aSB);
+      uint64_t dQG[2], dQS[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        dQG[t] = make_desc(smem_u32(sm + oQG + 2 * t * kQTile));
+        dQS[t] = make_desc(smem_u32(sm + oQS + 2 * t * kQTile));
+      }
       auto wait_full = [&](int idx) {
         NHA_WAIT(bFull + (idx & 3), (idx >> 2) & 1);
         tc_fence_after();
       };
       auto s_mma = [&](int t, int j) {   // S_j of tile t into accumulator j & 1 (window keys = load 4 + 2 j)
-        mma_tile(tbase + 256 * t + 64 * (j & 1), smem_u32(sm + oQS + 2 * t * kQTile), kQTile, ring(4 + 2 * j), 8192, 128, 64,
-                 8, 0, false);
+        mma_run<8, 0>(tbase + 256 * t + 64 * (j & 1), dQS[t], kT16, make_desc(ring(4 + 2 * j)), 8192 >> 4, iK, false);
         commit(&bar[bS + 2 * t + (j & 1)]);
       };
       uint32_t wph[2] = {0u, 0u};
@@ -338,10 +404,11 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
         NHA_WAIT(bQ + t, 0);
         if (t == 0) { wait_full(0); wait_full(1); }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sm + oQG + 2 * t * kQTile);
-        mma_tile(tbase + 256 * t, aQ, kQTile, ring(0), 8192, 128, 64, 8, 0, false);
-        mma_tile(tbase + 256 * t + 64, aQ, kQTile, ring(1), 0, 128, 64, 8, 1, false);
+        PROF(17);
+        mma_run<8, 0>(tbase + 256 * t, dQG[t], kT16, make_desc(ring(0)), 8192 >> 4, iK, false);
+        mma_run<8, 1>(tbase + 256 * t + 64, dQG[t], kT16, make_desc(ring(1)), 0, iMN, false);
         commit(&bar[bG + t]);
+        PROF(18);
       }
       commit(&bar[bEmpty + 0]);
       commit(&bar[bEmpty + 1]);
@@ -349,38 +416,45 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       for (int t = 0; t < 2; ++t) {
         NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
         tc_fence_after();
-        mma_tile(tbase + 256 * t, smem_u32(sm + oQG + 2 * t * kQTile), kQTile, aSB, 0, 128, 64, 4, 1, false);
+        PROF(19);
+        mma_run<4, 1>(tbase + 256 * t, dQG[t], kT16, dSB, 0, iMN, false);
         commit(&bar[bG + t]);
+        PROF(18);
       }
       // G3 (+ S_0)
       for (int t = 0; t < 2; ++t) {
         NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
+        PROF(19);
         if (t == 0) wait_full(2);
         tc_fence_after();
-        const uint32_t aPA = smem_u32(sm + oQG + 2 * t * kQTile), aPG = aPA + kQTile;
-#pragma unroll
-        for (int ct = 0; ct < 2; ++ct)
-          mma_tile(tbase + 256 * t + 128 + 64 * ct, aPG, kQTile, ring(2) + ct * 8192, 0, 128, 64, 4, 1, false);
-        mma_tile(tbase + 256 * t + 64, aPA, kQTile, aSB, 0, 128, 64, 4, 0, false);
+        PROF(17);
+        // O = (p~ a e^R) Hv: all 128 columns at once (the two 64-column tiles of Hv are 8192 bytes apart)
+        mma_run<4, 1>(tbase + 256 * t + 128, dQG[t] + kT16, 0, make_desc_lbo(ring(2), 8192), 0, iMN128, false);
+        mma_run<4, 0>(tbase + 256 * t + 64, dQG[t], 0, dSB, 0, iK, false);
         commit(&bar[bG + t]);
+        PROF(18);
         if (t == 0) wait_full(4);
+        PROF(17);
         s_mma(t, 0);
+        PROF(18);
       }
       commit(&bar[bEmpty + 2]);
       commit(&bar[bEmpty + 0]);                        // window keys of step 0 (load 4)
       // G4 (+ S_1)
       for (int t = 0; t < 2; ++t) {
         NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
+        PROF(19);
         if (t == 0) wait_full(3);
         tc_fence_after();
-        const uint32_t aAB = smem_u32(sm + oQG + 2 * t * kQTile);
-#pragma unroll
-        for (int ct = 0; ct < 2; ++ct)
-          mma_tile(tbase + 256 * t + 128 + 64 * ct, aAB, kQTile, ring(3) + ct * 8192, 0, 128, 64, 4, 1, true);
+        PROF(17);
+        mma_run<4, 1>(tbase + 256 * t + 128, dQG[t], 0, make_desc_lbo(ring(3), 8192), 0, iMN128, true);
         commit(&bar[bG + t]);
+        PROF(18);
         if (nst > 1) {
           if (t == 0) wait_full(6);
+          PROF(17);
           s_mma(t, 1);
+          PROF(18);
         }
       }
       commit(&bar[bEmpty + 3]);
@@ -390,16 +464,19 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
         const int b = j & 1;
         for (int t = 0; t < 2; ++t) {
           NHA_WAIT(bP + 2 * t + b, (j >> 1) & 1);
+          PROF(20);
           if (t == 0) wait_full(5 + 2 * j);
           tc_fence_after();
-          const uint32_t aP = smem_u32(sm + oQG + (2 * t + b) * kQTile);
-#pragma unroll
-          for (int ct = 0; ct < 2; ++ct)
-            mma_tile(tbase + 256 * t + 128 + 64 * ct, aP, kQTile, ring(5 + 2 * j) + ct * 8192, 0, 128, 64, 4, 1, true);
+          PROF(21);
+          mma_run<4, 1>(tbase + 256 * t + 128, dQG[t] + (uint32_t)b * kT16, 0, make_desc_lbo(ring(5 + 2 * j), 8192), 0, iMN128,
+                        true);
           commit(&bar[bPV + 2 * t + b]);
+          PROF(22);
           if (j + 2 < nst) {
             if (t == 0) wait_full(4 + 2 * (j + 2));
+            PROF(21);
             s_mma(t, j + 2);
+            PROF(22);
           }
         }
         commit(&bar[bEmpty + ((5 + 2 * j) & 3)]);
@@ -422,7 +499,13 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     const unsigned kspan = in_seq ? (unsigned)(pos - klo) : 0u;
     const float sc2 = d.scale * kLog2e;
     uint32_t gph = 0u;
-    const float* arow = As + tk * 65;
+    const float* arow = As + tk * kLdA;
+    // one lane of a warp polls a barrier, the others wait at the warp barrier: far fewer shared-memory polls
+#define NHA_WAIT_WARP(idx_, par_)                        \
+  do {                                                   \
+    if (lane == 0) NHA_WAIT(idx_, par_);                 \
+    __syncwarp();                                        \
+  } while (0)
     // this thread's row of tril of a [128][64] accumulator (token tk keeps columns i <= tk) -> bf16 A-operand tile
     auto tril_to = [&](uint32_t col0, unsigned char* dst) {
       float v[32];
@@ -444,29 +527,36 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       mbar_arrive(&bar[b_]);
     };
     // G1 -> tril(A)
-    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    NHA_WAIT_WARP(bG + t, gph); gph ^= 1u;
     tc_fence_after();
+    if (tid == 0 || tid == 128) PROF(2);
     tril_to(0, opA);
     hand_over(bW + t);
+    if (tid == 0 || tid == 128) PROF(3);
     // G2 -> slot logits, p~, operands
-    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    NHA_WAIT_WARP(bG + t, gph); gph ^= 1u;
     tc_fence_after();
+    if (tid == 0 || tid == 128) PROF(4);
     float mg, lg0;
     {
       float ok[64];
-      tmem_ld32(tl + 64, ok);
-      tmem_ld32(tl + 96, ok + 32);
+      tmem_ld64(tl + 64, ok);
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         float x[32];
         tmem_ld32(tl + 32 * half, x);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int m = 32 * half + e;
-          const float v = d.scale * arow[m] * (ER[m] * ok[m] + x[e]);
-          ok[m] = v;
-          m4[e & 3] = fmaxf(m4[e & 3], v);
+        for (int q = 0; q < 8; ++q) {
+          const int m = 32 * half + 4 * q;
+          const float4 a4 = *reinterpret_cast<const float4*>(arow + m);
+          const float4 e4 = *reinterpret_cast<const float4*>(ER + m);
+          ok[m] = d.scale * a4.x * (e4.x * ok[m] + x[4 * q]);
+          ok[m + 1] = d.scale * a4.y * (e4.y * ok[m + 1] + x[4 * q + 1]);
+          ok[m + 2] = d.scale * a4.z * (e4.z * ok[m + 2] + x[4 * q + 2]);
+          ok[m + 3] = d.scale * a4.w * (e4.w * ok[m + 3] + x[4 * q + 3]);
+          m4[0] = fmaxf(m4[0], ok[m]); m4[1] = fmaxf(m4[1], ok[m + 1]);
+          m4[2] = fmaxf(m4[2], ok[m + 2]); m4[3] = fmaxf(m4[3], ok[m + 3]);
         }
       }
       mg = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
@@ -474,15 +564,19 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
-        float pg8[8], pa8[8];
+        float pg8[8], pa8[8], a8[8], e8[8];
+        *reinterpret_cast<float4*>(a8) = *reinterpret_cast<const float4*>(arow + 8 * c8);
+        *reinterpret_cast<float4*>(a8 + 4) = *reinterpret_cast<const float4*>(arow + 8 * c8 + 4);
+        *reinterpret_cast<float4*>(e8) = *reinterpret_cast<const float4*>(ER + 8 * c8);
+        *reinterpret_cast<float4*>(e8 + 4) = *reinterpret_cast<const float4*>(ER + 8 * c8 + 4);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int m = 8 * c8 + e;
           const float p = exp2f(fmaf(ok[m], kLog2e, nmg));
           l4[e & 3] += p;
-          const float pa = in_seq ? p * arow[m] : 0.f;
+          const float pa = in_seq ? p * a8[e] : 0.f;
           pa8[e] = pa;
-          pg8[e] = pa * ER[m];
+          pg8[e] = pa * e8[e];
         }
         *reinterpret_cast<uint4*>(opA + sw_off(row, c8)) = pack8(pa8);
         *reinterpret_cast<uint4*>(opB + sw_off(row, c8)) = pack8(pg8);
@@ -490,14 +584,18 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       lg0 = (l4[0] + l4[1]) + (l4[2] + l4[3]);
     }
     hand_over(bW + t);
+    if (tid == 0 || tid == 128) PROF(5);
     // G3 -> tril(Bv)
-    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    NHA_WAIT_WARP(bG + t, gph); gph ^= 1u;
     tc_fence_after();
+    if (tid == 0 || tid == 128) PROF(6);
     tril_to(64, opA);
     hand_over(bW + t);
+    if (tid == 0 || tid == 128) PROF(7);
     // G4: the operand tiles are free for the P~ tiles from here on
-    NHA_WAIT(bG + t, gph); gph ^= 1u;
+    NHA_WAIT_WARP(bG + t, gph); gph ^= 1u;
     tc_fence_after();
+    if (tid == 0 || tid == 128) PROF(8);
 
     float mref = mg;            // reference of the unnormalised probabilities of this row
     float lgs = lg0;            // slot sum, in units of exp(-mref)
@@ -509,23 +607,32 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       for (int b = 0; b < 2; ++b) {
         const int need = (upto + 1 - b) >> 1;
         while (pvseen[b] < need) {
-          NHA_WAIT(bPV + 2 * t + b, pvseen[b] & 1);
+          NHA_WAIT_WARP(bPV + 2 * t + b, pvseen[b] & 1);
           ++pvseen[b];
         }
       }
     };
     for (int j = 0; j < nst; ++j) {
       const int b = j & 1;
-      NHA_WAIT(bS + 2 * t + b, (j >> 1) & 1);
+      NHA_WAIT_WARP(bS + 2 * t + b, (j >> 1) & 1);
       tc_fence_after();
+      if (tid == 0 || tid == 128) PROF(9);
       float s[64];
-      tmem_ld32(tl + 64 * b, s);
-      tmem_ld32(tl + 64 * b + 32, s + 32);
-      const int off = (ci - j) * kChunk - klo;
+      tmem_ld64(tl + 64 * b, s);
+      const int kb = (ci - j) * kChunk;
+      const int off = kb - klo;
+      // the diagonal tile (causal edge) and tiles that reach below the oldest visible key of the chunk's last row need
+      // the per-element test; every row of the chunk sees all keys of the tiles in between
+      const bool masked = j == 0 || (wl >= 0 && kb < c0 + kChunk - 1 - wl) || c0 + kChunk > len;
       {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (masked) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off + e) <= kspan ? s[e] : -INFINITY);
+          for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off + e) <= kspan ? s[e] : -INFINITY);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
+        }
         const float mc = d.scale * fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         const bool raise = mc > mref + kRaise;
         float f = 1.f;
@@ -550,26 +657,44 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
           ls *= f;
         }
       }
+      if (tid == 0 || tid == 128) PROF(10);
       if (j >= 2) wait_pv(j - 1);                        // P~ V of step j - 2 has read this operand tile
+      if (tid == 0 || tid == 128) PROF(11);
       unsigned char* pd = b ? opB : opA;
       const float nm = -mref * kLog2e;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (masked) {
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        float o8[8];
+        for (int c8 = 0; c8 < 8; ++c8) {
+          float o8[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float pe = (unsigned)(off + 8 * c8 + e) <= kspan ? exp2f(fmaf(s[8 * c8 + e], sc2, nm)) : 0.f;
-          l4[e & 3] += pe;
-          o8[e] = pe;
+          for (int e = 0; e < 8; ++e) {
+            const float pe = (unsigned)(off + 8 * c8 + e) <= kspan ? exp2f(fmaf(s[8 * c8 + e], sc2, nm)) : 0.f;
+            l4[e & 3] += pe;
+            o8[e] = pe;
+          }
+          *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
         }
-        *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
+      } else {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          float o8[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float pe = exp2f(fmaf(s[8 * c8 + e], sc2, nm));
+            l4[e & 3] += pe;
+            o8[e] = pe;
+          }
+          *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
+        }
       }
       ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       hand_over(bP + 2 * t + b);
+      if (tid == 0 || tid == 128) PROF(12);
     }
     wait_pv(nst);
     tc_fence_after();
+    if (tid == 0 || tid == 128) PROF(13);
     const float lsum = lgs + ls;
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
     if (in_seq) {
@@ -578,23 +703,41 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     }
     bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D;
 #pragma unroll 1
-    for (int q4 = 0; q4 < 4; ++q4) {
-      float ov[32];
-      tmem_ld32(tl + 128 + 32 * q4, ov);
+    for (int q2 = 0; q2 < 2; ++q2) {
+      float ov[64];
+      tmem_ld64(tl + 128 + 64 * q2, ov);
       if (in_seq) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) ov[e] *= inv;
+        for (int e = 0; e < 64; ++e) ov[e] *= inv;
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) *reinterpret_cast<uint4*>(orow + 32 * q4 + 8 * c8) = pack8(ov + 8 * c8);
+        for (int c8 = 0; c8 < 8; ++c8) *reinterpret_cast<uint4*>(orow + 64 * q2 + 8 * c8) = pack8(ov + 8 * c8);
       }
     }
   }
+  if (tid == 0 || tid == 128) PROF(14);
+#undef NHA_WAIT_WARP
 #undef NHA_WAIT
   if (failed) atomicExch(err, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tbase, 512);
 }
+
+#ifdef NHA_PIPE_PROF
+}  // namespace nha
+extern "C" int nha_debug_pipe_prof(unsigned long long* out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, nha::g_pipe_prof, sizeof(unsigned long long) * 64);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[64] = {0};
+    e = cudaMemcpyToSymbol(nha::g_pipe_prof, z, sizeof(z));
+  }
+  return e == cudaSuccess ? 0 : 4;
+}
+extern "C" int nha_debug_pipe_trace(unsigned int* out) {
+  return cudaMemcpyFromSymbol(out, nha::g_pipe_trace, sizeof(unsigned int) * 4 * 512) == cudaSuccess ? 0 : 4;
+}
+namespace nha {
+#endif
 
 bool fwd_pipe_supported(const nha_chunk_desc* d) {
   const int NG = d->HQ / d->H;

@@ -28,6 +28,18 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   return d;
 }
 
+// same, with the byte distance between consecutive 64-element blocks along the MN dimension of an MN-major operand
+// wider than one swizzle atom (N > 64) in the LBO field
+__device__ __forceinline__ uint64_t make_desc_lbo(uint32_t saddr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // kind::f16 instruction descriptor: bf16 x bf16 -> f32, A K-major, B K-major or MN-major
 __device__ __forceinline__ uint32_t make_idesc(int M, int N, int b_mn_major) {
   uint32_t d = 0;
@@ -62,6 +74,21 @@ __device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, int a
     const uint64_t da = make_desc(a_addr + kt * a_tile_bytes + kin * 32);
     const uint64_t db = b_mn ? make_desc(b_addr + ks * 2048) : make_desc(b_addr + kt * b_tile_bytes + kin * 32);
     mma_f16(d_tmem, da, db, idesc, accumulate || ks > 0);
+  }
+}
+
+// KS k steps of one product with the operand descriptors formed once: a k step advances the start-address field
+// (bits 0-13, units of 16 bytes) by 2 inside a 64-wide k tile of a K-major operand, by tile16 (tile bytes / 16) from
+// one k tile to the next, and by 128 (16 k rows) for an MN-major B.  A is K-major.
+template <int KS, int BMN>
+__device__ __forceinline__ void mma_run(uint32_t d_tmem, uint64_t da, uint32_t a_tile16, uint64_t db, uint32_t b_tile16,
+                                        uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const uint32_t kt = ks >> 2, kin = ks & 3;
+    const uint64_t a = da + (uint64_t)(kt * a_tile16 + kin * 2);
+    const uint64_t b = BMN ? db + (uint64_t)(ks * 128) : db + (uint64_t)(kt * b_tile16 + kin * 2);
+    mma_f16(d_tmem, a, b, idesc, accumulate || ks > 0);
   }
 }
 
@@ -136,6 +163,16 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* mbar, uint32_t parity,
   return done != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) { return mbar_wait_limit(mbar, parity, 1 << 22); }
+// one non-blocking test of an mbarrier phase
+__device__ __forceinline__ bool mbar_test(uint64_t* mbar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done)
+      : "r"(smem_u32(mbar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -166,6 +203,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* out) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) out[i] = __uint_as_float(r[i]);
+}
+
+// the same load without the wait: several loads can be in flight before one tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 64 consecutive fp32 columns of this thread's TMEM lane, one wait for both halves
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* out) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(out);
+  tmem_ld32_nowait(taddr, r);
+  tmem_ld32_nowait(taddr + 32, r + 32);
+  tmem_ld_wait();
 }
 
 // 16 consecutive fp32 columns of this thread's TMEM lane
