@@ -2,24 +2,29 @@
 // as a warp-specialised pipeline on the sm_100a tensor-core path.
 //
 // One CTA = one (64-token chunk, kv head, group of four query heads) = two 128-row tiles (two heads x 64 tokens each)
-// that share the chunk's slot operands (k', v', Hk, Hv, s' .* b) and every window key / value tile.  320 threads:
+// that share the chunk's slot operands (k', v', Hk, Hv, s' .* b) and every window key / value tile.  352 threads:
 //   warps 0-3 / 4-7  softmax group of tile 0 / tile 1: ONE thread per row (tcgen05.ld gives it its row of the
 //                    accumulator), element-wise work only;
 //   warp 8           loads: all operand tiles by TMA (cp.async.bulk.tensor on maps of this GPU's own tensors, no
 //                    multicast) into 128-byte-swizzled tiles, bytes counted on mbarriers; the slot operands and the
-//                    window tiles stream through one ring of four 16 KB slots; a tile that sticks out of its
-//                    sequence is written by the warp itself with zero fill, so that no row of a neighbouring sequence
-//                    ever enters a product;
-//   warp 9           one thread issues every tcgen05.mma and commits completions to mbarriers.
-// The two tiles run the same chain half a step apart, so the tensor pipe works on one while the other's softmax
-// group does its element-wise step:
+//                    window tiles stream through one ring of six 16 KB slots (window keys and values are polled
+//                    independently, a slot is refilled as soon as both tiles have read it); a tile that sticks out
+//                    of its sequence is written by the warp itself with zero fill, so that no row of a neighbouring
+//                    sequence ever enters a product;
+//   warp 9 / 10      one thread each issues the tcgen05.mma of tile 0 / tile 1 and commits completions to mbarriers,
+//                    so each tile's chain (group hands over -> products -> group continues) runs at its own pace.
+// While one tile's group does its element-wise step the tensor pipe works on the other tile:
 //     G1  A = q k'^T, QH = q Hk                group: tril(A) -> bf16 operand
 //     G2  X = tril(A) (s' .* b)                group: slot logits ok = scale a .* (e^R .* QH + X), p~ = exp(ok - max),
 //                                                     operands p~ a e^R and p~ a
 //     G3  O = (p~ a e^R) Hv, Bv = (p~ a)(s' .* b)^T      group: tril(Bv) -> bf16 operand
 //     G4  O += tril(Bv) v'
 //     window steps, newest key tile first (64 keys each):   S_j = q_swa K_j^T (two accumulators, S_{j+2} is issued as
-//         soon as the group has read S_j);   group: P~_j = exp(scale S_j - m) -> bf16 operand;   O += P~_j V_j
+//         soon as the group has read S_j);   group: P~_j = exp(scale S_j - m) written as bf16 pairs over the first 32
+//         columns of S_j in tensor memory;   O += P~_j V_j with P~_j as the tensor-memory A operand
+// Shared-memory bandwidth is what bounds the tensor pipe here (a 128 x 64 x 16 product reads 6 KB of operands in its
+// 32 cycles): the value products therefore take all 128 columns of V at once (an MN-major operand spanning two
+// swizzle atoms) and read P~ from tensor memory, which halves their shared-memory traffic.
 // ONE softmax over the slot logits and all window logits, in a single sweep: the running reference m of a row starts
 // as its slot maximum and is only raised when a window logit exceeds it by more than 8 ln 2 (probabilities then stay
 // below 256, exact in the fp32 accumulator); raising it rescales the row of O in tensor memory (tcgen05.ld / st by the
@@ -40,7 +45,7 @@ using namespace umma;
 
 namespace pipe {
 constexpr int D = 128, M = 64;
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;
 constexpr int kQTile = 128 * 128;                 // one 64-wide k tile of a 128-row A operand
 constexpr int kSlot = 16384, kNSlot = 4;
 constexpr int oQG = 0;                            // q_gsa [2 tiles][2 k tiles][128][64]; later tril / p~ operands, P~
@@ -54,7 +59,7 @@ constexpr int oBar = oER + 256;
 constexpr int total = oBar + 512 + 1024;          // + slack for the 1024-byte alignment of the base
 static_assert(total <= 227 * 1024, "shared memory of the pipelined output pass");
 // mbarriers
-constexpr int bQ = 0, bFull = 2, bEmpty = 6, bG = 10, bW = 12, bS = 14, bP = 18, bPV = 22, nBar = 26;
+constexpr int bQ = 0, bFull = 2, bEmpty = 8, bG = 14, bW = 16, bS = 18, bP = 22, bPV = 26, nBar = 28;
 constexpr int kPoll = 1 << 20;
 constexpr float kDecayLimit = 140.0f;
 constexpr float kRaise = 5.545177f;               // 8 ln 2
@@ -70,7 +75,7 @@ __device__ unsigned int g_pipe_trace[4 * 512];       // one CTA's events: (phase
   const long long tp0_ = tp_;                                                  \
   int tn_ = 0;                                                                 \
   const int trole_ = threadIdx.x == 0 ? 0 : (threadIdx.x == 128 ? 1 : (threadIdx.x == 256 ? 2 : 3));                \
-  const bool ttrace_ = blockIdx.x == 1000 && blockIdx.y == 0
+  const bool ttrace_ = blockIdx.x == 40 && blockIdx.y == 0
 #define PROF(i_)                                                               \
   do {                                                                         \
     const long long n_ = clock64();                                            \
@@ -135,7 +140,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
   if (warp == 9) {
     if (lane < nBar) {
       const bool many = (lane >= bW && lane < bW + 2) || (lane >= bP && lane < bP + 4);
-      mbar_init(&bar[lane], many ? 128 : 1);
+      const bool two = lane >= bEmpty && lane < bEmpty + 6;         // released by both MMA warps
+      mbar_init(&bar[lane], many ? 128 : (two ? 2 : 1));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (lane == 31) s_abort = *(volatile int*)err;    // an earlier CTA of this launch gave up on a wait: do not start
@@ -199,9 +205,15 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     fence_async_smem();
     __syncwarp();
   };
+  // Ring of six 16 KB slots: slots 0-3 lie in their own region, slots 4 and 5 are the second operand tile (p~ a e^R)
+  // of tile 0 and tile 1, free once the product that reads it (G3 of that tile) has completed.  The slot operands
+  // (loads 0-3) use slots 0-3; window keys of step j use slot 2 (j % 3), window values slot 2 (j % 3) + 1.
+  auto slot_ptr = [&](int slot) { return sm + (slot < 4 ? oRing + slot * kSlot : oQG + (2 * (slot - 4) + 1) * kQTile); };
+  auto slot_of = [&](int idx) { return idx < 4 ? idx : 2 * (((idx - 4) >> 1) % 3) + (idx & 1); };
   auto issue_load = [&](int idx) {
-    unsigned char* dst = sm + oRing + (idx & 3) * kSlot;
-    uint64_t* fb = &bar[bFull + (idx & 3)];
+    const int slot = slot_of(idx);
+    unsigned char* dst = slot_ptr(slot);
+    uint64_t* fb = &bar[bFull + slot];
     if (idx == 1) {
       if (lane == 0) {
         mbar_expect_tx(fb, 16384);
@@ -345,15 +357,16 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
   const uint32_t aSB = smem_u32(sm + oSB);
   if (warp == 8) {
     // ================= load warp: the rest of the ring ============================================================
-    // Window keys go through slots 0 and 2, values through slots 1 and 3.  A key tile is released as soon as both
-    // tiles' S products have read it, long before the value tile of the same step, so the two sequences are polled
-    // side by side: whichever next load finds its slot free is issued.
+    // Window keys go through slots 0, 2, 4, values through slots 1, 3, 5; every slot has had one earlier occupant (a
+    // slot operand, or a tile's p~ a e^R), so step j waits for release number j / 3 + 1 of its slot.  A key tile is
+    // released as soon as both tiles' S products have read it, long before the value tile of the same step, so the
+    // two sequences are polled side by side: whichever next load finds its slot free is issued.
     int kn = 0, vn = 0, spins = 0;
     while (kn < nst || vn < nst) {
       bool did = false;
       if (kn < nst) {
         const int idx = 4 + 2 * kn;
-        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + (idx & 3)], ((idx >> 2) - 1) & 1) : 0;
+        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + slot_of(idx)], (kn / 3) & 1) : 0;
         if (__shfl_sync(0xffffffffu, free_, 0)) {
           issue_load(idx);
           ++kn;
@@ -362,7 +375,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       }
       if (vn < nst) {
         const int idx = 5 + 2 * vn;
-        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + (idx & 3)], ((idx >> 2) - 1) & 1) : 0;
+        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + slot_of(idx)], (vn / 3) & 1) : 0;
         if (__shfl_sync(0xffffffffu, free_, 0)) {
           issue_load(idx);
           ++vn;
@@ -377,110 +390,95 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       }
     }
     if (lane == 0) PROF(25);
-  } else if (warp == 9) {
-    // ================= MMA warp: one thread issues everything =====================================================
+  } else if (warp >= 9) {
+    // ================= MMA warps: warp 9 issues for tile 0, warp 10 for tile 1 (one thread each) ====================
+    // Each tile's chain (group hands over -> products issued -> group continues) then runs at its own pace; a ring slot
+    // is released when BOTH issuers have committed behind their last product that reads it (barrier count 2).
     if (lane == 0) {
-      auto ring = [&](int idx) { return smem_u32(sm + oRing + (idx & 3) * kSlot); };
+      const int t = warp - 9;
+      auto ring = [&](int idx) { return smem_u32(slot_ptr(slot_of(idx))); };
       constexpr uint32_t kT16 = kQTile >> 4;             // k-tile pitch of a 128-row A operand, in descriptor units
       const uint32_t iK = make_idesc(128, 64, 0), iMN = make_idesc(128, 64, 1), iMN128 = make_idesc(128, 128, 1);
       const uint64_t dSB = make_desc(aSB);
-      uint64_t dQG[2], dQS[2];
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        dQG[t] = make_desc(smem_u32(sm + oQG + 2 * t * kQTile));
-        dQS[t] = make_desc(smem_u32(sm + oQS + 2 * t * kQTile));
-      }
+      const uint64_t dQG = make_desc(smem_u32(sm + oQG + 2 * t * kQTile));
+      const uint64_t dQS = make_desc(smem_u32(sm + oQS + 2 * t * kQTile));
+      const uint32_t tt = tbase + 256 * t;               // S0 at +0, S1 at +64, O at +128
       auto wait_full = [&](int idx) {
-        NHA_WAIT(bFull + (idx & 3), (idx >> 2) & 1);
+        // fill number of the slot: slots 0-3 were filled once by the slot operands before the window tiles
+        const int slot = slot_of(idx);
+        const int fills = idx < 4 ? 0 : ((idx - 4) >> 1) / 3 + (slot < 4 ? 1 : 0);
+        NHA_WAIT(bFull + slot, fills & 1);
         tc_fence_after();
       };
-      auto s_mma = [&](int t, int j) {   // S_j of tile t into accumulator j & 1 (window keys = load 4 + 2 j)
-        mma_run<8, 0>(tbase + 256 * t + 64 * (j & 1), dQS[t], kT16, make_desc(ring(4 + 2 * j)), 8192 >> 4, iK, false);
+      auto s_mma = [&](int j) {          // S_j into accumulator j & 1 (window keys = load 4 + 2 j), then release the keys
+        wait_full(4 + 2 * j);
+        mma_run<8, 0>(tt + 64 * (j & 1), dQS, kT16, make_desc(ring(4 + 2 * j)), 8192 >> 4, iK, false);
         commit(&bar[bS + 2 * t + (j & 1)]);
+        commit(&bar[bEmpty + slot_of(4 + 2 * j)]);
       };
-      uint32_t wph[2] = {0u, 0u};
-      // G1
-      for (int t = 0; t < 2; ++t) {
-        NHA_WAIT(bQ + t, 0);
-        if (t == 0) { wait_full(0); wait_full(1); }
-        tc_fence_after();
-        PROF(17);
-        mma_run<8, 0>(tbase + 256 * t, dQG[t], kT16, make_desc(ring(0)), 8192 >> 4, iK, false);
-        mma_run<8, 1>(tbase + 256 * t + 64, dQG[t], kT16, make_desc(ring(1)), 0, iMN, false);
-        commit(&bar[bG + t]);
-        PROF(18);
-      }
+      uint32_t wph = 0u;
+      // G1: A = q k'^T, QH = q Hk
+      NHA_WAIT(bQ + t, 0);
+      wait_full(0);
+      wait_full(1);
+      PROF(17);
+      mma_run<8, 0>(tt, dQG, kT16, make_desc(ring(0)), 8192 >> 4, iK, false);
+      mma_run<8, 1>(tt + 64, dQG, kT16, make_desc(ring(1)), 0, iMN, false);
+      commit(&bar[bG + t]);
       commit(&bar[bEmpty + 0]);
       commit(&bar[bEmpty + 1]);
-      // G2
-      for (int t = 0; t < 2; ++t) {
-        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
-        tc_fence_after();
-        PROF(19);
-        mma_run<4, 1>(tbase + 256 * t, dQG[t], kT16, dSB, 0, iMN, false);
-        commit(&bar[bG + t]);
-        PROF(18);
-      }
-      // G3 (+ S_0)
-      for (int t = 0; t < 2; ++t) {
-        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
-        PROF(19);
-        if (t == 0) wait_full(2);
-        tc_fence_after();
-        PROF(17);
-        // O = (p~ a e^R) Hv: all 128 columns at once (the two 64-column tiles of Hv are 8192 bytes apart)
-        mma_run<4, 1>(tbase + 256 * t + 128, dQG[t] + kT16, 0, make_desc_lbo(ring(2), 8192), 0, iMN128, false);
-        mma_run<4, 0>(tbase + 256 * t + 64, dQG[t], 0, dSB, 0, iK, false);
-        commit(&bar[bG + t]);
-        PROF(18);
-        if (t == 0) wait_full(4);
-        PROF(17);
-        s_mma(t, 0);
-        PROF(18);
-      }
+      PROF(18);
+      // G2: X = tril(A) (s' .* b)
+      NHA_WAIT(bW + t, wph); wph ^= 1u;
+      tc_fence_after();
+      PROF(19);
+      mma_run<4, 1>(tt, dQG, kT16, dSB, 0, iMN, false);
+      commit(&bar[bG + t]);
+      PROF(18);
+      // G3: O = (p~ a e^R) Hv over all 128 columns (the two 64-column tiles of Hv are 8192 bytes apart), Bv = (p~ a) SB^T
+      NHA_WAIT(bW + t, wph); wph ^= 1u;
+      PROF(19);
+      wait_full(2);
+      PROF(17);
+      mma_run<4, 1>(tt + 128, dQG + kT16, 0, make_desc_lbo(ring(2), 8192), 0, iMN128, false);
+      mma_run<4, 0>(tt + 64, dQG, 0, dSB, 0, iK, false);
+      commit(&bar[bG + t]);
       commit(&bar[bEmpty + 2]);
-      commit(&bar[bEmpty + 0]);                        // window keys of step 0 (load 4)
-      // G4 (+ S_1)
-      for (int t = 0; t < 2; ++t) {
-        NHA_WAIT(bW + t, wph[t]); wph[t] ^= 1u;
-        PROF(19);
-        if (t == 0) wait_full(3);
-        tc_fence_after();
-        PROF(17);
-        mma_run<4, 1>(tbase + 256 * t + 128, dQG[t], 0, make_desc_lbo(ring(3), 8192), 0, iMN128, true);
-        commit(&bar[bG + t]);
-        PROF(18);
-        if (nst > 1) {
-          if (t == 0) wait_full(6);
-          PROF(17);
-          s_mma(t, 1);
-          PROF(18);
-        }
-      }
+      commit(&bar[bEmpty + 4 + t]);                      // this tile's p~ a e^R operand becomes ring slot 4 + t:
+      commit(&bar[bEmpty + 4 + t]);                      // nobody else reads it, so this issuer gives both arrivals
+      PROF(18);
+      s_mma(0);                                          // S0 is free: QH and X have been read
+      PROF(18);
+      // G4: O += tril(Bv) v'
+      NHA_WAIT(bW + t, wph); wph ^= 1u;
+      PROF(19);
+      wait_full(3);
+      PROF(17);
+      mma_run<4, 1>(tt + 128, dQG, 0, make_desc_lbo(ring(3), 8192), 0, iMN128, true);
+      commit(&bar[bG + t]);
       commit(&bar[bEmpty + 3]);
-      if (nst > 1) commit(&bar[bEmpty + 2]);           // window keys of step 1 (load 6)
-      // window steps: O += P~_j V_j, then S_{j+2}
+      PROF(18);
+      if (nst > 1) s_mma(1);                             // S1 is free: Bv has been read
+      PROF(18);
+      // window steps: O += P~_j V_j with P~_j read from tensor memory (the group wrote it over the first 32 columns of
+      // S_j), then S_{j+2} into the accumulator the group has just finished with
       for (int j = 0; j < nst; ++j) {
         const int b = j & 1;
-        for (int t = 0; t < 2; ++t) {
-          NHA_WAIT(bP + 2 * t + b, (j >> 1) & 1);
-          PROF(20);
-          if (t == 0) wait_full(5 + 2 * j);
-          tc_fence_after();
-          PROF(21);
-          mma_run<4, 1>(tbase + 256 * t + 128, dQG[t] + (uint32_t)b * kT16, 0, make_desc_lbo(ring(5 + 2 * j), 8192), 0, iMN128,
-                        true);
-          commit(&bar[bPV + 2 * t + b]);
-          PROF(22);
-          if (j + 2 < nst) {
-            if (t == 0) wait_full(4 + 2 * (j + 2));
-            PROF(21);
-            s_mma(t, j + 2);
-            PROF(22);
-          }
+        NHA_WAIT(bP + 2 * t + b, (j >> 1) & 1);
+        PROF(20);
+        wait_full(5 + 2 * j);
+        PROF(21);
+        {
+          const uint64_t dV = make_desc_lbo(ring(5 + 2 * j), 8192);
+          const uint32_t aP = tt + 64 * b;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) mma_f16_ta(tt + 128, aP + 8 * ks, dV + (uint64_t)(ks * 128), iMN128, true);
         }
-        commit(&bar[bEmpty + ((5 + 2 * j) & 3)]);
-        if (j + 2 < nst) commit(&bar[bEmpty + ((4 + 2 * (j + 2)) & 3)]);
+        commit(&bar[bPV + t]);
+        commit(&bar[bEmpty + slot_of(5 + 2 * j)]);
+        PROF(22);
+        if (j + 2 < nst) s_mma(j + 2);
+        PROF(22);
       }
     }
   } else {
@@ -492,8 +490,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     const bool in_seq = pos < len;
     const int hq = hq0 + 2 * t + th;
     const uint32_t tl = tbase + ((uint32_t)(quarter * 32) << 16) + 256 * t;   // S0 at +0, S1 at +64, O at +128
-    unsigned char* opA = sm + oQG + 2 * t * kQTile;      // tril(A) / p~ a / tril(Bv); P~ of even steps
-    unsigned char* opB = opA + kQTile;                   // p~ a e^R; P~ of odd steps
+    unsigned char* opA = sm + oQG + 2 * t * kQTile;      // tril(A) / p~ a / tril(Bv); then P~ of every window step
+    unsigned char* opB = opA + kQTile;                   // p~ a e^R (afterwards a slot of the operand ring)
     constexpr float kLog2e = 1.4426950408889634f;
     const int klo = in_seq ? (wl < 0 ? 0 : max(0, pos - wl)) : (1 << 30);
     const unsigned kspan = in_seq ? (unsigned)(pos - klo) : 0u;
@@ -600,16 +598,13 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
     float mref = mg;            // reference of the unnormalised probabilities of this row
     float lgs = lg0;            // slot sum, in units of exp(-mref)
     float ls = 0.f;             // window sum, same units
-    int pvseen[2] = {0, 0};
-    // observe the completions of P~ V of steps 0 .. upto-1 (each of the two barriers is read phase by phase)
+    int pvseen = 0;
+    // observe the completions of P~ V of steps 0 .. upto-1 (one barrier per tile, read phase by phase: P~ V of step j
+    // is only issued after this group has handed over P~_j, so the barrier is never more than one phase ahead)
     auto wait_pv = [&](int upto) {
-#pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        const int need = (upto + 1 - b) >> 1;
-        while (pvseen[b] < need) {
-          NHA_WAIT_WARP(bPV + 2 * t + b, pvseen[b] & 1);
-          ++pvseen[b];
-        }
+      while (pvseen < upto) {
+        NHA_WAIT_WARP(bPV + t, pvseen & 1);
+        ++pvseen;
       }
     };
     for (int j = 0; j < nst; ++j) {
@@ -658,38 +653,42 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
         }
       }
       if (tid == 0 || tid == 128) PROF(10);
-      if (j >= 2) wait_pv(j - 1);                        // P~ V of step j - 2 has read this operand tile
       if (tid == 0 || tid == 128) PROF(11);
-      unsigned char* pd = b ? opB : opA;
       const float nm = -mref * kLog2e;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
       if (masked) {
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          float o8[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float pe = (unsigned)(off + 8 * c8 + e) <= kspan ? exp2f(fmaf(s[8 * c8 + e], sc2, nm)) : 0.f;
-            l4[e & 3] += pe;
-            o8[e] = pe;
-          }
-          *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
+        for (int e = 0; e < 64; ++e) {
+          s[e] = (unsigned)(off + e) <= kspan ? exp2f(fmaf(s[e], sc2, nm)) : 0.f;
+          l4[e & 3] += s[e];
         }
       } else {
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          float o8[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float pe = exp2f(fmaf(s[8 * c8 + e], sc2, nm));
-            l4[e & 3] += pe;
-            o8[e] = pe;
-          }
-          *reinterpret_cast<uint4*>(pd + sw_off(row, c8)) = pack8(o8);
+        for (int e = 0; e < 64; ++e) {
+          s[e] = exp2f(fmaf(s[e], sc2, nm));
+          l4[e & 3] += s[e];
         }
       }
+      if (tid == 0 || tid == 128) PROF(27);
+      {
+        // P~_j as bf16 pairs over the first 32 columns of S_j: the A operand of the value product
+        float pk[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(s[2 * e], s[2 * e + 1]);
+          pk[e] = __uint_as_float(*reinterpret_cast<const uint32_t*>(&h2));
+        }
+        tmem_st32(tl + 64 * b, pk);
+        tmem_st_wait();
+      }
+      if (tid == 0 || tid == 128) PROF(28);
       ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      hand_over(bP + 2 * t + b);
+      // Every completion phase of the value products is observed before the next one can happen: P~ V of step j is only
+      // issued after this hand-over, so seeing step j - 1 complete here (it was issued a whole step ago) keeps the
+      // barrier at most one phase ahead of what this thread has seen.
+      wait_pv(j);
+      tc_fence_before();
+      mbar_arrive(&bar[bP + 2 * t + b]);
       if (tid == 0 || tid == 128) PROF(12);
     }
     wait_pv(nst);
@@ -701,16 +700,34 @@ __global__ void __launch_bounds__(pipe::kThreads, 1)
       d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg0);
       d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = mref + __logf(ls);
     }
-    bf16* orow = (bf16*)d.o + ((size_t)(t0 + pos) * HQ + hq) * D;
+    // Output rows leave through shared memory: a thread holds one whole row (256 bytes), and stores of 32 lanes to 32
+    // rows 8 KB apart would cost one memory transaction per lane.  The rows are staged in this tile's q_swa tiles (dead:
+    // every S product has completed) with the 16-byte pieces of a row rotated by the row index (no bank conflicts), and
+    // each warp then writes its own 32 rows, two whole rows per instruction.
+    unsigned char* stage = sm + oQS + 2 * t * kQTile + (size_t)(quarter * 32) * 256;     // this warp's 32 rows
 #pragma unroll 1
     for (int q2 = 0; q2 < 2; ++q2) {
       float ov[64];
       tmem_ld64(tl + 128 + 64 * q2, ov);
-      if (in_seq) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) ov[e] *= inv;
+      for (int e = 0; e < 64; ++e) ov[e] *= inv;
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) *reinterpret_cast<uint4*>(orow + 64 * q2 + 8 * c8) = pack8(ov + 8 * c8);
+      for (int c8 = 0; c8 < 8; ++c8)
+        *reinterpret_cast<uint4*>(stage + lane * 256 + (((8 * q2 + c8) ^ (lane & 15)) << 4)) = pack8(ov + 8 * c8);
+    }
+    __syncwarp();
+    {
+      const int half = lane >> 4, c = lane & 15;          // two rows per instruction, 16 pieces of 16 bytes per row
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int r = 2 * i + half;                       // row of this warp
+        const int rr = quarter * 32 + r;                  // row of the tile
+        const int p2 = c0 + (rr & 63);
+        if (p2 < len) {
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((c ^ (r & 15)) << 4));
+          bf16* dst = (bf16*)d.o + ((size_t)(t0 + p2) * HQ + hq0 + 2 * t + (rr >> 6)) * D + 8 * c;
+          *reinterpret_cast<uint4*>(dst) = v;
+        }
       }
     }
   }

@@ -64,6 +64,17 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_
       : "memory");
 }
 
+// the same with the A operand in tensor memory: a_tmem addresses M lanes x 8 columns, each column holding two
+// consecutive bf16 elements of the row along k (the lower half first)
+__device__ __forceinline__ void mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
 // D[M x N] (+)= A[M x 16*ksteps] * B: A K-major tile(s), B K-major (b_mn = 0) or MN-major (b_mn = 1).
 // a_tile_bytes / b_tile_bytes: distance between consecutive 64-wide k tiles of the operand.
 __device__ __forceinline__ void mma_tile(uint32_t d_tmem, uint32_t a_addr, int a_tile_bytes, uint32_t b_addr,
