@@ -236,7 +236,7 @@ int nha_chunk_bwd(const nha_chunk_desc* d, void* stream);
    per-chunk scratch comes from a fixed array inside the library's device image
    (nha_chunk_state_pass_static_max_bytes() bytes, 16 MiB, held on every GPU that loads the
    library until the process exits).  The call itself allocates nothing.  A problem whose
-   scratch (nha_chunk_count_bound(Ttot, N)*H*(K*M+M*V+M) floats plus 256 bytes, = nha_chunk_fwd_workspace_bytes)
+   scratch (nha_chunk_count_bound(Ttot, N)*H*((K*M+M*V)*2 + M*4) + 256 bytes, = nha_chunk_fwd_workspace_bytes)
    exceeds the array is refused with NHA_ERR_STATIC_SCRATCH and nothing is launched.  The first
    call on each device looks up the array's device address (cudaGetSymbolAddress, with that
    device current); make that first call before any stream capture begins.  All calls on a

@@ -735,12 +735,12 @@ constexpr int kScanBatch = 8;
 __global__ void __launch_bounds__(256) nha_bwd_state_scan_kernel(const nha_chunk_desc d, const BwdWs w) {
   const int K = d.K, V = d.V, M = d.M, H = d.H;
   const int KM = K * M, MV = M * V;
-  const size_t nh = blockIdx.y;
+  const size_t nh = blockIdx.x;                     // (sequence, kv head) in x: no 65535 limit on packed batches
   const int n = nh / H, h = nh % H;
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int chunk0 = d.plan[n];
-  const int el = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int el = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (el >= KM + MV) return;
   const bool is_k = el < KM;
   const int e = is_k ? el : el - KM;
@@ -1130,7 +1130,7 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
     st = check_launch();
     if (st != NHA_OK) return st;
     const int SD = d->K * d->M + d->M * d->V;
-    nha_bwd_state_scan_kernel<<<dim3((SD / 4 + 255) / 256, d->N * d->H), 256, 0, cs>>>(*d, w);
+    nha_bwd_state_scan_kernel<<<dim3(d->N * d->H, (SD / 4 + 255) / 256), 256, 0, cs>>>(*d, w);
     st = check_launch();
     if (st != NHA_OK) return st;
   }

@@ -41,23 +41,55 @@ __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restr
   for (int c = total + threadIdx.x; c < NCB; c += blockDim.x) plan[N + 1 + c] = -1;
   int4* rec = reinterpret_cast<int4*>(plan + plan_rec_offset(N, NCB, H));
   for (int c = total + threadIdx.x; c < NCB; c += blockDim.x) rec[c] = make_int4(-1, 0, 0, 0);
-  for (int n = threadIdx.x; n < N; n += blockDim.x) {
-    const int c0 = plan[n], c1 = plan[n + 1];
-    for (int c = c0; c < c1; ++c) {
-      plan[N + 1 + c] = n;
-      rec[c] = make_int4(n, c - c0, cu[n], cu[n + 1] - cu[n]);
+  // one thread per chunk: its sequence is the last one whose first chunk is <= c (binary search over plan[0..N])
+  for (int c = threadIdx.x; c < total; c += blockDim.x) {
+    int lo = 0, hi = N - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (plan[mid] <= c) lo = mid; else hi = mid - 1;
     }
+    while (lo + 1 < N && plan[lo + 1] <= c) ++lo;      // empty sequences share their first chunk with the next one
+    plan[N + 1 + c] = lo;
+    rec[c] = make_int4(lo, c - plan[lo], cu[lo], cu[lo + 1] - cu[lo]);
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Scratch of the state pass: L [NCB*H][K*M + M*V] fp32, then Gend [NCB*H][M] fp32.
+// Scratch of the state pass: L [NCB*H][K*M + M*V] bf16 (the chunk-start states it is summed into are bf16 too; the
+// running sum itself stays fp32), then Gend [NCB*H][M] fp32.
 struct StateWs {
-  float* local;
+  bf16* local;
   float* gend;
 };
 
-struct StLocalLayout { int kt, vt, sbe, G, total; };
+// C[Mt*16 x Nt*16] = A^T B as tile_gemm<false, true, false>, with the fp32 accumulator tiles rounded to bf16 on their way
+// to global memory: a warp parks its 16 x 16 tile in its own 1 KB patch of shared memory and writes it out as 16 rows
+// of 32 bytes (whole sectors).
+__device__ __forceinline__ void tile_gemm_tn_bf16(bf16* C, int ldc, const bf16* A, int lda, const bf16* B, int ldb, int Mt,
+                                                  int Nt, int Kt, int warp, int nwarps, float* patch) {
+  using namespace nvcuda::wmma;
+  const int lane = threadIdx.x & 31;
+  float* mine = patch + warp * 256;
+  for (int t = warp; t < Mt * Nt; t += nwarps) {
+    const int mt = t / Nt, nt = t % Nt;
+    fragment<accumulator, 16, 16, 16, float> acc;
+    fill_fragment(acc, 0.0f);
+    for (int kt = 0; kt < Kt; ++kt) {
+      fragment<matrix_a, 16, 16, 16, bf16, col_major> fa;
+      fragment<matrix_b, 16, 16, 16, bf16, row_major> fb;
+      load_matrix_sync(fa, A + (size_t)kt * 16 * lda + mt * 16, lda);
+      load_matrix_sync(fb, B + (size_t)kt * 16 * ldb + nt * 16, ldb);
+      mma_sync(acc, fa, fb, acc);
+    }
+    store_matrix_sync(mine, acc, 16, mem_row_major);
+    __syncwarp();
+    const int r = lane >> 1, hf = lane & 1;
+    *reinterpret_cast<uint4*>(C + (size_t)(mt * 16 + r) * ldc + nt * 16 + 8 * hf) = pack8(mine + r * 16 + 8 * hf);
+    __syncwarp();
+  }
+}
+
+struct StLocalLayout { int kt, vt, sbe, G, patch, total; };
 __host__ __device__ inline int st_up128(int x) { return (x + 127) & ~127; }
 __host__ __device__ inline StLocalLayout st_local_layout(int K, int V, int M) {
   StLocalLayout L; int off = 0;
@@ -65,6 +97,7 @@ __host__ __device__ inline StLocalLayout st_local_layout(int K, int V, int M) {
   L.vt = off; off = st_up128(off + kChunk * (V + 8) * 2);
   L.sbe = off; off = st_up128(off + kChunk * (M + 8) * 2);
   L.G = off; off = st_up128(off + kChunk * (M + 4) * 4);
+  L.patch = off; off = st_up128(off + kStWarps * 256 * 4);
   L.total = off;
   return L;
 }
@@ -148,29 +181,29 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
     *reinterpret_cast<uint4*>(sbe + r * ldsb + 8 * c8) = pack8(out);
   }
   __syncthreads();
-  float* Lk = w.local + ((size_t)cg * H + h) * ((size_t)K * M + (size_t)M * V);
-  float* Lv = Lk + (size_t)K * M;
-  // L_k [K x M] = k'^T [K x 64] * sbe [64 x M];  L_v [M x V] = sbe^T [M x 64] * v' [64 x V], stored
-  // straight to global memory from the accumulator fragments
-  tile_gemm<false, true, false>(Lk, M, kt, ldk, sbe, ldsb, K / 16, M / 16, kChunk / 16, warp, kStWarps);
-  tile_gemm<false, true, false>(Lv, V, sbe, ldsb, vt, ldv, M / 16, V / 16, kChunk / 16, warp, kStWarps);
+  bf16* Lk = w.local + ((size_t)cg * H + h) * ((size_t)K * M + (size_t)M * V);
+  bf16* Lv = Lk + (size_t)K * M;
+  // L_k [K x M] = k'^T [K x 64] * sbe [64 x M];  L_v [M x V] = sbe^T [M x 64] * v' [64 x V]
+  float* patch = (float*)(smem + L.patch);
+  tile_gemm_tn_bf16(Lk, M, kt, ldk, sbe, ldsb, K / 16, M / 16, kChunk / 16, warp, kStWarps, patch);
+  tile_gemm_tn_bf16(Lv, V, sbe, ldsb, vt, ldv, M / 16, V / 16, kChunk / 16, warp, kStWarps, patch);
 }
 
 // Forward scan over the chunks of one (sequence, kv head): stores the state at every chunk start and
 // the final state.  One thread owns four consecutive state elements (one 8-byte bf16 store per chunk) and
 // fetches kStScanBatch chunks of L ahead of the serial recurrence, so that a long sequence with few heads
 // still keeps enough loads in flight.
-constexpr int kStScanBatch = 8;
+constexpr int kStScanBatch = 16;
 __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w) {
   const int K = d.K, V = d.V, M = d.M, H = d.H;
   const int KM = K * M, MV = M * V;
   const size_t SD = (size_t)KM + MV;
-  const size_t nh = blockIdx.y;
+  const size_t nh = blockIdx.x;                     // (sequence, kv head) in x: no 65535 limit on packed batches
   const int n = nh / H, h = nh % H;
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int chunk0 = d.plan[n];
-  const int el = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int el = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (el >= KM + MV) return;
   const bool is_k = el < KM;
   const int e = is_k ? el : el - KM;
@@ -183,13 +216,14 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
     if (h0) run = *reinterpret_cast<const float4*>(h0 + nh * per + e);
   }
   for (int lo = 0; lo < nchunks; lo += kStScanBatch) {
-    float4 la[kStScanBatch], da[kStScanBatch];
+    uint2 la[kStScanBatch];
+    float4 da[kStScanBatch];
 #pragma unroll
     for (int u = 0; u < kStScanBatch; ++u) {
       const int ci = lo + u;
       if (ci < nchunks) {
         const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-        la[u] = __ldcs((const float4*)(w.local + cgi * SD + el));
+        la[u] = __ldcs((const uint2*)(w.local + cgi * SD + el));
         if (is_k) da[u] = *(const float4*)(w.gend + cgi * M + m);
         else da[u].x = w.gend[cgi * M + m];
       }
@@ -206,8 +240,10 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
         float4 a;
         if (is_k) a = make_float4(__expf(da[u].x), __expf(da[u].y), __expf(da[u].z), __expf(da[u].w));
         else { const float x = __expf(da[u].x); a = make_float4(x, x, x, x); }
-        run.x = run.x * a.x + la[u].x; run.y = run.y * a.y + la[u].y;
-        run.z = run.z * a.z + la[u].z; run.w = run.w * a.w + la[u].w;
+        const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].x));
+        const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].y));
+        run.x = run.x * a.x + l01.x; run.y = run.y * a.y + l01.y;
+        run.z = run.z * a.z + l23.x; run.w = run.w * a.w + l23.y;
       }
     }
   }
@@ -218,7 +254,7 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
 int64_t state_workspace_bytes(const nha_chunk_desc* d) {
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   const int64_t rows = nha_chunk_count_bound(d->Ttot, d->N) * d->H;
-  return rows * (SD + d->M) * 4 + 256;
+  return rows * (SD * 2 + d->M * 4) + 256;
 }
 
 // Both launches of the state pass on `scratch` (>= state_workspace_bytes(d) bytes, 16-byte aligned).
@@ -227,15 +263,15 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   StateWs w;
-  w.local = (float*)scratch;
-  w.gend = w.local + (int64_t)NCB * d->H * SD;
+  w.local = (bf16*)scratch;
+  w.gend = (float*)(w.local + (int64_t)NCB * d->H * SD);
   const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
   cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
   nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
   int st = check_launch();
   if (st != NHA_OK) return st;
-  nha_state_scan_kernel<<<dim3((unsigned)((SD / 4 + 255) / 256), d->N * d->H), 256, 0, cs>>>(*d, w);
+  nha_state_scan_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD / 4 + 255) / 256)), 256, 0, cs>>>(*d, w);
   return check_launch();
 }
 

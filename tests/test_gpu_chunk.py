@@ -223,3 +223,32 @@ def test_api_errors():
         chunk_nha(x[0], x[0], x[0], x[0], x[0], sg[0], sg[0])
     out = chunk_nha(x, x, x, x, x, sg, sg, window_size_left=4, window_size_right=0)
     assert len(out) == 3 and out[0].shape == (1, 8, 2, 64) and out[1].dtype == torch.float32
+
+
+def test_many_tiny_sequences_in_one_packing():
+    """More (sequence, kv head) pairs than a grid's y dimension holds (65535): 4200 sequences of 1-3 tokens with 16 kv
+    heads.  Forward and backward must run (the scans put the pairs in the grid's x dimension) and a handful of the
+    sequences are checked against the oracle."""
+    from nha_b200 import chunk_nha
+    N, H, K, M = 4200, 16, 64, 16
+    g0 = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 4, (N,), generator=g0).tolist()
+    cu = [0]
+    for L in lens:
+        cu.append(cu[-1] + L)
+    T = cu[-1]
+    d = gen.layer_inputs(7001, 1, T, H, H, K, K, M, gate_div=1.0)
+    x = flat_inputs(d, 1, T)
+    dev = 'cuda'
+    xs = {n: x[n][None].to(dev).requires_grad_(True) for n in NAMES}
+    o, ls, lg = chunk_nha(xs['q_swa'], xs['k_swa'], xs['q_gsa'], xs['k_gsa'], xs['v'], xs['s'], xs['g'],
+                          cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev), max_seqlen=3, scale=K ** -0.5,
+                          window_size_left=1, window_size_right=0, gsa_kv_shift=1)
+    o.float().sum().backward()
+    assert torch.isfinite(o.float()).all() and all(torch.isfinite(xs[n].grad.float()).all() for n in NAMES)
+    for n in (0, 1, 2099, N - 1):
+        a, b = cu[n], cu[n + 1]
+        sl = {k: x[k][a:b].double() for k in NAMES}
+        want = orc.nha_varlen(sl['q_gsa'], sl['q_swa'], sl['k_gsa'], sl['k_swa'], sl['v'], sl['s'], sl['g'], [0, b - a],
+                              K ** -0.5, 1, 1, None, None)
+        assert_close(o[0, a:b], want[0], TOL_OUT, f'o of sequence {n}')
