@@ -320,11 +320,34 @@ def bench_prefill(dev, rank, world, dist, timed):
             return nha_b200.fused_chunk_nha_prefill(q=q, k=k, v=v, rotary_q=rq, rotary_k=rk, s=ss, g=gg, window_size=W,
                                                     output_final_state=True)
         return sequence_parallel_prefill(q, k, v, rq, rk, ss, gg, W)
+    # values first (N > 1): a short sequence (the same on every rank) cut into the ranks' segments must reproduce the
+    # single-GPU op on this rank's segment and, on the last rank, its final state
+    check = None
+    if world > 1:
+        Ts = 1024 * world
+        gs = torch.Generator(device='cpu').manual_seed(4242)
+        mks = lambda *sh: torch.randn(*sh, generator=gs).bfloat16().to(dev)
+        sq, srq, sk, srk, sv = mks(1, Ts, HQ, K), mks(1, Ts, HQ, K), mks(1, Ts, H, K), mks(1, Ts, H, K), mks(1, Ts, H, K)
+        sgl = F.logsigmoid(torch.randn(1, Ts, H, M, generator=gs)) / 8
+        sgg, sss = sgl.bfloat16().to(dev), (1 - sgl.exp()).bfloat16().to(dev)
+        ref_o, (ref_hk, ref_hv) = nha_b200.fused_chunk_nha_prefill(q=sq, k=sk, v=sv, rotary_q=srq, rotary_k=srk, s=sss, g=sgg,
+                                                                   window_size=W, output_final_state=True)
+        a, b = Ts * rank // world, Ts * (rank + 1) // world
+        seg = lambda x: x[:, a:b].contiguous()
+        so, (shk, shv) = sequence_parallel_prefill(seg(sq), seg(sk), seg(sv), seg(srq), seg(srk), seg(sss), seg(sgg), W)
+        rel = lambda x, y: float((x.float() - y.float()).norm() / y.float().norm().clamp_min(1e-30))
+        e = rel(so, ref_o[:, a:b])
+        if rank == world - 1:
+            e = max(e, rel(shk, ref_hk), rel(shv, ref_hv))
+        te = torch.tensor([e], device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        check = {'tokens': Ts, 'rel_l2_vs_single_gpu_max_over_ranks': float(te.item()), 'bound': 1e-2}
     for _ in range(2):
         step()
     ms = timed(step, 30) / 30
     flops = T * 9699328.0
     return {'workload': f'prefill fwd B1 T131072 HQ32 H8 D128 M64 W512 bf16, sequence-parallel x{world}', 'ms': ms,
+            'sequence_parallel_check': check,
             'tokens_per_s': T / (ms * 1e-3), 'tflops': flops / (ms * 1e-3) / 1e12,
             'roofline': {'bound': 'tensor', 'achieved': flops / (ms * 1e-3) / 1e12 / world,
                          'peak': tensor_peak(), 'unit': 'TFLOP/s per GPU',

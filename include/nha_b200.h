@@ -200,7 +200,13 @@ typedef struct nha_chunk_desc {
   int32_t max_seqlen;           /* longest sequence (grid sizing of the state pass) */
   int32_t window_left_all;      /* used when window_left == NULL */
   int32_t shift_all;            /* used when shift == NULL */
-  int32_t seg_chunks;           /* unused (kept so the struct layout stays put); set 0 */
+  int32_t q_offset;             /* 0, or (forward only, N == 1, a multiple of 64): q_gsa, q_swa, o, lse_swa and lse_gsa hold
+                                   only the positions >= q_offset of the sequence (row i = position q_offset + i), while the
+                                   kv-head tensors hold all Ttot positions.  The state pass covers every position; the output
+                                   pass skips the chunks below q_offset.  Used by the sequence-parallel prefill, whose ranks
+                                   prepend the last window of the rank before them to their kv-head tensors only.  Honoured by
+                                   the pipelined output pass (K == V == 128, M == 64, even HQ / H); other shapes return
+                                   NHA_ERR_UNSUPPORTED */
   float scale;
 } nha_chunk_desc;
 
@@ -218,6 +224,15 @@ int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d);
 int nha_chunk_plan(const nha_chunk_desc* d, void* stream);
 /* state pass: chunk-start states hk_chunks/hv_chunks (+ final states hkt/hvt when non-NULL) */
 int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream);
+/* Adds a start state to the result of a state pass that ran from a ZERO start (hk0 == hv0 == NULL) with this
+   descriptor: the recurrence is linear, so the state at the start of chunk c is the zero-start state plus
+   S .* exp(sum of the log gates of the chunks before c).  sk [N,H,K,M], sv [N,H,M,V] fp32.  Updates hk_chunks,
+   hv_chunks (bf16, rounded again) and, when non-NULL, hkt / hvt.  Reads the per-chunk gate totals the state pass left
+   in desc->workspace, so it must follow that state pass directly (same descriptor, same stream order).  This is what
+   lets a rank of the sequence-parallel prefill run ONE state pass: it summarises its segment from a zero start, the
+   ranks exchange the summaries, and the true start state is folded in afterwards.  The reference's resumption
+   contract is initial_state (nha_fla/ops/nha/chunk_fused.py:337-342); it has no counterpart of this call. */
+int nha_chunk_apply_state_prefix(const nha_chunk_desc* d, const float* sk, const float* sv, void* stream);
 /* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
 int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
 /* device-side error word of the last output pass run with this descriptor's plan (0 = none; non-zero:

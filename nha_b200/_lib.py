@@ -32,7 +32,7 @@ class ChunkDesc(C.Structure):
         ('ds', c_void_p), ('dg', c_void_p), ('dhk0', c_void_p), ('dhv0', c_void_p),
         ('Ttot', C.c_int32), ('N', C.c_int32), ('HQ', C.c_int32), ('H', C.c_int32), ('K', C.c_int32),
         ('V', C.c_int32), ('M', C.c_int32), ('max_seqlen', C.c_int32), ('window_left_all', C.c_int32),
-        ('shift_all', C.c_int32), ('seg_chunks', C.c_int32), ('scale', C.c_float),
+        ('shift_all', C.c_int32), ('q_offset', C.c_int32), ('scale', C.c_float),
     ]
 
 
@@ -65,6 +65,7 @@ SYMBOLS = {
     'nha_chunk_plan': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_output_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
+    'nha_chunk_apply_state_prefix': (C.c_int, [C.POINTER(ChunkDesc), c_void_p, c_void_p, c_void_p]),
     'nha_chunk_fwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass_static_max_bytes': (C.c_int64, []),

@@ -39,14 +39,15 @@ def _per_seq(x: IntOrTensor, N: int, device) -> Tuple[Optional[torch.Tensor], in
 class _Geometry:
     """Sizes + device-side plan shared by the forward and the backward of one call."""
 
-    def __init__(self, q_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, seg_chunks):
-        self.Ttot, self.HQ, self.K = q_gsa.shape
+    def __init__(self, q_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, q_offset=0):
+        self.Ttot = k_gsa.shape[0]                       # q may hold fewer rows (q_offset > 0)
+        _, self.HQ, self.K = q_gsa.shape
         self.H = k_gsa.shape[1]
         self.V = v.shape[-1]
         self.M = s.shape[-1]
         self.N = cu_seqlens.numel() - 1
         self.max_seqlen = int(max_seqlen)
-        self.seg_chunks = int(seg_chunks)
+        self.q_offset = int(q_offset)
         self.device = q_gsa.device
         lib = _lib.load()
         self.ncb = int(lib.nha_chunk_count_bound(self.Ttot, self.N))
@@ -67,25 +68,27 @@ def _fill_desc(geo: _Geometry, t: dict, scale, wl_t, wl_all, sh_t, sh_all) -> _l
     d.Ttot, d.N, d.HQ, d.H, d.K, d.V, d.M = geo.Ttot, geo.N, geo.HQ, geo.H, geo.K, geo.V, geo.M
     d.max_seqlen = geo.max_seqlen
     d.window_left_all, d.shift_all = wl_all, sh_all
-    d.seg_chunks = geo.seg_chunks
+    d.q_offset = geo.q_offset
     d.scale = float(scale)
     return d
 
 
 def chunk_forward(q_gsa, q_swa, k_gsa, k_swa, v, s, g, cu_seqlens, max_seqlen, scale, window_left, shift,
-                  hk0=None, hv0=None, output_final_state=False, seg_chunks=0):
+                  hk0=None, hv0=None, output_final_state=False, q_offset=0):
     """Flat packed forward on ``[Ttot, heads, dim]`` bf16 tensors.  Returns
     ``(o, lse_swa, lse_gsa, hkt, hvt, saved)`` where ``saved`` carries what the backward needs."""
     lib = _lib.load()
-    geo = _Geometry(q_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, seg_chunks)
+    geo = _Geometry(q_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, q_offset)
     dev = geo.device
     wl_t, wl_all = _per_seq(window_left, geo.N, dev)
     sh_t, sh_all = _per_seq(shift, geo.N, dev)
     t = dict(q_gsa=q_gsa, q_swa=q_swa, k_gsa=k_gsa, k_swa=k_swa, v=v, s=s, g=g, cu_seqlens=cu_seqlens,
              hk0=hk0, hv0=hv0)
-    t['o'] = torch.empty(geo.Ttot, geo.HQ, geo.V, dtype=_BF16, device=dev)
-    t['lse_swa'] = torch.empty(geo.Ttot, geo.HQ, dtype=torch.float32, device=dev)
-    t['lse_gsa'] = torch.empty(geo.Ttot, geo.HQ, dtype=torch.float32, device=dev)
+    nq = geo.Ttot - geo.q_offset
+    assert q_gsa.shape[0] == nq and q_swa.shape[0] == nq, 'q tensors must hold the positions from q_offset on'
+    t['o'] = torch.empty(nq, geo.HQ, geo.V, dtype=_BF16, device=dev)
+    t['lse_swa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
+    t['lse_gsa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
     if output_final_state:
         t['hkt'] = torch.empty(geo.N, geo.H, geo.K, geo.M, dtype=torch.float32, device=dev)
         t['hvt'] = torch.empty(geo.N, geo.H, geo.M, geo.V, dtype=torch.float32, device=dev)
@@ -143,10 +146,10 @@ class ChunkNativeHybridAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q_swa, k_swa, q_gsa, k_gsa, v, s, g, cu_seqlens, max_seqlen, scale, window_left, shift,
-                hk0, hv0, output_final_state, seg_chunks):
+                hk0, hv0, output_final_state, q_offset):
         o, lse_swa, lse_gsa, hkt, hvt, saved = chunk_forward(
             q_gsa, q_swa, k_gsa, k_swa, v, s, g, cu_seqlens, max_seqlen, scale, window_left, shift,
-            hk0, hv0, output_final_state, seg_chunks)
+            hk0, hv0, output_final_state, q_offset)
         ctx.save_for_backward(q_swa, k_swa, q_gsa, k_gsa, v, s, g, cu_seqlens, o, lse_swa, lse_gsa,
                               saved['hk_chunks'], saved['hv_chunks'], hk0, hv0, hkt, hvt)
         ctx.saved_meta = saved
@@ -254,12 +257,12 @@ def chunk_nha(
     return o, lse_swa, lse_gsa
 
 
-def chunk_final_state(k_gsa, v, s, g, cu_seqlens, max_seqlen, shift, hk0=None, hv0=None, seg_chunks=0):
+def chunk_final_state(k_gsa, v, s, g, cu_seqlens, max_seqlen, shift, hk0=None, hv0=None):
     """State pass alone on flat packed ``[Ttot, H, dim]`` bf16 tensors: the fp32 slot memory
     ``(hkt [N,H,K,M], hvt [N,H,M,V])`` after the last token that enters it.  Used by the
     sequence-parallel prefill to summarise a rank's segment before the cross-rank scan."""
     lib = _lib.load()
-    geo = _Geometry(k_gsa, k_gsa, v, s, cu_seqlens, max_seqlen, seg_chunks)
+    geo = _Geometry(k_gsa, k_gsa, v, s, cu_seqlens, max_seqlen)
     dev = geo.device
     sh_t, sh_all = _per_seq(shift, geo.N, dev)
     t = dict(q_gsa=k_gsa, q_swa=k_gsa, k_gsa=k_gsa, k_swa=k_gsa, v=v, s=s, g=g, cu_seqlens=cu_seqlens, hk0=hk0, hv0=hv0)
@@ -276,3 +279,60 @@ def chunk_final_state(k_gsa, v, s, g, cu_seqlens, max_seqlen, shift, hk0=None, h
         _lib.check(lib.nha_chunk_plan(d, _stream(dev)), 'nha_chunk_plan')
         _lib.check(lib.nha_chunk_state_pass(d, _stream(dev)), 'nha_chunk_state_pass')
     return t['hkt'], t['hvt']
+
+
+class SegmentForward:
+    """The forward of ONE packed sequence in three separately callable steps, for the sequence-parallel prefill: a rank
+    summarises its segment with a state pass from a zero start, the ranks exchange the summaries, the rank folds its
+    true start state into the chunk-start states, and only then runs the output pass.
+
+    kv-head tensors ``k_gsa, k_swa, v, s, g`` are flat ``[Tkv, H, dim]`` bf16 and may begin with ``q_offset`` tokens
+    of the rank before (its last window); ``q_gsa, q_swa`` hold the ``Tkv - q_offset`` positions after them."""
+
+    def __init__(self, q_gsa, q_swa, k_gsa, k_swa, v, s, g, scale, window_left, shift, q_offset=0):
+        lib = _lib.load()
+        dev = k_gsa.device
+        Tkv = k_gsa.shape[0]
+        self.cu = torch.tensor([0, Tkv], dtype=torch.int32, device=dev)
+        self.geo = geo = _Geometry(q_gsa, k_gsa, v, s, self.cu, Tkv, q_offset)
+        self.scale, self.wl, self.shift = float(scale), int(window_left), int(shift)
+        nq = Tkv - geo.q_offset
+        assert q_gsa.shape[0] == nq and q_swa.shape[0] == nq
+        t = dict(q_gsa=q_gsa, q_swa=q_swa, k_gsa=k_gsa, k_swa=k_swa, v=v, s=s, g=g, cu_seqlens=self.cu)
+        t['o'] = torch.empty(nq, geo.HQ, geo.V, dtype=_BF16, device=dev)
+        t['lse_swa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
+        t['lse_gsa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
+        t['hkt'] = torch.empty(1, geo.H, geo.K, geo.M, dtype=torch.float32, device=dev)
+        t['hvt'] = torch.empty(1, geo.H, geo.M, geo.V, dtype=torch.float32, device=dev)
+        t['hk_chunks'] = torch.empty(geo.ncb, geo.H, geo.K, geo.M, dtype=_BF16, device=dev)
+        t['hv_chunks'] = torch.empty(geo.ncb, geo.H, geo.M, geo.V, dtype=_BF16, device=dev)
+        d = _fill_desc(geo, t, self.scale, None, self.wl, None, self.shift)
+        t['workspace'] = torch.empty(max(16, int(lib.nha_chunk_fwd_workspace_bytes(d))), dtype=torch.uint8, device=dev)
+        self.t = t
+        self.desc = _fill_desc(geo, t, self.scale, None, self.wl, None, self.shift)
+
+    def state_pass(self):
+        """Plan + state pass from a zero start.  Returns the zero-start end state ``(hk, hv)`` (the segment's own
+        contribution to the slot memory; these tensors are updated in place by :meth:`apply_prefix`)."""
+        lib, dev = _lib.load(), self.geo.device
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_chunk_plan(self.desc, _stream(dev)), 'nha_chunk_plan')
+            _lib.check(lib.nha_chunk_state_pass(self.desc, _stream(dev)), 'nha_chunk_state_pass')
+        return self.t['hkt'], self.t['hvt']
+
+    def apply_prefix(self, sk: torch.Tensor, sv: torch.Tensor):
+        """Fold the true start state ``sk [1,H,K,M], sv [1,H,M,V]`` (fp32) into every chunk-start state and the end state."""
+        lib, dev = _lib.load(), self.geo.device
+        sk, sv = sk.float().contiguous(), sv.float().contiguous()
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_chunk_apply_state_prefix(self.desc, sk.data_ptr(), sv.data_ptr(), _stream(dev)),
+                       'nha_chunk_apply_state_prefix')
+
+    def output_pass(self):
+        """Output pass; returns ``(o [Tq,HQ,V], lse_swa, lse_gsa, hk, hv)``."""
+        lib, dev = _lib.load(), self.geo.device
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_chunk_output_pass(self.desc, _stream(dev)), 'nha_chunk_output_pass')
+            _lib.check_chunk_device(lib, self.desc, _stream(dev), 'nha_chunk_output_pass')
+        t = self.t
+        return t['o'], t['lse_swa'], t['lse_gsa'], t['hkt'], t['hvt']

@@ -1053,6 +1053,7 @@ static int bwd_run(const nha_chunk_desc* d, int stage_mask, void* stream) {
   if ((d->d_hkt == nullptr) != (d->d_hvt == nullptr)) return NHA_ERR_BAD_ARG;
   if (d->d_hkt && (!d->hkt || !d->hvt)) return NHA_ERR_BAD_ARG;
   if (d->V % 32 || d->K % 32) return NHA_ERR_UNSUPPORTED;
+  if (d->q_offset != 0) return NHA_ERR_UNSUPPORTED;        // late-starting queries exist in the forward only
   const int64_t need = bwd_ws_layout(d, nullptr, nullptr);
   if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
   BwdWs w;

@@ -123,6 +123,8 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
   const int t0 = rc.t0;
   const int len = rc.len;
   const int c0 = ci * kChunk;
+  if (c0 < d.q_offset) return;                     // chunks below q_offset have no queries (q_offset is a multiple of 64)
+  const int tq0 = t0 - d.q_offset;                 // row of q / o / lse that holds position 0 of the sequence
   const int wl = seq_window(d, n);
   const int shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -200,7 +202,7 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
   for (int qh = 0; qh < NG; ++qh) {
     const int hq = h * NG + qh;
     // ---- slot logits ---------------------------------------------------------------------------
-    load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((size_t)t0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K,
+    load_tile_bf16(qb, ldk, (const bf16*)d.q_gsa + ((int64_t)tq0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K,
                    tid, kFwdThreads);
     __syncthreads();
     tile_gemm<true, true, false>(OK, ldg, qb, ldk, Hk, ldhk, 4, M / 16, K / 16, warp, kFwdWarps);
@@ -231,7 +233,7 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
       lg += __shfl_xor_sync(0xffffffffu, lg, 2);
     }
     // ---- window logits, sweep 1: statistics ----------------------------------------------------
-    load_tile_bf16(qb, ldk, (const bf16*)d.q_swa + ((size_t)t0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K,
+    load_tile_bf16(qb, ldk, (const bf16*)d.q_swa + ((int64_t)tq0 * HQ + hq) * K, (int64_t)HQ * K, c0, 0, len, kChunk, K,
                    tid, kFwdThreads);
     float ms = -INFINITY, ls = 0.f;
     const int pos = c0 + rq;
@@ -273,8 +275,8 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
       if (sub == 0) {
         row_L[rq] = Lj;
         if (pos < len) {
-          d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = lse_g;
-          d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = lse_s;
+          d.lse_gsa[(size_t)(tq0 + pos) * HQ + hq] = lse_g;
+          d.lse_swa[(size_t)(tq0 + pos) * HQ + hq] = lse_s;
         }
       }
     }
@@ -368,7 +370,7 @@ __device__ __forceinline__ void nha_chunk_fwd_kernel_body(const nha_chunk_desc d
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = patch[r * 16 + 8 * half + e];
-          *reinterpret_cast<uint4*>((bf16*)d.o + ((size_t)(t0 + pq) * HQ + hq) * V + 16 * ct + 8 * half) = pack8(f);
+          *reinterpret_cast<uint4*>((bf16*)d.o + ((size_t)(tq0 + pq) * HQ + hq) * V + 16 * ct + 8 * half) = pack8(f);
         }
         __syncwarp();
       }
@@ -403,6 +405,7 @@ __global__ void __launch_bounds__(kFwdThreads) nha_chunk_fwd_kernel(const nha_ch
 int64_t state_workspace_bytes(const nha_chunk_desc* d);
 int check_chunk_desc(const nha_chunk_desc* d);
 int chunk_output_pass_umma(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t cs);
+bool fwd_pipe_supported(const nha_chunk_desc* d);
 
 }  // namespace nha
 
@@ -418,6 +421,8 @@ extern "C" int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream) {
   if (st != NHA_OK) return st;
   if (!d->o || !d->lse_swa || !d->lse_gsa || !d->hk_chunks || !d->hv_chunks) return NHA_ERR_BAD_ARG;
   if (d->V % 32) return NHA_ERR_UNSUPPORTED;
+  if (d->q_offset != 0 && (d->q_offset < 0 || d->q_offset % kChunk || d->N != 1 || !fwd_pipe_supported(d)))
+    return NHA_ERR_UNSUPPORTED;                    // only the pipelined output pass knows queries that start late
   cudaStream_t cs = (cudaStream_t)stream;
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   // Shapes with a tensor-memory kernel run it first; it flags the (rare) chunks whose gates decay too

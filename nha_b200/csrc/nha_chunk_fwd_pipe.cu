@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
   const ChunkRec rc = chunk_rec(d, cg);
   if (rc.n < 0) return;
   const int n = rc.n, ci = rc.ci, t0 = rc.t0, len = rc.len, c0 = ci * kChunk;
+  if (c0 < d.q_offset) return;                     // chunks below q_offset have no queries (q_offset is a multiple of 64)
+  const int tq0 = t0 - d.q_offset;                 // row of q / o / lse that holds position 0 of the sequence
   const int wl = seq_window(d, n), shift = seq_shift(d, n);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hq0 = h * NG + 2 * blockIdx.z;
@@ -217,8 +219,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
         for (int kt = 0; kt < 2; ++kt) {
-          tma_load_3d(slot_ptr(kt) + hh * 8192, &maps.qg, 64 * kt, hq0 + hh, t0 + c0, &bar[bFull + kt]);
-          tma_load_3d(sm + oQS + kt * kQTile + hh * 8192, &maps.qs, 64 * kt, hq0 + hh, t0 + c0, &bar[bQ]);
+          tma_load_3d(slot_ptr(kt) + hh * 8192, &maps.qg, 64 * kt, hq0 + hh, tq0 + c0, &bar[bFull + kt]);
+          tma_load_3d(sm + oQS + kt * kQTile + hh * 8192, &maps.qs, 64 * kt, hq0 + hh, tq0 + c0, &bar[bQ]);
         }
     }
     load_rows(2, &maps.kg, (const bf16*)d.k_gsa, c0 - shift, 0, hi);          // k'
@@ -622,8 +624,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
     const float lsum = lgs + ls;
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
     if (in_seq) {
-      d.lse_gsa[(size_t)(t0 + pos) * HQ + hq] = mg + __logf(lg0);
-      d.lse_swa[(size_t)(t0 + pos) * HQ + hq] = mref + __logf(ls);
+      d.lse_gsa[(size_t)(tq0 + pos) * HQ + hq] = mg + __logf(lg0);
+      d.lse_swa[(size_t)(tq0 + pos) * HQ + hq] = mref + __logf(ls);
     }
     // Output rows leave through shared memory: a thread holds one whole row (256 bytes), and stores of 32 lanes to 32
     // rows 8 KB apart would cost one memory transaction per lane.  The rows are staged in the q_swa tiles (dead: every
@@ -650,7 +652,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
         const int p2 = c0 + (rr & 63);
         if (p2 < len) {
           const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((c ^ (r & 15)) << 4));
-          bf16* dst = (bf16*)d.o + ((size_t)(t0 + p2) * HQ + hq0 + (rr >> 6)) * D + 8 * c;
+          bf16* dst = (bf16*)d.o + ((size_t)(tq0 + p2) * HQ + hq0 + (rr >> 6)) * D + 8 * c;
           *reinterpret_cast<uint4*>(dst) = v;
         }
       }
@@ -678,8 +680,8 @@ int fwd_pipe_launch(const nha_chunk_desc* d, int* flags, int* err, cudaStream_t 
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   PipeMaps maps;
   memset(&maps, 0, sizeof(maps));
-  const bool ok = make_map_rows_heads(&maps.qg, d->q_gsa, d->Ttot, d->HQ, D) &&
-                  make_map_rows_heads(&maps.qs, d->q_swa, d->Ttot, d->HQ, D) &&
+  const bool ok = make_map_rows_heads(&maps.qg, d->q_gsa, d->Ttot - d->q_offset, d->HQ, D) &&
+                  make_map_rows_heads(&maps.qs, d->q_swa, d->Ttot - d->q_offset, d->HQ, D) &&
                   make_map_rows_heads(&maps.kg, d->k_gsa, d->Ttot, d->H, D) &&
                   make_map_rows_heads(&maps.ks, d->k_swa, d->Ttot, d->H, D) &&
                   make_map_rows_heads(&maps.v, d->v, d->Ttot, d->H, D) &&

@@ -275,6 +275,53 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   return check_launch();
 }
 
+// Adds S .* exp(log gates of the chunks before c) to the zero-start state at the start of every chunk c of a sequence
+// (and S .* exp(all log gates) to the final state).  Same thread layout as the scan: one thread owns four consecutive
+// state elements and walks the chunks of its (sequence, kv head) with the running decay in registers.
+__global__ void __launch_bounds__(256) nha_state_prefix_kernel(const nha_chunk_desc d, const StateWs w, const float* __restrict__ sk,
+                                                               const float* __restrict__ sv) {
+  const int K = d.K, V = d.V, M = d.M, H = d.H;
+  const int KM = K * M, MV = M * V;
+  const size_t nh = blockIdx.x;
+  const int n = nh / H, h = nh % H;
+  const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
+  const int nchunks = (len + kChunk - 1) / kChunk;
+  const int chunk0 = d.plan[n];
+  const int el = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+  if (el >= KM + MV) return;
+  const bool is_k = el < KM;
+  const int e = is_k ? el : el - KM;
+  const int m = is_k ? e % M : e / V;
+  const size_t per = is_k ? KM : MV;
+  bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
+  float4 run = *reinterpret_cast<const float4*>((is_k ? sk : sv) + nh * per + e);
+  for (int ci = 0; ci < nchunks; ++ci) {
+    const size_t cgi = (size_t)(chunk0 + ci) * H + h;
+    uint2* p = reinterpret_cast<uint2*>(out + cgi * per + e);
+    const uint2 o = *p;
+    const float2 a01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.x));
+    const float2 a23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.y));
+    uint2 r;
+    *reinterpret_cast<__nv_bfloat162*>(&r.x) = __floats2bfloat162_rn(a01.x + run.x, a01.y + run.y);
+    *reinterpret_cast<__nv_bfloat162*>(&r.y) = __floats2bfloat162_rn(a23.x + run.z, a23.y + run.w);
+    *p = r;
+    if (is_k) {
+      const float4 g4 = *(const float4*)(w.gend + cgi * M + m);
+      run.x *= __expf(g4.x); run.y *= __expf(g4.y); run.z *= __expf(g4.z); run.w *= __expf(g4.w);
+    } else {
+      const float x = __expf(w.gend[cgi * M + m]);
+      run.x *= x; run.y *= x; run.z *= x; run.w *= x;
+    }
+  }
+  float* ht = is_k ? d.hkt : d.hvt;
+  if (ht) {
+    float4* q = reinterpret_cast<float4*>(ht + nh * per + e);
+    float4 t = *q;
+    t.x += run.x; t.y += run.y; t.z += run.z; t.w += run.w;
+    *q = t;
+  }
+}
+
 int check_chunk_desc(const nha_chunk_desc* d) {
   if (!d) return NHA_ERR_BAD_ARG;
   if (!d->q_gsa || !d->q_swa || !d->k_gsa || !d->k_swa || !d->v || !d->s || !d->g || !d->cu_seqlens || !d->plan)
@@ -313,6 +360,23 @@ extern "C" int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream) {
   const int64_t need = state_workspace_bytes(d);
   if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
   return state_pass_on(d, d->workspace, (cudaStream_t)stream);
+}
+
+extern "C" int nha_chunk_apply_state_prefix(const nha_chunk_desc* d, const float* sk, const float* sv, void* stream) {
+  int st = check_chunk_desc(d);
+  if (st != NHA_OK) return st;
+  if (!d->hk_chunks || !d->hv_chunks || !sk || !sv) return NHA_ERR_BAD_ARG;
+  if (d->hk0 || d->hv0) return NHA_ERR_BAD_ARG;            // the state pass must have run from a zero start
+  const int64_t need = state_workspace_bytes(d);
+  if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  StateWs w;
+  w.local = (bf16*)d->workspace;
+  w.gend = (float*)(w.local + (int64_t)NCB * d->H * SD);
+  nha_state_prefix_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD / 4 + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
+      *d, w, sk, sv);
+  return check_launch();
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -21,30 +21,96 @@ Two modes, following how the operator shards:
   ``initial_state`` resumption, nha_fla/ops/nha/chunk_fused.py:337-342); the single-device op is the
   oracle for this function.
 
-The arithmetic is injected (``local_state`` / ``forward``) so the host logic can be exercised on CPU
-ranks with the ``gloo`` backend; the defaults are the CUDA ops of this package.
+The arithmetic sits behind an ``engine`` (``summary`` / ``finish``) so the host logic can be exercised on CPU ranks
+with the ``gloo`` backend; the default engine runs the CUDA ops of this package: ONE state pass per rank from a zero
+start (it yields the chunk-start states and the segment summary together), the true start state folded into the
+chunk-start states afterwards (``nha_chunk_apply_state_prefix``), and an output pass whose query tensors are NOT
+extended by the halo (``q_offset``: only the kv-head tensors, a quarter of the bytes, are concatenated with it).
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
-
-def _cuda_local_state(k, v, s, g, W):
-    from .chunk import chunk_final_state
-    B, T = k.shape[0], k.shape[1]
-    flat = lambda x: x.reshape(B * T, *x.shape[2:]).to(torch.bfloat16).contiguous()
-    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=k.device)
-    return chunk_final_state(flat(k), flat(v), flat(s), flat(g), cu, T, W)
+_BF16 = torch.bfloat16
 
 
-def _cuda_forward(q, k, v, rq, rk, s, g, W, scale, state):
-    from .chunk_fused import fused_chunk_nha_prefill
-    o, (hk, hv) = fused_chunk_nha_prefill(q=q, k=k, v=v, rotary_q=rq, rotary_k=rk, s=s, g=g, window_size=W,
-                                          initial_state=state, output_final_state=True, scale=scale)
-    return o, hk, hv
+class CudaEngine:
+    """Default arithmetic of :func:`sequence_parallel_prefill` on this rank's GPU."""
+
+    def __init__(self, q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset):
+        from .chunk import SegmentForward
+        self.args = (q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
+        B = k_e.shape[0]
+        K, V, M = k_e.shape[-1], v_e.shape[-1], s_e.shape[-1]
+        NG = q.shape[2] // k_e.shape[2]
+        # the three-step path needs the pipelined output pass (it alone knows late-starting queries)
+        self.steps = None
+        if B == 1 and K == 128 and V == 128 and M == 64 and NG % 2 == 0 and q_offset % 64 == 0:
+            f = lambda x: x[0].to(_BF16).contiguous()
+            self.steps = SegmentForward(f(q), f(rq), f(k_e), f(rk_e), f(v_e), f(s_e), f(g_e), scale, W - 1, W, q_offset)
+
+    def summary(self):
+        """Zero-start end state of the (halo-extended) segment: ``(Lk [B,H,K,M], Lv [B,H,M,V])`` fp32."""
+        if self.steps is not None:
+            return self.steps.state_pass()
+        from .chunk import chunk_final_state
+        q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.args
+        B, T = k_e.shape[0], k_e.shape[1]
+        flat = lambda x: x.reshape(B * T, *x.shape[2:]).to(_BF16).contiguous()
+        cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=k_e.device)
+        return chunk_final_state(flat(k_e), flat(v_e), flat(s_e), flat(g_e), cu, T, W)
+
+    def finish(self, Sk, Sv):
+        """Outputs of the rank's own tokens and the slot memory at the end of its segment, from the start state."""
+        q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.args
+        if self.steps is not None:
+            self.steps.apply_prefix(Sk, Sv)
+            o, _, _, hk, hv = self.steps.output_pass()
+            return o[None].to(q.dtype), hk, hv
+        from .chunk_fused import fused_chunk_nha_prefill
+        if q_offset:
+            zq = q.new_zeros(q.shape[0], q_offset, *q.shape[2:])
+            q, rq = torch.cat([zq, q], 1), torch.cat([zq, rq], 1)
+        o, (hk, hv) = fused_chunk_nha_prefill(q=q, k=k_e, v=v_e, rotary_q=rq, rotary_k=rk_e, s=s_e, g=g_e, window_size=W,
+                                              initial_state=(Sk, Sv), output_final_state=True, scale=scale)
+        return o[:, q_offset:], hk, hv
+
+
+def segment_summary(eng, g_e: torch.Tensor, W: int):
+    """One rank's message to the others: its zero-start end state and the total log decay of the tokens that enter
+    its slot memory (all of the halo-extended segment but its last ``W``; summed from the gates as the kernels see
+    them, rounded to bf16), packed as ``[B, H*K*M + H*M*V + H*M]`` fp32.  Also returns ``(H, K, M, V)``."""
+    Lk, Lv = eng.summary()
+    B = g_e.shape[0]
+    G = g_e[:, :g_e.shape[1] - W].to(_BF16).float().sum(1)                # [B,H,M]
+    dims = (Lk.shape[1], Lk.shape[2], Lk.shape[3], Lv.shape[3])
+    pack = torch.cat([Lk.reshape(B, -1).float(), Lv.reshape(B, -1).float(), G.reshape(B, -1)], 1).contiguous()
+    return pack, dims
+
+
+def fold_start_state(allp: torch.Tensor, rank: int, dims, initial_state=None):
+    """Start state of rank ``rank`` from the summaries ``allp [world, B, P]`` of all ranks: the recurrence is linear, so
+    ``S_start = S_0 * exp(sum_{r<rank} G_r) + sum_{r<rank} L_r * exp(sum_{r<r'<rank} G_r')`` - a fixed number of
+    tensor operations whatever the rank."""
+    H, K, M, V = dims
+    B, dev = allp.shape[1], allp.device
+    nk, nv = H * K * M, H * M * V
+    if initial_state is not None and initial_state != (None, None):
+        Sk, Sv = initial_state[0].float(), initial_state[1].float()
+    else:
+        Sk = torch.zeros(B, H, K, M, dtype=torch.float32, device=dev)
+        Sv = torch.zeros(B, H, M, V, dtype=torch.float32, device=dev)
+    if rank > 0:
+        before = allp[:rank]
+        Gs = before[:, :, nk + nv:].reshape(rank, B, H, M)
+        wgt = (Gs.flip(0).cumsum(0).flip(0) - Gs).exp()                   # decay through the ranks between r and this one
+        tot = Gs.sum(0).exp()
+        Sk = Sk * tot[:, :, None, :] + (before[:, :, :nk].reshape(rank, B, H, K, M) * wgt[:, :, :, None, :]).sum(0)
+        Sv = Sv * tot[:, :, :, None] + (before[:, :, nk:nk + nv].reshape(rank, B, H, M, V) * wgt[..., None]).sum(0)
+    return Sk, Sv
 
 
 def sequence_parallel_prefill(
@@ -53,8 +119,7 @@ def sequence_parallel_prefill(
     initial_state: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
     scale: Optional[float] = None,
     group: Optional[dist.ProcessGroup] = None,
-    local_state: Callable = _cuda_local_state,
-    forward: Callable = _cuda_forward,
+    engine=CudaEngine,
 ):
     """``fused_chunk_nha_prefill`` over a sequence sharded along tokens.
 
@@ -76,50 +141,31 @@ def sequence_parallel_prefill(
     send = [x[:, Tr - W:].contiguous() for x in (k, rotary_k, v, s, g)]
     recv = [torch.empty_like(x) for x in send]
     ops = []
+    peer = lambda r: dist.get_global_rank(group, r) if group else r
     if rank + 1 < world:
-        ops += [dist.P2POp(dist.isend, x, dist.get_global_rank(group, rank + 1) if group else rank + 1, group) for x in send]
+        ops += [dist.P2POp(dist.isend, x, peer(rank + 1), group) for x in send]
     if rank > 0:
-        ops += [dist.P2POp(dist.irecv, x, dist.get_global_rank(group, rank - 1) if group else rank - 1, group) for x in recv]
+        ops += [dist.P2POp(dist.irecv, x, peer(rank - 1), group) for x in recv]
     if ops:
         for w in dist.batch_isend_irecv(ops):
             w.wait()
+    q_offset = W if rank > 0 else 0
     if rank > 0:
         hk_, hrk, hv_, hs, hg = recv
-        zq = q.new_zeros(B, W, *q.shape[2:])
-        q_e, rq_e = torch.cat([zq, q], 1), torch.cat([zq, rotary_q], 1)
         k_e, rk_e = torch.cat([hk_, k], 1), torch.cat([hrk, rotary_k], 1)
         v_e, s_e, g_e = torch.cat([hv_, v], 1), torch.cat([hs, s], 1), torch.cat([hg, g], 1)
     else:
-        q_e, rq_e, k_e, rk_e, v_e, s_e, g_e = q, rotary_q, k, rotary_k, v, s, g
+        k_e, rk_e, v_e, s_e, g_e = k, rotary_k, v, s, g
 
     # ---- 2. segment summary from a zero start --------------------------------------------------------------
-    # tokens entering the slot memory during this rank's steps: all of the extended segment but its last W
-    n_enter = k_e.shape[1] - W
-    Lk, Lv = local_state(k_e, v_e, s_e, g_e, W)
-    G = g_e[:, :n_enter].float().sum(1)                                   # [B,H,M] total log decay
+    eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
+    pack, dims = segment_summary(eng, g_e, W)
 
     # ---- 3. all-gather of the summaries, fold the ranks before this one ------------------------------------------
-    pack = torch.cat([Lk.reshape(B, -1).float(), Lv.reshape(B, -1).float(), G.reshape(B, -1)], 1).contiguous()
-    allp = [torch.empty_like(pack) for _ in range(world)]
-    dist.all_gather(allp, pack, group=group)
-    H, K, M = Lk.shape[1], Lk.shape[2], Lk.shape[3]
-    V = Lv.shape[3]
-    nk, nv = H * K * M, H * M * V
-    if initial_state is not None and initial_state != (None, None):
-        Sk, Sv = initial_state[0].float().clone(), initial_state[1].float().clone()
-    else:
-        Sk = torch.zeros(B, H, K, M, dtype=torch.float32, device=dev)
-        Sv = torch.zeros(B, H, M, V, dtype=torch.float32, device=dev)
-    for r in range(rank):
-        pr = allp[r]
-        lk = pr[:, :nk].reshape(B, H, K, M)
-        lv = pr[:, nk:nk + nv].reshape(B, H, M, V)
-        dec = pr[:, nk + nv:].reshape(B, H, M).exp()
-        Sk = Sk * dec[:, :, None, :] + lk
-        Sv = Sv * dec[:, :, :, None] + lv
+    allp = torch.empty(world * B, pack.shape[1], dtype=pack.dtype, device=dev)
+    dist.all_gather_into_tensor(allp, pack, group=group)
+    Sk, Sv = fold_start_state(allp.view(world, B, -1), rank, dims, initial_state)
 
-    # ---- 4. forward from the true start state -----------------------------------------------------------------------
-    o, hk, hv = forward(q_e, k_e, v_e, rq_e, rk_e, s_e, g_e, W, scale, (Sk, Sv))
-    if rank > 0:
-        o = o[:, W:]
+    # ---- 4. outputs of the rank's own tokens from its true start state -----------------------------------------------
+    o, hk, hv = eng.finish(Sk, Sv)
     return o, (hk, hv)

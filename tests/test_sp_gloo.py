@@ -12,16 +12,23 @@ from oracle import nha_oracle as orc
 from tests import inputs as gen
 
 
-def _oracle_local_state(k, v, s, g, W):
-    B = k.shape[0]
-    z = torch.zeros(B, k.shape[1], k.shape[2], k.shape[3])
-    _, hk, hv = orc.prefill(z, k, v, z, k, s, g, W, 1.0)
-    return hk.float(), hv.float()
+class OracleEngine:
+    """CPU stand-in for the CUDA arithmetic of the sequence-parallel prefill (same two calls)."""
 
+    def __init__(self, q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset):
+        self.a = (q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
 
-def _oracle_forward(q, k, v, rq, rk, s, g, W, scale, state):
-    o, hk, hv = orc.prefill(q, k, v, rq, rk, s, g, W, scale, state[0], state[1])
-    return o.float(), hk.float(), hv.float()
+    def summary(self):
+        q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.a
+        z = torch.zeros(k_e.shape[0], k_e.shape[1], k_e.shape[2], k_e.shape[3])
+        _, hk, hv = orc.prefill(z, k_e, v_e, z, k_e, s_e, g_e, W, 1.0)
+        return hk.float(), hv.float()
+
+    def finish(self, Sk, Sv):
+        q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.a
+        zq = torch.zeros(q.shape[0], q_offset, *q.shape[2:])
+        o, hk, hv = orc.prefill(torch.cat([zq, q], 1), k_e, v_e, torch.cat([zq, rq], 1), rk_e, s_e, g_e, W, scale, Sk, Sv)
+        return o[:, q_offset:].float(), hk.float(), hv.float()
 
 
 def _worker(rank, world, port, T, W, with_state, out):
@@ -38,8 +45,7 @@ def _worker(rank, world, port, T, W, with_state, out):
         st = (d['hk0'], d['hv0']) if with_state else None
         o, (hk, hv) = sequence_parallel_prefill(seg(d['q']), seg(d['k']), seg(d['v']), seg(d['rotary_q']),
                                                 seg(d['rotary_k']), seg(d['s']), seg(d['g']), W, initial_state=st,
-                                                scale=d['scale'], local_state=_oracle_local_state,
-                                                forward=_oracle_forward)
+                                                scale=d['scale'], engine=OracleEngine)
         ref_o, ref_hk, ref_hv = orc.prefill(d['q'], d['k'], d['v'], d['rotary_q'], d['rotary_k'], d['s'], d['g'], W,
                                             d['scale'], d.get('hk0'), d.get('hv0'))
         err = orc.rel_l2(o, ref_o[:, a:b])
