@@ -233,6 +233,17 @@ int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream);
    ranks exchange the summaries, and the true start state is folded in afterwards.  The reference's resumption
    contract is initial_state (nha_fla/ops/nha/chunk_fused.py:337-342); it has no counterpart of this call. */
 int nha_chunk_apply_state_prefix(const nha_chunk_desc* d, const float* sk, const float* sv, void* stream);
+/* *out = device pointer (inside desc->workspace) of the log gates of every sequence summed over its chunks,
+   [N, H, M] fp32, as left by the last state pass run with this descriptor: the total decay of the tokens that entered
+   the slot memory, the second half of a segment's summary in the sequence-parallel prefill. */
+int nha_chunk_gate_totals(const nha_chunk_desc* d, const float** out);
+/* Start state of rank `rank` of a sequence-parallel prefill of ONE sequence from the all-gathered summaries
+   allp [world][H*K*M + H*M*V + H*M] fp32 (zero-start end states L_k [H,K,M], L_v [H,M,V] and log gate totals G [H,M] of
+   every rank's segment):  S = S0 .* exp(sum_{r<rank} G_r) + sum_{r<rank} L_r .* exp(sum_{r<r'<rank} G_r').
+   hk0 / hv0: start state of the whole sequence or NULL (both).  One launch.  No counterpart in the reference, which has
+   no distributed code. */
+int nha_sp_fold_start_state(const float* allp, int world, int rank, int H, int K, int M, int V, const float* hk0,
+                            const float* hv0, float* sk, float* sv, void* stream);
 /* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
 int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
 /* device-side error word of the last output pass run with this descriptor's plan (0 = none; non-zero:

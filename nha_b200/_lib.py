@@ -66,6 +66,8 @@ SYMBOLS = {
     'nha_chunk_state_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_output_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_apply_state_prefix': (C.c_int, [C.POINTER(ChunkDesc), c_void_p, c_void_p, c_void_p]),
+    'nha_chunk_gate_totals': (C.c_int, [C.POINTER(ChunkDesc), C.POINTER(c_void_p)]),
+    'nha_sp_fold_start_state': (C.c_int, [c_void_p] + [C.c_int] * 6 + [c_void_p] * 5),
     'nha_chunk_fwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass_static_max_bytes': (C.c_int64, []),

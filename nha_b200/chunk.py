@@ -298,27 +298,53 @@ class SegmentForward:
         self.scale, self.wl, self.shift = float(scale), int(window_left), int(shift)
         nq = Tkv - geo.q_offset
         assert q_gsa.shape[0] == nq and q_swa.shape[0] == nq
+        H, K, M, V = geo.H, geo.K, geo.M, geo.V
+        self.nk, self.nv = H * K * M, H * M * V
+        # the segment's message to the other ranks, [L_k | L_v | G]: the state pass writes its end state straight into it
+        self.pack = torch.empty(1, self.nk + self.nv + H * M, dtype=torch.float32, device=dev)
         t = dict(q_gsa=q_gsa, q_swa=q_swa, k_gsa=k_gsa, k_swa=k_swa, v=v, s=s, g=g, cu_seqlens=self.cu)
-        t['o'] = torch.empty(nq, geo.HQ, geo.V, dtype=_BF16, device=dev)
+        t['o'] = torch.empty(nq, geo.HQ, V, dtype=_BF16, device=dev)
         t['lse_swa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
         t['lse_gsa'] = torch.empty(nq, geo.HQ, dtype=torch.float32, device=dev)
-        t['hkt'] = torch.empty(1, geo.H, geo.K, geo.M, dtype=torch.float32, device=dev)
-        t['hvt'] = torch.empty(1, geo.H, geo.M, geo.V, dtype=torch.float32, device=dev)
-        t['hk_chunks'] = torch.empty(geo.ncb, geo.H, geo.K, geo.M, dtype=_BF16, device=dev)
-        t['hv_chunks'] = torch.empty(geo.ncb, geo.H, geo.M, geo.V, dtype=_BF16, device=dev)
+        t['hkt'] = self.pack[0, :self.nk].view(1, H, K, M)
+        t['hvt'] = self.pack[0, self.nk:self.nk + self.nv].view(1, H, M, V)
+        t['hk_chunks'] = torch.empty(geo.ncb, H, K, M, dtype=_BF16, device=dev)
+        t['hv_chunks'] = torch.empty(geo.ncb, H, M, V, dtype=_BF16, device=dev)
         d = _fill_desc(geo, t, self.scale, None, self.wl, None, self.shift)
         t['workspace'] = torch.empty(max(16, int(lib.nha_chunk_fwd_workspace_bytes(d))), dtype=torch.uint8, device=dev)
-        self.t = t
-        self.desc = _fill_desc(geo, t, self.scale, None, self.wl, None, self.shift)
+        d.workspace = t['workspace'].data_ptr()
+        d.workspace_bytes = t['workspace'].numel()
+        self.t, self.desc = t, d
 
-    def state_pass(self):
-        """Plan + state pass from a zero start.  Returns the zero-start end state ``(hk, hv)`` (the segment's own
-        contribution to the slot memory; these tensors are updated in place by :meth:`apply_prefix`)."""
+    def summary(self):
+        """Plan + state pass from a zero start.  Returns the segment's message ``[1, H*K*M + H*M*V + H*M]`` fp32: its
+        zero-start end state and the total log decay of the tokens that entered the slot memory."""
+        import ctypes
         lib, dev = _lib.load(), self.geo.device
         with torch.cuda.device(dev):
             _lib.check(lib.nha_chunk_plan(self.desc, _stream(dev)), 'nha_chunk_plan')
             _lib.check(lib.nha_chunk_state_pass(self.desc, _stream(dev)), 'nha_chunk_state_pass')
-        return self.t['hkt'], self.t['hvt']
+        ptr = ctypes.c_void_p()
+        _lib.check(lib.nha_chunk_gate_totals(self.desc, ctypes.byref(ptr)), 'nha_chunk_gate_totals')
+        off = ptr.value - self.t['workspace'].data_ptr()
+        hm = self.geo.H * self.geo.M
+        self.pack[0, self.nk + self.nv:].copy_(self.t['workspace'][off:off + 4 * hm].view(torch.float32))
+        return self.pack
+
+    def fold(self, allp: torch.Tensor, rank: int, initial_state=None):
+        """Start state of rank ``rank`` from the all-gathered messages ``allp [world, P]`` (one launch)."""
+        lib, dev, g = _lib.load(), self.geo.device, self.geo
+        sk = torch.empty(1, g.H, g.K, g.M, dtype=torch.float32, device=dev)
+        sv = torch.empty(1, g.H, g.M, g.V, dtype=torch.float32, device=dev)
+        hk0 = hv0 = None
+        if initial_state is not None and initial_state != (None, None):
+            hk0, hv0 = initial_state[0].float().contiguous(), initial_state[1].float().contiguous()
+        allp = allp.contiguous()
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_sp_fold_start_state(allp.data_ptr(), allp.shape[0], rank, g.H, g.K, g.M, g.V, _lib.ptr(hk0),
+                                                   _lib.ptr(hv0), sk.data_ptr(), sv.data_ptr(), _stream(dev)),
+                       'nha_sp_fold_start_state')
+        return sk, sv
 
     def apply_prefix(self, sk: torch.Tensor, sv: torch.Tensor):
         """Fold the true start state ``sk [1,H,K,M], sv [1,H,M,V]`` (fp32) into every chunk-start state and the end state."""

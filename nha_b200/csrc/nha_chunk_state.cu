@@ -56,10 +56,12 @@ __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restr
 
 // ---------------------------------------------------------------------------------------------
 // Scratch of the state pass: L [NCB*H][K*M + M*V] bf16 (the chunk-start states it is summed into are bf16 too; the
-// running sum itself stays fp32), then Gend [NCB*H][M] fp32.
+// running sum itself stays fp32), then Gend [NCB*H][M] fp32, then Gtot [N*H][M] fp32 (the log gates of each sequence
+// summed over its chunks, left by the scan for nha_chunk_gate_totals).
 struct StateWs {
   bf16* local;
   float* gend;
+  float* gtot;
 };
 
 // C[Mt*16 x Nt*16] = A^T B as tile_gemm<false, true, false>, with the fp32 accumulator tiles rounded to bf16 on their way
@@ -211,6 +213,8 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
   const size_t per = is_k ? KM : MV;
   bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
   float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 gsum = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool sums = is_k && e < M;                  // the threads of hk's first row also total the log gates
   {
     const float* h0 = is_k ? d.hk0 : d.hv0;
     if (h0) run = *reinterpret_cast<const float4*>(h0 + nh * per + e);
@@ -240,6 +244,7 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
         float4 a;
         if (is_k) a = make_float4(__expf(da[u].x), __expf(da[u].y), __expf(da[u].z), __expf(da[u].w));
         else { const float x = __expf(da[u].x); a = make_float4(x, x, x, x); }
+        if (sums) { gsum.x += da[u].x; gsum.y += da[u].y; gsum.z += da[u].z; gsum.w += da[u].w; }
         const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].x));
         const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].y));
         run.x = run.x * a.x + l01.x; run.y = run.y * a.y + l01.y;
@@ -249,12 +254,21 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
   }
   float* ht = is_k ? d.hkt : d.hvt;
   if (ht) *reinterpret_cast<float4*>(ht + nh * per + e) = run;
+  if (sums) *reinterpret_cast<float4*>(w.gtot + nh * M + m) = gsum;
 }
 
 int64_t state_workspace_bytes(const nha_chunk_desc* d) {
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   const int64_t rows = nha_chunk_count_bound(d->Ttot, d->N) * d->H;
-  return rows * (SD * 2 + d->M * 4) + 256;
+  return rows * (SD * 2 + d->M * 4) + (int64_t)d->N * d->H * d->M * 4 + 256;
+}
+
+static void state_ws_layout(const nha_chunk_desc* d, void* scratch, StateWs* w) {
+  const int64_t NCB = nha_chunk_count_bound(d->Ttot, d->N);
+  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  w->local = (bf16*)scratch;
+  w->gend = (float*)(w->local + NCB * d->H * SD);
+  w->gtot = w->gend + NCB * d->H * d->M;
 }
 
 // Both launches of the state pass on `scratch` (>= state_workspace_bytes(d) bytes, 16-byte aligned).
@@ -263,8 +277,7 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   StateWs w;
-  w.local = (bf16*)scratch;
-  w.gend = (float*)(w.local + (int64_t)NCB * d->H * SD);
+  state_ws_layout(d, scratch, &w);
   const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
   cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
   if (e != cudaSuccess) return record_cuda_error(e);
@@ -275,51 +288,98 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   return check_launch();
 }
 
-// Adds S .* exp(log gates of the chunks before c) to the zero-start state at the start of every chunk c of a sequence
-// (and S .* exp(all log gates) to the final state).  Same thread layout as the scan: one thread owns four consecutive
-// state elements and walks the chunks of its (sequence, kv head) with the running decay in registers.
-__global__ void __launch_bounds__(256) nha_state_prefix_kernel(const nha_chunk_desc d, const StateWs w, const float* __restrict__ sk,
-                                                               const float* __restrict__ sv) {
-  const int K = d.K, V = d.V, M = d.M, H = d.H;
-  const int KM = K * M, MV = M * V;
-  const size_t nh = blockIdx.x;
-  const int n = nh / H, h = nh % H;
+// Start state folded into the zero-start chunk states, in two chunk-parallel steps.
+// 1. exclusive prefix sums of the per-chunk log gates over the chunks of each sequence: one warp per (sequence, kv head,
+//    slot); a lane sums a contiguous run of chunks, the lanes' totals are scanned with shuffles.  cum [NCB*H][M] fp32
+//    lives where the per-chunk terms L were (dead once the scan has consumed them).
+__global__ void __launch_bounds__(256) nha_state_gate_prefix_kernel(const nha_chunk_desc d, const StateWs w, float* __restrict__ cum) {
+  const int M = d.M, H = d.H;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= d.N * H * M) return;
+  const int m = gw % M, h = (gw / M) % H, n = gw / (M * H);
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int chunk0 = d.plan[n];
-  const int el = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
-  if (el >= KM + MV) return;
-  const bool is_k = el < KM;
-  const int e = is_k ? el : el - KM;
-  const int m = is_k ? e % M : e / V;
-  const size_t per = is_k ? KM : MV;
-  bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
-  float4 run = *reinterpret_cast<const float4*>((is_k ? sk : sv) + nh * per + e);
-  for (int ci = 0; ci < nchunks; ++ci) {
-    const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-    uint2* p = reinterpret_cast<uint2*>(out + cgi * per + e);
-    const uint2 o = *p;
-    const float2 a01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.x));
-    const float2 a23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o.y));
-    uint2 r;
-    *reinterpret_cast<__nv_bfloat162*>(&r.x) = __floats2bfloat162_rn(a01.x + run.x, a01.y + run.y);
-    *reinterpret_cast<__nv_bfloat162*>(&r.y) = __floats2bfloat162_rn(a23.x + run.z, a23.y + run.w);
-    *p = r;
-    if (is_k) {
-      const float4 g4 = *(const float4*)(w.gend + cgi * M + m);
-      run.x *= __expf(g4.x); run.y *= __expf(g4.y); run.z *= __expf(g4.z); run.w *= __expf(g4.w);
-    } else {
-      const float x = __expf(w.gend[cgi * M + m]);
-      run.x *= x; run.y *= x; run.z *= x; run.w *= x;
+  const int per = (nchunks + 31) / 32;
+  const int c_lo = min(nchunks, lane * per), c_hi = min(nchunks, c_lo + per);
+  float tot = 0.f;
+  for (int c = c_lo; c < c_hi; ++c) tot += w.gend[((size_t)(chunk0 + c) * H + h) * M + m];
+  float incl = tot;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  float run = incl - tot;
+  for (int c = c_lo; c < c_hi; ++c) {
+    const size_t i = ((size_t)(chunk0 + c) * H + h) * M + m;
+    cum[i] = run;
+    run += w.gend[i];
+  }
+}
+// 2. chunk start states += S .* exp(cum): one CTA per (chunk, kv head), 16-byte accesses; the CTAs of a sequence's
+//    first chunk also add S .* exp(total) to the final state.
+__global__ void __launch_bounds__(256) nha_state_prefix_add_kernel(const nha_chunk_desc d, const StateWs w, const float* __restrict__ cum,
+                                                                   const float* __restrict__ sk, const float* __restrict__ sv) {
+  const int K = d.K, V = d.V, M = d.M, H = d.H;
+  const int KM = K * M, MV = M * V;
+  const int cg = blockIdx.x, h = blockIdx.y;
+  const ChunkRec rc = chunk_rec(d, cg);
+  if (rc.n < 0) return;
+  const size_t nh = (size_t)rc.n * H + h, cgi = (size_t)cg * H + h;
+  __shared__ float dec[128], dtot[128];
+  for (int m = threadIdx.x; m < M; m += blockDim.x) {
+    dec[m] = __expf(cum[cgi * M + m]);
+    dtot[m] = __expf(w.gtot[nh * M + m]);
+  }
+  __syncthreads();
+  const bool last = rc.ci == 0;                     // one CTA per (sequence, kv head) updates the final state
+  for (int el = 8 * threadIdx.x; el < KM + MV; el += 8 * blockDim.x) {
+    const bool is_k = el < KM;
+    const int e = is_k ? el : el - KM;
+    const size_t per = is_k ? KM : MV;
+    const float* S = (is_k ? sk : sv) + nh * per + e;
+    const float4 s0 = *reinterpret_cast<const float4*>(S), s1 = *reinterpret_cast<const float4*>(S + 4);
+    const float sv8[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    bf16* out = (is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks) + cgi * per + e;
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(out), f);
+    const int m0 = is_k ? e % M : e / V;            // hk: eight consecutive slots; hv: one slot for all eight
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] += sv8[i] * dec[is_k ? m0 + i : m0];
+    *reinterpret_cast<uint4*>(out) = pack8(f);
+    float* ht = is_k ? d.hkt : d.hvt;
+    if (last && ht) {
+      float4* q = reinterpret_cast<float4*>(ht + nh * per + e);
+      float4 t0 = q[0], t1 = q[1];
+      t0.x += sv8[0] * dtot[is_k ? m0 : m0]; t0.y += sv8[1] * dtot[is_k ? m0 + 1 : m0];
+      t0.z += sv8[2] * dtot[is_k ? m0 + 2 : m0]; t0.w += sv8[3] * dtot[is_k ? m0 + 3 : m0];
+      t1.x += sv8[4] * dtot[is_k ? m0 + 4 : m0]; t1.y += sv8[5] * dtot[is_k ? m0 + 5 : m0];
+      t1.z += sv8[6] * dtot[is_k ? m0 + 6 : m0]; t1.w += sv8[7] * dtot[is_k ? m0 + 7 : m0];
+      q[0] = t0; q[1] = t1;
     }
   }
-  float* ht = is_k ? d.hkt : d.hvt;
-  if (ht) {
-    float4* q = reinterpret_cast<float4*>(ht + nh * per + e);
-    float4 t = *q;
-    t.x += run.x; t.y += run.y; t.z += run.z; t.w += run.w;
-    *q = t;
+}
+
+// Start state of rank `rank` of a sequence-parallel prefill from the summaries of all ranks (allp [world][P] fp32 with
+// P = H*K*M + H*M*V + H*M: zero-start end states L_k, L_v and the log gate totals G of each rank's segment):
+//   S = S0 .* exp(sum_{r<rank} G_r) + sum_{r<rank} L_r .* exp(sum_{r<r'<rank} G_r'),   marched over r in order.
+__global__ void __launch_bounds__(256) nha_sp_fold_kernel(const float* __restrict__ allp, int rank, int H, int K, int M, int V,
+                                                          const float* __restrict__ hk0, const float* __restrict__ hv0,
+                                                          float* __restrict__ sk, float* __restrict__ sv) {
+  const int nk = H * K * M, nv = H * M * V, P = nk + nv + H * M;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nk + nv) return;
+  const bool is_k = i < nk;
+  const int e = is_k ? i : i - nk;
+  const int h = is_k ? e / (K * M) : e / (M * V);
+  const int m = is_k ? e % M : (e / V) % M;
+  float run = is_k ? (hk0 ? hk0[e] : 0.f) : (hv0 ? hv0[e] : 0.f);
+  for (int r = 0; r < rank; ++r) {
+    const float* p = allp + (size_t)r * P;
+    run = run * __expf(p[nk + nv + h * M + m]) + p[i];
   }
+  (is_k ? sk : sv)[e] = run;
 }
 
 int check_chunk_desc(const nha_chunk_desc* d) {
@@ -367,15 +427,38 @@ extern "C" int nha_chunk_apply_state_prefix(const nha_chunk_desc* d, const float
   if (st != NHA_OK) return st;
   if (!d->hk_chunks || !d->hv_chunks || !sk || !sv) return NHA_ERR_BAD_ARG;
   if (d->hk0 || d->hv0) return NHA_ERR_BAD_ARG;            // the state pass must have run from a zero start
+  if (d->K % 8 || d->V % 8 || d->M % 8) return NHA_ERR_UNSUPPORTED;
   const int64_t need = state_workspace_bytes(d);
   if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   StateWs w;
-  w.local = (bf16*)d->workspace;
-  w.gend = (float*)(w.local + (int64_t)NCB * d->H * SD);
-  nha_state_prefix_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD / 4 + 255) / 256)), 256, 0, (cudaStream_t)stream>>>(
-      *d, w, sk, sv);
+  state_ws_layout(d, d->workspace, &w);
+  float* cum = (float*)w.local;                             // the per-chunk terms are dead: [NCB*H][M] floats fit easily
+  cudaStream_t cs = (cudaStream_t)stream;
+  const int warps = d->N * d->H * d->M;
+  nha_state_gate_prefix_kernel<<<(warps * 32 + 255) / 256, 256, 0, cs>>>(*d, w, cum);
+  st = check_launch();
+  if (st != NHA_OK) return st;
+  nha_state_prefix_add_kernel<<<dim3(NCB, d->H), 256, 0, cs>>>(*d, w, cum, sk, sv);
+  return check_launch();
+}
+
+extern "C" int nha_chunk_gate_totals(const nha_chunk_desc* d, const float** out) {
+  if (!d || !out || !d->workspace) return NHA_ERR_BAD_ARG;
+  if ((int64_t)d->workspace_bytes < state_workspace_bytes(d)) return NHA_ERR_WORKSPACE;
+  StateWs w;
+  state_ws_layout(d, d->workspace, &w);
+  *out = w.gtot;
+  return NHA_OK;
+}
+
+extern "C" int nha_sp_fold_start_state(const float* allp, int world, int rank, int H, int K, int M, int V, const float* hk0,
+                                       const float* hv0, float* sk, float* sv, void* stream) {
+  if (!allp || !sk || !sv || world <= 0 || rank < 0 || rank >= world || H <= 0 || K <= 0 || M <= 0 || V <= 0)
+    return NHA_ERR_BAD_ARG;
+  if ((hk0 == nullptr) != (hv0 == nullptr)) return NHA_ERR_BAD_ARG;
+  const int n = H * K * M + H * M * V;
+  nha_sp_fold_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(allp, rank, H, K, M, V, hk0, hv0, sk, sv);
   return check_launch();
 }
 

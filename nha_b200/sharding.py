@@ -38,7 +38,8 @@ _BF16 = torch.bfloat16
 
 
 class CudaEngine:
-    """Default arithmetic of :func:`sequence_parallel_prefill` on this rank's GPU."""
+    """Default arithmetic of :func:`sequence_parallel_prefill` on this rank's GPU: ``summary()`` gives the rank's message
+    to the others, ``finish()`` turns everybody's messages into this rank's outputs."""
 
     def __init__(self, q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset):
         from .chunk import SegmentForward
@@ -46,6 +47,7 @@ class CudaEngine:
         B = k_e.shape[0]
         K, V, M = k_e.shape[-1], v_e.shape[-1], s_e.shape[-1]
         NG = q.shape[2] // k_e.shape[2]
+        self.dims = (k_e.shape[2], K, M, V)
         # the three-step path needs the pipelined output pass (it alone knows late-starting queries)
         self.steps = None
         if B == 1 and K == 128 and V == 128 and M == 64 and NG % 2 == 0 and q_offset % 64 == 0:
@@ -53,24 +55,28 @@ class CudaEngine:
             self.steps = SegmentForward(f(q), f(rq), f(k_e), f(rk_e), f(v_e), f(s_e), f(g_e), scale, W - 1, W, q_offset)
 
     def summary(self):
-        """Zero-start end state of the (halo-extended) segment: ``(Lk [B,H,K,M], Lv [B,H,M,V])`` fp32."""
+        """``[B, H*K*M + H*M*V + H*M]`` fp32: zero-start end state of the (halo-extended) segment and the total log
+        decay of the tokens that enter its slot memory."""
         if self.steps is not None:
-            return self.steps.state_pass()
+            return self.steps.summary()
         from .chunk import chunk_final_state
         q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.args
         B, T = k_e.shape[0], k_e.shape[1]
         flat = lambda x: x.reshape(B * T, *x.shape[2:]).to(_BF16).contiguous()
         cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=k_e.device)
-        return chunk_final_state(flat(k_e), flat(v_e), flat(s_e), flat(g_e), cu, T, W)
+        Lk, Lv = chunk_final_state(flat(k_e), flat(v_e), flat(s_e), flat(g_e), cu, T, W)
+        return pack_summary(Lk, Lv, g_e, W)
 
-    def finish(self, Sk, Sv):
-        """Outputs of the rank's own tokens and the slot memory at the end of its segment, from the start state."""
+    def finish(self, allp, rank, initial_state=None):
+        """Outputs of the rank's own tokens and the slot memory at the end of its segment, from ``allp [world, B, P]``."""
         q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.args
         if self.steps is not None:
+            Sk, Sv = self.steps.fold(allp[:, 0], rank, initial_state)
             self.steps.apply_prefix(Sk, Sv)
             o, _, _, hk, hv = self.steps.output_pass()
             return o[None].to(q.dtype), hk, hv
         from .chunk_fused import fused_chunk_nha_prefill
+        Sk, Sv = fold_start_state(allp, rank, self.dims, initial_state)
         if q_offset:
             zq = q.new_zeros(q.shape[0], q_offset, *q.shape[2:])
             q, rq = torch.cat([zq, q], 1), torch.cat([zq, rq], 1)
@@ -79,16 +85,13 @@ class CudaEngine:
         return o[:, q_offset:], hk, hv
 
 
-def segment_summary(eng, g_e: torch.Tensor, W: int):
-    """One rank's message to the others: its zero-start end state and the total log decay of the tokens that enter
-    its slot memory (all of the halo-extended segment but its last ``W``; summed from the gates as the kernels see
-    them, rounded to bf16), packed as ``[B, H*K*M + H*M*V + H*M]`` fp32.  Also returns ``(H, K, M, V)``."""
-    Lk, Lv = eng.summary()
+def pack_summary(Lk, Lv, g_e: torch.Tensor, W: int):
+    """One rank's message to the others from its zero-start end state and its gates: the total log decay of the tokens
+    that enter its slot memory is all of the halo-extended segment but its last ``W`` rows, summed from the gates as the
+    kernels see them (rounded to bf16).  ``[B, H*K*M + H*M*V + H*M]`` fp32."""
     B = g_e.shape[0]
     G = g_e[:, :g_e.shape[1] - W].to(_BF16).float().sum(1)                # [B,H,M]
-    dims = (Lk.shape[1], Lk.shape[2], Lk.shape[3], Lv.shape[3])
-    pack = torch.cat([Lk.reshape(B, -1).float(), Lv.reshape(B, -1).float(), G.reshape(B, -1)], 1).contiguous()
-    return pack, dims
+    return torch.cat([Lk.reshape(B, -1).float(), Lv.reshape(B, -1).float(), G.reshape(B, -1)], 1).contiguous()
 
 
 def fold_start_state(allp: torch.Tensor, rank: int, dims, initial_state=None):
@@ -138,34 +141,44 @@ def sequence_parallel_prefill(
     dev = k.device
 
     # ---- 1. halo of W tokens from the left neighbour (kv-head tensors only) ---------------------------
-    send = [x[:, Tr - W:].contiguous() for x in (k, rotary_k, v, s, g)]
-    recv = [torch.empty_like(x) for x in send]
+    # The extended tensors are allocated first and the halo is received straight into their first W rows (contiguous
+    # for one sequence), while this rank's own rows are copied behind them.
+    own = (k, rotary_k, v, s, g)
+    send = [x[:, Tr - W:].contiguous() for x in own]
+    q_offset = W if rank > 0 else 0
+    direct = rank > 0 and B == 1
+    if direct:
+        ext = [torch.empty(B, Tr + W, *x.shape[2:], dtype=x.dtype, device=dev) for x in own]
+        recv = [e[:, :W] for e in ext]
+    else:
+        recv = [torch.empty_like(x) for x in send]
     ops = []
     peer = lambda r: dist.get_global_rank(group, r) if group else r
     if rank + 1 < world:
         ops += [dist.P2POp(dist.isend, x, peer(rank + 1), group) for x in send]
     if rank > 0:
         ops += [dist.P2POp(dist.irecv, x, peer(rank - 1), group) for x in recv]
-    if ops:
-        for w in dist.batch_isend_irecv(ops):
-            w.wait()
-    q_offset = W if rank > 0 else 0
-    if rank > 0:
-        hk_, hrk, hv_, hs, hg = recv
-        k_e, rk_e = torch.cat([hk_, k], 1), torch.cat([hrk, rotary_k], 1)
-        v_e, s_e, g_e = torch.cat([hv_, v], 1), torch.cat([hs, s], 1), torch.cat([hg, g], 1)
+    works = dist.batch_isend_irecv(ops) if ops else []
+    if direct:
+        for e, x in zip(ext, own):
+            e[:, W:].copy_(x)
+    for w in works:
+        w.wait()
+    if rank == 0:
+        k_e, rk_e, v_e, s_e, g_e = own
+    elif direct:
+        k_e, rk_e, v_e, s_e, g_e = ext
     else:
-        k_e, rk_e, v_e, s_e, g_e = k, rotary_k, v, s, g
+        k_e, rk_e, v_e, s_e, g_e = (torch.cat([h_, x], 1) for h_, x in zip(recv, own))
 
     # ---- 2. segment summary from a zero start --------------------------------------------------------------
     eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
-    pack, dims = segment_summary(eng, g_e, W)
+    pack = eng.summary()
 
-    # ---- 3. all-gather of the summaries, fold the ranks before this one ------------------------------------------
+    # ---- 3. all-gather of the summaries ------------------------------------------------------------------------
     allp = torch.empty(world * B, pack.shape[1], dtype=pack.dtype, device=dev)
     dist.all_gather_into_tensor(allp, pack, group=group)
-    Sk, Sv = fold_start_state(allp.view(world, B, -1), rank, dims, initial_state)
 
-    # ---- 4. outputs of the rank's own tokens from its true start state -----------------------------------------------
-    o, hk, hv = eng.finish(Sk, Sv)
+    # ---- 4. fold the ranks before this one, outputs of the rank's own tokens from its true start state ------------
+    o, hk, hv = eng.finish(allp.view(world, B, -1), rank, initial_state)
     return o, (hk, hv)

@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
                                                          (64, 32, 2, 32, 400, 2, True)])
 def test_emulated_ranks_match_the_single_call(K, M, NG, W, T, world, with_state):
     from nha_b200 import fused_chunk_nha_prefill
-    from nha_b200.sharding import CudaEngine, fold_start_state, segment_summary
+    from nha_b200.sharding import CudaEngine
     H = 2
     d = gen.prefill_inputs(6000 + K + W, 1, H, NG, K, K, M, W, T, with_state)
     ref_o, ref_hk, ref_hv = orc.prefill(d['q'], d['k'], d['v'], d['rotary_q'], d['rotary_k'], d['s'], d['g'], W,
@@ -42,14 +42,12 @@ def test_emulated_ranks_match_the_single_call(K, M, NG, W, T, world, with_state)
                          ext(c['g']), W, d['scale'], a - lo)
         if K == 128:
             assert eng.steps is not None, 'the long-context shape must take the three-step path'
-        pack, dims = segment_summary(eng, ext(c['g']), W)
         engines.append(eng)
-        packs.append(pack)
-    allp = torch.stack(packs, 0)
+        packs.append(eng.summary().clone())
+    allp = torch.stack(packs, 0)                       # [world, B, P], as the all-gather leaves it
     outs = []
     for r in range(world):
-        Sk, Sv = fold_start_state(allp, r, dims, st)
-        o, hk, hv = engines[r].finish(Sk, Sv)
+        o, hk, hv = engines[r].finish(allp, r, st)
         outs.append(o)
     o = torch.cat(outs, 1)
     assert_close(o, ref_o, TOL_OUT, 'o vs oracle')

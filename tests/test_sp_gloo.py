@@ -17,15 +17,19 @@ class OracleEngine:
 
     def __init__(self, q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset):
         self.a = (q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
+        self.dims = (k_e.shape[2], k_e.shape[3], s_e.shape[3], v_e.shape[3])
 
     def summary(self):
+        from nha_b200.sharding import pack_summary
         q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.a
         z = torch.zeros(k_e.shape[0], k_e.shape[1], k_e.shape[2], k_e.shape[3])
         _, hk, hv = orc.prefill(z, k_e, v_e, z, k_e, s_e, g_e, W, 1.0)
-        return hk.float(), hv.float()
+        return pack_summary(hk.float(), hv.float(), g_e, W)
 
-    def finish(self, Sk, Sv):
+    def finish(self, allp, rank, initial_state=None):
+        from nha_b200.sharding import fold_start_state
         q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.a
+        Sk, Sv = fold_start_state(allp, rank, self.dims, initial_state)
         zq = torch.zeros(q.shape[0], q_offset, *q.shape[2:])
         o, hk, hv = orc.prefill(torch.cat([zq, q], 1), k_e, v_e, torch.cat([zq, rq], 1), rk_e, s_e, g_e, W, scale, Sk, Sv)
         return o[:, q_offset:].float(), hk.float(), hv.float()
