@@ -63,7 +63,7 @@ static_assert(64 * kLdA * 4 >= kSlot, "the decay table's storage doubles as a ri
 static_assert(total <= 113 * 1024, "two CTAs of the pipelined output pass per SM");
 // mbarriers
 constexpr int bQ = 0, bFull = 1, bEmpty = 5, bTab = 9, bG = 10, bW = 11, bS = 12, bP = 14, bPV = 16, nBar = 17;
-constexpr int kPoll = 1 << 20;
+constexpr int kPoll = 1 << 15;                    // polls of a bounded wait (each sleeps up to 20 us in hardware)
 constexpr float kDecayLimit = 140.0f;
 constexpr float kRaise = 5.545177f;               // 8 ln 2
 constexpr int kTmemCols = 256;
@@ -349,8 +349,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
         }
       }
       if (did) spins = 0;
-      else __nanosleep(64);
-      if (!did && ++spins > kPoll) {                     // nothing was released for a very long time: give up
+      else __nanosleep(256);
+      if (!did && ++spins > 64 * kPoll) {                     // nothing was released for a very long time: give up
         failed = true;
         break;
       }

@@ -16,6 +16,7 @@
 #include <mutex>
 
 #include "nha_common.cuh"
+#include "nha_umma.cuh"
 
 namespace nha {
 
@@ -128,22 +129,55 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
   float* G = (float*)(smem + L.G);
 
   // rows of the chunk hold shifted tokens j = p - shift; rows before the sequence start or past its
-  // end contribute nothing
+  // end contribute nothing.  Every global load of the CTA is issued up front: the gate and write-weight rows into
+  // registers (the gates are scanned first, the weights are needed right after), the key and value tiles by
+  // asynchronous copies that land while the scan runs.
   const int lo = shift, hi = len;                  // valid shifted positions p: lo <= p < hi
-  load_tile_bf16(kt, ldk, (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * K - (size_t)shift * H * K, (int64_t)H * K, p0, lo,
-                 hi, kChunk, K, tid, kStThreads);
-  load_tile_bf16(vt, ldv, (const bf16*)d.v + ((size_t)t0 * H + h) * V - (size_t)shift * H * V, (int64_t)H * V, p0, lo, hi,
-                 kChunk, V, tid, kStThreads);
-  for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
-    const int r = i / (M / 8), c8 = i - r * (M / 8);
-    const int p = p0 + r, j = p - shift;
-    float gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (j >= 0 && p < len) {
-      const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
-      unpack8(u, gv);
-    }
+  constexpr int kMaxPieces = 4;                    // 16-byte pieces of a [64][M <= 128] bf16 tile per thread (256 threads)
+  const int M8 = M / 8, npieces = kChunk * M8;
+  uint4 greg[kMaxPieces], sreg[kMaxPieces];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
+  for (int u = 0; u < kMaxPieces; ++u) {
+    const int i = tid + u * kStThreads;
+    greg[u] = make_uint4(0u, 0u, 0u, 0u);
+    sreg[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < npieces) {
+      const int r = i / M8, c8 = i - r * M8;
+      const int p = p0 + r, j = p - shift;
+      if (j >= 0 && p < len) {
+        greg[u] = *reinterpret_cast<const uint4*>((const bf16*)d.g + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
+        sreg[u] = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
+      }
+    }
+  }
+  {
+    const bf16* kbase = (const bf16*)d.k_gsa + ((size_t)t0 * H + h) * K - (size_t)shift * H * K;
+    const bf16* vbase = (const bf16*)d.v + ((size_t)t0 * H + h) * V - (size_t)shift * H * V;
+    const int K8 = K / 8, V8 = V / 8;
+    for (int i = tid; i < kChunk * K8; i += kStThreads) {
+      const int r = i / K8, c = i - r * K8;
+      const int p = p0 + r;
+      const bool ok = p >= lo && p < hi;
+      umma::cp16(kt + r * ldk + 8 * c, kbase + (size_t)(ok ? p : lo) * H * K + 8 * c, ok);
+    }
+    for (int i = tid; i < kChunk * V8; i += kStThreads) {
+      const int r = i / V8, c = i - r * V8;
+      const int p = p0 + r;
+      const bool ok = p >= lo && p < hi;
+      umma::cp16(vt + r * ldv + 8 * c, vbase + (size_t)(ok ? p : lo) * H * V + 8 * c, ok);
+    }
+    umma::cp_commit();
+  }
+#pragma unroll
+  for (int u = 0; u < kMaxPieces; ++u) {
+    const int i = tid + u * kStThreads;
+    if (i < npieces) {
+      const int r = i / M8, c8 = i - r * M8;
+      float gv[8];
+      unpack8(greg[u], gv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) G[r * ldg + 8 * c8 + e] = gv[e];
+    }
   }
   __syncthreads();
   // inclusive running sum down the rows: two threads per column, the second adds the first half's total
@@ -166,22 +200,22 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
     __syncthreads();
   }
   if (tid < M) w.gend[((size_t)cg * H + h) * M + tid] = G[(kChunk - 1) * ldg + tid];
-  for (int i = tid; i < kChunk * (M / 8); i += kStThreads) {
-    const int r = i / (M / 8), c8 = i - r * (M / 8);
-    const int p = p0 + r, j = p - shift;
-    float sv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (j >= 0 && p < len) {
-      const uint4 u = *reinterpret_cast<const uint4*>((const bf16*)d.s + ((size_t)(t0 + j) * H + h) * M + 8 * c8);
-      unpack8(u, sv);
-    }
-    float out[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int m = 8 * c8 + e;
-      out[e] = sv[e] * __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]);
+  for (int u = 0; u < kMaxPieces; ++u) {
+    const int i = tid + u * kStThreads;
+    if (i < npieces) {
+      const int r = i / M8, c8 = i - r * M8;
+      float sv[8], out[8];
+      unpack8(sreg[u], sv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int m = 8 * c8 + e;
+        out[e] = sv[e] * __expf(G[(kChunk - 1) * ldg + m] - G[r * ldg + m]);
+      }
+      *reinterpret_cast<uint4*>(sbe + r * ldsb + 8 * c8) = pack8(out);
     }
-    *reinterpret_cast<uint4*>(sbe + r * ldsb + 8 * c8) = pack8(out);
   }
+  umma::cp_wait_all();
   __syncthreads();
   bf16* Lk = w.local + ((size_t)cg * H + h) * ((size_t)K * M + (size_t)M * V);
   bf16* Lv = Lk + (size_t)K * M;

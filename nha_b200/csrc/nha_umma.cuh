@@ -161,19 +161,22 @@ __device__ __forceinline__ void mbar_init(uint64_t* mbar, int count) {
 }
 
 // Bounded wait on an mbarrier phase; returns false when the limit is hit (the caller records an
-// error and leaves instead of spinning forever).
+// error and leaves instead of spinning forever).  Every try_wait carries a suspend-time hint: the thread sleeps in
+// hardware until the phase completes or the hint runs out, instead of re-issuing the poll - waiting threads then leave
+// the issue slots to the warps (and the other CTA of the SM) that have work.  `limit` polls of at most kWaitHintNs each.
+constexpr uint32_t kWaitHintNs = 20000;
 __device__ __forceinline__ bool mbar_wait_limit(uint64_t* mbar, uint32_t parity, int limit) {
   uint32_t done = 0;
   for (int it = 0; it < limit && !done; ++it) {
     asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done)
-        : "r"(smem_u32(mbar)), "r"(parity)
+        : "r"(smem_u32(mbar)), "r"(parity), "r"(kWaitHintNs)
         : "memory");
   }
   return done != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) { return mbar_wait_limit(mbar, parity, 1 << 22); }
+__device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) { return mbar_wait_limit(mbar, parity, 1 << 15); }
 // one non-blocking test of an mbarrier phase
 __device__ __forceinline__ bool mbar_test(uint64_t* mbar, uint32_t parity) {
   uint32_t done;
