@@ -52,8 +52,7 @@ CFG = dict(B=16, T=2048, H=16, D=64, M=64, W=64, shift=0)
 WORKLOAD = 'nha_attn_fwd_bwd B16 T2048 H16 D64 M64 W64 chunk64 bf16 (340M-layer shape)'
 CPU_SLICE_T = 512                             # tokens of the B=1 slice both CPU measurements run (cost grows with T)
 # dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one step per token, from the committed ncu captures
-# (None until a capture of the current kernels is committed)
-NCU_STEP_TRAFFIC_PER_TOKEN = None
+NCU_STEP_TRAFFIC_PER_TOKEN = 1107.8e6 / 8192       # profiles/step_traffic_chunk_fwd_bwd_B4_T2048.md
 ALG_BYTES_PER_TOKEN = 16512 + 32832          # forward + backward, all 16 heads (each input read once per pass)
 NAMES = ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v', 's', 'g')
 
@@ -527,6 +526,8 @@ def main():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='skip the decode and long-context prefill side measurements')
     ap.add_argument('--small', action='store_true', help='B=4 instead of 16 (profiling captures)')
+    ap.add_argument('--no-repeat', action='store_true', help='time each region once, without the inner repeats that '
+                    'stretch it to half a second (profiling captures: few launches)')
     ap.add_argument('--pre-op', action='store_true', help='only the slot-gate and rotary side measurements (profiling '
                     'captures of those kernels; prints their JSON, not the bench line)')
     args = ap.parse_args()
@@ -606,7 +607,7 @@ def main():
     # K steps are timed once to size the region, then K x inner_repeats steps back to back (about half a second, so
     # that the clock samples fall inside it); `ms` is the time of K steps
     ms_cal = timed(step, args.steps)
-    reps = max(1, int(math.ceil(500.0 / max(ms_cal, 1e-3))))
+    reps = 1 if args.no_repeat else max(1, int(math.ceil(500.0 / max(ms_cal, 1e-3))))
     if dist is not None:
         t_r = torch.tensor([reps], device=dev)
         dist.all_reduce(t_r, op=dist.ReduceOp.MAX)
@@ -617,6 +618,8 @@ def main():
     def timed_avg(fn, min_ms=250.0):
         """ms per call of `fn`, measured over a region of at least `min_ms`."""
         cal = timed(fn, args.steps) / args.steps
+        if args.no_repeat:
+            return cal
         n = max(args.steps, int(math.ceil(min_ms / max(cal, 1e-4))))
         if dist is not None:
             t_n = torch.tensor([n], device=dev)
