@@ -65,3 +65,43 @@ def unpatch_reference() -> None:
     while _undo:
         m, name, fn = _undo.pop()
         setattr(m, name, fn)
+
+
+class WideWindow(int):
+    """A window size that passes the reference models' ``window_size <= 64`` gates.
+
+    The hybrid model classes send a layer through the NHA ops (slot memory + window) only when ``self.window_size <= 64``
+    (``nha_fla/models/qwen3_moe_nha/qwennha.py:185, 219, 274, 345``; ``llama3_nha/llamanha.py:183, 218``;
+    ``qwen2_nha/qwennha.py:202, 236``; ``qwen3_nha/qwennha.py:190, 225``); wider layers fall to plain sliding-window /
+    full attention without slots, because the reference's fused kernels stop at 64 keys
+    (``nha_fla/ops/nha/chunk_fused.py:332``).  The kernels here take any window, so a layer whose ``window_size`` is a
+    ``WideWindow`` answers those comparisons with 64 as "not wider" and is otherwise the plain integer (arithmetic,
+    slicing, equality, the cache's ``window_size`` bookkeeping)."""
+
+    def __le__(self, other):
+        return True if other == 64 else int.__le__(self, other)
+
+    def __gt__(self, other):
+        return False if other == 64 else int.__gt__(self, other)
+
+    def __lt__(self, other):
+        return True if other == 65 else int.__lt__(self, other)
+
+    def __ge__(self, other):
+        return False if other == 65 else int.__ge__(self, other)
+
+
+def route_wide_windows(model, max_window: int = 1 << 20) -> List[str]:
+    """Send the wide-window attention layers of a reference model through the NHA ops as well: every sub-module that has
+    an integer ``window_size`` above 64 and slot parameters (``num_slots``) gets a :class:`WideWindow` of the same value.
+    Call :func:`patch_reference` too, so that those ops are this package's.  Returns the names of the modules changed.
+
+    This changes what such a layer computes (it now reads the slot memory, like the narrow layers), which is the point
+    of the routing; it needs weights trained for it."""
+    changed = []
+    for name, m in model.named_modules():
+        w = getattr(m, 'window_size', None)
+        if isinstance(w, int) and not isinstance(w, WideWindow) and 64 < w <= max_window and hasattr(m, 'num_slots'):
+            m.window_size = WideWindow(w)
+            changed.append(name)
+    return changed

@@ -79,3 +79,31 @@ def test_patch_reference_rebinds_every_import_site():
         nha_b200.unpatch_reference()
     import nha_fla.ops.nha as ops
     assert ops.chunk_nha is not nha_b200.chunk_nha
+
+
+def test_wide_window_layers_pass_the_reference_gates():
+    """route_wide_windows() makes a layer with window_size > 64 take the branches the reference reserves for
+    window_size <= 64 (its gates are literal comparisons with 64), while the value stays usable as the integer it is."""
+    import torch
+    import nha_b200
+
+    class Attn(torch.nn.Module):               # the attributes the reference's attention classes carry
+        def __init__(self, w):
+            super().__init__()
+            self.window_size, self.num_slots = w, 64
+
+        def takes_nha_path(self):
+            # the reference's gate expressions (nha_fla/models/qwen3_moe_nha/qwennha.py:185, 219, 274, 345)
+            return (not (self.window_size > 64)) and self.window_size <= 64
+
+    model = torch.nn.ModuleList([Attn(64), Attn(2048), Attn(512)])
+    assert [m.takes_nha_path() for m in model] == [True, False, False]
+    assert nha_b200.route_wide_windows(model) == ['1', '2']
+    assert all(m.takes_nha_path() for m in model)
+    w = model[1].window_size
+    assert w == 2048 and w - 1 == 2047 and int(w) == 2048 and list(range(3000))[-w:][0] == 952
+    assert w <= 4096 and not (w <= 100) and w > 100                  # other comparisons are the integer's
+    # the cache's bookkeeping (nha_fla/models/nha_cache.py:86-104): sizes compared with and sliced by window_size
+    x = torch.zeros(1, 3000, 4)
+    assert x.shape[-2] > w and x[..., -w:, :].shape[-2] == 2048 and (x[..., -w:, :].shape[-2] == w)
+    assert nha_b200.route_wide_windows(model) == []                  # idempotent
