@@ -793,6 +793,9 @@ int decode_stream_splits(int B, int H, int W, int M) {
   while (spl < 16 && (int64_t)B * H * spl * 2 <= 2 * (int64_t)sms && W / (spl * 2) >= kStrStage && M / (spl * 2) >= 4 &&
          M % (spl * 2 * 4) == 0)
     spl *= 2;
+  // a CTA keeps all logits of its key range in shared memory: very wide windows are split further (more than one wave
+  // then) so that a split holds at most 512 keys
+  while (spl < 16 && (W + spl - 1) / spl > 512 && M / (spl * 2) >= 4 && M % (spl * 2 * 4) == 0) spl *= 2;
   return spl;
 }
 

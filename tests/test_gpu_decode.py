@@ -180,6 +180,25 @@ def test_decode_cluster_merge_matches_workspace_merge(B, monkeypatch):
     assert (res[0][0] - res[1][0]).abs().max() < 1e-2
 
 
+@pytest.mark.parametrize('B', [2, 48])
+def test_decode_with_a_2048_key_window(B):
+    """The window of the model classes' wide layers (2048 keys), few and many sequences: the streaming kernel splits a
+    (sequence, kv head) until a split holds at most 512 keys, whatever the batch."""
+    from nha_b200 import fused_recurrent_nha_decode
+    H, NG, K, M, W = 2, 4, 128, 64, 2048
+    d = gen.decode_inputs(500 + B, B, H, NG, K, K, M, W)
+    d['cos'], d['sin'] = gen.rope_tables(W, K, first_pos=5000)
+    ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'],
+                          sin=d['sin'], hk0=d['hk0'], hv0=d['hv0'])
+    c = cuda(d)
+    o, (hk, hv) = fused_recurrent_nha_decode(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'],
+                                             cos=c['cos'], sin=c['sin'], initial_state=(c['hk0'], c['hv0']),
+                                             output_final_state=True)
+    assert_close(o, ref[0], TOL_OUT, 'o')
+    assert_close(hk, ref[1], 1e-5, 'hkt')
+    assert_close(hv, ref[2], 1e-5, 'hvt')
+
+
 @pytest.fixture
 def pdl_mode():
     """Sets the dependent-launch mode of the streaming decode kernel for a test and restores the default."""
