@@ -344,8 +344,25 @@ def bench_prefill(dev, rank, world, dist, timed):
     for _ in range(2):
         step()
     ms = timed(step, 30) / 30
+    ms_eager, captured = ms, False
+    if world > 1:
+        # the same call captured once as a CUDA graph (kernels, halo messages, all-gather): a rank's host work per call
+        # shrinks to one graph launch.  Every rank must take the same branch, so the outcome of the capture is agreed on.
+        from nha_b200.sharding import GraphedPrefill
+        graphed = None
+        try:
+            graphed = GraphedPrefill(q, k, v, rq, rk, ss, gg, W)
+        except Exception as e:                                   # noqa: BLE001 - reported, the eager figure stands
+            print(f'[bench] rank {rank}: graph capture failed: {e}', file=sys.stderr)
+        ok = torch.tensor([1 if graphed is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 1:
+            for _ in range(3):
+                graphed()
+            ms, captured = timed(graphed, 30) / 30, True
     flops = T * 9699328.0
     return {'workload': f'prefill fwd B1 T131072 HQ32 H8 D128 M64 W512 bf16, sequence-parallel x{world}', 'ms': ms,
+            'ms_eager_calls': ms_eager, 'captured_as_graph': captured,
             'sequence_parallel_check': check,
             'tokens_per_s': T / (ms * 1e-3), 'tflops': flops / (ms * 1e-3) / 1e12,
             'roofline': {'bound': 'tensor', 'achieved': flops / (ms * 1e-3) / 1e12 / world,

@@ -126,8 +126,12 @@ def check(status: int, what: str):
 
 def check_device_words() -> bool:
     """True when ``NHA_B200_CHECK=1``: the ops then read the kernels' device error word after every call (a bounded
-    wait that ran out leaves it non-zero) and raise.  Reading it synchronises the stream, so it is off by default."""
-    return os.environ.get('NHA_B200_CHECK') == '1'
+    wait that ran out leaves it non-zero) and raise.  Reading it synchronises the stream, so it is off by default, and
+    it is skipped while the stream is being captured into a CUDA graph (a capture cannot be synchronised)."""
+    if os.environ.get('NHA_B200_CHECK') != '1':
+        return False
+    import torch
+    return not torch.cuda.is_current_stream_capturing()
 
 
 def check_chunk_device(lib, desc, stream, what: str):

@@ -293,7 +293,8 @@ class SegmentForward:
         lib = _lib.load()
         dev = k_gsa.device
         Tkv = k_gsa.shape[0]
-        self.cu = torch.tensor([0, Tkv], dtype=torch.int32, device=dev)
+        self.cu = torch.zeros(2, dtype=torch.int32, device=dev)      # built by kernels only: legal inside a graph capture
+        self.cu[1:].fill_(Tkv)
         self.geo = geo = _Geometry(q_gsa, k_gsa, v, s, self.cu, Tkv, q_offset)
         self.scale, self.wl, self.shift = float(scale), int(window_left), int(shift)
         nq = Tkv - geo.q_offset

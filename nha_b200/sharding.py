@@ -182,3 +182,35 @@ def sequence_parallel_prefill(
     # ---- 4. fold the ranks before this one, outputs of the rank's own tokens from its true start state ------------
     o, hk, hv = eng.finish(allp.view(world, B, -1), rank, initial_state)
     return o, (hk, hv)
+
+
+class GraphedPrefill:
+    """:func:`sequence_parallel_prefill` for one fixed segment shape, captured once as a CUDA graph - the rank's kernels,
+    its halo messages and the all-gather - and replayed per call.  A call then costs the host one graph launch instead of
+    some sixty launches, copies and NCCL calls; from eight ranks on that host work is longer than the rank's kernels.
+
+    The tensors passed to the constructor ARE the graph's inputs: write the next segment into them in place, call the
+    object, read ``(o, (hk, hv))`` (the same output tensors every call).  Every rank of the group must construct the
+    object and call it the same number of times (the graph contains collectives), and must drop it before the process
+    group is destroyed (``destroy_process_group`` waits for ever on a communicator that a live graph still uses).  The constructor runs the eager function
+    ``warmup`` times first (communicators and kernel attributes are set up outside the capture)."""
+
+    def __init__(self, q, k, v, rotary_q, rotary_k, s, g, window_size, initial_state=None, scale=None, group=None,
+                 warmup: int = 2):
+        run = lambda: sequence_parallel_prefill(q, k, v, rotary_q, rotary_k, s, g, window_size, initial_state=initial_state,
+                                                scale=scale, group=group)
+        cur = torch.cuda.current_stream(k.device)
+        side = torch.cuda.Stream(k.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):
+                run()
+        cur.wait_stream(side)
+        torch.cuda.synchronize(k.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode='thread_local'):
+            self.out = run()
+
+    def __call__(self):
+        self.graph.replay()
+        return self.out
