@@ -43,8 +43,8 @@ class RingLayer:
             return r
         self.ring_k, self.ring_v, self.ring_g = ring(k), ring(v), ring(g)
         self.head = torch.zeros(k.shape[0], dtype=torch.int32, device=k.device)
-        self.hk = hk.float().contiguous().clone()
-        self.hv = hv.float().contiguous().clone()
+        self.hk = None if hk is None else hk.float().contiguous().clone()
+        self.hv = None if hv is None else hv.float().contiguous().clone()
         # rope = (cos, sin) [1|B, T, K] of the T kept tokens' absolute positions: a second key ring holds the keys
         # rotated on entry, and a decode step then rotates only its own token (rotary by absolute position does
         # not change while the window slides)
@@ -64,6 +64,56 @@ class RingLayer:
     @property
     def window(self) -> int:
         return self.ring_k.shape[1]
+
+    conv_state = None
+    ffn_state = None
+
+    def __getitem__(self, key: str):
+        """The reference cache hands its callers a dict per layer (nha_fla/models/nha_cache.py:31-35); the same keys read
+        from the rings: ``recurrent_state`` -> ``(hk, hv)``, ``attn_state`` -> the window in time order, flattened to
+        ``[B, fill, H*D]`` as the reference stores it (copies)."""
+        if key == 'recurrent_state':
+            return None if self.hk is None else (self.hk, self.hv)
+        if key == 'attn_state':
+            return tuple(x.flatten(2) for x in self.ordered())
+        if key in ('conv_state', 'ffn_state'):
+            return getattr(self, key)
+        raise KeyError(key)
+
+    def as_dict(self) -> dict:
+        return {k: self[k] for k in ('recurrent_state', 'attn_state', 'conv_state', 'ffn_state')}
+
+    def set_state(self, recurrent_state) -> None:
+        hk, hv = recurrent_state
+        if self.hk is not None and hk.data_ptr() == self.hk.data_ptr() and hv.data_ptr() == self.hv.data_ptr():
+            return                                     # the kernels already updated the layer's own tensors in place
+        self.hk, self.hv = hk.float().contiguous().clone(), hv.float().contiguous().clone()
+
+    def append(self, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor) -> None:
+        """Append ``n < W`` tokens ``[B,n,H,*]`` (oldest first) without a decode step: index arithmetic in torch, for
+        callers that drive the cache through ``update`` as they drive the reference cache.  Rings with keys rotated on
+        entry are appended to by their decode step only."""
+        assert self.ring_kr is None, 'a ring with rotated keys is advanced by its decode step'
+        W, n = self.window, k.shape[1]
+        assert n < W
+        if self.fill + n > W:                          # the prompt's tail and the new tokens together: keep the last W
+            ok, ov, og = self.ordered()
+            cat = lambda a, b: torch.cat([a, b.to(_BF16).reshape(b.shape[0], n, *a.shape[2:])], 1)[:, -W:]
+            self.ring_k, self.ring_v, self.ring_g = (cat(a, b).contiguous() for a, b in ((ok, k), (ov, v), (og, g)))
+            self.head.zero_()
+            self.fill = W
+            return
+        if self.fill < W:
+            rows = torch.arange(self.fill, self.fill + n, device=self.head.device)[None].expand(self.head.shape[0], -1)
+        else:
+            rows = (self.head.long()[:, None] + torch.arange(n, device=self.head.device)[None]) % W
+        b = torch.arange(self.head.shape[0], device=self.head.device)[:, None]
+        for ring, x in ((self.ring_k, k), (self.ring_v, v), (self.ring_g, g)):
+            ring[b, rows] = x.to(_BF16).reshape(x.shape[0], n, *ring.shape[2:])
+        if self.fill < W:
+            self.fill += n
+        else:
+            self.head.copy_((self.head + n) % W)
 
     def ordered(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """The window in time order (oldest first), as the reference cache would hold it (copies)."""
@@ -148,14 +198,104 @@ def _decode_ring_rot(q, k, v, g, layer: RingLayer, cos, sin, scale) -> torch.Ten
 
 
 class NHARingCache:
-    """Per-layer ring caches with the read-side surface of the reference's ``NHACache``."""
+    """Per-layer ring caches with the surface of the reference's ``NHACache`` (nha_fla/models/nha_cache.py:11-182).
+
+    Two ways to drive it.  A caller written against the rings uses :meth:`init_layer` after the prefill and
+    :meth:`decode` per token (two launches, nothing shifted).  A caller written against the reference cache keeps its
+    calls - ``get_pop_kvf``, ``update(attn_state=...)``, ``update(recurrent_state=...)``, ``get_seq_length``,
+    ``cache[layer]['recurrent_state']`` - and gets the reference's answers (the window comes back in time order,
+    gathered from the ring, which costs what the reference's ``torch.cat`` costs).  One deviation: a window that is
+    not yet full and receives more tokens than it has room for keeps the newest ``window_size`` tokens, where the
+    reference's cat lets that layer's cache grow past ``window_size`` for good (nha_cache.py:127-131)."""
 
     def __init__(self, seen_tokens: int = 0):
         self.layers: List[Optional[RingLayer]] = []
+        self.former_tokens = seen_tokens
         self._seen_tokens = seen_tokens
 
     def __len__(self) -> int:
         return len(self.layers)
+
+    def __iter__(self):
+        for layer in self.layers:
+            yield layer
+
+    def update(self, recurrent_state=None, attn_state=None, conv_state=None, ffn_state=None, layer_idx: int = 0,
+               offset: Optional[int] = 1, cache_kwargs: Optional[dict] = None) -> dict:
+        """``NHACache.update`` (nha_cache.py:44-141) on rings: same arguments, same returned dict.  ``attn_state`` is
+        ``(k, v, g)`` of the new tokens, ``[B, n, H*D]`` (or ``[B, n, H, D]``), ``cache_kwargs['window_size']`` the
+        window.  The first call for a layer keeps the last ``window_size`` tokens; later calls slide the window; a chunk
+        longer than the window replaces it and is handed back whole, as the reference does."""
+        if layer_idx == 0:
+            self.former_tokens = self._seen_tokens
+            self._seen_tokens += offset
+        W = None
+        if attn_state is not None:
+            if not isinstance(attn_state, tuple) or len(attn_state) != 3:
+                raise ValueError('`attn_state` must be a tuple of three tensors (key, value, gate states)')
+            W = (cache_kwargs or {}).get('window_size', None)
+            if W is None:
+                raise ValueError("a ring needs its size: pass cache_kwargs={'window_size': W}")
+            n = attn_state[0].shape[1]
+        four_d = lambda x: x if x.dim() == 4 else x.unsqueeze(2)        # head split unknown here: one "head" of H*D
+        hand_back = None
+        if len(self.layers) <= layer_idx or self.layers[layer_idx] is None:
+            while len(self.layers) <= layer_idx:
+                self.layers.append(None)
+            if attn_state is None:
+                raise ValueError('the first update of a layer must bring its window (attn_state)')
+            k, v, g = (four_d(x)[:, -W:] for x in attn_state)
+            rs = recurrent_state if recurrent_state is not None else (None, None)
+            layer = self.layers[layer_idx] = RingLayer(k, v, g, rs[0], rs[1], window_size=W)
+        else:
+            layer = self.layers[layer_idx]
+            if recurrent_state is not None:
+                layer.set_state(recurrent_state)
+            if attn_state is not None:
+                assert W == layer.window, 'the window size of a layer is fixed by its first update'
+                k, v, g = (four_d(x) for x in attn_state)
+                if n >= W:
+                    fresh = RingLayer(k[:, -W:], v[:, -W:], g[:, -W:], layer.hk, layer.hv, window_size=W)
+                    layer.ring_k, layer.ring_v, layer.ring_g = fresh.ring_k, fresh.ring_v, fresh.ring_g
+                    layer.head.zero_()
+                    was_full, layer.fill = layer.fill == W, W
+                    if was_full and n > W:
+                        hand_back = attn_state                           # nha_cache.py:106-118
+                else:
+                    layer.append(k, v, g)
+        if conv_state is not None:
+            layer.conv_state = conv_state
+        if ffn_state is not None:
+            layer.ffn_state = ffn_state
+        state = layer.as_dict()
+        if attn_state is not None and attn_state[0].dim() == 4:
+            state['attn_state'] = tuple(x.view(x.shape[0], x.shape[1], *y.shape[2:])
+                                        for x, y in zip(state['attn_state'], attn_state))
+        if hand_back is not None:
+            state['attn_state'] = hand_back
+        return state
+
+    def get_max_length(self) -> Optional[int]:
+        return None
+
+    def to_legacy_cache(self) -> tuple:
+        return tuple(None if layer is None else layer.as_dict() for layer in self.layers)
+
+    @classmethod
+    def from_legacy_cache(cls, past_key_values=None, seen_tokens: int = 0, window_size: Optional[int] = None):
+        """From the reference cache's list of per-layer dicts (nha_cache.py:170-182).  ``window_size`` sizes the rings;
+        without it each layer's ring is as long as its stored window."""
+        cache = cls(seen_tokens)
+        if isinstance(past_key_values, (list, tuple)):
+            for i, st in enumerate(past_key_values):
+                if st is None or st.get('attn_state') is None:
+                    cache.layers.append(None)
+                    continue
+                W = window_size or st['attn_state'][0].shape[1]
+                cache.update(attn_state=tuple(st['attn_state']), recurrent_state=st.get('recurrent_state'), layer_idx=i,
+                             offset=0, cache_kwargs={'window_size': W})
+                cache.layers[i].conv_state, cache.layers[i].ffn_state = st.get('conv_state'), st.get('ffn_state')
+        return cache
 
     def __getitem__(self, layer_idx: int) -> RingLayer:
         if layer_idx < len(self.layers) and self.layers[layer_idx] is not None:
@@ -182,10 +322,13 @@ class NHARingCache:
     def decode(self, layer_idx: int, q, k, v, g, cos, sin, scale=None) -> torch.Tensor:
         if layer_idx == 0:
             self._seen_tokens += 1
+            self.former_tokens = self._seen_tokens
         return fused_recurrent_nha_decode_ring(q, k, v, g, self[layer_idx], cos, sin, scale)
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
-        return self._seen_tokens if layer_idx < len(self.layers) else 0
+        """Tokens seen before the update in progress, as the reference counts them (nha_cache.py:156-160); after
+        :meth:`decode` steps, all tokens decoded so far."""
+        return self.former_tokens if layer_idx < len(self.layers) else 0
 
     def get_pop_kvf(self, layer_idx: int, window_size: int):
         """The oldest window entry ``(k, v, g)`` as ``[B,1,H*D]`` views' equivalents (copies), or Nones."""

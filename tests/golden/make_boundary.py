@@ -14,6 +14,10 @@
    ``ref_prefill`` (:147-191).  Stored per step: the tensors exactly as the cache handed them to the op (views of
    its ``[B, W, H*D]`` buffers reshaped to heads) and the op's outputs, so a GPU test can feed the CUDA op the same
    hand-over and compare, and can step the device ring cache beside it.
+3. ``cache_update_walk.npz``: the same real ``NHACache`` driven through ``update`` / ``get_pop_kvf`` /
+   ``get_seq_length`` alone (no operator) on tiny tensors: a long prompt, single tokens, a short chunk, a chunk longer
+   than the window; and a prompt shorter than the window that fills up token by token.  Every call's inputs and
+   answers are stored in call order; ``tests/test_ring_cache_update.py`` replays the calls on ``NHARingCache``.
 """
 import argparse
 import inspect
@@ -98,6 +102,46 @@ def cache_walk(vp):
     return {k: v.detach().float().numpy() for k, v in out.items()}, meta
 
 
+def _patched_cache_class():
+    import transformers.cache_utils as tcu
+
+    def lenient_init(self, layers=None, layer_class_to_replicate=None, offloading=False, offload_only_non_sliding=True):
+        self.layers = layers if layers is not None else []
+        self.layer_class_to_replicate = layer_class_to_replicate
+        self.offloading = offloading
+        self.offload_only_non_sliding = offload_only_non_sliding
+    tcu.Cache.__init__ = lenient_init
+    from nha_fla.models.nha_cache import NHACache
+    return NHACache
+
+
+def cache_update_walk():
+    """Scripts of ``update`` calls; per call i of script S: ``S/i/in_k|in_v|in_g`` (the new tokens), ``S/i/pop_*`` (what
+    get_pop_kvf gave before the call, absent when it gave None), ``S/i/ret_*`` (the returned window) and
+    ``S/i/seq`` (get_seq_length after the call)."""
+    NHACache = _patched_cache_class()
+    B, DK, DV, DG, W = 2, 12, 12, 6, 16
+    gen_ = torch.Generator().manual_seed(2024)
+    out, scripts = {}, {'long_prompt': [40, 1, 1, 1, 5, 1, 20, 1, 1], 'short_prompt': [6] + [1] * 14}
+    for name, lens in scripts.items():
+        cache = NHACache()
+        for i, n in enumerate(lens):
+            k, v, g = (torch.randn(B, n, D, generator=gen_).to(torch.bfloat16) for D in (DK, DV, DG))
+            pop = cache.get_pop_kvf(0, W)
+            st = cache.update(attn_state=(k, v, g), layer_idx=0, offset=0, cache_kwargs=dict(window_size=W))['attn_state']
+            cache.update(recurrent_state=(torch.zeros(1), torch.zeros(1)), layer_idx=0, offset=n)
+            for tag, x in zip(('k', 'v', 'g'), (k, v, g)):
+                out[f'{name}/{i}/in_{tag}'] = x
+            if pop[0] is not None:
+                for tag, x in zip(('k', 'v', 'g'), pop):
+                    out[f'{name}/{i}/pop_{tag}'] = x
+            for tag, x in zip(('k', 'v', 'g'), st):
+                out[f'{name}/{i}/ret_{tag}'] = x
+            out[f'{name}/{i}/seq'] = torch.tensor([cache.get_seq_length(0)])
+    meta = dict(B=B, DK=DK, DV=DV, DG=DG, W=W, scripts=scripts)
+    return {k: v.detach().float().numpy() for k, v in out.items()}, meta
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', required=True, help='path of a checkout of the reference project')
@@ -108,9 +152,11 @@ def main():
     vp.DEVICE = 'cpu'
     walk, meta = cache_walk(vp)
     np.savez_compressed(os.path.join(HERE, 'cache_walk.npz'), **walk)
+    upd, upd_meta = cache_update_walk()
+    np.savez_compressed(os.path.join(HERE, 'cache_update_walk.npz'), **upd)
     with open(os.path.join(HERE, 'boundary.json'), 'w') as f:
-        json.dump({'signatures': signatures(), 'cache_walk': meta}, f, indent=1)
-    print('wrote boundary.json and cache_walk.npz', meta)
+        json.dump({'signatures': signatures(), 'cache_walk': meta, 'cache_update_walk': upd_meta}, f, indent=1)
+    print('wrote boundary.json, cache_walk.npz and cache_update_walk.npz', meta)
 
 
 if __name__ == '__main__':

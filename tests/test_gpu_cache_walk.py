@@ -76,3 +76,25 @@ def test_ring_cache_beside_the_reference_cache():
         assert_close(cache[0].hk, s('hk'), 1e-4, f'ring step {i} hk')
         assert_close(cache[0].hv, s('hv'), 1e-4, f'ring step {i} hv')
     assert cache.get_seq_length(0) == T + m['steps']
+
+
+def test_ring_cache_filled_through_update_then_decoded():
+    """The layer filled the reference's way - ``update(attn_state=(k, v, g) flattened to [B, T, H*D])`` then
+    ``update(recurrent_state=...)`` - and stepped with the ring decode: same outputs and states as the reference's flow."""
+    from nha_b200 import NHARingCache
+    m, z = META, _walk()
+    B, H, NG, K, M, W, T = m['B'], m['H'], m['NG'], m['K'], m['M'], m['W'], m['T']
+    d = gen.prefill_inputs(m['seed'], B, H, NG, K, K, M, W, T + m['steps'], with_state=False)
+    bf = lambda x: x.to(torch.bfloat16).cuda()
+    cache = NHARingCache()
+    st = cache.update(attn_state=tuple(bf(d[n][:, :T]).flatten(-2, -1) for n in ('k', 'v', 'g')), layer_idx=0, offset=0,
+                      cache_kwargs=dict(window_size=W))
+    assert st['attn_state'][0].shape == (B, W, H * K)
+    cache.update(recurrent_state=(z['step0/hk_in'].cuda(), z['step0/hv_in'].cuda()), layer_idx=0, offset=T)
+    for i in range(m['steps']):
+        s = lambda n: z[f'step{i}/{n}']
+        o = cache.decode(0, bf(s('q')), bf(s('k_new')), bf(s('v_new')), bf(s('g_new')), bf(s('cos')), bf(s('sin')))
+        assert_close(o, s('o'), TOL_OUT, f'step {i} o')
+        assert_close(cache[0]['recurrent_state'][0], s('hk'), 1e-4, f'step {i} hk')
+        assert_close(cache[0]['recurrent_state'][1], s('hv'), 1e-4, f'step {i} hv')
+    assert cache.get_seq_length(0) == T + m['steps']
