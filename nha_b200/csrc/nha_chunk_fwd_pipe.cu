@@ -556,15 +556,22 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       // the per-element test; every row of the chunk sees all keys of the tiles in between
       const bool masked = j == 0 || (wl >= 0 && kb < c0 + kChunk - 1 - wl) || c0 + kChunk > len;
       {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float m0 = -INFINITY, m1 = -INFINITY;
         if (masked) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], (unsigned)(off + e) <= kspan ? s[e] : -INFINITY);
+          for (int e = 0; e < 64; e += 4) {
+            m0 = max3(m0, (unsigned)(off + e) <= kspan ? s[e] : -INFINITY, (unsigned)(off + e + 1) <= kspan ? s[e + 1] : -INFINITY);
+            m1 = max3(m1, (unsigned)(off + e + 2) <= kspan ? s[e + 2] : -INFINITY,
+                      (unsigned)(off + e + 3) <= kspan ? s[e + 3] : -INFINITY);
+          }
         } else {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) m4[e & 3] = fmaxf(m4[e & 3], s[e]);
+          for (int e = 0; e < 64; e += 4) {
+            m0 = max3(m0, s[e], s[e + 1]);
+            m1 = max3(m1, s[e + 2], s[e + 3]);
+          }
         }
-        const float mc = d.scale * fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        const float mc = d.scale * fmaxf(m0, m1);
         const bool raise = mc > mref + kRaise;
         float f = 1.f;
         if (raise) {
@@ -589,18 +596,33 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
         }
       }
       const float nm = -mref * kLog2e;
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t sc2p = pack2(sc2, sc2), nmp = pack2(nm, nm);
+      uint64_t l0 = pack2(0.f, 0.f), l1 = l0;
       if (masked) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          s[e] = (unsigned)(off + e) <= kspan ? exp2f(fmaf(s[e], sc2, nm)) : 0.f;
-          l4[e & 3] += s[e];
+        for (int e = 0; e < 64; e += 4) {
+          float a0, a1, a2, a3;
+          unpack2(ffma2(pack2(s[e], s[e + 1]), sc2p, nmp), a0, a1);
+          unpack2(ffma2(pack2(s[e + 2], s[e + 3]), sc2p, nmp), a2, a3);
+          s[e] = (unsigned)(off + e) <= kspan ? exp2f(a0) : 0.f;
+          s[e + 1] = (unsigned)(off + e + 1) <= kspan ? exp2f(a1) : 0.f;
+          s[e + 2] = (unsigned)(off + e + 2) <= kspan ? exp2f(a2) : 0.f;
+          s[e + 3] = (unsigned)(off + e + 3) <= kspan ? exp2f(a3) : 0.f;
+          l0 = fadd2(l0, pack2(s[e], s[e + 1]));
+          l1 = fadd2(l1, pack2(s[e + 2], s[e + 3]));
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          s[e] = exp2f(fmaf(s[e], sc2, nm));
-          l4[e & 3] += s[e];
+        for (int e = 0; e < 64; e += 4) {
+          float a0, a1, a2, a3;
+          unpack2(ffma2(pack2(s[e], s[e + 1]), sc2p, nmp), a0, a1);
+          unpack2(ffma2(pack2(s[e + 2], s[e + 3]), sc2p, nmp), a2, a3);
+          s[e] = exp2f(a0);
+          s[e + 1] = exp2f(a1);
+          s[e + 2] = exp2f(a2);
+          s[e + 3] = exp2f(a3);
+          l0 = fadd2(l0, pack2(s[e], s[e + 1]));
+          l1 = fadd2(l1, pack2(s[e + 2], s[e + 3]));
         }
       }
       {
@@ -611,7 +633,11 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
         tmem_st32(tl + 64 * b, pk);
         tmem_st_wait();
       }
-      ls += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      {
+        float a0, a1;
+        unpack2(fadd2(l0, l1), a0, a1);
+        ls += a0 + a1;
+      }
       // Every completion phase of the value products is observed before the next one can happen: P~ V of step j is only
       // issued after this hand-over, so seeing step j - 1 complete here (it was issued a whole step ago) keeps the
       // barrier at most one phase ahead of what this thread has seen.

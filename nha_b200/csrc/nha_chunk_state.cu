@@ -16,9 +16,13 @@
 #include <mutex>
 
 #include "nha_common.cuh"
+#include "nha_tma.cuh"
 #include "nha_umma.cuh"
 
 namespace nha {
+
+bool state_local_umma_supported(const nha_chunk_desc* d);
+int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err, cudaStream_t cs);
 
 constexpr int kStThreads = 256;
 constexpr int kStWarps = kStThreads / 32;
@@ -56,15 +60,6 @@ __global__ void nha_plan_kernel(const int32_t* __restrict__ cu, int32_t* __restr
 }
 
 // ---------------------------------------------------------------------------------------------
-// Scratch of the state pass: L [NCB*H][K*M + M*V] bf16 (the chunk-start states it is summed into are bf16 too; the
-// running sum itself stays fp32), then Gend [NCB*H][M] fp32, then Gtot [N*H][M] fp32 (the log gates of each sequence
-// summed over its chunks, left by the scan for nha_chunk_gate_totals).
-struct StateWs {
-  bf16* local;
-  float* gend;
-  float* gtot;
-};
-
 // C[Mt*16 x Nt*16] = A^T B as tile_gemm<false, true, false>, with the fp32 accumulator tiles rounded to bf16 on their way
 // to global memory: a warp parks its 16 x 16 tile in its own 1 KB patch of shared memory and writes it out as 16 rows
 // of 32 bytes (whole sectors).
@@ -225,12 +220,42 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
   tile_gemm_tn_bf16(Lv, V, sbe, ldsb, vt, ldv, M / 16, V / 16, kChunk / 16, warp, kStWarps, patch);
 }
 
-// Forward scan over the chunks of one (sequence, kv head): stores the state at every chunk start and
-// the final state.  One thread owns four consecutive state elements (one 8-byte bf16 store per chunk) and
-// fetches kStScanBatch chunks of L ahead of the serial recurrence, so that a long sequence with few heads
-// still keeps enough loads in flight.
-constexpr int kStScanBatch = 16;
-__global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w) {
+// Forward scan over the chunks of one (sequence, kv head): stores the state at every chunk start and the final state.
+// A CTA owns 1024 consecutive state elements (a thread four of them: one 8-byte bf16 store per chunk) and walks the
+// chunks in order.  The recurrence is serial, its inputs are not: a producer thread streams the CTA's 2 KB slice of L
+// and the chunk's gate totals through a ring of kScanStages stages of kScanGroup chunks each (one bulk copy per slice,
+// completion counted on the stage's mbarrier), so that tens of chunks are in flight per CTA whatever the sequence
+// length - with one long sequence and few heads there are only N*H*SD/1024 CTAs to keep the memory system busy.
+constexpr int kScanElems = 512;                  // state elements per CTA
+constexpr int kScanThreads = kScanElems / 4;      // consumer threads; one more warp hosts the producer
+constexpr int kScanGroup = 8;                     // chunks per ring stage (two copies each: at most 16 issuing lanes)
+constexpr int kScanStages = 5;
+constexpr int kScanSlot = kScanElems * 2 + 512;   // bytes per chunk in a stage: the L slice, then up to 128 gate totals
+constexpr int kScanPoll = 1 << 12;
+constexpr int kScanSmem = kScanStages * kScanGroup * kScanSlot + 2 * kScanStages * 8 + 16;
+
+// bounded wait without a suspend-time hint: the consumers of the scan wait often and briefly
+__device__ __forceinline__ bool scan_wait(uint64_t* mbar, uint32_t parity) {
+  uint32_t done = 0;
+  for (int it = 0; it < (1 << 22) && !done; ++it) {
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(umma::smem_u32(mbar)), "r"(parity)
+        : "memory");
+  }
+  return done != 0;
+}
+
+__device__ __forceinline__ void scan_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   umma::smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(umma::smem_u32(mbar))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kScanThreads + 32) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w,
+                                                                           int* __restrict__ err) {
   const int K = d.K, V = d.V, M = d.M, H = d.H;
   const int KM = K * M, MV = M * V;
   const size_t SD = (size_t)KM + MV;
@@ -239,8 +264,56 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
   const int len = d.cu_seqlens[n + 1] - d.cu_seqlens[n];
   const int nchunks = (len + kChunk - 1) / kChunk;
   const int chunk0 = d.plan[n];
-  const int el = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
-  if (el >= KM + MV) return;
+  const int el0 = blockIdx.y * kScanElems;
+  const int nel = min(kScanElems, (int)SD - el0);   // a multiple of 8: K, V and M are multiples of 16
+  const int tid = threadIdx.x;
+  extern __shared__ __align__(128) unsigned char scan_smem[];
+  uint64_t* full = (uint64_t*)(scan_smem + kScanStages * kScanGroup * kScanSlot);
+  uint64_t* empty = full + kScanStages;
+  volatile int* abort_flag = (volatile int*)(empty + kScanStages);
+  if (tid == 0) {
+    for (int s = 0; s < kScanStages; ++s) {
+      umma::mbar_init(&full[s], 1);
+      umma::mbar_init(&empty[s], kScanThreads / 32);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int nrounds = (nchunks + kScanGroup - 1) / kScanGroup;
+  if (tid >= kScanThreads) {
+    // ---- producer: one warp; lane 0 keeps the books, every lane issues one copy of the stage (a single thread issuing
+    // all copies of a stage was the bottleneck of the whole kernel) ----
+    const int lane = tid - kScanThreads;
+    const uint32_t lbytes = (uint32_t)nel * 2, gbytes = (uint32_t)M * 4;
+    for (int it = 0; it < nrounds; ++it) {
+      const int s = it % kScanStages, round = it / kScanStages;
+      const int cnt = min(kScanGroup, nchunks - it * kScanGroup);
+      int stop = 0;
+      if (lane == 0) {
+        stop = *abort_flag;
+        if (!stop && round > 0 && !scan_wait(&empty[s], (round - 1) & 1)) {
+          *abort_flag = 1;
+          atomicExch(err, 1);
+          stop = 1;
+        }
+        if (!stop) mbar_expect_tx(&full[s], cnt * (lbytes + gbytes));
+      }
+      stop = __shfl_sync(0xffffffffu, stop, 0);
+      if (stop) break;
+      const int u = lane >> 1;
+      if (u < cnt) {
+        const size_t cgi = (size_t)(chunk0 + it * kScanGroup + u) * H + h;
+        unsigned char* slot = scan_smem + (size_t)(s * kScanGroup + u) * kScanSlot;
+        if (lane & 1) scan_bulk_g2s(slot + kScanElems * 2, w.gend + cgi * M, gbytes, &full[s]);
+        else scan_bulk_g2s(slot, w.local + cgi * SD + el0, lbytes, &full[s]);
+      }
+    }
+    return;
+  }
+  // ---- consumers ----
+  const int el = el0 + 4 * tid;
+  const bool active = 4 * tid < nel;
   const bool is_k = el < KM;
   const int e = is_k ? el : el - KM;
   const int m = is_k ? e % M : e / V;
@@ -248,44 +321,52 @@ __global__ void __launch_bounds__(256) nha_state_scan_kernel(const nha_chunk_des
   bf16* out = is_k ? (bf16*)d.hk_chunks : (bf16*)d.hv_chunks;
   float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
   float4 gsum = make_float4(0.f, 0.f, 0.f, 0.f);
-  const bool sums = is_k && e < M;                  // the threads of hk's first row also total the log gates
-  {
+  const bool sums = active && is_k && e < M;        // the threads of hk's first row also total the log gates
+  if (active) {
     const float* h0 = is_k ? d.hk0 : d.hv0;
     if (h0) run = *reinterpret_cast<const float4*>(h0 + nh * per + e);
   }
-  for (int lo = 0; lo < nchunks; lo += kStScanBatch) {
-    uint2 la[kStScanBatch];
-    float4 da[kStScanBatch];
+  bool failed = false;
+  for (int it = 0; it < nrounds; ++it) {
+    const int s = it % kScanStages, round = it / kScanStages;
+    if (*abort_flag) { failed = true; break; }
+    if (!scan_wait(&full[s], round & 1)) {
+      *abort_flag = 1;
+      atomicExch(err, 1);
+      failed = true;
+      break;
+    }
+    const int cnt = min(kScanGroup, nchunks - it * kScanGroup);
+    if (active) {
 #pragma unroll
-    for (int u = 0; u < kStScanBatch; ++u) {
-      const int ci = lo + u;
-      if (ci < nchunks) {
-        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-        la[u] = __ldcs((const uint2*)(w.local + cgi * SD + el));
-        if (is_k) da[u] = *(const float4*)(w.gend + cgi * M + m);
-        else da[u].x = w.gend[cgi * M + m];
+      for (int u = 0; u < kScanGroup; ++u) {
+        if (u < cnt) {
+          const unsigned char* slot = scan_smem + (size_t)(s * kScanGroup + u) * kScanSlot;
+          const uint2 la = *reinterpret_cast<const uint2*>(slot + 8 * tid);
+          const float* gp = reinterpret_cast<const float*>(slot + kScanElems * 2) + m;
+          float4 da;
+          if (is_k) da = *reinterpret_cast<const float4*>(gp);
+          else da.x = *gp;
+          const size_t cgi = (size_t)(chunk0 + it * kScanGroup + u) * H + h;
+          uint2 o;
+          *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(run.x, run.y);
+          *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(run.z, run.w);
+          *reinterpret_cast<uint2*>(out + cgi * per + e) = o;
+          float4 a;
+          if (is_k) a = make_float4(__expf(da.x), __expf(da.y), __expf(da.z), __expf(da.w));
+          else { const float x = __expf(da.x); a = make_float4(x, x, x, x); }
+          if (sums) { gsum.x += da.x; gsum.y += da.y; gsum.z += da.z; gsum.w += da.w; }
+          const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la.x));
+          const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la.y));
+          run.x = run.x * a.x + l01.x; run.y = run.y * a.y + l01.y;
+          run.z = run.z * a.z + l23.x; run.w = run.w * a.w + l23.y;
+        }
       }
     }
-#pragma unroll
-    for (int u = 0; u < kStScanBatch; ++u) {
-      const int ci = lo + u;
-      if (ci < nchunks) {
-        const size_t cgi = (size_t)(chunk0 + ci) * H + h;
-        uint2 o;
-        *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(run.x, run.y);
-        *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(run.z, run.w);
-        *reinterpret_cast<uint2*>(out + cgi * per + e) = o;
-        float4 a;
-        if (is_k) a = make_float4(__expf(da[u].x), __expf(da[u].y), __expf(da[u].z), __expf(da[u].w));
-        else { const float x = __expf(da[u].x); a = make_float4(x, x, x, x); }
-        if (sums) { gsum.x += da[u].x; gsum.y += da[u].y; gsum.z += da[u].z; gsum.w += da[u].w; }
-        const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].x));
-        const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].y));
-        run.x = run.x * a.x + l01.x; run.y = run.y * a.y + l01.y;
-        run.z = run.z * a.z + l23.x; run.w = run.w * a.w + l23.y;
-      }
-    }
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(&empty[s]);
   }
+  if (failed || !active) return;
   float* ht = is_k ? d.hkt : d.hvt;
   if (ht) *reinterpret_cast<float4*>(ht + nh * per + e) = run;
   if (sums) *reinterpret_cast<float4*>(w.gtot + nh * M + m) = gsum;
@@ -312,13 +393,28 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
   const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
   StateWs w;
   state_ws_layout(d, scratch, &w);
-  const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
-  cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
-  if (e != cudaSuccess) return record_cuda_error(e);
-  nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
-  int st = check_launch();
-  if (st != NHA_OK) return st;
-  nha_state_scan_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD / 4 + 255) / 256)), 256, 0, cs>>>(*d, w);
+  // per-chunk terms: the tensor-core kernel where it has the shape, else the wmma kernel
+  int st = NHA_ERR_UNSUPPORTED;
+  if (state_local_umma_supported(d)) {
+    int* err = d->plan + d->N + 1 + NCB + (size_t)NCB * d->H;
+    st = state_local_umma_launch(d, w, err, cs);
+    if (st != NHA_OK && st != NHA_ERR_UNSUPPORTED) return st;
+  }
+  if (st == NHA_ERR_UNSUPPORTED) {
+    const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
+    cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
+    st = check_launch();
+    if (st != NHA_OK) return st;
+  }
+  {
+    cudaError_t e = set_max_smem((const void*)nha_state_scan_kernel, kScanSmem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    int* err = d->plan + d->N + 1 + NCB + (size_t)NCB * d->H;
+    nha_state_scan_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD + kScanElems - 1) / kScanElems)), kScanThreads + 32,
+                            kScanSmem, cs>>>(*d, w, err);
+  }
   return check_launch();
 }
 

@@ -135,6 +135,15 @@ __device__ __forceinline__ ChunkRec chunk_rec(const nha_chunk_desc& d, int cg) {
   return c;
 }
 
+// Scratch of the state pass: L [NCB*H][K*M + M*V] bf16 (the chunk-start states it is summed into are bf16 too; the
+// running sum itself stays fp32), then Gend [NCB*H][M] fp32, then Gtot [N*H][M] fp32 (the log gates of each sequence
+// summed over its chunks, left by the scan for nha_chunk_gate_totals).
+struct StateWs {
+  bf16* local;
+  float* gend;
+  float* gtot;
+};
+
 __device__ __forceinline__ int seq_window(const nha_chunk_desc& d, int n) {
   return d.window_left ? d.window_left[n] : d.window_left_all;
 }

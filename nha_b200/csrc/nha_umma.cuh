@@ -177,6 +177,37 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* mbar, uint32_t parity,
   return done != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* mbar, uint32_t parity) { return mbar_wait_limit(mbar, parity, 1 << 15); }
+// Packed fp32 pairs (one instruction for two lanes of arithmetic) and the three-input maximum: the element-wise loops of
+// the softmax threads are bound by instruction count, and these halve it for the multiply-adds, sums and maxima.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(a), "f"(b));
+  return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // one non-blocking test of an mbarrier phase
 __device__ __forceinline__ bool mbar_test(uint64_t* mbar, uint32_t parity) {
   uint32_t done;
