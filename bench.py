@@ -254,6 +254,17 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             st = lib.nha_ring_append(d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), d['k'].data_ptr(),
                                      d['v'].data_ptr(), gn.data_ptr(), hd.data_ptr(), B, H, K, K, M, W, W, stream)
             assert st == 0
+    heads_kv = [torch.zeros(B, H, dtype=torch.int32, device=dev) for _ in range(LAYERS)]
+
+    def step_ring_fused():
+        # one launch per layer: the decode kernel stores the step's token over the entry that left the window
+        for d, gn, gw, hd in zip(layers, gnew, gwin, heads_kv):
+            st = lib.nha_decode_step_ring_fused(d['q'].data_ptr(), d['k'].data_ptr(), d['v'].data_ptr(), gn.data_ptr(),
+                                                d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), gw.data_ptr(), hd.data_ptr(),
+                                                cos.data_ptr(), sin.data_ptr(), 0, cos.stride(1), d['hk'].data_ptr(),
+                                                d['hv'].data_ptr(), d['o'].data_ptr(), ws.data_ptr(), ws.numel(), B, H * NG,
+                                                H, K, K, M, W, W, K ** -0.5, stream)
+            assert st == 0
     # rings whose keys were rotated when they entered (absolute positions): the step rotates only its own token
     kr = [torch.empty_like(d['sw_k']) for d in layers]
     for d, x in zip(layers, kr):
@@ -277,13 +288,17 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     for _ in range(2):
         step_shift()
         step_ring()
+        step_ring_fused()
         step_ring_rot()
     ms_shift = timed(step_shift, 10) / 10
     ms_ring = timed(step_ring, 50) / 50
+    ms_fused = timed(step_ring_fused, 100) / 100
     ms_rot = timed(step_ring_rot, 50) / 50
     ms_rot_only = timed(lambda: step_ring_rot(False), 50) / 50
     with_cache = {'shifted_window_us_per_layer': 1e3 * ms_shift / LAYERS, 'ring_us_per_layer': 1e3 * ms_ring / LAYERS,
                   'ring_tokens_per_s': world * B / (ms_ring * 1e-3),
+                  'ring_fused_us_per_layer': 1e3 * ms_fused / LAYERS,
+                  'ring_fused_tokens_per_s': world * B / (ms_fused * 1e-3),
                   'ring_rotated_keys_us_per_layer': 1e3 * ms_rot / LAYERS,
                   'ring_rotated_keys_tokens_per_s': world * B / (ms_rot * 1e-3),
                   'ring_rotated_keys_decode_only_us_per_layer': 1e3 * ms_rot_only / LAYERS,

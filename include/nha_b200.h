@@ -127,6 +127,19 @@ int nha_decode_step_ring(const void* q, const void* k_new, const void* v_new, co
 int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new, const void* g_new,
                     int32_t* head, int B, int H, int K, int V, int M, int W, int fill, void* stream);
 
+/* nha_decode_step_ring and nha_ring_append in ONE launch.  `head [B*H]` holds one index per (sequence, kv head)
+ * (all H entries of a sequence are equal between calls): the CTA that merges the splits of a (sequence, kv head) -
+ * the last to touch it, after every split has read the rings - stores the step's token (k_new, v_new, g_new) over
+ * the entry that left the window (fill == W) or into row `fill` of a ring that is still filling, and advances that
+ * kv head's index.  Same results as the two separate calls; K == V in {64, 128} with the streaming kernel only
+ * (NHA_ERR_UNSUPPORTED otherwise).  The reference shifts its window with three torch.cat per layer and token
+ * (nha_fla/models/nha_cache.py:119-126). */
+int nha_decode_step_ring_fused(const void* q, const void* k_new, const void* v_new, const void* g_new, void* ring_k,
+                               void* ring_v, void* ring_g, int32_t* head, const void* cos, const void* sin,
+                               int64_t cs_batch, int64_t cs_row, float* hk, float* hv, void* o, void* workspace,
+                               int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M, int W, int fill,
+                               float scale, void* stream);
+
 /* Rings with keys rotated on entry (optional layout of the ring cache above).  Rotary by absolute position does
  * not change while the window slides, so a key is rotated once, when it enters the ring, and the decode step no
  * longer rotates (or reads tables for) the W-1 old window keys; the reference rotates the whole window at every

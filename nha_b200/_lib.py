@@ -52,6 +52,8 @@ SYMBOLS = {
     'nha_decode_step_ring': (C.c_int, [c_void_p] * 9 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                        C.c_int64] + [C.c_int] * 8 + [C.c_float, c_void_p]),
     'nha_ring_append': (C.c_int, [c_void_p] * 7 + [C.c_int] * 7 + [c_void_p]),
+    'nha_decode_step_ring_fused': (C.c_int, [c_void_p] * 10 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             C.c_int64] + [C.c_int] * 8 + [C.c_float, c_void_p]),
     'nha_ring_rotate_rows': (C.c_int, [c_void_p] * 4 + [C.c_int64, C.c_int64] + [C.c_int] * 5 + [c_void_p]),
     'nha_decode_step_ring_rot': (C.c_int, [c_void_p] * 10 + [C.c_int64, c_void_p, c_void_p, c_void_p, c_void_p, C.c_int64]
                                  + [C.c_int] * 8 + [C.c_float, c_void_p]),

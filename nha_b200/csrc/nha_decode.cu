@@ -467,7 +467,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
                       cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
-                      const void* ring_kraw);
+                      const void* ring_kraw, const void* g_new);
 
 // Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
 // every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
@@ -557,7 +557,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   if (stream_ok)
     return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
                              errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, nullptr,
-                             nullptr, W, 0, nullptr);
+                             nullptr, W, 0, nullptr, nullptr);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;
@@ -621,7 +621,30 @@ extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void
   float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop, nullptr);
+                           ring_g, W, nopop, nullptr, nullptr);
+}
+
+extern "C" int nha_decode_step_ring_fused(const void* q, const void* k_new, const void* v_new, const void* g_new, void* ring_k,
+                                          void* ring_v, void* ring_g, int32_t* head, const void* cosp, const void* sinp,
+                                          int64_t cs_batch, int64_t cs_row, float* hk, float* hv, void* o, void* workspace,
+                                          int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M, int W, int fill,
+                                          float scale, void* stream) {
+  if (!q || !k_new || !v_new || !g_new || !ring_k || !ring_v || !ring_g || !head || !cosp || !sinp || !hk || !hv || !o)
+    return NHA_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1 || fill < 0 || fill > W) return NHA_ERR_BAD_ARG;
+  const int NG = HQ / H;
+  const int nopop = fill < W, Weff = nopop ? fill + 1 : W;
+  if (!decode_stream_supported(K, V, M, Weff, NG, false) || M % 8) return NHA_ERR_UNSUPPORTED;
+  const int splits = decode_stream_splits(B, H, Weff, M);
+  if (!workspace || workspace_bytes < nha_decode_workspace_bytes(B, HQ, H, V, W)) return NHA_ERR_WORKSPACE;
+  int* tickets = (int*)workspace;
+  int* errw = tickets + (size_t)B * H;
+  char* base = (char*)workspace + align_up((B * H + 1) * 4, 256);
+  float* part_ml = (float*)base;
+  float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
+  return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
+                           o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
+                           ring_g, W, nopop, nullptr, g_new);
 }
 
 extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
@@ -736,7 +759,7 @@ extern "C" int nha_decode_step_ring_rot(const void* q, const void* k_new, const 
   // token of this step
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_kr, ring_v, cos_q, sin_q, cs_batch, 0, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop, ring_k);
+                           ring_g, W, nopop, ring_k, nullptr);
 }
 
 extern "C" int nha_ring_append_rot(void* ring_k, void* ring_kr, void* ring_v, void* ring_g, const void* k_new,

@@ -60,6 +60,12 @@ struct DecodeStreamArgs {
   // absolute position does not change while the window slides), so only the token of this step is rotated here;
   // the raw key that enters the slot memory comes from ring_kraw
   const bf16* ring_kraw;
+  // fused append (ring mode, raw keys): g_new != NULL makes the CTA that merges the splits of a (sequence, kv head)
+  // also store the step's token (k, v, g_new) over the entry that left the window (or into the next free row of a
+  // filling ring) and advance that kv head's index.  `head` then holds one index per (sequence, kv head), [B*H]: every
+  // (sequence, kv head) is finished by exactly one CTA, after all its splits have read the rings, so no other CTA
+  // reads the index or the row that is overwritten.
+  const bf16* g_new;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
@@ -170,7 +176,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     grid_dep_wait();
     grid_dep_launch();
   }
-  const int hd = isring ? (a.nopop ? -1 : a.head[b]) : 0;              // physical row of the oldest ring entry
+  const int hd = isring ? (a.nopop ? -1 : a.head[a.g_new ? bh : b]) : 0;   // physical row of the oldest ring entry
   // the token that enters the slot memory: separate small tensors, or the oldest ring entry
   const bool prerot = a.ring_kraw != nullptr;
   const bf16* kpop_g = isring ? (prerot ? a.ring_kraw : a.sw_k) + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D
@@ -178,6 +184,25 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   const bf16* vpop_g = isring ? a.sw_v + (((size_t)b * WR + max(hd, 0)) * a.H + h) * D : a.v + (size_t)bh * D;
   const bf16* gpop_g = isring ? a.ring_g + (((size_t)b * WR + max(hd, 0)) * a.H + h) * M : a.g + (size_t)bh * M;
   bool failed = false;
+  // the step's token into the rings (called by the one CTA that finishes this (sequence, kv head))
+  auto append_token = [&]() {
+    if (!a.g_new) return;
+    const int row = a.nopop ? W - 1 : hd;                          // a filling ring holds W - 1 entries: next free row
+    const size_t at = ((size_t)b * WR + row) * a.H + h;
+    uint4* rk = reinterpret_cast<uint4*>(const_cast<bf16*>(a.sw_k) + at * D);
+    uint4* rv = reinterpret_cast<uint4*>(const_cast<bf16*>(a.sw_v) + at * D);
+    uint4* rg = reinterpret_cast<uint4*>(const_cast<bf16*>(a.ring_g) + at * M);
+    const uint4* kn = reinterpret_cast<const uint4*>(a.k + (size_t)bh * D);
+    const uint4* vn = reinterpret_cast<const uint4*>(a.v + (size_t)bh * D);
+    const uint4* gn = reinterpret_cast<const uint4*>(a.g_new + (size_t)bh * M);
+    const int nd = D / 8, ng = M / 8;
+    for (int i = tid; i < 2 * nd + ng; i += kStrThreads) {
+      if (i < nd) rk[i] = kn[i];
+      else if (i < 2 * nd) rv[i - nd] = vn[i - nd];
+      else rg[i - 2 * nd] = gn[i - 2 * nd];
+    }
+    if (tid == 0 && !a.nopop) const_cast<int*>(a.head)[bh] = hd + 1 == WR ? 0 : hd + 1;
+  };
 
   if (tid == 0) {
     for (int i = 0; i < kStrSlots + 1; ++i) umma::mbar_init(&bars[i], 1);
@@ -645,13 +670,17 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     }
   }
   if (failed && tid == 0 && a.err) atomicExch(a.err, 1);
-  if (SPL == 1) return;
+  if (SPL == 1) {
+    append_token();
+    return;
+  }
 
   if (a.cluster) {
     // ---- merge inside the cluster: CTA 0 reads the partial outputs, maxima and sums of its peers from their shared
     //      memory; the second barrier keeps the peers' memory alive until it has ----------------------------------
     cluster_sync_all();
     if (sp == 0) {
+      append_token();
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const int i = tid + u * kStrThreads;
@@ -692,6 +721,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  append_token();
   const float* all_ml = a.part_ml + (size_t)bh * SPL * NG * 2;
   const float* all_o = a.part_o + (size_t)bh * SPL * NG * V;
   if (SPL <= 4) {
@@ -871,7 +901,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
                       cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
-                      const void* ring_kraw) {
+                      const void* ring_kraw, const void* g_new) {
   DecodeStreamArgs a;
   a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
   a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
@@ -881,6 +911,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
   a.head = head; a.ring_g = (const bf16*)ring_g;
   a.WR = head ? ring_rows : W; a.nopop = head ? nopop : 0;
   a.ring_kraw = head ? (const bf16*)ring_kraw : nullptr;
+  a.g_new = (head && !ring_kraw) ? (const bf16*)g_new : nullptr;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
   a.zero_state = zero_state; a.scale = scale;

@@ -3,8 +3,9 @@
 The reference keeps the sliding window of a layer as three tensors that it shifts with ``torch.cat``
 on every generated token (``NHACache.update``, nha_fla/models/nha_cache.py:105-126) and hands the
 oldest entry to the layer with ``get_pop_kvf`` (:143-154).  Here the window lives in rings of ``W``
-rows per sequence and a per-sequence head index, all on the device; a decode step is two launches
-(``nha_decode_step_ring`` + ``nha_ring_append``).  Once the rings are full the launches carry no
+rows per sequence and an index of the oldest entry, all on the device; a decode step is ONE launch
+(``nha_decode_step_ring_fused``: the CTA that finishes a (sequence, kv head) also stores the step's token over the
+entry that left the window; with ``fused=False`` two launches, ``nha_decode_step_ring`` + ``nha_ring_append``).  Once the rings are full the launches carry no
 host-side state, so a step can be captured in a CUDA graph; while a short prompt is still filling them
 the host passes the fill level (one integer per layer) and nothing leaves the window, as in the
 reference, whose callers feed the op an all-zero entry then (qwennha.py:152-160).  The rings hold the raw (un-rotated) keys, the values and the log-decay rows ``g`` of the
@@ -29,7 +30,8 @@ class RingLayer:
     """Rings, head indices and slot memory of one layer."""
 
     def __init__(self, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, hk: torch.Tensor, hv: torch.Tensor,
-                 window_size: Optional[int] = None, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+                 window_size: Optional[int] = None, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                 fused: bool = True):
         # k [B,T,H,K], v [B,T,H,V], g [B,T,H,M]: the last T <= W tokens, oldest first; hk [B,H,K,M], hv [B,H,M,V] fp32.
         # With T < W the rings are still filling: entries in rows 0 .. T-1, `fill` counts them (host side).
         assert k.dim() == 4 and v.dim() == 4 and g.dim() == 4 and k.shape[:3] == v.shape[:3] == g.shape[:3]
@@ -42,7 +44,12 @@ class RingLayer:
             r[:, :x.shape[1]] = x.to(_BF16)
             return r
         self.ring_k, self.ring_v, self.ring_g = ring(k), ring(v), ring(g)
-        self.head = torch.zeros(k.shape[0], dtype=torch.int32, device=k.device)
+        # fused: the decode kernel also appends the step's token (one launch per step); the index of the oldest entry
+        # is then kept per (sequence, kv head), [B, H] with equal entries along H, because each (sequence, kv head) is
+        # finished - and advanced - by its own CTA.  Otherwise one index per sequence and a separate append launch.
+        self.fused = bool(fused) and rope is None
+        self.head = torch.zeros((k.shape[0], k.shape[2]) if self.fused else (k.shape[0],), dtype=torch.int32,
+                                device=k.device)
         self.hk = None if hk is None else hk.float().contiguous().clone()
         self.hv = None if hv is None else hv.float().contiguous().clone()
         # rope = (cos, sin) [1|B, T, K] of the T kept tokens' absolute positions: a second key ring holds the keys
@@ -106,7 +113,7 @@ class RingLayer:
         if self.fill < W:
             rows = torch.arange(self.fill, self.fill + n, device=self.head.device)[None].expand(self.head.shape[0], -1)
         else:
-            rows = (self.head.long()[:, None] + torch.arange(n, device=self.head.device)[None]) % W
+            rows = (self.oldest()[:, None] + torch.arange(n, device=self.head.device)[None]) % W
         b = torch.arange(self.head.shape[0], device=self.head.device)[:, None]
         for ring, x in ((self.ring_k, k), (self.ring_v, v), (self.ring_g, g)):
             ring[b, rows] = x.to(_BF16).reshape(x.shape[0], n, *ring.shape[2:])
@@ -115,12 +122,16 @@ class RingLayer:
         else:
             self.head.copy_((self.head + n) % W)
 
+    def oldest(self) -> torch.Tensor:
+        """Row of the oldest entry per sequence, ``[B]`` int64."""
+        return (self.head if self.head.dim() == 1 else self.head[:, 0]).long()
+
     def ordered(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """The window in time order (oldest first), as the reference cache would hold it (copies)."""
         W = self.window
         if self.fill < W:
             return self.ring_k[:, :self.fill].clone(), self.ring_v[:, :self.fill].clone(), self.ring_g[:, :self.fill].clone()
-        idx = (self.head.long()[:, None] + torch.arange(W, device=self.head.device)[None]) % W
+        idx = (self.oldest()[:, None] + torch.arange(W, device=self.head.device)[None]) % W
         gather = lambda r: torch.gather(r, 1, idx[:, :, None, None].expand(-1, -1, *r.shape[2:]))
         return gather(self.ring_k), gather(self.ring_v), gather(self.ring_g)
 
@@ -152,14 +163,23 @@ def fused_recurrent_nha_decode_ring(q: torch.Tensor, k: torch.Tensor, v: torch.T
     with torch.cuda.device(dev):                       # split count and launches follow the tensors' device
         ws = _decode_workspace(dev, B, HQ, H, V, W)
         st = _stream(dev)
-        _lib.check(lib.nha_decode_step_ring(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
-                                            layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), layer.head.data_ptr(),
-                                            cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2),
-                                            layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
-                                            ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st), 'nha_decode_step_ring')
-        _lib.check(lib.nha_ring_append(layer.ring_k.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
-                                       kc.data_ptr(), vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M,
-                                       W, fill, st), 'nha_ring_append')
+        if layer.fused:
+            if layer.head.shape[1] != H:               # rings made through update(): the kv-head count is known only now
+                layer.head = layer.head[:, :1].repeat(1, H)
+            _lib.check(lib.nha_decode_step_ring_fused(
+                qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), gc.data_ptr(), layer.ring_k.data_ptr(), layer.ring_v.data_ptr(),
+                layer.ring_g.data_ptr(), layer.head.data_ptr(), cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2),
+                layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(), ws.numel(), B, HQ, H, K, V, M, W, fill,
+                sc, st), 'nha_decode_step_ring_fused')
+        else:
+            _lib.check(lib.nha_decode_step_ring(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), layer.ring_k.data_ptr(),
+                                                layer.ring_v.data_ptr(), layer.ring_g.data_ptr(), layer.head.data_ptr(),
+                                                cosc.data_ptr(), sinc.data_ptr(), cs_batch, cosc.stride(-2),
+                                                layer.hk.data_ptr(), layer.hv.data_ptr(), o.data_ptr(), ws.data_ptr(),
+                                                ws.numel(), B, HQ, H, K, V, M, W, fill, sc, st), 'nha_decode_step_ring')
+            _lib.check(lib.nha_ring_append(layer.ring_k.data_ptr(), layer.ring_v.data_ptr(), layer.ring_g.data_ptr(),
+                                           kc.data_ptr(), vc.data_ptr(), gc.data_ptr(), layer.head.data_ptr(), B, H, K, V, M,
+                                           W, fill, st), 'nha_ring_append')
         _lib.check_decode_device(lib, ws, B, H, st, 'nha_decode_step_ring')
     layer.fill = min(fill + 1, W)
     return o
@@ -304,7 +324,7 @@ class NHARingCache:
 
     def init_layer(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, window_size: int,
                    recurrent_state: Tuple[torch.Tensor, torch.Tensor],
-                   rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> RingLayer:
+                   rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, fused: bool = True) -> RingLayer:
         """Fill a layer from its prefill: ``k, v, g [B,T,H,*]`` (the last ``window_size`` tokens are kept, as
         ``NHACache.update`` does; a shorter prompt leaves the rings partly filled) and the slot memory after the
         prefill.  With ``rope = (cos, sin) [1|B, T, K]`` (tables of the T tokens' absolute positions) the layer also
@@ -315,7 +335,7 @@ class NHARingCache:
         while len(self.layers) <= layer_idx:
             self.layers.append(None)
         layer = RingLayer(k[:, -window_size:], v[:, -window_size:], g[:, -window_size:], *recurrent_state,
-                          window_size=window_size, rope=rope)
+                          window_size=window_size, rope=rope, fused=fused)
         self.layers[layer_idx] = layer
         return layer
 
@@ -338,5 +358,5 @@ class NHARingCache:
         if L.fill < L.window:
             return (None, None, None)                 # as NHACache: nothing leaves a window that is not full
         b = torch.arange(L.head.shape[0], device=L.head.device)
-        pick = lambda r: r[b, L.head.long()].reshape(r.shape[0], 1, -1)
+        pick = lambda r: r[b, L.oldest()].reshape(r.shape[0], 1, -1)
         return pick(L.ring_k), pick(L.ring_v), pick(L.ring_g)

@@ -15,8 +15,10 @@ from tests.gpu_util import TOL_OUT, assert_close
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize('B,H,NG,D,M,W,steps', [(2, 2, 4, 64, 32, 64, 70), (3, 4, 8, 128, 64, 256, 20), (1, 1, 1, 64, 64, 16, 40)])
-def test_ring_decode_matches_shifted_window(B, H, NG, D, M, W, steps):
+@pytest.mark.parametrize('fused', [True, False], ids=['one_launch', 'two_launches'])
+@pytest.mark.parametrize('B,H,NG,D,M,W,steps', [(2, 2, 4, 64, 32, 64, 70), (3, 4, 8, 128, 64, 256, 20), (1, 1, 1, 64, 64, 16, 40),
+                                                (48, 4, 8, 128, 64, 512, 6)])
+def test_ring_decode_matches_shifted_window(B, H, NG, D, M, W, steps, fused):
     from nha_b200 import NHARingCache, fused_recurrent_nha_decode
     dev = 'cuda'
     g0 = torch.Generator().manual_seed(100 + W)
@@ -31,7 +33,8 @@ def test_ring_decode_matches_shifted_window(B, H, NG, D, M, W, steps):
     cos, sin = gen.rope_tables(W, D, first_pos=1000)
     cos, sin = cos.to(dev), sin.to(dev)
     cache = NHARingCache()
-    cache.init_layer(0, win_k, win_v, win_g, W, (hk, hv))
+    cache.init_layer(0, win_k, win_v, win_g, W, (hk, hv), fused=fused)
+    assert cache[0].head.shape == ((B, H) if fused else (B,))
     ref_k, ref_v, ref_g = win_k.clone(), win_v.clone(), win_g.clone()
     ref_hk, ref_hv = hk.clone(), hv.clone()
     for t in range(steps):
@@ -62,8 +65,9 @@ def test_ring_decode_matches_shifted_window(B, H, NG, D, M, W, steps):
     assert cache.get_seq_length() == steps
 
 
+@pytest.mark.parametrize('fused', [True, False], ids=['one_launch', 'two_launches'])
 @pytest.mark.parametrize('B,H,NG,D,M,W,T0,steps', [(2, 2, 4, 64, 32, 16, 0, 40), (2, 4, 8, 128, 64, 64, 5, 80)])
-def test_ring_decode_warm_up_matches_growing_window(B, H, NG, D, M, W, T0, steps):
+def test_ring_decode_warm_up_matches_growing_window(B, H, NG, D, M, W, T0, steps, fused):
     """A prompt shorter than the window: the rings fill up step by step.  Until they are full nothing leaves the
     window; the reference's callers hand the op an all-zero entry then (qwennha.py:152-160) and a window that grows
     by one token per step (NHACache.update).  Same flow here with the shifted-window decode as the reference arm."""
@@ -78,7 +82,8 @@ def test_ring_decode_warm_up_matches_growing_window(B, H, NG, D, M, W, T0, steps
     hk = (r(B, H, D, M) * 0.5).to(dev)
     hv = (r(B, H, M, D) * 0.5).to(dev)
     cache = NHARingCache()
-    cache.init_layer(0, win_k, win_v, win_g, W, (hk, hv))
+    cache.init_layer(0, win_k, win_v, win_g, W, (hk, hv), fused=fused)
+    assert cache[0].head.shape == ((B, H) if fused else (B,))
     ref_k, ref_v, ref_g = win_k.clone(), win_v.clone(), win_g.clone()
     ref_hk, ref_hv = hk.clone(), hv.clone()
     for t in range(steps):
