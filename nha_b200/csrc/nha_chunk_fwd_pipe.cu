@@ -62,7 +62,7 @@ constexpr int total = oBar + 256 + 1024;          // + slack for the 1024-byte a
 static_assert(64 * kLdA * 4 >= kSlot, "the decay table's storage doubles as a ring slot");
 static_assert(total <= 113 * 1024, "two CTAs of the pipelined output pass per SM");
 // mbarriers
-constexpr int bQ = 0, bFull = 1, bEmpty = 5, bTab = 9, bG = 10, bW = 11, bS = 12, bP = 14, bPV = 16, nBar = 17;
+constexpr int bQ = 0, bFull = 1, bEmpty = 5, bTab = 9, bG = 10, bW = 11, bS = 12, bP = 14, bPV = 16, bKq = 17, nBar = 18;
 constexpr int kPoll = 1 << 15;                    // polls of a bounded wait (each sleeps up to 20 us in hardware)
 constexpr float kDecayLimit = 140.0f;
 constexpr float kRaise = 5.545177f;               // 8 ln 2
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
   // ---- loads (warp 4) ---------------------------------------------------------------------------------------------
   // Ring slots and what passes through them, in fill order:
   //   slot 0: q_gsa k tile 0, Hv, window values of the even steps      slot 1: q_gsa k tile 1, v', window keys of the odd steps
-  //   slot 2: k', Hk, window keys of the even steps                    slot 3 (the decay table's storage): values of the odd steps
+  //   slot 2: Hk, window keys of the even steps (k' passes through the q_swa tiles)                    slot 3 (the decay table's storage): values of the odd steps
   // Fill number f of a slot waits for release number f - 1 of that slot (a commit of the MMA thread behind the last
   // product that read it); the first fill of slot 3 waits for the softmax group to have finished with the table.
   auto slot_ptr = [&](int slot) { return sm + (slot < 3 ? oRing + slot * kSlot : oA); };
@@ -195,9 +195,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
     __syncwarp();
   };
   // rows [r0, r0 + 64) of one kv head of a [tokens][H][128] tensor into a slot: by TMA when they lie inside [rlo, rhi)
-  auto load_rows = [&](int slot, const CUtensorMap* mp, const bf16* base, int r0, int rlo, int rhi) {
-    unsigned char* dst = slot_ptr(slot);
-    uint64_t* fb = &bar[bFull + slot];
+  auto load_rows_to = [&](unsigned char* dst, uint64_t* fb, const CUtensorMap* mp, const bf16* base, int r0, int rlo, int rhi) {
     if (r0 >= rlo && r0 + kChunk <= rhi) {
       if (lane == 0) {
         mbar_expect_tx(fb, 16384);
@@ -209,21 +207,25 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       if (lane == 0) mbar_arrive(fb);
     }
   };
+  auto load_rows = [&](int slot, const CUtensorMap* mp, const bf16* base, int r0, int rlo, int rhi) {
+    load_rows_to(slot_ptr(slot), &bar[bFull + slot], mp, base, r0, rlo, rhi);
+  };
   if (warp == 4) {
+    // Everything the first product group needs goes in flight at once: q_gsa (k tile kt into slot kt; rows 0-63 head hq0,
+    // rows 64-127 head hq0 + 1), Hk into slot 2, and k' into the first half of the q_swa tiles, which the window steps
+    // need only much later (q_swa is fetched once A = q k'^T has read k').
     if (lane == 0) {
-      // q_swa (its own tiles) and q_gsa (k tile kt into slot kt): rows 0-63 head hq0, rows 64-127 head hq0 + 1
-      mbar_expect_tx(&bar[bQ], 32768);
       mbar_expect_tx(&bar[bFull + 0], 16384);
       mbar_expect_tx(&bar[bFull + 1], 16384);
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-        for (int kt = 0; kt < 2; ++kt) {
+        for (int kt = 0; kt < 2; ++kt)
           tma_load_3d(slot_ptr(kt) + hh * 8192, &maps.qg, 64 * kt, hq0 + hh, tq0 + c0, &bar[bFull + kt]);
-          tma_load_3d(sm + oQS + kt * kQTile + hh * 8192, &maps.qs, 64 * kt, hq0 + hh, tq0 + c0, &bar[bQ]);
-        }
+      mbar_expect_tx(&bar[bFull + 2], 16384);
+      tma_load_2d(slot_ptr(2), &maps.hk, 0, (cg * H + h) * D, &bar[bFull + 2]);              // Hk [128][64]
     }
-    load_rows(2, &maps.kg, (const bf16*)d.k_gsa, c0 - shift, 0, hi);          // k'
+    load_rows_to(sm + oQS, &bar[bQ], &maps.kg, (const bf16*)d.k_gsa, c0 - shift, 0, hi);     // k'
   }
 
   // ---- decay tables (threads 0..127), as in nha_chunk_fwd_umma.cu -------------------------------------------------
@@ -306,10 +308,14 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
 
   if (warp == 4) {
     // ================= load warp: the rest of the slot operands, then the window tiles ===============================
-    NHA_WAIT(bEmpty + 2, 0);                                                   // k' has been read (A = q k'^T)
+    NHA_WAIT(bKq, 0);                                                          // k' has been read (A = q k'^T)
     if (lane == 0) {
-      mbar_expect_tx(&bar[bFull + 2], 16384);
-      tma_load_2d(slot_ptr(2), &maps.hk, 0, (cg * H + h) * D, &bar[bFull + 2]);            // Hk [128][64]
+      mbar_expect_tx(&bar[bQ], 32768);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt)
+          tma_load_3d(sm + oQS + kt * kQTile + hh * 8192, &maps.qs, 64 * kt, hq0 + hh, tq0 + c0, &bar[bQ]);
     }
     NHA_WAIT(bEmpty + 0, 0);                                                   // q_gsa has been read (QH = q Hk)
     if (lane == 0) {
@@ -327,7 +333,8 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       bool did = false;
       if (kn < nst) {
         const int slot = (kn & 1) ? 1 : 2;
-        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + slot], (1 + (kn >> 1)) & 1) : 0;
+        // fill f of a slot waits for its release f - 1; keys are fills 1, 2, .. of slot 2 (after Hk) and 2, 3, .. of slot 1
+        const int free_ = lane == 0 ? (int)mbar_test(&bar[bEmpty + slot], ((kn & 1) + (kn >> 1)) & 1) : 0;
         if (__shfl_sync(0xffffffffu, free_, 0)) {
           load_rows(slot, &maps.ks, (const bf16*)d.k_swa, (ci - kn) * kChunk, 0, len);
           ++kn;
@@ -376,20 +383,21 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       };
       auto s_mma = [&](int j) {          // S_j into accumulator j & 1, then release the keys
         const int slot = (j & 1) ? 1 : 2;
-        wait_full(slot, 2 + (j >> 1));
+        wait_full(slot, (j & 1) + 1 + (j >> 1));
         mma_run<8, 0>((j & 1) ? cS1 : cS0, dQS, kT16, make_desc(aS[slot]), 8192 >> 4, iK, false);
         commit(&bar[bS + (j & 1)]);
         commit(&bar[bEmpty + slot]);
       };
       uint32_t wph = 0u;
-      // G1: A = q k'^T (q_gsa k tiles in slots 0 and 1, 16384 bytes apart; k' in slot 2), then QH = q Hk (Hk in slot 2)
+      // G1: A = q k'^T (q_gsa k tiles in slots 0 and 1, 16384 bytes apart; k' in the q_swa tiles), QH = q Hk (Hk in slot 2)
       wait_full(0, 0);
       wait_full(1, 0);
-      wait_full(2, 0);
+      NHA_WAIT(bQ, 0);                                   // k' in the first half of the q_swa tiles
+      tc_fence_after();
       const uint64_t dQG = make_desc(aS[0]);
-      mma_run<8, 0>(cS0, dQG, kSlot >> 4, make_desc(aS[2]), 8192 >> 4, iK, false);
-      commit(&bar[bEmpty + 2]);
-      wait_full(2, 1);
+      mma_run<8, 0>(cS0, dQG, kSlot >> 4, make_desc(smem_u32(sm + oQS)), 8192 >> 4, iK, false);
+      commit(&bar[bKq]);
+      wait_full(2, 0);
       mma_run<8, 1>(cS1, dQG, kSlot >> 4, make_desc(aS[2]), 0, iMN, false);
       commit(&bar[bG]);
       commit(&bar[bEmpty + 0]);
@@ -408,7 +416,7 @@ __global__ void __launch_bounds__(pipe::kThreads, 2)
       mma_ta(cS1, cS0 + 32, dSB, false, iK, false);
       commit(&bar[bG]);
       commit(&bar[bEmpty + 0]);
-      NHA_WAIT(bQ, 0);
+      NHA_WAIT(bQ, 1);                                   // q_swa
       s_mma(0);                                          // S0 is free once G3 has read the operands in it (in order)
       // G4: O += tril(Bv) v', tril(Bv) in the first 32 columns of S1
       NHA_WAIT(bW, wph); wph ^= 1u;

@@ -13,6 +13,7 @@
 // Replaces chunk_nha_fused_state_kernel (nha_fla/ops/nha/chunk_fused.py:31-114) and the state part of
 // fla's chunk_gsa_fwd reached from nha_fla/ops/nha/chunk_gsa.py:38-45; the in-sequence shift replaces
 // _packed_shift_right / _batch_shift_right (nha_fla/ops/nha/chunk.py:53-111).
+#include <algorithm>
 #include <mutex>
 
 #include "nha_common.cuh"
@@ -226,13 +227,14 @@ __global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_c
 // and the chunk's gate totals through a ring of kScanStages stages of kScanGroup chunks each (one bulk copy per slice,
 // completion counted on the stage's mbarrier), so that tens of chunks are in flight per CTA whatever the sequence
 // length - with one long sequence and few heads there are only N*H*SD/1024 CTAs to keep the memory system busy.
-constexpr int kScanElems = 512;                  // state elements per CTA
-constexpr int kScanThreads = kScanElems / 4;      // consumer threads; one more warp hosts the producer
 constexpr int kScanGroup = 8;                     // chunks per ring stage (two copies each: at most 16 issuing lanes)
-constexpr int kScanStages = 5;
-constexpr int kScanSlot = kScanElems * 2 + 512;   // bytes per chunk in a stage: the L slice, then up to 128 gate totals
+constexpr int kScanMaxStages = 10;
 constexpr int kScanPoll = 1 << 12;
-constexpr int kScanSmem = kScanStages * kScanGroup * kScanSlot + 2 * kScanStages * 8 + 16;
+// ELEMS state elements per CTA (a thread owns four); bytes per chunk in a stage: the L slice, then up to 128 gate totals
+__host__ __device__ constexpr int scan_slot_bytes(int elems) { return elems * 2 + 512; }
+__host__ __device__ constexpr int scan_smem_bytes(int elems, int stages) {
+  return stages * kScanGroup * scan_slot_bytes(elems) + 2 * kScanMaxStages * 8 + 16;
+}
 
 // bounded wait without a suspend-time hint: the consumers of the scan wait often and briefly
 __device__ __forceinline__ bool scan_wait(uint64_t* mbar, uint32_t parity) {
@@ -254,8 +256,11 @@ __device__ __forceinline__ void scan_bulk_g2s(void* dst, const void* src, uint32
                : "memory");
 }
 
-__global__ void __launch_bounds__(kScanThreads + 32) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w,
-                                                                           int* __restrict__ err) {
+template <int kScanElems>
+__global__ void __launch_bounds__(kScanElems / 4 + 32) nha_state_scan_kernel(const nha_chunk_desc d, const StateWs w,
+                                                                             int* __restrict__ err, const int kScanStages) {
+  constexpr int kScanThreads = kScanElems / 4;      // consumer threads; one more warp hosts the producer
+  constexpr int kScanSlot = scan_slot_bytes(kScanElems);
   const int K = d.K, V = d.V, M = d.M, H = d.H;
   const int KM = K * M, MV = M * V;
   const size_t SD = (size_t)KM + MV;
@@ -269,8 +274,8 @@ __global__ void __launch_bounds__(kScanThreads + 32) nha_state_scan_kernel(const
   const int tid = threadIdx.x;
   extern __shared__ __align__(128) unsigned char scan_smem[];
   uint64_t* full = (uint64_t*)(scan_smem + kScanStages * kScanGroup * kScanSlot);
-  uint64_t* empty = full + kScanStages;
-  volatile int* abort_flag = (volatile int*)(empty + kScanStages);
+  uint64_t* empty = full + kScanMaxStages;
+  volatile int* abort_flag = (volatile int*)(empty + kScanMaxStages);
   if (tid == 0) {
     for (int s = 0; s < kScanStages; ++s) {
       umma::mbar_init(&full[s], 1);
@@ -338,28 +343,38 @@ __global__ void __launch_bounds__(kScanThreads + 32) nha_state_scan_kernel(const
     }
     const int cnt = min(kScanGroup, nchunks - it * kScanGroup);
     if (active) {
+      // everything the stage holds for this thread comes into registers first (the stores below go through generic
+      // pointers, so the compiler will not move a shared-memory load across them): the serial part is then four
+      // multiply-adds per chunk
+      uint2 la[kScanGroup];
+      float4 da[kScanGroup];
+#pragma unroll
+      for (int u = 0; u < kScanGroup; ++u) {
+        const unsigned char* slot = scan_smem + (size_t)(s * kScanGroup + u) * kScanSlot;
+        la[u] = *reinterpret_cast<const uint2*>(slot + 8 * tid);
+        const float* gp = reinterpret_cast<const float*>(slot + kScanElems * 2) + m;
+        if (is_k) da[u] = *reinterpret_cast<const float4*>(gp);
+        else da[u] = make_float4(*gp, 0.f, 0.f, 0.f);
+      }
+      float4 av[kScanGroup];
+#pragma unroll
+      for (int u = 0; u < kScanGroup; ++u) {
+        if (is_k) av[u] = make_float4(__expf(da[u].x), __expf(da[u].y), __expf(da[u].z), __expf(da[u].w));
+        else { const float x = __expf(da[u].x); av[u] = make_float4(x, x, x, x); }
+      }
 #pragma unroll
       for (int u = 0; u < kScanGroup; ++u) {
         if (u < cnt) {
-          const unsigned char* slot = scan_smem + (size_t)(s * kScanGroup + u) * kScanSlot;
-          const uint2 la = *reinterpret_cast<const uint2*>(slot + 8 * tid);
-          const float* gp = reinterpret_cast<const float*>(slot + kScanElems * 2) + m;
-          float4 da;
-          if (is_k) da = *reinterpret_cast<const float4*>(gp);
-          else da.x = *gp;
           const size_t cgi = (size_t)(chunk0 + it * kScanGroup + u) * H + h;
           uint2 o;
           *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(run.x, run.y);
           *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(run.z, run.w);
           *reinterpret_cast<uint2*>(out + cgi * per + e) = o;
-          float4 a;
-          if (is_k) a = make_float4(__expf(da.x), __expf(da.y), __expf(da.z), __expf(da.w));
-          else { const float x = __expf(da.x); a = make_float4(x, x, x, x); }
-          if (sums) { gsum.x += da.x; gsum.y += da.y; gsum.z += da.z; gsum.w += da.w; }
-          const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la.x));
-          const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la.y));
-          run.x = run.x * a.x + l01.x; run.y = run.y * a.y + l01.y;
-          run.z = run.z * a.z + l23.x; run.w = run.w * a.w + l23.y;
+          if (sums) { gsum.x += da[u].x; gsum.y += da[u].y; gsum.z += da[u].z; gsum.w += da[u].w; }
+          const float2 l01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].x));
+          const float2 l23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&la[u].y));
+          run.x = run.x * av[u].x + l01.x; run.y = run.y * av[u].y + l01.y;
+          run.z = run.z * av[u].z + l23.x; run.w = run.w * av[u].w + l23.y;
         }
       }
     }
@@ -409,11 +424,29 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
     if (st != NHA_OK) return st;
   }
   {
-    cudaError_t e = set_max_smem((const void*)nha_state_scan_kernel, kScanSmem);
-    if (e != cudaSuccess) return record_cuda_error(e);
+    // Ring depth and CTA width: the scan of one CTA is a serial walk over the sequence's chunks whose inputs take a
+    // memory round trip to arrive, so its speed is (chunks in flight) / (round trip).  Few CTAs (one long sequence, few
+    // heads): 1024 elements per CTA and as deep a ring as the longest sequence can use; many CTAs (a batch): 512
+    // elements and a ring short enough for several CTAs per SM.
+    int maxlen = d->max_seqlen > 0 ? d->max_seqlen : (int)d->Ttot;
+    const int rounds = ((maxlen + kChunk - 1) / kChunk + kScanGroup - 1) / kScanGroup;
+    const int64_t wide_ctas = (int64_t)d->N * d->H * ((SD + 1023) / 1024);
     int* err = d->plan + d->N + 1 + NCB + (size_t)NCB * d->H;
-    nha_state_scan_kernel<<<dim3((unsigned)(d->N * d->H), (unsigned)((SD + kScanElems - 1) / kScanElems)), kScanThreads + 32,
-                            kScanSmem, cs>>>(*d, w, err);
+    if (wide_ctas <= 160) {
+      const int stages = std::max(2, std::min(kScanMaxStages, rounds));
+      const int smem = scan_smem_bytes(1024, stages);
+      cudaError_t e = set_max_smem((const void*)nha_state_scan_kernel<1024>, smem);
+      if (e != cudaSuccess) return record_cuda_error(e);
+      nha_state_scan_kernel<1024><<<dim3((unsigned)(d->N * d->H), (unsigned)((SD + 1023) / 1024)), 1024 / 4 + 32, smem, cs>>>(
+          *d, w, err, stages);
+    } else {
+      const int stages = std::max(2, std::min(5, rounds));
+      const int smem = scan_smem_bytes(512, stages);
+      cudaError_t e = set_max_smem((const void*)nha_state_scan_kernel<512>, smem);
+      if (e != cudaSuccess) return record_cuda_error(e);
+      nha_state_scan_kernel<512><<<dim3((unsigned)(d->N * d->H), (unsigned)((SD + 511) / 512)), 512 / 4 + 32, smem, cs>>>(
+          *d, w, err, stages);
+    }
   }
   return check_launch();
 }
