@@ -52,7 +52,7 @@ CFG = dict(B=16, T=2048, H=16, D=64, M=64, W=64, shift=0)
 WORKLOAD = 'nha_attn_fwd_bwd B16 T2048 H16 D64 M64 W64 chunk64 bf16 (340M-layer shape)'
 CPU_SLICE_T = 512                             # tokens of the B=1 slice both CPU measurements run (cost grows with T)
 # dram__bytes_read.sum + dram__bytes_write.sum of all kernels of one step per token, from the committed ncu captures
-NCU_STEP_TRAFFIC_PER_TOKEN = 1107.8e6 / 8192       # profiles/step_traffic_chunk_fwd_bwd_B4_T2048.md
+NCU_STEP_TRAFFIC_PER_TOKEN = 1104.2e6 / 8192       # profiles/step_traffic_chunk_fwd_bwd_B4_T2048.md
 ALG_BYTES_PER_TOKEN = 16512 + 32832          # forward + backward, all 16 heads (each input read once per pass)
 NAMES = ('q_swa', 'k_swa', 'q_gsa', 'k_gsa', 'v', 's', 'g')
 
