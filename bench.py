@@ -487,6 +487,76 @@ def bench_rotary(lib, dev, rank, timed, peak):
                          'frac': nbytes / (ms * 1e-3) / 1e9 / peak}}
 
 
+def bench_layer_ops(lib, dev, rank, timed, peak):
+    """The layer's element-wise work around the operator at the bench workload's shape (B16 T2048 H16 D64, hidden 1024):
+    feature map of q and k with silu(v) in one launch (nha_fla/layers/nha.py:219-223) and silu + RMS norm in front of the
+    output projection (nha_fla/layers/nha.py:277-278), forward and backward through the C ABI, beside the same lines in
+    torch with autograd."""
+    import ctypes
+    import torch.nn.functional as F
+    B, T, H, K = 16, 2048, 16, 64
+    gd = torch.Generator(device=dev).manual_seed(41 + rank)
+    mk = lambda *sh: torch.randn(*sh, generator=gd, device=dev).bfloat16()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    xs = [mk(B * T, H, K) for _ in range(3)]
+    dys = [mk(B * T, H, K) for _ in range(3)]
+    ys = [torch.empty_like(x) for x in xs]
+    arr = lambda ts: (ctypes.c_void_p * 3)(*[t.data_ptr() for t in ts])
+    n3 = (ctypes.c_int64 * 3)(*[x.numel() for x in xs])
+
+    def fm_fwd():
+        assert lib.nha_act3_fwd(arr(xs), arr(ys), n3, None, 3, stream) == 0
+
+    def fm_bwd():
+        assert lib.nha_act3_bwd(arr(xs), arr(dys), arr(ys), n3, None, 3, stream) == 0
+    xg = [x.clone().requires_grad_(True) for x in xs]
+
+    def fm_torch():
+        torch.autograd.backward([F.silu(x) for x in xg], dys)
+    rows, cols = B * T, H * K
+    o, dy, y, d_o = mk(rows, cols), mk(rows, cols), torch.empty(rows, cols, dtype=torch.bfloat16, device=dev), None
+    d_o = torch.empty_like(o)
+    w = torch.rand(cols, generator=gd, device=dev) + 0.5
+    bias = torch.zeros(cols, device=dev)
+    rstd = torch.empty(rows, device=dev)
+    nparts = int(lib.nha_silu_rmsnorm_bwd_ctas(rows))
+    pw, pb = torch.empty(nparts, cols, device=dev), torch.empty(nparts, cols, device=dev)
+
+    def nm_fwd():
+        assert lib.nha_silu_rmsnorm_fwd(o.data_ptr(), w.data_ptr(), bias.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, cols,
+                                        1e-5, stream) == 0
+
+    def nm_bwd():
+        assert lib.nha_silu_rmsnorm_bwd(o.data_ptr(), w.data_ptr(), rstd.data_ptr(), dy.data_ptr(), d_o.data_ptr(),
+                                        pw.data_ptr(), pb.data_ptr(), rows, cols, stream) == 0
+        pw.sum(0), pb.sum(0)
+    og, wg, bg = o.clone().requires_grad_(True), w.clone().requires_grad_(True), bias.clone().requires_grad_(True)
+
+    def nm_torch():
+        x = F.silu(og).float()
+        (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * wg + bg).to(og.dtype).backward(dy)
+    res = {}
+    for name, fn in (('fm_fwd', fm_fwd), ('fm_bwd', fm_bwd), ('fm_torch', fm_torch), ('nm_fwd', nm_fwd), ('nm_bwd', nm_bwd),
+                     ('nm_torch', nm_torch)):
+        for _ in range(3):
+            fn()
+        res[name] = timed(fn, 20) / 20
+    e3, eo = 3 * xs[0].numel() * 2, o.numel() * 2
+    gbs = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9
+    return {'workload': 'feature map of q, k + silu(v) (B16 T2048 H16 D64: 201 MB per tensor set) and silu + RMS norm over '
+                        'hidden 1024 (67 MB), bf16; every pass larger than L2',
+            'feature_maps': {'fwd_ms': res['fm_fwd'], 'bwd_ms': res['fm_bwd'], 'torch_fwd_bwd_ms': res['fm_torch'],
+                             'fwd_gbs': gbs(2 * e3, res['fm_fwd']), 'bwd_gbs': gbs(3 * e3, res['fm_bwd']), 'gpu_launches': 2},
+            'silu_rms_norm': {'fwd_ms': res['nm_fwd'], 'bwd_ms': res['nm_bwd'], 'torch_fwd_bwd_ms': res['nm_torch'],
+                              'fwd_gbs': gbs(2 * eo, res['nm_fwd']), 'bwd_gbs': gbs(3 * eo, res['nm_bwd']),
+                              'gpu_launches': '1 forward; 1 + two small column sums backward'},
+            'roofline': {'bound': 'hbm', 'peak': peak, 'unit': 'GB/s',
+                         'achieved': gbs(5 * e3, res['fm_fwd'] + res['fm_bwd']),
+                         'frac': gbs(5 * e3, res['fm_fwd'] + res['fm_bwd']) / peak,
+                         'silu_rms_norm_achieved': gbs(5 * eo, res['nm_fwd'] + res['nm_bwd']),
+                         'silu_rms_norm_frac': gbs(5 * eo, res['nm_fwd'] + res['nm_bwd']) / peak}}
+
+
 def bench_lse_stats(lib, dev, rank, timed):
     """The training layer's aux loss and compression statistic at the bench shape (T*HQ = 524288 log-sum-exp pairs,
     4 MB): one launch for both means plus one for the gradient, beside the layer's chain of torch kernels with
@@ -626,7 +696,7 @@ def main():
     if args.pre_op:
         pk = peaks()[0]
         out = {'gates': bench_gates(lib, dev, rank, timed, pk), 'rotary': bench_rotary(lib, dev, rank, timed, pk),
-               'lse_stats': bench_lse_stats(lib, dev, rank, timed)}
+               'lse_stats': bench_lse_stats(lib, dev, rank, timed), 'layer_ops': bench_layer_ops(lib, dev, rank, timed, pk)}
         if rank == 0:
             emit(out)
         return 0
@@ -799,7 +869,8 @@ def main():
                   'varlen': bench_varlen(dev, rank, timed),
                   'gates': bench_gates(lib, dev, rank, timed, peak),
                   'rotary': bench_rotary(lib, dev, rank, timed, peak),
-                  'lse_stats': bench_lse_stats(lib, dev, rank, timed)}
+                  'lse_stats': bench_lse_stats(lib, dev, rank, timed),
+                  'layer_ops': bench_layer_ops(lib, dev, rank, timed, peak)}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

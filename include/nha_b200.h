@@ -323,6 +323,34 @@ int nha_rope_pair(const void* q, const void* k, void* q_out, void* k_out, const 
                   int H, int K, int offset, int inverse, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Feature map and value activation of the calling layer, up to three tensors in one launch
+ * (nha_fla/layers/nha.py:219-223: q_gsa = feature_map(q), k_gsa = feature_map(k), v = silu(v); the 'swish'
+ * feature map of flash-linear-attention is x * sigmoid(x), the same function as silu; 'relu' is max(x, 0)).
+ *   x, y (dx), dy: host arrays of `count` (1..3) device pointers, bf16, n[i] elements each, contiguous,
+ *   16-byte aligned; relu[i] != 0 selects max(x, 0) for tensor i (NULL: all swish).  y may alias x.
+ *   nha_act3_bwd: dx = dy * act'(x). */
+int nha_act3_fwd(const void* const* x, void* const* y, const int64_t* n, const int* relu, int count, void* stream);
+int nha_act3_bwd(const void* const* x, const void* const* dy, void* const* dx, const int64_t* n, const int* relu,
+                 int count, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Output side of the calling layer: the normalisation in front of the output projection
+ * (nha_fla/layers/nha.py:277-278, o = rms_norm_linear(silu(o), g_norm.weight, g_norm.bias, o_proj.weight,
+ * o_proj.bias); flash-linear-attention's rms_norm_linear is RMS norm + affine, then F.linear).
+ *   nha_silu_rmsnorm_fwd: y = silu(o) * rstd * weight + bias with rstd = rsqrt(mean(silu(o)^2) + eps) per row;
+ *     o, y bf16 [rows, cols]; weight, bias (may be NULL) fp32 [cols]; rstd fp32 [rows] (may be NULL; needed by
+ *     the backward).  cols a multiple of 256, at most 2048 (NHA_ERR_UNSUPPORTED otherwise).
+ *   nha_silu_rmsnorm_bwd: d_o from dy (gradient of y); part_w, part_b (may be NULL) fp32
+ *     [nha_silu_rmsnorm_bwd_ctas(rows), cols]: per-CTA partial sums of the weight and bias gradients, to be
+ *     summed over their first axis by the caller.
+ * The projection itself is a plain GEMM and stays with the GEMM library. */
+int nha_silu_rmsnorm_fwd(const void* o, const float* weight, const float* bias, void* y, float* rstd, int64_t rows,
+                         int cols, float eps, void* stream);
+int nha_silu_rmsnorm_bwd_ctas(int64_t rows);
+int nha_silu_rmsnorm_bwd(const void* o, const float* weight, const float* rstd, const void* dy, void* d_o,
+                         float* part_w, float* part_b, int64_t rows, int cols, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Layer-side consumers of lse_swa / lse_gsa, fused (the training layer's aux loss and compression
  * statistic, nha_fla/layers/nha.py:255-264, 288-323): with delta = lse_gsa - lse_swa over n = T*HQ
  * elements (fp32),

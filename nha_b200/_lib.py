@@ -76,6 +76,13 @@ SYMBOLS = {
     'nha_chunk_state_pass_static': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd_stage': (C.c_int, [C.POINTER(ChunkDesc), C.c_int, c_void_p]),
     'nha_slot_gates_fwd': (C.c_int, [c_void_p, c_void_p, c_void_p, C.c_int64, C.c_float, c_void_p]),
+    'nha_act3_fwd': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, C.c_int, c_void_p]),
+    'nha_act3_bwd': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, C.c_int, c_void_p]),
+    'nha_silu_rmsnorm_fwd': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, C.c_int64, C.c_int, C.c_float,
+                                       c_void_p]),
+    'nha_silu_rmsnorm_bwd_ctas': (C.c_int, [C.c_int64]),
+    'nha_silu_rmsnorm_bwd': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, C.c_int64,
+                                       C.c_int, c_void_p]),
     'nha_rope_pair': (C.c_int, [c_void_p] * 6 + [C.c_int64, C.c_int, c_void_p, C.c_int, C.c_int, C.c_int64] + [C.c_int] * 5
                       + [c_void_p]),
     'nha_lse_stats_scratch_bytes': (C.c_int64, []),

@@ -47,6 +47,8 @@ __all__ = [
     "decode_step",
     "recurrent_step",
     "slot_gates",
+    "feature_maps",
+    "silu_rms_norm",
     "rotary_positions",
     "gsa_aux",
     "rel_l2",
@@ -257,6 +259,24 @@ def rotary_positions(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     s = sin.double()[positions, None, :R]
     x0, x1 = x[..., :R], x[..., R:]
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], -1)
+
+
+def feature_maps(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, feature_map: str = 'swish'):
+    """The layer's feature map on q and k and ``silu`` on v in fp64 (nha_fla/layers/nha.py:219-223; the 'swish'
+    feature map of flash-linear-attention 0.5.1 is ``x * sigmoid(x)``, 'relu' is ``max(x, 0)``)."""
+    act = (lambda x: x * torch.sigmoid(x)) if feature_map == 'swish' else torch.relu
+    q, k, v = q.double(), k.double(), v.double()
+    return act(q), act(k), v * torch.sigmoid(v)
+
+
+def silu_rms_norm(o: torch.Tensor, weight: torch.Tensor, bias=None, eps: float = 1e-5) -> torch.Tensor:
+    """``rms_norm(silu(o)) * weight + bias`` over the last dimension in fp64: what the layer's
+    ``rms_norm_linear(F.silu(o), ...)`` computes in front of its projection (nha_fla/layers/nha.py:277-278;
+    flash-linear-attention 0.5.1 ``layer_norm_linear(..., is_rms_norm=True)``, eps 1e-5)."""
+    x = o.double()
+    x = x * torch.sigmoid(x)
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.double()
+    return y if bias is None else y + bias.double()
 
 
 def gsa_aux(lse_swa: torch.Tensor, lse_gsa: torch.Tensor, target: float) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -181,3 +181,24 @@ def test_gsa_aux_against_the_layer_chain():
     d2 = lg2 - ls
     (g2,) = torch.autograd.grad(F.binary_cross_entropy_with_logits(d2, torch.full_like(d2, 0.3)), lg2)
     assert torch.allclose(g1, g2, rtol=0, atol=1e-15)
+
+
+def test_layer_activations_and_norm_against_fla_references():
+    """The oracle's feature map / value activation and its silu + RMS norm against the layer's own lines
+    (nha_fla/layers/nha.py:219-223, 277-278) written with the third-party pieces they call: torch's silu / relu (the
+    swish feature map of flash-linear-attention 0.5.1 is x * sigmoid(x)) and fla.modules.layernorm.rms_norm_ref."""
+    import torch.nn.functional as F
+    torch.manual_seed(11)
+    q, k, v = (torch.randn(2, 9, 3, 16, dtype=torch.float64) * 2 for _ in range(3))
+    qg, kg, va = orc.feature_maps(q, k, v, 'swish')
+    assert torch.allclose(qg, F.silu(q), atol=1e-15) and torch.allclose(kg, F.silu(k), atol=1e-15)
+    assert torch.allclose(va, F.silu(v), atol=1e-15)
+    qr, kr, _ = orc.feature_maps(q, k, v, 'relu')
+    assert torch.equal(qr, F.relu(q)) and torch.equal(kr, F.relu(k))
+    o = torch.randn(7, 256, dtype=torch.float64) * 3
+    w, b = torch.rand(256, dtype=torch.float64) + 0.5, torch.randn(256, dtype=torch.float64) * 0.1
+    got = orc.silu_rms_norm(o, w, b, 1e-5)
+    ln = pytest.importorskip('fla.modules.layernorm')
+    want = ln.rms_norm_ref(F.silu(o), w, b, eps=1e-5)
+    assert torch.allclose(got, want, rtol=0, atol=1e-13)
+    assert torch.allclose(orc.silu_rms_norm(o, w, None, 1e-5), ln.rms_norm_ref(F.silu(o), w, None, eps=1e-5), atol=1e-13)
