@@ -225,6 +225,28 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     ms = by_mode[2]
     per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
     gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
+    # the slot memory kept in bf16 (an extension; the reference keeps fp32 states): half the state bytes per step
+    for d in layers:
+        d['hk16'], d['hv16'] = d['hk'].bfloat16(), d['hv'].bfloat16()
+
+    def step_bf16_state():
+        for d in layers:
+            st = lib.nha_decode_step_bf16_state(d['q'].data_ptr(), None, d['k'].data_ptr(), d['v'].data_ptr(),
+                                                d['g'].data_ptr(), None, d['sw_k'].data_ptr(), d['sw_v'].data_ptr(),
+                                                cos.data_ptr(), sin.data_ptr(), 0, cos.stride(1), d['hk16'].data_ptr(),
+                                                d['hv16'].data_ptr(), 0, d['o'].data_ptr(), ws.data_ptr(), ws.numel(), B,
+                                                H * NG, H, K, K, M, W, K ** -0.5, stream)
+            assert st == 0
+    for _ in range(3):
+        step_bf16_state()
+    ms16 = timed(step_bf16_state, 200) / 200
+    per_seq_layer16 = per_seq_layer - H * (K * M + M * K) * 4
+    bf16_state = {'us_per_layer': 1e3 * ms16 / LAYERS, 'tokens_per_s': world * B / (ms16 * 1e-3),
+                  'gbs': per_seq_layer16 * B * LAYERS / (ms16 * 1e-3) / 1e9,
+                  'frac': per_seq_layer16 * B * LAYERS / (ms16 * 1e-3) / 1e9 / peak,
+                  'algorithmic_bytes_per_launch': per_seq_layer16 * B,
+                  'note': 'slot memory in bf16 (nha_decode_step_bf16_state): not the reference\'s numerics, reported beside '
+                          'the fp32-state figure'}
     # the same stack with the cache maintenance of one generated token inside the timed region: the reference's
     # NHACache shifts each layer's window with torch.cat (keys, values, gate rows) and pops the oldest entry; the
     # ring cache replaces that with nha_decode_step_ring + nha_ring_append
@@ -307,6 +329,7 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     return {'workload': 'decode 48 layers x 32 seq/GPU HQ32 H4 D128 M64 W512 bf16, fp32 state', 'ms_per_token_step': ms,
             'with_cache_update': with_cache,
             'tokens_per_s': world * B / (ms * 1e-3), 'us_per_layer': 1e3 * ms / LAYERS,
+            'bf16_state': bf16_state,
             'dependent_launch': {'us_per_layer_plain': 1e3 * by_mode[0] / LAYERS,
                                  'us_per_layer_wait_first': 1e3 * by_mode[1] / LAYERS,
                                  'us_per_layer_early_requests': 1e3 * by_mode[2] / LAYERS,

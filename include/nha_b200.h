@@ -85,6 +85,18 @@ int nha_decode_step(const void* q, const void* sq, const void* k, const void* v,
                     int64_t cs_row, const void* win_logits, float* hk, float* hv, int zero_state, void* o,
                     float* win_prob, void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K, int V,
                     int M, int W, float scale, void* stream);
+
+/* nha_decode_step with the slot memory kept in bf16 (hk [B,H,K,M], hv [B,H,M,V] bf16, 16-byte aligned, updated in
+ * place): half the state bytes per step.  Arithmetic stays fp32 in registers; the state is rounded once per step when
+ * it is stored, and the step's own readout uses the rounded values, so a step sees exactly what the next one reads.
+ * An extension: the reference keeps fp32 states (nha_fla/ops/nha/fused_recurrent.py:536-545), so results follow it
+ * only to bf16 accuracy of the state.  Window-key mode with K == V in {64, 128} (streaming kernel) only;
+ * NHA_ERR_UNSUPPORTED otherwise.  Arguments as nha_decode_step without win_logits / win_prob. */
+int nha_decode_step_bf16_state(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
+                               const void* sw_k, const void* sw_v, const void* cos, const void* sin, int64_t cs_batch,
+                               int64_t cs_row, void* hk, void* hv, int zero_state, void* o, void* workspace,
+                               int64_t workspace_bytes, int B, int HQ, int H, int K, int V, int M, int W, float scale,
+                               void* stream);
 /* Programmatic dependent launch of the streaming decode kernel (the reference chains its two decode kernels the same
  * way and switches it with the environment variable NHA_PDL, nha_fla/ops/nha/fused_recurrent.py:13-44, 560-582).
  *   0  plain launches.

@@ -46,6 +46,8 @@ SYMBOLS = {
     'nha_decode_step': (C.c_int, [c_void_p] * 10 + [C.c_int64, C.c_int64, c_void_p, c_void_p, c_void_p, C.c_int,
                                                      c_void_p, c_void_p, c_void_p, C.c_int64] + [C.c_int] * 7
                         + [C.c_float, c_void_p]),
+    'nha_decode_step_bf16_state': (C.c_int, [c_void_p] * 10 + [C.c_int64, C.c_int64, c_void_p, c_void_p, C.c_int, c_void_p,
+                                                                c_void_p, C.c_int64] + [C.c_int] * 7 + [C.c_float, c_void_p]),
     'nha_decode_device_error': (C.c_int, [c_void_p, C.c_int, C.c_int, c_void_p]),
     'nha_decode_set_pdl': (C.c_int, [C.c_int]),
     'nha_decode_get_pdl': (C.c_int, []),

@@ -467,7 +467,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
                       cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
-                      const void* ring_kraw, const void* g_new);
+                      const void* ring_kraw, const void* g_new, int state_bf16);
 
 // Workspace: [B*H tickets | error word] (ints, zero between calls), then the (max, sum) and the partial outputs of
 // every split.  Sized for whichever kernel cuts a (sequence, kv head) into more splits.
@@ -504,11 +504,11 @@ extern "C" int nha_decode_device_error(const void* workspace, int B, int H, void
   return v;
 }
 
-extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g,
-                               const void* s, const void* sw_k, const void* sw_v, const void* cosp, const void* sinp,
-                               int64_t cs_batch, int64_t cs_row, const void* win_logits, float* hk, float* hv,
-                               int zero_state, void* o, float* win_prob, void* workspace, int64_t workspace_bytes,
-                               int B, int HQ, int H, int K, int V, int M, int W, float scale, void* stream) {
+static int decode_step_impl(const void* q, const void* sq, const void* k, const void* v, const void* g, const void* s,
+                            const void* sw_k, const void* sw_v, const void* cosp, const void* sinp, int64_t cs_batch,
+                            int64_t cs_row, const void* win_logits, float* hk, float* hv, int state_bf16, int zero_state,
+                            void* o, float* win_prob, void* workspace, int64_t workspace_bytes, int B, int HQ, int H, int K,
+                            int V, int M, int W, float scale, void* stream) {
   if (!q || !k || !v || !g || !hk || !hv || !o) return NHA_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || HQ <= 0 || HQ % H != 0 || W < 1) return NHA_ERR_BAD_ARG;
   const bool logits_mode = win_logits != nullptr;
@@ -530,6 +530,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   // common shapes take the streaming kernel (ring of bulk copies, whole grid resident in one wave)
   const char* force_general = getenv("NHA_B200_DECODE_GENERAL");
   const bool stream_ok = decode_stream_supported(K, V, M, W, NG, logits_mode) && !(force_general && force_general[0] == '1');
+  if (state_bf16 && !stream_ok) return NHA_ERR_UNSUPPORTED;      // bf16 slot memory: streaming kernel only
   a.SPLITS = stream_ok ? decode_stream_splits(B, H, W, M) : decode_splits(W, logits_mode);
   if (a.SPLITS > kMaxSplits) return NHA_ERR_UNSUPPORTED;
   if (logits_mode) {
@@ -557,7 +558,7 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   if (stream_ok)
     return decode_stream_try(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, hk, hv, zero_state, o, a.tickets,
                              errw, a.part_ml, a.part_o, a.SPLITS, B, HQ, H, K, M, W, scale, (cudaStream_t)stream, nullptr,
-                             nullptr, W, 0, nullptr, nullptr);
+                             nullptr, W, 0, nullptr, nullptr, state_bf16);
   const int smem = decode_layout(a);
   if (smem > kMaxSmem) return NHA_ERR_SMEM;
   cudaStream_t st = (cudaStream_t)stream;
@@ -574,6 +575,25 @@ extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, con
   else NHA_LAUNCH_DECODE(0, 0);
 #undef NHA_LAUNCH_DECODE
   return check_launch();
+}
+
+extern "C" int nha_decode_step(const void* q, const void* sq, const void* k, const void* v, const void* g,
+                               const void* s, const void* sw_k, const void* sw_v, const void* cosp, const void* sinp,
+                               int64_t cs_batch, int64_t cs_row, const void* win_logits, float* hk, float* hv,
+                               int zero_state, void* o, float* win_prob, void* workspace, int64_t workspace_bytes,
+                               int B, int HQ, int H, int K, int V, int M, int W, float scale, void* stream) {
+  return decode_step_impl(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, win_logits, hk, hv, 0, zero_state, o,
+                          win_prob, workspace, workspace_bytes, B, HQ, H, K, V, M, W, scale, stream);
+}
+
+extern "C" int nha_decode_step_bf16_state(const void* q, const void* sq, const void* k, const void* v, const void* g,
+                                          const void* s, const void* sw_k, const void* sw_v, const void* cosp,
+                                          const void* sinp, int64_t cs_batch, int64_t cs_row, void* hk, void* hv,
+                                          int zero_state, void* o, void* workspace, int64_t workspace_bytes, int B, int HQ,
+                                          int H, int K, int V, int M, int W, float scale, void* stream) {
+  if (((uintptr_t)hk & 15) || ((uintptr_t)hv & 15)) return NHA_ERR_BAD_ARG;
+  return decode_step_impl(q, sq, k, v, g, s, sw_k, sw_v, cosp, sinp, cs_batch, cs_row, nullptr, (float*)hk, (float*)hv, 1,
+                          zero_state, o, nullptr, workspace, workspace_bytes, B, HQ, H, K, V, M, W, scale, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -621,7 +641,7 @@ extern "C" int nha_decode_step_ring(const void* q, const void* k_new, const void
   float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop, nullptr, nullptr);
+                           ring_g, W, nopop, nullptr, nullptr, 0);
 }
 
 extern "C" int nha_decode_step_ring_fused(const void* q, const void* k_new, const void* v_new, const void* g_new, void* ring_k,
@@ -644,7 +664,7 @@ extern "C" int nha_decode_step_ring_fused(const void* q, const void* k_new, cons
   float* part_o = (float*)(base + align_up(B * H * splits * NG * 2 * 4, 256));
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_k, ring_v, cosp, sinp, cs_batch, cs_row, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop, nullptr, g_new);
+                           ring_g, W, nopop, nullptr, g_new, 0);
 }
 
 extern "C" int nha_ring_append(void* ring_k, void* ring_v, void* ring_g, const void* k_new, const void* v_new,
@@ -759,7 +779,7 @@ extern "C" int nha_decode_step_ring_rot(const void* q, const void* k_new, const 
   // token of this step
   return decode_stream_try(q, nullptr, k_new, v_new, nullptr, nullptr, ring_kr, ring_v, cos_q, sin_q, cs_batch, 0, hk, hv, 0,
                            o, tickets, errw, part_ml, part_o, splits, B, HQ, H, K, M, Weff, scale, (cudaStream_t)stream, head,
-                           ring_g, W, nopop, ring_k, nullptr);
+                           ring_g, W, nopop, ring_k, nullptr, 0);
 }
 
 extern "C" int nha_ring_append_rot(void* ring_k, void* ring_kr, void* ring_v, void* ring_g, const void* k_new,

@@ -66,6 +66,8 @@ struct DecodeStreamArgs {
   // (sequence, kv head) is finished by exactly one CTA, after all its splits have read the rings, so no other CTA
   // reads the index or the row that is overwritten.
   const bf16* g_new;
+  // state_bf16 != 0: hk and hv point to bf16 tensors (half the state bytes; arithmetic stays fp32 in registers)
+  int state_bf16;
   int64_t cs_batch, cs_row;
   int B, HQ, H, M, W, NG, SPLITS, KSPL, MQ, zero_state;
   int cluster;        // 1: the SPLITS CTAs of a (sequence, kv head) form a thread-block cluster and merge through shared memory
@@ -82,6 +84,19 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                    umma::smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(umma::smem_u32(mbar))
                : "memory");
+}
+// one element of the slot memory, fp32 or bf16 storage
+__device__ __forceinline__ float ld_state(const float* base, size_t idx, int is_bf16) {
+  return is_bf16 ? __bfloat162float(reinterpret_cast<const bf16*>(base)[idx]) : base[idx];
+}
+__device__ __forceinline__ void st_state(float* base, size_t idx, float& v, int is_bf16) {
+  if (is_bf16) {
+    const bf16 r = __float2bfloat16_rn(v);
+    reinterpret_cast<bf16*>(base)[idx] = r;
+    v = __bfloat162float(r);                 // the rounded value is the state from here on
+  } else {
+    base[idx] = v;
+  }
 }
 __device__ __forceinline__ void mbar_expect(uint64_t* mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(umma::smem_u32(mbar)), "r"(bytes) : "memory");
@@ -137,7 +152,7 @@ __device__ __forceinline__ void mma_1688(float (&c)[4], uint32_t a0, uint32_t a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
-template <int D>
+template <int D, bool SB16>
 __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const DecodeStreamArgs a) {
   using namespace nvcuda::wmma;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -261,14 +276,20 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   do {                                                                                              \
     if (!a.zero_state && nslots > 0) {                                                              \
       _Pragma("unroll") for (int j = 0; j < kRowsPer; ++j)                                          \
-        hreg[j] = lane < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane] : 0.f; \
+        hreg[j] = lane < nslots ? ld_state(a.hk, ((size_t)bh * K + kRowsPer * warp + j) * M + m0 + lane, SB16) : 0.f; \
     }                                                                                               \
   } while (0)
 #define NHA_LOAD_HV_ROWS()                                                                          \
   do {                                                                                              \
     if (nslots > 0 && !a.zero_state && tid == 0) {                                                  \
-      mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);                                      \
-      bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]);  \
+      if (SB16) {     /* bf16 rows land in the second half of their fp32 home */                \
+        mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 2);                                    \
+        bulk_g2s(reinterpret_cast<bf16*>(hvS) + (size_t)nslots * V,                                 \
+                 reinterpret_cast<const bf16*>(a.hv) + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 2, &bars[kStrSlots]); \
+      } else {                                                                                      \
+        mbar_expect(&bars[kStrSlots], (uint32_t)nslots * V * 4);                                    \
+        bulk_g2s(hvS, a.hv + ((size_t)bh * M + m0) * V, (uint32_t)nslots * V * 4, &bars[kStrSlots]); \
+      }                                                                                             \
     }                                                                                               \
   } while (0)
   // Dependent launch with early requests (pdl == 2): the state and the window of this call do not depend on the
@@ -390,7 +411,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     if (cb > 0 && !a.zero_state) {
 #pragma unroll
       for (int j = 0; j < kRowsPer; ++j)
-        hreg[j] = m < nslots ? a.hk[((size_t)bh * K + kRowsPer * warp + j) * M + m0 + m] : 0.f;
+        hreg[j] = m < nslots ? ld_state(a.hk, ((size_t)bh * K + kRowsPer * warp + j) * M + m0 + m, SB16) : 0.f;
     }
     const float e = m < MQ ? eg[m] : 1.f, sm = m < MQ ? sv[m] : 0.f;
     float hval[kRowsPer];
@@ -398,7 +419,7 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
     for (int j = 0; j < kRowsPer; ++j) {
       const int kk = kRowsPer * warp + j;
       hval[j] = (a.zero_state ? 0.f : hreg[j]) * e + kpop[kk] * sm;
-      if (m < nslots) a.hk[((size_t)bh * K + kk) * M + m0 + m] = hval[j];
+      if (m < nslots) st_state(a.hk, ((size_t)bh * K + kk) * M + m0 + m, hval[j], SB16);
     }
     // this warp's rows of every query head: 16-byte loads of the query (the same address for all lanes)
 #pragma unroll
@@ -505,8 +526,12 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
   if (nslots > 0) {
     if (!a.zero_state && !umma::mbar_wait(&bars[kStrSlots], 0)) failed = true;
     float4* hg = reinterpret_cast<float4*>(a.hv + ((size_t)bh * M + m0) * V);
-    // four elements per thread and round: all loads of a round before its stores
-    for (int i0 = tid; i0 < nslots * V4; i0 += 4 * kStrThreads) {
+    uint2* hg16 = reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.hv) + ((size_t)bh * M + m0) * V);
+    const uint2* stage16 = reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(hvS) + (size_t)nslots * V);
+    // four elements per thread and round: all loads of a round before its stores.  bf16 states: the rows were staged
+    // in the second half of the fp32 rows they are expanded into, so a block barrier separates a round's loads from its
+    // stores (round r writes the bytes [16 KB r, 16 KB (r + 1)), the staging of the later rounds lies behind them)
+    for (int i0 = tid; i0 - tid < nslots * V4; i0 += 4 * kStrThreads) {
       float4 hh[4], vp4[4];
       float e[4], sm[4];
 #pragma unroll
@@ -514,11 +539,21 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
         const int i = i0 + u * kStrThreads;
         if (i < nslots * V4) {
           const int m = i / V4, c = i - m * V4;
-          hh[u] = a.zero_state ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+          if (a.zero_state) {
+            hh[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else if (SB16) {
+            const uint2 raw = stage16[i];
+            const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            hh[u] = make_float4(lo2.x, lo2.y, hi2.x, hi2.y);
+          } else {
+            hh[u] = *reinterpret_cast<const float4*>(hvS + m * V + 4 * c);
+          }
           vp4[u] = *reinterpret_cast<const float4*>(vpop + 4 * c);
           e[u] = eg[m]; sm[u] = sv[m];
         }
       }
+      if (SB16) __syncthreads();
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * kStrThreads;
@@ -527,8 +562,19 @@ __global__ void __launch_bounds__(kStrThreads, 2) nha_decode_stream_kernel(const
           hh[u].y = hh[u].y * e[u] + sm[u] * vp4[u].y;
           hh[u].z = hh[u].z * e[u] + sm[u] * vp4[u].z;
           hh[u].w = hh[u].w * e[u] + sm[u] * vp4[u].w;
-          reinterpret_cast<float4*>(hvS)[i] = hh[u];
-          hg[i] = hh[u];
+          if (SB16) {
+            // the rounded value is the state from here on: the readout uses what the next step will read
+            uint2 pk;
+            *reinterpret_cast<__nv_bfloat162*>(&pk.x) = __floats2bfloat162_rn(hh[u].x, hh[u].y);
+            *reinterpret_cast<__nv_bfloat162*>(&pk.y) = __floats2bfloat162_rn(hh[u].z, hh[u].w);
+            hg16[i] = pk;
+            const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.x));
+            const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.y));
+            reinterpret_cast<float4*>(hvS)[i] = make_float4(lo2.x, lo2.y, hi2.x, hi2.y);
+          } else {
+            reinterpret_cast<float4*>(hvS)[i] = hh[u];
+            hg[i] = hh[u];
+          }
         }
       }
     }
@@ -863,7 +909,9 @@ int decode_stream_launch(const DecodeStreamArgs& in, int D, cudaStream_t st) {
   if (const char* nc = getenv("NHA_B200_DECODE_NO_CLUSTER")) {
     if (nc[0] == '1') a.cluster = 0;                 // merge through the workspace instead
   }
-  const void* fn = D == 128 ? (const void*)nha_decode_stream_kernel<128> : (const void*)nha_decode_stream_kernel<64>;
+  const void* fn = a.state_bf16 ? (D == 128 ? (const void*)nha_decode_stream_kernel<128, true> : (const void*)nha_decode_stream_kernel<64, true>)
+                                : (D == 128 ? (const void*)nha_decode_stream_kernel<128, false>
+                                            : (const void*)nha_decode_stream_kernel<64, false>);
   cudaError_t e = set_max_smem(fn, smem);
   if (e != cudaSuccess) return record_cuda_error(e);
   cudaLaunchConfig_t cfg;
@@ -901,7 +949,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
                       int64_t cs_row, float* hk, float* hv, int zero_state, void* o, int* tickets, int* err,
                       float* part_ml, float* part_o, int splits, int B, int HQ, int H, int D, int M, int W, float scale,
                       cudaStream_t st, const int* head, const void* ring_g, int ring_rows, int nopop,
-                      const void* ring_kraw, const void* g_new) {
+                      const void* ring_kraw, const void* g_new, int state_bf16) {
   DecodeStreamArgs a;
   a.q = (const bf16*)q; a.sq = (const bf16*)sq; a.k = (const bf16*)k; a.v = (const bf16*)v; a.g = (const bf16*)g;
   a.s = (const bf16*)s; a.sw_k = (const bf16*)sw_k; a.sw_v = (const bf16*)sw_v; a.cosp = (const bf16*)cosp;
@@ -912,6 +960,7 @@ int decode_stream_try(const void* q, const void* sq, const void* k, const void* 
   a.WR = head ? ring_rows : W; a.nopop = head ? nopop : 0;
   a.ring_kraw = head ? (const bf16*)ring_kraw : nullptr;
   a.g_new = (head && !ring_kraw) ? (const bf16*)g_new : nullptr;
+  a.state_bf16 = state_bf16;
   a.cs_batch = cs_batch; a.cs_row = cs_row;
   a.B = B; a.HQ = HQ; a.H = H; a.M = M; a.W = W; a.NG = HQ / H; a.SPLITS = splits;
   a.zero_state = zero_state; a.scale = scale;

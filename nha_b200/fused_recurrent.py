@@ -36,6 +36,14 @@ def _decode_workspace(device, B, HQ, H, V, W):
     return ws
 
 
+class _Bf16StateSwitch:
+    """Set while ``fused_recurrent_nha_decode_bf16_state`` runs: the decode op then keeps the slot memory in bf16."""
+    active = False
+
+
+_BF16_STATE = _Bf16StateSwitch()
+
+
 def _bf16c(x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if x is None:
         return None
@@ -44,19 +52,19 @@ def _bf16c(x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return x.contiguous()
 
 
-def _state(initial_state, B, H, K, V, M, device, output_final_state):
+def _state(initial_state, B, H, K, V, M, device, output_final_state, dtype=torch.float32):
     """Returns (hk, hv, zero_state).  The kernel updates the state buffers in place."""
     if initial_state is not None and initial_state != (None, None):
         hk0, hv0 = initial_state
         assert hk0.shape == (B, H, K, M) and hv0.shape == (B, H, M, V), \
             f"initial_state must be ([B,H,K,M], [B,H,M,V]) at the kv-head count {H}, got {tuple(hk0.shape)} / {tuple(hv0.shape)}"
-        inplace_ok = (output_final_state and hk0.dtype == torch.float32 and hv0.dtype == torch.float32
+        inplace_ok = (output_final_state and hk0.dtype == dtype and hv0.dtype == dtype
                       and hk0.is_contiguous() and hv0.is_contiguous())
         if inplace_ok:
             return hk0, hv0, 0
-        return hk0.float().contiguous().clone(), hv0.float().contiguous().clone(), 0
-    hk = torch.empty(B, H, K, M, dtype=torch.float32, device=device)
-    hv = torch.empty(B, H, M, V, dtype=torch.float32, device=device)
+        return hk0.to(dtype).contiguous().clone(), hv0.to(dtype).contiguous().clone(), 0
+    hk = torch.empty(B, H, K, M, dtype=dtype, device=device)
+    hv = torch.empty(B, H, M, V, dtype=dtype, device=device)
     return hk, hv, 1
 
 
@@ -142,23 +150,45 @@ def fused_recurrent_nha_decode(
     kf, vf, gf = _bf16c(k.reshape(B, H, K)), _bf16c(v.reshape(B, H, V)), _bf16c(g.reshape(B, H, M))
     sf = None if s is None else _bf16c(s.reshape(B, H, M))
     swk, swv = _bf16c(sw_k), _bf16c(sw_v)
-    hk, hv, zero = _state(initial_state, B, H, K, V, M, dev, output_final_state)
+    bf16_state = _BF16_STATE.active
+    hk, hv, zero = _state(initial_state, B, H, K, V, M, dev, output_final_state, _BF16 if bf16_state else torch.float32)
     o = torch.empty(B, HQ, V, dtype=_BF16, device=dev)
     lib = _lib.load()
     with torch.cuda.device(dev):
-        ws = _decode_workspace(dev, B, HQ, H, V, W) if W > 64 else None
-        st = lib.nha_decode_step(
-            _lib.ptr(qf), _lib.ptr(sqf), _lib.ptr(kf), _lib.ptr(vf), _lib.ptr(gf), _lib.ptr(sf),
-            _lib.ptr(swk), _lib.ptr(swv), _lib.ptr(cos if rotary else None), _lib.ptr(sin if rotary else None),
-            cs_batch, cs_row, None, _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o), None,
-            _lib.ptr(ws), 0 if ws is None else ws.numel(),
-            B, HQ, H, K, V, M, W, float(scale), _stream(dev))
+        ws = _decode_workspace(dev, B, HQ, H, V, W) if (W > 64 or bf16_state) else None
+        if bf16_state:
+            st = lib.nha_decode_step_bf16_state(
+                _lib.ptr(qf), _lib.ptr(sqf), _lib.ptr(kf), _lib.ptr(vf), _lib.ptr(gf), _lib.ptr(sf),
+                _lib.ptr(swk), _lib.ptr(swv), _lib.ptr(cos if rotary else None), _lib.ptr(sin if rotary else None),
+                cs_batch, cs_row, _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o),
+                _lib.ptr(ws), 0 if ws is None else ws.numel(),
+                B, HQ, H, K, V, M, W, float(scale), _stream(dev))
+        else:
+            st = lib.nha_decode_step(
+                _lib.ptr(qf), _lib.ptr(sqf), _lib.ptr(kf), _lib.ptr(vf), _lib.ptr(gf), _lib.ptr(sf),
+                _lib.ptr(swk), _lib.ptr(swv), _lib.ptr(cos if rotary else None), _lib.ptr(sin if rotary else None),
+                cs_batch, cs_row, None, _lib.ptr(hk), _lib.ptr(hv), zero, _lib.ptr(o), None,
+                _lib.ptr(ws), 0 if ws is None else ws.numel(),
+                B, HQ, H, K, V, M, W, float(scale), _stream(dev))
         _lib.check(st, 'nha_decode_step')
         _lib.check_decode_device(lib, ws, B, H, _stream(dev), 'nha_decode_step')
     o = o.view(B, 1, HQ, V)
     if out_dtype != _BF16:
         o = o.to(out_dtype)
     return o, ((hk, hv) if output_final_state else (None, None))
+
+
+@torch.compiler.disable
+def fused_recurrent_nha_decode_bf16_state(*args, **kwargs):
+    """``fused_recurrent_nha_decode`` with the slot memory kept in bf16: same arguments; ``initial_state`` tensors in
+    bf16 are updated in place (others are converted once), and the returned states are bf16.  Half the state bytes per
+    step.  An extension: the reference keeps fp32 states (nha_fla/ops/nha/fused_recurrent.py:536-545), so results follow
+    it to bf16 accuracy of the state only.  ``K == V`` in {64, 128} with window keys (the streaming kernel)."""
+    _BF16_STATE.active = True
+    try:
+        return fused_recurrent_nha_decode(*args, **kwargs)
+    finally:
+        _BF16_STATE.active = False
 
 
 @torch.compiler.disable

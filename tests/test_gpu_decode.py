@@ -199,6 +199,44 @@ def test_decode_with_a_2048_key_window(B):
     assert_close(hv, ref[2], 1e-5, 'hvt')
 
 
+@pytest.mark.parametrize('B,H,NG,K,M,W', [(3, 2, 4, 128, 64, 256), (32, 4, 8, 128, 64, 512), (2, 1, 1, 64, 64, 130),
+                                          (1, 1, 2, 64, 32, 64)])
+def test_decode_with_bf16_slot_memory(B, H, NG, K, M, W):
+    """The slot memory kept in bf16 (an extension; the reference keeps it in fp32): three steps in a row on the same
+    window with the state carried in bf16, against the oracle stepping in fp64 from the same bf16-rounded start state.
+    Outputs to the usual bar; states to bf16 rounding (one rounding per step and element)."""
+    from nha_b200 import fused_recurrent_nha_decode_bf16_state
+    d = gen.decode_inputs(700 + B, B, H, NG, K, K, M, W)
+    d['cos'], d['sin'] = gen.rope_tables(W, K, first_pos=900)
+    c = cuda(d)
+    hk = c['hk0'].bfloat16().contiguous()
+    hv = c['hv0'].bfloat16().contiguous()
+    rk, rv = hk.double().cpu(), hv.double().cpu()
+    for step in range(3):
+        ref = orc.decode_step(d['q'], d['k'], d['v'], d['g'], d['sw_k_raw'], d['vw'], d['scale'], cos=d['cos'],
+                              sin=d['sin'], hk0=rk, hv0=rv)
+        o, (hk2, hv2) = fused_recurrent_nha_decode_bf16_state(
+            q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'], cos=c['cos'], sin=c['sin'],
+            initial_state=(hk, hv), output_final_state=True)
+        assert hk2.dtype == torch.bfloat16 and hk2.data_ptr() == hk.data_ptr(), 'bf16 states are updated in place'
+        assert_close(o, ref[0], TOL_OUT, f'step {step} o')
+        assert_close(hk2, ref[1], 6e-3 * (step + 1), f'step {step} hkt')
+        assert_close(hv2, ref[2], 6e-3 * (step + 1), f'step {step} hvt')
+        rk, rv = ref[1], ref[2]
+
+
+def test_bf16_slot_memory_is_refused_without_the_streaming_kernel():
+    from nha_b200 import fused_recurrent_nha_decode_bf16_state
+    from nha_b200._lib import NHALibraryError
+    d = gen.decode_inputs(710, 1, 1, 1, 32, 32, 16, 16)                      # K = 32: general kernel only
+    d['cos'], d['sin'] = gen.rope_tables(16, 32, first_pos=0)
+    c = cuda(d)
+    with pytest.raises(NHALibraryError):
+        fused_recurrent_nha_decode_bf16_state(q=c['q'], k=c['k'], v=c['v'], g=c['g'], sw_k=c['sw_k_raw'], sw_v=c['vw'],
+                                              cos=c['cos'], sin=c['sin'], initial_state=(c['hk0'], c['hv0']),
+                                              output_final_state=True)
+
+
 @pytest.fixture
 def pdl_mode():
     """Sets the dependent-launch mode of the streaming decode kernel for a test and restores the default."""
