@@ -206,7 +206,7 @@ def bench_decode(lib, dev, rank, world, timed, peak):
     ws = torch.zeros(int(lib.nha_decode_workspace_bytes(B, H * NG, H, K, W)), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
 
-    def step():
+    def step(stream=stream):
         for d in layers:
             st = lib.nha_decode_step(d['q'].data_ptr(), None, d['k'].data_ptr(), d['v'].data_ptr(), d['g'].data_ptr(), None,
                                      d['sw_k'].data_ptr(), d['sw_v'].data_ptr(), cos.data_ptr(), sin.data_ptr(), 0,
@@ -223,6 +223,18 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             step()
         by_mode[mode] = timed(step, 200) / 200
     ms = by_mode[2]
+    # the same 48 launches captured once as a CUDA graph and replayed (the dependent-launch edges are kept by the capture)
+    graph_us = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(torch.cuda.current_stream(dev).cuda_stream)
+        for _ in range(3):
+            graph.replay()
+        graph_us = 1e3 * (timed(graph.replay, 200) / 200) / LAYERS
+        del graph
+    except Exception as e:                                       # noqa: BLE001 - reported, the eager figure stands
+        print(f'[bench] rank {rank}: decode graph capture failed: {e}', file=sys.stderr)
     per_seq_layer = H * (2 * (K * M + M * K) * 4 + 2 * W * K * 2) + (2 * H * NG * K + H * (2 * K + M)) * 2
     gbs = per_seq_layer * B * LAYERS / (ms * 1e-3) / 1e9
     # the slot memory kept in bf16 (an extension; the reference keeps fp32 states): half the state bytes per step
@@ -333,7 +345,8 @@ def bench_decode(lib, dev, rank, world, timed, peak):
             'dependent_launch': {'us_per_layer_plain': 1e3 * by_mode[0] / LAYERS,
                                  'us_per_layer_wait_first': 1e3 * by_mode[1] / LAYERS,
                                  'us_per_layer_early_requests': 1e3 * by_mode[2] / LAYERS,
-                                 'headline_mode': 'early requests (mode 2)'},
+                                 'us_per_layer_early_requests_cuda_graph': graph_us,
+                                 'headline_mode': 'early requests (mode 2), eager launches'},
             'roofline': {'bound': 'hbm', 'achieved': gbs, 'peak': peak, 'unit': 'GB/s', 'frac': gbs / peak,
                          'algorithmic_bytes_per_launch': per_seq_layer * B}, 'gpu_launches_per_step': LAYERS}
 

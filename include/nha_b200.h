@@ -249,6 +249,14 @@ int64_t nha_chunk_bwd_workspace_bytes(const nha_chunk_desc* d);
 int nha_chunk_plan(const nha_chunk_desc* d, void* stream);
 /* state pass: chunk-start states hk_chunks/hv_chunks (+ final states hkt/hvt when non-NULL) */
 int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream);
+/* The two halves of nha_chunk_state_pass, for callers that have part of their inputs early (the sequence-parallel
+   prefill starts on the chunks that read only its own rows while the rows of the rank before it are still on the wire):
+   nha_chunk_state_terms computes the per-chunk terms of the chunks [chunk_lo, chunk_lo + chunk_n) into desc->workspace
+   (chunk c reads the rows [64 c - shift, 64 c + 64 - shift) of its sequence's k_gsa, v, s, g); nha_chunk_state_scan,
+   once every chunk's terms are there, writes hk_chunks / hv_chunks and hkt / hvt.  Same workspace and plan as
+   nha_chunk_state_pass, which is terms over all chunks followed by the scan. */
+int nha_chunk_state_terms(const nha_chunk_desc* d, int chunk_lo, int chunk_n, void* stream);
+int nha_chunk_state_scan(const nha_chunk_desc* d, void* stream);
 /* Adds a start state to the result of a state pass that ran from a ZERO start (hk0 == hv0 == NULL) with this
    descriptor: the recurrence is linear, so the state at the start of chunk c is the zero-start state plus
    S .* exp(sum of the log gates of the chunks before c).  sk [N,H,K,M], sv [N,H,M,V] fp32.  Updates hk_chunks,

@@ -68,6 +68,8 @@ SYMBOLS = {
     'nha_chunk_bwd_workspace_bytes': (C.c_int64, [C.POINTER(ChunkDesc)]),
     'nha_chunk_plan': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
+    'nha_chunk_state_terms': (C.c_int, [C.POINTER(ChunkDesc), C.c_int, C.c_int, c_void_p]),
+    'nha_chunk_state_scan': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_output_pass': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_apply_state_prefix': (C.c_int, [C.POINTER(ChunkDesc), c_void_p, c_void_p, c_void_p]),
     'nha_chunk_gate_totals': (C.c_int, [C.POINTER(ChunkDesc), C.POINTER(c_void_p)]),

@@ -317,14 +317,44 @@ class SegmentForward:
         d.workspace_bytes = t['workspace'].numel()
         self.t, self.desc = t, d
 
+    def _halo_chunks(self):
+        """Chunks whose shifted rows ``[64 c - shift, 64 c + 64 - shift)`` touch the first ``q_offset`` kv rows."""
+        ncb, q_off, shift = self.geo.ncb, self.geo.q_offset, max(0, self.shift)
+        if q_off == 0:
+            return 0, 0
+        lo = max(0, (shift - 64) // 64 + 1)
+        hi = min(ncb, -(-(q_off + shift) // 64))
+        return min(lo, hi), hi
+
+    def start(self):
+        """Plan and the per-chunk terms of every chunk that does not read the first ``q_offset`` kv rows (the rows of
+        the rank before): callable while those rows are still arriving."""
+        lib, dev = _lib.load(), self.geo.device
+        lo, hi = self._halo_chunks()
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_chunk_plan(self.desc, _stream(dev)), 'nha_chunk_plan')
+            if lo > 0:
+                _lib.check(lib.nha_chunk_state_terms(self.desc, 0, lo, _stream(dev)), 'nha_chunk_state_terms')
+            _lib.check(lib.nha_chunk_state_terms(self.desc, hi, self.geo.ncb - hi, _stream(dev)), 'nha_chunk_state_terms')
+        self._started = True
+
     def summary(self):
-        """Plan + state pass from a zero start.  Returns the segment's message ``[1, H*K*M + H*M*V + H*M]`` fp32: its
-        zero-start end state and the total log decay of the tokens that entered the slot memory."""
+        """The rest of the state pass from a zero start (the terms of the chunks that read the first ``q_offset`` kv
+        rows, then the scan; all of it when :meth:`start` was not called).  Returns the segment's message
+        ``[1, H*K*M + H*M*V + H*M]`` fp32: its zero-start end state and the total log decay of the tokens that entered
+        the slot memory."""
         import ctypes
         lib, dev = _lib.load(), self.geo.device
         with torch.cuda.device(dev):
-            _lib.check(lib.nha_chunk_plan(self.desc, _stream(dev)), 'nha_chunk_plan')
-            _lib.check(lib.nha_chunk_state_pass(self.desc, _stream(dev)), 'nha_chunk_state_pass')
+            if getattr(self, '_started', False):
+                lo, hi = self._halo_chunks()
+                if hi > lo:
+                    _lib.check(lib.nha_chunk_state_terms(self.desc, lo, hi - lo, _stream(dev)), 'nha_chunk_state_terms')
+                _lib.check(lib.nha_chunk_state_scan(self.desc, _stream(dev)), 'nha_chunk_state_scan')
+                self._started = False
+            else:
+                _lib.check(lib.nha_chunk_plan(self.desc, _stream(dev)), 'nha_chunk_plan')
+                _lib.check(lib.nha_chunk_state_pass(self.desc, _stream(dev)), 'nha_chunk_state_pass')
         ptr = ctypes.c_void_p()
         _lib.check(lib.nha_chunk_gate_totals(self.desc, ctypes.byref(ptr)), 'nha_chunk_gate_totals')
         off = ptr.value - self.t['workspace'].data_ptr()

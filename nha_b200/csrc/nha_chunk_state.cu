@@ -23,7 +23,7 @@
 namespace nha {
 
 bool state_local_umma_supported(const nha_chunk_desc* d);
-int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err, cudaStream_t cs);
+int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err, int chunk_lo, int chunk_n, cudaStream_t cs);
 
 constexpr int kStThreads = 256;
 constexpr int kStWarps = kStThreads / 32;
@@ -102,8 +102,8 @@ __host__ __device__ inline StLocalLayout st_local_layout(int K, int V, int M) {
 }
 
 // One CTA per (chunk, kv head): L_k, L_v and Gend of that chunk.
-__global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_chunk_desc d, const StateWs w) {
-  const int cg = blockIdx.x, h = blockIdx.y;
+__global__ void __launch_bounds__(kStThreads) nha_state_local_kernel(const nha_chunk_desc d, const StateWs w, const int chunk_lo) {
+  const int cg = chunk_lo + blockIdx.x, h = blockIdx.y;
   const int NCB = gridDim.x;
   const ChunkRec rc = chunk_rec(d, cg);
   const int n = rc.n;
@@ -401,28 +401,37 @@ static void state_ws_layout(const nha_chunk_desc* d, void* scratch, StateWs* w) 
   w->gtot = w->gend + NCB * d->H * d->M;
 }
 
-// Both launches of the state pass on `scratch` (>= state_workspace_bytes(d) bytes, 16-byte aligned).
-// Every scratch element that the scan reads is written by the first kernel of the same call.
-static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs) {
+// Per-chunk terms of the chunks [chunk_lo, chunk_lo + chunk_n) on `scratch`: the tensor-core kernel where it has the
+// shape, else the wmma kernel.
+static int state_terms_on(const nha_chunk_desc* d, void* scratch, int chunk_lo, int chunk_n, cudaStream_t cs) {
   const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
-  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  if (chunk_lo < 0 || chunk_n < 0 || chunk_lo + chunk_n > NCB) return NHA_ERR_BAD_ARG;
+  if (chunk_n == 0) return NHA_OK;
   StateWs w;
   state_ws_layout(d, scratch, &w);
-  // per-chunk terms: the tensor-core kernel where it has the shape, else the wmma kernel
   int st = NHA_ERR_UNSUPPORTED;
   if (state_local_umma_supported(d)) {
     int* err = d->plan + d->N + 1 + NCB + (size_t)NCB * d->H;
-    st = state_local_umma_launch(d, w, err, cs);
+    st = state_local_umma_launch(d, w, err, chunk_lo, chunk_n, cs);
     if (st != NHA_OK && st != NHA_ERR_UNSUPPORTED) return st;
   }
   if (st == NHA_ERR_UNSUPPORTED) {
     const StLocalLayout L = st_local_layout(d->K, d->V, d->M);
     cudaError_t e = set_max_smem((const void*)nha_state_local_kernel, L.total);
     if (e != cudaSuccess) return record_cuda_error(e);
-    nha_state_local_kernel<<<dim3(NCB, d->H), kStThreads, L.total, cs>>>(*d, w);
+    nha_state_local_kernel<<<dim3(chunk_n, d->H), kStThreads, L.total, cs>>>(*d, w, chunk_lo);
     st = check_launch();
-    if (st != NHA_OK) return st;
   }
+  return st;
+}
+
+// The scan over the chunks on `scratch` (>= state_workspace_bytes(d) bytes, 16-byte aligned).  Every scratch element
+// that it reads has been written by state_terms_on with the same descriptor.
+static int state_scan_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs) {
+  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
+  const int64_t SD = (int64_t)d->K * d->M + (int64_t)d->M * d->V;
+  StateWs w;
+  state_ws_layout(d, scratch, &w);
   {
     // Ring depth and CTA width: the scan of one CTA is a serial walk over the sequence's chunks whose inputs take a
     // memory round trip to arrive, so its speed is (chunks in flight) / (round trip).  Few CTAs (one long sequence, few
@@ -449,6 +458,12 @@ static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs
     }
   }
   return check_launch();
+}
+
+// Both parts of the state pass.
+static int state_pass_on(const nha_chunk_desc* d, void* scratch, cudaStream_t cs) {
+  const int st = state_terms_on(d, scratch, 0, (int)nha_chunk_count_bound(d->Ttot, d->N), cs);
+  return st != NHA_OK ? st : state_scan_on(d, scratch, cs);
 }
 
 // Start state folded into the zero-start chunk states, in two chunk-parallel steps.
@@ -583,6 +598,23 @@ extern "C" int nha_chunk_state_pass(const nha_chunk_desc* d, void* stream) {
   const int64_t need = state_workspace_bytes(d);
   if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
   return state_pass_on(d, d->workspace, (cudaStream_t)stream);
+}
+
+extern "C" int nha_chunk_state_terms(const nha_chunk_desc* d, int chunk_lo, int chunk_n, void* stream) {
+  int st = check_chunk_desc(d);
+  if (st != NHA_OK) return st;
+  const int64_t need = state_workspace_bytes(d);
+  if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
+  return state_terms_on(d, d->workspace, chunk_lo, chunk_n, (cudaStream_t)stream);
+}
+
+extern "C" int nha_chunk_state_scan(const nha_chunk_desc* d, void* stream) {
+  int st = check_chunk_desc(d);
+  if (st != NHA_OK) return st;
+  if (!d->hk_chunks || !d->hv_chunks) return NHA_ERR_BAD_ARG;
+  const int64_t need = state_workspace_bytes(d);
+  if (!d->workspace || (int64_t)d->workspace_bytes < need) return NHA_ERR_WORKSPACE;
+  return state_scan_on(d, d->workspace, (cudaStream_t)stream);
 }
 
 extern "C" int nha_chunk_apply_state_prefix(const nha_chunk_desc* d, const float* sk, const float* sv, void* stream) {

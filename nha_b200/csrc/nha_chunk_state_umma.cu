@@ -43,12 +43,12 @@ struct StateMaps {
 
 template <int D>
 __global__ void __launch_bounds__(stu::kThreads) nha_state_local_umma_kernel(const nha_chunk_desc d, const StateWs w,
-                                                                             int* __restrict__ err,
+                                                                             int* __restrict__ err, const int chunk_lo,
                                                                              const __grid_constant__ StateMaps maps) {
   using namespace stu;
   constexpr int DT = D / 64;                      // 64-column tiles of k' and v'
   constexpr int M = 64;
-  const int cg = blockIdx.x, h = blockIdx.y;
+  const int cg = chunk_lo + blockIdx.x, h = blockIdx.y;
   const ChunkRec rc = chunk_rec(d, cg);
   if (rc.n < 0) return;
   const int H = d.H;
@@ -231,9 +231,8 @@ bool state_local_umma_supported(const nha_chunk_desc* d) {
 
 // Launches the tensor-core version of the per-chunk terms; NHA_ERR_UNSUPPORTED when the tensor maps cannot be made (the
 // caller then runs nha_state_local_kernel).
-int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err, cudaStream_t cs) {
+int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err, int chunk_lo, int chunk_n, cudaStream_t cs) {
   using namespace stu;
-  const int NCB = (int)nha_chunk_count_bound(d->Ttot, d->N);
   StateMaps maps;
   memset(&maps, 0, sizeof(maps));
   const bool ok = make_map_rows_heads(&maps.k, d->k_gsa, d->Ttot, d->H, d->K) &&
@@ -246,8 +245,8 @@ int state_local_umma_launch(const nha_chunk_desc* d, const StateWs& w, int* err,
   const void* fn = DT == 2 ? (const void*)nha_state_local_umma_kernel<128> : (const void*)nha_state_local_umma_kernel<64>;
   cudaError_t e = set_max_smem(fn, total);
   if (e != cudaSuccess) return record_cuda_error(e);
-  if (DT == 2) nha_state_local_umma_kernel<128><<<dim3(NCB, d->H), kThreads, total, cs>>>(*d, w, err, maps);
-  else nha_state_local_umma_kernel<64><<<dim3(NCB, d->H), kThreads, total, cs>>>(*d, w, err, maps);
+  if (DT == 2) nha_state_local_umma_kernel<128><<<dim3(chunk_n, d->H), kThreads, total, cs>>>(*d, w, err, chunk_lo, maps);
+  else nha_state_local_umma_kernel<64><<<dim3(chunk_n, d->H), kThreads, total, cs>>>(*d, w, err, chunk_lo, maps);
   return check_launch();
 }
 

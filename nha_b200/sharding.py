@@ -54,6 +54,12 @@ class CudaEngine:
             f = lambda x: x[0].to(_BF16).contiguous()
             self.steps = SegmentForward(f(q), f(rq), f(k_e), f(rk_e), f(v_e), f(s_e), f(g_e), scale, W - 1, W, q_offset)
 
+    def start(self):
+        """What can run before the halo has arrived: the per-chunk state terms of the chunks that read only this rank's
+        own rows."""
+        if self.steps is not None:
+            self.steps.start()
+
     def summary(self):
         """``[B, H*K*M + H*M*V + H*M]`` fp32: zero-start end state of the (halo-extended) segment and the total log
         decay of the tokens that enter its slot memory."""
@@ -123,6 +129,7 @@ def sequence_parallel_prefill(
     scale: Optional[float] = None,
     group: Optional[dist.ProcessGroup] = None,
     engine=CudaEngine,
+    halo_room=None,
 ):
     """``fused_chunk_nha_prefill`` over a sequence sharded along tokens.
 
@@ -131,6 +138,10 @@ def sequence_parallel_prefill(
     tokens long), plus on every rank the same ``initial_state`` of the whole sequence (or None).
     Returns ``(o [B,Tr,HQ,V], (hk, hv))`` where the state is the slot memory at the END of this
     rank's segment (the last rank holds the final state of the sequence).
+
+    ``halo_room`` (one sequence, ranks > 0): five tensors ``[1, W + Tr, H, *]`` whose rows ``W:`` ARE the ``k,
+    rotary_k, v, s, g`` passed (views of them); the halo is then received into their first ``W`` rows and nothing is
+    copied.
     """
     W = int(window_size)
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -142,13 +153,16 @@ def sequence_parallel_prefill(
 
     # ---- 1. halo of W tokens from the left neighbour (kv-head tensors only) ---------------------------
     # The extended tensors are allocated first and the halo is received straight into their first W rows (contiguous
-    # for one sequence), while this rank's own rows are copied behind them.
+    # for one sequence), while this rank's own rows are copied behind them - or nothing is copied at all when the caller
+    # keeps its kv tensors in buffers with W free rows in front (halo_room).
     own = (k, rotary_k, v, s, g)
     send = [x[:, Tr - W:].contiguous() for x in own]
     q_offset = W if rank > 0 else 0
     direct = rank > 0 and B == 1
+    ext = None
     if direct:
-        ext = [torch.empty(B, Tr + W, *x.shape[2:], dtype=x.dtype, device=dev) for x in own]
+        ext = halo_room if halo_room is not None else \
+            [torch.empty(B, Tr + W, *x.shape[2:], dtype=x.dtype, device=dev) for x in own]
         recv = [e[:, :W] for e in ext]
     else:
         recv = [torch.empty_like(x) for x in send]
@@ -159,20 +173,23 @@ def sequence_parallel_prefill(
     if rank > 0:
         ops += [dist.P2POp(dist.irecv, x, peer(rank - 1), group) for x in recv]
     works = dist.batch_isend_irecv(ops) if ops else []
-    if direct:
+    if direct and halo_room is None:
         for e, x in zip(ext, own):
             e[:, W:].copy_(x)
+    eng = None
+    if direct or rank == 0:
+        # ---- 2a. everything that does not need the halo runs while it is on the wire --------------------------
+        k_e, rk_e, v_e, s_e, g_e = ext if direct else own
+        eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
+        if hasattr(eng, 'start'):
+            eng.start()
     for w in works:
         w.wait()
-    if rank == 0:
-        k_e, rk_e, v_e, s_e, g_e = own
-    elif direct:
-        k_e, rk_e, v_e, s_e, g_e = ext
-    else:
+    if eng is None:
         k_e, rk_e, v_e, s_e, g_e = (torch.cat([h_, x], 1) for h_, x in zip(recv, own))
+        eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
 
-    # ---- 2. segment summary from a zero start --------------------------------------------------------------
-    eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
+    # ---- 2b. segment summary from a zero start ------------------------------------------------------------
     pack = eng.summary()
 
     # ---- 3. all-gather of the summaries ------------------------------------------------------------------------
@@ -189,16 +206,30 @@ class GraphedPrefill:
     its halo messages and the all-gather - and replayed per call.  A call then costs the host one graph launch instead of
     some sixty launches, copies and NCCL calls; from eight ranks on that host work is longer than the rank's kernels.
 
-    The tensors passed to the constructor ARE the graph's inputs: write the next segment into them in place, call the
-    object, read ``(o, (hk, hv))`` (the same output tensors every call).  Every rank of the group must construct the
-    object and call it the same number of times (the graph contains collectives), and must drop it before the process
-    group is destroyed (``destroy_process_group`` waits for ever on a communicator that a live graph still uses).  The constructor runs the eager function
-    ``warmup`` times first (communicators and kernel attributes are set up outside the capture)."""
+    The graph's inputs are the attributes ``q, rotary_q`` (the tensors passed to the constructor) and ``k, rotary_k, v, s,
+    g``: for one sequence these are views of buffers that keep ``window_size`` free rows in front for the halo of the
+    rank before (initialised from the tensors passed in), so that nothing is copied per call.  Write the next segment
+    into them in place, call the object, read ``(o, (hk, hv))`` (the same output tensors every call).  Every rank of the
+    group must construct the object and call it the same number of times (the graph contains collectives), and must
+    drop it before the process group is destroyed (``destroy_process_group`` waits for ever on a communicator that a
+    live graph still uses).  The constructor runs the eager function ``warmup`` times first (communicators and kernel
+    attributes are set up outside the capture)."""
 
     def __init__(self, q, k, v, rotary_q, rotary_k, s, g, window_size, initial_state=None, scale=None, group=None,
                  warmup: int = 2):
-        run = lambda: sequence_parallel_prefill(q, k, v, rotary_q, rotary_k, s, g, window_size, initial_state=initial_state,
-                                                scale=scale, group=group)
+        W = int(window_size)
+        self.q, self.rotary_q = q, rotary_q
+        room = None
+        if k.shape[0] == 1 and dist.get_rank(group) > 0:
+            room = []
+            for x in (k, rotary_k, v, s, g):
+                e = torch.empty(1, W + x.shape[1], *x.shape[2:], dtype=x.dtype, device=x.device)
+                e[:, W:].copy_(x)
+                room.append(e)
+            k, rotary_k, v, s, g = (e[:, W:] for e in room)
+        self.k, self.rotary_k, self.v, self.s, self.g = k, rotary_k, v, s, g
+        run = lambda: sequence_parallel_prefill(q, k, v, rotary_q, rotary_k, s, g, W, initial_state=initial_state,
+                                                scale=scale, group=group, halo_room=room)
         cur = torch.cuda.current_stream(k.device)
         side = torch.cuda.Stream(k.device)
         side.wait_stream(cur)

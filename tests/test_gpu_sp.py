@@ -72,8 +72,9 @@ def _graph_worker(rank, world, port, out):
                 static = {n: c[n][:, a:b].contiguous() for n in names}
                 graphed = GraphedPrefill(*(static[n] for n in names), W)
             else:
+                # the graph's inputs: q and rotary_q as passed, the kv-head tensors as the object holds them
                 for n in names:
-                    static[n].copy_(c[n][:, a:b])
+                    getattr(graphed, n).copy_(c[n][:, a:b])
             o, (hk, hv) = graphed()
             torch.cuda.synchronize()
             err = orc.rel_l2(o.float().cpu(), ref_o[:, a:b].float().cpu())

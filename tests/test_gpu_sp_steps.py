@@ -43,6 +43,13 @@ def test_emulated_ranks_match_the_single_call(K, M, NG, W, T, world, with_state)
         if K == 128:
             assert eng.steps is not None, 'the long-context shape must take the three-step path'
         engines.append(eng)
+        if r % 2 == 1:
+            # the early start (per-chunk terms of the chunks that do not read the halo rows) followed by the rest must
+            # give the same message as the state pass in one go
+            want = eng.summary().clone()
+            eng.start()
+            got = eng.summary().clone()
+            assert torch.equal(got, want), 'split state pass differs from the one-call state pass'
         packs.append(eng.summary().clone())
     allp = torch.stack(packs, 0)                       # [world, B, P], as the all-gather leaves it
     outs = []
