@@ -277,6 +277,22 @@ int nha_chunk_gate_totals(const nha_chunk_desc* d, const float** out);
    no distributed code. */
 int nha_sp_fold_start_state(const float* allp, int world, int rank, int H, int K, int M, int V, const float* hk0,
                             const float* hv0, float* sk, float* sv, void* stream);
+
+/* The same exchange without a collective library: summaries travel over peer memory (NVLink) and the fold waits for
+ * exactly the ranks it consumes.  Symmetric mailboxes, allocated by the caller so that every rank can address every
+ * other rank's copy: box float [depth][world][P] and flag uint32 [depth][world] (zero before the first call) on every
+ * rank, P = H*K*M + H*M*V + H*M; box_ptrs / flag_ptrs: DEVICE arrays of `world` pointers to the ranks' copies;
+ * ctr: two zero-initialised uint32 in this rank's own memory; depth >= world + 1.
+ *   nha_sp_publish: stores this rank's summary `pack [P]` into the mailboxes of the ranks after it and raises their
+ *     flags; advances ctr[0].  Every rank calls it once per prefill, the last rank too.
+ *   nha_sp_fold_wait: after nha_sp_publish on the same stream; waits (bounded: about a second, then *err_word = 1 and
+ *     the outputs are invalid) for the summaries of the ranks before this one in this rank's own mailbox
+ *     (box, flag: this rank's copies) and writes the start state sk [1,H,K,M], sv [1,H,M,V] like
+ *     nha_sp_fold_start_state.  Both launches may be captured in a CUDA graph. */
+int nha_sp_publish(const float* pack, int64_t P, float* const* box_ptrs, uint32_t* const* flag_ptrs, uint32_t* ctr, int world,
+                   int rank, int depth, void* stream);
+int nha_sp_fold_wait(const float* box, const uint32_t* flag, const uint32_t* ctr, int world, int rank, int depth, int H, int K,
+                     int M, int V, const float* hk0, const float* hv0, float* sk, float* sv, int* err_word, void* stream);
 /* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
 int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
 /* device-side error word of the last output pass run with this descriptor's plan (0 = none; non-zero:

@@ -74,6 +74,8 @@ SYMBOLS = {
     'nha_chunk_apply_state_prefix': (C.c_int, [C.POINTER(ChunkDesc), c_void_p, c_void_p, c_void_p]),
     'nha_chunk_gate_totals': (C.c_int, [C.POINTER(ChunkDesc), C.POINTER(c_void_p)]),
     'nha_sp_fold_start_state': (C.c_int, [c_void_p] + [C.c_int] * 6 + [c_void_p] * 5),
+    'nha_sp_publish': (C.c_int, [c_void_p, C.c_int64, c_void_p, c_void_p, c_void_p, C.c_int, C.c_int, C.c_int, c_void_p]),
+    'nha_sp_fold_wait': (C.c_int, [c_void_p, c_void_p, c_void_p] + [C.c_int] * 7 + [c_void_p] * 6),
     'nha_chunk_fwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass_static_max_bytes': (C.c_int64, []),

@@ -377,6 +377,22 @@ class SegmentForward:
                        'nha_sp_fold_start_state')
         return sk, sv
 
+    def fold_from_mailbox(self, box, rank: int, initial_state=None):
+        """Start state of rank ``rank`` from the peer-memory mailbox ``box`` (a ``sharding.PeerMailbox`` whose
+        ``publish`` ran on this stream for this call): one launch that waits for the ranks before this one."""
+        lib, dev, g = _lib.load(), self.geo.device, self.geo
+        sk = torch.empty(1, g.H, g.K, g.M, dtype=torch.float32, device=dev)
+        sv = torch.empty(1, g.H, g.M, g.V, dtype=torch.float32, device=dev)
+        hk0 = hv0 = None
+        if initial_state is not None and initial_state != (None, None):
+            hk0, hv0 = initial_state[0].float().contiguous(), initial_state[1].float().contiguous()
+        err = g.plan.data_ptr() + 4 * (g.N + 1 + g.ncb + g.ncb * g.H)          # the plan's device error word
+        with torch.cuda.device(dev):
+            _lib.check(lib.nha_sp_fold_wait(box.box.data_ptr(), box.flag.data_ptr(), box.ctr.data_ptr(), box.world, rank,
+                                            box.depth, g.H, g.K, g.M, g.V, _lib.ptr(hk0), _lib.ptr(hv0), sk.data_ptr(),
+                                            sv.data_ptr(), err, _stream(dev)), 'nha_sp_fold_wait')
+        return sk, sv
+
     def apply_prefix(self, sk: torch.Tensor, sv: torch.Tensor):
         """Fold the true start state ``sk [1,H,K,M], sv [1,H,M,V]`` (fp32) into every chunk-start state and the end state."""
         lib, dev = _lib.load(), self.geo.device

@@ -37,6 +37,65 @@ import torch.distributed as dist
 _BF16 = torch.bfloat16
 
 
+class PeerMailbox:
+    """Symmetric mailboxes for the segment summaries: every rank holds ``box [depth, world, P]`` floats and ``flag
+    [depth, world]`` words that every other rank of the group can address over NVLink (``torch.distributed``'s symmetric
+    memory supplies the allocation and the peer pointers; the stores, flags and waits are this package's kernels,
+    ``nha_sp_publish`` / ``nha_sp_fold_wait``).  One object per (group, message size); made by the first eager call of
+    :func:`sequence_parallel_prefill` (a collective: all ranks create it together), never inside a graph capture."""
+
+    _cache = {}
+
+    def __init__(self, P: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.depth, self.P = self.world + 1, int(P)
+        pg = group if group is not None else dist.group.WORLD
+        try:                                             # older releases want the group registered first
+            import warnings
+            with warnings.catch_warnings():
+                warnings.simplefilter('ignore')
+                symm.enable_symm_mem_for_group(pg.group_name)
+        except Exception:                                # noqa: BLE001
+            pass
+        self.box = symm.empty(self.depth * self.world * self.P, dtype=torch.float32, device=device)
+        self.flag = symm.empty(self.depth * self.world, dtype=torch.int32, device=device)
+        self.box.zero_()
+        self.flag.zero_()
+        self._hb = symm.rendezvous(self.box, pg.group_name)
+        self._hf = symm.rendezvous(self.flag, pg.group_name)
+        self.box_ptrs, self.flag_ptrs = int(self._hb.buffer_ptrs_dev), int(self._hf.buffer_ptrs_dev)
+        self.ctr = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                              # every rank's flags are zero before anybody publishes
+
+    @classmethod
+    def get(cls, P: int, device, group=None):
+        """The mailbox of this (group, message size, device), or None when peer memory cannot be set up here (the
+        exchange then goes through the collective library).  Collective on first use."""
+        import os
+        if os.environ.get('NHA_B200_SP_NCCL') == '1' or device.type != 'cuda' or torch.cuda.is_current_stream_capturing():
+            return None
+        key = (id(group), int(P), device.index)
+        if key not in cls._cache:
+            try:
+                box = cls(P, device, group)
+            except Exception:                            # noqa: BLE001 - no peer access / no symmetric memory: NCCL path
+                box = None
+            ok = torch.tensor([1 if box is not None else 0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)           # every rank takes the same path
+            cls._cache[key] = box if int(ok.item()) == 1 else None
+        return cls._cache[key]
+
+    def publish(self, pack: torch.Tensor):
+        from . import _lib
+        lib = _lib.load()
+        with torch.cuda.device(pack.device):
+            _lib.check(lib.nha_sp_publish(pack.data_ptr(), self.P, self.box_ptrs, self.flag_ptrs, self.ctr.data_ptr(), self.world,
+                                          self.rank, self.depth, torch.cuda.current_stream(pack.device).cuda_stream),
+                       'nha_sp_publish')
+
+
 class CudaEngine:
     """Default arithmetic of :func:`sequence_parallel_prefill` on this rank's GPU: ``summary()`` gives the rank's message
     to the others, ``finish()`` turns everybody's messages into this rank's outputs."""
@@ -73,11 +132,15 @@ class CudaEngine:
         Lk, Lv = chunk_final_state(flat(k_e), flat(v_e), flat(s_e), flat(g_e), cu, T, W)
         return pack_summary(Lk, Lv, g_e, W)
 
-    def finish(self, allp, rank, initial_state=None):
-        """Outputs of the rank's own tokens and the slot memory at the end of its segment, from ``allp [world, B, P]``."""
+    def finish(self, allp, rank, initial_state=None, mailbox=None):
+        """Outputs of the rank's own tokens and the slot memory at the end of its segment, from ``allp [world, B, P]`` or,
+        with ``mailbox`` (the three-step path only), from the summaries the other ranks put there."""
         q, rq, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset = self.args
         if self.steps is not None:
-            Sk, Sv = self.steps.fold(allp[:, 0], rank, initial_state)
+            if mailbox is not None:
+                Sk, Sv = self.steps.fold_from_mailbox(mailbox, rank, initial_state)
+            else:
+                Sk, Sv = self.steps.fold(allp[:, 0], rank, initial_state)
             self.steps.apply_prefix(Sk, Sv)
             o, _, _, hk, hv = self.steps.output_pass()
             return o[None].to(q.dtype), hk, hv
@@ -89,6 +152,15 @@ class CudaEngine:
         o, (hk, hv) = fused_chunk_nha_prefill(q=q, k=k_e, v=v_e, rotary_q=rq, rotary_k=rk_e, s=s_e, g=g_e, window_size=W,
                                               initial_state=(Sk, Sv), output_final_state=True, scale=scale)
         return o[:, q_offset:], hk, hv
+
+
+def _mailbox_for(pack: torch.Tensor, group):
+    """The peer-memory mailbox for messages like ``pack``.  Inside a graph capture only a mailbox made earlier (by an
+    eager call with the same group and message size) can be used."""
+    key = (id(group), int(pack.shape[1]), pack.device.index)
+    if torch.cuda.is_current_stream_capturing():
+        return PeerMailbox._cache.get(key)
+    return PeerMailbox.get(pack.shape[1], pack.device, group)
 
 
 def pack_summary(Lk, Lv, g_e: torch.Tensor, W: int):
@@ -192,7 +264,16 @@ def sequence_parallel_prefill(
     # ---- 2b. segment summary from a zero start ------------------------------------------------------------
     pack = eng.summary()
 
-    # ---- 3. all-gather of the summaries ------------------------------------------------------------------------
+    # ---- 3. exchange of the summaries: over peer memory where the engine and the system allow it (each rank stores its
+    #         summary into the mailboxes of the ranks after it; the fold kernel waits for the ranks before it), else one
+    #         all-gather ------------------------------------------------------------------------------------------
+    mailbox = None
+    if getattr(eng, 'steps', None) is not None and B == 1:
+        mailbox = _mailbox_for(pack, group)
+    if mailbox is not None:
+        mailbox.publish(pack)
+        o, hk, hv = eng.finish(None, rank, initial_state, mailbox=mailbox)
+        return o, (hk, hv)
     allp = torch.empty(world * B, pack.shape[1], dtype=pack.dtype, device=dev)
     dist.all_gather_into_tensor(allp, pack, group=group)
 
