@@ -69,6 +69,11 @@ class PeerMailbox:
         torch.cuda.synchronize(device)
         dist.barrier(group)                              # every rank's flags are zero before anybody publishes
 
+    @staticmethod
+    def key(P: int, device, group=None):
+        pg = group if group is not None else dist.group.WORLD
+        return (pg.group_name, int(P), device.index)
+
     @classmethod
     def get(cls, P: int, device, group=None):
         """The mailbox of this (group, message size, device), or None when peer memory cannot be set up here (the
@@ -76,7 +81,7 @@ class PeerMailbox:
         import os
         if os.environ.get('NHA_B200_SP_NCCL') == '1' or device.type != 'cuda' or torch.cuda.is_current_stream_capturing():
             return None
-        key = (id(group), int(P), device.index)
+        key = cls.key(P, device, group)
         if key not in cls._cache:
             try:
                 box = cls(P, device, group)
@@ -157,9 +162,8 @@ class CudaEngine:
 def _mailbox_for(pack: torch.Tensor, group):
     """The peer-memory mailbox for messages like ``pack``.  Inside a graph capture only a mailbox made earlier (by an
     eager call with the same group and message size) can be used."""
-    key = (id(group), int(pack.shape[1]), pack.device.index)
     if torch.cuda.is_current_stream_capturing():
-        return PeerMailbox._cache.get(key)
+        return PeerMailbox._cache.get(PeerMailbox.key(pack.shape[1], pack.device, group))
     return PeerMailbox.get(pack.shape[1], pack.device, group)
 
 
