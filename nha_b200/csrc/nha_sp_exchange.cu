@@ -50,9 +50,10 @@ __global__ void __launch_bounds__(kPubThreads) nha_sp_publish_kernel(const float
   __threadfence_system();                                // this thread's stores are visible to the receivers ...
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();                              // (cumulative: what the CTA's threads fenced, this thread orders too)
     const unsigned t = atomicAdd(ctr + 1, 1u);           // ... before its CTA is counted
     if (t == gridDim.x - 1) {
-      __threadfence();
+      __threadfence_system();                            // every CTA has been counted: all their stores precede the flags
       ctr[1] = 0u;
       for (int p = rank + 1; p < world; ++p) st_release_sys(flag_ptrs[p] + slot * world + rank, epoch);
       *(volatile uint32_t*)ctr = epoch;
@@ -86,6 +87,7 @@ __global__ void __launch_bounds__(256) nha_sp_fold_wait_kernel(const float* __re
     if (threadIdx.x == 0 && err) atomicExch(err, 1);
     return;
   }
+  __threadfence_system();                                // the waiting threads' acquires, passed on by the barrier, order every thread's reads
   const float* allp = box + (size_t)slot * world * ((size_t)H * K * M + (size_t)H * M * V + (size_t)H * M);
   const int nk = H * K * M, nv = H * M * V, P = nk + nv + H * M;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
