@@ -50,3 +50,34 @@ def test_ops_raise_when_the_device_word_is_set(monkeypatch):
     geo.plan[word] = 1
     with pytest.raises(_lib.NHALibraryError):
         _lib.check_chunk_device(lib, ctypes.byref(desc), stream, 'marked')
+
+
+def test_the_fold_of_the_peer_exchange_gives_up_on_a_summary_that_never_arrives():
+    """nha_sp_fold_wait on a mailbox whose flag nothing raises (the rank before 'never publishes'): the wait is bounded,
+    the kernel sets the error word and returns, the context stays usable; with the flag raised the same call folds the
+    summary in the mailbox.  One GPU, no peer involved: the mailbox is ordinary device memory here."""
+    from nha_b200 import _lib
+    lib = _lib.load()
+    H, K, M, V, world, depth, rank = 1, 16, 16, 16, 2, 3, 1
+    nk, nv = H * K * M, H * M * V
+    P = nk + nv + H * M
+    box = torch.zeros(depth, world, P, device='cuda')
+    flag = torch.zeros(depth, world, dtype=torch.int32, device='cuda')
+    ctr = torch.tensor([1, 0], dtype=torch.int32, device='cuda')             # call number 1 -> slot 1
+    sk, sv = torch.full((1, H, K, M), 7.0, device='cuda'), torch.full((1, H, M, V), 7.0, device='cuda')
+    err = torch.zeros(1, dtype=torch.int32, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda: lib.nha_sp_fold_wait(box.data_ptr(), flag.data_ptr(), ctr.data_ptr(), world, rank, depth, H, K, M, V, None,
+                                        None, sk.data_ptr(), sv.data_ptr(), err.data_ptr(), stream)
+    assert call() == 0
+    torch.cuda.synchronize()
+    assert int(err.item()) == 1 and float(sk.min().item()) == 7.0, 'the wait must run out and leave the outputs alone'
+    assert float((torch.ones(4, device='cuda') * 2).sum().item()) == 8.0      # the context is still usable
+    # the summary of rank 0 arrives: end state 2.0 everywhere, log decay 0
+    err.zero_()
+    box[1, 0, :nk + nv] = 2.0
+    flag[1, 0] = 1
+    assert call() == 0
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert torch.equal(sk, torch.full_like(sk, 2.0)) and torch.equal(sv, torch.full_like(sv, 2.0))
