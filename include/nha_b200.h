@@ -293,6 +293,23 @@ int nha_sp_publish(const float* pack, int64_t P, float* const* box_ptrs, uint32_
                    int rank, int depth, void* stream);
 int nha_sp_fold_wait(const float* box, const uint32_t* flag, const uint32_t* ctr, int world, int rank, int depth, int H, int K,
                      int M, int V, const float* hk0, const float* hv0, float* sk, float* sv, int* err_word, void* stream);
+
+/* The halo of the sequence-parallel prefill over peer memory (instead of a send / receive pair of a collective library):
+ * a rank stores the last rows of its kv-head tensors straight into the first rows of the next rank's halo-extended
+ * tensors, which therefore live in buffers that the sender can address (symmetric allocations).
+ *   nha_sp_halo_push (sender): waits (bounded) until the receiver has acknowledged the halo before this one
+ *     (ack_local, a word in this rank's memory written by the receiver), copies `count` (<= 5) byte ranges src[i] ->
+ *     dst_peer[i] (host arrays of device pointers; 16-byte aligned, sizes multiples of 16) and raises the receiver's
+ *     flag (flag_peer).  ctr: two zero-initialised uint32 of this rank (halos pushed, ticket).
+ *   nha_sp_halo_wait (receiver): before the first kernel that reads the halo rows; waits (bounded) for its flag
+ *     (flag_local).  ctr: one zero-initialised uint32 of this rank (halos received).
+ *   nha_sp_halo_ack (receiver): after the last kernel that reads the halo rows; writes the count of halos received into
+ *     the sender's ack word (ack_peer).
+ * A wait that runs out (about a second) sets *err_word and the kernel returns.  All three may be captured in a graph. */
+int nha_sp_halo_push(const void* const* src, void* const* dst_peer, const int64_t* bytes, int count, uint32_t* flag_peer,
+                     const uint32_t* ack_local, uint32_t* ctr, int* err_word, void* stream);
+int nha_sp_halo_wait(const uint32_t* flag_local, uint32_t* ctr, int* err_word, void* stream);
+int nha_sp_halo_ack(uint32_t* ack_peer, const uint32_t* ctr, void* stream);
 /* output pass: o, lse_swa, lse_gsa from the inputs and the chunk-start states */
 int nha_chunk_output_pass(const nha_chunk_desc* d, void* stream);
 /* device-side error word of the last output pass run with this descriptor's plan (0 = none; non-zero:

@@ -76,6 +76,9 @@ SYMBOLS = {
     'nha_sp_fold_start_state': (C.c_int, [c_void_p] + [C.c_int] * 6 + [c_void_p] * 5),
     'nha_sp_publish': (C.c_int, [c_void_p, C.c_int64, c_void_p, c_void_p, c_void_p, C.c_int, C.c_int, C.c_int, c_void_p]),
     'nha_sp_fold_wait': (C.c_int, [c_void_p, c_void_p, c_void_p] + [C.c_int] * 7 + [c_void_p] * 6),
+    'nha_sp_halo_push': (C.c_int, [c_void_p, c_void_p, c_void_p, C.c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'nha_sp_halo_wait': (C.c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    'nha_sp_halo_ack': (C.c_int, [c_void_p, c_void_p, c_void_p]),
     'nha_chunk_fwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_bwd': (C.c_int, [C.POINTER(ChunkDesc), c_void_p]),
     'nha_chunk_state_pass_static_max_bytes': (C.c_int64, []),

@@ -48,7 +48,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError('nha_b200: nvcc not found and libnha_b200.so is missing or stale; '
                            'there is no fallback implementation')
     objs = []
-    tmp = os.path.join(HERE, 'build')
+    # objects and the linked library under names of this process: several ranks that find the library stale at the same
+    # time each build their own and the last rename wins, instead of linking each other's half-written objects
+    tmp = os.path.join(HERE, 'build', f'p{os.getpid()}')
     os.makedirs(tmp, exist_ok=True)
     procs = []
     for src in sources():
@@ -65,11 +67,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f'nvcc failed on {src}:\n{out}')
-    link = [nvcc, '-shared', '-cudart', 'static', '-gencode', 'arch=compute_100a,code=sm_100a', '-o', LIB + '.tmp'] + objs
+    out = f'{LIB}.{os.getpid()}.tmp'
+    link = [nvcc, '-shared', '-cudart', 'static', '-gencode', 'arch=compute_100a,code=sm_100a', '-o', out] + objs
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f'link failed:\n{r.stdout}')
-    os.replace(LIB + '.tmp', LIB)
+    os.replace(out, LIB)
+    shutil.rmtree(tmp, ignore_errors=True)
     return LIB
 
 

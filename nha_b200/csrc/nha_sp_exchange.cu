@@ -104,9 +104,104 @@ __global__ void __launch_bounds__(256) nha_sp_fold_wait_kernel(const float* __re
   (is_k ? sk : sv)[e] = run;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The halo of a sequence-parallel prefill over peer memory: a rank stores the last W rows of its kv-head tensors
+// straight into the first W rows of the next rank's (halo-extended) tensors.  One-sided, so both directions are
+// flagged: the receiver raises `ack` once it has finished reading the halo of call e (after its output pass), and the
+// sender's call e + 1 waits for that before it overwrites the rows; the sender raises `flag` once the rows of call e
+// are there, and the receiver's first kernel that reads them is preceded by a wait for it.  Calls are counted on both
+// sides by device counters (every rank makes the same sequence of calls), so nothing is reset and all three kernels
+// can sit in a CUDA graph.  Every wait is bounded (about a second, then the error word is set and the kernel returns).
+struct HaloCopies {
+  const uint4* src[5];
+  uint4* dst[5];
+  int64_t nvec[5];
+};
+
+__device__ __forceinline__ bool wait_word_at_least(const uint32_t* p, uint32_t want) {
+  for (int it = 0; it < (1 << 22); ++it) {
+    if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
+    __nanosleep(200);
+  }
+  return false;
+}
+
+// ctr[0]: halos pushed so far; ctr[1]: arrival ticket of the CTAs of the running call
+__global__ void __launch_bounds__(kPubThreads) nha_sp_halo_push_kernel(const HaloCopies c, uint32_t* flag_peer,
+                                                                       const uint32_t* ack_local, uint32_t* ctr, int* err) {
+  const uint32_t epoch = *(volatile uint32_t*)ctr + 1u;
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = wait_word_at_least(ack_local, epoch - 1u) ? 0 : 1;   // the halo before this one was consumed
+  __syncthreads();
+  if (!s_bad) {
+    __threadfence_system();
+#pragma unroll 1
+    for (int t = 0; t < 5; ++t)
+      for (int64_t i = (int64_t)blockIdx.x * kPubThreads + threadIdx.x; i < c.nvec[t]; i += (int64_t)gridDim.x * kPubThreads)
+        c.dst[t][i] = c.src[t][i];
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_bad && err) atomicExch(err, 1);
+    __threadfence_system();
+    const unsigned t = atomicAdd(ctr + 1, 1u);
+    if (t == gridDim.x - 1) {
+      __threadfence_system();
+      ctr[1] = 0u;
+      st_release_sys(flag_peer, epoch);                  // raised even after a failed wait: the receiver must not hang too
+      *(volatile uint32_t*)ctr = epoch;
+    }
+  }
+}
+
+// receiver: ctr[0] counts the halos received
+__global__ void nha_sp_halo_wait_kernel(const uint32_t* flag_local, uint32_t* ctr, int* err) {
+  const uint32_t epoch = *(volatile uint32_t*)ctr + 1u;
+  if (!wait_word_at_least(flag_local, epoch) && err) atomicExch(err, 1);
+  __threadfence_system();
+  *(volatile uint32_t*)ctr = epoch;
+}
+
+// receiver, after the last kernel that reads the halo rows: tells the sender that they may be overwritten
+__global__ void nha_sp_halo_ack_kernel(uint32_t* ack_peer, const uint32_t* ctr) {
+  st_release_sys(ack_peer, *(volatile const uint32_t*)ctr);
+}
+
 }  // namespace nha
 
 using namespace nha;
+
+extern "C" int nha_sp_halo_push(const void* const* src, void* const* dst_peer, const int64_t* bytes, int count,
+                                uint32_t* flag_peer, const uint32_t* ack_local, uint32_t* ctr, int* err_word, void* stream) {
+  if (!src || !dst_peer || !bytes || count < 1 || count > 5 || !flag_peer || !ack_local || !ctr) return NHA_ERR_BAD_ARG;
+  HaloCopies c;
+  int64_t most = 0;
+  for (int t = 0; t < 5; ++t) {
+    c.src[t] = nullptr; c.dst[t] = nullptr; c.nvec[t] = 0;
+    if (t >= count) continue;
+    if (!src[t] || !dst_peer[t] || bytes[t] < 0 || bytes[t] % 16 || ((uintptr_t)src[t] & 15) || ((uintptr_t)dst_peer[t] & 15))
+      return NHA_ERR_BAD_ARG;
+    c.src[t] = (const uint4*)src[t]; c.dst[t] = (uint4*)dst_peer[t]; c.nvec[t] = bytes[t] / 16;
+    most = most > c.nvec[t] ? most : c.nvec[t];
+  }
+  int grid = (int)((most + kPubThreads - 1) / kPubThreads);
+  grid = grid < 1 ? 1 : (grid > 128 ? 128 : grid);
+  nha_sp_halo_push_kernel<<<grid, kPubThreads, 0, (cudaStream_t)stream>>>(c, flag_peer, ack_local, ctr, err_word);
+  return check_launch();
+}
+
+extern "C" int nha_sp_halo_wait(const uint32_t* flag_local, uint32_t* ctr, int* err_word, void* stream) {
+  if (!flag_local || !ctr) return NHA_ERR_BAD_ARG;
+  nha_sp_halo_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag_local, ctr, err_word);
+  return check_launch();
+}
+
+extern "C" int nha_sp_halo_ack(uint32_t* ack_peer, const uint32_t* ctr, void* stream) {
+  if (!ack_peer || !ctr) return NHA_ERR_BAD_ARG;
+  nha_sp_halo_ack_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ack_peer, ctr);
+  return check_launch();
+}
 
 extern "C" int nha_sp_publish(const float* pack, int64_t P, float* const* box_ptrs, uint32_t* const* flag_ptrs, uint32_t* ctr,
                               int world, int rank, int depth, void* stream) {

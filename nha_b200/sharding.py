@@ -101,6 +101,67 @@ class PeerMailbox:
                        'nha_sp_publish')
 
 
+class PeerHalo:
+    """Halo-extended kv tensors in symmetric memory, so that the rank before can store its last window straight into
+    their first ``W`` rows (``nha_sp_halo_push`` / ``_wait`` / ``_ack``): for callers that keep their kv inputs in
+    these buffers, i.e. :class:`GraphedPrefill`.  Construction is a collective of the group."""
+
+    def __init__(self, own, W: int, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        pg = group if group is not None else dist.group.WORLD
+        dev = own[0].device
+        self.W, self.Tr = int(W), own[0].shape[1]
+        self.ext, handles = [], []
+        for x in own:
+            e = symm.empty((self.W + self.Tr) * x[0, 0].numel(), dtype=x.dtype, device=dev)
+            handles.append(symm.rendezvous(e, pg.group_name))
+            e = e.view(1, self.W + self.Tr, *x.shape[2:])
+            e[:, self.W:].copy_(x)
+            self.ext.append(e)
+        self.flags = symm.empty(4, dtype=torch.int32, device=dev)            # [0] data flag, [1] acknowledgement
+        self.flags.zero_()
+        hf = symm.rendezvous(self.flags, pg.group_name)
+        self._handles = handles + [hf]
+        self.ctr_push = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.ctr_recv = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.side = torch.cuda.Stream(dev)
+        nxt, prv = self.rank + 1, self.rank - 1
+        rows = [self.W * x[0, 0].numel() * x.element_size() for x in own]     # bytes of W rows
+        if nxt < self.world:
+            self._src = (ctypes.c_void_p * 5)(*[e[:, self.Tr:].data_ptr() for e in self.ext])
+            self._dst = (ctypes.c_void_p * 5)(*[int(h.buffer_ptrs[nxt]) for h in handles])
+            self._bytes = (ctypes.c_int64 * 5)(*rows)
+            self._flag_peer = int(hf.buffer_ptrs[nxt])
+        if prv >= 0:
+            self._ack_peer = int(hf.buffer_ptrs[prv]) + 4
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)                              # every rank's flags are zero before anybody pushes
+
+    def _st(self):
+        return torch.cuda.current_stream(self.flags.device).cuda_stream
+
+    def push(self):
+        from . import _lib
+        with torch.cuda.device(self.flags.device):
+            _lib.check(_lib.load().nha_sp_halo_push(self._src, self._dst, self._bytes, 5, self._flag_peer,
+                                                    self.flags.data_ptr() + 4, self.ctr_push.data_ptr(), self.err.data_ptr(),
+                                                    self._st()), 'nha_sp_halo_push')
+
+    def wait(self):
+        from . import _lib
+        with torch.cuda.device(self.flags.device):
+            _lib.check(_lib.load().nha_sp_halo_wait(self.flags.data_ptr(), self.ctr_recv.data_ptr(), self.err.data_ptr(),
+                                                    self._st()), 'nha_sp_halo_wait')
+
+    def ack(self):
+        from . import _lib
+        with torch.cuda.device(self.flags.device):
+            _lib.check(_lib.load().nha_sp_halo_ack(self._ack_peer, self.ctr_recv.data_ptr(), self._st()), 'nha_sp_halo_ack')
+
+
 class CudaEngine:
     """Default arithmetic of :func:`sequence_parallel_prefill` on this rank's GPU: ``summary()`` gives the rank's message
     to the others, ``finish()`` turns everybody's messages into this rank's outputs."""
@@ -167,6 +228,17 @@ def _mailbox_for(pack: torch.Tensor, group):
     return PeerMailbox.get(pack.shape[1], pack.device, group)
 
 
+def _halo_done(halo_peer, rank, world, dev):
+    """End of a call that used a :class:`PeerHalo`: the receiver tells the sender that the halo rows have been read for
+    the last time, the sender's store stream joins the caller's."""
+    if halo_peer is None:
+        return
+    if rank > 0:
+        halo_peer.ack()
+    if rank + 1 < world:
+        torch.cuda.current_stream(dev).wait_stream(halo_peer.side)
+
+
 def pack_summary(Lk, Lv, g_e: torch.Tensor, W: int):
     """One rank's message to the others from its zero-start end state and its gates: the total log decay of the tokens
     that enter its slot memory is all of the halo-extended segment but its last ``W`` rows, summed from the gates as the
@@ -206,6 +278,7 @@ def sequence_parallel_prefill(
     group: Optional[dist.ProcessGroup] = None,
     engine=CudaEngine,
     halo_room=None,
+    halo_peer=None,
 ):
     """``fused_chunk_nha_prefill`` over a sequence sharded along tokens.
 
@@ -217,7 +290,8 @@ def sequence_parallel_prefill(
 
     ``halo_room`` (one sequence, ranks > 0): five tensors ``[1, W + Tr, H, *]`` whose rows ``W:`` ARE the ``k,
     rotary_k, v, s, g`` passed (views of them); the halo is then received into their first ``W`` rows and nothing is
-    copied.
+    copied.  ``halo_peer``: a :class:`PeerHalo` whose ``ext`` tensors are ``halo_room``: the halo then travels over peer
+    memory (a store kernel on the sender, a flag wait on the receiver) instead of a send / receive pair.
     """
     W = int(window_size)
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -232,7 +306,7 @@ def sequence_parallel_prefill(
     # for one sequence), while this rank's own rows are copied behind them - or nothing is copied at all when the caller
     # keeps its kv tensors in buffers with W free rows in front (halo_room).
     own = (k, rotary_k, v, s, g)
-    send = [x[:, Tr - W:].contiguous() for x in own]
+    send = [x[:, Tr - W:].contiguous() for x in own] if halo_peer is None else []
     q_offset = W if rank > 0 else 0
     direct = rank > 0 and B == 1
     ext = None
@@ -241,13 +315,23 @@ def sequence_parallel_prefill(
             [torch.empty(B, Tr + W, *x.shape[2:], dtype=x.dtype, device=dev) for x in own]
         recv = [e[:, :W] for e in ext]
     else:
-        recv = [torch.empty_like(x) for x in send]
+        recv = [torch.empty_like(x[:, Tr - W:]) for x in own]
     ops = []
     peer = lambda r: dist.get_global_rank(group, r) if group else r
-    if rank + 1 < world:
-        ops += [dist.P2POp(dist.isend, x, peer(rank + 1), group) for x in send]
-    if rank > 0:
-        ops += [dist.P2POp(dist.irecv, x, peer(rank - 1), group) for x in recv]
+    if halo_peer is not None:
+        assert B == 1 and (rank == 0 or halo_room is not None)
+        if rank + 1 < world:
+            # on a stream of its own: the store kernel first waits for the receiver's acknowledgement of the call before,
+            # and this rank's kernels need not wait with it (joined at the end of the call)
+            cur = torch.cuda.current_stream(dev)
+            halo_peer.side.wait_stream(cur)
+            with torch.cuda.stream(halo_peer.side):
+                halo_peer.push()                         # the last W rows of this rank's kv tensors into the next rank's
+    else:
+        if rank + 1 < world:
+            ops += [dist.P2POp(dist.isend, x, peer(rank + 1), group) for x in send]
+        if rank > 0:
+            ops += [dist.P2POp(dist.irecv, x, peer(rank - 1), group) for x in recv]
     works = dist.batch_isend_irecv(ops) if ops else []
     if direct and halo_room is None:
         for e, x in zip(ext, own):
@@ -261,6 +345,8 @@ def sequence_parallel_prefill(
             eng.start()
     for w in works:
         w.wait()
+    if halo_peer is not None and rank > 0:
+        halo_peer.wait()
     if eng is None:
         k_e, rk_e, v_e, s_e, g_e = (torch.cat([h_, x], 1) for h_, x in zip(recv, own))
         eng = engine(q, rotary_q, k_e, rk_e, v_e, s_e, g_e, W, scale, q_offset)
@@ -277,12 +363,14 @@ def sequence_parallel_prefill(
     if mailbox is not None:
         mailbox.publish(pack)
         o, hk, hv = eng.finish(None, rank, initial_state, mailbox=mailbox)
+        _halo_done(halo_peer, rank, world, dev)
         return o, (hk, hv)
     allp = torch.empty(world * B, pack.shape[1], dtype=pack.dtype, device=dev)
     dist.all_gather_into_tensor(allp, pack, group=group)
 
     # ---- 4. fold the ranks before this one, outputs of the rank's own tokens from its true start state ------------
     o, hk, hv = eng.finish(allp.view(world, B, -1), rank, initial_state)
+    _halo_done(halo_peer, rank, world, dev)
     return o, (hk, hv)
 
 
@@ -302,19 +390,38 @@ class GraphedPrefill:
 
     def __init__(self, q, k, v, rotary_q, rotary_k, s, g, window_size, initial_state=None, scale=None, group=None,
                  warmup: int = 2):
+        import os
         W = int(window_size)
         self.q, self.rotary_q = q, rotary_q
-        room = None
-        if k.shape[0] == 1 and dist.get_rank(group) > 0:
-            room = []
-            for x in (k, rotary_k, v, s, g):
-                e = torch.empty(1, W + x.shape[1], *x.shape[2:], dtype=x.dtype, device=x.device)
-                e[:, W:].copy_(x)
-                room.append(e)
-            k, rotary_k, v, s, g = (e[:, W:] for e in room)
+        room, halo = None, None
+        rank = dist.get_rank(group)
+        if k.shape[0] == 1 and dist.get_world_size(group) > 1:
+            # kv inputs in buffers with W free rows in front; in symmetric memory where the system has it, so that the
+            # halo is a store by the rank before instead of a send / receive pair (every rank takes the same path)
+            if os.environ.get('NHA_B200_SP_NCCL') != '1':
+                try:
+                    halo = PeerHalo((k, rotary_k, v, s, g), W, group)
+                except Exception:                        # noqa: BLE001 - no symmetric memory here
+                    halo = None
+                ok = torch.tensor([1 if halo is not None else 0], device=k.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+                if int(ok.item()) != 1:
+                    halo = None
+            if halo is not None:
+                room = halo.ext
+            elif rank > 0:
+                room = []
+                for x in (k, rotary_k, v, s, g):
+                    e = torch.empty(1, W + x.shape[1], *x.shape[2:], dtype=x.dtype, device=x.device)
+                    e[:, W:].copy_(x)
+                    room.append(e)
+            if room is not None:
+                k, rotary_k, v, s, g = (e[:, W:] for e in room)
         self.k, self.rotary_k, self.v, self.s, self.g = k, rotary_k, v, s, g
+        self.halo = halo
         run = lambda: sequence_parallel_prefill(q, k, v, rotary_q, rotary_k, s, g, W, initial_state=initial_state,
-                                                scale=scale, group=group, halo_room=room)
+                                                scale=scale, group=group, halo_room=room if rank > 0 else None,
+                                                halo_peer=halo)
         cur = torch.cuda.current_stream(k.device)
         side = torch.cuda.Stream(k.device)
         side.wait_stream(cur)
@@ -329,4 +436,9 @@ class GraphedPrefill:
 
     def __call__(self):
         self.graph.replay()
+        if self.halo is not None:
+            from . import _lib
+            if _lib.check_device_words() and int(self.halo.err.item()) != 0:
+                raise _lib.NHALibraryError('sequence-parallel prefill: a bounded wait of the peer-memory halo ran out; the '
+                                           'outputs of this call are invalid')
         return self.out
