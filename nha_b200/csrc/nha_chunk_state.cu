@@ -8,7 +8,9 @@
 // chunk only, so a chunk-parallel kernel produces them with two 64-deep matrix products per
 // (chunk, kv head), and what remains of the march is an element-wise scan over the chunks that stores
 // the state at every chunk start (bf16, the operand type of the later matrix products) and the fp32
-// final state.  Every exponent is <= 0, so no reference point is needed.
+// final state.  Every exponent is <= 0, so no reference point is needed.  The chunk-parallel kernel of this file
+// (nha_state_local_kernel, wmma) serves every shape; K == V in {64, 128} with M == 64 takes the tensor-core version in
+// nha_chunk_state_umma.cu.  The scan streams the per-chunk terms through a ring of bulk copies (nha_tma.cuh).
 //
 // Replaces chunk_nha_fused_state_kernel (nha_fla/ops/nha/chunk_fused.py:31-114) and the state part of
 // fla's chunk_gsa_fwd reached from nha_fla/ops/nha/chunk_gsa.py:38-45; the in-sequence shift replaces
