@@ -40,6 +40,10 @@ __global__ void __launch_bounds__(kPubThreads) nha_sp_publish_kernel(const float
                                                                      uint32_t* const* flag_ptrs, uint32_t* ctr, int world,
                                                                      int rank, int depth) {
   const uint32_t epoch = *(volatile uint32_t*)ctr + 1u;
+  if (rank + 1 >= world) {                               // the last rank has nobody to tell: it only counts the call
+    if (blockIdx.x == 0 && threadIdx.x == 0) *(volatile uint32_t*)ctr = epoch;
+    return;
+  }
   const int slot = (int)(epoch % (uint32_t)depth);
   const int nvec = P >> 2;                               // P is a multiple of 4 (K, V, M are multiples of 16)
   const float4* src = reinterpret_cast<const float4*>(pack);
@@ -87,7 +91,8 @@ __global__ void __launch_bounds__(256) nha_sp_fold_wait_kernel(const float* __re
     if (threadIdx.x == 0 && err) atomicExch(err, 1);
     return;
   }
-  __threadfence_system();                                // the waiting threads' acquires, passed on by the barrier, order every thread's reads
+  // (the waiting threads' acquire loads, passed on by the barrier above, order the reads of every thread of the CTA;
+  // the reads below bypass L1, which may still hold lines of an earlier call's slot)
   const float* allp = box + (size_t)slot * world * ((size_t)H * K * M + (size_t)H * M * V + (size_t)H * M);
   const int nk = H * K * M, nv = H * M * V, P = nk + nv + H * M;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -208,9 +213,11 @@ extern "C" int nha_sp_publish(const float* pack, int64_t P, float* const* box_pt
   if (!pack || !box_ptrs || !flag_ptrs || !ctr || P <= 0 || P % 4 || world < 1 || rank < 0 || rank >= world || depth < 2)
     return NHA_ERR_BAD_ARG;
   if (((uintptr_t)pack & 15)) return NHA_ERR_BAD_ARG;
-  const int grid = (int)((P / 4 + kPubThreads - 1) / kPubThreads);
-  nha_sp_publish_kernel<<<grid < 64 ? grid : 64, kPubThreads, 0, (cudaStream_t)stream>>>(pack, (int)P, box_ptrs, flag_ptrs, ctr,
-                                                                                        world, rank, depth);
+  // enough CTAs to keep the peer links busy (one 16-byte store per thread and receiver); one for the last rank
+  int grid = (int)((P / 4 + kPubThreads - 1) / kPubThreads);
+  grid = rank + 1 >= world ? 1 : (grid > 296 ? 296 : grid);
+  nha_sp_publish_kernel<<<grid, kPubThreads, 0, (cudaStream_t)stream>>>(pack, (int)P, box_ptrs, flag_ptrs, ctr, world, rank,
+                                                                        depth);
   return check_launch();
 }
 
