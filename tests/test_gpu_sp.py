@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 def _worker(rank, world, port, out):
     import faulthandler
     import torch.distributed as dist
-    faulthandler.dump_traceback_later(120, exit=True)        # a rank that waits for a lost peer reports where and leaves
+    faulthandler.dump_traceback_later(240, exit=True)        # a rank that waits for a lost peer reports where and leaves
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     os.environ['NCCL_NVLS_ENABLE'] = '0'
@@ -46,7 +46,7 @@ def _graph_worker(rank, world, port, out):
     """The captured form at the shape the pipelined kernels serve: two different inputs through one graph."""
     import faulthandler
     import torch.distributed as dist
-    faulthandler.dump_traceback_later(120, exit=True)        # a rank that waits for a lost peer reports where and leaves
+    faulthandler.dump_traceback_later(240, exit=True)        # a rank that waits for a lost peer reports where and leaves
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     os.environ['NCCL_NVLS_ENABLE'] = '0'
